@@ -1,0 +1,114 @@
+/* b200q — C ABI of the B200 (sm_100a) low-precision linear path.
+ *
+ * One shared library, plain pointers and sizes.  Every entry point
+ *   - returns an int status (0 = ok, < 0 = B200Q_ERR_*), never throws, aborts or traps;
+ *   - is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy stream);
+ *   - works on buffers the caller owns, on the current device;
+ *   - allocates nothing.
+ *
+ * The path these replace is the quantized-linear path of gongyisheng/pretrain, which is
+ * Python calling torch library kernels; each entry names the reference lines it stands for.
+ * All matrices are row-major.  "Contraction dimension" = the dimension the GEMM sums over;
+ * quantization scales always run along it (src/quant/fp8.py:52-54).
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  B200Q_OK = 0,
+  B200Q_ERR_INVALID_ARG = -1,   /* null pointer, negative size, unknown enum value */
+  B200Q_ERR_SHAPE = -2,         /* size not a multiple the kernel needs (see each entry) */
+  B200Q_ERR_ALIGNMENT = -3,     /* pointer or pitch not 16-byte aligned */
+  B200Q_ERR_CUDA = -4,          /* a CUDA runtime / driver call failed (b200q_last_cuda_error) */
+  B200Q_ERR_NOT_SM100 = -5,     /* current device is not compute capability 10.x */
+  B200Q_ERR_DEVICE_TIMEOUT = -6 /* a bounded device-side wait gave up (b200q_device_status) */
+};
+
+enum { B200Q_E4M3 = 0, B200Q_E5M2 = 1 };
+enum { B200Q_SF_NATURAL = 0, B200Q_SF_SWIZZLE_128x4 = 1 };
+
+const char* b200q_status_string(int status);
+/* cudaError_t of the last failing CUDA call made by this library on this thread (0 if none). */
+int b200q_last_cuda_error(void);
+/* Reads (synchronously) and clears the device-side status word that kernels set when a
+ * bounded wait expires: 0 = clean.  Returns B200Q_ERR_DEVICE_TIMEOUT if it was set. */
+int b200q_device_status(void);
+
+/* Bytes of a scale-factor buffer for `outer` rows and `nblk` blocks per row. */
+int64_t b200q_sf_bytes(int64_t outer, int64_t nblk, int sf_layout);
+
+/* ---- quantizers -------------------------------------------------------------------------
+ * x is bf16 [rows, cols] with row pitch `ld` elements (ld % 8 == 0, base 16-byte aligned).
+ * axis = 1: scales run along the columns (each row is quantized on its own); codes come out
+ *           as [rows, cols].
+ * axis = 0: scales run along the rows (per column); codes come out TRANSPOSED as
+ *           [cols, rows], so that the contraction dimension is contiguous for the GEMM.
+ */
+
+/* max |x| over the whole matrix -> *amax (fp32, device).  The call zeroes *amax first.
+ * Stands for `x.abs().max()` of quantize_fp8(dim=None), src/quant/fp8.py:26-27. */
+int b200q_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, float* amax, void* stream);
+
+/* quantize_fp8(x, dtype, dim) of src/quant/fp8.py:16-32 with dim=-1 (axis=1) or dim=0
+ * (axis=0): scale = max(amax/qmax, 1e-12), codes = cast(clamp(x/scale)).  `scales` is fp32,
+ * one per row (axis=1) or per column (axis=0).  cols % 8 == 0; for axis=0 rows % 16 == 0. */
+int b200q_quantize_fp8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int fmt,
+                       void* codes, float* scales, void* stream);
+
+/* quantize_fp8(x, dtype, dim=None): one scale for the tensor from *tensor_amax (device,
+ * e.g. from b200q_amax); writes it to *scale_out (device).  transpose != 0 writes codes
+ * as [cols, rows]. */
+int b200q_quantize_fp8_tensorwise(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose,
+                                  int fmt, const float* tensor_amax, void* codes, float* scale_out,
+                                  void* stream);
+
+/* MXFP8: 32-element blocks along the contraction dimension, fp8 codes, one E8M0 byte per
+ * block (2^e = smallest power of two >= max(amax/qmax, 1e-12)).  No counterpart in the
+ * reference yet (TODO at src/quant/__init__.py:26); extends src/quant/fp8.py:16-32.
+ * Contraction length % 32 == 0.  `sf` holds b200q_sf_bytes(outer, C/32, sf_layout) bytes;
+ * pad bytes of the swizzled layout are written as zero. */
+int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int fmt,
+                         void* codes, void* sf, int sf_layout, void* stream);
+
+/* NVFP4: 16-element blocks, packed E2M1 codes (element 2i in the low nibble), one E4M3 scale
+ * byte per block and one fp32 scale per tensor derived from *tensor_amax (device):
+ * s_t = max(amax/2688, 1e-12), written to *tensor_scale_out.  No counterpart in the reference
+ * yet (TODOs at src/quant/__init__.py:20,30).  Contraction length % 32 == 0. */
+int b200q_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis,
+                         const float* tensor_amax, void* codes, void* sf, int sf_layout,
+                         float* tensor_scale_out, void* stream);
+
+/* ---- GEMMs: D[M,N] (bf16, pitch ldd) = A[M,K] . B[N,K]^T, fp32 accumulation -------------
+ * Both operands have the contraction dimension contiguous ("K-major"), pitch = K codes.
+ * Scale-factor buffers are in B200Q_SF_SWIZZLE_128x4 layout.  N % 8 == 0, ldd % 8 == 0.
+ */
+
+/* Stands for torch._scaled_mm at src/quant/fp8.py:59-65.  scale_a: per row of A (M values)
+ * or one value (a_scale_is_scalar); scale_b: per row of B (N values) or one value.
+ * K % 16 == 0. */
+int b200q_gemm_fp8(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a,
+                   int a_scale_is_scalar, const float* scale_b, int b_scale_is_scalar, int64_t M,
+                   int64_t N, int64_t K, void* D, int64_t ldd, void* stream);
+
+/* Block-scaled MXFP8 GEMM (the `_gemm` seam, src/quant/linear.py:27-56, for MX formats).
+ * K % 32 == 0. */
+int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
+                     const void* sfB, int64_t M, int64_t N, int64_t K, void* D, int64_t ldd,
+                     void* stream);
+
+/* Block-scaled NVFP4 GEMM; D is multiplied by (*tsA) * (*tsB) (device fp32).  K % 32 == 0;
+ * A and B hold K/2 bytes per row. */
+int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* sfB,
+                     const float* tsA, const float* tsB, int64_t M, int64_t N, int64_t K, void* D,
+                     int64_t ldd, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,58 @@
+"""ctypes binding of libb200q.so (declared in include/b200q.h).
+
+There is no fallback: if the library is missing or a call fails, a RuntimeError is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "_lib", "libb200q.so")
+
+_i64, _int, _vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+
+# name -> (restype, argtypes); mirrors include/b200q.h one to one
+SIGNATURES = {
+    "b200q_status_string": (ctypes.c_char_p, [_int]),
+    "b200q_last_cuda_error": (_int, []),
+    "b200q_device_status": (_int, []),
+    "b200q_sf_bytes": (_i64, [_i64, _i64, _int]),
+    "b200q_amax": (_int, [_vp, _i64, _i64, _i64, _vp, _vp]),
+    "b200q_quantize_fp8": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]),
+    "b200q_quantize_fp8_tensorwise": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp, _vp]),
+    "b200q_quantize_mxfp8": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _int, _vp]),
+    "b200q_quantize_nvfp4": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp, _vp]),
+    "b200q_gemm_fp8": (_int, [_vp, _int, _vp, _int, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "b200q_gemm_mxfp8": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "b200q_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+}
+DEBUG_SIGNATURES = {
+    "b200q_debug_set_gemm_bn": (_int, [_int]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m pretrain_b200.build` "
+                "(there is no CPU or PyTorch fallback for this path)")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in {**SIGNATURES, **DEBUG_SIGNATURES}.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        lib = load()
+        msg = lib.b200q_status_string(status).decode()
+        extra = f" (cudaError {lib.b200q_last_cuda_error()})" if status == -4 else ""
+        raise RuntimeError(f"{what}: {msg}{extra}")

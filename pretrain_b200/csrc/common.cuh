@@ -1,0 +1,58 @@
+// Shared host/device helpers of the library: status plumbing, argument checks,
+// vector loads, warp reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200q.h"
+#include "numeric.cuh"
+
+namespace b200q {
+
+constexpr int kNumSMs = 148;
+
+// The library is built as one translation unit (b200q_lib.cu), so these are single objects.
+// Last failing CUDA error on this host thread.
+static thread_local int g_last_cuda_error = 0;
+// Device status word set by kernels whose bounded waits expire.
+static __device__ int g_device_status = 0;
+
+inline int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return B200Q_ERR_CUDA;
+}
+#define B200Q_CUDA(call)                                      \
+  do {                                                        \
+    cudaError_t _e = (call);                                  \
+    if (_e != cudaSuccess) return ::b200q::cuda_fail(_e);     \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Checks the current device is sm_10x (cached per device).
+int require_sm100();
+
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// |bf16x2| max of two packed words, as packed bf16x2 (exact: comparisons only).
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t v) {
+  __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&acc);
+  __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&v);
+  __nv_bfloat162 r = __hmax2(__habs2(a), __habs2(b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+// max over the 8 bf16 of a uint4 -> float
+__device__ __forceinline__ float absmax8(uint4 v) {
+  uint32_t m = absmax_bf16x2(v.x, v.y);
+  m = absmax_bf16x2(m, absmax_bf16x2(v.z, v.w));
+  return fmaxf(bf16lo(m), bf16hi(m));
+}
+
+}  // namespace b200q

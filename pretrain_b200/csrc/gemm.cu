@@ -1,0 +1,412 @@
+// Scaled GEMMs on the 5th-generation tensor cores:  D[M,N] (bf16) = A[M,K] . B[N,K]^T
+//
+//   KIND_F8  : fp8 codes, fp32 scale per row of A and per row of B applied in the epilogue
+//              (stands for torch._scaled_mm, src/quant/fp8.py:59-65)
+//   KIND_MX  : MXFP8, tcgen05.mma kind::mxf8f6f4.block_scale (E8M0 scale per 32 elements)
+//   KIND_NV  : NVFP4, tcgen05.mma kind::mxf4nvf4.block_scale.block16 (E4M3 scale per 16
+//              elements), fp32 tensor scales applied in the epilogue
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0    TMA producer: A/B tiles (128-byte-swizzled, K-major) and the scale-factor atoms of
+//             each K step into a ring of shared-memory stages, signalled through mbarriers;
+//   warp 1    MMA issuer: one thread copies the stage's scale factors to tensor memory
+//             (tcgen05.cp), issues the four K=32-byte tcgen05.mma of the stage, and commits to
+//             the stage's "empty" barrier; accumulators live in tensor memory;
+//   warps 2-5 epilogue: tcgen05.ld the fp32 accumulators (lane = row), scale, round to bf16,
+//             16-byte stores.  With two accumulator stages the epilogue of tile i overlaps the
+//             main loop of tile i+1.
+// No cluster launch and no multicast: the same binary runs under any number of processes.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200q {
+namespace {
+
+enum { KIND_F8 = 0, KIND_MX = 1, KIND_NV = 2 };
+
+constexpr int BM = 128;
+constexpr int BKB = 128;                 // bytes of K per stage (= one 128-byte swizzle row)
+constexpr int kGemmThreads = 192;
+constexpr int kSmemBudget = 227 * 1024;
+
+template <int KIND, int BN_>
+struct Cfg {
+  static constexpr int BN = BN_;
+  static constexpr int NB_ATOMS = (BN + 127) / 128;                        // 128-row groups of B
+  static constexpr int K_ATOMS = KIND == KIND_NV ? 4 : 1;                  // 512-byte SF atoms per K step and row group
+  static constexpr int A_BYTES = BM * BKB;
+  static constexpr int B_BYTES = BN * BKB;
+  static constexpr int SFA_BYTES = KIND == KIND_F8 ? 0 : K_ATOMS * 512;
+  static constexpr int SFB_BYTES = KIND == KIND_F8 ? 0 : NB_ATOMS * K_ATOMS * 512;
+  static constexpr int STAGE_BYTES = ((A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024) * 1024;
+  static constexpr int TX_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGES_RAW = (kSmemBudget - 2048) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SFA_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS;
+  static constexpr int SFB_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS * NB_ATOMS;
+  static constexpr int ACC_STAGES = (2 * BN + SFA_COLS + SFB_COLS <= 512) ? 2 : 1;
+  static constexpr int SFA_COL0 = ACC_STAGES * BN;
+  static constexpr int SFB_COL0 = SFA_COL0 + SFA_COLS;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tcgen05.mma with M=128 needs N % 16 == 0, N <= 256");
+  static_assert(SFB_COL0 + SFB_COLS <= TMEM_COLS, "tensor memory overflow");
+  static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
+};
+
+struct GemmParams {
+  const uint8_t* sfa;      // swizzled scale factors of A (block-scaled kinds)
+  const uint8_t* sfb;
+  const float* scale_a;    // F8: per row of A (or one value); NV: tensor scale of A
+  const float* scale_b;
+  int a_scalar, b_scalar;
+  int a_fmt, b_fmt;
+  int64_t M, N, K;         // K in elements
+  uint16_t* D;
+  int64_t ldd;
+  int num_m, num_n, num_k; // tiles
+  int sf_kt;               // 512-byte atoms per row group along K in the SF buffers
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m, int& n) {
+  constexpr int GM = 16;   // m-blocks per raster group: concurrent CTAs share A and B tiles through L2
+  const int per_group = GM * num_n;
+  const int g = t / per_group, r = t - g * per_group;
+  const int first_m = g * GM;
+  const int gm = num_m - first_m < GM ? num_m - first_m : GM;
+  m = first_m + r % gm;
+  n = r / gm;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  using C = Cfg<KIND, BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+  // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem ptr, abort
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 4));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = p.num_m * p.num_n;
+
+  if (KIND != KIND_F8) {
+    // Scale-factor stage buffers start as zeros so that atoms beyond the end of K (never
+    // loaded) multiply the zero-filled operand tail by a finite scale.
+    for (int s = 0; s < C::STAGES; ++s) {
+      uint32_t* sfz = reinterpret_cast<uint32_t*>(smem_gen + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+      for (int i = threadIdx.x; i < (C::SFA_BYTES + C::SFB_BYTES) / 4; i += kGemmThreads) sfz[i] = 0;
+    }
+    ptx::fence_proxy_async();
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 4); }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (ptx::elect_one()) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(t, p.num_m, p.num_n, m_blk, n_blk);
+        for (int k = 0; k < p.num_k; ++k) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1) || *abort_flag) { ok = false; break; }
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          const uint32_t fb = full_bar(stage);
+          uint32_t tx = C::A_BYTES + C::B_BYTES;
+          if (KIND != KIND_F8) {
+            // atoms of this K step that exist in the (padded) scale-factor buffers
+            const int ka0 = k * C::K_ATOMS;
+            const int ka = p.sf_kt - ka0 < C::K_ATOMS ? p.sf_kt - ka0 : C::K_ATOMS;
+            tx += (uint32_t)(ka * 512 * (1 + C::NB_ATOMS));
+            ptx::mbar_expect_tx(fb, tx);
+            const uint32_t ssfa = sb + C::B_BYTES, ssfb = ssfa + C::SFA_BYTES;
+            ptx::bulk_load(ssfa, p.sfa + ((int64_t)m_blk * p.sf_kt + ka0) * 512, ka * 512, fb);
+#pragma unroll
+            for (int j = 0; j < C::NB_ATOMS; ++j) {
+              const int64_t rg = (int64_t)n_blk * BN / 128 + j;   // BN is a multiple of 128 whenever NB_ATOMS > 1
+              if (rg * 128 < p.N || j == 0)
+                ptx::bulk_load(ssfb + j * C::K_ATOMS * 512, p.sfb + (rg * p.sf_kt + ka0) * 512, ka * 512, fb);
+              else
+                ptx::bulk_load(ssfb + j * C::K_ATOMS * 512, p.sfb + (((int64_t)n_blk * BN / 128) * p.sf_kt + ka0) * 512, ka * 512, fb);
+            }
+          } else {
+            ptx::mbar_expect_tx(fb, tx);
+          }
+          ptx::tma_load_2d(sa, &tmap_a, k * BKB, m_blk * BM, fb);
+          ptx::tma_load_2d(sb, &tmap_b, k * BKB, n_blk * BN, fb);
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(&g_device_status, 1); }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ----------------------------------------------
+    if (ptx::elect_one()) {
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1) || *abort_flag) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int k = 0; k < p.num_k; ++k) {
+          if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          if (KIND != KIND_F8) {
+            const uint32_t ssfa = sb + C::B_BYTES, ssfb = ssfa + C::SFA_BYTES;
+#pragma unroll
+            for (int a = 0; a < C::K_ATOMS; ++a) {
+              ptx::tmem_cp_32x128b_warpx4(tmem_base + C::SFA_COL0 + 4 * a, ptx::smem_desc_sf(ssfa + a * 512));
+#pragma unroll
+              for (int j = 0; j < C::NB_ATOMS; ++j)
+                ptx::tmem_cp_32x128b_warpx4(tmem_base + C::SFB_COL0 + 4 * (a * C::NB_ATOMS + j),
+                                            ptx::smem_desc_sf(ssfb + (j * C::K_ATOMS + a) * 512));
+            }
+          }
+          const uint64_t da = ptx::smem_desc_k_sw128(sa), db = ptx::smem_desc_k_sw128(sb);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t accum = (k | kk) != 0;
+            const uint64_t adv = (uint64_t)(kk * 32 >> 4);   // 32 bytes of K per instruction
+            if (KIND == KIND_F8) {
+              ptx::mma_f8(d_tmem, da + adv, db + adv, ptx::idesc_f8(p.a_fmt, p.b_fmt, BM, BN), accum);
+            } else if (KIND == KIND_MX) {
+              ptx::mma_mxf8(d_tmem, da + adv, db + adv, ptx::idesc_block_scaled(p.a_fmt, p.b_fmt, 1, BM, BN, kk), accum,
+                            tmem_base + C::SFA_COL0, tmem_base + C::SFB_COL0);
+            } else {
+              ptx::mma_nvf4(d_tmem, da + adv, db + adv, ptx::idesc_block_scaled(1, 1, 0, BM, BN, 0), accum,
+                            tmem_base + C::SFA_COL0 + 4 * kk, tmem_base + C::SFB_COL0 + 4 * C::NB_ATOMS * kk);
+            }
+          }
+          ptx::tc_commit(empty_bar(stage));   // stage reusable once these MMAs have read it
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        ptx::tc_commit(tfull_bar(acc));       // accumulator complete
+        if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(&g_device_status, 2); }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue ------------------------------------------------
+    const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    float alpha = 1.f;
+    if (KIND == KIND_NV) alpha = __ldg(p.scale_a) * __ldg(p.scale_b);
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(t, p.num_m, p.num_n, m_blk, n_blk);
+      if (!ptx::mbar_wait(tfull_bar(acc), acc_phase) || *abort_flag) { ok = false; break; }
+      ptx::tc_fence_after();
+      const int64_t row = (int64_t)m_blk * BM + q * 32 + lane;
+      const int64_t col0 = (int64_t)n_blk * BN;
+      float row_scale = alpha;
+      if (KIND == KIND_F8) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
+      uint16_t* drow = p.D + row * p.ldd;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        if (col0 + c >= p.N) break;               // warp-uniform
+        uint32_t r[16];
+        ptx::tmem_ld16(taddr + c, r);
+        ptx::tmem_ld_wait();
+        float f[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) f[i] = u2f(r[i]) * row_scale;
+        if (KIND == KIND_F8) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int64_t col = col0 + c + i;
+            f[i] *= p.b_scalar ? __ldg(p.scale_b) : (col < p.N ? __ldg(p.scale_b + col) : 0.f);
+          }
+        }
+        if (row < p.M) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (col0 + c + 8 * h < p.N) {         // N % 8 == 0: whole 16-byte vectors
+              uint4 o;
+              o.x = pack_bf16(f[8 * h + 0], f[8 * h + 1]); o.y = pack_bf16(f[8 * h + 2], f[8 * h + 3]);
+              o.z = pack_bf16(f[8 * h + 4], f[8 * h + 5]); o.w = pack_bf16(f[8 * h + 6], f[8 * h + 7]);
+              *reinterpret_cast<uint4*>(drow + col0 + c + 8 * h) = o;
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(&g_device_status, 3); }
+  }
+
+  // Teardown.  On the abort path give copies still in flight time to land before the CTA's
+  // shared memory is released.
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D byte tensor [rows, row_bytes] (pitch row_bytes), box = [128 bytes, box_rows], 128-byte swizzle.
+int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return B200Q_ERR_CUDA;
+  cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)BKB, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return B200Q_ERR_CUDA; }
+  return B200Q_OK;
+}
+
+template <int KIND, int BN>
+int launch(const void* A, const void* B, GemmParams p, cudaStream_t st) {
+  using C = Cfg<KIND, BN>;
+  const int64_t row_bytes = KIND == KIND_NV ? p.K / 2 : p.K;
+  CUtensorMap ma, mb;
+  int rc;
+  if ((rc = make_operand_map(&ma, A, p.M, row_bytes, BM))) return rc;
+  if ((rc = make_operand_map(&mb, B, p.N, row_bytes, BN))) return rc;
+  p.num_m = (int)((p.M + BM - 1) / BM);
+  p.num_n = (int)((p.N + BN - 1) / BN);
+  p.num_k = (int)((row_bytes + BKB - 1) / BKB);
+  const int64_t nblk = KIND == KIND_MX ? p.K / 32 : p.K / 16;
+  p.sf_kt = (int)((nblk + 3) / 4);
+  B200Q_CUDA(cudaFuncSetAttribute(gemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  const int tiles = p.num_m * p.num_n;
+  const int grid = tiles < kNumSMs ? tiles : kNumSMs;
+  gemm_kernel<KIND, BN><<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(ma, mb, p);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int g_force_bn = 0;   // test hook: 0 = choose by N
+
+template <int KIND>
+int dispatch(const void* A, const void* B, const GemmParams& p, cudaStream_t st) {
+  int bn = g_force_bn ? g_force_bn : (p.N > 128 ? 256 : 128);
+  switch (bn) {
+    case 128: return launch<KIND, 128>(A, B, p, st);
+    case 256: return launch<KIND, 256>(A, B, p, st);
+    default: return B200Q_ERR_INVALID_ARG;
+  }
+}
+
+int check_gemm(const void* A, const void* B, const void* D, int64_t M, int64_t N, int64_t K, int64_t ldd, int kmult) {
+  if (A == nullptr || B == nullptr || D == nullptr || M <= 0 || N <= 0 || K <= 0 || ldd < N) return B200Q_ERR_INVALID_ARG;
+  if ((K % kmult) || (N & 7) || (ldd & 7)) return B200Q_ERR_SHAPE;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(D)) return B200Q_ERR_ALIGNMENT;
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B200Q_ERR_SHAPE;
+  return require_sm100();
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+// Test hook: force the N tile width (128 or 256; 0 restores the default choice).
+int b200q_debug_set_gemm_bn(int bn) {
+  if (bn != 0 && bn != 128 && bn != 256) return B200Q_ERR_INVALID_ARG;
+  g_force_bn = bn;
+  return B200Q_OK;
+}
+
+int b200q_gemm_fp8(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a, int a_scale_is_scalar,
+                   const float* scale_b, int b_scale_is_scalar, int64_t M, int64_t N, int64_t K, void* D, int64_t ldd,
+                   void* stream) {
+  int rc = check_gemm(A, B, D, M, N, K, ldd, 16);
+  if (rc) return rc;
+  if (scale_a == nullptr || scale_b == nullptr || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
+  GemmParams p = {};
+  p.scale_a = scale_a; p.scale_b = scale_b; p.a_scalar = a_scale_is_scalar; p.b_scalar = b_scale_is_scalar;
+  p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.M = M; p.N = N; p.K = K; p.D = (uint16_t*)D; p.ldd = ldd;
+  return dispatch<KIND_F8>(A, B, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
+                     int64_t N, int64_t K, void* D, int64_t ldd, void* stream) {
+  int rc = check_gemm(A, B, D, M, N, K, ldd, 32);
+  if (rc) return rc;
+  if (sfA == nullptr || sfB == nullptr || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.M = M; p.N = N; p.K = K; p.D = (uint16_t*)D; p.ldd = ldd;
+  return dispatch<KIND_MX>(A, B, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,
+                     int64_t M, int64_t N, int64_t K, void* D, int64_t ldd, void* stream) {
+  int rc = check_gemm(A, B, D, M, N, K, ldd, 32);
+  if (rc) return rc;
+  if (sfA == nullptr || sfB == nullptr || tsA == nullptr || tsB == nullptr) return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.scale_a = tsA; p.scale_b = tsB;
+  p.M = M; p.N = N; p.K = K; p.D = (uint16_t*)D; p.ldd = ldd;
+  return dispatch<KIND_NV>(A, B, p, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,549 @@
+// Quantize kernels: amax, FP8 (per-row / per-column / per-tensor fp32 scales), MXFP8
+// (32-element blocks, E8M0 scales) and NVFP4 (16-element blocks, E4M3 scales + fp32 tensor
+// scale), each in a row-wise form (contraction dimension contiguous in the input) and a
+// transposing form (contraction dimension = input rows; output written transposed).
+//
+// All of them are HBM-bound streaming kernels: 16-byte coalesced loads with several loads in
+// flight per thread, warp-shuffle reductions for the block / row maxima, hardware fp8 / fp4
+// conversion instructions, 8- or 16-byte coalesced stores.  Arithmetic is the bit-exact core
+// in numeric.cuh (reference formula: src/quant/fp8.py:16-32).
+#include "common.cuh"
+
+namespace b200q {
+
+int require_sm100() {
+  static thread_local int cached_dev = -1;
+  static thread_local int cached_ok = 0;
+  int dev = -1;
+  B200Q_CUDA(cudaGetDevice(&dev));
+  if (dev != cached_dev) {
+    int major = 0;
+    B200Q_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    cached_dev = dev;
+    cached_ok = (major == 10);
+  }
+  return cached_ok ? B200Q_OK : B200Q_ERR_NOT_SM100;
+}
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+  f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
+}
+
+// ------------------------------------------------------------------------------------------
+// amax over a matrix
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) amax_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
+                                                        int64_t ld, float* __restrict__ amax) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t m = 0;
+  for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows; row += (int64_t)gridDim.x * kWarps) {
+    const uint16_t* xr = x + row * ld;
+    for (int64_t c0 = 0; c0 < cols; c0 += 1024) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int64_t c = c0 + u * 256 + lane * 8;
+        v[u] = c < cols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        m = absmax_bf16x2(m, absmax_bf16x2(v[u].x, v[u].y));
+        m = absmax_bf16x2(m, absmax_bf16x2(v[u].z, v[u].w));
+      }
+    }
+  }
+  float a = warp_max(fmaxf(bf16lo(m), bf16hi(m)));
+  __shared__ float s[kWarps];
+  if (lane == 0) s[warp] = a;
+  __syncthreads();
+  if (warp == 0) {
+    a = warp_max(lane < kWarps ? s[lane] : 0.f);
+    if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), f2u(a));   // a >= 0: uint order == float order
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Row-wise block quantizers (MXFP8 / NVFP4): one warp walks a row, each lane owns 8
+// consecutive elements per step, blocks are reduced with 2 (MX) or 1 (NV) shuffle steps.
+// ------------------------------------------------------------------------------------------
+enum { MODE_MX = 0, MODE_NV = 1, MODE_FP8 = 2 };
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads)
+rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, int fmt,
+                           uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, int swz,
+                           const float* __restrict__ tensor_amax, float* __restrict__ tensor_scale_out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int BS = MODE == MODE_MX ? 32 : 16;
+  const int64_t nblk = cols / BS;
+  float s_t = 0.f;
+  if (MODE == MODE_NV) {
+    s_t = nv_tensor_scale(*tensor_amax);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *tensor_scale_out = s_t;
+  }
+  for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows; row += (int64_t)gridDim.x * kWarps) {
+    const uint16_t* xr = x + row * ld;
+    for (int64_t c0 = 0; c0 < cols; c0 += 1024) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int64_t c = c0 + u * 256 + lane * 8;
+        v[u] = c < cols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t c = c0 + u * 256 + lane * 8;
+        if (c0 + u * 256 >= cols) break;   // warp-uniform
+        float a = absmax8(v[u]);
+        a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
+        if (MODE == MODE_MX) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
+        float f[8];
+        unpack8(v[u], f);
+        if (MODE == MODE_MX) {
+          const int e = mx_scale_exp(a, fmt);
+          const float inv = mx_inv_scale(e);
+          uint2 o;
+          o.x = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, fmt);
+          o.y = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, fmt);
+          if (c < cols) {
+            *reinterpret_cast<uint2*>(codes + row * cols + c) = o;
+            if ((lane & 3) == 0) sf[sf_offset(row, c >> 5, nblk, swz)] = (uint8_t)(e + 127);
+          }
+        } else {
+          const uint8_t sq = nv_block_scale(a, s_t);
+          const float eff = mul_rn(e4m3_to_float(sq), s_t);
+          const float rcp = rcp_rn(eff);
+          uint32_t o = 0;
+          if (sq != 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              o |= (uint32_t)cvt_e2m1x2(div_by_rcp(f[2 * i], eff, rcp), div_by_rcp(f[2 * i + 1], eff, rcp)) << (8 * i);
+          }
+          if (c < cols) {
+            *reinterpret_cast<uint32_t*>(codes + row * (cols >> 1) + (c >> 1)) = o;
+            if ((lane & 1) == 0) sf[sf_offset(row, c >> 4, nblk, swz)] = sq;
+          }
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Row-wise FP8 with one fp32 scale per row (or one for the tensor): a warp owns a row and
+// keeps it in registers between the amax pass and the conversion pass (NVEC 16-byte vectors
+// per lane); NVEC == 0 re-reads the row (it is still in L2) for very long rows.
+// ------------------------------------------------------------------------------------------
+template <int NVEC>
+__global__ void __launch_bounds__(kThreads)
+rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, int fmt,
+                   uint8_t* __restrict__ codes, float* __restrict__ scales, const float* __restrict__ tensor_amax,
+                   float* __restrict__ tensor_scale_out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows; row += (int64_t)gridDim.x * kWarps) {
+    const uint16_t* xr = x + row * ld;
+    uint4 v[NVEC > 0 ? NVEC : 1];
+    uint32_t m = 0;
+    if (NVEC > 0) {
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        int64_t c = (int64_t)(i * 32 + lane) * 8;
+        v[i] = c < cols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        m = absmax_bf16x2(m, absmax_bf16x2(v[i].x, v[i].y));
+        m = absmax_bf16x2(m, absmax_bf16x2(v[i].z, v[i].w));
+      }
+    } else if (tensor_amax == nullptr) {
+      for (int64_t c = lane * 8; c < cols; c += 256) {
+        uint4 t = ld_nc_v4(xr + c);
+        m = absmax_bf16x2(m, absmax_bf16x2(t.x, t.y));
+        m = absmax_bf16x2(m, absmax_bf16x2(t.z, t.w));
+      }
+    }
+    float amax = tensor_amax ? *tensor_amax : warp_max(fmaxf(bf16lo(m), bf16hi(m)));
+    const float scale = fp8_scale_from_amax(amax, fmt);
+    const float rcp = rcp_rn(scale);
+    if (lane == 0) {
+      if (tensor_amax == nullptr) scales[row] = scale;
+      else if (row == 0) *tensor_scale_out = scale;
+    }
+    uint8_t* cr = codes + row * cols;
+    if (NVEC > 0) {
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        int64_t c = (int64_t)(i * 32 + lane) * 8;
+        float f[8];
+        unpack8(v[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = div_by_rcp(f[j], scale, rcp);
+        uint2 o;
+        o.x = cvt_fp8x4(f[0], f[1], f[2], f[3], fmt);
+        o.y = cvt_fp8x4(f[4], f[5], f[6], f[7], fmt);
+        if (c < cols) *reinterpret_cast<uint2*>(cr + c) = o;
+      }
+    } else {
+      for (int64_t c = lane * 8; c < cols; c += 256) {
+        float f[8];
+        unpack8(ld_nc_v4(xr + c), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = div_by_rcp(f[j], scale, rcp);
+        uint2 o;
+        o.x = cvt_fp8x4(f[0], f[1], f[2], f[3], fmt);
+        o.y = cvt_fp8x4(f[4], f[5], f[6], f[7], fmt);
+        *reinterpret_cast<uint2*>(cr + c) = o;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Per-column amax (for FP8 scales that run along the rows), then amax -> scale in place.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+col_amax_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, unsigned int* __restrict__ amax_bits) {
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t c = ((int64_t)blockIdx.x * 32 + tx) * 8;
+  uint32_t m[4] = {0, 0, 0, 0};
+  if (c < cols) {
+    for (int64_t r0 = (int64_t)blockIdx.y * kWarps * 4 + ty; r0 < rows; r0 += (int64_t)gridDim.y * kWarps * 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int64_t r = r0 + u * kWarps;
+        v[u] = r < rows ? ld_nc_v4(x + r * ld + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        m[0] = absmax_bf16x2(m[0], v[u].x); m[1] = absmax_bf16x2(m[1], v[u].y);
+        m[2] = absmax_bf16x2(m[2], v[u].z); m[3] = absmax_bf16x2(m[3], v[u].w);
+      }
+    }
+  }
+  __shared__ uint32_t s[kWarps][32][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s[ty][tx][i] = m[i];
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t a = 0;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) a = absmax_bf16x2(a, s[w][tx][i]);
+      atomicMax(amax_bits + c + 2 * i, f2u(bf16lo(a)));
+      atomicMax(amax_bits + c + 2 * i + 1, f2u(bf16hi(a)));
+    }
+  }
+}
+
+__global__ void amax_to_scale_kernel(float* __restrict__ scales, int64_t n, int fmt) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) scales[i] = fp8_scale_from_amax(scales[i], fmt);
+}
+
+// ------------------------------------------------------------------------------------------
+// Transposing quantizers: scales run along the input rows; codes are written transposed.
+// A CTA stages a 128-row x 64-column bf16 tile in shared memory (16-byte coalesced loads, four
+// in flight per thread); each thread then owns one column and a run of 32 rows, and the code
+// tile goes back out through shared memory as 128-byte (64-byte for FP4) row segments.
+// ------------------------------------------------------------------------------------------
+constexpr int kTR = 128, kTC = 64;
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads)
+transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, int fmt,
+                       uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, int swz,
+                       const float* __restrict__ col_scales, const float* __restrict__ tensor_amax,
+                       float* __restrict__ tensor_scale_out) {
+  __shared__ __align__(16) uint16_t tin[kTR * kTC];
+  constexpr int OUT_PITCH = (MODE == MODE_NV ? kTR / 2 : kTR) + 16;
+  __shared__ __align__(16) uint8_t tout[kTC * OUT_PITCH];
+  const int tid = threadIdx.x;
+  const int64_t c0 = (int64_t)blockIdx.x * kTC, r0 = (int64_t)blockIdx.y * kTR;
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int id = i * kThreads + tid, r = id >> 3, ch = id & 7;
+    const int64_t gr = r0 + r, gc = c0 + ch * 8;
+    uint4 v = (gr < rows && gc < cols) ? ld_nc_v4(x + gr * ld + gc) : make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(&tin[r * kTC + ch * 8]) = v;
+  }
+  float s_t = 0.f, t_scale = 0.f;
+  if (MODE == MODE_NV) {
+    s_t = nv_tensor_scale(*tensor_amax);
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) *tensor_scale_out = s_t;
+  }
+  if (MODE == MODE_FP8 && tensor_amax != nullptr) {
+    t_scale = fp8_scale_from_amax(*tensor_amax, fmt);
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) *tensor_scale_out = t_scale;
+  }
+  __syncthreads();
+
+  const int c = tid & 63, j = tid >> 6;
+  const int64_t gc = c0 + c, gr = r0 + 32 * j;
+  float f[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) f[i] = u2f((uint32_t)tin[(32 * j + i) * kTC + c] << 16);
+
+  if (MODE == MODE_MX) {
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) a = fmaxf(a, fabsf(f[i]));
+    const int e = mx_scale_exp(a, fmt);
+    const float inv = mx_inv_scale(e);
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = cvt_fp8x4(f[4 * i] * inv, f[4 * i + 1] * inv, f[4 * i + 2] * inv, f[4 * i + 3] * inv, fmt);
+    uint4* dst = reinterpret_cast<uint4*>(&tout[c * OUT_PITCH + 32 * j]);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    if (gc < cols && gr < rows) sf[sf_offset(gc, gr >> 5, rows >> 5, swz)] = (uint8_t)(e + 127);
+  } else if (MODE == MODE_NV) {
+    uint32_t o[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float a = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) a = fmaxf(a, fabsf(f[16 * h + i]));
+      const uint8_t sq = nv_block_scale(a, s_t);
+      const float eff = mul_rn(e4m3_to_float(sq), s_t);
+      const float rcp = rcp_rn(eff);
+      o[2 * h] = o[2 * h + 1] = 0;
+      if (sq != 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint32_t b = cvt_e2m1x2(div_by_rcp(f[16 * h + 2 * i], eff, rcp), div_by_rcp(f[16 * h + 2 * i + 1], eff, rcp));
+          o[2 * h + (i >> 2)] |= b << (8 * (i & 3));
+        }
+      }
+      if (gc < cols && gr + 16 * h < rows) sf[sf_offset(gc, (gr >> 4) + h, rows >> 4, swz)] = sq;
+    }
+    *reinterpret_cast<uint4*>(&tout[c * OUT_PITCH + 16 * j]) = make_uint4(o[0], o[1], o[2], o[3]);
+  } else {
+    const float scale = tensor_amax ? t_scale : (gc < cols ? col_scales[gc] : 1.f);
+    const float rcp = rcp_rn(scale);
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      o[i] = cvt_fp8x4(div_by_rcp(f[4 * i], scale, rcp), div_by_rcp(f[4 * i + 1], scale, rcp),
+                       div_by_rcp(f[4 * i + 2], scale, rcp), div_by_rcp(f[4 * i + 3], scale, rcp), fmt);
+    uint4* dst = reinterpret_cast<uint4*>(&tout[c * OUT_PITCH + 32 * j]);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+  __syncthreads();
+
+  if (MODE == MODE_NV) {
+    const int oc = tid >> 2, ch = tid & 3;
+    if (c0 + oc < cols && r0 + ch * 32 < rows)
+      *reinterpret_cast<uint4*>(codes + (c0 + oc) * (rows >> 1) + (r0 >> 1) + ch * 16) =
+          *reinterpret_cast<const uint4*>(&tout[oc * OUT_PITCH + ch * 16]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int id = i * kThreads + tid, oc = id >> 3, ch = id & 7;
+      if (c0 + oc < cols && r0 + ch * 16 < rows)
+        *reinterpret_cast<uint4*>(codes + (c0 + oc) * rows + r0 + ch * 16) =
+            *reinterpret_cast<const uint4*>(&tout[oc * OUT_PITCH + ch * 16]);
+    }
+  }
+}
+
+int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
+  if (x == nullptr || rows <= 0 || cols <= 0 || ld < cols) return B200Q_ERR_INVALID_ARG;
+  if ((cols & 7) || (ld & 7)) return B200Q_ERR_SHAPE;
+  if (!aligned16(x)) return B200Q_ERR_ALIGNMENT;
+  return B200Q_OK;
+}
+
+inline int rowwise_grid(int64_t rows) {
+  int64_t want = (rows + kWarps - 1) / kWarps;
+  int64_t cap = (int64_t)kNumSMs * 8;
+  return (int)(want < cap ? want : cap);
+}
+
+int zero_sf_pads(void* sf, int64_t outer, int64_t nblk, int layout, cudaStream_t st) {
+  if (layout == B200Q_SF_SWIZZLE_128x4 && ((outer & 127) || (nblk & 3)))
+    B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(outer, nblk, layout), st));
+  return B200Q_OK;
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+const char* b200q_status_string(int status) {
+  switch (status) {
+    case B200Q_OK: return "ok";
+    case B200Q_ERR_INVALID_ARG: return "invalid argument";
+    case B200Q_ERR_SHAPE: return "unsupported shape (size is not a multiple the kernel requires)";
+    case B200Q_ERR_ALIGNMENT: return "pointer or pitch is not 16-byte aligned";
+    case B200Q_ERR_CUDA: return "CUDA call failed";
+    case B200Q_ERR_NOT_SM100: return "device is not sm_100 (B200)";
+    case B200Q_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+    default: return "unknown status";
+  }
+}
+
+int b200q_last_cuda_error(void) { return g_last_cuda_error; }
+
+int b200q_device_status(void) {
+  int v = 0, zero = 0;
+  B200Q_CUDA(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
+  if (v != 0) {
+    B200Q_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+    return B200Q_ERR_DEVICE_TIMEOUT;
+  }
+  return B200Q_OK;
+}
+
+int64_t b200q_sf_bytes(int64_t outer, int64_t nblk, int sf_layout) {
+  if (outer < 0 || nblk < 0) return 0;
+  if (sf_layout == B200Q_SF_SWIZZLE_128x4) return ((outer + 127) / 128) * ((nblk + 3) / 4) * 512;
+  return outer * nblk;
+}
+
+int b200q_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, float* amax, void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (amax == nullptr) return B200Q_ERR_INVALID_ARG;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  B200Q_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), st));
+  amax_kernel<<<rowwise_grid(rows), kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, amax);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+static int launch_rowwise_fp8(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes,
+                              float* scales, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st) {
+  const int grid = rowwise_grid(rows);
+  const int64_t nvec = (cols + 255) / 256;
+#define B200Q_LAUNCH(NV) \
+  rowwise_fp8_kernel<NV><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, fmt, codes, scales, tensor_amax, tensor_scale_out)
+  if (nvec <= 1) B200Q_LAUNCH(1);
+  else if (nvec <= 2) B200Q_LAUNCH(2);
+  else if (nvec <= 4) B200Q_LAUNCH(4);
+  else if (nvec <= 8) B200Q_LAUNCH(8);
+  else if (nvec <= 16) B200Q_LAUNCH(16);
+  else B200Q_LAUNCH(0);
+#undef B200Q_LAUNCH
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_quantize_fp8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int fmt, void* codes,
+                       float* scales, void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes == nullptr || scales == nullptr || (axis != 0 && axis != 1) || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (axis == 1) return launch_rowwise_fp8((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, scales, nullptr, nullptr, st);
+  if (rows & 15) return B200Q_ERR_SHAPE;
+  B200Q_CUDA(cudaMemsetAsync(scales, 0, (size_t)cols * sizeof(float), st));
+  {
+    dim3 grid((unsigned)((cols / 8 + 31) / 32), 1);
+    int64_t ymax = (rows + kWarps * 4 - 1) / (kWarps * 4);
+    int64_t want = (int64_t)kNumSMs * 4 / grid.x + 1;
+    grid.y = (unsigned)(want < ymax ? want : ymax);
+    col_amax_kernel<<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, (unsigned int*)scales);
+    B200Q_CUDA(cudaGetLastError());
+  }
+  amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, fmt);
+  B200Q_CUDA(cudaGetLastError());
+  dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
+  transpose_quant_kernel<MODE_FP8><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes,
+                                                              nullptr, 0, scales, nullptr, nullptr);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_quantize_fp8_tensorwise(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose, int fmt,
+                                  const float* tensor_amax, void* codes, float* scale_out, void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes == nullptr || tensor_amax == nullptr || scale_out == nullptr || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!transpose)
+    return launch_rowwise_fp8((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, nullptr, tensor_amax, scale_out, st);
+  if (rows & 15) return B200Q_ERR_SHAPE;
+  dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
+  transpose_quant_kernel<MODE_FP8><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes,
+                                                              nullptr, 0, nullptr, tensor_amax, scale_out);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int fmt, void* codes,
+                         void* sf, int sf_layout, void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes == nullptr || sf == nullptr || (axis != 0 && axis != 1) || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2) ||
+      (sf_layout != B200Q_SF_NATURAL && sf_layout != B200Q_SF_SWIZZLE_128x4))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
+  const int64_t contraction = axis == 1 ? cols : rows, outer = axis == 1 ? rows : cols;
+  if (contraction & 31) return B200Q_ERR_SHAPE;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((rc = zero_sf_pads(sf, outer, contraction / 32, sf_layout, st))) return rc;
+  if (axis == 1) {
+    rowwise_block_quant_kernel<MODE_MX><<<rowwise_grid(rows), kThreads, 0, st>>>(
+        (const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr);
+  } else {
+    dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
+    transpose_quant_kernel<MODE_MX><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes,
+                                                               (uint8_t*)sf, sf_layout, nullptr, nullptr, nullptr);
+  }
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, const float* tensor_amax,
+                         void* codes, void* sf, int sf_layout, float* tensor_scale_out, void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes == nullptr || sf == nullptr || tensor_amax == nullptr || tensor_scale_out == nullptr ||
+      (axis != 0 && axis != 1) || (sf_layout != B200Q_SF_NATURAL && sf_layout != B200Q_SF_SWIZZLE_128x4))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
+  const int64_t contraction = axis == 1 ? cols : rows, outer = axis == 1 ? rows : cols;
+  if (contraction & 31) return B200Q_ERR_SHAPE;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((rc = zero_sf_pads(sf, outer, contraction / 16, sf_layout, st))) return rc;
+  if (axis == 1) {
+    rowwise_block_quant_kernel<MODE_NV><<<rowwise_grid(rows), kThreads, 0, st>>>(
+        (const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax, tensor_scale_out);
+  } else {
+    dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
+    transpose_quant_kernel<MODE_NV><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes,
+                                                               (uint8_t*)sf, sf_layout, nullptr, tensor_amax, tensor_scale_out);
+  }
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,56 @@
+"""The C-ABI library builds for sm_100a without a GPU, loads, and exports every symbol that
+include/b200q.h declares (no compute calls here)."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+@pytest.fixture(scope="module")
+def lib_path():
+    from pretrain_b200 import build
+    return build.build()
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "b200q.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200q_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib_path):
+    lib = ctypes.CDLL(lib_path)
+    names = _declared()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/b200q.h but not exported"
+
+
+def test_binding_table_matches_header(lib_path):
+    from pretrain_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == _declared()
+
+
+def test_host_only_entry_points(lib_path):
+    from pretrain_b200 import _lib
+    lib = _lib.load()
+    assert lib.b200q_status_string(0) == b"ok"
+    assert b"shape" in lib.b200q_status_string(-2)
+    assert lib.b200q_sf_bytes(128, 4, 1) == 512
+    assert lib.b200q_sf_bytes(129, 5, 1) == 2 * 2 * 512
+    assert lib.b200q_sf_bytes(129, 5, 0) == 129 * 5
+    # argument validation happens before any CUDA call
+    assert lib.b200q_amax(None, 4, 8, 8, None, None) == -1
+    assert lib.b200q_quantize_mxfp8(ctypes.c_void_p(16), 4, 12, 16, 1, 0, ctypes.c_void_p(16), ctypes.c_void_p(16), 1, None) == -2
+    assert lib.b200q_quantize_mxfp8(ctypes.c_void_p(8), 4, 32, 32, 1, 0, ctypes.c_void_p(16), ctypes.c_void_p(16), 1, None) == -3
+
+
+def test_ops_refuse_cpu_tensors(lib_path):
+    import torch
+    from pretrain_b200 import ops
+    with pytest.raises(RuntimeError):
+        ops.quantize_mxfp8(torch.zeros(4, 32, dtype=torch.bfloat16))

@@ -1,0 +1,189 @@
+"""Parity of the CUDA quantizers, called through the C-ABI, with the CPU oracle: codes and
+scales bit-exact (integer / byte outputs), on seeded inputs, golden fixtures and edge cases."""
+
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import restate as R
+from conftest import ROOT, bf16_from_bits
+
+pytestmark = pytest.mark.gpu
+E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from pretrain_b200 import build, ops
+    build.build()
+    return ops
+
+
+def _cases():
+    g = torch.Generator().manual_seed(5)
+    x, w = R.inputs_mxfp8_linear(512, 768, 384)
+    xo, wgu, _ = R.inputs_nvfp4_mlp(256, 1024, 64)
+    wide = torch.randn(96, 160, generator=g) * torch.exp2(torch.randint(-30, 30, (96, 160), generator=g).float())
+    tiny = torch.randn(32, 64, generator=g) * 1e-20
+    zeros = torch.zeros(32, 32)
+    big = torch.randn(64, 4352, generator=g) * 3        # > 4096 columns: re-read path of the per-row kernel
+    odd = torch.randn(160, 96, generator=g)             # partial tiles in both directions
+    return {"x": x, "w": w, "outlier": xo, "wgu": wgu, "wide": wide.bfloat16(), "tiny": tiny.bfloat16(),
+            "zeros": zeros.bfloat16(), "long": big.bfloat16(), "odd": odd.bfloat16()}
+
+
+CASES = _cases()
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_amax(ops, name):
+    x = CASES[name]
+    got = ops.amax(x.cuda()).cpu()
+    assert got.item() == x.abs().max().float().item()
+
+
+@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("dt", [E4, E5])
+@pytest.mark.parametrize("axis", [1, 0])
+def test_fp8_row_and_col(ops, name, dt, axis):
+    x = CASES[name]
+    codes, scales = ops.quantize_fp8(x.cuda(), dt, axis)
+    rc, rs = R.quantize_fp8(x, dt, dim=-1 if axis == 1 else 0)
+    rc = rc.view(torch.uint8)
+    if axis == 0:
+        rc = rc.t().contiguous()
+    assert torch.equal(scales.cpu().view(torch.int32), rs.reshape(-1).view(torch.int32))
+    assert torch.equal(codes.cpu(), rc)
+
+
+@pytest.mark.parametrize("name", ["x", "wide", "zeros", "odd"])
+@pytest.mark.parametrize("dt", [E4, E5])
+@pytest.mark.parametrize("transpose", [False, True])
+def test_fp8_tensorwise(ops, name, dt, transpose):
+    x = CASES[name]
+    codes, scale = ops.quantize_fp8_tensorwise(x.cuda(), dt, transpose)
+    rc, rs = R.quantize_fp8(x, dt, None)
+    rc = rc.view(torch.uint8)
+    assert scale.cpu().view(torch.int32).item() == rs.view(torch.int32).item()
+    assert torch.equal(codes.cpu(), rc.t().contiguous() if transpose else rc)
+
+
+def test_fp8_matches_reference_golden(ops, golden):
+    for name in ("a", "b", "grad", "edge"):
+        x = bf16_from_bits(golden[f"in_{name}"])
+        for dname, dt in (("e4m3", E4), ("e5m2", E5)):
+            codes, scales = ops.quantize_fp8(x.cuda(), dt, 1)
+            assert np.array_equal(codes.cpu().numpy(), golden[f"q_{name}_{dname}_row_codes"])
+            assert np.array_equal(scales.cpu().numpy().view(np.uint32), golden[f"q_{name}_{dname}_row_scale"].view(np.uint32))
+            codes, scales = ops.quantize_fp8(x.cuda(), dt, 0)
+            assert np.array_equal(codes.cpu().numpy(), golden[f"q_{name}_{dname}_col_codes"].T)
+            assert np.array_equal(scales.cpu().numpy().view(np.uint32), golden[f"q_{name}_{dname}_col_scale"].view(np.uint32))
+            codes, scale = ops.quantize_fp8_tensorwise(x.cuda(), dt)
+            assert np.array_equal(codes.cpu().numpy(), golden[f"q_{name}_{dname}_tensor_codes"])
+
+
+def test_fp8_digests_at_benchmark_size(ops):
+    """FP8 training triple (M=16384, K=N=2048): sha256 of codes and scales equals what the
+    reference's quantize_fp8 produced for the same seeded inputs."""
+    with open(os.path.join(ROOT, "tests", "golden", "ref_digests.json")) as f:
+        dig = json.load(f)
+    x, w, dy = R.inputs_fp8_triple()
+
+    def sha(t):
+        return hashlib.sha256(t.cpu().contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+    # name -> (tensor, dtype, axis, codes come out transposed relative to the reference's)
+    table = {
+        "fprop_x_row_e4m3": (x, E4, 1, False), "fprop_wT_col_e4m3": (w, E4, 1, True),
+        "dgrad_dy_row_e5m2": (dy, E5, 1, False), "dgrad_w_col_e4m3": (w, E4, 0, True),
+        "wgrad_dyT_row_e5m2": (dy, E5, 0, False), "wgrad_x_col_e4m3": (x, E4, 0, True),
+    }
+    for name, (t, dt, axis, transposed) in table.items():
+        codes, scales = ops.quantize_fp8(t.cuda(), dt, axis)
+        ref_layout = codes.t().contiguous() if transposed else codes
+        assert list(ref_layout.shape) == dig[name]["shape"]
+        assert sha(ref_layout) == dig[name]["codes"], name
+        assert sha(scales) == dig[name]["scale"], name
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if CASES[n].shape[1] % 32 == 0])
+@pytest.mark.parametrize("dt", [E4, E5])
+@pytest.mark.parametrize("layout", [0, 1])
+def test_mxfp8_rowwise(ops, name, dt, layout):
+    x = CASES[name]
+    codes, sf = ops.quantize_mxfp8(x.cuda(), 1, dt, layout)
+    rc, rs = R.quantize_mxfp8(x, -1, dt)
+    want_sf = R.swizzle_sf(rs) if layout else rs.reshape(-1)
+    assert torch.equal(sf.cpu(), want_sf)
+    assert torch.equal(codes.cpu(), rc)
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if CASES[n].shape[0] % 32 == 0])
+@pytest.mark.parametrize("dt", [E4, E5])
+@pytest.mark.parametrize("layout", [0, 1])
+def test_mxfp8_transposing(ops, name, dt, layout):
+    x = CASES[name]
+    codes, sf = ops.quantize_mxfp8(x.cuda(), 0, dt, layout)
+    rc, rs = R.quantize_mxfp8(x, 0, dt)
+    want_sf = R.swizzle_sf(rs) if layout else rs.reshape(-1)
+    assert codes.shape == (x.shape[1], x.shape[0])
+    assert torch.equal(sf.cpu(), want_sf)
+    assert torch.equal(codes.cpu(), rc)
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if CASES[n].shape[1] % 32 == 0])
+@pytest.mark.parametrize("layout", [0, 1])
+def test_nvfp4_rowwise(ops, name, layout):
+    x = CASES[name]
+    packed, sf, ts = ops.quantize_nvfp4(x.cuda(), 1, None, layout)
+    rp, rs, rt = R.quantize_nvfp4(x)
+    assert ts.cpu().view(torch.int32).item() == rt.view(torch.int32).item()
+    assert torch.equal(sf.cpu(), R.swizzle_sf(rs) if layout else rs.reshape(-1))
+    assert torch.equal(packed.cpu(), rp)
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if CASES[n].shape[0] % 32 == 0])
+@pytest.mark.parametrize("layout", [0, 1])
+def test_nvfp4_transposing(ops, name, layout):
+    x = CASES[name]
+    packed, sf, ts = ops.quantize_nvfp4(x.cuda(), 0, None, layout)
+    rp, rs, rt = R.quantize_nvfp4(x, 0)
+    assert packed.shape == (x.shape[1], x.shape[0] // 2)
+    assert torch.equal(sf.cpu(), R.swizzle_sf(rs) if layout else rs.reshape(-1))
+    assert torch.equal(packed.cpu(), rp)
+
+
+def test_strided_input_is_read_in_place(ops):
+    x = CASES["x"]
+    big = torch.zeros(x.shape[0], x.shape[1] + 64, dtype=torch.bfloat16)
+    big[:, : x.shape[1]] = x
+    view = big.cuda()[:, : x.shape[1]]
+    codes, sf = ops.quantize_mxfp8(view, 1, E4, 0)
+    rc, rs = R.quantize_mxfp8(x, -1, E4)
+    assert torch.equal(codes.cpu(), rc) and torch.equal(sf.cpu(), rs.reshape(-1))
+
+
+def test_full_size_properties(ops):
+    """Benchmark-size square operand (8192 x 8192): properties that need no CPU pass over the
+    data — never clips, scale is tight, transposing kernel == row-wise kernel on the transpose."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(8192, 8192, generator=g, device="cuda", dtype=torch.bfloat16)
+    codes, sf = ops.quantize_mxfp8(x, 1, E4, 0)
+    e = sf.view(8192, 256).float() - 127
+    amax = x.float().view(8192, 256, 32).abs().amax(-1)
+    scaled = amax * torch.exp2(-e)
+    assert (scaled <= 448).all() and (scaled > 224).all()
+    deq = (codes.view(E4).float().view(8192, 256, 32) * torch.exp2(e).unsqueeze(-1)).view(8192, 8192)
+    assert ((deq - x.float()).norm() / x.float().norm()).item() < 0.04
+    ct, sft = ops.quantize_mxfp8(x.t().contiguous(), 0, E4, 0)
+    assert torch.equal(ct, codes) and torch.equal(sft, sf)
+    p1, s1, t1 = ops.quantize_nvfp4(x, 1, None, 1)
+    p2, s2, t2 = ops.quantize_nvfp4(x.t().contiguous(), 0, None, 1)
+    assert torch.equal(p1, p2) and torch.equal(s1, s2) and torch.equal(t1, t2)
+    c1, sc1 = ops.quantize_fp8(x, E4, 1)
+    c2, sc2 = ops.quantize_fp8(x.t().contiguous(), E4, 0)
+    assert torch.equal(c1, c2) and torch.equal(sc1, sc2)
