@@ -1,0 +1,129 @@
+"""Quantized linear: ``_gemm``, ``QuantizedLinearFn`` and ``QuantLinear`` with the signatures and
+conventions of src/quant/linear.py, on the sm_100a kernels.
+
+``_gemm(a, b, ...)`` always receives a (rows, C) and b (C, cols) — possibly as transposed views
+(``w.t()``, ``g.t()``) — and scales run along C.  Same-family quantized operands go to the fused
+tensor-core GEMM; mixed or one-sided formats are fake-quantized and multiplied in high
+precision, as the reference does (src/quant/linear.py:27-56)."""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .. import torch_ops as T
+from ..ops import SF_NATURAL, fmt_of
+from .config import QuantConfig
+from .fp8 import _k_major, fake_quantize_fp8, fp8_gemm
+from .mx import mxfp8_gemm, nvfp4_gemm
+from .utils import is_fp8, is_int8s, is_mxfp8, is_nvfp4, is_quantized, str_to_dtype_fp8
+
+_E2M1_LUT = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+
+
+def _fake_quant_block(x: torch.Tensor, fmt: str, contraction_dim: int) -> torch.Tensor:
+    """dequant(quant(x)) for a block-scaled format, blocks along ``contraction_dim`` of the 2-D
+    view x; quantization on the CUDA kernels, dequantization in plain torch."""
+    m, axis = _k_major(x, contraction_dim)
+    if is_mxfp8(fmt):
+        dt = str_to_dtype_fp8(fmt)
+        codes, sf = T.quantize_mxfp8(m, axis, fmt_of(dt), SF_NATURAL)
+        outer, c = codes.shape
+        scale = torch.exp2(sf.view(outer, c // 32).float() - 127.0)
+        deq = (codes.view(dt).float().view(outer, c // 32, 32) * scale.unsqueeze(-1)).view(outer, c)
+    else:
+        packed, sf, ts = T.quantize_nvfp4(m, axis, SF_NATURAL)
+        outer, c = packed.shape[0], packed.shape[1] * 2
+        lut = torch.tensor(_E2M1_LUT + [-v for v in _E2M1_LUT], device=x.device)
+        vals = torch.stack((lut[(packed & 0xF).long()], lut[(packed >> 4).long()]), dim=-1).view(outer, c)
+        eff = sf.view(outer, c // 16).view(torch.float8_e4m3fn).float() * ts
+        deq = (vals.view(outer, c // 16, 16) * eff.unsqueeze(-1)).view(outer, c)
+    deq = deq.to(x.dtype)                       # (outer, C)
+    return deq if contraction_dim == 1 else deq.t()
+
+
+def _fake_quant(x, fmt, dim, contraction_dim):
+    """dequant(quant(x)) for one operand in its format; identity for passthrough formats."""
+    if is_fp8(fmt):
+        return fake_quantize_fp8(x, str_to_dtype_fp8(fmt), dim=dim)
+    if is_mxfp8(fmt) or is_nvfp4(fmt):
+        return _fake_quant_block(x, fmt, contraction_dim)
+    if is_int8s(fmt):
+        raise NotImplementedError("the int8-series formats are outside this build's hot path")
+    return x
+
+
+def _gemm(a, b, a_fmt, b_fmt, out_dtype, rowwise=False):
+    """`a @ b` dispatched on the operands' format families."""
+    if is_fp8(a_fmt) and is_fp8(b_fmt):
+        return fp8_gemm(a, b, out_dtype, str_to_dtype_fp8(a_fmt), str_to_dtype_fp8(b_fmt), rowwise=rowwise)
+    if is_mxfp8(a_fmt) and is_mxfp8(b_fmt):
+        return mxfp8_gemm(a, b, out_dtype, str_to_dtype_fp8(a_fmt), str_to_dtype_fp8(b_fmt))
+    if is_nvfp4(a_fmt) and is_nvfp4(b_fmt):
+        return nvfp4_gemm(a, b, out_dtype)
+    if is_int8s(a_fmt) or is_int8s(b_fmt):
+        raise NotImplementedError("the int8-series formats are outside this build's hot path")
+    if is_quantized(a_fmt):
+        a = _fake_quant(a, a_fmt, -1 if rowwise else None, 1)
+    if is_quantized(b_fmt):
+        b = _fake_quant(b, b_fmt, 0 if rowwise else None, 0)
+    return (a @ b).to(out_dtype)
+
+
+class QuantizedLinearFn(torch.autograd.Function):
+    """y = x . W^T (+ bias) with the three GEMMs of a linear layer quantized per ``cfg``:
+    fprop act x weight, dgrad input_grad x weight, wgrad weight_grad x act
+    (src/quant/linear.py:59-115)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, cfg: QuantConfig):
+        dev = x.device.type
+        compute_dtype = torch.get_autocast_dtype(dev) if torch.is_autocast_enabled(dev) else x.dtype
+        rowwise = cfg.scaling["granularity"] == "rowwise"
+        x2d = x.reshape(-1, x.shape[-1]).to(compute_dtype)
+        w = weight.to(compute_dtype)
+        y = _gemm(x2d, w.t(), cfg.dtype["act"], cfg.dtype["weight"], compute_dtype, rowwise)
+        if bias is not None:
+            y = y + bias.to(compute_dtype)
+        ctx.save_for_backward(x2d, w)
+        ctx.cfg, ctx.has_bias = cfg, bias is not None
+        ctx.x_shape, ctx.x_dtype, ctx.w_dtype = x.shape, x.dtype, weight.dtype
+        return y.reshape(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x2d, w = ctx.saved_tensors
+        cfg = ctx.cfg
+        dt = x2d.dtype
+        g = grad_out.reshape(-1, grad_out.shape[-1]).to(dt)          # (M, N)
+        rowwise = cfg.scaling["granularity"] == "rowwise"
+        dx = _gemm(g, w, cfg.dtype["input_grad"], cfg.dtype["weight"], dt, rowwise)        # (M,N)@(N,K)
+        dw = _gemm(g.t(), x2d, cfg.dtype["weight_grad"], cfg.dtype["act"], dt, rowwise)    # (N,M)@(M,K)
+        db = g.sum(dim=0).to(ctx.w_dtype) if ctx.has_bias else None
+        return dx.reshape(*ctx.x_shape).to(ctx.x_dtype), dw.to(ctx.w_dtype), db, None
+
+
+class QuantLinear(nn.Module):
+    """Drop-in for ``nn.Linear``: same parameter names and shapes (state-dict compatible), keeps
+    the high-precision master weight; only the GEMMs run quantized."""
+
+    def __init__(self, in_features, out_features, bias, cfg: QuantConfig):
+        super().__init__()
+        self.in_features, self.out_features, self.cfg = in_features, out_features, cfg
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.bias = nn.Parameter(torch.empty(out_features)) if bias else None
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, cfg: QuantConfig) -> "QuantLinear":
+        q = cls(linear.in_features, linear.out_features, linear.bias is not None, cfg)
+        with torch.no_grad():
+            q.weight.copy_(linear.weight)
+            if linear.bias is not None:
+                q.bias.copy_(linear.bias)
+        return q.to(linear.weight.device, linear.weight.dtype)
+
+    def forward(self, x):
+        return QuantizedLinearFn.apply(x, self.weight, self.bias, self.cfg)
+
+    def extra_repr(self):
+        return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}"

@@ -1,0 +1,156 @@
+"""Host logic of the quantized-linear front end (config, rule matching, converter): the cases
+the reference's own tests cover (tests/fast/utils/test_config.py:712-872,
+tests/fast/quant/test_utils.py, tests/fast/quant/test_converter.py), plus the block-scaled
+extensions.  No GPU needed."""
+
+from types import SimpleNamespace
+
+import pytest
+import torch
+import torch.nn as nn
+
+from pretrain_b200.quant import QUANT_DTYPE_RECIPES, QUANT_FORMATS, QUANT_GRANULARITY
+from pretrain_b200.quant.config import QuantConfig, TrainingConfig
+from pretrain_b200.quant.convert import apply_quantization
+from pretrain_b200.quant.linear import QuantLinear
+from pretrain_b200.quant.utils import (is_fp8, is_mxfp8, is_nvfp4, is_quantized, resolve_rule, should_quantize,
+                                       str_to_dtype_fp8, str_to_qmax_int8s)
+
+
+def _only(tc):
+    assert len(tc.quant) == 1
+    return tc.quant[0]
+
+
+def test_defaults_disabled_and_inert():
+    q = QuantConfig()
+    assert q.enabled is False and q.exclude == ["lm_head"] and q.include == []
+    assert q.dtype == {} and q.scaling == {}
+    QuantConfig(enabled=False, dtype={"weight": "not_a_fmt"})     # not validated when off
+
+
+def test_operand_defaults_follow_mixed_precision():
+    r = _only(TrainingConfig(mixed_precision="bf16", quant={"enabled": True}))
+    assert r.dtype == {k: "bf16" for k in ("weight", "act", "input_grad", "weight_grad")}
+    assert _only(TrainingConfig(mixed_precision="no", quant={"enabled": True})).dtype["weight"] == "fp32"
+    r2 = _only(TrainingConfig(quant={"enabled": True, "dtype": {"weight": "fp8"}}))
+    assert r2.dtype == {"weight": "fp8", "act": "bf16", "input_grad": "bf16", "weight_grad": "bf16"}
+    assert _only(TrainingConfig(quant={"enabled": False})).dtype == {}
+
+
+def test_fp8_recipe_and_overrides():
+    q = QuantConfig(enabled=True, dtype_recipe="fp8")
+    assert q.dtype == {"weight": "fp8_e4m3", "act": "fp8_e4m3", "input_grad": "fp8_e5m2", "weight_grad": "fp8_e5m2"}
+    assert q.scaling["granularity"] == "tensorwise"
+    q = QuantConfig(enabled=True, dtype_recipe="fp8", dtype={"weight_grad": "bf16"})
+    assert q.dtype["weight"] == "fp8_e4m3" and q.dtype["weight_grad"] == "bf16" and q.dtype["input_grad"] == "fp8_e5m2"
+    q = QuantConfig(enabled=True, dtype_recipe="fp8", scaling={"granularity": "rowwise"})
+    assert q.scaling["granularity"] == "rowwise"
+
+
+def test_validation_errors():
+    with pytest.raises(ValueError, match="dtype_recipe"):
+        QuantConfig(enabled=True, dtype_recipe="fp3")
+    with pytest.raises(ValueError, match="unknown quant fmt"):
+        QuantConfig(enabled=True, dtype={"weight": "not_a_fmt"})
+    with pytest.raises(ValueError, match="dtype key"):
+        QuantConfig(enabled=True, dtype={"grad_weight": "bf16"})
+    with pytest.raises(ValueError, match="granularity"):
+        QuantConfig(enabled=True, dtype_recipe="fp8", scaling={"granularity": "row"})
+
+
+def test_rule_list_normalisation():
+    tc = TrainingConfig(quant=[{"enabled": True, "dtype_recipe": "fp8", "include": ["*.mlp.*"]},
+                               {"enabled": True, "dtype": {"weight": "fp8"}, "include": ["*.attn.*"]}])
+    assert len(tc.quant) == 2 and tc.quant[0].include == ["*.mlp.*"]
+    assert tc.quant[1].dtype == {"weight": "fp8", "act": "bf16", "input_grad": "bf16", "weight_grad": "bf16"}
+    r = TrainingConfig(quant={"enabled": True, "dtype_recipe": "fp8"}).quant[0]
+    assert r.dtype["input_grad"] == r.dtype["weight_grad"] == "fp8_e5m2" and "grad" not in r.dtype
+
+
+def test_block_scaled_extensions():
+    assert {"mxfp8", "nvfp4"} <= set(QUANT_DTYPE_RECIPES) and "blockwise" in QUANT_GRANULARITY
+    assert {"mxfp8_e4m3", "mxfp8_e5m2", "nvfp4", "fp4_nv"} <= QUANT_FORMATS
+    q = QuantConfig(enabled=True, dtype_recipe="mxfp8")
+    assert q.scaling == {"granularity": "blockwise", "block_size": 32}
+    assert q.dtype["weight"] == "mxfp8_e4m3" and q.dtype["input_grad"] == "mxfp8_e5m2"
+    q = QuantConfig(enabled=True, dtype_recipe="nvfp4")
+    assert q.scaling == {"granularity": "blockwise", "block_size": 16}
+    # plain fp8 names under blockwise scaling are read as their MX forms
+    q = QuantConfig(enabled=True, dtype_recipe="fp8", scaling={"granularity": "blockwise", "block_size": 32})
+    assert q.dtype["act"] == "mxfp8_e4m3" and q.dtype["weight_grad"] == "mxfp8_e5m2"
+    with pytest.raises(ValueError, match="block_size"):
+        QuantConfig(enabled=True, dtype_recipe="mxfp8", scaling={"granularity": "blockwise", "block_size": 64})
+    with pytest.raises(ValueError, match="blockwise"):
+        QuantConfig(enabled=True, dtype_recipe="nvfp4", scaling={"granularity": "rowwise"})
+
+
+def test_format_predicates():
+    assert is_fp8("fp8") and is_fp8("fp8_e5m2") and not is_fp8("mxfp8")
+    assert is_mxfp8("mxfp8_e5m2") and is_nvfp4("fp4_nv") and not is_quantized("bf16")
+    assert str_to_dtype_fp8("fp8") == torch.float8_e4m3fn and str_to_dtype_fp8("mxfp8_e5m2") == torch.float8_e5m2
+    assert str_to_dtype_fp8("bf16") is None
+    assert [str_to_qmax_int8s(f) for f in ("int8", "int7", "int4")] == [127, 63, 7]
+
+
+def test_rule_matching():
+    cfg = QuantConfig(enabled=True, dtype_recipe="fp8")
+    assert should_quantize("blocks.0.mlp.down_proj", cfg) and not should_quantize("lm_head", cfg)
+    cfg = QuantConfig(enabled=True, dtype_recipe="fp8", include=["*.mlp.*"], exclude=["down_proj"])
+    assert should_quantize("blocks.0.mlp.gate_up_proj", cfg)
+    assert not should_quantize("blocks.0.mlp.down_proj", cfg)       # exclude wins, leaf-name match
+    assert not should_quantize("blocks.0.attn.q_proj", cfg)
+    off = QuantConfig(enabled=False)
+    mlp = QuantConfig(enabled=True, dtype_recipe="fp8", include=["*.mlp.*"])
+    rest = QuantConfig(enabled=True, dtype_recipe="mxfp8")
+    assert resolve_rule("blocks.1.mlp.down_proj", [off, mlp, rest]) is mlp
+    assert resolve_rule("blocks.1.attn.o_proj", [off, mlp, rest]) is rest
+    assert resolve_rule("lm_head", [off, mlp, rest]) is None
+
+
+class _Tiny(nn.Module):
+    def __init__(self, tie=False):
+        super().__init__()
+        self.embed = nn.Embedding(32, 16)
+        self.blocks = nn.ModuleList([nn.ModuleDict({"mlp": nn.Sequential(nn.Linear(16, 64), nn.Linear(64, 16)),
+                                                    "attn": nn.ModuleDict({"q_proj": nn.Linear(16, 16, bias=False)})})])
+        self.lm_head = nn.Linear(16, 32, bias=False)
+        self.proj_tied = nn.Linear(16, 32, bias=False)
+        if tie:
+            self.proj_tied.weight = self.embed.weight
+
+
+def _cfg(quant):
+    return SimpleNamespace(training=TrainingConfig(quant=quant))
+
+
+def test_converter_disabled_is_noop_and_passthrough_rule_swaps_nothing():
+    m = apply_quantization(_Tiny(), _cfg({"enabled": False}))
+    assert not any(isinstance(x, QuantLinear) for x in m.modules())
+    m = apply_quantization(_Tiny(), _cfg({"enabled": True}))         # every operand passthrough
+    assert not any(isinstance(x, QuantLinear) for x in m.modules())
+
+
+@pytest.mark.skipif(torch.cuda.is_available() and torch.cuda.get_device_capability()[0] == 10, reason="needs a non-B200 host")
+def test_converter_raises_without_capable_gpu():
+    with pytest.raises(RuntimeError, match="requires"):
+        apply_quantization(_Tiny(), _cfg({"enabled": True, "dtype_recipe": "mxfp8"}))
+    with pytest.raises(RuntimeError, match="not built"):
+        apply_quantization(_Tiny(), _cfg({"enabled": True, "dtype_recipe": "int8"}))
+
+
+def test_converter_swaps_by_rule(monkeypatch):
+    from pretrain_b200.quant import fp8
+    monkeypatch.setattr(fp8, "is_supported", lambda: True)
+    m = _Tiny(tie=True)
+    w0 = m.blocks[0]["mlp"][0].weight.detach().clone()
+    with pytest.warns(UserWarning, match="tied"):
+        apply_quantization(m, _cfg([{"enabled": True, "dtype_recipe": "nvfp4", "include": ["*.mlp.*"]},
+                                    {"enabled": True, "dtype_recipe": "fp8", "scaling": {"granularity": "rowwise"}}]))
+    mlp0, q = m.blocks[0]["mlp"][0], m.blocks[0]["attn"]["q_proj"]
+    assert isinstance(mlp0, QuantLinear) and mlp0.cfg.dtype["weight"] == "nvfp4"
+    assert isinstance(q, QuantLinear) and q.cfg.dtype["weight"] == "fp8_e4m3" and q.bias is None
+    assert torch.equal(mlp0.weight, w0) and mlp0.bias is not None
+    assert type(m.lm_head) is nn.Linear                    # default exclude
+    assert type(m.proj_tied) is nn.Linear                  # tie guard
+    assert set(mlp0.state_dict()) == {"weight", "bias"}    # state-dict compatible with nn.Linear
