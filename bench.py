@@ -1,0 +1,333 @@
+"""Benchmark of the low-precision linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One "step" is one pass of the path over one batch of synthetic operands already in HBM:
+quantize A (bf16 -> MXFP8), quantize B, block-scaled GEMM D = A . B^T (bf16 out) — what
+`_gemm(a, b, "mxfp8", "mxfp8", ...)` does for one linear layer.  The default workload is the
+square 8192^3 case the GEMM targets are quoted on.  With N > 1 (launched by torchrun, one rank
+per GPU) every rank runs the same step on its own M-shard of a problem that is N times taller
+(weak scaling, B replicated, no collective on the data path); the output all-gather the
+M-sharded layout would need for a replicated result is timed separately and reported under
+"allgather".
+
+Prints ONE JSON line (rank 0).  `value` is device-timed whole-job TFLOPS; `e2e` is the same
+metric through the public `_gemm` call with host buffers (H2D of both operands and D2H of the
+result inside the timed region); `roofline` is the GEMM kernel against the measured tensor
+peak; `cpu_baseline` is the oracle's fake-quantize-then-matmul on this box's host cores.
+`--impl reference` times that CPU path alone.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "block-scaled GEMM TFLOPS/GPU (linear step: quantize A + quantize B + GEMM)"
+WORKLOADS = {
+    # name: (kind, M, N, K)
+    "mxfp8_square_8192": ("mxfp8", 8192, 8192, 8192),
+    "nvfp4_square_8192": ("nvfp4", 8192, 8192, 8192),
+    "mxfp8_square_4096": ("mxfp8", 4096, 4096, 4096),
+    "mxfp8_gpt2_mlp_up": ("mxfp8", 8192, 3072, 768),
+    "fp8_rowwise_linear_16384x2048x2048": ("fp8", 16384, 2048, 2048),
+}
+NOMINAL_TFLOPS = {"mxfp8": 4500.0, "fp8": 4500.0, "nvfp4": 9000.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the ncu captures summarised
+# under profiles/ (null until captured for that workload)
+GEMM_DRAM_TRAFFIC = {}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].startswith("Active") for r in self.rows)]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the oracle's emulated path (fake-quantize each operand along K, bf16 matmul)
+# ------------------------------------------------------------------------------------------
+def cpu_step(kind, a, b):
+    from oracle import restate as R
+    if kind == "mxfp8":
+        ca, sa = R.quantize_mxfp8(a, -1)
+        cb, sb = R.quantize_mxfp8(b, -1)
+        fa, fb = R.dequantize_mxfp8(ca, sa).bfloat16(), R.dequantize_mxfp8(cb, sb).bfloat16()
+    elif kind == "nvfp4":
+        pa, sa, ta = R.quantize_nvfp4(a, -1)
+        pb, sb, tb = R.quantize_nvfp4(b, -1)
+        fa, fb = R.dequantize_nvfp4(pa, sa, ta).bfloat16(), R.dequantize_nvfp4(pb, sb, tb).bfloat16()
+    else:
+        fa, fb = R.fake_quantize_fp8(a, torch.float8_e4m3fn, dim=-1), R.fake_quantize_fp8(b, torch.float8_e4m3fn, dim=-1)
+    return fa @ fb.t()
+
+
+def cpu_sample_shape(kind, m, n, k):
+    """A bounded slice of the workload: full K, operands cut so one step is ~0.5 TFLOP."""
+    budget = 5.5e11
+    ms = max(128, min(m, int(budget / (2 * n * k)) // 128 * 128))
+    ns = n if 2 * ms * n * k <= 2 * budget else max(128, int(budget / (2 * ms * k)) // 128 * 128)
+    return ms, ns, k
+
+
+def run_cpu(kind, m, n, k, steps, warmup):
+    ms, ns, ks = cpu_sample_shape(kind, m, n, k)
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(ms, ks, generator=g).bfloat16()
+    b = torch.randn(ns, ks, generator=g).bfloat16()
+    for _ in range(warmup):
+        cpu_step(kind, a, b)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(kind, a, b)
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": 2.0 * ms * ns * ks / dt / 1e12, "unit": "TFLOPS", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{ms}x{ns}x{ks} slice of the {m}x{n}x{k} workload, {steps} step(s) after {warmup} warm-up",
+            "ms_per_step": dt * 1e3}
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def make_step(kind, a, b, out):
+    """Returns (step_fn, gemm_only_fn_factory, launches_per_step).  step_fn records CUDA events
+    around the GEMM launch into `marks`."""
+    from pretrain_b200 import ops
+    E4 = torch.float8_e4m3fn
+
+    def step(marks=None):
+        if kind == "mxfp8":
+            ca, sfa = ops.quantize_mxfp8(a, 1)
+            cb, sfb = ops.quantize_mxfp8(b, 1)
+            if marks is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e0.record()
+            ops.gemm_mxfp8(ca, sfa, cb, sfb, out=out)
+        elif kind == "nvfp4":
+            aa, ab = ops.amax(a), ops.amax(b)
+            pa, sfa, ta = ops.quantize_nvfp4(a, 1, aa)
+            pb, sfb, tb = ops.quantize_nvfp4(b, 1, ab)
+            if marks is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e0.record()
+            ops.gemm_nvfp4(pa, sfa, ta, pb, sfb, tb, out=out)
+        else:
+            ca, sa = ops.quantize_fp8(a, E4, 1)
+            cb, sb = ops.quantize_fp8(b, E4, 1)
+            if marks is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e0.record()
+            ops.gemm_fp8(ca, E4, cb, E4, sa, sb, out=out)
+        if marks is not None:
+            e1 = torch.cuda.Event(enable_timing=True); e1.record()
+            marks.append((e0, e1))
+        return out
+
+    launches = {"mxfp8": 3, "nvfp4": 5, "fp8": 3}[kind]
+    return step, launches
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
+    ap.add_argument("--workload", default="mxfp8_square_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    kind, m, n, k = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": args.workload, "kind": kind, "M_per_gpu": m, "N": n, "K": k,
+              "sharding": "rows of A (M) across ranks, B replicated" if world > 1 else "single GPU",
+              "l2": "operands, codes and output of a step total > 126 MB (larger than L2); no flush needed"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+        cb = run_cpu(kind, m, n, k, steps, warm)
+        print(json.dumps({"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOPS", "n_gpus": args.gpus,
+                          "steps": steps, "warmup": warm, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "bf16 matmul of fake-quantized operands (CPU)",
+                          "data": "synthetic", "config": config,
+                          "cpu_baseline": {k2: cb[k2] for k2 in ("value", "unit", "cores", "kind", "sample")},
+                          "e2e": {"value": cb["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path for the product arm")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from pretrain_b200 import build, ops
+    if rank == 0:
+        build.build()
+    if dist is not None:
+        dist.barrier()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    a = torch.randn(m, k, generator=g, device="cuda", dtype=torch.bfloat16)
+    gb = torch.Generator(device="cuda").manual_seed(99)
+    b = torch.randn(n, k, generator=gb, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    step, launches = make_step(kind, a, b, out)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    marks = []
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        barrier()
+        t0.record()
+        for _ in range(args.steps):
+            step(marks)
+        t1.record()
+        barrier()
+    ops.device_status()
+    ms_total = t0.elapsed_time(t1)
+    gemm_ms = sum(e0.elapsed_time(e1) for e0, e1 in marks) / len(marks)
+    if dist is not None:
+        t = torch.tensor([ms_total, gemm_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, gemm_ms = t.tolist()
+    ms_step = ms_total / args.steps
+    flops = 2.0 * m * n * k
+    value = world * flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public call, host buffers --------------------------------
+    from pretrain_b200.quant.linear import _gemm
+    fmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3"}[kind]
+    ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
+    hout = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        da, db = ha.to("cuda", non_blocking=True), hb.to("cuda", non_blocking=True)
+        d = _gemm(da, db.t(), fmt, fmt, torch.bfloat16, rowwise=True)
+        hout.copy_(d, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": ha.numel() * 2 + hb.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2}
+
+    # ---- output all-gather of the M-sharded layout (not on the data path; reported beside) --
+    allgather = None
+    if dist is not None:
+        full = torch.empty(world * m, n, device="cuda", dtype=torch.bfloat16)
+        for _ in range(2):
+            dist.all_gather_into_tensor(full, out)
+        barrier()
+        t0.record()
+        for _ in range(5):
+            step()
+            dist.all_gather_into_tensor(full, out)
+        t1.record()
+        barrier()
+        t = torch.tensor([t0.elapsed_time(t1) / 5], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ag_ms = t.item()
+        allgather = {"ms_per_step_with_allgather": ag_ms, "tflops_with_allgather": world * flops / (ag_ms * 1e-3) / 1e12,
+                     "bytes_received_per_rank": (world - 1) * m * n * 2, "collective": "ncclAllGather (NCCL over NVLink)"}
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    # fp8 / fp4 tensor peak is not measured directly: the driver's measured bf16 cuBLAS rate,
+    # sustained (this kernel is timed inside a seconds-long loop), times the format's rate ratio
+    ratio = {"mxfp8": 2.0, "fp8": 2.0, "nvfp4": 4.0}[kind]
+    peak = peaks["bf16_tflops_sustained"] * ratio
+    achieved = flops / (gemm_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": f"gemm_kernel<{kind}>", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "peak_source": f"{ratio:g} x bf16_tflops_sustained, {peaks['source']}",
+                "frac_of_nominal": achieved / NOMINAL_TFLOPS[kind], "nominal_peak": NOMINAL_TFLOPS[kind],
+                "traffic": GEMM_DRAM_TRAFFIC.get(args.workload), "kernel_ms": gemm_ms}
+    line = {"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind,
+            "data": "synthetic", "config": config, "clocks": clk.summary(), "e2e": e2e, "gpu_launches": launches * args.steps,
+            "roofline": roofline}
+    if allgather is not None:
+        line["allgather"] = allgather
+    if world == 1 and not args.no_cpu_baseline:
+        cb = run_cpu(kind, m, n, k, 2, 1)
+        line["cpu_baseline"] = {k2: cb[k2] for k2 in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,139 @@
+"""QuantLinear / QuantizedLinearFn / _gemm on the GPU, in the style of the reference's
+tests/fast/quant/test_linear.py: forward and the two backward GEMMs against the oracle's
+fake-quantize-then-matmul, dtype plumbing under autocast, and tracing with torch.compile."""
+
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import restate as R
+
+pytestmark = pytest.mark.gpu
+E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _built():
+    from pretrain_b200 import build
+    build.build()
+
+
+def _cfg(recipe, granularity=None, **dtype):
+    from pretrain_b200.quant.config import TrainingConfig
+    q = {"enabled": True, "dtype_recipe": recipe, "dtype": dict(dtype)}
+    if granularity:
+        q["scaling"] = {"granularity": granularity}
+    return TrainingConfig(quant=q).quant[0]
+
+
+def _rel(out, ref):
+    return ((out.float() - ref.float()).norm() / ref.float().norm()).item()
+
+
+def _oracle_gemm(kind, a, b, a_dt=E4, b_dt=E4):
+    """a (M,K) @ b (K,N) on the CPU oracle, operands scaled along K."""
+    if kind == "fp8_rowwise":
+        return R.fp8_gemm_ref(a, b, torch.bfloat16, a_dt, b_dt, rowwise=True)
+    if kind == "fp8_tensorwise":
+        return R.fp8_gemm_ref(a, b, torch.bfloat16, a_dt, b_dt, rowwise=False)
+    if kind == "mxfp8":
+        return R.mxfp8_gemm_ref(a, b, torch.bfloat16, a_dt, b_dt)
+    return R.nvfp4_gemm_ref(a, b)
+
+
+CASES = [("fp8", "rowwise", "fp8_rowwise"), ("fp8", None, "fp8_tensorwise"), ("mxfp8", None, "mxfp8"), ("nvfp4", None, "nvfp4")]
+
+
+@pytest.mark.parametrize("recipe,gran,kind", CASES)
+def test_gemm_seam_matches_oracle_in_all_three_layouts(recipe, gran, kind):
+    """fprop / dgrad / wgrad call shapes of src/quant/linear.py:74,98,102 (views included)."""
+    from pretrain_b200.quant.linear import _gemm
+    cfg = _cfg(recipe, gran)
+    g = torch.Generator().manual_seed(0)
+    M, K, N = 256, 128, 192
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (0.05 * torch.randn(N, K, generator=g)).bfloat16()
+    dy = (1e-2 * torch.randn(M, N, generator=g)).bfloat16()
+    xd, wd, dyd = x.cuda(), w.cuda(), dy.cuda()
+    rw = gran == "rowwise"
+    e5 = E4 if recipe == "nvfp4" else E5
+    y = _gemm(xd, wd.t(), cfg.dtype["act"], cfg.dtype["weight"], torch.bfloat16, rw)
+    assert y.shape == (M, N) and _rel(y.cpu(), _oracle_gemm(kind, x, w.t())) < 0.01
+    dx = _gemm(dyd, wd, cfg.dtype["input_grad"], cfg.dtype["weight"], torch.bfloat16, rw)
+    assert dx.shape == (M, K) and _rel(dx.cpu(), _oracle_gemm(kind, dy, w, e5, E4)) < 0.01
+    dw = _gemm(dyd.t(), xd, cfg.dtype["weight_grad"], cfg.dtype["act"], torch.bfloat16, rw)
+    assert dw.shape == (N, K) and _rel(dw.cpu(), _oracle_gemm(kind, dy.t(), x, e5, E4)) < 0.01
+
+
+def test_mixed_formats_fall_to_fake_quant_matmul():
+    from pretrain_b200.quant.linear import _gemm
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(64, 128, generator=g).bfloat16()
+    b = torch.randn(128, 96, generator=g).bfloat16()
+    out = _gemm(a.cuda(), b.cuda(), "fp8_e4m3", "bf16", torch.bfloat16, rowwise=True)
+    ref = (R.fake_quantize_fp8(a, E4, dim=-1).float() @ b.float()).bfloat16()
+    assert _rel(out.cpu(), ref) < 0.01
+    out = _gemm(a.cuda(), b.cuda(), "bf16", "mxfp8", torch.bfloat16)
+    cb, sb = R.quantize_mxfp8(b, 0)
+    ref = (a.float() @ R.dequantize_mxfp8(cb, sb).t()).bfloat16()
+    assert _rel(out.cpu(), ref) < 0.01
+    with pytest.raises(NotImplementedError):
+        _gemm(a.cuda(), b.cuda(), "int8", "int8", torch.bfloat16)
+
+
+@pytest.mark.parametrize("recipe,gran,kind", CASES)
+def test_module_forward_backward(recipe, gran, kind):
+    from pretrain_b200.quant.linear import QuantLinear
+    torch.manual_seed(0)
+    lin = nn.Linear(128, 96, bias=True)
+    q = QuantLinear.from_linear(lin, _cfg(recipe, gran)).cuda()
+    assert torch.equal(q.weight.cpu(), lin.weight) and torch.equal(q.bias.cpu(), lin.bias)
+    x = torch.randn(4, 16, 128)                       # batch dims are flattened and restored
+    xd = x.cuda().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = q(xd)
+    assert y.shape == (4, 16, 96) and y.dtype == torch.bfloat16
+    ref = _oracle_gemm(kind, x.reshape(-1, 128).bfloat16(), lin.weight.detach().bfloat16().t()).float() + lin.bias.detach()
+    assert _rel(y.float().cpu().reshape(-1, 96), ref) < 0.05     # module tolerance of the reference's tests
+    y.float().square().mean().backward()
+    assert xd.grad.dtype == torch.float32 and xd.grad.shape == x.shape
+    assert q.weight.grad.dtype == torch.float32 and q.weight.grad.shape == (96, 128)   # master-weight dtype
+    assert q.bias.grad is not None and torch.isfinite(q.weight.grad).all()
+
+
+def test_hp_weight_grad_differs_from_quantized():
+    from pretrain_b200.quant.linear import QuantLinear
+    torch.manual_seed(0)
+    lin = nn.Linear(64, 64, bias=False)
+    x = torch.randn(128, 64).cuda()
+    grads = []
+    for cfg in (_cfg("fp8", "rowwise"), _cfg("fp8", "rowwise", weight_grad="bf16")):
+        q = QuantLinear.from_linear(lin, cfg).cuda()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            q(x).float().square().mean().backward()
+        grads.append(q.weight.grad.clone())
+    assert not torch.equal(grads[0], grads[1]) and _rel(grads[0], grads[1]) < 0.1
+
+
+def test_swapped_model_trains_one_step_and_compiles():
+    from types import SimpleNamespace
+    from pretrain_b200.quant.config import TrainingConfig
+    from pretrain_b200.quant.convert import apply_quantization
+    from pretrain_b200.quant.linear import QuantLinear
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(128, 256), nn.SiLU(), nn.Linear(256, 128)).cuda()
+    cfg = SimpleNamespace(training=TrainingConfig(quant={"enabled": True, "dtype_recipe": "mxfp8", "exclude": []}))
+    apply_quantization(model, cfg)
+    assert sum(isinstance(m, QuantLinear) for m in model.modules()) == 2
+    opt = torch.optim.SGD(model.parameters(), lr=1e-2)
+    x = torch.randn(64, 128, device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        eager = model(x)
+        loss = eager.float().square().mean()
+    loss.backward()
+    opt.step()
+    assert torch.isfinite(loss)
+    compiled = torch.compile(model, fullgraph=True)
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        a, b = model(x), compiled(x)
+    assert torch.equal(a, b)
