@@ -108,6 +108,65 @@ int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* 
                      const float* tsA, const float* tsB, int64_t M, int64_t N, int64_t K, void* D,
                      int64_t ldd, void* stream);
 
+/* ---- MoE: top-k permute, ragged grouped GEMM, SwiGLU, weighted unpermute ------------------
+ * Layout used between these calls ("padded expert-sorted"): rows sorted by expert in the
+ * reference's order (stable sort of the flattened (token, slot) pairs by expert id,
+ * src/layers/mlp.py:447-452), each expert's segment starting on a multiple of 128 rows so
+ * that every 128-row GEMM tile belongs to one expert; pad rows are zero.
+ */
+
+/* Rows of the padded layout for n_pairs = T*k routed pairs and E experts (upper bound, a
+ * multiple of 128), and bytes of the scratch buffer b200q_moe_permute_plan needs. */
+int64_t b200q_moe_padded_rows(int64_t n_pairs, int E);
+int64_t b200q_moe_plan_workspace_bytes(int64_t n_pairs, int E);
+
+/* Permute plan from the router's choice (src/layers/mlp.py:446-457).  top_idx: int64 [T*k]
+ * expert ids, token-major.  Outputs (device): offs int32 [E] cumulative ends of the unpadded
+ * segments (the reference's `offs`); padded_offs int32 [E+1] first padded row of each expert;
+ * row_of int32 [T*k] padded row of every (token, slot); src_of_row int32 [padded_rows] token
+ * of every padded row, -1 for pad rows; tile_expert int32 [padded_rows/128] expert of every
+ * 128-row tile, -1 beyond the last; num_tiles int32 [1].  E <= 256.  `workspace` holds
+ * b200q_moe_plan_workspace_bytes() bytes of scratch. */
+int b200q_moe_permute_plan(const int64_t* top_idx, int64_t n_pairs, int k, int E, int32_t* offs,
+                           int32_t* padded_offs, int32_t* row_of, int32_t* src_of_row,
+                           int32_t* tile_expert, int32_t* num_tiles, void* workspace, void* stream);
+
+/* The same plan outputs for rows that are ALREADY expert-sorted (the input convention of
+ * grouped_mlp, src/layers/mlp.py:55-72): offs int32 [E] cumulative ends; src_of_row maps a
+ * padded row to its row in the sorted input. */
+int b200q_moe_pad_plan(const int32_t* offs, int E, int64_t n_rows, int32_t* padded_offs,
+                       int32_t* src_of_row, int32_t* tile_expert, int32_t* num_tiles, void* stream);
+
+/* Gather rows into the padded layout: out row r = x[src_of_row[r]] (zero when -1), for the
+ * rows of the first *num_tiles tiles.  x bf16 [*, D] pitch ld; D % 32 == 0.
+ * quantize = 0: bf16 copy into `out` (the reference's x_flat[token_ids_sorted],
+ * src/layers/mlp.py:458).  quantize = 1: MXFP8 codes (fmt) into `out` and E8M0 scale factors,
+ * swizzled, into `sf`. */
+int b200q_moe_gather(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row,
+                     const int32_t* num_tiles, int64_t padded_rows, int quantize, int fmt, void* out,
+                     void* sf, void* stream);
+
+/* Ragged grouped GEMM (stands for torch._grouped_mm at src/layers/mlp.py:89,97):
+ * D[r, :] = A[r, :] . B[e(r)]^T for the padded layout.  A: MXFP8 codes [padded_rows, K] + sfA;
+ * B: codes [E*N, K] + sfB (each expert's [N, K] weight quantized along K, N % 128 == 0);
+ * D: bf16 [padded_rows, N].  Only the first *num_tiles row tiles are computed. */
+int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
+                             const void* sfB, const int32_t* tile_expert, const int32_t* num_tiles,
+                             int64_t padded_rows, int E, int64_t N, int64_t K, void* D, int64_t ldd,
+                             void* stream);
+
+/* h[r, 0:I] = silu(gate) * up with gate = g[r, 0:I], up = g[r, I:2I] (src/layers/activation.py:80-81,
+ * the step between the two grouped GEMMs, src/layers/mlp.py:92-94), rounded to bf16 as the
+ * reference does, then (quantize = 1) MXFP8-quantized along I into `out` + swizzled `sf`, or
+ * (quantize = 0) written as bf16.  I % 32 == 0. */
+int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantize, int fmt, void* out,
+                 void* sf, void* stream);
+
+/* Weighted unpermute (src/layers/mlp.py:472-477): out[t, :] = sum_j w[t, j] * y[row_of[t*k+j], :],
+ * accumulated in fp32 and rounded once to bf16.  y bf16 [padded_rows, D] pitch ldy; w bf16 [T, k]. */
+int b200q_moe_unpermute(const void* y, int64_t ldy, const void* w, const int32_t* row_of, int64_t T,
+                        int k, int64_t D, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

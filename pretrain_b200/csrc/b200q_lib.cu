@@ -2,3 +2,4 @@
 // inline helpers, so the sources are compiled together instead of with relocatable device code.
 #include "quantize.cu"
 #include "gemm.cu"
+#include "moe.cu"

@@ -5,6 +5,8 @@
 //   KIND_MX  : MXFP8, tcgen05.mma kind::mxf8f6f4.block_scale (E8M0 scale per 32 elements)
 //   KIND_NV  : NVFP4, tcgen05.mma kind::mxf4nvf4.block_scale.block16 (E4M3 scale per 16
 //              elements), fp32 tensor scales applied in the epilogue
+// and the ragged grouped form of KIND_MX (stands for torch._grouped_mm, src/layers/mlp.py:89,97),
+// where every 128-row tile of A belongs to one expert and B holds the experts' weights stacked.
 //
 // One persistent CTA per SM, 192 threads in three roles:
 //   warp 0    TMA producer: A/B tiles (128-byte-swizzled, K-major) and the scale-factor atoms of
@@ -12,12 +14,17 @@
 //   warp 1    MMA issuer: one thread copies the stage's scale factors to tensor memory
 //             (tcgen05.cp), issues the four K=32-byte tcgen05.mma of the stage, and commits to
 //             the stage's "empty" barrier; accumulators live in tensor memory;
-//   warps 2-5 epilogue: tcgen05.ld the fp32 accumulators (lane = row), scale, round to bf16,
-//             16-byte stores.  With two accumulator stages the epilogue of tile i overlaps the
-//             main loop of tile i+1.
+//   warps 2-5 epilogue: tcgen05.ld the fp32 accumulators (lane = row) 32 columns at a time,
+//             scale, round to bf16, stage a 32x32 block in 64-byte-swizzled shared memory and
+//             hand it to a TMA store (which also clips the ragged edges).  The accumulator is
+//             released as soon as its last column has been read, and with two accumulator
+//             stages (tile widths 128 and 192) the epilogue of tile i overlaps the main loop
+//             of tile i+1.
 // No cluster launch and no multicast: the same binary runs under any number of processes.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+
+#include <algorithm>
 
 namespace b200q {
 namespace {
@@ -28,19 +35,26 @@ constexpr int BM = 128;
 constexpr int BKB = 128;                 // bytes of K per stage (= one 128-byte swizzle row)
 constexpr int kGemmThreads = 192;
 constexpr int kSmemBudget = 227 * 1024;
+constexpr int EPI_COLS = 32;             // columns per epilogue block
+constexpr int EPI_BLOCK_BYTES = 32 * EPI_COLS * 2;
+constexpr int EPI_BYTES = 4 * 2 * EPI_BLOCK_BYTES;   // 4 warps x 2 buffers
+
+constexpr int cgcd(int a, int b) { return b == 0 ? a : cgcd(b, a % b); }
 
 template <int KIND, int BN_>
 struct Cfg {
   static constexpr int BN = BN_;
-  static constexpr int NB_ATOMS = (BN + 127) / 128;                        // 128-row groups of B
+  // A B tile that does not start on a multiple of 128 rows straddles one more 128-row group of
+  // scale factors; NB_ATOMS is the number of groups loaded per K step (enough for any offset).
+  static constexpr int MAX_OFF = 128 - cgcd(BN, 128);
+  static constexpr int NB_ATOMS = (MAX_OFF + BN + 127) / 128;
   static constexpr int K_ATOMS = KIND == KIND_NV ? 4 : 1;                  // 512-byte SF atoms per K step and row group
   static constexpr int A_BYTES = BM * BKB;
   static constexpr int B_BYTES = BN * BKB;
   static constexpr int SFA_BYTES = KIND == KIND_F8 ? 0 : K_ATOMS * 512;
   static constexpr int SFB_BYTES = KIND == KIND_F8 ? 0 : NB_ATOMS * K_ATOMS * 512;
   static constexpr int STAGE_BYTES = ((A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024) * 1024;
-  static constexpr int TX_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-  static constexpr int STAGES_RAW = (kSmemBudget - 2048) / STAGE_BYTES;
+  static constexpr int STAGES_RAW = (kSmemBudget - 2048 - EPI_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SFA_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS;
   static constexpr int SFB_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS * NB_ATOMS;
@@ -48,10 +62,15 @@ struct Cfg {
   static constexpr int SFA_COL0 = ACC_STAGES * BN;
   static constexpr int SFB_COL0 = SFA_COL0 + SFA_COLS;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tcgen05.mma with M=128 needs N % 16 == 0, N <= 256");
+  static constexpr int EPI_OFF = STAGES * STAGE_BYTES;                     // 1024-aligned
+  static constexpr int BAR_OFF = EPI_OFF + EPI_BYTES;
+  static constexpr int SMEM_BYTES = BAR_OFF + 256 /*barriers*/ + 1024 /*alignment slack*/;
+  // A B tile may start 64 rows into a 128-row scale-factor group (tensor-memory column offset 2);
+  // offsets of 32 or 96 rows (odd column offsets) are misaligned for the MMA's scale operand.
+  static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "tile width: multiple of 64");
   static_assert(SFB_COL0 + SFB_COLS <= TMEM_COLS, "tensor memory overflow");
   static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
+  static_assert(SMEM_BYTES <= kSmemBudget, "shared memory overflow");
 };
 
 struct GemmParams {
@@ -61,11 +80,12 @@ struct GemmParams {
   const float* scale_b;
   int a_scalar, b_scalar;
   int a_fmt, b_fmt;
-  int64_t M, N, K;         // K in elements
-  uint16_t* D;
-  int64_t ldd;
-  int num_m, num_n, num_k; // tiles
+  int64_t M, N, K;         // K in elements; grouped: M = padded rows, N = columns per expert
+  int num_m, num_n, num_k; // tiles (grouped: num_m is an upper bound, the true count is *num_tiles)
   int sf_kt;               // 512-byte atoms per row group along K in the SF buffers
+  int64_t sfb_groups;      // 128-row groups in the SF buffer of B
+  const int32_t* tile_expert;   // grouped: expert of every 128-row tile of A; null otherwise
+  const int32_t* num_tiles;     // grouped: device count of row tiles in use
 };
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m, int& n) {
@@ -85,22 +105,28 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 template <int KIND, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
   using C = Cfg<KIND, BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+  const uint32_t bar_base = smem_base + C::BAR_OFF;
   // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem ptr, abort
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + 2 + a); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 4));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::BAR_OFF + 8 * (2 * C::STAGES + 4));
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = p.num_m * p.num_n;
+  int num_m = p.num_m;
+  if (p.num_tiles != nullptr) {
+    const int live = __ldg(p.num_tiles);
+    num_m = live < num_m ? live : num_m;
+  }
+  const int total_tiles = num_m * p.num_n;
 
   if (KIND != KIND_F8) {
     // Scale-factor stage buffers start as zeros so that atoms beyond the end of K (never
@@ -118,6 +144,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
+    ptx::prefetch_tensormap(&tmap_d);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::TMEM_COLS);
@@ -135,7 +162,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(t, p.num_m, p.num_n, m_blk, n_blk);
+        tile_coords(t, num_m, p.num_n, m_blk, n_blk);
+        const int expert = p.tile_expert ? __ldg(p.tile_expert + m_blk) : 0;
+        const int64_t brow0 = (int64_t)expert * p.N + (int64_t)n_blk * BN;   // first row of the B tile
         for (int k = 0; k < p.num_k; ++k) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1) || *abort_flag) { ok = false; break; }
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
@@ -149,19 +178,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             ptx::mbar_expect_tx(fb, tx);
             const uint32_t ssfa = sb + C::B_BYTES, ssfb = ssfa + C::SFA_BYTES;
             ptx::bulk_load(ssfa, p.sfa + ((int64_t)m_blk * p.sf_kt + ka0) * 512, ka * 512, fb);
+            const int64_t g0 = brow0 >> 7;
 #pragma unroll
             for (int j = 0; j < C::NB_ATOMS; ++j) {
-              const int64_t rg = (int64_t)n_blk * BN / 128 + j;   // BN is a multiple of 128 whenever NB_ATOMS > 1
-              if (rg * 128 < p.N || j == 0)
-                ptx::bulk_load(ssfb + j * C::K_ATOMS * 512, p.sfb + (rg * p.sf_kt + ka0) * 512, ka * 512, fb);
-              else
-                ptx::bulk_load(ssfb + j * C::K_ATOMS * 512, p.sfb + (((int64_t)n_blk * BN / 128) * p.sf_kt + ka0) * 512, ka * 512, fb);
+              const int64_t rg = g0 + j < p.sfb_groups ? g0 + j : g0;     // past the end: any valid group
+              ptx::bulk_load(ssfb + j * C::K_ATOMS * 512, p.sfb + (rg * p.sf_kt + ka0) * 512, ka * 512, fb);
             }
           } else {
             ptx::mbar_expect_tx(fb, tx);
           }
           ptx::tma_load_2d(sa, &tmap_a, k * BKB, m_blk * BM, fb);
-          ptx::tma_load_2d(sb, &tmap_b, k * BKB, n_blk * BN, fb);
+          ptx::tma_load_2d(sb, &tmap_b, k * BKB, (int32_t)brow0, fb);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -175,6 +202,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, p.num_n, m_blk, n_blk);
+        const int expert = p.tile_expert ? __ldg(p.tile_expert + m_blk) : 0;
+        const int64_t brow0 = (int64_t)expert * p.N + (int64_t)n_blk * BN;
+        const uint32_t sfb_off = (uint32_t)(brow0 & 127) >> 5;   // B tile starts this many 32-row columns into its first SF group
         if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1) || *abort_flag) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -202,10 +234,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               ptx::mma_f8(d_tmem, da + adv, db + adv, ptx::idesc_f8(p.a_fmt, p.b_fmt, BM, BN), accum);
             } else if (KIND == KIND_MX) {
               ptx::mma_mxf8(d_tmem, da + adv, db + adv, ptx::idesc_block_scaled(p.a_fmt, p.b_fmt, 1, BM, BN, kk), accum,
-                            tmem_base + C::SFA_COL0, tmem_base + C::SFB_COL0);
+                            tmem_base + C::SFA_COL0, tmem_base + C::SFB_COL0 + sfb_off);
             } else {
               ptx::mma_nvf4(d_tmem, da + adv, db + adv, ptx::idesc_block_scaled(1, 1, 0, BM, BN, 0), accum,
-                            tmem_base + C::SFA_COL0 + 4 * kk, tmem_base + C::SFB_COL0 + 4 * C::NB_ATOMS * kk);
+                            tmem_base + C::SFA_COL0 + 4 * kk, tmem_base + C::SFB_COL0 + 4 * C::NB_ATOMS * kk + sfb_off);
             }
           }
           ptx::tc_commit(empty_bar(stage));   // stage reusable once these MMAs have read it
@@ -221,54 +253,78 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else {
     // ------------------------------- epilogue ------------------------------------------------
     const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
+    const uint32_t epi_s = smem_base + C::EPI_OFF + q * 2 * EPI_BLOCK_BYTES;
+    uint8_t* epi_g = smem_gen + C::EPI_OFF + q * 2 * EPI_BLOCK_BYTES;
+    int buf = 0;
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     float alpha = 1.f;
     if (KIND == KIND_NV) alpha = __ldg(p.scale_a) * __ldg(p.scale_b);
+    constexpr int NBLK = BN / EPI_COLS;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int m_blk, n_blk;
-      tile_coords(t, p.num_m, p.num_n, m_blk, n_blk);
+      tile_coords(t, num_m, p.num_n, m_blk, n_blk);
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase) || *abort_flag) { ok = false; break; }
       ptx::tc_fence_after();
-      const int64_t row = (int64_t)m_blk * BM + q * 32 + lane;
+      const int64_t row0 = (int64_t)m_blk * BM + q * 32, row = row0 + lane;
       const int64_t col0 = (int64_t)n_blk * BN;
       float row_scale = alpha;
       if (KIND == KIND_F8) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
-      uint16_t* drow = p.D + row * p.ldd;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        if (col0 + c >= p.N) break;               // warp-uniform
-        uint32_t r[16];
-        ptx::tmem_ld16(taddr + c, r);
-        ptx::tmem_ld_wait();
-        float f[16];
+
+      // One 32-column block: scale, round, stage in swizzled shared memory, TMA store.
+      auto emit = [&](int c, const uint32_t (&r)[32]) {
+        const int64_t colg = col0 + c * EPI_COLS;
+        float sbv = 1.f;
+        if (KIND == KIND_F8) sbv = p.b_scalar ? __ldg(p.scale_b) : (colg + lane < p.N ? __ldg(p.scale_b + colg + lane) : 0.f);
+        uint32_t o[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) f[i] = u2f(r[i]) * row_scale;
-        if (KIND == KIND_F8) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int64_t col = col0 + c + i;
-            f[i] *= p.b_scalar ? __ldg(p.scale_b) : (col < p.N ? __ldg(p.scale_b + col) : 0.f);
+        for (int i = 0; i < 16; ++i) {
+          float lo = u2f(r[2 * i]) * row_scale, hi = u2f(r[2 * i + 1]) * row_scale;
+          if (KIND == KIND_F8) {
+            lo *= __shfl_sync(0xFFFFFFFFu, sbv, 2 * i);
+            hi *= __shfl_sync(0xFFFFFFFFu, sbv, 2 * i + 1);
           }
+          o[i] = pack_bf16(lo, hi);
         }
-        if (row < p.M) {
+        if (lane == 0) ptx::bulk_wait_read<1>();      // the store that last read this buffer is done with it
+        __syncwarp();
+        uint8_t* dst = epi_g + buf * EPI_BLOCK_BYTES + lane * 64;
+        const int sw = (lane >> 1) & 3;               // 64-byte swizzle: 16-byte chunk j of row r sits at j ^ ((r >> 1) & 3)
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (col0 + c + 8 * h < p.N) {         // N % 8 == 0: whole 16-byte vectors
-              uint4 o;
-              o.x = pack_bf16(f[8 * h + 0], f[8 * h + 1]); o.y = pack_bf16(f[8 * h + 2], f[8 * h + 3]);
-              o.z = pack_bf16(f[8 * h + 4], f[8 * h + 5]); o.w = pack_bf16(f[8 * h + 6], f[8 * h + 7]);
-              *reinterpret_cast<uint4*>(drow + col0 + c + 8 * h) = o;
-            }
-          }
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(dst + ((j ^ sw) << 4)) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_2d(&tmap_d, (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
+          ptx::bulk_commit();
+        }
+        buf ^= 1;
+      };
+
+      uint32_t ra[32], rb[32];
+      ptx::tmem_ld32(taddr, ra);
+#pragma unroll
+      for (int c = 0; c < NBLK; ++c) {
+        ptx::tmem_ld_wait();
+        if (c + 1 < NBLK) {
+          if (c & 1) ptx::tmem_ld32(taddr + (c + 1) * EPI_COLS, ra);
+          else ptx::tmem_ld32(taddr + (c + 1) * EPI_COLS, rb);
+        } else {
+          // every column has been read: hand the accumulator back before the last block is stored
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+        }
+        if (col0 + c * EPI_COLS < p.N && row0 < p.M) {      // warp-uniform
+          if (c & 1) emit(c, rb);
+          else emit(c, ra);
         }
       }
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
       if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
     }
+    if (lane == 0) ptx::bulk_wait<0>();           // all stores of this warp have landed
     if (!ok && lane == 0) { *abort_flag = 1; atomicExch(&g_device_status, 3); }
   }
 
@@ -303,50 +359,76 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D byte tensor [rows, row_bytes] (pitch row_bytes), box = [128 bytes, box_rows], 128-byte swizzle.
-int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
+int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+              uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return B200Q_ERR_CUDA;
-  cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
-  cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)BKB, (cuuint32_t)box_rows};
+  cuuint64_t gdim[2] = {inner, rows};
+  cuuint64_t gstride[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return B200Q_ERR_CUDA; }
   return B200Q_OK;
 }
 
 template <int KIND, int BN>
-int launch(const void* A, const void* B, GemmParams p, cudaStream_t st) {
+int launch(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, GemmParams p, cudaStream_t st) {
   using C = Cfg<KIND, BN>;
   const int64_t row_bytes = KIND == KIND_NV ? p.K / 2 : p.K;
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, md;
   int rc;
-  if ((rc = make_operand_map(&ma, A, p.M, row_bytes, BM))) return rc;
-  if ((rc = make_operand_map(&mb, B, p.N, row_bytes, BN))) return rc;
+  // operands: byte matrices [rows, row_bytes], box = 128 bytes x tile rows, 128-byte swizzle
+  if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, p.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, b_rows, row_bytes, BKB, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  // output: bf16 [M, N] pitch ldd, box = 32 x 32 elements, 64-byte swizzle
+  if ((rc = encode_2d(&md, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, p.N, p.M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
   p.num_m = (int)((p.M + BM - 1) / BM);
   p.num_n = (int)((p.N + BN - 1) / BN);
   p.num_k = (int)((row_bytes + BKB - 1) / BKB);
   const int64_t nblk = KIND == KIND_MX ? p.K / 32 : p.K / 16;
   p.sf_kt = (int)((nblk + 3) / 4);
+  p.sfb_groups = (b_rows + 127) / 128;
   B200Q_CUDA(cudaFuncSetAttribute(gemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < kNumSMs ? tiles : kNumSMs;
-  gemm_kernel<KIND, BN><<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(ma, mb, p);
+  gemm_kernel<KIND, BN><<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(ma, mb, md, p);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
 
-int g_force_bn = 0;   // test hook: 0 = choose by N
+int g_force_bn = 0;   // test hook: 0 = choose by shape
+
+// Tile width by a small cost model (cycles per tile x waves): the main loop is bound by the
+// tensor pipe (2*BN cycles per K step) or by shared-memory reads ((128+BN)*128 bytes per K
+// step at ~120 B/clk); the epilogue hides behind the next main loop only when two
+// accumulators fit in tensor memory (every width but 256).
+template <int KIND>
+int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
+  const int cands[3] = {256, 192, 128};
+  const int64_t num_k = (row_bytes + BKB - 1) / BKB, num_m = (M + BM - 1) / BM;
+  double best = 1e30;
+  int best_bn = 256;
+  for (int bn : cands) {
+    const int64_t tiles = num_m * ((N + bn - 1) / bn);
+    const int64_t waves = (tiles + kNumSMs - 1) / kNumSMs;
+    const double kstep = std::max(2.0 * bn, (128.0 + bn) * 128.0 / 120.0);
+    const double mainloop = num_k * kstep + 600.0, epi = 300.0 + (bn / 32) * 220.0;
+    const double per_tile = bn == 256 && KIND != KIND_F8 ? mainloop + epi : std::max(mainloop, epi);
+    const double cost = waves * per_tile;
+    if (cost < best * 0.995) { best = cost; best_bn = bn; }
+  }
+  return best_bn;
+}
 
 template <int KIND>
-int dispatch(const void* A, const void* B, const GemmParams& p, cudaStream_t st) {
-  int bn = g_force_bn ? g_force_bn : (p.N > 128 ? 256 : 128);
+int dispatch(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, const GemmParams& p, cudaStream_t st) {
+  const int bn = g_force_bn ? g_force_bn : choose_bn<KIND>(p.M, p.N, KIND == KIND_NV ? p.K / 2 : p.K);
   switch (bn) {
-    case 128: return launch<KIND, 128>(A, B, p, st);
-    case 256: return launch<KIND, 256>(A, B, p, st);
+    case 128: return launch<KIND, 128>(A, B, D, ldd, b_rows, p, st);
+    case 192: return launch<KIND, 192>(A, B, D, ldd, b_rows, p, st);
+    case 256: return launch<KIND, 256>(A, B, D, ldd, b_rows, p, st);
     default: return B200Q_ERR_INVALID_ARG;
   }
 }
@@ -366,9 +448,9 @@ using namespace b200q;
 
 extern "C" {
 
-// Test hook: force the N tile width (128 or 256; 0 restores the default choice).
+// Test hook: force the N tile width (128, 192 or 256; 0 restores the choice by shape).
 int b200q_debug_set_gemm_bn(int bn) {
-  if (bn != 0 && bn != 128 && bn != 256) return B200Q_ERR_INVALID_ARG;
+  if (bn != 0 && bn != 128 && bn != 192 && bn != 256) return B200Q_ERR_INVALID_ARG;
   g_force_bn = bn;
   return B200Q_OK;
 }
@@ -381,8 +463,8 @@ int b200q_gemm_fp8(const void* A, int a_fmt, const void* B, int b_fmt, const flo
   if (scale_a == nullptr || scale_b == nullptr || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
   GemmParams p = {};
   p.scale_a = scale_a; p.scale_b = scale_b; p.a_scalar = a_scale_is_scalar; p.b_scalar = b_scale_is_scalar;
-  p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.M = M; p.N = N; p.K = K; p.D = (uint16_t*)D; p.ldd = ldd;
-  return dispatch<KIND_F8>(A, B, p, (cudaStream_t)stream);
+  p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.M = M; p.N = N; p.K = K;
+  return dispatch<KIND_F8>(A, B, D, ldd, N, p, (cudaStream_t)stream);
 }
 
 int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
@@ -393,8 +475,8 @@ int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, i
   if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
-  p.M = M; p.N = N; p.K = K; p.D = (uint16_t*)D; p.ldd = ldd;
-  return dispatch<KIND_MX>(A, B, p, (cudaStream_t)stream);
+  p.M = M; p.N = N; p.K = K;
+  return dispatch<KIND_MX>(A, B, D, ldd, N, p, (cudaStream_t)stream);
 }
 
 int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,
@@ -405,8 +487,23 @@ int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* 
   if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.scale_a = tsA; p.scale_b = tsB;
-  p.M = M; p.N = N; p.K = K; p.D = (uint16_t*)D; p.ldd = ldd;
-  return dispatch<KIND_NV>(A, B, p, (cudaStream_t)stream);
+  p.M = M; p.N = N; p.K = K;
+  return dispatch<KIND_NV>(A, B, D, ldd, N, p, (cudaStream_t)stream);
+}
+
+int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB,
+                             const int32_t* tile_expert, const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
+                             int64_t K, void* D, int64_t ldd, void* stream) {
+  int rc = check_gemm(A, B, D, padded_rows, N, K, ldd, 32);
+  if (rc) return rc;
+  if (sfA == nullptr || sfB == nullptr || tile_expert == nullptr || num_tiles == nullptr || E <= 0 || (a_fmt | b_fmt) & ~1)
+    return B200Q_ERR_INVALID_ARG;
+  if ((padded_rows & 127) || (N & 31) || (int64_t)E * N > INT32_MAX) return B200Q_ERR_SHAPE;
+  if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.M = padded_rows; p.N = N; p.K = K; p.tile_expert = tile_expert; p.num_tiles = num_tiles;
+  return dispatch<KIND_MX>(A, B, D, ldd, (int64_t)E * N, p, (cudaStream_t)stream);
 }
 
 }  // extern "C"

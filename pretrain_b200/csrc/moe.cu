@@ -1,0 +1,398 @@
+// MoE data movement around the ragged grouped GEMM: permute plan (stable counting sort of the
+// routed (token, slot) pairs by expert, in the reference's order, src/layers/mlp.py:446-457),
+// gather into the padded expert-sorted layout (optionally fused with MXFP8 quantization), SwiGLU
+// between the two GEMMs (src/layers/activation.py:80-81), and the weighted unpermute
+// (src/layers/mlp.py:472-477).  Index work is integer and bit-exact; the row movers are
+// HBM-bound: 16-byte coalesced accesses, one warp per row.
+#include "common.cuh"
+
+namespace b200q {
+namespace {
+
+constexpr int kPlanThreads = 1024;       // pairs per CTA in the plan kernels
+constexpr int kMaxExperts = 256;
+
+// ---- plan, step 1: per-CTA histogram of expert ids -------------------------------------------
+__global__ void __launch_bounds__(kPlanThreads)
+moe_hist_kernel(const int64_t* __restrict__ top_idx, int64_t n, int E, int32_t* __restrict__ block_counts) {
+  __shared__ int hist[kMaxExperts];
+  for (int i = threadIdx.x; i < E; i += kPlanThreads) hist[i] = 0;
+  __syncthreads();
+  const int64_t i = (int64_t)blockIdx.x * kPlanThreads + threadIdx.x;
+  if (i < n) {
+    const int e = (int)top_idx[i];
+    if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += kPlanThreads) block_counts[(int64_t)blockIdx.x * E + e] = hist[e];
+}
+
+// ---- plan, step 2 (one CTA): scan over CTAs per expert, then the segment tables -----------------
+// block_counts becomes the exclusive prefix over CTAs; offs = cumulative ends of the unpadded
+// segments; padded_offs = starts of the 128-row-aligned segments; tile_expert / num_tiles.
+__global__ void __launch_bounds__(kMaxExperts)
+moe_scan_kernel(int32_t* __restrict__ block_counts, int nblocks, int E, int32_t* __restrict__ offs,
+                int32_t* __restrict__ padded_offs, int32_t* __restrict__ tile_expert, int32_t* __restrict__ num_tiles,
+                int max_tiles) {
+  __shared__ int count[kMaxExperts];
+  __shared__ int pstart[kMaxExperts + 1];
+  const int e = threadIdx.x;
+  if (e < E) {
+    int run = 0;
+    for (int b = 0; b < nblocks; ++b) {
+      const int c = block_counts[(int64_t)b * E + e];
+      block_counts[(int64_t)b * E + e] = run;
+      run += c;
+    }
+    count[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int end = 0, p = 0;
+    for (int i = 0; i < E; ++i) {
+      end += count[i];
+      offs[i] = end;
+      pstart[i] = p;
+      p += (count[i] + 127) & ~127;
+    }
+    pstart[E] = p;
+    *num_tiles = p >> 7;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i <= E; i += blockDim.x) padded_offs[i] = pstart[i];
+  if (e < E)
+    for (int t = pstart[e] >> 7; t < (pstart[e + 1] >> 7); ++t) tile_expert[t] = e;
+  for (int t = (pstart[E] >> 7) + threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+}
+
+// ---- plan, step 3: stable destination of every pair ----------------------------------------------
+// rank inside the CTA = pairs of the same expert in earlier warps + earlier lanes of this warp.
+__global__ void __launch_bounds__(kPlanThreads)
+moe_scatter_kernel(const int64_t* __restrict__ top_idx, int64_t n, int k, int E, const int32_t* __restrict__ block_excl,
+                   const int32_t* __restrict__ padded_offs, int32_t* __restrict__ row_of, int32_t* __restrict__ src_of_row) {
+  extern __shared__ int warp_counts[];      // [32 warps][E]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 32 * E; i += kPlanThreads) warp_counts[i] = 0;
+  __syncthreads();
+  const int64_t i = (int64_t)blockIdx.x * kPlanThreads + threadIdx.x;
+  int e = -1;
+  if (i < n) {
+    e = (int)top_idx[i];
+    if (e < 0 || e >= E) e = -1;
+  }
+  const unsigned same = __match_any_sync(0xFFFFFFFFu, e);
+  const int rank_in_warp = __popc(same & ((1u << lane) - 1));
+  if (e >= 0 && rank_in_warp == 0) warp_counts[warp * E + e] = __popc(same);
+  __syncthreads();
+  for (int x = threadIdx.x; x < E; x += kPlanThreads) {     // exclusive prefix over the 32 warps
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = warp_counts[w * E + x];
+      warp_counts[w * E + x] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  if (e >= 0) {
+    const int dest = padded_offs[e] + block_excl[(int64_t)blockIdx.x * E + e] + warp_counts[warp * E + e] + rank_in_warp;
+    row_of[i] = dest;
+    src_of_row[dest] = (int32_t)(i / k);
+  }
+}
+
+// ---- plan for rows that are already expert-sorted (grouped_mlp's input convention) ----------------
+__global__ void __launch_bounds__(kMaxExperts)
+moe_pad_plan_kernel(const int32_t* __restrict__ offs, int E, int32_t* __restrict__ padded_offs,
+                    int32_t* __restrict__ tile_expert, int32_t* __restrict__ num_tiles, int max_tiles) {
+  __shared__ int pstart[kMaxExperts + 1];
+  if (threadIdx.x == 0) {
+    int prev = 0, p = 0;
+    for (int i = 0; i < E; ++i) {
+      const int c = offs[i] - prev;
+      prev = offs[i];
+      pstart[i] = p;
+      p += ((c > 0 ? c : 0) + 127) & ~127;
+    }
+    pstart[E] = p;
+    *num_tiles = p >> 7;
+  }
+  __syncthreads();
+  const int e = threadIdx.x;
+  for (int i = threadIdx.x; i <= E; i += blockDim.x) padded_offs[i] = pstart[i];
+  if (e < E)
+    for (int t = pstart[e] >> 7; t < (pstart[e + 1] >> 7); ++t) tile_expert[t] = e;
+  for (int t = (pstart[E] >> 7) + threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+}
+
+// src_of_row[r] = sorted-input row of padded row r, or -1 for pad rows
+__global__ void moe_pad_src_kernel(const int32_t* __restrict__ offs, const int32_t* __restrict__ padded_offs,
+                                   const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ num_tiles,
+                                   int32_t* __restrict__ src_of_row, int64_t padded_rows) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= padded_rows) return;
+  int src = -1;
+  if ((r >> 7) < *num_tiles) {
+    const int e = tile_expert[r >> 7];
+    const int start = e > 0 ? offs[e - 1] : 0, cnt = offs[e] - start;
+    const int within = (int)(r - padded_offs[e]);
+    if (within < cnt) src = start + within;
+  }
+  src_of_row[r] = src;
+}
+
+__device__ __forceinline__ void unpack8f(const uint4& v, float (&f)[8]) {
+  f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+  f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
+}
+
+// 8 bf16 of one lane -> MXFP8 codes; the 32-element block spans 4 lanes
+__device__ __forceinline__ uint2 mx_quant8(const uint4& v, int fmt, int& e_out) {
+  float a = absmax8(v);
+  a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
+  a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
+  const int e = mx_scale_exp(a, fmt);
+  const float inv = mx_inv_scale(e);
+  float f[8];
+  unpack8f(v, f);
+  uint2 o;
+  o.x = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, fmt);
+  o.y = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, fmt);
+  e_out = e;
+  return o;
+}
+
+// ---- gather rows into the padded layout (+ MXFP8) ------------------------------------------------
+template <int QUANT>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const uint16_t* __restrict__ x, int64_t D, int64_t ld, const int32_t* __restrict__ src_of_row,
+                  const int32_t* __restrict__ num_tiles, int64_t padded_rows, int fmt, uint8_t* __restrict__ out,
+                  uint8_t* __restrict__ sf) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int64_t live_rows = (int64_t)(*num_tiles) << 7;
+  if (live_rows > padded_rows) live_rows = padded_rows;
+  const int64_t nblk = D >> 5;
+  for (int64_t r = (int64_t)blockIdx.x * 8 + warp; r < live_rows; r += (int64_t)gridDim.x * 8) {
+    const int src = src_of_row[r];
+    const uint16_t* xr = x + (int64_t)(src < 0 ? 0 : src) * ld;
+    for (int64_t c0 = 0; c0 < D; c0 += 1024) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t c = c0 + u * 256 + lane * 8;
+        v[u] = (src >= 0 && c < D) ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t c = c0 + u * 256 + lane * 8;
+        if (c0 + u * 256 >= D) break;      // warp-uniform
+        if (QUANT) {
+          int e;
+          const uint2 o = mx_quant8(v[u], fmt, e);
+          if (c < D) {
+            *reinterpret_cast<uint2*>(out + r * D + c) = o;
+            if ((lane & 3) == 0) sf[sf_offset(r, c >> 5, nblk, 1)] = (uint8_t)(e + 127);
+          }
+        } else if (c < D) {
+          *reinterpret_cast<uint4*>(out + (r * D + c) * 2) = v[u];
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float bf16_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+
+// ---- SwiGLU (+ MXFP8) between the two grouped GEMMs -------------------------------------------------
+// h = bf16(bf16(silu(gate)) * up), the roundings of the reference's bf16 tensor ops.
+template <int QUANT>
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t ld, int fmt, uint8_t* __restrict__ out,
+              uint8_t* __restrict__ sf) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t nblk = I >> 5, chunks = (I + 255) >> 8, items = rows * chunks;
+  for (int64_t item = (int64_t)blockIdx.x * 8 + warp; item < items; item += (int64_t)gridDim.x * 8) {
+    const int64_t r = item / chunks, c = (item - r * chunks) * 256 + lane * 8;
+    const bool live = c < I;
+    uint4 vg = make_uint4(0, 0, 0, 0), vu = vg;
+    if (live) {
+      vg = ld_nc_v4(g + r * ld + c);
+      vu = ld_nc_v4(g + r * ld + I + c);
+    }
+    float a[8], b[8];
+    unpack8f(vg, a);
+    unpack8f(vu, b);
+    uint32_t h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float s0 = bf16_round(a[2 * i] / (1.f + expf(-a[2 * i])));
+      const float s1 = bf16_round(a[2 * i + 1] / (1.f + expf(-a[2 * i + 1])));
+      __nv_bfloat162 p = __floats2bfloat162_rn(s0 * b[2 * i], s1 * b[2 * i + 1]);
+      h[i] = *reinterpret_cast<uint32_t*>(&p);
+    }
+    const uint4 hv = make_uint4(h[0], h[1], h[2], h[3]);
+    if (QUANT) {
+      int e;
+      const uint2 o = mx_quant8(hv, fmt, e);
+      if (live) {
+        *reinterpret_cast<uint2*>(out + r * I + c) = o;
+        if ((lane & 3) == 0) sf[sf_offset(r, c >> 5, nblk, 1)] = (uint8_t)(e + 127);
+      }
+    } else if (live) {
+      *reinterpret_cast<uint4*>(out + (r * I + c) * 2) = hv;
+    }
+  }
+}
+
+// ---- weighted unpermute: out[t] = sum_j w[t,j] * y[row_of[t*k+j]] (fp32 accumulate) ----------------
+__global__ void __launch_bounds__(256)
+moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t* __restrict__ w,
+                     const int32_t* __restrict__ row_of, int64_t T, int k, int64_t D, uint16_t* __restrict__ out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t chunks = (D + 255) >> 8, items = T * chunks;
+  for (int64_t item = (int64_t)blockIdx.x * 8 + warp; item < items; item += (int64_t)gridDim.x * 8) {
+    const int64_t t = item / chunks, c = (item - t * chunks) * 256 + lane * 8;
+    if (c >= D) continue;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < k; ++j) {
+      const int row = row_of[t * k + j];
+      const float wj = u2f((uint32_t)w[t * k + j] << 16);
+      float f[8];
+      unpack8f(ld_nc_v4(y + (int64_t)row * ldy + c), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(wj, f[i], acc[i]);
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      o[i] = *reinterpret_cast<uint32_t*>(&p);
+    }
+    *reinterpret_cast<uint4*>(out + t * D + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+inline int row_grid(int64_t items) {
+  int64_t want = (items + 7) / 8, cap = (int64_t)kNumSMs * 8;
+  return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int64_t b200q_moe_padded_rows(int64_t n_pairs, int E) {
+  if (n_pairs < 0 || E <= 0) return 0;
+  // every expert wastes at most 127 rows; round the bound itself up to a tile
+  return ((n_pairs + (int64_t)E * 127 + 127) / 128) * 128;
+}
+
+int64_t b200q_moe_plan_workspace_bytes(int64_t n_pairs, int E) {
+  if (n_pairs < 0 || E <= 0) return 0;
+  const int64_t nblocks = (n_pairs + kPlanThreads - 1) / kPlanThreads;
+  return (nblocks > 0 ? nblocks : 1) * E * (int64_t)sizeof(int32_t);
+}
+
+int b200q_moe_permute_plan(const int64_t* top_idx, int64_t n_pairs, int k, int E, int32_t* offs, int32_t* padded_offs,
+                           int32_t* row_of, int32_t* src_of_row, int32_t* tile_expert, int32_t* num_tiles, void* workspace,
+                           void* stream) {
+  if (top_idx == nullptr || offs == nullptr || padded_offs == nullptr || row_of == nullptr || src_of_row == nullptr ||
+      tile_expert == nullptr || num_tiles == nullptr || workspace == nullptr || n_pairs <= 0 || k <= 0 || E <= 0)
+    return B200Q_ERR_INVALID_ARG;
+  if (E > kMaxExperts || n_pairs > INT32_MAX / 2) return B200Q_ERR_SHAPE;
+  int rc = require_sm100();
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nblocks = (int)((n_pairs + kPlanThreads - 1) / kPlanThreads);
+  const int64_t padded_rows = b200q_moe_padded_rows(n_pairs, E);
+  int32_t* block_counts = (int32_t*)workspace;
+  B200Q_CUDA(cudaMemsetAsync(src_of_row, 0xFF, (size_t)padded_rows * sizeof(int32_t), st));   // -1 = pad row
+  moe_hist_kernel<<<nblocks, kPlanThreads, 0, st>>>(top_idx, n_pairs, E, block_counts);
+  B200Q_CUDA(cudaGetLastError());
+  moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(block_counts, nblocks, E, offs, padded_offs, tile_expert, num_tiles,
+                                             (int)(padded_rows / 128));
+  B200Q_CUDA(cudaGetLastError());
+  moe_scatter_kernel<<<nblocks, kPlanThreads, 32 * E * sizeof(int), st>>>(top_idx, n_pairs, k, E, block_counts, padded_offs,
+                                                                           row_of, src_of_row);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_pad_plan(const int32_t* offs, int E, int64_t n_rows, int32_t* padded_offs, int32_t* src_of_row,
+                       int32_t* tile_expert, int32_t* num_tiles, void* stream) {
+  if (offs == nullptr || padded_offs == nullptr || src_of_row == nullptr || tile_expert == nullptr || num_tiles == nullptr ||
+      E <= 0 || n_rows < 0)
+    return B200Q_ERR_INVALID_ARG;
+  if (E > kMaxExperts || n_rows > INT32_MAX / 2) return B200Q_ERR_SHAPE;
+  int rc = require_sm100();
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t padded_rows = b200q_moe_padded_rows(n_rows, E);
+  moe_pad_plan_kernel<<<1, kMaxExperts, 0, st>>>(offs, E, padded_offs, tile_expert, num_tiles, (int)(padded_rows / 128));
+  B200Q_CUDA(cudaGetLastError());
+  moe_pad_src_kernel<<<(unsigned)((padded_rows + 255) / 256), 256, 0, st>>>(offs, padded_offs, tile_expert, num_tiles, src_of_row,
+                                                                            padded_rows);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_gather(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row, const int32_t* num_tiles,
+                     int64_t padded_rows, int quantize, int fmt, void* out, void* sf, void* stream) {
+  if (x == nullptr || src_of_row == nullptr || num_tiles == nullptr || out == nullptr || D <= 0 || ld < D || padded_rows <= 0 ||
+      (quantize && sf == nullptr) || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 31) || (ld & 7) || (padded_rows & 127)) return B200Q_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(out)) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (quantize) {
+    if ((D >> 5) & 3) B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(padded_rows, D >> 5, B200Q_SF_SWIZZLE_128x4), st));
+    moe_gather_kernel<1><<<row_grid(padded_rows), 256, 0, st>>>((const uint16_t*)x, D, ld, src_of_row, num_tiles, padded_rows, fmt,
+                                                                (uint8_t*)out, (uint8_t*)sf);
+  } else {
+    moe_gather_kernel<0><<<row_grid(padded_rows), 256, 0, st>>>((const uint16_t*)x, D, ld, src_of_row, num_tiles, padded_rows, fmt,
+                                                                (uint8_t*)out, nullptr);
+  }
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantize, int fmt, void* out, void* sf, void* stream) {
+  if (g == nullptr || out == nullptr || rows <= 0 || I <= 0 || ld < 2 * I || (quantize && sf == nullptr) ||
+      (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
+    return B200Q_ERR_INVALID_ARG;
+  if ((I & 31) || (ld & 7)) return B200Q_ERR_SHAPE;
+  if (!aligned16(g) || !aligned16(out)) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t items = rows * ((I + 255) / 256);
+  if (quantize) {
+    if ((rows & 127) || ((I >> 5) & 3))
+      B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(rows, I >> 5, B200Q_SF_SWIZZLE_128x4), st));
+    swiglu_kernel<1><<<row_grid(items), 256, 0, st>>>((const uint16_t*)g, rows, I, ld, fmt, (uint8_t*)out, (uint8_t*)sf);
+  } else {
+    swiglu_kernel<0><<<row_grid(items), 256, 0, st>>>((const uint16_t*)g, rows, I, ld, fmt, (uint8_t*)out, nullptr);
+  }
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_unpermute(const void* y, int64_t ldy, const void* w, const int32_t* row_of, int64_t T, int k, int64_t D, void* out,
+                        void* stream) {
+  if (y == nullptr || w == nullptr || row_of == nullptr || out == nullptr || T <= 0 || k <= 0 || D <= 0 || ldy < D)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 7) || (ldy & 7)) return B200Q_ERR_SHAPE;
+  if (!aligned16(y) || !aligned16(out)) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  moe_unpermute_kernel<<<row_grid(T * ((D + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(
+      (const uint16_t*)y, ldy, (const uint16_t*)w, row_of, T, k, D, (uint16_t*)out);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+}  // extern "C"

@@ -154,6 +154,18 @@ B200Q_HD uint8_t nv_block_scale(float amax_block, float s_t) {
   return cvt_e4m3(r);
 }
 
+// The same value with both divisions done by hoisted reciprocals: rcp6 = RN(1/6) and
+// rcp_st = RN(1/s_t).  Equal to nv_block_scale() for every bf16 block maximum (the host
+// check walks all of them): quotients that could differ are fp32 subnormals, which either
+// fall under the 1e-12 floor or round to the scale byte 0 both ways.
+B200Q_HD uint8_t nv_block_scale_fast(float amax_block, float s_t, float rcp_st) {
+  float d = div_by_rcp(amax_block, kE2M1Max, 0.16666667163372039794921875f);
+  d = d < kEps ? kEps : d;
+  float r = div_by_rcp(d, s_t, rcp_st);
+  r = r > 448.0f ? 448.0f : r;
+  return cvt_e4m3(r);
+}
+
 // Scale-factor byte offset in the 128x4-tiled layout the tensor core's scale copy reads:
 // rows padded to 128, blocks to 4, each tile 512 contiguous bytes, K-tile fastest.
 B200Q_HD int64_t sf_offset(int64_t r, int64_t kb, int64_t nblk, int swizzled) {

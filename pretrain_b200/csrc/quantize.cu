@@ -48,20 +48,21 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const uint16_t* __restri
                                                         int64_t ld, float* __restrict__ amax) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t m = 0;
-  for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows; row += (int64_t)gridDim.x * kWarps) {
+  // work item = (row, 1024-column chunk); items are dealt round-robin to all warps of the grid
+  const int64_t chunks = (cols + 1023) >> 10, items = rows * chunks;
+  for (int64_t item = (int64_t)blockIdx.x * kWarps + warp; item < items; item += (int64_t)gridDim.x * kWarps) {
+    const int64_t row = item / chunks, c0 = (item - row * chunks) << 10;
     const uint16_t* xr = x + row * ld;
-    for (int64_t c0 = 0; c0 < cols; c0 += 1024) {
-      uint4 v[4];
+    uint4 v[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        int64_t c = c0 + u * 256 + lane * 8;
-        v[u] = c < cols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
-      }
+    for (int u = 0; u < 4; ++u) {
+      int64_t c = c0 + u * 256 + lane * 8;
+      v[u] = c < cols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        m = absmax_bf16x2(m, absmax_bf16x2(v[u].x, v[u].y));
-        m = absmax_bf16x2(m, absmax_bf16x2(v[u].z, v[u].w));
-      }
+    for (int u = 0; u < 4; ++u) {
+      m = absmax_bf16x2(m, absmax_bf16x2(v[u].x, v[u].y));
+      m = absmax_bf16x2(m, absmax_bf16x2(v[u].z, v[u].w));
     }
   }
   float a = warp_max(fmaxf(bf16lo(m), bf16hi(m)));
@@ -88,14 +89,18 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int BS = MODE == MODE_MX ? 32 : 16;
   const int64_t nblk = cols / BS;
-  float s_t = 0.f;
+  float s_t = 0.f, rcp_st = 0.f;
   if (MODE == MODE_NV) {
     s_t = nv_tensor_scale(*tensor_amax);
+    rcp_st = rcp_rn(s_t);
     if (blockIdx.x == 0 && threadIdx.x == 0) *tensor_scale_out = s_t;
   }
-  for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows; row += (int64_t)gridDim.x * kWarps) {
+  // work item = (row, 1024-column chunk), dealt round-robin to all warps of the grid
+  const int64_t chunks = (cols + 1023) >> 10, items = rows * chunks;
+  for (int64_t item = (int64_t)blockIdx.x * kWarps + warp; item < items; item += (int64_t)gridDim.x * kWarps) {
+    const int64_t row = item / chunks, c0 = (item - row * chunks) << 10;
     const uint16_t* xr = x + row * ld;
-    for (int64_t c0 = 0; c0 < cols; c0 += 1024) {
+    {
       uint4 v[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -122,7 +127,7 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
             if ((lane & 3) == 0) sf[sf_offset(row, c >> 5, nblk, swz)] = (uint8_t)(e + 127);
           }
         } else {
-          const uint8_t sq = nv_block_scale(a, s_t);
+          const uint8_t sq = nv_block_scale_fast(a, s_t, rcp_st);
           const float eff = mul_rn(e4m3_to_float(sq), s_t);
           const float rcp = rcp_rn(eff);
           uint32_t o = 0;
@@ -142,50 +147,62 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
 }
 
 // ------------------------------------------------------------------------------------------
-// Row-wise FP8 with one fp32 scale per row (or one for the tensor): a warp owns a row and
-// keeps it in registers between the amax pass and the conversion pass (NVEC 16-byte vectors
-// per lane); NVEC == 0 re-reads the row (it is still in L2) for very long rows.
+// Row-wise FP8 with one fp32 scale per row (or one for the tensor).  `wpr` warps (1, 2, 4 or 8)
+// share a row and keep it in registers between the amax pass and the conversion pass (NVEC
+// 16-byte vectors per lane; partial maxima meet in shared memory).  NVEC == 0 re-reads the row
+// (it is still in L2) for rows too long for that.
 // ------------------------------------------------------------------------------------------
 template <int NVEC>
 __global__ void __launch_bounds__(kThreads)
 rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, int fmt,
                    uint8_t* __restrict__ codes, float* __restrict__ scales, const float* __restrict__ tensor_amax,
-                   float* __restrict__ tensor_scale_out) {
+                   float* __restrict__ tensor_scale_out, int wpr) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows; row += (int64_t)gridDim.x * kWarps) {
-    const uint16_t* xr = x + row * ld;
+  const int grp = warp / wpr, wig = warp - grp * wpr, rpc = kWarps / wpr;
+  __shared__ float smax[2][kWarps];
+  int it = 0;
+  for (int64_t base = (int64_t)blockIdx.x * rpc; base < rows; base += (int64_t)gridDim.x * rpc, ++it) {
+    const int64_t row = base + grp;
+    const bool live = row < rows;
+    const uint16_t* xr = x + (live ? row : 0) * ld;
     uint4 v[NVEC > 0 ? NVEC : 1];
     uint32_t m = 0;
     if (NVEC > 0) {
 #pragma unroll
       for (int i = 0; i < NVEC; ++i) {
-        int64_t c = (int64_t)(i * 32 + lane) * 8;
-        v[i] = c < cols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
+        int64_t c = (int64_t)((i * wpr + wig) * 32 + lane) * 8;
+        v[i] = (live && c < cols) ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int i = 0; i < NVEC; ++i) {
         m = absmax_bf16x2(m, absmax_bf16x2(v[i].x, v[i].y));
         m = absmax_bf16x2(m, absmax_bf16x2(v[i].z, v[i].w));
       }
-    } else if (tensor_amax == nullptr) {
-      for (int64_t c = lane * 8; c < cols; c += 256) {
+    } else if (tensor_amax == nullptr && live) {
+      for (int64_t c = (wig * 32 + lane) * 8; c < cols; c += 256 * wpr) {
         uint4 t = ld_nc_v4(xr + c);
         m = absmax_bf16x2(m, absmax_bf16x2(t.x, t.y));
         m = absmax_bf16x2(m, absmax_bf16x2(t.z, t.w));
       }
     }
-    float amax = tensor_amax ? *tensor_amax : warp_max(fmaxf(bf16lo(m), bf16hi(m)));
+    float amax = warp_max(fmaxf(bf16lo(m), bf16hi(m)));
+    if (wpr > 1) {
+      if (lane == 0) smax[it & 1][warp] = amax;
+      __syncthreads();
+      for (int j = 0; j < wpr; ++j) amax = fmaxf(amax, smax[it & 1][grp * wpr + j]);
+    }
+    if (tensor_amax) amax = *tensor_amax;
     const float scale = fp8_scale_from_amax(amax, fmt);
     const float rcp = rcp_rn(scale);
-    if (lane == 0) {
+    if (lane == 0 && wig == 0 && live) {
       if (tensor_amax == nullptr) scales[row] = scale;
       else if (row == 0) *tensor_scale_out = scale;
     }
-    uint8_t* cr = codes + row * cols;
+    uint8_t* cr = codes + (live ? row : 0) * cols;
     if (NVEC > 0) {
 #pragma unroll
       for (int i = 0; i < NVEC; ++i) {
-        int64_t c = (int64_t)(i * 32 + lane) * 8;
+        int64_t c = (int64_t)((i * wpr + wig) * 32 + lane) * 8;
         float f[8];
         unpack8(v[i], f);
 #pragma unroll
@@ -193,10 +210,10 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
         uint2 o;
         o.x = cvt_fp8x4(f[0], f[1], f[2], f[3], fmt);
         o.y = cvt_fp8x4(f[4], f[5], f[6], f[7], fmt);
-        if (c < cols) *reinterpret_cast<uint2*>(cr + c) = o;
+        if (live && c < cols) *reinterpret_cast<uint2*>(cr + c) = o;
       }
-    } else {
-      for (int64_t c = lane * 8; c < cols; c += 256) {
+    } else if (live) {
+      for (int64_t c = (wig * 32 + lane) * 8; c < cols; c += 256 * wpr) {
         float f[8];
         unpack8(ld_nc_v4(xr + c), f);
 #pragma unroll
@@ -281,9 +298,10 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
     uint4 v = (gr < rows && gc < cols) ? ld_nc_v4(x + gr * ld + gc) : make_uint4(0, 0, 0, 0);
     *reinterpret_cast<uint4*>(&tin[r * kTC + ch * 8]) = v;
   }
-  float s_t = 0.f, t_scale = 0.f;
+  float s_t = 0.f, t_scale = 0.f, rcp_st = 0.f;
   if (MODE == MODE_NV) {
     s_t = nv_tensor_scale(*tensor_amax);
+    rcp_st = rcp_rn(s_t);
     if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) *tensor_scale_out = s_t;
   }
   if (MODE == MODE_FP8 && tensor_amax != nullptr) {
@@ -318,7 +336,7 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
       float a = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) a = fmaxf(a, fabsf(f[16 * h + i]));
-      const uint8_t sq = nv_block_scale(a, s_t);
+      const uint8_t sq = nv_block_scale_fast(a, s_t, rcp_st);
       const float eff = mul_rn(e4m3_to_float(sq), s_t);
       const float rcp = rcp_rn(eff);
       o[2 * h] = o[2 * h + 1] = 0;
@@ -369,9 +387,12 @@ int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
   return B200Q_OK;
 }
 
-inline int rowwise_grid(int64_t rows) {
-  int64_t want = (rows + kWarps - 1) / kWarps;
-  int64_t cap = (int64_t)kNumSMs * 8;
+// Grid for the item-based row-wise kernels: one resident wave (4 CTAs of 256 threads per SM);
+// the (row, chunk) items are dealt round-robin, so every warp gets the same share.
+inline int rowwise_grid(int64_t rows, int64_t cols, int ctas_per_sm = 4) {
+  int64_t items = rows * ((cols + 1023) / 1024);
+  int64_t want = (items + kWarps - 1) / kWarps;
+  int64_t cap = (int64_t)kNumSMs * ctas_per_sm;
   return (int)(want < cap ? want : cap);
 }
 
@@ -426,17 +447,22 @@ int b200q_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, float* ama
   if ((rc = require_sm100())) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   B200Q_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), st));
-  amax_kernel<<<rowwise_grid(rows), kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, amax);
+  amax_kernel<<<rowwise_grid(rows, cols, 8), kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, amax);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
 
 static int launch_rowwise_fp8(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes,
                               float* scales, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st) {
-  const int grid = rowwise_grid(rows);
-  const int64_t nvec = (cols + 255) / 256;
+  // warps per row: enough that a lane keeps at most 4 vectors (32 elements), up to the whole CTA
+  const int64_t nv = cols / 8;
+  int wpr = 1;
+  while (wpr < kWarps && nv > (int64_t)wpr * 32 * 4) wpr *= 2;
+  const int64_t nvec = (nv + wpr * 32 - 1) / (wpr * 32);
+  const int64_t rpc = kWarps / wpr, want = (rows + rpc - 1) / rpc, cap = (int64_t)kNumSMs * 8;
+  const int grid = (int)(want < cap ? want : cap);
 #define B200Q_LAUNCH(NV) \
-  rowwise_fp8_kernel<NV><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, fmt, codes, scales, tensor_amax, tensor_scale_out)
+  rowwise_fp8_kernel<NV><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, fmt, codes, scales, tensor_amax, tensor_scale_out, wpr)
   if (nvec <= 1) B200Q_LAUNCH(1);
   else if (nvec <= 2) B200Q_LAUNCH(2);
   else if (nvec <= 4) B200Q_LAUNCH(4);
@@ -510,7 +536,7 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf, outer, contraction / 32, sf_layout, st))) return rc;
   if (axis == 1) {
-    rowwise_block_quant_kernel<MODE_MX><<<rowwise_grid(rows), kThreads, 0, st>>>(
+    rowwise_block_quant_kernel<MODE_MX><<<rowwise_grid(rows, cols), kThreads, 0, st>>>(
         (const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr);
   } else {
     dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
@@ -535,7 +561,7 @@ int b200q_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf, outer, contraction / 16, sf_layout, st))) return rc;
   if (axis == 1) {
-    rowwise_block_quant_kernel<MODE_NV><<<rowwise_grid(rows), kThreads, 0, st>>>(
+    rowwise_block_quant_kernel<MODE_NV><<<rowwise_grid(rows, cols), kThreads, 0, st>>>(
         (const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax, tensor_scale_out);
   } else {
     dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));

@@ -1,0 +1,176 @@
+"""MoE expert FFN on the sm_100a kernels, behind the call signatures of the reference's
+``src/layers/mlp.py``: ``grouped_mlp`` (:55-100), ``MoERouter`` (:248-302) and
+``SparseMoEBlock`` (:324-494).
+
+The two bf16 ``torch._grouped_mm`` calls of the reference become ragged MXFP8 grouped GEMMs on
+the tensor cores; the permute is a stable counting sort (same row order as the reference's
+``sort(stable=True)``) whose gather is fused with the MXFP8 quantization; SwiGLU is fused with
+the re-quantization of the hidden activations; the unpermute is a gather-reduce in fp32.
+Forward (fprop) only: the backward of the expert path is not built yet, so tensors that require
+grad are rejected instead of silently detaching them.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+
+
+def silu_glu(gate, up):
+    """SwiGLU, the gated activation of the reference's default experts (src/layers/activation.py:80-81)."""
+    return F.silu(gate) * up
+
+
+GATED_ACTIVATIONS = {"silu": silu_glu, "relu": lambda g, u: F.relu(g) * u, "gelu": lambda g, u: F.gelu(g) * u,
+                     "bilinear": lambda g, u: g * u}
+UNGATED_ACTIVATIONS = {"silu": F.silu, "relu": F.relu, "gelu": F.gelu}
+
+MOE_ROUTER_SCORE_FNS = {
+    "softmax": lambda logits: logits.softmax(dim=-1),
+    "sigmoid": lambda logits: logits.sigmoid(),
+}
+
+
+def _no_grad_only(*tensors):
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        raise NotImplementedError("the MXFP8 expert path is forward-only in this build; call it under torch.no_grad()")
+
+
+def _quantize_expert_weights(w: torch.Tensor):
+    """(E, out, in) weight stack -> MXFP8 codes (E*out, in) + swizzled scales, blocks along `in`."""
+    e, n, k = w.shape
+    if n % 128:
+        raise ValueError("expert output width must be a multiple of 128 (scale-factor tiles must not straddle experts)")
+    return ops.quantize_mxfp8(w.reshape(e * n, k), 1)
+
+
+def _expert_of_padded_row(plan) -> torch.Tensor:
+    return plan.tile_expert.clamp_min(0).repeat_interleave(128).long()
+
+
+def _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in=None, b_down=None):
+    """Both grouped GEMMs and the activation on the padded layout; returns (padded_rows, D_out) bf16."""
+    n1, n2 = w_in.shape[1], w_down.shape[1]
+    wq1, wsf1 = _quantize_expert_weights(w_in)
+    wq2, wsf2 = _quantize_expert_weights(w_down)
+    h = ops.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, n1)
+    if b_in is not None:
+        h = h + b_in.to(h.dtype)[_expert_of_padded_row(plan)]
+    if gated and act_fn is silu_glu:
+        hq, hsf = ops.swiglu(h, True)                     # fused silu(gate)*up + MXFP8
+    else:
+        act = act_fn(*h.chunk(2, dim=-1)) if gated else act_fn(h)
+        hq, hsf = ops.quantize_mxfp8(act.contiguous(), 1)
+    out = ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, n2)
+    if b_down is not None:
+        out = out + b_down.to(out.dtype)[_expert_of_padded_row(plan)]
+    return out
+
+
+def grouped_mlp(x, w_in, w_down, act_fn, offs, gated, row_expert_ids=None, b_in=None, b_down=None):
+    """Dropless MoE expert FFN over expert-sorted rows.
+
+    x is (R, D) with rows grouped by expert and ``offs`` the (E,) int32 cumulative end offsets
+    (offs[-1] == R); weights are (E, out, in); empty groups are fine; biases, when given, are
+    (E, out) and are added per row.  Returns (R, D_out) in bf16, rows in the input order.
+    """
+    _no_grad_only(x, w_in, w_down, b_in, b_down)
+    if not x.is_cuda:
+        raise RuntimeError("grouped_mlp runs on the B200 kernels only (no CPU path)")
+    r = x.shape[0]
+    e = w_in.shape[0]
+    x, w_in, w_down = x.to(torch.bfloat16), w_in.to(torch.bfloat16), w_down.to(torch.bfloat16)
+    plan = ops.moe_pad_plan(offs, r)
+    a, sfa = ops.moe_gather(x, plan, True)
+    out_p = _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in, b_down)
+    # back to the caller's unpadded row order
+    rows = torch.arange(r, device=x.device)
+    expert = torch.searchsorted(plan.offs.long(), rows, right=True).clamp_max(e - 1)
+    starts = torch.cat([plan.offs.new_zeros(1), plan.offs[:-1]]).long()
+    return out_p[plan.padded_offs.long()[expert] + rows - starts[expert]]
+
+
+class MoERouter(nn.Module):
+    """Top-k router with an fp32-pinned gate (src/layers/mlp.py:248-302): fp32 logits, score
+    function, top-k, weights normalised by their sum + 1e-9."""
+
+    def __init__(self, d_model, n_routed_experts, n_routed_experts_per_token, normalize=True, expert_bias=False,
+                 expert_bias_update_rate=0.001, router_score_fn="sigmoid"):
+        super().__init__()
+        if expert_bias:
+            raise NotImplementedError("expert-bias load balancing is not part of this build's path")
+        self.n_routed_experts = n_routed_experts
+        self.n_routed_experts_per_token = n_routed_experts_per_token
+        self.normalize = normalize
+        self.score_fn = MOE_ROUTER_SCORE_FNS[router_score_fn]
+        self.gate = nn.Linear(d_model, n_routed_experts, bias=False)
+
+    def _apply(self, fn, recurse=True):
+        result = super()._apply(fn, recurse)
+        if self.gate.weight.dtype != torch.float32:
+            self.gate.weight.data = self.gate.weight.data.float()
+        return result
+
+    def forward(self, x):
+        with torch.amp.autocast(device_type=x.device.type, enabled=False):
+            probs = self.score_fn(self.gate(x.float()))
+        top_w, top_i = torch.topk(probs, self.n_routed_experts_per_token, dim=-1)
+        if self.normalize:
+            top_w = top_w / (top_w.sum(-1, keepdim=True) + 1e-9)
+        return top_i, top_w.to(x.dtype), probs.to(x.dtype)
+
+
+class SparseMoEBlock(nn.Module):
+    """Sparse MoE MLP block, dropless dispatch (src/layers/mlp.py:324-494): route, permute by
+    expert, grouped FFN, weighted unpermute, Switch auxiliary loss.  Parameters keep the
+    reference's names and (E, out, in) shapes: ``expert_gate_up`` / ``expert_up``, ``expert_down``."""
+
+    def __init__(self, d_model, *, intermediate_size, n_routed_experts, n_routed_experts_per_token, n_shared_experts=0,
+                 aux_loss=True, aux_loss_coef=0.001, expert_bias=False, expert_bias_update_rate=0.001,
+                 router_score_fn="sigmoid", activation="silu", gated=True, bias=False, dropout=0.0):
+        super().__init__()
+        if aux_loss and expert_bias:
+            raise ValueError("aux_loss and expert_bias are mutually exclusive MoE balancing strategies")
+        if n_shared_experts or dropout:
+            raise NotImplementedError("shared experts and expert dropout are outside this build's path")
+        self.n_routed_experts = n_routed_experts
+        self.n_routed_experts_per_token = n_routed_experts_per_token
+        self.aux_loss, self.aux_loss_coef = aux_loss, aux_loss_coef
+        self.router_score_fn, self.gated = router_score_fn, gated
+        self.act_fn = (GATED_ACTIVATIONS if gated else UNGATED_ACTIVATIONS)[activation]
+        self.router = MoERouter(d_model, n_routed_experts, n_routed_experts_per_token, expert_bias=expert_bias,
+                                expert_bias_update_rate=expert_bias_update_rate, router_score_fn=router_score_fn)
+        width = 2 * intermediate_size if gated else intermediate_size
+        name = "expert_gate_up" if gated else "expert_up"
+        setattr(self, name, nn.Parameter(torch.empty(n_routed_experts, width, d_model)))
+        setattr(self, name + "_bias", nn.Parameter(torch.zeros(n_routed_experts, width)) if bias else None)
+        self.expert_down = nn.Parameter(torch.empty(n_routed_experts, d_model, intermediate_size))
+        self.expert_down_bias = nn.Parameter(torch.zeros(n_routed_experts, d_model)) if bias else None
+
+    def forward(self, x):
+        b, s, d = x.shape
+        e = self.n_routed_experts
+        x_flat = x.reshape(b * s, d)
+        top_indices, top_weights, router_probs = self.router(x_flat)
+        w_in = self.expert_gate_up if self.gated else self.expert_up
+        b_in = self.expert_gate_up_bias if self.gated else self.expert_up_bias
+        _no_grad_only(x, w_in, self.expert_down)
+
+        plan = ops.moe_permute_plan(top_indices, e)                        # stable sort by expert
+        a, sfa = ops.moe_gather(x_flat.to(torch.bfloat16), plan, True)    # permute fused with MXFP8
+        y = _grouped_ffn_padded(a, sfa, plan, w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
+                                self.act_fn, self.gated, b_in, self.expert_down_bias)
+        out = ops.moe_unpermute(y, top_weights, plan.row_of, b * s).to(x.dtype)
+
+        aux = None
+        if self.aux_loss:
+            counts = torch.diff(plan.offs, prepend=plan.offs.new_zeros(1))
+            f = counts.to(x.dtype) / (b * s)
+            probs = router_probs
+            if self.router_score_fn == "sigmoid":
+                probs = probs / (probs.sum(-1, keepdim=True) + 1e-9)
+            aux = self.aux_loss_coef * e * (f * probs.mean(0)).sum()
+        return out.view(b, s, d), aux

@@ -142,6 +142,113 @@ def gemm_nvfp4(a_packed, a_sf, a_ts, b_packed, b_sf, b_ts, out=None):
     return d
 
 
+# ---- MoE ------------------------------------------------------------------------------------
+
+class MoEPlan:
+    """Device-side tables of the padded expert-sorted layout (see include/b200q.h)."""
+    __slots__ = ("offs", "padded_offs", "row_of", "src_of_row", "tile_expert", "num_tiles", "padded_rows", "n_experts")
+
+
+def moe_padded_rows(n_pairs: int, n_experts: int) -> int:
+    return _lib.load().b200q_moe_padded_rows(n_pairs, n_experts)
+
+
+def _new_plan(n_rows: int, n_experts: int, device) -> MoEPlan:
+    p = MoEPlan()
+    p.n_experts = n_experts
+    p.padded_rows = moe_padded_rows(n_rows, n_experts)
+    i32 = dict(dtype=torch.int32, device=device)
+    p.offs = torch.empty(n_experts, **i32)
+    p.padded_offs = torch.empty(n_experts + 1, **i32)
+    p.src_of_row = torch.empty(p.padded_rows, **i32)
+    p.tile_expert = torch.empty(p.padded_rows // 128, **i32)
+    p.num_tiles = torch.empty(1, **i32)
+    p.row_of = None
+    return p
+
+
+def moe_permute_plan(top_indices: torch.Tensor, n_experts: int) -> MoEPlan:
+    """top_indices: int64 (T, k) expert ids -> plan (stable sort by expert, reference order)."""
+    t, k = top_indices.shape
+    idx = top_indices.contiguous().view(-1)
+    if idx.dtype != torch.int64:
+        idx = idx.to(torch.int64)
+    lib = _lib.load()
+    p = _new_plan(t * k, n_experts, idx.device)
+    p.row_of = torch.empty(t * k, dtype=torch.int32, device=idx.device)
+    ws = torch.empty(lib.b200q_moe_plan_workspace_bytes(t * k, n_experts), dtype=torch.uint8, device=idx.device)
+    _lib.check(lib.b200q_moe_permute_plan(idx.data_ptr(), t * k, k, n_experts, p.offs.data_ptr(), p.padded_offs.data_ptr(),
+                                          p.row_of.data_ptr(), p.src_of_row.data_ptr(), p.tile_expert.data_ptr(),
+                                          p.num_tiles.data_ptr(), ws.data_ptr(), _stream()), "b200q_moe_permute_plan")
+    return p
+
+
+def moe_pad_plan(offs: torch.Tensor, n_rows: int) -> MoEPlan:
+    """Plan for rows already sorted by expert; offs int32 (E,) cumulative ends."""
+    offs = offs.to(torch.int32).contiguous()
+    p = _new_plan(n_rows, offs.numel(), offs.device)
+    p.offs = offs
+    _lib.check(_lib.load().b200q_moe_pad_plan(offs.data_ptr(), offs.numel(), n_rows, p.padded_offs.data_ptr(),
+                                              p.src_of_row.data_ptr(), p.tile_expert.data_ptr(), p.num_tiles.data_ptr(),
+                                              _stream()), "b200q_moe_pad_plan")
+    return p
+
+
+def moe_gather(x: torch.Tensor, plan: MoEPlan, quantize: bool, fmt=E4M3):
+    """Rows of x into the padded layout: bf16 copy, or (codes, swizzled sf) when quantize.
+    Rows past the plan's live tiles are left unwritten."""
+    x = _mat(x)
+    d = x.shape[1]
+    if quantize:
+        out = torch.empty(plan.padded_rows, d, dtype=torch.uint8, device=x.device)
+        sf = torch.empty(sf_bytes(plan.padded_rows, d // 32), dtype=torch.uint8, device=x.device)
+    else:
+        out = torch.empty(plan.padded_rows, d, dtype=torch.bfloat16, device=x.device)
+        sf = None
+    _lib.check(_lib.load().b200q_moe_gather(x.data_ptr(), d, x.stride(0), plan.src_of_row.data_ptr(), plan.num_tiles.data_ptr(),
+                                            plan.padded_rows, int(quantize), fmt_of(fmt), out.data_ptr(),
+                                            sf.data_ptr() if quantize else None, _stream()), "b200q_moe_gather")
+    return (out, sf) if quantize else out
+
+
+def grouped_gemm_mxfp8(a_codes, a_sf, b_codes, b_sf, plan: MoEPlan, n: int, a_fmt=E4M3, b_fmt=E4M3, out=None):
+    """D[padded_rows, n]: row tile i times the (n, K) weight of expert plan.tile_expert[i];
+    b_codes is (E * n, K)."""
+    rows, k = a_codes.shape
+    d = _out(rows, n, a_codes.device, out)
+    _lib.check(_lib.load().b200q_grouped_gemm_mxfp8(a_codes.data_ptr(), fmt_of(a_fmt), a_sf.data_ptr(), b_codes.data_ptr(),
+                                                    fmt_of(b_fmt), b_sf.data_ptr(), plan.tile_expert.data_ptr(),
+                                                    plan.num_tiles.data_ptr(), rows, plan.n_experts, n, k, d.data_ptr(),
+                                                    d.stride(0), _stream()), "b200q_grouped_gemm_mxfp8")
+    return d
+
+
+def swiglu(g: torch.Tensor, quantize: bool, fmt=E4M3):
+    """g (rows, 2I) bf16 = [gate | up] -> silu(gate) * up as bf16 (rows, I), or MXFP8 (codes, sf)."""
+    g = _mat(g)
+    rows, i2 = g.shape
+    i = i2 // 2
+    if quantize:
+        out = torch.empty(rows, i, dtype=torch.uint8, device=g.device)
+        sf = torch.empty(sf_bytes(rows, i // 32), dtype=torch.uint8, device=g.device)
+    else:
+        out, sf = torch.empty(rows, i, dtype=torch.bfloat16, device=g.device), None
+    _lib.check(_lib.load().b200q_swiglu(g.data_ptr(), rows, i, g.stride(0), int(quantize), fmt_of(fmt), out.data_ptr(),
+                                        sf.data_ptr() if quantize else None, _stream()), "b200q_swiglu")
+    return (out, sf) if quantize else out
+
+
+def moe_unpermute(y: torch.Tensor, weights: torch.Tensor, row_of: torch.Tensor, n_tokens: int):
+    """out[t] = sum_j weights[t, j] * y[row_of[t*k + j]] (fp32 accumulate, bf16 out)."""
+    k = row_of.numel() // n_tokens
+    w = weights.to(torch.bfloat16).contiguous()
+    d = y.shape[1]
+    out = torch.empty(n_tokens, d, dtype=torch.bfloat16, device=y.device)
+    _lib.check(_lib.load().b200q_moe_unpermute(y.data_ptr(), y.stride(0), w.data_ptr(), row_of.data_ptr(), n_tokens, k, d,
+                                               out.data_ptr(), _stream()), "b200q_moe_unpermute")
+    return out
+
+
 def device_status() -> None:
     """Raises if a kernel's bounded wait expired since the last check (synchronizes)."""
     _lib.check(_lib.load().b200q_device_status(), "b200q device status")

@@ -100,7 +100,7 @@ void hc_quant_nvfp4_rows(const uint16_t* x, int64_t rows, int64_t cols, float te
       const uint16_t* p = x + r * cols + b * 16;
       float amax = 0.f;
       for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(bf(p[i])));
-      uint8_t sq = nv_block_scale(amax, s_t);
+      uint8_t sq = nv_block_scale_fast(amax, s_t, rcp_rn(s_t));
       sf[r * nblk + b] = sq;
       float eff = e4m3_to_float(sq) * s_t;
       float rcp = rcp_rn(eff);
@@ -109,6 +109,22 @@ void hc_quant_nvfp4_rows(const uint16_t* x, int64_t rows, int64_t cols, float te
         packed[r * (cols / 2) + b * 8 + i / 2] = c;
       }
     }
+}
+
+// Every bf16 block maximum against every `stride`-th bf16 tensor maximum >= it: the
+// hoisted-reciprocal block scale must equal the one computed with IEEE divisions.
+void hc_nv_block_scale_exhaustive(int stride, int64_t* out) {
+  int64_t bad = 0, n = 0;
+  for (uint32_t tb = 1; tb < 0x7F80u; tb += stride) {
+    float s_t = nv_tensor_scale(bf((uint16_t)tb));
+    float rcp_st = rcp_rn(s_t);
+    for (uint32_t ab = 0; ab <= tb; ++ab) {
+      float a = bf((uint16_t)ab);
+      ++n;
+      if (nv_block_scale(a, s_t) != nv_block_scale_fast(a, s_t, rcp_st)) ++bad;
+    }
+  }
+  out[0] = bad; out[1] = n;
 }
 
 void hc_e4m3_decode_table(float* out256) {

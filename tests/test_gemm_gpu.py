@@ -134,11 +134,14 @@ def test_nvfp4_single_scale_factor_lands_where_expected(ops):
         assert torch.equal(out, want), (row, kb, on_a)
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 192, 256])
 @pytest.mark.parametrize("kind", ["fp8", "mxfp8", "nvfp4"])
-def test_both_tile_widths(ops, bn, kind):
+@pytest.mark.parametrize("n", [768, 1000])
+def test_every_tile_width(ops, bn, kind, n):
+    """Width 192 starts every other B tile off the 128-row scale-factor groups (column offset into
+    the tensor-memory scale block); n = 1000 adds a ragged last tile."""
     from pretrain_b200 import _lib
-    a, b = _rand(512, 1024, 9), _rand(768, 1024, 10)
+    a, b = _rand(512, 1024, 9), _rand(n, 1024, 10)
     _lib.load().b200q_debug_set_gemm_bn(bn)
     try:
         if kind == "fp8":

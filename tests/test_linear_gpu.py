@@ -136,4 +136,4 @@ def test_swapped_model_trains_one_step_and_compiles():
     compiled = torch.compile(model, fullgraph=True)
     with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
         a, b = model(x), compiled(x)
-    assert torch.equal(a, b)
+    assert _rel(a, b) < 5e-2          # Inductor fuses bias add and SiLU with other roundings; requantization amplifies them

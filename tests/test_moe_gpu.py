@@ -1,0 +1,218 @@
+"""MoE path on the GPU through the C-ABI: permute plan bit-exact against the reference's own
+sort (golden vectors), gather / quantize bit-exact against the oracle, ragged grouped GEMM,
+SwiGLU and weighted unpermute within tolerance, including empty experts first / middle / last
+(the group patterns of the reference's tests/fast/layers/test_mlp.py:929)."""
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import restate as R
+from conftest import bf16_from_bits
+import gpu_ref as G
+
+pytestmark = pytest.mark.gpu
+E4 = torch.float8_e4m3fn
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from pretrain_b200 import build, ops
+    build.build()
+    return ops
+
+
+def _rel(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return ((a - b).norm() / b.norm()).item()
+
+
+def _check_plan(plan, top_i, n_experts):
+    order, tok, counts, offs = R.moe_permute(top_i, n_experts)
+    assert torch.equal(plan.offs.cpu(), offs)
+    pstart = torch.zeros(n_experts + 1, dtype=torch.int64)
+    pstart[1:] = ((counts + 127) // 128 * 128).cumsum(0)
+    assert torch.equal(plan.padded_offs.cpu().long(), pstart)
+    assert plan.num_tiles.item() == pstart[-1] // 128
+    starts = offs.long() - counts
+    expert_sorted = top_i.reshape(-1)[order]
+    want_rows = pstart[expert_sorted] + torch.arange(order.numel()) - starts[expert_sorted]
+    row_of = plan.row_of.cpu().long()
+    assert torch.equal(row_of[order], want_rows)                      # stable: the reference's row order
+    src = plan.src_of_row.cpu().long()
+    assert torch.equal(src[want_rows], tok)
+    mask = torch.ones(plan.padded_rows, dtype=torch.bool)
+    mask[want_rows] = False
+    assert (src[mask] == -1).all()
+    te = plan.tile_expert.cpu()
+    for e in range(n_experts):
+        assert (te[pstart[e] // 128: pstart[e + 1] // 128] == e).all()
+    assert (te[pstart[-1] // 128:] == -1).all()
+    return want_rows, tok
+
+
+def test_permute_plan_matches_reference_golden(ops, golden):
+    top_i = torch.from_numpy(golden["moe_top_i"])
+    plan = ops.moe_permute_plan(top_i.cuda(), 6)
+    assert np.array_equal(plan.offs.cpu().numpy(), golden["moe_offs"])
+    want_rows, tok = _check_plan(plan, top_i, 6)
+    assert np.array_equal(tok.numpy(), golden["moe_token_ids_sorted"])
+    x = bf16_from_bits(golden["moe_x"])
+    xs = ops.moe_gather(x.cuda(), plan, False).cpu()
+    assert np.array_equal(xs[want_rows].view(torch.int16).numpy(), golden["moe_x_sorted"])
+    live = plan.num_tiles.item() * 128
+    pad = torch.ones(live, dtype=torch.bool)
+    pad[want_rows] = False
+    assert (xs[:live][pad] == 0).all()
+
+
+@pytest.mark.parametrize("t,k,e", [(16384, 4, 64), (1000, 2, 8), (3000, 8, 256), (7, 1, 4)])
+def test_permute_plan_large_and_ragged(ops, t, k, e):
+    g = torch.Generator().manual_seed(t)
+    logits = torch.randn(t, e, generator=g)
+    if e >= 8:
+        logits[:, 3] = -1e9                                            # an expert nobody picks
+    top_i = torch.topk(logits, k, dim=-1).indices
+    plan = ops.moe_permute_plan(top_i.cuda(), e)
+    _check_plan(plan, top_i, e)
+
+
+def test_fused_permute_quantize_is_bit_exact(ops):
+    x, logits, _, _ = R.inputs_moe(2048, 768, 64, 4, 384)
+    top_i, _ = R.router_topk(logits, 4)
+    plan = ops.moe_permute_plan(top_i.cuda(), 64)
+    want_rows, tok = _check_plan(plan, top_i, 64)
+    codes, sf = ops.moe_gather(x.cuda(), plan, True)
+    rc, rs = R.quantize_mxfp8(x[tok])
+    assert torch.equal(codes.cpu()[want_rows], rc)
+    sf_nat = G.unswizzle(sf, plan.padded_rows, 768 // 32).cpu()
+    assert torch.equal(sf_nat[want_rows], rs)
+
+
+def _grouped_ref(a_deq, w_deq, counts):
+    out = torch.zeros(a_deq.shape[0], w_deq.shape[1], device=a_deq.device)
+    s = 0
+    for e, c in enumerate(counts):
+        if c:
+            out[s:s + c] = G.matmul_fp32(a_deq[s:s + c], w_deq[e])
+        s += c
+    return out
+
+
+@pytest.mark.parametrize("counts", [[5, 0, 7, 4], [0, 5, 7, 4], [5, 7, 4, 0], [200, 0, 0, 131], [128, 256, 1, 0]])
+@pytest.mark.parametrize("d,n", [(256, 384), (768, 768)])
+def test_grouped_gemm_with_empty_experts(ops, counts, d, n):
+    g = torch.Generator().manual_seed(sum(counts) + d)
+    r, e = sum(counts), len(counts)
+    x = torch.randn(r, d, generator=g).bfloat16().cuda()
+    w = (0.05 * torch.randn(e, n, d, generator=g)).bfloat16().cuda()
+    offs = torch.tensor(counts).cumsum(0).int().cuda()
+    plan = ops.moe_pad_plan(offs, r)
+    a, sfa = ops.moe_gather(x, plan, True)
+    wq, wsf = ops.quantize_mxfp8(w.reshape(e * n, d), 1)
+    out = ops.grouped_gemm_mxfp8(a, sfa, wq, wsf, plan, n)
+    ops.device_status()
+    xq, xsf = ops.quantize_mxfp8(x, 1)
+    ref = _grouped_ref(G.deq_mxfp8(xq, xsf), G.deq_mxfp8(wq, wsf).view(e, n, d), counts)
+    pstart = plan.padded_offs.cpu().tolist()
+    s = 0
+    for ei, c in enumerate(counts):
+        if c:
+            got = out[pstart[ei]: pstart[ei] + c]
+            mx, fro = G.rel_errors(got, ref[s:s + c])
+            assert mx <= 1e-2 and fro <= 1e-2, (ei, mx, fro)
+            assert (out[pstart[ei] + c: pstart[ei + 1]] == 0).all()   # pad rows stay zero
+        s += c
+
+
+def test_swiglu(ops):
+    g = torch.Generator().manual_seed(0)
+    h = (2.0 * torch.randn(384, 768, generator=g)).bfloat16().cuda()
+    ref = F.silu(h[:, :384]) * h[:, 384:]                             # the reference's bf16 tensor ops
+    out = ops.swiglu(h, False)
+    assert (out.float() - ref.float()).abs().max() <= 2 ** -7 * ref.float().abs().max()
+    assert _rel(out, ref) < 3e-3
+    codes, sf = ops.swiglu(h, True)
+    rc, rsf = ops.quantize_mxfp8(out, 1)
+    assert torch.equal(codes, rc) and torch.equal(sf, rsf)            # fused == unfused
+
+
+def test_unpermute(ops, golden):
+    top_i = torch.from_numpy(golden["moe_top_i"])
+    top_w = bf16_from_bits(golden["moe_top_w"])
+    eo = bf16_from_bits(golden["moe_expert_out"])
+    plan = ops.moe_permute_plan(top_i.cuda(), 6)
+    want_rows, tok = _check_plan(plan, top_i, 6)
+    y_pad = torch.zeros(plan.padded_rows, eo.shape[1], dtype=torch.bfloat16)
+    y_pad[want_rows] = eo
+    out = ops.moe_unpermute(y_pad.cuda(), top_w.cuda(), plan.row_of, top_i.shape[0]).cpu()
+    order = torch.from_numpy(golden["moe_order"])
+    ref32 = R.moe_unpermute_fp32(eo, top_w.reshape(-1)[order], tok, top_i.shape[0])
+    assert (out.float() - ref32.float()).abs().max() <= 2 ** -7 * ref32.float().abs().max()
+    gold = bf16_from_bits(golden["moe_y"])                            # the reference's bf16 index_add_
+    assert (out.float() - gold.float()).abs().max() <= 2e-2 * gold.float().abs().max()
+
+
+def _mx_fake(t):
+    c, s = R.quantize_mxfp8(t)
+    return R.dequantize_mxfp8(c, s).to(t.dtype)
+
+
+@pytest.mark.parametrize("counts", [[5, 0, 7, 4], [0, 5, 7, 4], [5, 7, 4, 0], [300, 40, 0, 129]])
+def test_grouped_mlp_drop_in(ops, counts):
+    from pretrain_b200.layers.mlp import grouped_mlp, silu_glu
+    g = torch.Generator().manual_seed(len(counts) + counts[0])
+    r, e, d, i = sum(counts), len(counts), 256, 128
+    x = torch.randn(r, d, generator=g).bfloat16()
+    w_in = (0.05 * torch.randn(e, 2 * i, d, generator=g)).bfloat16()
+    w_down = (0.05 * torch.randn(e, d, i, generator=g)).bfloat16()
+    offs = torch.tensor(counts).cumsum(0).int()
+    with torch.no_grad():
+        out = grouped_mlp(x.cuda(), w_in.cuda(), w_down.cuda(), silu_glu, offs.cuda(), True)
+    assert out.shape == (r, d)
+    ref = R.grouped_mlp_ref(x, w_in, w_down, offs, fake_quant=_mx_fake)
+    assert _rel(out, ref) < 2e-2
+    plain = R.grouped_mlp_ref(x, w_in, w_down, offs)                   # unquantized reference: only quantization noise apart
+    assert _rel(out, plain) < 0.08
+    with pytest.raises(NotImplementedError):
+        grouped_mlp(x.cuda().requires_grad_(True), w_in.cuda(), w_down.cuda(), silu_glu, offs.cuda(), True)
+
+
+def test_grouped_mlp_against_reference_golden(ops, golden):
+    from pretrain_b200.layers.mlp import grouped_mlp, silu_glu
+    xs = bf16_from_bits(golden["moe_x_sorted"])
+    w_in, w_down = bf16_from_bits(golden["moe_w_in"]), bf16_from_bits(golden["moe_w_down"])
+    offs = torch.from_numpy(golden["moe_offs"])
+    with torch.no_grad():
+        out = grouped_mlp(xs.cuda(), w_in.cuda(), w_down.cuda(), silu_glu, offs.cuda(), True)
+    gold = bf16_from_bits(golden["moe_expert_out"])                    # the reference's bf16 grouped_mlp
+    assert _rel(out, gold) < 0.08
+
+
+def test_sparse_moe_block_full_config(ops):
+    """16384 tokens, hidden 768, 64 experts, top-4, intermediate 384: the block against the
+    oracle's per-expert loop with fake-quantized operands on a sample of tokens, plus exact
+    conservation of the routing (every pair lands in exactly one row)."""
+    from pretrain_b200.layers.mlp import SparseMoEBlock
+    x, logits, w_gu, w_d = R.inputs_moe()
+    blk = SparseMoEBlock(768, intermediate_size=384, n_routed_experts=64, n_routed_experts_per_token=4,
+                         router_score_fn="softmax").cuda()
+    with torch.no_grad():
+        blk.expert_gate_up.copy_(w_gu)
+        blk.expert_down.copy_(w_d)
+        torch.nn.init.normal_(blk.router.gate.weight, std=0.02)
+        out, aux = blk(x.cuda().view(16, 1024, 768))
+        top_i, top_w, _ = blk.router(x.cuda())
+    assert out.shape == (16, 1024, 768) and torch.isfinite(out).all() and aux is not None and torch.isfinite(aux)
+    top_i, top_w = top_i.cpu(), top_w.cpu()
+    sample = torch.arange(0, 16384, 257)
+    ref = torch.zeros(len(sample), 768)
+    for n, t in enumerate(sample.tolist()):
+        for j in range(4):
+            e = top_i[t, j].item()
+            h = (_mx_fake(x[t:t + 1]).float() @ _mx_fake(w_gu[e]).float().t()).bfloat16()
+            h = R.silu_glu(*h.chunk(2, dim=-1))
+            y = (_mx_fake(h).float() @ _mx_fake(w_d[e]).float().t()).bfloat16()
+            ref[n] += top_w[t, j].float() * y[0].float()
+    assert _rel(out.view(-1, 768)[sample], ref) < 2e-2
