@@ -37,7 +37,7 @@ constexpr int kGemmThreads = 192;
 constexpr int kSmemBudget = 227 * 1024;
 constexpr int EPI_COLS = 32;             // columns per epilogue block
 constexpr int EPI_BLOCK_BYTES = 32 * EPI_COLS * 2;
-constexpr int EPI_BYTES = 4 * 2 * EPI_BLOCK_BYTES;   // 4 warps x 2 buffers
+constexpr int kEpiBytes1 = 4 * EPI_BLOCK_BYTES;      // one staging block per epilogue warp
 
 constexpr int cgcd(int a, int b) { return b == 0 ? a : cgcd(b, a % b); }
 
@@ -54,7 +54,13 @@ struct Cfg {
   static constexpr int SFA_BYTES = KIND == KIND_F8 ? 0 : K_ATOMS * 512;
   static constexpr int SFB_BYTES = KIND == KIND_F8 ? 0 : NB_ATOMS * K_ATOMS * 512;
   static constexpr int STAGE_BYTES = ((A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024) * 1024;
-  static constexpr int STAGES_RAW = (kSmemBudget - 2048 - EPI_BYTES) / STAGE_BYTES;
+  // Two staging blocks per epilogue warp unless giving one up buys another pipeline stage
+  // (NVFP4 at width 256: 4 stages of 54 KB only fit beside 8 KB of staging).
+  static constexpr int STAGES_2BUF = (kSmemBudget - 2048 - 2 * kEpiBytes1) / STAGE_BYTES;
+  static constexpr int STAGES_1BUF = (kSmemBudget - 2048 - kEpiBytes1) / STAGE_BYTES;
+  static constexpr int EPI_BUFS = (STAGES_1BUF > STAGES_2BUF && STAGES_2BUF < 4) ? 1 : 2;
+  static constexpr int EPI_BYTES = EPI_BUFS * kEpiBytes1;
+  static constexpr int STAGES_RAW = EPI_BUFS == 1 ? STAGES_1BUF : STAGES_2BUF;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SFA_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS;
   static constexpr int SFB_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS * NB_ATOMS;
@@ -63,7 +69,7 @@ struct Cfg {
   static constexpr int SFB_COL0 = SFA_COL0 + SFA_COLS;
   static constexpr int TMEM_COLS = 512;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;                     // 1024-aligned
-  static constexpr int BAR_OFF = EPI_OFF + EPI_BYTES;
+  static constexpr int BAR_OFF = EPI_OFF + EPI_BYTES;   // EPI_BYTES is a multiple of 1024
   static constexpr int SMEM_BYTES = BAR_OFF + 256 /*barriers*/ + 1024 /*alignment slack*/;
   // A B tile may start 64 rows into a 128-row scale-factor group (tensor-memory column offset 2);
   // offsets of 32 or 96 rows (odd column offsets) are misaligned for the MMA's scale operand.
@@ -253,8 +259,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else {
     // ------------------------------- epilogue ------------------------------------------------
     const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
-    const uint32_t epi_s = smem_base + C::EPI_OFF + q * 2 * EPI_BLOCK_BYTES;
-    uint8_t* epi_g = smem_gen + C::EPI_OFF + q * 2 * EPI_BLOCK_BYTES;
+    const uint32_t epi_s = smem_base + C::EPI_OFF + q * C::EPI_BUFS * EPI_BLOCK_BYTES;
+    uint8_t* epi_g = smem_gen + C::EPI_OFF + q * C::EPI_BUFS * EPI_BLOCK_BYTES;
     int buf = 0;
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
@@ -287,7 +293,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
           o[i] = pack_bf16(lo, hi);
         }
-        if (lane == 0) ptx::bulk_wait_read<1>();      // the store that last read this buffer is done with it
+        if (lane == 0) ptx::bulk_wait_read<C::EPI_BUFS - 1>();   // the store that last read this buffer is done with it
         __syncwarp();
         uint8_t* dst = epi_g + buf * EPI_BLOCK_BYTES + lane * 64;
         const int sw = (lane >> 1) & 3;               // 64-byte swizzle: 16-byte chunk j of row r sits at j ^ ((r >> 1) & 3)
@@ -300,7 +306,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           ptx::tma_store_2d(&tmap_d, (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
           ptx::bulk_commit();
         }
-        buf ^= 1;
+        buf = (buf + 1) % C::EPI_BUFS;
       };
 
       uint32_t ra[32], rb[32];
@@ -402,7 +408,7 @@ int g_force_bn = 0;   // test hook: 0 = choose by shape
 
 // Tile width by a small cost model (cycles per tile x waves): the main loop is bound by the
 // tensor pipe (2*BN cycles per K step) or by shared-memory reads ((128+BN)*128 bytes per K
-// step at ~120 B/clk); the epilogue hides behind the next main loop only when two
+// step at ~100 B/clk, fitted to measurements); the epilogue hides behind the next main loop only when two
 // accumulators fit in tensor memory (every width but 256).
 template <int KIND>
 int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
@@ -413,7 +419,7 @@ int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
   for (int bn : cands) {
     const int64_t tiles = num_m * ((N + bn - 1) / bn);
     const int64_t waves = (tiles + kNumSMs - 1) / kNumSMs;
-    const double kstep = std::max(2.0 * bn, (128.0 + bn) * 128.0 / 120.0);
+    const double kstep = std::max(2.0 * bn, (128.0 + bn) * 128.0 / 100.0);
     const double mainloop = num_k * kstep + 600.0, epi = 300.0 + (bn / 32) * 220.0;
     const double per_tile = bn == 256 && KIND != KIND_F8 ? mainloop + epi : std::max(mainloop, epi);
     const double cost = waves * per_tile;

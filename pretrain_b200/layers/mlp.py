@@ -43,8 +43,9 @@ def _quantize_expert_weights(w: torch.Tensor):
     """(E, out, in) weight stack -> MXFP8 codes (E*out, in) + swizzled scales, blocks along `in`."""
     e, n, k = w.shape
     if n % 128:
-        raise ValueError("expert output width must be a multiple of 128 (scale-factor tiles must not straddle experts)")
-    return ops.quantize_mxfp8(w.reshape(e * n, k), 1)
+        # scale-factor tiles hold 128 rows and must not straddle experts: pad every expert's rows
+        w = torch.cat([w, w.new_zeros(e, 128 - n % 128, k)], dim=1)
+    return ops.quantize_mxfp8(w.reshape(-1, k), 1)
 
 
 def _expert_of_padded_row(plan) -> torch.Tensor:
@@ -56,7 +57,8 @@ def _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in=None, b_
     n1, n2 = w_in.shape[1], w_down.shape[1]
     wq1, wsf1 = _quantize_expert_weights(w_in)
     wq2, wsf2 = _quantize_expert_weights(w_down)
-    h = ops.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, n1)
+    e = w_in.shape[0]
+    h = ops.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, wq1.shape[0] // e)[:, :n1]
     if b_in is not None:
         h = h + b_in.to(h.dtype)[_expert_of_padded_row(plan)]
     if gated and act_fn is silu_glu:
@@ -64,7 +66,7 @@ def _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in=None, b_
     else:
         act = act_fn(*h.chunk(2, dim=-1)) if gated else act_fn(h)
         hq, hsf = ops.quantize_mxfp8(act.contiguous(), 1)
-    out = ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, n2)
+    out = ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, wq2.shape[0] // e)[:, :n2]
     if b_down is not None:
         out = out + b_down.to(out.dtype)[_expert_of_padded_row(plan)]
     return out
