@@ -1,0 +1,139 @@
+"""Multi-GPU forms of the path, one process per GPU over ``torch.distributed``.
+
+* Dense GEMMs shard by rows of A (B replicated).  Quantization is row-local along K, so a shard is
+  quantized and multiplied exactly as the same rows would be on one GPU; the only collective is the
+  optional all-gather of the output shards.
+* The MoE block is expert-parallel: tokens are sharded across ranks, experts are split in
+  contiguous ranges; one count exchange and one all-to-all of rows each way around the local
+  grouped FFN.
+
+The exchange logic is plain ``torch.distributed`` on whatever backend the group has (NCCL on GPUs,
+gloo in the CPU tests); the compute steps are passed in as callables so that the CPU tests can
+exercise the exchange with a reference computation.  Nothing here exists in the reference, which is
+single-GPU (no collective call anywhere in it).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def row_shard(m: int, world: int, rank: int, multiple: int = 128) -> tuple[int, int]:
+    """[start, stop) of this rank's rows: `multiple`-row tiles dealt as evenly as possible, in
+    rank order (the last ranks may get one tile less; a rank can be empty when m is small)."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} for world size {world}")
+    tiles = (m + multiple - 1) // multiple
+    base, extra = divmod(tiles, world)
+    first = rank * base + min(rank, extra)
+    count = base + (1 if rank < extra else 0)
+    return min(first * multiple, m), min((first + count) * multiple, m)
+
+
+def all_gather_rows(local: torch.Tensor, m: int, group=None, multiple: int = 128) -> torch.Tensor:
+    """Concatenate the ranks' row shards (shards as dealt by `row_shard`) into the full (m, n) matrix."""
+    world = dist.get_world_size(group)
+    sizes = [b - a for a, b in (row_shard(m, world, r, multiple) for r in range(world))]
+    if local.shape[0] != sizes[dist.get_rank(group)]:
+        raise ValueError(f"shard has {local.shape[0]} rows, expected {sizes[dist.get_rank(group)]}")
+    if len(set(sizes)) == 1:
+        out = local.new_empty(m, *local.shape[1:])
+        dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+        return out
+    # ragged shards: collectives want equal sizes, so pad to the largest shard and cut afterwards
+    biggest = max(sizes)
+    padded = local.new_zeros(biggest, *local.shape[1:])
+    padded[: local.shape[0]] = local
+    out = local.new_empty(world * biggest, *local.shape[1:])
+    dist.all_gather_into_tensor(out, padded, group=group)
+    return torch.cat([out[r * biggest: r * biggest + s] for r, s in enumerate(sizes)], dim=0)
+
+
+def sharded_gemm(a_shard: torch.Tensor, b: torch.Tensor, a_fmt: str, b_fmt: str, out_dtype, m: int, rowwise: bool = False,
+                 gather: bool = True, group=None, gemm: Optional[Callable] = None) -> torch.Tensor:
+    """`a @ b` with a's rows sharded across the group: every rank multiplies its shard, the output
+    shards are all-gathered when `gather`.  `gemm` defaults to the quantized `_gemm`."""
+    if gemm is None:
+        from .quant.linear import _gemm as gemm
+    local = gemm(a_shard, b, a_fmt, b_fmt, out_dtype, rowwise)
+    return all_gather_rows(local, m, group) if gather else local
+
+
+# ---- expert parallelism ---------------------------------------------------------------------
+
+@dataclass
+class DispatchState:
+    send_order: torch.Tensor      # (n_pairs,) flat (token, slot) index of every sent row, in send order
+    send_splits: list             # rows sent to each rank
+    recv_splits: list             # rows received from each rank
+    recv_expert: torch.Tensor     # (n_recv,) local expert id of every received row
+    n_pairs: int
+
+
+def ep_dispatch(x: torch.Tensor, top_indices: torch.Tensor, n_experts: int, group=None):
+    """Send every routed (token, slot) pair's row to the rank that owns its expert.
+
+    Experts are split in contiguous ranges of n_experts / world.  Rows leave sorted by (expert, token,
+    slot) — the reference's stable expert order (src/layers/mlp.py:447-452) restricted to each
+    destination — after a count exchange that tells every rank how many rows per local expert each
+    peer sends.  Returns (received rows, DispatchState)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if n_experts % world:
+        raise ValueError(f"{n_experts} experts do not split evenly over {world} ranks")
+    e_local = n_experts // world
+    t, k = top_indices.shape
+    flat_e = top_indices.reshape(-1)
+    _, order = flat_e.sort(stable=True)
+    counts = torch.bincount(flat_e, minlength=n_experts)                      # rows per global expert
+    recv_counts = torch.empty_like(counts)
+    dist.all_to_all_single(recv_counts, counts, group=group)                  # [src rank][local expert]
+    send_splits = counts.view(world, e_local).sum(1).tolist()
+    recv_mat = recv_counts.view(world, e_local)
+    recv_splits = recv_mat.sum(1).tolist()
+    rows = x[order // k]                                                      # expert-sorted rows
+    recv = rows.new_empty(sum(recv_splits), x.shape[1])
+    dist.all_to_all_single(recv, rows.contiguous(), output_split_sizes=recv_splits, input_split_sizes=send_splits, group=group)
+    local_ids = torch.arange(e_local, device=x.device).repeat(world)
+    recv_expert = torch.repeat_interleave(local_ids, recv_mat.reshape(-1))
+    return recv, DispatchState(order, send_splits, recv_splits, recv_expert, t * k)
+
+
+def ep_combine(y: torch.Tensor, state: DispatchState, top_weights: torch.Tensor, group=None) -> torch.Tensor:
+    """Return every processed row to its sender and reduce the k rows of a token with its routing
+    weights (fp32 accumulation, one rounding — as b200q_moe_unpermute does)."""
+    back = y.new_empty(state.n_pairs, y.shape[1])
+    dist.all_to_all_single(back, y.contiguous(), output_split_sizes=state.send_splits, input_split_sizes=state.recv_splits,
+                           group=group)
+    t, k = top_weights.shape
+    per_pair = torch.empty_like(back)
+    per_pair[state.send_order] = back                                          # undo the expert sort
+    w = top_weights.reshape(t, k, 1).float()
+    return (per_pair.view(t, k, -1).float() * w).sum(1).to(y.dtype)
+
+
+def expert_ffn_local(rows: torch.Tensor, expert_ids: torch.Tensor, w_in: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """Gated-SwiGLU expert FFN for rows in ARBITRARY order with their local expert ids, on the
+    MXFP8 kernels: local permute plan, fused gather+quantize, two grouped GEMMs with the fused
+    SwiGLU between them, rows returned in the input order."""
+    from . import ops
+    from .layers.mlp import _grouped_ffn_padded, silu_glu
+    if rows.shape[0] == 0:
+        return rows.new_empty(0, w_down.shape[1])
+    plan = ops.moe_permute_plan(expert_ids.view(-1, 1), w_in.shape[0])
+    a, sfa = ops.moe_gather(rows, plan, True)
+    y = _grouped_ffn_padded(a, sfa, plan, w_in, w_down, silu_glu, True)
+    return y[plan.row_of.long()]
+
+
+def expert_parallel_moe(x: torch.Tensor, top_indices: torch.Tensor, top_weights: torch.Tensor, w_in_local: torch.Tensor,
+                        w_down_local: torch.Tensor, n_experts: int, group=None, ffn: Callable = expert_ffn_local) -> torch.Tensor:
+    """Expert-parallel MoE forward for this rank's tokens: dispatch all-to-all, local expert FFN
+    on this rank's experts (`w_*_local` are its (E/world, out, in) slices), combine all-to-all,
+    weighted reduction.  Equals the single-GPU block on the concatenated tokens."""
+    recv, state = ep_dispatch(x, top_indices, n_experts, group)
+    y = ffn(recv, state.recv_expert, w_in_local, w_down_local)
+    return ep_combine(y, state, top_weights, group)
