@@ -147,6 +147,12 @@ def run_cpu(kind, m, n, k, steps, warmup):
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
+def _mark(marks):
+    e = torch.cuda.Event(enable_timing=True)
+    e.record()
+    marks.append(e)
+
+
 def make_step(kind, a, b, out):
     """Returns (step_fn, gemm_only_fn_factory, launches_per_step).  step_fn records CUDA events
     around the GEMM launch into `marks`."""
@@ -154,28 +160,25 @@ def make_step(kind, a, b, out):
     E4 = torch.float8_e4m3fn
 
     def step(marks=None):
+        ev = (lambda: None) if marks is None else (lambda: _mark(marks))
+        ev()                                        # start of the quantize kernels
         if kind == "mxfp8":
             ca, sfa = ops.quantize_mxfp8(a, 1)
             cb, sfb = ops.quantize_mxfp8(b, 1)
-            if marks is not None:
-                e0 = torch.cuda.Event(enable_timing=True); e0.record()
+            ev()                                    # start of the GEMM
             ops.gemm_mxfp8(ca, sfa, cb, sfb, out=out)
         elif kind == "nvfp4":
             aa, ab = ops.amax(a), ops.amax(b)
             pa, sfa, ta = ops.quantize_nvfp4(a, 1, aa)
             pb, sfb, tb = ops.quantize_nvfp4(b, 1, ab)
-            if marks is not None:
-                e0 = torch.cuda.Event(enable_timing=True); e0.record()
+            ev()
             ops.gemm_nvfp4(pa, sfa, ta, pb, sfb, tb, out=out)
         else:
             ca, sa = ops.quantize_fp8(a, E4, 1)
             cb, sb = ops.quantize_fp8(b, E4, 1)
-            if marks is not None:
-                e0 = torch.cuda.Event(enable_timing=True); e0.record()
+            ev()
             ops.gemm_fp8(ca, E4, cb, E4, sa, sb, out=out)
-        if marks is not None:
-            e1 = torch.cuda.Event(enable_timing=True); e1.record()
-            marks.append((e0, e1))
+        ev()                                        # end of the GEMM
         return out
 
     launches = {"mxfp8": 3, "nvfp4": 5, "fp8": 3}[kind]
@@ -251,11 +254,13 @@ def main():
         barrier()
     ops.device_status()
     ms_total = t0.elapsed_time(t1)
-    gemm_ms = sum(e0.elapsed_time(e1) for e0, e1 in marks) / len(marks)
+    trip = [marks[i:i + 3] for i in range(0, len(marks), 3)]       # (quantize start, GEMM start, GEMM end) per step
+    quant_ms = sum(q.elapsed_time(g0) for q, g0, _ in trip) / len(trip)
+    gemm_ms = sum(g0.elapsed_time(g1) for _, g0, g1 in trip) / len(trip)
     if dist is not None:
-        t = torch.tensor([ms_total, gemm_ms], device="cuda", dtype=torch.float64)
+        t = torch.tensor([ms_total, gemm_ms, quant_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, gemm_ms = t.tolist()
+        ms_total, gemm_ms, quant_ms = t.tolist()
     ms_step = ms_total / args.steps
     flops = 2.0 * m * n * k
     value = world * flops / (ms_step * 1e-3) / 1e12
@@ -322,10 +327,17 @@ def main():
                 "frac": achieved / peak, "peak_source": f"{ratio:g} x bf16_tflops_sustained, {peaks['source']}",
                 "frac_of_nominal": achieved / NOMINAL_TFLOPS[kind], "nominal_peak": NOMINAL_TFLOPS[kind],
                 "traffic": GEMM_DRAM_TRAFFIC.get(args.workload), "kernel_ms": gemm_ms}
+    # the quantize kernels of the step against the measured HBM copy bandwidth (algorithmic bytes:
+    # bf16 in, codes + scale bytes out; NVFP4 also reads each operand once more for its amax)
+    bpe = {"mxfp8": 3.03125, "fp8": 3.0, "nvfp4": 2.0 + 2.5625}[kind]
+    q_bytes = (m * k + n * k) * bpe
+    quantize = {"bound": "hbm", "achieved": q_bytes / (quant_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": q_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": f"hbm_gbs, {peaks['source']}",
+                "kernels_ms": quant_ms, "bytes": q_bytes}
     line = {"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind,
             "data": "synthetic", "config": config, "clocks": clk.summary(), "e2e": e2e, "gpu_launches": launches * args.steps,
-            "roofline": roofline}
+            "roofline": roofline, "quantize": quantize}
     if allgather is not None:
         line["allgather"] = allgather
     if world == 1 and not args.no_cpu_baseline:

@@ -55,4 +55,22 @@ __device__ __forceinline__ float absmax8(uint4 v) {
   return fmaxf(bf16lo(m), bf16hi(m));
 }
 
+// Walks (row, chunk) work items that are dealt round-robin over all warps of the grid, without
+// a division inside the loop: item = first, first + stride, ...; row = item / chunks.
+struct ItemWalker {
+  int64_t row, row_step;
+  int chunk, chunks, chunk_step;
+  __device__ __forceinline__ ItemWalker(int64_t first, int64_t stride, int chunks_) : chunks(chunks_) {
+    row = first / chunks_;
+    chunk = (int)(first - row * chunks_);
+    row_step = stride / chunks_;
+    chunk_step = (int)(stride - row_step * chunks_);
+  }
+  __device__ __forceinline__ void next() {
+    row += row_step;
+    chunk += chunk_step;
+    if (chunk >= chunks) { chunk -= chunks; ++row; }
+  }
+};
+
 }  // namespace b200q

@@ -209,9 +209,9 @@ __global__ void __launch_bounds__(256)
 swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t ld, int fmt, uint8_t* __restrict__ out,
               uint8_t* __restrict__ sf) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t nblk = I >> 5, chunks = (I + 255) >> 8, items = rows * chunks;
-  for (int64_t item = (int64_t)blockIdx.x * 8 + warp; item < items; item += (int64_t)gridDim.x * 8) {
-    const int64_t r = item / chunks, c = (item - r * chunks) * 256 + lane * 8;
+  const int64_t nblk = I >> 5;
+  for (ItemWalker w((int64_t)blockIdx.x * 8 + warp, (int64_t)gridDim.x * 8, (int)((I + 255) >> 8)); w.row < rows; w.next()) {
+    const int64_t r = w.row, c = (int64_t)w.chunk * 256 + lane * 8;
     const bool live = c < I;
     uint4 vg = make_uint4(0, 0, 0, 0), vu = vg;
     if (live) {
@@ -248,9 +248,8 @@ __global__ void __launch_bounds__(256)
 moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t* __restrict__ w,
                      const int32_t* __restrict__ row_of, int64_t T, int k, int64_t D, uint16_t* __restrict__ out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t chunks = (D + 255) >> 8, items = T * chunks;
-  for (int64_t item = (int64_t)blockIdx.x * 8 + warp; item < items; item += (int64_t)gridDim.x * 8) {
-    const int64_t t = item / chunks, c = (item - t * chunks) * 256 + lane * 8;
+  for (ItemWalker it((int64_t)blockIdx.x * 8 + warp, (int64_t)gridDim.x * 8, (int)((D + 255) >> 8)); it.row < T; it.next()) {
+    const int64_t t = it.row, c = (int64_t)it.chunk * 256 + lane * 8;
     if (c >= D) continue;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < k; ++j) {

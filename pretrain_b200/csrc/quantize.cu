@@ -49,15 +49,15 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const uint16_t* __restri
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t m = 0;
   // work item = (row, 1024-column chunk); items are dealt round-robin to all warps of the grid
-  const int64_t chunks = (cols + 1023) >> 10, items = rows * chunks;
-  for (int64_t item = (int64_t)blockIdx.x * kWarps + warp; item < items; item += (int64_t)gridDim.x * kWarps) {
-    const int64_t row = item / chunks, c0 = (item - row * chunks) << 10;
-    const uint16_t* xr = x + row * ld;
+  const int chunks = (int)((cols + 1023) >> 10), ncols = (int)cols;
+  for (ItemWalker w((int64_t)blockIdx.x * kWarps + warp, (int64_t)gridDim.x * kWarps, chunks); w.row < rows; w.next()) {
+    const int c0 = w.chunk << 10;
+    const uint16_t* xr = x + w.row * ld + c0;
     uint4 v[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      int64_t c = c0 + u * 256 + lane * 8;
-      v[u] = c < cols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
+      const int c = u * 256 + lane * 8;
+      v[u] = c0 + c < ncols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -96,50 +96,56 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
     if (blockIdx.x == 0 && threadIdx.x == 0) *tensor_scale_out = s_t;
   }
   // work item = (row, 1024-column chunk), dealt round-robin to all warps of the grid
-  const int64_t chunks = (cols + 1023) >> 10, items = rows * chunks;
-  for (int64_t item = (int64_t)blockIdx.x * kWarps + warp; item < items; item += (int64_t)gridDim.x * kWarps) {
-    const int64_t row = item / chunks, c0 = (item - row * chunks) << 10;
-    const uint16_t* xr = x + row * ld;
-    {
-      uint4 v[4];
+  const int chunks = (int)((cols + 1023) >> 10), ncols = (int)cols;
+  const int64_t kt = (nblk + 3) >> 2;
+  for (ItemWalker w((int64_t)blockIdx.x * kWarps + warp, (int64_t)gridDim.x * kWarps, chunks); w.row < rows; w.next()) {
+    const int64_t row = w.row;
+    const int c0 = w.chunk << 10;
+    const uint16_t* xr = x + row * ld + c0;
+    uint8_t* cr = codes + (MODE == MODE_MX ? row * cols + c0 : (row * cols + c0) >> 1);
+    // scale-factor address of block kb of this row = sfr + (swizzled ? (kb >> 2) * 512 + (kb & 3) : kb)
+    uint8_t* sfr = sf + (swz ? (row >> 7) * kt * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 : row * nblk);
+    uint4 v[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        int64_t c = c0 + u * 256 + lane * 8;
-        v[u] = c < cols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
-      }
+    for (int u = 0; u < 4; ++u) {
+      const int c = u * 256 + lane * 8;
+      v[u] = c0 + c < ncols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int64_t c = c0 + u * 256 + lane * 8;
-        if (c0 + u * 256 >= cols) break;   // warp-uniform
-        float a = absmax8(v[u]);
-        a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
-        if (MODE == MODE_MX) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
-        float f[8];
-        unpack8(v[u], f);
-        if (MODE == MODE_MX) {
-          const int e = mx_scale_exp(a, fmt);
-          const float inv = mx_inv_scale(e);
-          uint2 o;
-          o.x = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, fmt);
-          o.y = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, fmt);
-          if (c < cols) {
-            *reinterpret_cast<uint2*>(codes + row * cols + c) = o;
-            if ((lane & 3) == 0) sf[sf_offset(row, c >> 5, nblk, swz)] = (uint8_t)(e + 127);
-          }
-        } else {
-          const uint8_t sq = nv_block_scale_fast(a, s_t, rcp_st);
-          const float eff = mul_rn(e4m3_to_float(sq), s_t);
-          const float rcp = rcp_rn(eff);
-          uint32_t o = 0;
-          if (sq != 0) {
+    for (int u = 0; u < 4; ++u) {
+      const int c = u * 256 + lane * 8;
+      if (c0 + u * 256 >= ncols) break;   // warp-uniform
+      const bool live = c0 + c < ncols;
+      float a = absmax8(v[u]);
+      a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
+      if (MODE == MODE_MX) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
+      float f[8];
+      unpack8(v[u], f);
+      if (MODE == MODE_MX) {
+        const int e = mx_scale_exp(a, fmt);
+        const float inv = mx_inv_scale(e);
+        uint2 o;
+        o.x = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, fmt);
+        o.y = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, fmt);
+        if (live) {
+          *reinterpret_cast<uint2*>(cr + c) = o;
+          const int kb = (c0 + c) >> 5;
+          if ((lane & 3) == 0) sfr[swz ? (kb >> 2) * 512 + (kb & 3) : kb] = (uint8_t)(e + 127);
+        }
+      } else {
+        const uint8_t sq = nv_block_scale_fast(a, s_t, rcp_st);
+        const float eff = mul_rn(e4m3_to_float(sq), s_t);
+        const float rcp = rcp_rn(eff);
+        uint32_t o = 0;
+        if (sq != 0) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              o |= (uint32_t)cvt_e2m1x2(div_by_rcp(f[2 * i], eff, rcp), div_by_rcp(f[2 * i + 1], eff, rcp)) << (8 * i);
-          }
-          if (c < cols) {
-            *reinterpret_cast<uint32_t*>(codes + row * (cols >> 1) + (c >> 1)) = o;
-            if ((lane & 1) == 0) sf[sf_offset(row, c >> 4, nblk, swz)] = sq;
-          }
+          for (int i = 0; i < 4; ++i)
+            o |= (uint32_t)cvt_e2m1x2(div_by_rcp(f[2 * i], eff, rcp), div_by_rcp(f[2 * i + 1], eff, rcp)) << (8 * i);
+        }
+        if (live) {
+          *reinterpret_cast<uint32_t*>(cr + (c >> 1)) = o;
+          const int kb = (c0 + c) >> 4;
+          if ((lane & 1) == 0) sfr[swz ? (kb >> 2) * 512 + (kb & 3) : kb] = sq;
         }
       }
     }
@@ -387,12 +393,15 @@ int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
   return B200Q_OK;
 }
 
-// Grid for the item-based row-wise kernels: one resident wave (4 CTAs of 256 threads per SM);
-// the (row, chunk) items are dealt round-robin, so every warp gets the same share.
-inline int rowwise_grid(int64_t rows, int64_t cols, int ctas_per_sm = 4) {
-  int64_t items = rows * ((cols + 1023) / 1024);
-  int64_t want = (items + kWarps - 1) / kWarps;
-  int64_t cap = (int64_t)kNumSMs * ctas_per_sm;
+// Grid for the item-based row-wise kernels: exactly one resident wave (as many CTAs of 256
+// threads per SM as the kernel's registers allow); the (row, chunk) items are dealt round-robin,
+// so every warp gets the same share and there is no tail wave.
+template <typename Kernel>
+int rowwise_grid(Kernel kernel, int64_t rows, int64_t cols) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+  const int64_t items = rows * ((cols + 1023) / 1024);
+  const int64_t want = (items + kWarps - 1) / kWarps, cap = (int64_t)kNumSMs * per_sm;
   return (int)(want < cap ? want : cap);
 }
 
@@ -447,7 +456,7 @@ int b200q_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, float* ama
   if ((rc = require_sm100())) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   B200Q_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), st));
-  amax_kernel<<<rowwise_grid(rows, cols, 8), kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, amax);
+  amax_kernel<<<rowwise_grid(amax_kernel, rows, cols), kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, amax);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -536,7 +545,7 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf, outer, contraction / 32, sf_layout, st))) return rc;
   if (axis == 1) {
-    rowwise_block_quant_kernel<MODE_MX><<<rowwise_grid(rows, cols), kThreads, 0, st>>>(
+    rowwise_block_quant_kernel<MODE_MX><<<rowwise_grid(rowwise_block_quant_kernel<MODE_MX>, rows, cols), kThreads, 0, st>>>(
         (const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr);
   } else {
     dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
@@ -561,7 +570,7 @@ int b200q_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf, outer, contraction / 16, sf_layout, st))) return rc;
   if (axis == 1) {
-    rowwise_block_quant_kernel<MODE_NV><<<rowwise_grid(rows, cols), kThreads, 0, st>>>(
+    rowwise_block_quant_kernel<MODE_NV><<<rowwise_grid(rowwise_block_quant_kernel<MODE_NV>, rows, cols), kThreads, 0, st>>>(
         (const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax, tensor_scale_out);
   } else {
     dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
