@@ -131,6 +131,19 @@ int b200q_moe_permute_plan(const int64_t* top_idx, int64_t n_pairs, int k, int E
                            int32_t* padded_offs, int32_t* row_of, int32_t* src_of_row,
                            int32_t* tile_expert, int32_t* num_tiles, void* workspace, void* stream);
 
+/* b200q_moe_permute_plan without a workspace argument, for callers that cannot allocate
+ * device memory when they need the plan: a runtime that carved up all of HBM at start-up and
+ * forbids cudaMalloc afterwards (it synchronizes the device and can fail late), or a host in
+ * another language that owns only the tensors it passes in.  The scratch is a fixed 1 MiB array
+ * inside the library, held by every GPU that loads it until the process exits.  It has no
+ * counterpart in the reference.  Limit: ceil(n_pairs / 1024) * E <= 262144, otherwise
+ * B200Q_ERR_SHAPE.  The first call on a device looks up the array's device address; make that
+ * call before any stream capture.  All calls on a device share the array: calls that overlap
+ * on the GPU race on it.  Outputs are identical to b200q_moe_permute_plan's. */
+int b200q_moe_permute_plan_static(const int64_t* top_idx, int64_t n_pairs, int k, int E, int32_t* offs,
+                                  int32_t* padded_offs, int32_t* row_of, int32_t* src_of_row,
+                                  int32_t* tile_expert, int32_t* num_tiles, void* stream);
+
 /* The same plan outputs for rows that are ALREADY expert-sorted (the input convention of
  * grouped_mlp, src/layers/mlp.py:55-72): offs int32 [E] cumulative ends; src_of_row maps a
  * padded row to its row in the sorted input. */

@@ -30,6 +30,7 @@ SIGNATURES = {
     "b200q_moe_padded_rows": (_i64, [_i64, _int]),
     "b200q_moe_plan_workspace_bytes": (_i64, [_i64, _int]),
     "b200q_moe_permute_plan": (_int, [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_moe_permute_plan_static": (_int, [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_pad_plan": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_gather": (_int, [_vp, _i64, _i64, _vp, _vp, _i64, _int, _int, _vp, _vp, _vp]),
     "b200q_grouped_gemm_mxfp8": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _i64, _int, _i64, _i64, _vp, _i64, _vp]),

@@ -270,6 +270,14 @@ moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t
   }
 }
 
+// Scratch of b200q_moe_permute_plan_static: the per-CTA expert histograms of the plan kernels
+// ([CTAs][E] int32).  It lives in the library image, so every GPU that loads the library holds
+// these 1 MiB until the process exits.
+constexpr int64_t kStaticPlanInts = 262144;
+static __device__ __align__(256) int32_t g_static_plan_scratch[kStaticPlanInts];
+constexpr int kMaxDevices = 64;
+static int32_t* g_static_plan_ptr[kMaxDevices] = {};   // device address of the array, per device
+
 inline int row_grid(int64_t items) {
   int64_t want = (items + 7) / 8, cap = (int64_t)kNumSMs * 8;
   return (int)(want < 1 ? 1 : (want < cap ? want : cap));
@@ -390,6 +398,52 @@ int b200q_moe_unpermute(const void* y, int64_t ldy, const void* w, const int32_t
   if (rc) return rc;
   moe_unpermute_kernel<<<row_grid(T * ((D + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(
       (const uint16_t*)y, ldy, (const uint16_t*)w, row_of, T, k, D, (uint16_t*)out);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+// Same plan as b200q_moe_permute_plan, for callers that cannot hand over a workspace because
+// they cannot allocate device memory at this point.  The scratch is a fixed array inside the
+// library (g_static_plan_scratch) instead of a caller buffer; nothing is allocated or freed here.
+//
+// `g_static_plan_scratch` in host code is only a handle: the kernels need the array's address on
+// the current device, which cudaGetSymbolAddress returns.  The first call on each device looks
+// it up (with that device current) and remembers it, so make that first call outside any stream
+// capture.  Limits: ceil(n_pairs / 1024) * E <= 262144 entries, else B200Q_ERR_SHAPE.  The array
+// is shared by all calls on a device and keeps what the last call left in it: every entry a call
+// reads is first written by that call's own histogram kernel, so nothing has to be cleared, but
+// two calls that overlap on the GPU (different streams) race on it — serialize them.
+int b200q_moe_permute_plan_static(const int64_t* top_idx, int64_t n_pairs, int k, int E, int32_t* offs,
+                                  int32_t* padded_offs, int32_t* row_of, int32_t* src_of_row, int32_t* tile_expert,
+                                  int32_t* num_tiles, void* stream) {
+  if (top_idx == nullptr || offs == nullptr || padded_offs == nullptr || row_of == nullptr || src_of_row == nullptr ||
+      tile_expert == nullptr || num_tiles == nullptr || n_pairs <= 0 || k <= 0 || E <= 0)
+    return B200Q_ERR_INVALID_ARG;
+  if (E > kMaxExperts || n_pairs > INT32_MAX / 2) return B200Q_ERR_SHAPE;
+  const int64_t nblocks64 = (n_pairs + kPlanThreads - 1) / kPlanThreads;
+  if (nblocks64 * E > kStaticPlanInts) return B200Q_ERR_SHAPE;     // beyond the built-in scratch
+  int rc = require_sm100();
+  if (rc) return rc;
+  int dev = -1;
+  B200Q_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return B200Q_ERR_INVALID_ARG;
+  if (g_static_plan_ptr[dev] == nullptr) {
+    int32_t* ptr = nullptr;
+    B200Q_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_plan_scratch));
+    g_static_plan_ptr[dev] = ptr;
+  }
+  int32_t* block_counts = g_static_plan_ptr[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nblocks = (int)nblocks64;
+  const int64_t padded_rows = b200q_moe_padded_rows(n_pairs, E);
+  B200Q_CUDA(cudaMemsetAsync(src_of_row, 0xFF, (size_t)padded_rows * sizeof(int32_t), st));   // -1 = pad row
+  moe_hist_kernel<<<nblocks, kPlanThreads, 0, st>>>(top_idx, n_pairs, E, block_counts);
+  B200Q_CUDA(cudaGetLastError());
+  moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(block_counts, nblocks, E, offs, padded_offs, tile_expert, num_tiles,
+                                             (int)(padded_rows / 128));
+  B200Q_CUDA(cudaGetLastError());
+  moe_scatter_kernel<<<nblocks, kPlanThreads, 32 * E * sizeof(int), st>>>(top_idx, n_pairs, k, E, block_counts, padded_offs,
+                                                                           row_of, src_of_row);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
