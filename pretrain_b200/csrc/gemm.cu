@@ -16,10 +16,10 @@
 //             the stage's "empty" barrier; accumulators live in tensor memory;
 //   warps 2-5 epilogue: tcgen05.ld the fp32 accumulators (lane = row) 32 columns at a time,
 //             scale, round to bf16, stage a 32x32 block in 64-byte-swizzled shared memory and
-//             hand it to a TMA store (which also clips the ragged edges).  The accumulator is
-//             released as soon as its last column has been read, and with two accumulator
-//             stages (tile widths 128 and 192) the epilogue of tile i overlaps the main loop
-//             of tile i+1.
+//             hand it to a TMA store (which also clips the ragged edges).  Two accumulators in
+//             tensor memory let the epilogue of tile i overlap the main loop of tile i+1; at
+//             width 256 with scale factors they overlap by 32 / 64 columns, which the epilogue
+//             reads first.
 // No cluster launch and no multicast: the same binary runs under any number of processes.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -64,8 +64,16 @@ struct Cfg {
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SFA_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS;
   static constexpr int SFB_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS * NB_ATOMS;
-  static constexpr int ACC_STAGES = (2 * BN + SFA_COLS + SFB_COLS <= 512) ? 2 : 1;
-  static constexpr int SFA_COL0 = ACC_STAGES * BN;
+  // Two accumulators always.  When two whole ones and the scale factors do not fit in the 512
+  // columns (width 256, block-scaled kinds) the second accumulator starts OVL columns early, so
+  // the two share OVL columns: the epilogue reads that shared strip of a tile first and only
+  // then lets the next tile's MMA (which overwrites it) start; the rest of the tile drains while
+  // the next main loop runs.  OVL = scale-factor columns rounded up to an epilogue block.
+  static constexpr int SF_COLS = SFA_COLS + SFB_COLS;
+  static constexpr bool OVERLAP = 2 * BN + SF_COLS > 512;
+  static constexpr int OVL = OVERLAP ? ((2 * BN + SF_COLS - 512 + EPI_COLS - 1) / EPI_COLS) * EPI_COLS : 0;
+  static constexpr int ACC1_COL0 = BN - OVL;
+  static constexpr int SFA_COL0 = 2 * BN - OVL;
   static constexpr int SFB_COL0 = SFA_COL0 + SFA_COLS;
   static constexpr int TMEM_COLS = 512;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;                     // 1024-aligned
@@ -206,16 +214,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (ptx::elect_one()) {
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
+      uint32_t tile_iter = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
         int m_blk, n_blk;
         tile_coords(t, num_m, p.num_n, m_blk, n_blk);
         const int expert = p.tile_expert ? __ldg(p.tile_expert + m_blk) : 0;
         const int64_t brow0 = (int64_t)expert * p.N + (int64_t)n_blk * BN;
         const uint32_t sfb_off = (uint32_t)(brow0 & 127) >> 5;   // B tile starts this many 32-row columns into its first SF group
-        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1) || *abort_flag) { ok = false; break; }
+        // Plain double buffering: wait until this accumulator's previous tile has been read.
+        // Overlapped: wait until the PREVIOUS tile's epilogue (other accumulator) has read the
+        // shared strip; every epilogue warp gets there only after finishing the tile before, which
+        // used this accumulator.
+        if (C::OVERLAP) {
+          if (tile_iter > 0 && (!ptx::mbar_wait(tempty_bar(acc ^ 1), ((tile_iter - 1) >> 1) & 1) || *abort_flag)) { ok = false; break; }
+        } else {
+          if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1) || *abort_flag) { ok = false; break; }
+        }
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (acc ? C::ACC1_COL0 : 0);
         for (int k = 0; k < p.num_k; ++k) {
           if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
           ptx::tc_fence_after();
@@ -251,7 +268,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         if (!ok) break;
         ptx::tc_commit(tfull_bar(acc));       // accumulator complete
-        if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok) { *abort_flag = 1; atomicExch(&g_device_status, 2); }
     }
@@ -276,7 +293,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int64_t col0 = (int64_t)n_blk * BN;
       float row_scale = alpha;
       if (KIND == KIND_F8) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
       // One 32-column block: scale, round, stage in swizzled shared memory, TMA store.
       auto emit = [&](int c, const uint32_t (&r)[32]) {
@@ -309,26 +326,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         buf = (buf + 1) % C::EPI_BUFS;
       };
 
+      // Block order: natural, except that an overlapped accumulator 0 is read from its last
+      // block down, because its LAST columns are the strip shared with accumulator 1 (whose
+      // shared strip is its first columns).  The accumulator is released for the MMA after the
+      // strip has been read (overlapped) or after the last block has been read (otherwise).
+      const bool rev = C::OVERLAP && acc == 0;
+      constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;
       uint32_t ra[32], rb[32];
-      ptx::tmem_ld32(taddr, ra);
+      ptx::tmem_ld32(taddr + (rev ? NBLK - 1 : 0) * EPI_COLS, ra);
 #pragma unroll
-      for (int c = 0; c < NBLK; ++c) {
+      for (int i = 0; i < NBLK; ++i) {
+        const int c = rev ? NBLK - 1 - i : i;
         ptx::tmem_ld_wait();
-        if (c + 1 < NBLK) {
-          if (c & 1) ptx::tmem_ld32(taddr + (c + 1) * EPI_COLS, ra);
-          else ptx::tmem_ld32(taddr + (c + 1) * EPI_COLS, rb);
-        } else {
-          // every column has been read: hand the accumulator back before the last block is stored
+        if (i == RELEASE_AFTER) {
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
         }
+        if (i + 1 < NBLK) {
+          const int cn = rev ? c - 1 : c + 1;
+          if (i & 1) ptx::tmem_ld32(taddr + cn * EPI_COLS, ra);
+          else ptx::tmem_ld32(taddr + cn * EPI_COLS, rb);
+        }
         if (col0 + c * EPI_COLS < p.N && row0 < p.M) {      // warp-uniform
-          if (c & 1) emit(c, rb);
+          if (i & 1) emit(c, rb);
           else emit(c, ra);
         }
       }
-      if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (lane == 0) ptx::bulk_wait<0>();           // all stores of this warp have landed
     if (!ok && lane == 0) { *abort_flag = 1; atomicExch(&g_device_status, 3); }
@@ -421,7 +446,9 @@ int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
     const int64_t waves = (tiles + kNumSMs - 1) / kNumSMs;
     const double kstep = std::max(2.0 * bn, (128.0 + bn) * 128.0 / 100.0);
     const double mainloop = num_k * kstep + 600.0, epi = 300.0 + (bn / 32) * 220.0;
-    const double per_tile = bn == 256 && KIND != KIND_F8 ? mainloop + epi : std::max(mainloop, epi);
+    // the epilogue hides behind the next main loop; at width 256 with scale factors the MMA
+    // still waits for the first epilogue block(s) of the previous tile
+    const double per_tile = std::max(mainloop + (bn == 256 && KIND != KIND_F8 ? 500.0 : 0.0), epi);
     const double cost = waves * per_tile;
     if (cost < best * 0.995) { best = cost; best_bn = bn; }
   }

@@ -55,6 +55,12 @@ def test_division_random_fp4(hc):
     assert out[0] == 0 and out[1] == 0
 
 
+def test_nvfp4_block_scale_with_hoisted_reciprocals_is_exact(hc):
+    out = (ctypes.c_int64 * 3)()
+    hc.hc_nv_block_scale_exhaustive(13, out)   # every bf16 block amax x every 13th bf16 tensor amax >= it
+    assert out[1] > 3e7 and out[0] == 0
+
+
 def test_e4m3_decode_table(hc):
     tab = (ctypes.c_float * 256)()
     hc.hc_e4m3_decode_table(tab)
