@@ -40,7 +40,10 @@ WORKLOADS = {
     "mxfp8_square_4096": ("mxfp8", 4096, 4096, 4096),
     "mxfp8_gpt2_mlp_up": ("mxfp8", 8192, 3072, 768),
     "fp8_rowwise_linear_16384x2048x2048": ("fp8", 16384, 2048, 2048),
+    # MoE block: (kind, tokens, hidden, intermediate); 64 experts, top-4
+    "moe_mxfp8_16384x768_e64_top4": ("moe", 16384, 768, 384),
 }
+MOE_EXPERTS, MOE_TOPK = 64, 4
 NOMINAL_TFLOPS = {"mxfp8": 4500.0, "fp8": 4500.0, "nvfp4": 9000.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the ncu captures summarised
 # under profiles/ (null until captured for that workload)
@@ -185,6 +188,130 @@ def make_step(kind, a, b, out):
     return step, launches
 
 
+def cpu_moe_sample(t, d, inter, ts=1024):
+    """The oracle's MoE path on the host cores for a sample of tokens: permute, per-expert loop
+    with MXFP8 fake-quantized operands (both GEMMs, SwiGLU between), as grouped_mlp does."""
+    from oracle import restate as R
+    e, k = MOE_EXPERTS, MOE_TOPK
+    x, logits, w_gu, w_d = R.inputs_moe(ts, d, e, k, inter)
+    top_i, _ = R.router_topk(logits, k)
+    fq = lambda v: R.dequantize_mxfp8(*R.quantize_mxfp8(v)).to(v.dtype)
+    tc = time.perf_counter()
+    order, tok, counts, offs = R.moe_permute(top_i, e)
+    R.grouped_mlp_ref(x[tok], w_gu, w_d, offs, fake_quant=fq)
+    dt = time.perf_counter() - tc
+    return {"value": 2.0 * ts * k * (2 * inter * d + d * inter) / dt / 1e12, "unit": "TFLOPS", "cores": torch.get_num_threads(),
+            "kind": "port", "sample": f"{ts} of {t} tokens through the oracle's per-expert fake-quant loop, 1 pass",
+            "ms_per_step": dt * 1e3}
+
+
+def run_moe(args, t, d, inter, rank, world, local):
+    """MoE block workload: one step = permute plan, gather fused with MXFP8, quantize both expert
+    weight stacks, grouped GEMM, SwiGLU + MXFP8, grouped GEMM, weighted unpermute (what
+    SparseMoEBlock.forward does after the router).  Throughput counts the two grouped GEMMs'
+    2*R*N*K FLOP (pad rows not counted)."""
+    from oracle import restate as R
+    from pretrain_b200 import build, ops
+    from pretrain_b200.layers.mlp import SparseMoEBlock
+    if rank == 0:
+        build.build()
+    e, k = MOE_EXPERTS, MOE_TOPK
+    x, logits, w_gu, w_d = R.inputs_moe(t, d, e, k, inter, seed=rank)
+    top_i, top_w = R.router_topk(logits, k)
+    x, top_i, top_w, w_gu, w_d = (v.cuda() for v in (x, top_i, top_w, w_gu, w_d))
+    n_pairs = t * k
+    flops = 2.0 * n_pairs * (2 * inter * d + d * inter)
+    ev = lambda marks: None if marks is None else _mark(marks)
+
+    def step(marks=None):
+        ev(marks)
+        plan = ops.moe_permute_plan(top_i, e)
+        a, sfa = ops.moe_gather(x, plan, True)
+        ev(marks)
+        wq1, wsf1 = ops.quantize_mxfp8(w_gu.view(e * 2 * inter, d), 1)
+        wq2, wsf2 = ops.quantize_mxfp8(w_d.view(e * d, inter), 1)
+        ev(marks)
+        h = ops.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, 2 * inter)
+        ev(marks)
+        hq, hsf = ops.swiglu(h, True)
+        ev(marks)
+        y = ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, d)
+        ev(marks)
+        out = ops.moe_unpermute(y, top_w, plan.row_of, t)
+        ev(marks)
+        return out
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    marks = []
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        torch.cuda.synchronize()
+        t0.record()
+        for _ in range(args.steps):
+            step(marks)
+        t1.record()
+        torch.cuda.synchronize()
+    ops.device_status()
+    ms_step = t0.elapsed_time(t1) / args.steps
+    seg = [marks[i:i + 7] for i in range(0, len(marks), 7)]
+    avg = lambda i: sum(sg[i].elapsed_time(sg[i + 1]) for sg in seg) / len(seg)
+    permute_ms, wquant_ms, gemm1_ms, swiglu_ms, gemm2_ms, unperm_ms = (avg(i) for i in range(6))
+
+    blk = SparseMoEBlock(d, intermediate_size=inter, n_routed_experts=e, n_routed_experts_per_token=k, router_score_fn="softmax").cuda()
+    with torch.no_grad():
+        blk.expert_gate_up.copy_(w_gu)
+        blk.expert_down.copy_(w_d)
+        torch.nn.init.normal_(blk.router.gate.weight, std=0.02)
+    hx = x.cpu().view(16, t // 16, d).pin_memory()
+    hout = torch.empty_like(hx).pin_memory()
+
+    def e2e_step():
+        with torch.no_grad():
+            o, _ = blk(hx.to("cuda", non_blocking=True))
+        hout.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    n_e2e = max(3, min(args.steps, 20))
+    t0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / n_e2e
+
+    peaks = measured_peaks()
+    peak = peaks["bf16_tflops_sustained"] * 2.0
+    gemm_ms = gemm1_ms + gemm2_ms
+    achieved = flops / (gemm_ms * 1e-3) / 1e12
+    hbm = lambda nbytes, ms: {"achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                              "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "kernels_ms": ms, "bytes": nbytes}
+    line = {"metric": "MoE block grouped-GEMM TFLOPS/GPU (permute + MXFP8 grouped GEMMs + SwiGLU + unpermute)",
+            "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "mxfp8", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens_per_gpu": t, "hidden": d, "intermediate": inter, "experts": e, "top_k": k,
+                       "l2": "weights (108 MB bf16) + permuted activations exceed L2; no flush needed"},
+            "clocks": clk.summary(),
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2},
+            "gpu_launches": 10 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<mxfp8> (grouped, 2 launches)", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"2 x bf16_tflops_sustained, {peaks['source']}",
+                         "frac_of_nominal": achieved / 4500.0, "nominal_peak": 4500.0, "traffic": None, "kernel_ms": gemm_ms},
+            "permute": dict(bound="hbm", **hbm(n_pairs * d * 3.03125, permute_ms), note="plan kernels + gather fused with MXFP8"),
+            "weight_quantize": dict(bound="hbm", **hbm((w_gu.numel() + w_d.numel()) * 3.03125, wquant_ms)),
+            "swiglu_quantize": dict(bound="hbm", **hbm(n_pairs * (2 * inter * 2 + inter * 1.03125), swiglu_ms)),
+            "unpermute": dict(bound="hbm", **hbm(n_pairs * d * 2 + t * d * 2, unperm_ms))}
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_moe_sample(t, d, inter)
+        print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -206,7 +333,7 @@ def main():
         if rank != 0:
             return
         steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
-        cb = run_cpu(kind, m, n, k, steps, warm)
+        cb = cpu_moe_sample(m, n, k) if kind == "moe" else run_cpu(kind, m, n, k, steps, warm)
         print(json.dumps({"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOPS", "n_gpus": args.gpus,
                           "steps": steps, "warmup": warm, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
                           "scaling": "weak", "vs_baseline": None, "dtype": "bf16 matmul of fake-quantized operands (CPU)",
@@ -218,6 +345,8 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path for the product arm")
     torch.cuda.set_device(local)
+    if kind == "moe":
+        return run_moe(args, m, n, k, rank, world, local)
     dist = None
     if world > 1:
         import torch.distributed as dist
