@@ -47,7 +47,7 @@ MOE_EXPERTS, MOE_TOPK = 64, 4
 NOMINAL_TFLOPS = {"mxfp8": 4500.0, "fp8": 4500.0, "nvfp4": 9000.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the ncu captures summarised
 # under profiles/ (null until captured for that workload)
-GEMM_DRAM_TRAFFIC = {}
+GEMM_DRAM_TRAFFIC = {"mxfp8_square_8192": 462.7e6, "nvfp4_square_8192": 258.3e6}   # one-CTA kernel captures
 
 
 def measured_peaks():
@@ -452,7 +452,7 @@ def main():
     ratio = {"mxfp8": 2.0, "fp8": 2.0, "nvfp4": 4.0}[kind]
     peak = peaks["bf16_tflops_sustained"] * ratio
     achieved = flops / (gemm_ms * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": f"gemm_kernel<{kind}>", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+    roofline = {"bound": "tensor", "kernel": f"gemm_pair_kernel<{kind}> / gemm_kernel<{kind}> (chosen by shape)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "peak_source": f"{ratio:g} x bf16_tflops_sustained, {peaks['source']}",
                 "frac_of_nominal": achieved / NOMINAL_TFLOPS[kind], "nominal_peak": NOMINAL_TFLOPS[kind],
                 "traffic": GEMM_DRAM_TRAFFIC.get(args.workload), "kernel_ms": gemm_ms}

@@ -39,6 +39,7 @@ SIGNATURES = {
 }
 DEBUG_SIGNATURES = {
     "b200q_debug_set_gemm_bn": (_int, [_int]),
+    "b200q_debug_set_gemm_pair": (_int, [_int]),
 }
 
 _lib = None

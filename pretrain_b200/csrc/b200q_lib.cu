@@ -2,4 +2,5 @@
 // inline helpers, so the sources are compiled together instead of with relocatable device code.
 #include "quantize.cu"
 #include "gemm.cu"
+#include "gemm_2cta.cu"
 #include "moe.cu"

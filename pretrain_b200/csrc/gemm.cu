@@ -455,8 +455,14 @@ int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
   return best_bn;
 }
 
+// CTA-pair form of the dense GEMMs (gemm_2cta.cu, same translation unit)
+bool pair_eligible(int64_t M, int64_t N, int64_t row_bytes, bool grouped);
+template <int KIND>
+int launch_pair(const void* A, const void* B, void* D, int64_t ldd, const GemmParams& gp, cudaStream_t st);
+
 template <int KIND>
 int dispatch(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, const GemmParams& p, cudaStream_t st) {
+  if (pair_eligible(p.M, p.N, KIND == KIND_NV ? p.K / 2 : p.K, p.tile_expert != nullptr)) return launch_pair<KIND>(A, B, D, ldd, p, st);
   const int bn = g_force_bn ? g_force_bn : choose_bn<KIND>(p.M, p.N, KIND == KIND_NV ? p.K / 2 : p.K);
   switch (bn) {
     case 128: return launch<KIND, 128>(A, B, D, ldd, b_rows, p, st);

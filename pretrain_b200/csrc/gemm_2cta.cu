@@ -1,0 +1,352 @@
+// The dense GEMMs of gemm.cu on CTA pairs (tcgen05 cta_group::2): two CTAs of a cluster share one
+// 256-row x 256-column output tile.  Each CTA stages only its own 128 rows of A and its own 128
+// rows of B per K step (32 KB instead of the 48 KB a lone CTA needs for 128 x 256), which cuts the
+// L2 -> shared-memory traffic and the shared-memory reads per FLOP by a third and leaves room for
+// a deeper ring.  The leader CTA (cluster rank 0) issues the MMAs for the pair; each CTA keeps its
+// 128 accumulator rows in its own tensor memory and runs its own epilogue.
+//
+// Differences from the one-CTA kernel, all of them about who signals whom:
+//   * every TMA load (operands and scale-factor atoms, the latter through a 2-D view of the
+//     scale buffers, 256 bytes per row) counts its bytes on the LEADER's "full" barrier, on which
+//     both producers also arrive;
+//   * the leader's tcgen05.commit arrives on the "empty" / "accumulator full" barriers of both CTAs;
+//   * the peer's epilogue warps arrive remotely on the leader's "accumulator free" barrier;
+//   * the pair synchronizes as a cluster after barrier set-up and before tear-down.
+// No TMA multicast is used.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200q {
+namespace {
+
+namespace pair {
+
+constexpr int PBN = 256;                          // columns of the pair's tile
+constexpr int HALF_N = PBN / 2;                   // B rows each CTA stages
+
+template <int KIND>
+struct PCfg {
+  static constexpr int K_ATOMS = KIND == KIND_NV ? 4 : 1;
+  static constexpr int A_BYTES = BM * BKB, B_BYTES = HALF_N * BKB;
+  static constexpr int SFA_BYTES = KIND == KIND_F8 ? 0 : K_ATOMS * 512;
+  static constexpr int SFB_BYTES = KIND == KIND_F8 ? 0 : 2 * K_ATOMS * 512;       // both halves of B's columns
+  static constexpr int TX_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;      // per CTA and K step
+  static constexpr int STAGE_BYTES = ((TX_BYTES + 1023) / 1024) * 1024;
+  static constexpr int EPI_BYTES = 2 * kEpiBytes1;
+  static constexpr int STAGES_RAW = (kSmemBudget - 2048 - EPI_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SFA_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS;
+  static constexpr int SFB_COLS = KIND == KIND_F8 ? 0 : 8 * K_ATOMS;
+  static constexpr int SF_COLS = SFA_COLS + SFB_COLS;
+  static constexpr bool OVERLAP = SF_COLS > 0;     // two 256-column accumulators + scale columns > 512
+  static constexpr int OVL = OVERLAP ? ((SF_COLS + EPI_COLS - 1) / EPI_COLS) * EPI_COLS : 0;
+  static constexpr int ACC1_COL0 = PBN - OVL;
+  static constexpr int SFA_COL0 = 2 * PBN - OVL;
+  static constexpr int SFB_COL0 = SFA_COL0 + SFA_COLS;
+  static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = EPI_OFF + EPI_BYTES;
+  static constexpr int SMEM_BYTES = BAR_OFF + 256 + 1024;
+  static_assert(SFB_COL0 + SFB_COLS <= 512, "tensor memory overflow");
+  static_assert(SMEM_BYTES <= kSmemBudget, "shared memory overflow");
+};
+
+struct PairParams {
+  const float* scale_a;
+  const float* scale_b;
+  int a_scalar, b_scalar, a_fmt, b_fmt;
+  int64_t M, N;
+  int num_mp, num_n, num_k;      // pair tiles (256 rows), column tiles, K steps
+  int sf_kt;                     // 512-byte scale atoms per 128-row group along K
+};
+
+__device__ __forceinline__ void pair_tile_coords(int t, int num_mp, int num_n, int& mp, int& n) {
+  constexpr int GM = 8;          // 8 pair tiles = 2048 rows per raster group
+  const int per_group = GM * num_n;
+  const int g = t / per_group, r = t - g * per_group;
+  const int first = g * GM;
+  const int gm = num_mp - first < GM ? num_mp - first : GM;
+  mp = first + r % gm;
+  n = r / gm;
+}
+
+}  // namespace pair
+
+template <int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                 const __grid_constant__ CUtensorMap tmap_d, const pair::PairParams p) {
+  using C = pair::PCfg<KIND>;
+  constexpr int BN = pair::PBN;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + C::BAR_OFF;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };                       // used in the leader only
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };        // one per CTA
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + a); };    // one per CTA
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + 2 + a); };   // used in the leader only
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::BAR_OFF + 8 * (2 * C::STAGES + 4));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = ptx::cluster_ctarank();       // 0 = leader
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int total_tiles = p.num_mp * p.num_n;
+
+  if (threadIdx.x == 0) {
+    // full: one arrival (with its byte count) per producer of the pair; empty / accumulator-full: the
+    // leader's commit; accumulator-free: 4 epilogue warps of each CTA
+    for (int s = 0; s < C::STAGES; ++s) { ptx::mbar_init(full_bar(s), 2); ptx::mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 8); }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+    ptx::prefetch_tensormap(&tmap_d);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();            // both CTAs' barriers exist before anyone signals the peer
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) ---------------------------------
+    if (ptx::elect_one()) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
+        int mp, n_blk;
+        pair::pair_tile_coords(t, p.num_mp, p.num_n, mp, n_blk);
+        const int row0 = mp * 256 + (int)cta * BM;                   // this CTA's rows of A
+        const int brow0 = n_blk * BN + (int)cta * pair::HALF_N;      // this CTA's rows of B
+        for (int k = 0; k < p.num_k; ++k) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1) || *abort_flag) { ok = false; break; }
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          const uint32_t fb = full_bar(stage) & ptx::kLeaderMask;    // the leader's barrier, from either CTA
+          ptx::mbar_expect_tx_cluster(fb, C::TX_BYTES);
+          ptx::tma_load_2d_pair(sa, &tmap_a, k * BKB, row0, fb);
+          ptx::tma_load_2d_pair(sb, &tmap_b, k * BKB, brow0, fb);
+          if (KIND != KIND_F8) {
+            // scale buffers viewed as rows of 256 bytes: a 512-byte atom is 2 rows, the K_ATOMS atoms of
+            // one K step and row group are contiguous
+            const uint32_t ssfa = sb + C::B_BYTES, ssfb = ssfa + C::SFA_BYTES;
+            const int sf_kt = p.sf_kt;
+            ptx::tma_load_2d_pair(ssfa, &tmap_sfa, 0, 2 * ((row0 >> 7) * sf_kt + k * C::K_ATOMS), fb);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              ptx::tma_load_2d_pair(ssfb + j * C::K_ATOMS * 512, &tmap_sfb, 0, 2 * ((n_blk * 2 + j) * sf_kt + k * C::K_ATOMS), fb);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(&g_device_status, 11); }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader CTA only) -----------------------------
+    if (cta == 0 && ptx::elect_one()) {
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++tile_iter) {
+        if (C::OVERLAP) {
+          if (tile_iter > 0 && (!ptx::mbar_wait(tempty_bar(acc ^ 1), ((tile_iter - 1) >> 1) & 1) || *abort_flag)) { ok = false; break; }
+        } else {
+          if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1) || *abort_flag) { ok = false; break; }
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (acc ? C::ACC1_COL0 : 0);
+        for (int k = 0; k < p.num_k; ++k) {
+          if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          if (KIND != KIND_F8) {
+            const uint32_t ssfa = sb + C::B_BYTES, ssfb = ssfa + C::SFA_BYTES;
+#pragma unroll
+            for (int a = 0; a < C::K_ATOMS; ++a) {
+              ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + C::SFA_COL0 + 4 * a, ptx::smem_desc_sf(ssfa + a * 512));
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+                ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + C::SFB_COL0 + 4 * (a * 2 + j),
+                                                 ptx::smem_desc_sf(ssfb + (j * C::K_ATOMS + a) * 512));
+            }
+          }
+          const uint64_t da = ptx::smem_desc_k_sw128(sa), db = ptx::smem_desc_k_sw128(sb);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t accum = (k | kk) != 0;
+            const uint64_t adv = (uint64_t)(kk * 32 >> 4);
+            if (KIND == KIND_F8) {
+              ptx::mma_f8_pair(d_tmem, da + adv, db + adv, ptx::idesc_f8(p.a_fmt, p.b_fmt, 256, BN), accum);
+            } else if (KIND == KIND_MX) {
+              ptx::mma_mxf8_pair(d_tmem, da + adv, db + adv, ptx::idesc_block_scaled(p.a_fmt, p.b_fmt, 1, 256, BN, kk), accum,
+                                 tmem_base + C::SFA_COL0, tmem_base + C::SFB_COL0);
+            } else {
+              ptx::mma_nvf4_pair(d_tmem, da + adv, db + adv, ptx::idesc_block_scaled(1, 1, 0, 256, BN, 0), accum,
+                                 tmem_base + C::SFA_COL0 + 4 * kk, tmem_base + C::SFB_COL0 + 8 * kk);
+            }
+          }
+          ptx::tc_commit_pair(empty_bar(stage));
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        ptx::tc_commit_pair(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(&g_device_status, 12); }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue (both CTAs, own 128 rows) ------------------------
+    const int q = warp & 3;
+    const uint32_t epi_s = smem_base + C::EPI_OFF + q * 2 * EPI_BLOCK_BYTES;
+    uint8_t* epi_g = smem_gen + C::EPI_OFF + q * 2 * EPI_BLOCK_BYTES;
+    int buf = 0;
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    float alpha = 1.f;
+    if (KIND == KIND_NV) alpha = __ldg(p.scale_a) * __ldg(p.scale_b);
+    constexpr int NBLK = BN / EPI_COLS;
+    for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
+      int mp, n_blk;
+      pair::pair_tile_coords(t, p.num_mp, p.num_n, mp, n_blk);
+      if (!ptx::mbar_wait(tfull_bar(acc), acc_phase) || *abort_flag) { ok = false; break; }
+      ptx::tc_fence_after();
+      const int64_t row0 = (int64_t)mp * 256 + cta * BM + q * 32, row = row0 + lane;
+      const int64_t col0 = (int64_t)n_blk * BN;
+      float row_scale = alpha;
+      if (KIND == KIND_F8) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
+
+      auto emit = [&](int c, const uint32_t (&r)[32]) {
+        const int64_t colg = col0 + c * EPI_COLS;
+        float sbv = 1.f;
+        if (KIND == KIND_F8) sbv = p.b_scalar ? __ldg(p.scale_b) : (colg + lane < p.N ? __ldg(p.scale_b + colg + lane) : 0.f);
+        uint32_t o[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float lo = u2f(r[2 * i]) * row_scale, hi = u2f(r[2 * i + 1]) * row_scale;
+          if (KIND == KIND_F8) {
+            lo *= __shfl_sync(0xFFFFFFFFu, sbv, 2 * i);
+            hi *= __shfl_sync(0xFFFFFFFFu, sbv, 2 * i + 1);
+          }
+          o[i] = pack_bf16(lo, hi);
+        }
+        if (lane == 0) ptx::bulk_wait_read<1>();
+        __syncwarp();
+        uint8_t* dst = epi_g + buf * EPI_BLOCK_BYTES + lane * 64;
+        const int sw = (lane >> 1) & 3;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(dst + ((j ^ sw) << 4)) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_2d(&tmap_d, (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
+          ptx::bulk_commit();
+        }
+        buf ^= 1;
+      };
+
+      const bool rev = C::OVERLAP && acc == 0;
+      constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;
+      uint32_t ra[32], rb[32];
+      ptx::tmem_ld32(taddr + (rev ? NBLK - 1 : 0) * EPI_COLS, ra);
+#pragma unroll
+      for (int i = 0; i < NBLK; ++i) {
+        const int c = rev ? NBLK - 1 - i : i;
+        ptx::tmem_ld_wait();
+        if (i == RELEASE_AFTER) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(tempty_bar(acc) & ptx::kLeaderMask);   // the leader's barrier
+        }
+        if (i + 1 < NBLK) {
+          const int cn = rev ? c - 1 : c + 1;
+          if (i & 1) ptx::tmem_ld32(taddr + cn * EPI_COLS, ra);
+          else ptx::tmem_ld32(taddr + cn * EPI_COLS, rb);
+        }
+        if (col0 + c * EPI_COLS < p.N && row0 < p.M) {
+          if (i & 1) emit(c, rb);
+          else emit(c, ra);
+        }
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (lane == 0) ptx::bulk_wait<0>();
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(&g_device_status, 13); }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();            // neither CTA leaves while the other may still touch its memory
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+int g_pair_mode = 0;   // test hook: 0 = choose by shape, 1 = always (when eligible), -1 = never
+
+// Pair tiles pay off when there are enough 256 x 256 tiles to occupy the 74 CTA pairs for a few waves.
+bool pair_eligible(int64_t M, int64_t N, int64_t row_bytes, bool grouped) {
+  if (grouped || g_pair_mode < 0) return false;
+  if (g_pair_mode > 0) return true;
+  const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  return tiles >= kNumSMs / 2 && row_bytes >= 8 * BKB;
+}
+
+template <int KIND>
+int launch_pair(const void* A, const void* B, void* D, int64_t ldd, const GemmParams& gp, cudaStream_t st) {
+  using C = pair::PCfg<KIND>;
+  const int64_t row_bytes = KIND == KIND_NV ? gp.K / 2 : gp.K;
+  CUtensorMap ma, mb, msa, msb, md;
+  int rc;
+  if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, gp.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, gp.N, row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = encode_2d(&md, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, gp.N, gp.M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+  int sf_kt = 0;
+  if (KIND != KIND_F8) {
+    // scale buffers as rows of 256 bytes (two rows per 512-byte atom); box = the atoms of one K step
+    const int64_t nblk = KIND == KIND_MX ? gp.K / 32 : gp.K / 16;
+    sf_kt = (int)((nblk + 3) / 4);
+    const uint64_t rows_a = (uint64_t)((gp.M + 127) / 128) * sf_kt * 2, rows_b = (uint64_t)((gp.N + 127) / 128) * sf_kt * 2;
+    if ((rc = encode_2d(&msa, CU_TENSOR_MAP_DATA_TYPE_UINT8, gp.sfa, 256, rows_a, 256, 256, 2 * C::K_ATOMS, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    if ((rc = encode_2d(&msb, CU_TENSOR_MAP_DATA_TYPE_UINT8, gp.sfb, 256, rows_b, 256, 256, 2 * C::K_ATOMS, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+  } else {
+    msa = ma; msb = mb;   // unused
+  }
+  pair::PairParams p = {};
+  p.scale_a = gp.scale_a; p.scale_b = gp.scale_b; p.a_scalar = gp.a_scalar; p.b_scalar = gp.b_scalar;
+  p.a_fmt = gp.a_fmt; p.b_fmt = gp.b_fmt; p.M = gp.M; p.N = gp.N;
+  p.num_mp = (int)((gp.M + 255) / 256);
+  p.num_n = (int)((gp.N + pair::PBN - 1) / pair::PBN);
+  p.num_k = (int)((row_bytes + BKB - 1) / BKB);
+  p.sf_kt = sf_kt;
+  B200Q_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  const int tiles = p.num_mp * p.num_n, pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
+  gemm_pair_kernel<KIND><<<2 * pairs, kGemmThreads, C::SMEM_BYTES, st>>>(ma, mb, msa, msb, md, p);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" {
+// Test hook: 1 = run eligible dense GEMMs on CTA pairs, -1 = never, 0 = choose by shape.
+int b200q_debug_set_gemm_pair(int mode) {
+  b200q::g_pair_mode = mode > 0 ? 1 : (mode < 0 ? -1 : 0);
+  return B200Q_OK;
+}
+}

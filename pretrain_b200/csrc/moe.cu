@@ -39,10 +39,15 @@ moe_scan_kernel(int32_t* __restrict__ block_counts, int nblocks, int E, int32_t*
   const int e = threadIdx.x;
   if (e < E) {
     int run = 0;
-    for (int b = 0; b < nblocks; ++b) {
-      const int c = block_counts[(int64_t)b * E + e];
-      block_counts[(int64_t)b * E + e] = run;
-      run += c;
+    for (int b0 = 0; b0 < nblocks; b0 += 16) {       // 16 independent loads in flight, then the prefix
+      int c[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) c[i] = b0 + i < nblocks ? block_counts[(int64_t)(b0 + i) * E + e] : 0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if (b0 + i < nblocks) block_counts[(int64_t)(b0 + i) * E + e] = run;
+        run += c[i];
+      }
     }
     count[e] = run;
   }
@@ -170,30 +175,34 @@ moe_gather_kernel(const uint16_t* __restrict__ x, int64_t D, int64_t ld, const i
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int64_t live_rows = (int64_t)(*num_tiles) << 7;
   if (live_rows > padded_rows) live_rows = padded_rows;
-  const int64_t nblk = D >> 5;
+  const int ncols = (int)D;
+  const int64_t kt = ((D >> 5) + 3) >> 2;
   for (int64_t r = (int64_t)blockIdx.x * 8 + warp; r < live_rows; r += (int64_t)gridDim.x * 8) {
     const int src = src_of_row[r];
     const uint16_t* xr = x + (int64_t)(src < 0 ? 0 : src) * ld;
-    for (int64_t c0 = 0; c0 < D; c0 += 1024) {
+    uint8_t* orow = out + r * D * (QUANT ? 1 : 2);
+    uint8_t* sfr = QUANT ? sf + (r >> 7) * kt * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 : nullptr;
+    for (int c0 = 0; c0 < ncols; c0 += 1024) {
       uint4 v[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int64_t c = c0 + u * 256 + lane * 8;
-        v[u] = (src >= 0 && c < D) ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
+        const int c = c0 + u * 256 + lane * 8;
+        v[u] = (src >= 0 && c < ncols) ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int64_t c = c0 + u * 256 + lane * 8;
-        if (c0 + u * 256 >= D) break;      // warp-uniform
+        const int c = c0 + u * 256 + lane * 8;
+        if (c0 + u * 256 >= ncols) break;      // warp-uniform
         if (QUANT) {
           int e;
           const uint2 o = mx_quant8(v[u], fmt, e);
-          if (c < D) {
-            *reinterpret_cast<uint2*>(out + r * D + c) = o;
-            if ((lane & 3) == 0) sf[sf_offset(r, c >> 5, nblk, 1)] = (uint8_t)(e + 127);
+          if (c < ncols) {
+            *reinterpret_cast<uint2*>(orow + c) = o;
+            const int kb = c >> 5;
+            if ((lane & 3) == 0) sfr[(kb >> 2) * 512 + (kb & 3)] = (uint8_t)(e + 127);
           }
-        } else if (c < D) {
-          *reinterpret_cast<uint4*>(out + (r * D + c) * 2) = v[u];
+        } else if (c < ncols) {
+          *reinterpret_cast<uint4*>(orow + c * 2) = v[u];
         }
       }
     }
@@ -209,14 +218,16 @@ __global__ void __launch_bounds__(256)
 swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t ld, int fmt, uint8_t* __restrict__ out,
               uint8_t* __restrict__ sf) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t nblk = I >> 5;
+  const int64_t kt = ((I >> 5) + 3) >> 2;
   for (ItemWalker w((int64_t)blockIdx.x * 8 + warp, (int64_t)gridDim.x * 8, (int)((I + 255) >> 8)); w.row < rows; w.next()) {
-    const int64_t r = w.row, c = (int64_t)w.chunk * 256 + lane * 8;
-    const bool live = c < I;
+    const int64_t r = w.row;
+    const int c = w.chunk * 256 + lane * 8;
+    const bool live = c < (int)I;
+    const uint16_t* gr = g + r * ld + c;
     uint4 vg = make_uint4(0, 0, 0, 0), vu = vg;
     if (live) {
-      vg = ld_nc_v4(g + r * ld + c);
-      vu = ld_nc_v4(g + r * ld + I + c);
+      vg = ld_nc_v4(gr);
+      vu = ld_nc_v4(gr + I);
     }
     float a[8], b[8];
     unpack8f(vg, a);
@@ -224,8 +235,10 @@ swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t l
     uint32_t h[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float s0 = bf16_round(a[2 * i] / (1.f + expf(-a[2 * i])));
-      const float s1 = bf16_round(a[2 * i + 1] / (1.f + expf(-a[2 * i + 1])));
+      // silu(x) = x / (1 + e^-x) with the hardware exponential and reciprocal: within 2 fp32 ulp,
+      // far inside the bf16 rounding that follows
+      const float s0 = bf16_round(__fdividef(a[2 * i], 1.f + __expf(-a[2 * i])));
+      const float s1 = bf16_round(__fdividef(a[2 * i + 1], 1.f + __expf(-a[2 * i + 1])));
       __nv_bfloat162 p = __floats2bfloat162_rn(s0 * b[2 * i], s1 * b[2 * i + 1]);
       h[i] = *reinterpret_cast<uint32_t*>(&p);
     }
@@ -235,7 +248,8 @@ swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t l
       const uint2 o = mx_quant8(hv, fmt, e);
       if (live) {
         *reinterpret_cast<uint2*>(out + r * I + c) = o;
-        if ((lane & 3) == 0) sf[sf_offset(r, c >> 5, nblk, 1)] = (uint8_t)(e + 127);
+        const int kb = c >> 5;
+        if ((lane & 3) == 0) sf[(r >> 7) * kt * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (kb >> 2) * 512 + (kb & 3)] = (uint8_t)(e + 127);
       }
     } else if (live) {
       *reinterpret_cast<uint4*>(out + (r * I + c) * 2) = hv;

@@ -161,6 +161,33 @@ def test_every_tile_width(ops, bn, kind, n):
     _check(out, ref)
 
 
+@pytest.mark.parametrize("kind", ["fp8", "mxfp8", "nvfp4"])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 512, 1024), (300, 520, 256), (2048, 1024, 4096), (128, 256, 96)])
+def test_cta_pair_kernel(ops, kind, m, n, k):
+    """The dense GEMMs on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2), forced on for shapes
+    with ragged rows / columns / K as well."""
+    from pretrain_b200 import _lib
+    a, b = _rand(m, k, 11), _rand(n, k, 12)
+    _lib.load().b200q_debug_set_gemm_pair(1)
+    try:
+        if kind == "fp8":
+            ca, sa = ops.quantize_fp8(a, E4, 1); cb, sb = ops.quantize_fp8(b, E4, 1)
+            out = ops.gemm_fp8(ca, E4, cb, E4, sa, sb)
+            ref = G.matmul_fp32(G.deq_fp8(ca, E4) * sa[:, None], G.deq_fp8(cb, E4) * sb[:, None])
+        elif kind == "mxfp8":
+            ca, sfa = ops.quantize_mxfp8(a); cb, sfb = ops.quantize_mxfp8(b)
+            out = ops.gemm_mxfp8(ca, sfa, cb, sfb)
+            ref = G.matmul_fp32(G.deq_mxfp8(ca, sfa), G.deq_mxfp8(cb, sfb))
+        else:
+            pa, sfa, ta = ops.quantize_nvfp4(a); pb, sfb, tb = ops.quantize_nvfp4(b)
+            out = ops.gemm_nvfp4(pa, sfa, ta, pb, sfb, tb)
+            ref = G.matmul_fp32(G.deq_nvfp4(pa, sfa, ta), G.deq_nvfp4(pb, sfb, tb))
+        ops.device_status()
+    finally:
+        _lib.load().b200q_debug_set_gemm_pair(0)
+    _check(out, ref)
+
+
 def test_mxfp8_linear_config_against_cpu_oracle(ops):
     """GPT-2 MLP up-projection (X[8192,768] . W[3072,768]^T, seed 0): the full path against
     the CPU oracle's dequantize-then-matmul on a row sample."""

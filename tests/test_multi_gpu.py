@@ -1,0 +1,84 @@
+"""Two-rank NCCL runs of the multi-GPU forms (skipped with fewer than 2 GPUs): the M-sharded GEMM
+with output all-gather equals the single-GPU GEMM bit for bit (quantization is row-local), and
+the expert-parallel MoE block equals the single-GPU block on the concatenated tokens."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import restate as R
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, fn, world, port, args):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        fn(rank, world, *args)
+        torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(fn, world, *args):
+    mp.spawn(_entry, args=(fn, world, _free_port(), args), nprocs=world, join=True)
+
+
+def _sharded_gemm_rank(rank, world, fmt):
+    from pretrain_b200 import dist as D
+    from pretrain_b200.quant.linear import _gemm
+    m, k, n = 1024, 512, 768
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(m, k, generator=g).bfloat16().cuda()
+    w = (0.05 * torch.randn(n, k, generator=g)).bfloat16().cuda()
+    lo, hi = D.row_shard(m, world, rank)
+    full = D.sharded_gemm(a[lo:hi], w.t(), fmt, fmt, torch.bfloat16, m, rowwise=True)
+    ref = _gemm(a, w.t(), fmt, fmt, torch.bfloat16, rowwise=True)
+    assert full.shape == (m, n)
+    if fmt == "nvfp4":       # the tensor-level scale sees only the shard's amax: same values within tolerance
+        assert ((full.float() - ref.float()).norm() / ref.float().norm()).item() < 0.1
+    else:
+        assert torch.equal(full, ref)
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "fp8_e4m3", "nvfp4"])
+def test_m_sharded_gemm_matches_single_gpu(fmt):
+    _run(_sharded_gemm_rank, 2, fmt)
+
+
+def _ep_rank(rank, world):
+    from pretrain_b200 import dist as D, ops
+    from pretrain_b200.layers.mlp import _grouped_ffn_padded, silu_glu
+    t, d, e, k, i = 1024, 256, 16, 4, 128
+    x, logits, w_gu, w_d = R.inputs_moe(world * t, d, e, k, i, seed=5)
+    top_i, top_w = R.router_topk(logits, k)
+    x, top_i, top_w, w_gu, w_d = (v.cuda() for v in (x, top_i, top_w, w_gu, w_d))
+    lo, hi, el = rank * t, (rank + 1) * t, e // world
+    with torch.no_grad():
+        out = D.expert_parallel_moe(x[lo:hi], top_i[lo:hi], top_w[lo:hi], w_gu[rank * el:(rank + 1) * el].contiguous(),
+                                    w_d[rank * el:(rank + 1) * el].contiguous(), e)
+        # single-GPU block on all tokens with the same kernels
+        plan = ops.moe_permute_plan(top_i, e)
+        a, sfa = ops.moe_gather(x, plan, True)
+        y = _grouped_ffn_padded(a, sfa, plan, w_gu, w_d, silu_glu, True)
+        ref = ops.moe_unpermute(y, top_w, plan.row_of, world * t)[lo:hi]
+    # per-row arithmetic is identical; only the fp32 reduction order over a token's k rows may differ
+    assert ((out.float() - ref.float()).abs().max() <= 2 ** -7 * ref.float().abs().max()).item()
+    assert ((out.float() - ref.float()).norm() / ref.float().norm()).item() < 2e-3
+
+
+def test_expert_parallel_moe_matches_single_gpu():
+    _run(_ep_rank, 2)
