@@ -35,9 +35,8 @@ constexpr int BM = 128;
 constexpr int BKB = 128;                 // bytes of K per stage (= one 128-byte swizzle row)
 constexpr int kGemmThreads = 192;
 constexpr int kSmemBudget = 227 * 1024;
-constexpr int EPI_COLS = 32;             // columns per epilogue block
-constexpr int EPI_BLOCK_BYTES = 32 * EPI_COLS * 2;
-constexpr int kEpiBytes1 = 4 * EPI_BLOCK_BYTES;      // one staging block per epilogue warp
+
+#include "gemm_epilogue.cuh"
 
 constexpr int cgcd(int a, int b) { return b == 0 ? a : cgcd(b, a % b); }
 
@@ -81,7 +80,7 @@ struct Cfg {
   static constexpr int SMEM_BYTES = BAR_OFF + 256 /*barriers*/ + 1024 /*alignment slack*/;
   // A B tile may start 64 rows into a 128-row scale-factor group (tensor-memory column offset 2);
   // offsets of 32 or 96 rows (odd column offsets) are misaligned for the MMA's scale operand.
-  static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "tile width: multiple of 64");
+  static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "tile width: multiple of 64 (also the epilogue block)");
   static_assert(SFB_COL0 + SFB_COLS <= TMEM_COLS, "tensor memory overflow");
   static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
   static_assert(SMEM_BYTES <= kSmemBudget, "shared memory overflow");
@@ -112,10 +111,6 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m,
   n = r / gm;
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 template <int KIND, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -295,64 +290,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       if (KIND == KIND_F8) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
-      // One 32-column block: scale, round, stage in swizzled shared memory, TMA store.
-      auto emit = [&](int c, const uint32_t (&r)[32]) {
-        const int64_t colg = col0 + c * EPI_COLS;
-        float sbv = 1.f;
-        if (KIND == KIND_F8) sbv = p.b_scalar ? __ldg(p.scale_b) : (colg + lane < p.N ? __ldg(p.scale_b + colg + lane) : 0.f);
-        uint32_t o[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float lo = u2f(r[2 * i]) * row_scale, hi = u2f(r[2 * i + 1]) * row_scale;
-          if (KIND == KIND_F8) {
-            lo *= __shfl_sync(0xFFFFFFFFu, sbv, 2 * i);
-            hi *= __shfl_sync(0xFFFFFFFFu, sbv, 2 * i + 1);
-          }
-          o[i] = pack_bf16(lo, hi);
-        }
-        if (lane == 0) ptx::bulk_wait_read<C::EPI_BUFS - 1>();   // the store that last read this buffer is done with it
-        __syncwarp();
-        uint8_t* dst = epi_g + buf * EPI_BLOCK_BYTES + lane * 64;
-        const int sw = (lane >> 1) & 3;               // 64-byte swizzle: 16-byte chunk j of row r sits at j ^ ((r >> 1) & 3)
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(dst + ((j ^ sw) << 4)) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-        ptx::fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          ptx::tma_store_2d(&tmap_d, (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
-          ptx::bulk_commit();
-        }
-        buf = (buf + 1) % C::EPI_BUFS;
-      };
-
       // Block order: natural, except that an overlapped accumulator 0 is read from its last
       // block down, because its LAST columns are the strip shared with accumulator 1 (whose
       // shared strip is its first columns).  The accumulator is released for the MMA after the
       // strip has been read (overlapped) or after the last block has been read (otherwise).
-      const bool rev = C::OVERLAP && acc == 0;
       constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;
-      uint32_t ra[32], rb[32];
-      ptx::tmem_ld32(taddr + (rev ? NBLK - 1 : 0) * EPI_COLS, ra);
-#pragma unroll
-      for (int i = 0; i < NBLK; ++i) {
-        const int c = rev ? NBLK - 1 - i : i;
-        ptx::tmem_ld_wait();
-        if (i == RELEASE_AFTER) {
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
-        }
-        if (i + 1 < NBLK) {
-          const int cn = rev ? c - 1 : c + 1;
-          if (i & 1) ptx::tmem_ld32(taddr + cn * EPI_COLS, ra);
-          else ptx::tmem_ld32(taddr + cn * EPI_COLS, rb);
-        }
-        if (col0 + c * EPI_COLS < p.N && row0 < p.M) {      // warp-uniform
-          if (i & 1) emit(c, rb);
-          else emit(c, ra);
-        }
-      }
+      const uint32_t release_bar = tempty_bar(acc);
+      epilogue_tile<KIND == KIND_F8, NBLK, C::EPI_BUFS, RELEASE_AFTER>(
+          taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &tmap_d, epi_s, epi_g, buf, lane,
+          [&]() {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(release_bar);
+          });
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (lane == 0) ptx::bulk_wait<0>();           // all stores of this warp have landed
@@ -413,8 +363,8 @@ int launch(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, G
   // operands: byte matrices [rows, row_bytes], box = 128 bytes x tile rows, 128-byte swizzle
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, p.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, b_rows, row_bytes, BKB, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  // output: bf16 [M, N] pitch ldd, box = 32 x 32 elements, 64-byte swizzle
-  if ((rc = encode_2d(&md, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, p.N, p.M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+  // output: bf16 [M, N] pitch ldd, box = 64 columns x 32 rows, 128-byte swizzle
+  if ((rc = encode_2d(&md, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, p.N, p.M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   p.num_m = (int)((p.M + BM - 1) / BM);
   p.num_n = (int)((p.N + BN - 1) / BN);
   p.num_k = (int)((row_bytes + BKB - 1) / BKB);

@@ -225,59 +225,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (KIND == KIND_F8) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
-      auto emit = [&](int c, const uint32_t (&r)[32]) {
-        const int64_t colg = col0 + c * EPI_COLS;
-        float sbv = 1.f;
-        if (KIND == KIND_F8) sbv = p.b_scalar ? __ldg(p.scale_b) : (colg + lane < p.N ? __ldg(p.scale_b + colg + lane) : 0.f);
-        uint32_t o[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float lo = u2f(r[2 * i]) * row_scale, hi = u2f(r[2 * i + 1]) * row_scale;
-          if (KIND == KIND_F8) {
-            lo *= __shfl_sync(0xFFFFFFFFu, sbv, 2 * i);
-            hi *= __shfl_sync(0xFFFFFFFFu, sbv, 2 * i + 1);
-          }
-          o[i] = pack_bf16(lo, hi);
-        }
-        if (lane == 0) ptx::bulk_wait_read<1>();
-        __syncwarp();
-        uint8_t* dst = epi_g + buf * EPI_BLOCK_BYTES + lane * 64;
-        const int sw = (lane >> 1) & 3;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(dst + ((j ^ sw) << 4)) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-        ptx::fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          ptx::tma_store_2d(&tmap_d, (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
-          ptx::bulk_commit();
-        }
-        buf ^= 1;
-      };
-
-      const bool rev = C::OVERLAP && acc == 0;
       constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;
-      uint32_t ra[32], rb[32];
-      ptx::tmem_ld32(taddr + (rev ? NBLK - 1 : 0) * EPI_COLS, ra);
-#pragma unroll
-      for (int i = 0; i < NBLK; ++i) {
-        const int c = rev ? NBLK - 1 - i : i;
-        ptx::tmem_ld_wait();
-        if (i == RELEASE_AFTER) {
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(tempty_bar(acc) & ptx::kLeaderMask);   // the leader's barrier
-        }
-        if (i + 1 < NBLK) {
-          const int cn = rev ? c - 1 : c + 1;
-          if (i & 1) ptx::tmem_ld32(taddr + cn * EPI_COLS, ra);
-          else ptx::tmem_ld32(taddr + cn * EPI_COLS, rb);
-        }
-        if (col0 + c * EPI_COLS < p.N && row0 < p.M) {
-          if (i & 1) emit(c, rb);
-          else emit(c, ra);
-        }
-      }
+      const uint32_t release_bar = tempty_bar(acc) & ptx::kLeaderMask;       // the leader's barrier, from either CTA
+      epilogue_tile<KIND == KIND_F8, NBLK, 2, RELEASE_AFTER>(
+          taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &tmap_d, epi_s, epi_g, buf, lane,
+          [&]() {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(release_bar);
+          });
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (lane == 0) ptx::bulk_wait<0>();
@@ -303,7 +259,8 @@ bool pair_eligible(int64_t M, int64_t N, int64_t row_bytes, bool grouped) {
   if (grouped || g_pair_mode < 0) return false;
   if (g_pair_mode > 0) return true;
   const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
-  return tiles >= kNumSMs / 2 && row_bytes >= 8 * BKB;
+  (void)row_bytes;
+  return tiles >= kNumSMs / 2;     // measured faster than the one-CTA kernel from K = 384 up once the pairs are busy
 }
 
 template <int KIND>
@@ -314,7 +271,7 @@ int launch_pair(const void* A, const void* B, void* D, int64_t ldd, const GemmPa
   int rc;
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, gp.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, gp.N, row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = encode_2d(&md, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, gp.N, gp.M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+  if ((rc = encode_2d(&md, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, gp.N, gp.M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   int sf_kt = 0;
   if (KIND != KIND_F8) {
     // scale buffers as rows of 256 bytes (two rows per 512-byte atom); box = the atoms of one K step
