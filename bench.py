@@ -332,6 +332,7 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
+        torch.set_num_threads(len(os.sched_getaffinity(0)))     # torchrun pins OMP_NUM_THREADS=1
         steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
         cb = cpu_moe_sample(m, n, k) if kind == "moe" else run_cpu(kind, m, n, k, steps, warm)
         print(json.dumps({"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOPS", "n_gpus": args.gpus,
@@ -440,6 +441,26 @@ def main():
         ag_ms = t.item()
         allgather = {"ms_per_step_with_allgather": ag_ms, "tflops_with_allgather": world * flops / (ag_ms * 1e-3) / 1e12,
                      "bytes_received_per_rank": (world - 1) * m * n * 2, "collective": "ncclAllGather (NCCL over NVLink)"}
+        # the same step with the gather fused into the GEMM epilogue (TMA stores into the peers' buffers)
+        try:
+            from pretrain_b200 import dist as D
+            gout = D.GatheredOutput(m, n)
+            ffmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3"}[kind]
+            for _ in range(3):
+                D.sharded_gemm_fused(a, b, ffmt, gout)
+            barrier()
+            t0.record()
+            for _ in range(20):
+                D.sharded_gemm_fused(a, b, ffmt, gout)
+            t1.record()
+            barrier()
+            t = torch.tensor([t0.elapsed_time(t1) / 20], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            allgather["fused_ms_per_step"] = t.item()
+            allgather["fused_tflops"] = world * flops / (t.item() * 1e-3) / 1e12
+            allgather["fused"] = "GEMM epilogue stores every tile into all ranks' gathered buffers (symmetric memory, NVLink)"
+        except Exception as ex:                       # symmetric memory not available on this system
+            allgather["fused_error"] = str(ex)[:200]
 
     if rank != 0:
         if dist is not None:

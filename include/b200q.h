@@ -108,6 +108,25 @@ int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* 
                      const float* tsA, const float* tsB, int64_t M, int64_t N, int64_t K, void* D,
                      int64_t ldd, void* stream);
 
+/* Fused GEMM + all-gather of an output sharded by rows across `world` GPUs (new functionality: the
+ * reference is single-GPU).  Each call computes this rank's [M, N] block exactly as the plain entry
+ * point does and its epilogue stores every block into rows [rank*M, rank*M + M) of EVERY rank's
+ * gathered buffer D_all[g] (bf16 [world*M, N], pitch ldd): D_all[rank] is local memory, the others
+ * are peer-mapped pointers to the peers' buffers (CUDA IPC or symmetric memory).  Only stores cross
+ * NVLink, tile by tile while the main loop runs; nothing is loaded from a peer.  The gathered
+ * matrix is complete on a rank once every rank's kernel has finished: synchronize the ranks before
+ * reading it.  world <= 8; every rank passes the same M. */
+int b200q_gemm_fp8_allgather(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a,
+                             int a_scale_is_scalar, const float* scale_b, int b_scale_is_scalar,
+                             int64_t M, int64_t N, int64_t K, void* const* D_all, int world, int rank,
+                             int64_t ldd, void* stream);
+int b200q_gemm_mxfp8_allgather(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
+                               const void* sfB, int64_t M, int64_t N, int64_t K, void* const* D_all,
+                               int world, int rank, int64_t ldd, void* stream);
+int b200q_gemm_nvfp4_allgather(const void* A, const void* sfA, const void* B, const void* sfB,
+                               const float* tsA, const float* tsB, int64_t M, int64_t N, int64_t K,
+                               void* const* D_all, int world, int rank, int64_t ldd, void* stream);
+
 /* ---- MoE: top-k permute, ragged grouped GEMM, SwiGLU, weighted unpermute ------------------
  * Layout used between these calls ("padded expert-sorted"): rows sorted by expert in the
  * reference's order (stable sort of the flattened (token, slot) pairs by expert id,

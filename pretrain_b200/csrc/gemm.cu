@@ -115,7 +115,7 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m,
 template <int KIND, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
+            const __grid_constant__ OutMaps outs, const GemmParams p) {
   using C = Cfg<KIND, BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -153,7 +153,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
-    ptx::prefetch_tensormap(&tmap_d);
+    for (int g = 0; g < outs.count; ++g) ptx::prefetch_tensormap(&outs.m[g]);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), C::TMEM_COLS);
@@ -297,7 +297,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;
       const uint32_t release_bar = tempty_bar(acc);
       epilogue_tile<KIND == KIND_F8, NBLK, C::EPI_BUFS, RELEASE_AFTER>(
-          taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &tmap_d, epi_s, epi_g, buf, lane,
+          taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
           [&]() {
             ptx::tc_fence_before();
             __syncwarp();
@@ -354,17 +354,39 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64
   return B200Q_OK;
 }
 
+// Output buffers of one launch: [M, N] bf16 each, pitch ldd (the local one first).
+struct OutSpec {
+  void* ptr[kMaxOutputs];
+  int count;
+};
+inline OutSpec one_output(void* D) {
+  OutSpec o = {};
+  o.ptr[0] = D;
+  o.count = 1;
+  return o;
+}
+// output maps: bf16 [M, N] pitch ldd, box = 64 columns x 32 rows, 128-byte swizzle
+int make_out_maps(OutMaps* om, const OutSpec& outs, int64_t M, int64_t N, int64_t ldd) {
+  om->count = outs.count;
+  for (int g = 0; g < outs.count; ++g) {
+    int rc = encode_2d(&om->m[g], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, outs.ptr[g], N, M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  for (int g = outs.count; g < kMaxOutputs; ++g) om->m[g] = om->m[0];
+  return B200Q_OK;
+}
+
 template <int KIND, int BN>
-int launch(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, GemmParams p, cudaStream_t st) {
+int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, GemmParams p, cudaStream_t st) {
   using C = Cfg<KIND, BN>;
   const int64_t row_bytes = KIND == KIND_NV ? p.K / 2 : p.K;
-  CUtensorMap ma, mb, md;
+  CUtensorMap ma, mb;
+  OutMaps md;
   int rc;
   // operands: byte matrices [rows, row_bytes], box = 128 bytes x tile rows, 128-byte swizzle
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, p.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, b_rows, row_bytes, BKB, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  // output: bf16 [M, N] pitch ldd, box = 64 columns x 32 rows, 128-byte swizzle
-  if ((rc = encode_2d(&md, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, p.N, p.M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_out_maps(&md, D, p.M, p.N, ldd))) return rc;
   p.num_m = (int)((p.M + BM - 1) / BM);
   p.num_n = (int)((p.N + BN - 1) / BN);
   p.num_k = (int)((row_bytes + BKB - 1) / BKB);
@@ -408,10 +430,10 @@ int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
 // CTA-pair form of the dense GEMMs (gemm_2cta.cu, same translation unit)
 bool pair_eligible(int64_t M, int64_t N, int64_t row_bytes, bool grouped);
 template <int KIND>
-int launch_pair(const void* A, const void* B, void* D, int64_t ldd, const GemmParams& gp, cudaStream_t st);
+int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, const GemmParams& gp, cudaStream_t st);
 
 template <int KIND>
-int dispatch(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, const GemmParams& p, cudaStream_t st) {
+int dispatch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, const GemmParams& p, cudaStream_t st) {
   if (pair_eligible(p.M, p.N, KIND == KIND_NV ? p.K / 2 : p.K, p.tile_expert != nullptr)) return launch_pair<KIND>(A, B, D, ldd, p, st);
   const int bn = g_force_bn ? g_force_bn : choose_bn<KIND>(p.M, p.N, KIND == KIND_NV ? p.K / 2 : p.K);
   switch (bn) {
@@ -420,6 +442,22 @@ int dispatch(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows,
     case 256: return launch<KIND, 256>(A, B, D, ldd, b_rows, p, st);
     default: return B200Q_ERR_INVALID_ARG;
   }
+}
+
+// Destination list of a fused GEMM + all-gather: rows [rank*M, rank*M + M) of every rank's gathered
+// buffer, the local one first, then the peers starting with the next rank (so that at any moment
+// the ranks write to different peers).
+int gathered_outputs(OutSpec* o, void* const* d_all, int world, int rank, int64_t M, int64_t ldd) {
+  if (d_all == nullptr || world < 1 || world > kMaxOutputs || rank < 0 || rank >= world) return B200Q_ERR_INVALID_ARG;
+  *o = OutSpec{};
+  o->count = world;
+  for (int i = 0; i < world; ++i) {
+    void* base = d_all[(rank + i) % world];
+    if (base == nullptr) return B200Q_ERR_INVALID_ARG;
+    if (!aligned16(base)) return B200Q_ERR_ALIGNMENT;
+    o->ptr[i] = static_cast<uint8_t*>(base) + (size_t)rank * M * ldd * 2;
+  }
+  return B200Q_OK;
 }
 
 int check_gemm(const void* A, const void* B, const void* D, int64_t M, int64_t N, int64_t K, int64_t ldd, int kmult) {
@@ -453,7 +491,7 @@ int b200q_gemm_fp8(const void* A, int a_fmt, const void* B, int b_fmt, const flo
   GemmParams p = {};
   p.scale_a = scale_a; p.scale_b = scale_b; p.a_scalar = a_scale_is_scalar; p.b_scalar = b_scale_is_scalar;
   p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.M = M; p.N = N; p.K = K;
-  return dispatch<KIND_F8>(A, B, D, ldd, N, p, (cudaStream_t)stream);
+  return dispatch<KIND_F8>(A, B, one_output(D), ldd, N, p, (cudaStream_t)stream);
 }
 
 int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
@@ -465,7 +503,7 @@ int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, i
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   p.M = M; p.N = N; p.K = K;
-  return dispatch<KIND_MX>(A, B, D, ldd, N, p, (cudaStream_t)stream);
+  return dispatch<KIND_MX>(A, B, one_output(D), ldd, N, p, (cudaStream_t)stream);
 }
 
 int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,
@@ -477,7 +515,7 @@ int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* 
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.scale_a = tsA; p.scale_b = tsB;
   p.M = M; p.N = N; p.K = K;
-  return dispatch<KIND_NV>(A, B, D, ldd, N, p, (cudaStream_t)stream);
+  return dispatch<KIND_NV>(A, B, one_output(D), ldd, N, p, (cudaStream_t)stream);
 }
 
 int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB,
@@ -492,7 +530,50 @@ int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const vo
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   p.M = padded_rows; p.N = N; p.K = K; p.tile_expert = tile_expert; p.num_tiles = num_tiles;
-  return dispatch<KIND_MX>(A, B, D, ldd, (int64_t)E * N, p, (cudaStream_t)stream);
+  return dispatch<KIND_MX>(A, B, one_output(D), ldd, (int64_t)E * N, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_fp8_allgather(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a, int a_scale_is_scalar,
+                             const float* scale_b, int b_scale_is_scalar, int64_t M, int64_t N, int64_t K, void* const* D_all,
+                             int world, int rank, int64_t ldd, void* stream) {
+  OutSpec outs;
+  int rc = gathered_outputs(&outs, D_all, world, rank, M, ldd);
+  if (rc) return rc;
+  if ((rc = check_gemm(A, B, outs.ptr[0], M, N, K, ldd, 16))) return rc;
+  if (scale_a == nullptr || scale_b == nullptr || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
+  GemmParams p = {};
+  p.scale_a = scale_a; p.scale_b = scale_b; p.a_scalar = a_scale_is_scalar; p.b_scalar = b_scale_is_scalar;
+  p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.M = M; p.N = N; p.K = K;
+  return dispatch<KIND_F8>(A, B, outs, ldd, N, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_mxfp8_allgather(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
+                               int64_t N, int64_t K, void* const* D_all, int world, int rank, int64_t ldd, void* stream) {
+  OutSpec outs;
+  int rc = gathered_outputs(&outs, D_all, world, rank, M, ldd);
+  if (rc) return rc;
+  if ((rc = check_gemm(A, B, outs.ptr[0], M, N, K, ldd, 32))) return rc;
+  if (sfA == nullptr || sfB == nullptr || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.M = M; p.N = N; p.K = K;
+  return dispatch<KIND_MX>(A, B, outs, ldd, N, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_nvfp4_allgather(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,
+                               int64_t M, int64_t N, int64_t K, void* const* D_all, int world, int rank, int64_t ldd,
+                               void* stream) {
+  OutSpec outs;
+  int rc = gathered_outputs(&outs, D_all, world, rank, M, ldd);
+  if (rc) return rc;
+  if ((rc = check_gemm(A, B, outs.ptr[0], M, N, K, ldd, 32))) return rc;
+  if (sfA == nullptr || sfB == nullptr || tsA == nullptr || tsB == nullptr) return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.scale_a = tsA; p.scale_b = tsB;
+  p.M = M; p.N = N; p.K = K;
+  return dispatch<KIND_NV>(A, B, outs, ldd, N, p, (cudaStream_t)stream);
 }
 
 }  // extern "C"

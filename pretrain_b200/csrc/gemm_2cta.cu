@@ -75,7 +75,7 @@ template <int KIND>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                 const __grid_constant__ CUtensorMap tmap_d, const pair::PairParams p) {
+                 const __grid_constant__ OutMaps outs, const pair::PairParams p) {
   using C = pair::PCfg<KIND>;
   constexpr int BN = pair::PBN;
   extern __shared__ uint8_t smem_raw[];
@@ -103,7 +103,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
-    ptx::prefetch_tensormap(&tmap_d);
+    for (int g = 0; g < outs.count; ++g) ptx::prefetch_tensormap(&outs.m[g]);
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -228,7 +228,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;
       const uint32_t release_bar = tempty_bar(acc) & ptx::kLeaderMask;       // the leader's barrier, from either CTA
       epilogue_tile<KIND == KIND_F8, NBLK, 2, RELEASE_AFTER>(
-          taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &tmap_d, epi_s, epi_g, buf, lane,
+          taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
           [&]() {
             ptx::tc_fence_before();
             __syncwarp();
@@ -264,14 +264,15 @@ bool pair_eligible(int64_t M, int64_t N, int64_t row_bytes, bool grouped) {
 }
 
 template <int KIND>
-int launch_pair(const void* A, const void* B, void* D, int64_t ldd, const GemmParams& gp, cudaStream_t st) {
+int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, const GemmParams& gp, cudaStream_t st) {
   using C = pair::PCfg<KIND>;
   const int64_t row_bytes = KIND == KIND_NV ? gp.K / 2 : gp.K;
-  CUtensorMap ma, mb, msa, msb, md;
+  CUtensorMap ma, mb, msa, msb;
+  OutMaps md;
   int rc;
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, gp.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, gp.N, row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = encode_2d(&md, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, gp.N, gp.M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_out_maps(&md, D, gp.M, gp.N, ldd))) return rc;
   int sf_kt = 0;
   if (KIND != KIND_F8) {
     // scale buffers as rows of 256 bytes (two rows per 512-byte atom); box = the atoms of one K step

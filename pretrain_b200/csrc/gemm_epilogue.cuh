@@ -9,6 +9,15 @@ constexpr int EPI_COLS = 64;                         // columns per epilogue blo
 constexpr int EPI_BLOCK_BYTES = 32 * EPI_COLS * 2;   // 4 KB staging block
 constexpr int kEpiBytes1 = 4 * EPI_BLOCK_BYTES;      // one staging block per epilogue warp
 
+// Where a tile's blocks are stored: this GPU's output and, for the fused GEMM + all-gather, the
+// same rows of every peer's copy of the gathered output (peer-mapped device memory, written by
+// TMA stores over NVLink; stores only — nothing is ever loaded from a peer).
+constexpr int kMaxOutputs = 8;
+struct OutMaps {
+  CUtensorMap m[kMaxOutputs];
+  int count;
+};
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -26,7 +35,7 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
 template <bool COL_SCALE, int NBLK, int EPI_BUFS, int RELEASE_AFTER, class Release>
 __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t row0, int64_t col0, int64_t M, int64_t N,
                                               float row_scale, const float* __restrict__ scale_b, int b_scalar,
-                                              const CUtensorMap* tmap_d, uint32_t epi_s, uint8_t* epi_g, int& buf, int lane,
+                                              const OutMaps* outs, uint32_t epi_s, uint8_t* epi_g, int& buf, int lane,
                                               Release release) {
   auto emit = [&](int c, const uint32_t (&r)[64]) {
     const int64_t colg = col0 + c * EPI_COLS;
@@ -59,7 +68,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t 
     ptx::fence_proxy_async();
     __syncwarp();
     if (lane == 0) {
-      ptx::tma_store_2d(tmap_d, (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
+      for (int g = 0; g < outs->count; ++g)
+        ptx::tma_store_2d(&outs->m[g], (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
       ptx::bulk_commit();
     }
     buf = (buf + 1) % EPI_BUFS;

@@ -63,6 +63,53 @@ def sharded_gemm(a_shard: torch.Tensor, b: torch.Tensor, a_fmt: str, b_fmt: str,
     return all_gather_rows(local, m, group) if gather else local
 
 
+class GatheredOutput:
+    """The gathered (world * m, n) bf16 output of an M-sharded GEMM as symmetric memory: every rank
+    owns one copy and has its peers' copies mapped, so that the GEMM's epilogue can store each tile
+    straight into all of them over NVLink (fused GEMM + all-gather, no separate collective)."""
+
+    def __init__(self, m: int, n: int, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.m, self.n = m, n
+        self.buf = symm.empty((self.world * m, n), dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm.rendezvous(self.buf, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._flag = torch.zeros(1, device=self.buf.device)
+
+    def sync(self) -> None:
+        """Stream-ordered rendezvous of the ranks: once it has run, every rank's stores have landed."""
+        dist.all_reduce(self._flag, group=self.group)
+
+
+def sharded_gemm_fused(a_shard: torch.Tensor, w: torch.Tensor, fmt: str, out: GatheredOutput) -> torch.Tensor:
+    """`a_shard @ w.T` for this rank's rows of A (w is the (n, k) weight, replicated), quantized to
+    `fmt` ("mxfp8", "nvfp4" or "fp8_e4m3" with per-row scales), with the output all-gather fused
+    into the GEMM's epilogue.  Returns the gathered (world * m, n) matrix (valid after `out.sync()`,
+    which this function calls)."""
+    from . import ops
+    if a_shard.shape[0] != out.m or w.shape[0] != out.n:
+        raise ValueError("shard / weight shape does not match the gathered output")
+    if fmt in ("mxfp8", "mxfp8_e4m3"):
+        ca, sfa = ops.quantize_mxfp8(a_shard, 1)
+        cb, sfb = ops.quantize_mxfp8(w, 1)
+        ops.gemm_mxfp8_allgather(ca, sfa, cb, sfb, out.ptrs, out.rank, out.n, out.n)
+    elif fmt in ("nvfp4", "fp4_nv"):
+        pa, sfa, ta = ops.quantize_nvfp4(a_shard, 1)
+        pb, sfb, tb = ops.quantize_nvfp4(w, 1)
+        ops.gemm_nvfp4_allgather(pa, sfa, ta, pb, sfb, tb, out.ptrs, out.rank, out.n, out.n)
+    elif fmt in ("fp8", "fp8_e4m3"):
+        e4 = torch.float8_e4m3fn
+        ca, sa = ops.quantize_fp8(a_shard, e4, 1)
+        cb, sb = ops.quantize_fp8(w, e4, 1)
+        ops.gemm_fp8_allgather(ca, e4, cb, e4, sa, sb, out.ptrs, out.rank, out.n, out.n)
+    else:
+        raise ValueError(f"unsupported format for the fused GEMM + all-gather: {fmt!r}")
+    out.sync()
+    return out.buf
+
+
 # ---- expert parallelism ---------------------------------------------------------------------
 
 @dataclass

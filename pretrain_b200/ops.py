@@ -142,6 +142,35 @@ def gemm_nvfp4(a_packed, a_sf, a_ts, b_packed, b_sf, b_ts, out=None):
     return d
 
 
+def _ptr_array(ptrs):
+    import ctypes
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+def gemm_mxfp8_allgather(a_codes, a_sf, b_codes, b_sf, out_ptrs, rank: int, n: int, ldd: int, a_fmt=E4M3, b_fmt=E4M3):
+    """Fused GEMM + all-gather: this rank's (M, n) block goes to rows [rank*M, rank*M+M) of the gathered
+    buffer of every rank; `out_ptrs` are the device pointers of those buffers (own and peer-mapped)."""
+    m, k = a_codes.shape
+    _lib.check(_lib.load().b200q_gemm_mxfp8_allgather(a_codes.data_ptr(), fmt_of(a_fmt), a_sf.data_ptr(), b_codes.data_ptr(),
+                                                      fmt_of(b_fmt), b_sf.data_ptr(), m, n, k, _ptr_array(out_ptrs),
+                                                      len(out_ptrs), rank, ldd, _stream()), "b200q_gemm_mxfp8_allgather")
+
+
+def gemm_nvfp4_allgather(a_packed, a_sf, a_ts, b_packed, b_sf, b_ts, out_ptrs, rank: int, n: int, ldd: int):
+    m, k2 = a_packed.shape
+    _lib.check(_lib.load().b200q_gemm_nvfp4_allgather(a_packed.data_ptr(), a_sf.data_ptr(), b_packed.data_ptr(), b_sf.data_ptr(),
+                                                      a_ts.data_ptr(), b_ts.data_ptr(), m, n, 2 * k2, _ptr_array(out_ptrs),
+                                                      len(out_ptrs), rank, ldd, _stream()), "b200q_gemm_nvfp4_allgather")
+
+
+def gemm_fp8_allgather(a_codes, a_fmt, b_codes, b_fmt, scale_a, scale_b, out_ptrs, rank: int, n: int, ldd: int):
+    m, k = a_codes.shape
+    _lib.check(_lib.load().b200q_gemm_fp8_allgather(a_codes.data_ptr(), fmt_of(a_fmt), b_codes.data_ptr(), fmt_of(b_fmt),
+                                                    scale_a.data_ptr(), int(scale_a.numel() == 1), scale_b.data_ptr(),
+                                                    int(scale_b.numel() == 1), m, n, k, _ptr_array(out_ptrs), len(out_ptrs),
+                                                    rank, ldd, _stream()), "b200q_gemm_fp8_allgather")
+
+
 # ---- MoE ------------------------------------------------------------------------------------
 
 class MoEPlan:

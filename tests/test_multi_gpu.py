@@ -59,6 +59,34 @@ def test_m_sharded_gemm_matches_single_gpu(fmt):
     _run(_sharded_gemm_rank, 2, fmt)
 
 
+def _fused_rank(rank, world, fmt):
+    from pretrain_b200 import dist as D, ops
+    from pretrain_b200.quant.linear import _gemm
+    m, k, n = 2048, 1024, 1536                 # per-rank rows; 8 x 6 pair tiles per rank
+    g = torch.Generator().manual_seed(rank)
+    a = torch.randn(m, k, generator=g).bfloat16().cuda()
+    w = (0.05 * torch.randn(n, k, generator=torch.Generator().manual_seed(77))).bfloat16().cuda()
+    out = D.GatheredOutput(m, n)
+    for _ in range(2):                          # the second pass overwrites the first in place
+        full = D.sharded_gemm_fused(a, w, fmt, out)
+    local = _gemm(a, w.t(), fmt, fmt, torch.bfloat16, rowwise=True)
+    ref = D.all_gather_rows(local, world * m)   # the NCCL all-gather of the same shards
+    torch.cuda.synchronize()
+    assert torch.equal(full, ref)
+    ops.device_status()
+    for small_m in (128, 96):                   # one-CTA kernel path, ragged rows
+        o2 = D.GatheredOutput(small_m, n)
+        f2 = D.sharded_gemm_fused(a[:small_m], w, fmt, o2)
+        r2 = D.all_gather_rows(_gemm(a[:small_m], w.t(), fmt, fmt, torch.bfloat16, rowwise=True), world * small_m, multiple=small_m)
+        torch.cuda.synchronize()
+        assert torch.equal(f2, r2)
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4", "fp8_e4m3"])
+def test_fused_gemm_allgather_equals_nccl_allgather(fmt):
+    _run(_fused_rank, 2, fmt)
+
+
 def _ep_rank(rank, world):
     from pretrain_b200 import dist as D, ops
     from pretrain_b200.layers.mlp import _grouped_ffn_padded, silu_glu
