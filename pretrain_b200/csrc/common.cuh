@@ -41,6 +41,32 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
   return v;
 }
 
+// 32 bytes per lane: one 256-bit load when the address allows it (WIDE), else two 128-bit
+// loads that keep the line in L1 between them (the pair covers one 32-byte sector).
+template <bool WIDE>
+__device__ __forceinline__ void ld_nc_32B(const void* p, uint4& a, uint4& b) {
+  if (WIDE) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p));
+  } else {
+    asm volatile("ld.global.nc.L1::evict_first.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p));
+    asm volatile("ld.global.nc.L1::evict_first.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(static_cast<const char*>(p) + 16));
+  }
+}
+template <bool WIDE>
+__device__ __forceinline__ void st_32B(void* p, const uint4& a, const uint4& b) {
+  if (WIDE) {
+    asm volatile("st.global.v8.u32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};"
+                 :: "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w), "l"(p) : "memory");
+  } else {
+    reinterpret_cast<uint4*>(p)[0] = a;
+    reinterpret_cast<uint4*>(p)[1] = b;
+  }
+}
+__host__ __device__ inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; }
+
 // |bf16x2| max of two packed words, as packed bf16x2 (exact: comparisons only).
 __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t v) {
   __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&acc);

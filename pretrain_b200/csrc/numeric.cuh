@@ -96,6 +96,21 @@ B200Q_HD float div_by_rcp(float a, float b, float r) {
   return u2f((f2u(q) & 0x7FFFFFFFu) | (f2u(a) & 0x80000000u));
 }
 
+// a / b for a value that is about to be narrowed to fp8 or fp4: one multiply and ONE
+// residual correction.  The result is within one fp32 ulp of the quotient, which is not
+// always the correctly rounded fp32 value, but the narrow cast of it equals the narrow cast
+// of the IEEE quotient: the host check walks every (bf16 x, bf16-derived scale) pair for
+// both fp8 formats, and for fp4 every bf16 x next to a rounding boundary of every
+// (block scale byte, tensor scale) product.  Only a bf16 input makes this safe: its 8-bit
+// significand keeps quotients away from the narrow formats' ties unless they sit on them.
+B200Q_HD float quot_for_cast(float a, float b, float r) {
+  float q = mul_rn(a, r);
+  // residual with its sign flipped, so that a = -0 (q = -0, e = +0) ends as -0 + -0 = -0 and a
+  // zero quotient keeps a's sign without a fix-up; for every other input it is the same value
+  float e = fma_rn(b, q, -a);
+  return fma_rn(e, -r, q);   // negate the reciprocal, not e: no compiler may fold that into e's fma
+}
+
 // scale = max(amax / qmax, 1e-12)   (src/quant/fp8.py:30)
 B200Q_HD float fp8_scale_from_amax(float amax, int fmt) {
   float s = div_rn(amax, fp8_max(fmt));

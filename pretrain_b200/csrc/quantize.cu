@@ -76,12 +76,15 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const uint16_t* __restri
 }
 
 // ------------------------------------------------------------------------------------------
-// Row-wise block quantizers (MXFP8 / NVFP4): one warp walks a row, each lane owns 8
-// consecutive elements per step, blocks are reduced with 2 (MX) or 1 (NV) shuffle steps.
+// Row-wise block quantizers (MXFP8 / NVFP4).  A warp takes a 1024-column chunk of a row and
+// each lane owns 32 consecutive elements of it: one MX block or two NV blocks, so the block
+// maximum, the scale and the scale-factor store are done once per block with no shuffles.  A
+// lane reads its 64 bytes as two 32-byte sectors (256-bit loads when the pitch allows) and
+// writes 32 (MX) or 16 (NV) contiguous code bytes; the warp's accesses tile the chunk exactly.
 // ------------------------------------------------------------------------------------------
 enum { MODE_MX = 0, MODE_NV = 1, MODE_FP8 = 2 };
 
-template <int MODE>
+template <int MODE, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
 rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, int fmt,
                            uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, int swz,
@@ -98,56 +101,63 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
   // work item = (row, 1024-column chunk), dealt round-robin to all warps of the grid
   const int chunks = (int)((cols + 1023) >> 10), ncols = (int)cols;
   const int64_t kt = (nblk + 3) >> 2;
+  const int c = lane * 32;
   for (ItemWalker w((int64_t)blockIdx.x * kWarps + warp, (int64_t)gridDim.x * kWarps, chunks); w.row < rows; w.next()) {
     const int64_t row = w.row;
     const int c0 = w.chunk << 10;
-    const uint16_t* xr = x + row * ld + c0;
-    uint8_t* cr = codes + (MODE == MODE_MX ? row * cols + c0 : (row * cols + c0) >> 1);
+    if (c0 + c >= ncols) continue;   // cols is a multiple of 32: a lane's run is whole or absent
+    const uint16_t* xp = x + row * ld + c0 + c;
+    uint4 v[4];
+    ld_nc_32B<WIDE>(xp, v[0], v[1]);
+    ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
     // scale-factor address of block kb of this row = sfr + (swizzled ? (kb >> 2) * 512 + (kb & 3) : kb)
     uint8_t* sfr = sf + (swz ? (row >> 7) * kt * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 : row * nblk);
-    uint4 v[4];
+    if (MODE == MODE_MX) {
+      uint32_t m = absmax_bf16x2(absmax_bf16x2(v[0].x, v[0].y), absmax_bf16x2(v[0].z, v[0].w));
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int c = u * 256 + lane * 8;
-      v[u] = c0 + c < ncols ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
-    }
+      for (int u = 1; u < 4; ++u) {
+        m = absmax_bf16x2(m, absmax_bf16x2(v[u].x, v[u].y));
+        m = absmax_bf16x2(m, absmax_bf16x2(v[u].z, v[u].w));
+      }
+      const int e = mx_scale_exp(fmaxf(bf16lo(m), bf16hi(m)), fmt);
+      const float inv = mx_inv_scale(e);
+      uint32_t o[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int c = u * 256 + lane * 8;
-      if (c0 + u * 256 >= ncols) break;   // warp-uniform
-      const bool live = c0 + c < ncols;
-      float a = absmax8(v[u]);
-      a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
-      if (MODE == MODE_MX) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
-      float f[8];
-      unpack8(v[u], f);
-      if (MODE == MODE_MX) {
-        const int e = mx_scale_exp(a, fmt);
-        const float inv = mx_inv_scale(e);
-        uint2 o;
-        o.x = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, fmt);
-        o.y = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, fmt);
-        if (live) {
-          *reinterpret_cast<uint2*>(cr + c) = o;
-          const int kb = (c0 + c) >> 5;
-          if ((lane & 3) == 0) sfr[swz ? (kb >> 2) * 512 + (kb & 3) : kb] = (uint8_t)(e + 127);
-        }
-      } else {
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        unpack8(v[u], f);
+        o[2 * u] = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, fmt);
+        o[2 * u + 1] = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, fmt);
+      }
+      st_32B<WIDE>(codes + row * cols + c0 + c, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+      const int kb = (c0 >> 5) + lane;
+      sfr[swz ? (kb >> 2) * 512 + (kb & 3) : kb] = (uint8_t)(e + 127);
+    } else {
+      uint32_t o[4];
+      uint8_t sq2[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float a = fmaxf(absmax8(v[2 * h]), absmax8(v[2 * h + 1]));
         const uint8_t sq = nv_block_scale_fast(a, s_t, rcp_st);
         const float eff = mul_rn(e4m3_to_float(sq), s_t);
         const float rcp = rcp_rn(eff);
-        uint32_t o = 0;
-        if (sq != 0) {
+        sq2[h] = sq;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          float f[8];
+          unpack8(v[2 * h + q], f);
+          uint32_t t = 0;
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            o |= (uint32_t)cvt_e2m1x2(div_by_rcp(f[2 * i], eff, rcp), div_by_rcp(f[2 * i + 1], eff, rcp)) << (8 * i);
-        }
-        if (live) {
-          *reinterpret_cast<uint32_t*>(cr + (c >> 1)) = o;
-          const int kb = (c0 + c) >> 4;
-          if ((lane & 1) == 0) sfr[swz ? (kb >> 2) * 512 + (kb & 3) : kb] = sq;
+            t |= (uint32_t)cvt_e2m1x2(quot_for_cast(f[2 * i], eff, rcp), quot_for_cast(f[2 * i + 1], eff, rcp)) << (8 * i);
+          o[2 * h + q] = sq != 0 ? t : 0u;
         }
       }
+      *reinterpret_cast<uint4*>(codes + ((row * cols + c0 + c) >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
+      const int kb = (c0 >> 4) + 2 * lane;   // even: the pair of scale bytes is adjacent in both layouts
+      uint8_t* sp = sfr + (swz ? (kb >> 2) * 512 + (kb & 3) : kb);
+      sp[0] = sq2[0];
+      sp[1] = sq2[1];
     }
   }
 }
@@ -212,7 +222,7 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
         float f[8];
         unpack8(v[i], f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = div_by_rcp(f[j], scale, rcp);
+        for (int j = 0; j < 8; ++j) f[j] = quot_for_cast(f[j], scale, rcp);
         uint2 o;
         o.x = cvt_fp8x4(f[0], f[1], f[2], f[3], fmt);
         o.y = cvt_fp8x4(f[4], f[5], f[6], f[7], fmt);
@@ -223,7 +233,7 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
         float f[8];
         unpack8(ld_nc_v4(xr + c), f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = div_by_rcp(f[j], scale, rcp);
+        for (int j = 0; j < 8; ++j) f[j] = quot_for_cast(f[j], scale, rcp);
         uint2 o;
         o.x = cvt_fp8x4(f[0], f[1], f[2], f[3], fmt);
         o.y = cvt_fp8x4(f[4], f[5], f[6], f[7], fmt);
@@ -349,7 +359,7 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
       if (sq != 0) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          uint32_t b = cvt_e2m1x2(div_by_rcp(f[16 * h + 2 * i], eff, rcp), div_by_rcp(f[16 * h + 2 * i + 1], eff, rcp));
+          uint32_t b = cvt_e2m1x2(quot_for_cast(f[16 * h + 2 * i], eff, rcp), quot_for_cast(f[16 * h + 2 * i + 1], eff, rcp));
           o[2 * h + (i >> 2)] |= b << (8 * (i & 3));
         }
       }
@@ -362,8 +372,8 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
     uint32_t o[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      o[i] = cvt_fp8x4(div_by_rcp(f[4 * i], scale, rcp), div_by_rcp(f[4 * i + 1], scale, rcp),
-                       div_by_rcp(f[4 * i + 2], scale, rcp), div_by_rcp(f[4 * i + 3], scale, rcp), fmt);
+      o[i] = cvt_fp8x4(quot_for_cast(f[4 * i], scale, rcp), quot_for_cast(f[4 * i + 1], scale, rcp),
+                       quot_for_cast(f[4 * i + 2], scale, rcp), quot_for_cast(f[4 * i + 3], scale, rcp), fmt);
     uint4* dst = reinterpret_cast<uint4*>(&tout[c * OUT_PITCH + 32 * j]);
     dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
     dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
@@ -545,8 +555,13 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf, outer, contraction / 32, sf_layout, st))) return rc;
   if (axis == 1) {
-    rowwise_block_quant_kernel<MODE_MX><<<rowwise_grid(rowwise_block_quant_kernel<MODE_MX>, rows, cols), kThreads, 0, st>>>(
-        (const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr);
+    // 256-bit loads and stores need 32-byte aligned rows on both sides
+    if (aligned32(x) && aligned32(codes) && (ld & 15) == 0)
+      rowwise_block_quant_kernel<MODE_MX, true><<<rowwise_grid(rowwise_block_quant_kernel<MODE_MX, true>, rows, cols), kThreads, 0, st>>>(
+          (const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr);
+    else
+      rowwise_block_quant_kernel<MODE_MX, false><<<rowwise_grid(rowwise_block_quant_kernel<MODE_MX, false>, rows, cols), kThreads, 0, st>>>(
+          (const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr);
   } else {
     dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
     transpose_quant_kernel<MODE_MX><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes,
@@ -570,8 +585,12 @@ int b200q_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf, outer, contraction / 16, sf_layout, st))) return rc;
   if (axis == 1) {
-    rowwise_block_quant_kernel<MODE_NV><<<rowwise_grid(rowwise_block_quant_kernel<MODE_NV>, rows, cols), kThreads, 0, st>>>(
-        (const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax, tensor_scale_out);
+    if (aligned32(x) && (ld & 15) == 0)
+      rowwise_block_quant_kernel<MODE_NV, true><<<rowwise_grid(rowwise_block_quant_kernel<MODE_NV, true>, rows, cols), kThreads, 0, st>>>(
+          (const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax, tensor_scale_out);
+    else
+      rowwise_block_quant_kernel<MODE_NV, false><<<rowwise_grid(rowwise_block_quant_kernel<MODE_NV, false>, rows, cols), kThreads, 0, st>>>(
+          (const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax, tensor_scale_out);
   } else {
     dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
     transpose_quant_kernel<MODE_NV><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes,

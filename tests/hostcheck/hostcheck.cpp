@@ -13,9 +13,11 @@ static inline float bf(uint16_t b) { return u2f((uint32_t)b << 16); }
 
 extern "C" {
 
-// Every positive finite bf16 amax, every bf16 |x| <= amax: the hoisted-reciprocal division
-// must give the same fp8 code as the IEEE division (and is also counted at fp32 level).
-// out[0] = code mismatches, out[1] = fp32 mismatches whose quotient is >= 2^-20, out[2] = pairs
+// Every positive finite bf16 amax, every bf16 |x| <= amax: the two-correction division must
+// equal the IEEE division at fp32 level, and the one-correction quotient the kernels feed
+// to the narrow cast must give the same fp8 code.
+// out[0] = code mismatches of quot_for_cast, out[1] = fp32 mismatches of div_by_rcp whose
+// quotient is >= 2^-20, out[2] = pairs
 void hc_div_exhaustive_fp8(int fmt, int amax_stride, int64_t* out) {
   int64_t bad_code = 0, bad_f32 = 0, n = 0;
   for (uint32_t ab = 1; ab < 0x7F80u; ab += amax_stride) {
@@ -28,7 +30,8 @@ void hc_div_exhaustive_fp8(int fmt, int amax_stride, int64_t* out) {
       float q1 = div_by_rcp(x, scale, r);
       ++n;
       if (f2u(q0) != f2u(q1) && fabsf(q0) >= 9.5367431640625e-07f) ++bad_f32;
-      if (cvt_fp8x2(q0, -q0, fmt) != cvt_fp8x2(q1, -q1, fmt)) ++bad_code;
+      float q2 = quot_for_cast(x, scale, r);
+      if (cvt_fp8x2(q0, -q0, fmt) != cvt_fp8x2(q2, -q2, fmt)) ++bad_code;
     }
   }
   out[0] = bad_code; out[1] = bad_f32; out[2] = n;
@@ -50,11 +53,48 @@ void hc_div_random_fp4(int64_t count, uint64_t seed, int64_t* out) {
     float x = bf(xb);
     if (!(x <= eff * 8.0f)) x = eff * (float)(xb & 7);
     float r = rcp_rn(eff);
-    float q0 = x / eff, q1 = div_by_rcp(x, eff, r);
+    float q0 = x / eff, q1 = div_by_rcp(x, eff, r), q2 = quot_for_cast(x, eff, r);
     if (f2u(q0) != f2u(q1) && fabsf(q0) >= 9.5367431640625e-07f) ++bad_f32;
-    if (cvt_e2m1x2(q0, -q0) != cvt_e2m1x2(q1, -q1)) ++bad_code;
+    if (cvt_e2m1x2(q0, -q0) != cvt_e2m1x2(q2, -q2)) ++bad_code;
   }
   out[0] = bad_code; out[1] = bad_f32;
+}
+
+// The fp4 cast can only differ where the quotient is within an fp32 ulp of a rounding
+// boundary of E2M1, so walk exactly those: for every block scale byte and every `stride`-th
+// tensor scale derived from a bf16 maximum (plus `extra` random fp32 tensor scales), the
+// bf16 inputs nearest to boundary * eff.  out[0] = code mismatches, out[1] = cases
+void hc_quot_fp4_boundaries(int stride, int64_t extra, uint64_t seed, int64_t* out) {
+  static const float kBoundary[8] = {0.25f, 0.75f, 1.25f, 1.75f, 2.5f, 3.5f, 5.0f, 6.0f};
+  int64_t bad = 0, n = 0;
+  auto walk = [&](float eff) {
+    if (!(eff > 0.f) || isinf(eff)) return;
+    float r = rcp_rn(eff);
+    for (int bi = 0; bi < 8; ++bi) {
+      uint32_t tb = f2u(kBoundary[bi] * eff) >> 16;
+      for (int d = -3; d <= 3; ++d) {
+        int xb = (int)tb + d;
+        if (xb < 0 || xb >= 0x7F80) continue;
+        float x = bf((uint16_t)xb);
+        float q0 = x / eff, q2 = quot_for_cast(x, eff, r);
+        ++n;
+        if (cvt_e2m1x2(q0, -q0) != cvt_e2m1x2(q2, -q2)) ++bad;
+      }
+    }
+  };
+  for (uint32_t ab = 1; ab < 0x7F80u; ab += stride) {
+    float s_t = nv_tensor_scale(bf((uint16_t)ab));
+    for (int sq = 1; sq < 127; ++sq) walk(mul_rn(e4m3_to_float((uint8_t)sq), s_t));
+  }
+  uint64_t s = seed * 6364136223846793005ull + 1442695040888963407ull;
+  for (int64_t i = 0; i < extra; ++i) {
+    s = s * 6364136223846793005ull + 1442695040888963407ull;
+    uint32_t u = (uint32_t)(s >> 32);
+    float s_t = u2f(((127u - 45u + (u >> 23) % 90u) << 23) | (u & 0x7FFFFFu));
+    s = s * 6364136223846793005ull + 1442695040888963407ull;
+    walk(mul_rn(e4m3_to_float((uint8_t)(1 + (s >> 40) % 126)), s_t));
+  }
+  out[0] = bad; out[1] = n;
 }
 
 // codes [rows, cols], scales [rows]: per-row FP8 quantization as the kernel does it.
@@ -66,8 +106,8 @@ void hc_quant_fp8_rows(const uint16_t* x, int64_t rows, int64_t cols, int fmt, u
     float rcp = rcp_rn(scale);
     scales[r] = scale;
     for (int64_t c = 0; c < cols; c += 2) {
-      uint16_t p = cvt_fp8x2(div_by_rcp(bf(x[r * cols + c]), scale, rcp),
-                             div_by_rcp(bf(x[r * cols + c + 1]), scale, rcp), fmt);
+      uint16_t p = cvt_fp8x2(quot_for_cast(bf(x[r * cols + c]), scale, rcp),
+                             quot_for_cast(bf(x[r * cols + c + 1]), scale, rcp), fmt);
       codes[r * cols + c] = (uint8_t)p; codes[r * cols + c + 1] = (uint8_t)(p >> 8);
     }
   }
@@ -105,7 +145,7 @@ void hc_quant_nvfp4_rows(const uint16_t* x, int64_t rows, int64_t cols, float te
       float eff = e4m3_to_float(sq) * s_t;
       float rcp = rcp_rn(eff);
       for (int i = 0; i < 16; i += 2) {
-        uint8_t c = sq == 0 ? 0 : cvt_e2m1x2(div_by_rcp(bf(p[i]), eff, rcp), div_by_rcp(bf(p[i + 1]), eff, rcp));
+        uint8_t c = sq == 0 ? 0 : cvt_e2m1x2(quot_for_cast(bf(p[i]), eff, rcp), quot_for_cast(bf(p[i + 1]), eff, rcp));
         packed[r * (cols / 2) + b * 8 + i / 2] = c;
       }
     }

@@ -39,7 +39,11 @@ def _cases():
     wide = (torch.randn(32, 256, generator=g) * torch.exp2(torch.randint(-30, 30, (32, 256), generator=g).float()))
     tiny = torch.randn(8, 128, generator=g) * 1e-20
     zeros = torch.zeros(4, 64)
-    return [x, w, xo, wide.to(torch.bfloat16), tiny.to(torch.bfloat16), zeros.to(torch.bfloat16)]
+    signed = torch.randn(8, 64, generator=g)
+    signed[:, ::3] = -0.0          # negative zeros keep their sign bit through every format
+    signed[:, 1::7] *= -1e-30      # negative values that underflow to -0 after scaling
+    return [x, w, xo, wide.to(torch.bfloat16), tiny.to(torch.bfloat16), zeros.to(torch.bfloat16),
+            signed.to(torch.bfloat16), (-zeros).to(torch.bfloat16)]
 
 
 @pytest.mark.parametrize("fmt,dt", [(0, E4), (1, E5)])
@@ -53,6 +57,12 @@ def test_division_random_fp4(hc):
     out = (ctypes.c_int64 * 3)()
     hc.hc_div_random_fp4(ctypes.c_int64(20_000_000), ctypes.c_uint64(7), out)
     assert out[0] == 0 and out[1] == 0
+
+
+def test_fp4_codes_at_every_rounding_boundary(hc):
+    out = (ctypes.c_int64 * 2)()
+    hc.hc_quot_fp4_boundaries(5, ctypes.c_int64(2_000_000), ctypes.c_uint64(11), out)
+    assert out[1] > 4e7 and out[0] == 0
 
 
 def test_nvfp4_block_scale_with_hoisted_reciprocals_is_exact(hc):
