@@ -81,8 +81,41 @@ __device__ __forceinline__ float absmax8(uint4 v) {
   return fmaxf(bf16lo(m), bf16hi(m));
 }
 
-// Walks (row, chunk) work items that are dealt round-robin over all warps of the grid, without
-// a division inside the loop: item = first, first + stride, ...; row = item / chunks.
+// bf16 x 8 in a 16-byte word -> floats (exact)
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+  f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
+}
+
+// One MXFP8 block held by one thread: 32 bf16 in four 16-byte words -> 32 code bytes in o[0..7];
+// returns the block's unbiased scale exponent.
+template <int FMT>
+__device__ __forceinline__ int mx_quant_block32(const uint4 (&v)[4], uint32_t (&o)[8]) {
+  uint32_t m = absmax_bf16x2(absmax_bf16x2(v[0].x, v[0].y), absmax_bf16x2(v[0].z, v[0].w));
+#pragma unroll
+  for (int u = 1; u < 4; ++u) {
+    m = absmax_bf16x2(m, absmax_bf16x2(v[u].x, v[u].y));
+    m = absmax_bf16x2(m, absmax_bf16x2(v[u].z, v[u].w));
+  }
+  const int e = mx_scale_exp(fmaxf(bf16lo(m), bf16hi(m)), FMT);
+  const float inv = mx_inv_scale(e);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    float f[8];
+    unpack8(v[u], f);
+    o[2 * u] = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, FMT);
+    o[2 * u + 1] = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, FMT);
+  }
+  return e;
+}
+
+// Byte offset of the scale factor of (row, block kb) in the 128x4-tiled layout; kt = K-tiles per row tile.
+__device__ __forceinline__ int64_t sf_swizzled(int64_t row, int kb, int64_t kt) {
+  return ((row >> 7) * kt + (kb >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3);
+}
+
+// Walks (row, chunk) work items that are dealt round-robin over the warps (or the threads) of the
+// grid, without a division inside the loop: item = first, first + stride, ...; row = item / chunks.
 struct ItemWalker {
   int64_t row, row_step;
   int chunk, chunks, chunk_step;

@@ -145,114 +145,90 @@ __global__ void moe_pad_src_kernel(const int32_t* __restrict__ offs, const int32
   src_of_row[r] = src;
 }
 
-__device__ __forceinline__ void unpack8f(const uint4& v, float (&f)[8]) {
-  f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
-  f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
-}
-
-// 8 bf16 of one lane -> MXFP8 codes; the 32-element block spans 4 lanes
-__device__ __forceinline__ uint2 mx_quant8(const uint4& v, int fmt, int& e_out) {
-  float a = absmax8(v);
-  a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
-  a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
-  const int e = mx_scale_exp(a, fmt);
-  const float inv = mx_inv_scale(e);
-  float f[8];
-  unpack8f(v, f);
-  uint2 o;
-  o.x = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, fmt);
-  o.y = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, fmt);
-  e_out = e;
-  return o;
-}
-
 // ---- gather rows into the padded layout (+ MXFP8) ------------------------------------------------
-template <int QUANT>
+// Work item = 32 consecutive elements of one padded row (one MX block), owned by one thread and
+// dealt round-robin over the grid's threads: 64 bytes in (two sectors), 32 code bytes + one scale
+// byte (or the 64 bytes themselves) out.  Pad rows (source -1) become zero rows.
+template <int QUANT, bool WIDE, int FMT>
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const uint16_t* __restrict__ x, int64_t D, int64_t ld, const int32_t* __restrict__ src_of_row,
-                  const int32_t* __restrict__ num_tiles, int64_t padded_rows, int fmt, uint8_t* __restrict__ out,
+                  const int32_t* __restrict__ num_tiles, int64_t padded_rows, uint8_t* __restrict__ out,
                   uint8_t* __restrict__ sf) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int64_t live_rows = (int64_t)(*num_tiles) << 7;
   if (live_rows > padded_rows) live_rows = padded_rows;
-  const int ncols = (int)D;
+  const int runs = (int)(D >> 5);
   const int64_t kt = ((D >> 5) + 3) >> 2;
-  for (int64_t r = (int64_t)blockIdx.x * 8 + warp; r < live_rows; r += (int64_t)gridDim.x * 8) {
+  for (ItemWalker w((int64_t)blockIdx.x * 256 + threadIdx.x, (int64_t)gridDim.x * 256, runs); w.row < live_rows; w.next()) {
+    const int64_t r = w.row;
+    const int c = w.chunk << 5;
     const int src = src_of_row[r];
-    const uint16_t* xr = x + (int64_t)(src < 0 ? 0 : src) * ld;
-    uint8_t* orow = out + r * D * (QUANT ? 1 : 2);
-    uint8_t* sfr = QUANT ? sf + (r >> 7) * kt * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 : nullptr;
-    for (int c0 = 0; c0 < ncols; c0 += 1024) {
-      uint4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = c0 + u * 256 + lane * 8;
-        v[u] = (src >= 0 && c < ncols) ? ld_nc_v4(xr + c) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = c0 + u * 256 + lane * 8;
-        if (c0 + u * 256 >= ncols) break;      // warp-uniform
-        if (QUANT) {
-          int e;
-          const uint2 o = mx_quant8(v[u], fmt, e);
-          if (c < ncols) {
-            *reinterpret_cast<uint2*>(orow + c) = o;
-            const int kb = c >> 5;
-            if ((lane & 3) == 0) sfr[(kb >> 2) * 512 + (kb & 3)] = (uint8_t)(e + 127);
-          }
-        } else if (c < ncols) {
-          *reinterpret_cast<uint4*>(orow + c * 2) = v[u];
-        }
-      }
+    uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (src >= 0) {
+      const uint16_t* xp = x + (int64_t)src * ld + c;
+      ld_nc_32B<WIDE>(xp, v[0], v[1]);
+      ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
+    }
+    if (QUANT) {
+      uint32_t o[8];
+      const int e = mx_quant_block32<FMT>(v, o);
+      st_32B<WIDE>(out + r * D + c, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+      sf[sf_swizzled(r, w.chunk, kt)] = (uint8_t)(e + 127);
+    } else {
+      uint8_t* op = out + (r * D + c) * 2;
+      st_32B<WIDE>(op, v[0], v[1]);
+      st_32B<WIDE>(op + 32, v[2], v[3]);
     }
   }
 }
 
 __device__ __forceinline__ float bf16_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
 
-// ---- SwiGLU (+ MXFP8) between the two grouped GEMMs -------------------------------------------------
-// h = bf16(bf16(silu(gate)) * up), the roundings of the reference's bf16 tensor ops.
-template <int QUANT>
-__global__ void __launch_bounds__(256)
-swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t ld, int fmt, uint8_t* __restrict__ out,
-              uint8_t* __restrict__ sf) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t kt = ((I >> 5) + 3) >> 2;
-  for (ItemWalker w((int64_t)blockIdx.x * 8 + warp, (int64_t)gridDim.x * 8, (int)((I + 255) >> 8)); w.row < rows; w.next()) {
-    const int64_t r = w.row;
-    const int c = w.chunk * 256 + lane * 8;
-    const bool live = c < (int)I;
-    const uint16_t* gr = g + r * ld + c;
-    uint4 vg = make_uint4(0, 0, 0, 0), vu = vg;
-    if (live) {
-      vg = ld_nc_v4(gr);
-      vu = ld_nc_v4(gr + I);
-    }
-    float a[8], b[8];
-    unpack8f(vg, a);
-    unpack8f(vu, b);
-    uint32_t h[4];
+// h = bf16(bf16(silu(gate)) * up) for 8 (gate, up) pairs packed as bf16: the roundings of the
+// reference's bf16 tensor ops.  silu(x) = x / (1 + e^-x) with the hardware exponential and
+// reciprocal: within 2 fp32 ulp, far inside the bf16 rounding that follows.
+__device__ __forceinline__ uint4 swiglu8(const uint4& vg, const uint4& vu) {
+  float a[8], b[8];
+  unpack8(vg, a);
+  unpack8(vu, b);
+  uint32_t h[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      // silu(x) = x / (1 + e^-x) with the hardware exponential and reciprocal: within 2 fp32 ulp,
-      // far inside the bf16 rounding that follows
-      const float s0 = bf16_round(__fdividef(a[2 * i], 1.f + __expf(-a[2 * i])));
-      const float s1 = bf16_round(__fdividef(a[2 * i + 1], 1.f + __expf(-a[2 * i + 1])));
-      __nv_bfloat162 p = __floats2bfloat162_rn(s0 * b[2 * i], s1 * b[2 * i + 1]);
-      h[i] = *reinterpret_cast<uint32_t*>(&p);
-    }
-    const uint4 hv = make_uint4(h[0], h[1], h[2], h[3]);
+  for (int i = 0; i < 4; ++i) {
+    const float s0 = bf16_round(__fdividef(a[2 * i], 1.f + __expf(-a[2 * i])));
+    const float s1 = bf16_round(__fdividef(a[2 * i + 1], 1.f + __expf(-a[2 * i + 1])));
+    __nv_bfloat162 p = __floats2bfloat162_rn(s0 * b[2 * i], s1 * b[2 * i + 1]);
+    h[i] = *reinterpret_cast<uint32_t*>(&p);
+  }
+  return make_uint4(h[0], h[1], h[2], h[3]);
+}
+
+// ---- SwiGLU (+ MXFP8) between the two grouped GEMMs -------------------------------------------------
+// Input rows are [gate (I) | up (I)]; work item = 32 consecutive outputs of one row, one thread.
+template <int QUANT, bool WIDE, int FMT>
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t ld, uint8_t* __restrict__ out,
+              uint8_t* __restrict__ sf) {
+  const int runs = (int)(I >> 5);
+  const int64_t kt = ((I >> 5) + 3) >> 2;
+  for (ItemWalker w((int64_t)blockIdx.x * 256 + threadIdx.x, (int64_t)gridDim.x * 256, runs); w.row < rows; w.next()) {
+    const int64_t r = w.row;
+    const int c = w.chunk << 5;
+    const uint16_t* gp = g + r * ld + c;
+    uint4 vg[4], vu[4], h[4];
+    ld_nc_32B<WIDE>(gp, vg[0], vg[1]);
+    ld_nc_32B<WIDE>(gp + 16, vg[2], vg[3]);
+    ld_nc_32B<WIDE>(gp + I, vu[0], vu[1]);
+    ld_nc_32B<WIDE>(gp + I + 16, vu[2], vu[3]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) h[u] = swiglu8(vg[u], vu[u]);
     if (QUANT) {
-      int e;
-      const uint2 o = mx_quant8(hv, fmt, e);
-      if (live) {
-        *reinterpret_cast<uint2*>(out + r * I + c) = o;
-        const int kb = c >> 5;
-        if ((lane & 3) == 0) sf[(r >> 7) * kt * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (kb >> 2) * 512 + (kb & 3)] = (uint8_t)(e + 127);
-      }
-    } else if (live) {
-      *reinterpret_cast<uint4*>(out + (r * I + c) * 2) = hv;
+      uint32_t o[8];
+      const int e = mx_quant_block32<FMT>(h, o);
+      st_32B<WIDE>(out + r * I + c, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+      sf[sf_swizzled(r, w.chunk, kt)] = (uint8_t)(e + 127);
+    } else {
+      uint8_t* op = out + (r * I + c) * 2;
+      st_32B<WIDE>(op, h[0], h[1]);
+      st_32B<WIDE>(op + 32, h[2], h[3]);
     }
   }
 }
@@ -270,7 +246,7 @@ moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t
       const int row = row_of[t * k + j];
       const float wj = u2f((uint32_t)w[t * k + j] << 16);
       float f[8];
-      unpack8f(ld_nc_v4(y + (int64_t)row * ldy + c), f);
+      unpack8(ld_nc_v4(y + (int64_t)row * ldy + c), f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = fmaf(wj, f[i], acc[i]);
     }
@@ -291,6 +267,12 @@ constexpr int64_t kStaticPlanInts = 262144;
 static __device__ __align__(256) int32_t g_static_plan_scratch[kStaticPlanInts];
 constexpr int kMaxDevices = 64;
 static int32_t* g_static_plan_ptr[kMaxDevices] = {};   // device address of the array, per device
+
+// grid for kernels whose work items belong to single threads (256 per CTA), capped at one wave
+inline int thread_item_grid(int64_t items) {
+  int64_t want = (items + 255) / 256, cap = (int64_t)kNumSMs * 5;
+  return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
 
 inline int row_grid(int64_t items) {
   int64_t want = (items + 7) / 8, cap = (int64_t)kNumSMs * 8;
@@ -369,14 +351,17 @@ int b200q_moe_gather(const void* x, int64_t D, int64_t ld, const int32_t* src_of
   int rc = require_sm100();
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  if (quantize) {
-    if ((D >> 5) & 3) B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(padded_rows, D >> 5, B200Q_SF_SWIZZLE_128x4), st));
-    moe_gather_kernel<1><<<row_grid(padded_rows), 256, 0, st>>>((const uint16_t*)x, D, ld, src_of_row, num_tiles, padded_rows, fmt,
-                                                                (uint8_t*)out, (uint8_t*)sf);
-  } else {
-    moe_gather_kernel<0><<<row_grid(padded_rows), 256, 0, st>>>((const uint16_t*)x, D, ld, src_of_row, num_tiles, padded_rows, fmt,
-                                                                (uint8_t*)out, nullptr);
-  }
+  if (quantize && ((D >> 5) & 3))
+    B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(padded_rows, D >> 5, B200Q_SF_SWIZZLE_128x4), st));
+  const bool wide = aligned32(x) && aligned32(out) && (ld & 15) == 0;
+  const int grid = thread_item_grid(padded_rows * (D >> 5));
+#define B200Q_GO(Q, W, F)                                                                                              \
+  moe_gather_kernel<Q, W, F><<<grid, 256, 0, st>>>((const uint16_t*)x, D, ld, src_of_row, num_tiles, padded_rows, (uint8_t*)out, \
+                                                   (uint8_t*)sf)
+  if (!quantize) { if (wide) B200Q_GO(0, true, FMT_E4M3); else B200Q_GO(0, false, FMT_E4M3); }
+  else if (fmt == B200Q_E4M3) { if (wide) B200Q_GO(1, true, FMT_E4M3); else B200Q_GO(1, false, FMT_E4M3); }
+  else { if (wide) B200Q_GO(1, true, FMT_E5M2); else B200Q_GO(1, false, FMT_E5M2); }
+#undef B200Q_GO
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -390,14 +375,15 @@ int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantiz
   int rc = require_sm100();
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  const int64_t items = rows * ((I + 255) / 256);
-  if (quantize) {
-    if ((rows & 127) || ((I >> 5) & 3))
-      B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(rows, I >> 5, B200Q_SF_SWIZZLE_128x4), st));
-    swiglu_kernel<1><<<row_grid(items), 256, 0, st>>>((const uint16_t*)g, rows, I, ld, fmt, (uint8_t*)out, (uint8_t*)sf);
-  } else {
-    swiglu_kernel<0><<<row_grid(items), 256, 0, st>>>((const uint16_t*)g, rows, I, ld, fmt, (uint8_t*)out, nullptr);
-  }
+  if (quantize && ((rows & 127) || ((I >> 5) & 3)))
+    B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(rows, I >> 5, B200Q_SF_SWIZZLE_128x4), st));
+  const bool wide = aligned32(g) && aligned32(out) && (ld & 15) == 0;
+  const int grid = thread_item_grid(rows * (I >> 5));
+#define B200Q_GO(Q, W, F) swiglu_kernel<Q, W, F><<<grid, 256, 0, st>>>((const uint16_t*)g, rows, I, ld, (uint8_t*)out, (uint8_t*)sf)
+  if (!quantize) { if (wide) B200Q_GO(0, true, FMT_E4M3); else B200Q_GO(0, false, FMT_E4M3); }
+  else if (fmt == B200Q_E4M3) { if (wide) B200Q_GO(1, true, FMT_E4M3); else B200Q_GO(1, false, FMT_E4M3); }
+  else { if (wide) B200Q_GO(1, true, FMT_E5M2); else B200Q_GO(1, false, FMT_E5M2); }
+#undef B200Q_GO
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -36,11 +36,6 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-  f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
-  f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
-}
-
 // ------------------------------------------------------------------------------------------
 // amax over a matrix
 // ------------------------------------------------------------------------------------------
@@ -76,20 +71,20 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const uint16_t* __restri
 }
 
 // ------------------------------------------------------------------------------------------
-// Row-wise block quantizers (MXFP8 / NVFP4).  A warp takes a 1024-column chunk of a row and
-// each lane owns 32 consecutive elements of it: one MX block or two NV blocks, so the block
-// maximum, the scale and the scale-factor store are done once per block with no shuffles.  A
-// lane reads its 64 bytes as two 32-byte sectors (256-bit loads when the pitch allows) and
-// writes 32 (MX) or 16 (NV) contiguous code bytes; the warp's accesses tile the chunk exactly.
+// Row-wise block quantizers (MXFP8 / NVFP4).  The work item is a run of 32 consecutive elements
+// of a row (one MX block, or two NV blocks) and belongs to ONE thread: block maximum, scale and
+// scale-factor store happen once per block with no shuffles.  Items are dealt round-robin to
+// the threads of the grid, so the lanes of a warp read consecutive 64-byte runs (two 32-byte
+// sectors each, as 256-bit loads when the pitch allows) whatever the row length, and write 32
+// (MX) or 16 (NV) contiguous code bytes.
 // ------------------------------------------------------------------------------------------
 enum { MODE_MX = 0, MODE_NV = 1, MODE_FP8 = 2 };
 
-template <int MODE, bool WIDE>
+template <int MODE, bool WIDE, int FMT>
 __global__ void __launch_bounds__(kThreads)
-rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, int fmt,
+rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                            uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, int swz,
                            const float* __restrict__ tensor_amax, float* __restrict__ tensor_scale_out) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int BS = MODE == MODE_MX ? 32 : 16;
   const int64_t nblk = cols / BS;
   float s_t = 0.f, rcp_st = 0.f;
@@ -98,40 +93,20 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
     rcp_st = rcp_rn(s_t);
     if (blockIdx.x == 0 && threadIdx.x == 0) *tensor_scale_out = s_t;
   }
-  // work item = (row, 1024-column chunk), dealt round-robin to all warps of the grid
-  const int chunks = (int)((cols + 1023) >> 10), ncols = (int)cols;
+  const int runs = (int)(cols >> 5);            // 32-element runs per row
   const int64_t kt = (nblk + 3) >> 2;
-  const int c = lane * 32;
-  for (ItemWalker w((int64_t)blockIdx.x * kWarps + warp, (int64_t)gridDim.x * kWarps, chunks); w.row < rows; w.next()) {
+  for (ItemWalker w((int64_t)blockIdx.x * kThreads + threadIdx.x, (int64_t)gridDim.x * kThreads, runs); w.row < rows; w.next()) {
     const int64_t row = w.row;
-    const int c0 = w.chunk << 10;
-    if (c0 + c >= ncols) continue;   // cols is a multiple of 32: a lane's run is whole or absent
-    const uint16_t* xp = x + row * ld + c0 + c;
+    const int c = w.chunk << 5;
+    const uint16_t* xp = x + row * ld + c;
     uint4 v[4];
     ld_nc_32B<WIDE>(xp, v[0], v[1]);
     ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
-    // scale-factor address of block kb of this row = sfr + (swizzled ? (kb >> 2) * 512 + (kb & 3) : kb)
-    uint8_t* sfr = sf + (swz ? (row >> 7) * kt * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 : row * nblk);
     if (MODE == MODE_MX) {
-      uint32_t m = absmax_bf16x2(absmax_bf16x2(v[0].x, v[0].y), absmax_bf16x2(v[0].z, v[0].w));
-#pragma unroll
-      for (int u = 1; u < 4; ++u) {
-        m = absmax_bf16x2(m, absmax_bf16x2(v[u].x, v[u].y));
-        m = absmax_bf16x2(m, absmax_bf16x2(v[u].z, v[u].w));
-      }
-      const int e = mx_scale_exp(fmaxf(bf16lo(m), bf16hi(m)), fmt);
-      const float inv = mx_inv_scale(e);
       uint32_t o[8];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        float f[8];
-        unpack8(v[u], f);
-        o[2 * u] = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, fmt);
-        o[2 * u + 1] = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, fmt);
-      }
-      st_32B<WIDE>(codes + row * cols + c0 + c, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
-      const int kb = (c0 >> 5) + lane;
-      sfr[swz ? (kb >> 2) * 512 + (kb & 3) : kb] = (uint8_t)(e + 127);
+      const int e = mx_quant_block32<FMT>(v, o);
+      st_32B<WIDE>(codes + row * cols + c, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+      sf[swz ? sf_swizzled(row, w.chunk, kt) : row * nblk + w.chunk] = (uint8_t)(e + 127);
     } else {
       uint32_t o[4];
       uint8_t sq2[2];
@@ -153,9 +128,9 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
           o[2 * h + q] = sq != 0 ? t : 0u;
         }
       }
-      *reinterpret_cast<uint4*>(codes + ((row * cols + c0 + c) >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
-      const int kb = (c0 >> 4) + 2 * lane;   // even: the pair of scale bytes is adjacent in both layouts
-      uint8_t* sp = sfr + (swz ? (kb >> 2) * 512 + (kb & 3) : kb);
+      *reinterpret_cast<uint4*>(codes + ((row * cols + c) >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
+      const int kb = 2 * w.chunk;   // even: the pair of scale bytes is adjacent in both layouts
+      uint8_t* sp = sf + (swz ? sf_swizzled(row, kb, kt) : row * nblk + kb);
       sp[0] = sq2[0];
       sp[1] = sq2[1];
     }
@@ -168,12 +143,13 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
 // 16-byte vectors per lane; partial maxima meet in shared memory).  NVEC == 0 re-reads the row
 // (it is still in L2) for rows too long for that.
 // ------------------------------------------------------------------------------------------
-template <int NVEC>
+template <int NVEC, int FMT>
 __global__ void __launch_bounds__(kThreads)
-rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, int fmt,
+rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                    uint8_t* __restrict__ codes, float* __restrict__ scales, const float* __restrict__ tensor_amax,
                    float* __restrict__ tensor_scale_out, int wpr) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int fmt = FMT;
   const int grp = warp / wpr, wig = warp - grp * wpr, rpc = kWarps / wpr;
   __shared__ float smax[2][kWarps];
   int it = 0;
@@ -295,15 +271,16 @@ __global__ void amax_to_scale_kernel(float* __restrict__ scales, int64_t n, int 
 // ------------------------------------------------------------------------------------------
 constexpr int kTR = 128, kTC = 64;
 
-template <int MODE>
+template <int MODE, int FMT>
 __global__ void __launch_bounds__(kThreads)
-transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, int fmt,
+transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                        uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, int swz,
                        const float* __restrict__ col_scales, const float* __restrict__ tensor_amax,
                        float* __restrict__ tensor_scale_out) {
   __shared__ __align__(16) uint16_t tin[kTR * kTC];
   constexpr int OUT_PITCH = (MODE == MODE_NV ? kTR / 2 : kTR) + 16;
   __shared__ __align__(16) uint8_t tout[kTC * OUT_PITCH];
+  constexpr int fmt = FMT;
   const int tid = threadIdx.x;
   const int64_t c0 = (int64_t)blockIdx.x * kTC, r0 = (int64_t)blockIdx.y * kTR;
 
@@ -404,14 +381,13 @@ int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
 }
 
 // Grid for the item-based row-wise kernels: exactly one resident wave (as many CTAs of 256
-// threads per SM as the kernel's registers allow); the (row, chunk) items are dealt round-robin,
-// so every warp gets the same share and there is no tail wave.
+// threads per SM as the kernel's registers allow); the items are dealt round-robin, so every
+// warp gets the same share and there is no tail wave.  `per_cta` = items one CTA takes per pass.
 template <typename Kernel>
-int rowwise_grid(Kernel kernel, int64_t rows, int64_t cols) {
+int rowwise_grid(Kernel kernel, int64_t items, int per_cta) {
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
-  const int64_t items = rows * ((cols + 1023) / 1024);
-  const int64_t want = (items + kWarps - 1) / kWarps, cap = (int64_t)kNumSMs * per_sm;
+  const int64_t want = (items + per_cta - 1) / per_cta, cap = (int64_t)kNumSMs * per_sm;
   return (int)(want < cap ? want : cap);
 }
 
@@ -419,6 +395,33 @@ int zero_sf_pads(void* sf, int64_t outer, int64_t nblk, int layout, cudaStream_t
   if (layout == B200Q_SF_SWIZZLE_128x4 && ((outer & 127) || (nblk & 3)))
     B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(outer, nblk, layout), st));
   return B200Q_OK;
+}
+
+// Launch helpers: the kernels take the fp8 format and the load width as template arguments.
+template <int MODE, bool WIDE, int FMT>
+void launch_rowwise_block(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, uint8_t* codes, uint8_t* sf, int swz,
+                          const float* tensor_amax, float* tensor_scale_out, cudaStream_t st) {
+  auto kernel = rowwise_block_quant_kernel<MODE, WIDE, FMT>;
+  kernel<<<rowwise_grid(kernel, rows * (cols / 32), kThreads), kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, tensor_amax, tensor_scale_out);
+}
+template <int MODE>
+void launch_rowwise_block(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes, uint8_t* sf,
+                          int swz, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st) {
+  // 256-bit loads and stores need 32-byte aligned rows on both sides
+  const bool wide = aligned32(x) && aligned32(codes) && (ld & 15) == 0;
+#define B200Q_GO(W, F) launch_rowwise_block<MODE, W, F>(x, rows, cols, ld, codes, sf, swz, tensor_amax, tensor_scale_out, st)
+  if (MODE == MODE_NV || fmt == FMT_E4M3) { if (wide) B200Q_GO(true, FMT_E4M3); else B200Q_GO(false, FMT_E4M3); }
+  else { if (wide) B200Q_GO(true, FMT_E5M2); else B200Q_GO(false, FMT_E5M2); }
+#undef B200Q_GO
+}
+template <int MODE>
+void launch_transpose(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes, uint8_t* sf, int swz,
+                      const float* col_scales, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st) {
+  dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
+  if (MODE == MODE_NV || fmt == FMT_E4M3)
+    transpose_quant_kernel<MODE, FMT_E4M3><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out);
+  else
+    transpose_quant_kernel<MODE, FMT_E5M2><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out);
 }
 
 }  // namespace
@@ -466,7 +469,7 @@ int b200q_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, float* ama
   if ((rc = require_sm100())) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   B200Q_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), st));
-  amax_kernel<<<rowwise_grid(amax_kernel, rows, cols), kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, amax);
+  amax_kernel<<<rowwise_grid(amax_kernel, rows * ((cols + 1023) / 1024), kWarps), kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, amax);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -480,8 +483,13 @@ static int launch_rowwise_fp8(const uint16_t* x, int64_t rows, int64_t cols, int
   const int64_t nvec = (nv + wpr * 32 - 1) / (wpr * 32);
   const int64_t rpc = kWarps / wpr, want = (rows + rpc - 1) / rpc, cap = (int64_t)kNumSMs * 8;
   const int grid = (int)(want < cap ? want : cap);
-#define B200Q_LAUNCH(NV) \
-  rowwise_fp8_kernel<NV><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, fmt, codes, scales, tensor_amax, tensor_scale_out, wpr)
+#define B200Q_LAUNCH(NV)                                                                                                   \
+  do {                                                                                                                     \
+    if (fmt == FMT_E4M3)                                                                                                   \
+      rowwise_fp8_kernel<NV, FMT_E4M3><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr); \
+    else                                                                                                                   \
+      rowwise_fp8_kernel<NV, FMT_E5M2><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr); \
+  } while (0)
   if (nvec <= 1) B200Q_LAUNCH(1);
   else if (nvec <= 2) B200Q_LAUNCH(2);
   else if (nvec <= 4) B200Q_LAUNCH(4);
@@ -515,9 +523,7 @@ int b200q_quantize_fp8(const void* x, int64_t rows, int64_t cols, int64_t ld, in
   }
   amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, fmt);
   B200Q_CUDA(cudaGetLastError());
-  dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
-  transpose_quant_kernel<MODE_FP8><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes,
-                                                              nullptr, 0, scales, nullptr, nullptr);
+  launch_transpose<MODE_FP8>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, nullptr, 0, scales, nullptr, nullptr, st);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -534,9 +540,7 @@ int b200q_quantize_fp8_tensorwise(const void* x, int64_t rows, int64_t cols, int
   if (!transpose)
     return launch_rowwise_fp8((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, nullptr, tensor_amax, scale_out, st);
   if (rows & 15) return B200Q_ERR_SHAPE;
-  dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
-  transpose_quant_kernel<MODE_FP8><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes,
-                                                              nullptr, 0, nullptr, tensor_amax, scale_out);
+  launch_transpose<MODE_FP8>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, nullptr, 0, nullptr, tensor_amax, scale_out, st);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -554,19 +558,10 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   if ((rc = require_sm100())) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf, outer, contraction / 32, sf_layout, st))) return rc;
-  if (axis == 1) {
-    // 256-bit loads and stores need 32-byte aligned rows on both sides
-    if (aligned32(x) && aligned32(codes) && (ld & 15) == 0)
-      rowwise_block_quant_kernel<MODE_MX, true><<<rowwise_grid(rowwise_block_quant_kernel<MODE_MX, true>, rows, cols), kThreads, 0, st>>>(
-          (const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr);
-    else
-      rowwise_block_quant_kernel<MODE_MX, false><<<rowwise_grid(rowwise_block_quant_kernel<MODE_MX, false>, rows, cols), kThreads, 0, st>>>(
-          (const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr);
-  } else {
-    dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
-    transpose_quant_kernel<MODE_MX><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes,
-                                                               (uint8_t*)sf, sf_layout, nullptr, nullptr, nullptr);
-  }
+  if (axis == 1)
+    launch_rowwise_block<MODE_MX>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr, st);
+  else
+    launch_transpose<MODE_MX>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr, nullptr, st);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -584,18 +579,10 @@ int b200q_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   if ((rc = require_sm100())) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf, outer, contraction / 16, sf_layout, st))) return rc;
-  if (axis == 1) {
-    if (aligned32(x) && (ld & 15) == 0)
-      rowwise_block_quant_kernel<MODE_NV, true><<<rowwise_grid(rowwise_block_quant_kernel<MODE_NV, true>, rows, cols), kThreads, 0, st>>>(
-          (const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax, tensor_scale_out);
-    else
-      rowwise_block_quant_kernel<MODE_NV, false><<<rowwise_grid(rowwise_block_quant_kernel<MODE_NV, false>, rows, cols), kThreads, 0, st>>>(
-          (const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax, tensor_scale_out);
-  } else {
-    dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
-    transpose_quant_kernel<MODE_NV><<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes,
-                                                               (uint8_t*)sf, sf_layout, nullptr, tensor_amax, tensor_scale_out);
-  }
+  if (axis == 1)
+    launch_rowwise_block<MODE_NV>((const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax, tensor_scale_out, st);
+  else
+    launch_transpose<MODE_NV>((const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, tensor_amax, tensor_scale_out, st);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -90,6 +90,35 @@ def test_fused_permute_quantize_is_bit_exact(ops):
     assert torch.equal(sf_nat[want_rows], rs)
 
 
+def test_gather_and_swiglu_from_rows_that_are_only_16_byte_aligned(ops):
+    """Views whose start and pitch rule out 256-bit loads give the same bytes as aligned copies."""
+    x, logits, _, _ = R.inputs_moe(512, 256, 8, 2, 128)
+    top_i, _ = R.router_topk(logits, 2)
+    plan = ops.moe_permute_plan(top_i.cuda(), 8)
+    big = torch.zeros(512, 256 + 24, dtype=torch.bfloat16, device="cuda")
+    big[:, 8:264] = x.cuda()
+    view = big[:, 8:264]
+    assert view.data_ptr() % 32 == 16 and view.stride(0) % 16 == 8
+    for quant in (True, False):
+        a = ops.moe_gather(view, plan, quant)
+        b = ops.moe_gather(x.cuda(), plan, quant)
+        live = int(plan.num_tiles.item()) * 128
+        if quant:
+            n_sf = live // 128 * (256 // 32 // 4) * 512       # scale bytes of the live row tiles
+            assert torch.equal(a[0][:live], b[0][:live]) and torch.equal(a[1][:n_sf], b[1][:n_sf])
+        else:
+            assert torch.equal(a[:live], b[:live])
+    h = torch.zeros(384, 512 + 24, dtype=torch.bfloat16, device="cuda")
+    hv = h[:, 8:520]
+    hv.copy_(2.0 * torch.randn(384, 512, device="cuda"))
+    for quant in (True, False):
+        a, b = ops.swiglu(hv, quant), ops.swiglu(hv.contiguous(), quant)
+        if quant:
+            assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+        else:
+            assert torch.equal(a, b)
+
+
 def _grouped_ref(a_deq, w_deq, counts):
     out = torch.zeros(a_deq.shape[0], w_deq.shape[1], device=a_deq.device)
     s = 0

@@ -167,6 +167,25 @@ def test_strided_input_is_read_in_place(ops):
     assert torch.equal(codes.cpu(), rc) and torch.equal(sf.cpu(), rs.reshape(-1))
 
 
+def test_rows_that_are_only_16_byte_aligned(ops):
+    """Pitch and start that rule out the 256-bit loads: the 128-bit path must give the same bytes."""
+    x = CASES["x"]
+    big = torch.zeros(x.shape[0], x.shape[1] + 24, dtype=torch.bfloat16)
+    big[:, 8: 8 + x.shape[1]] = x
+    view = big.cuda()[:, 8: 8 + x.shape[1]]
+    assert view.data_ptr() % 32 == 16 and view.stride(0) % 16 == 8
+    for dt in (E4, E5):
+        codes, sf = ops.quantize_mxfp8(view, 1, dt, 0)
+        rc, rs = R.quantize_mxfp8(x, -1, dt)
+        assert torch.equal(codes.cpu(), rc) and torch.equal(sf.cpu(), rs.reshape(-1))
+        c8, s8 = ops.quantize_fp8(view, dt, 1)
+        r8, rs8 = R.quantize_fp8(x, dt, dim=-1)
+        assert torch.equal(c8.cpu(), r8.view(torch.uint8)) and torch.equal(s8.cpu(), rs8.reshape(-1))
+    packed, sf, ts = ops.quantize_nvfp4(view, 1, None, 0)
+    rp, rs, rt = R.quantize_nvfp4(x, -1)
+    assert torch.equal(packed.cpu(), rp) and torch.equal(sf.cpu(), rs.reshape(-1)) and ts.item() == rt.item()
+
+
 def test_full_size_properties(ops):
     """Benchmark-size square operand (8192 x 8192): properties that need no CPU pass over the
     data — never clips, scale is tight, transposing kernel == row-wise kernel on the transpose."""
