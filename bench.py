@@ -207,8 +207,8 @@ def cpu_moe_sample(t, d, inter, ts=1024):
 
 def run_moe(args, t, d, inter, rank, world, local):
     """MoE block workload: one step = permute plan, gather fused with MXFP8, quantize both expert
-    weight stacks, grouped GEMM, SwiGLU + MXFP8, grouped GEMM, weighted unpermute (what
-    SparseMoEBlock.forward does after the router).  Throughput counts the two grouped GEMMs'
+    weight stacks, grouped GEMM with the SwiGLU + MXFP8 epilogue, grouped GEMM, weighted unpermute
+    (what SparseMoEBlock.forward does after the router).  Throughput counts the two grouped GEMMs'
     2*R*N*K FLOP (pad rows not counted)."""
     from oracle import restate as R
     from pretrain_b200 import build, ops
@@ -222,18 +222,17 @@ def run_moe(args, t, d, inter, rank, world, local):
     n_pairs = t * k
     flops = 2.0 * n_pairs * (2 * inter * d + d * inter)
     ev = lambda marks: None if marks is None else _mark(marks)
+    row_map = ops.glu_row_map(e, inter, x.device)      # gate / up rows interleaved for the SwiGLU epilogue
 
     def step(marks=None):
         ev(marks)
         plan = ops.moe_permute_plan(top_i, e)
         a, sfa = ops.moe_gather(x, plan, True)
         ev(marks)
-        wq1, wsf1 = ops.quantize_mxfp8(w_gu.view(e * 2 * inter, d), 1)
+        wq1, wsf1 = ops.quantize_mxfp8_rowmap(w_gu.view(e * 2 * inter, d), row_map)
         wq2, wsf2 = ops.quantize_mxfp8(w_d.view(e * d, inter), 1)
         ev(marks)
-        h = ops.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, 2 * inter)
-        ev(marks)
-        hq, hsf = ops.swiglu(h, True)
+        hq, hsf = ops.grouped_gemm_mxfp8_swiglu(a, sfa, wq1, wsf1, plan, 2 * inter)
         ev(marks)
         y = ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, d)
         ev(marks)
@@ -255,9 +254,9 @@ def run_moe(args, t, d, inter, rank, world, local):
         torch.cuda.synchronize()
     ops.device_status()
     ms_step = t0.elapsed_time(t1) / args.steps
-    seg = [marks[i:i + 7] for i in range(0, len(marks), 7)]
+    seg = [marks[i:i + 6] for i in range(0, len(marks), 6)]
     avg = lambda i: sum(sg[i].elapsed_time(sg[i + 1]) for sg in seg) / len(seg)
-    permute_ms, wquant_ms, gemm1_ms, swiglu_ms, gemm2_ms, unperm_ms = (avg(i) for i in range(6))
+    permute_ms, wquant_ms, gemm1_ms, gemm2_ms, unperm_ms = (avg(i) for i in range(5))
 
     blk = SparseMoEBlock(d, intermediate_size=inter, n_routed_experts=e, n_routed_experts_per_token=k, router_score_fn="softmax").cuda()
     with torch.no_grad():
@@ -298,13 +297,14 @@ def run_moe(args, t, d, inter, rank, world, local):
             "clocks": clk.summary(),
             "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2},
-            "gpu_launches": 10 * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<mxfp8> (grouped, 2 launches)", "achieved": achieved, "peak": peak,
+            "gpu_launches": 9 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<mxfp8> (grouped, 2 launches; the first one's epilogue does "
+                                                       "SwiGLU + MXFP8)", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"2 x bf16_tflops_sustained, {peaks['source']}",
-                         "frac_of_nominal": achieved / 4500.0, "nominal_peak": 4500.0, "traffic": None, "kernel_ms": gemm_ms},
+                         "frac_of_nominal": achieved / 4500.0, "nominal_peak": 4500.0, "traffic": None, "kernel_ms": gemm_ms,
+                         "gemm1_swiglu_ms": gemm1_ms, "gemm2_ms": gemm2_ms},
             "permute": dict(bound="hbm", **hbm(n_pairs * d * 3.03125, permute_ms), note="plan kernels + gather fused with MXFP8"),
             "weight_quantize": dict(bound="hbm", **hbm((w_gu.numel() + w_d.numel()) * 3.03125, wquant_ms)),
-            "swiglu_quantize": dict(bound="hbm", **hbm(n_pairs * (2 * inter * 2 + inter * 1.03125), swiglu_ms)),
             "unpermute": dict(bound="hbm", **hbm(n_pairs * d * 2 + t * d * 2, unperm_ms))}
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

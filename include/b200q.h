@@ -76,6 +76,14 @@ int b200q_quantize_fp8_tensorwise(const void* x, int64_t rows, int64_t cols, int
 int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int fmt,
                          void* codes, void* sf, int sf_layout, void* stream);
 
+/* Row-wise b200q_quantize_mxfp8 (axis = 1) that writes input row r as output row dst_row[r]
+ * (codes and scale factors alike); dst_row is a permutation of 0 .. rows-1 in device memory.
+ * Used to store gated-MLP weights (src/layers/mlp.py:404-411, expert_gate_up) in the interleaved
+ * row order the SwiGLU epilogue reads, without a copy of the bf16 weights. */
+int b200q_quantize_mxfp8_rowmap(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt,
+                                const int32_t* dst_row, void* codes, void* sf, int sf_layout,
+                                void* stream);
+
 /* NVFP4: 16-element blocks, packed E2M1 codes (element 2i in the low nibble), one E4M3 scale
  * byte per block and one fp32 scale per tensor derived from *tensor_amax (device):
  * s_t = max(amax/2688, 1e-12), written to *tensor_scale_out.  No counterpart in the reference
@@ -193,6 +201,26 @@ int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const vo
  * (quantize = 0) written as bf16.  I % 32 == 0. */
 int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantize, int fmt, void* out,
                  void* sf, void* stream);
+
+/* The first GEMM of a gated MLP with the activation and the re-quantization done in its epilogue:
+ * the step "h = grouped_mm(x, w_in); h = silu_glu(gate, up)" (src/layers/mlp.py:89-94,
+ * src/layers/activation.py:80-81) followed by the MXFP8 quantization of h that the second GEMM
+ * needs, without the bf16 [M, 2I] intermediate ever being written.  Same arithmetic as
+ * b200q_(grouped_)gemm_mxfp8 -> b200q_swiglu(quantize = 1): accumulators rounded to bf16, SwiGLU in
+ * the reference's bf16 steps, one E8M0 scale per 32 outputs; results are bit-identical to that chain.
+ *
+ * B must hold the N = 2I weight rows (per expert) in GLU-INTERLEAVED order: rows 64j .. 64j+31 are
+ * gate rows 32j .. 32j+31 and rows 64j+32 .. 64j+63 are the up rows of the same outputs
+ * (b200q_quantize_mxfp8_rowmap writes them so).  N % 64 == 0.
+ * H: E4M3 codes [M, N/2], pitch ldh bytes (ldh % 16 == 0); sfH: 128x4-tiled scale factors over
+ * (M, N/64), b200q_sf_bytes(M, N/64, B200Q_SF_SWIZZLE_128x4) bytes. */
+int b200q_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
+                            const void* sfB, int64_t M, int64_t N, int64_t K, void* H, int64_t ldh,
+                            void* sfH, void* stream);
+int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
+                                    const void* sfB, const int32_t* tile_expert,
+                                    const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
+                                    int64_t K, void* H, int64_t ldh, void* sfH, void* stream);
 
 /* Weighted unpermute (src/layers/mlp.py:472-477): out[t, :] = sum_j w[t, j] * y[row_of[t*k+j], :],
  * accumulated in fp32 and rounded once to bf16.  y bf16 [padded_rows, D] pitch ldy; w bf16 [T, k]. */

@@ -109,6 +109,26 @@ __device__ __forceinline__ int mx_quant_block32(const uint4 (&v)[4], uint32_t (&
   return e;
 }
 
+__device__ __forceinline__ float bf16_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+
+// h = bf16(bf16(silu(gate)) * up) for 8 (gate, up) pairs packed as bf16: the roundings of the
+// reference's bf16 tensor ops.  silu(x) = x / (1 + e^-x) with the hardware exponential and
+// reciprocal: within 2 fp32 ulp, far inside the bf16 rounding that follows.
+__device__ __forceinline__ uint4 swiglu8(const uint4& vg, const uint4& vu) {
+  float a[8], b[8];
+  unpack8(vg, a);
+  unpack8(vu, b);
+  uint32_t h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float s0 = bf16_round(__fdividef(a[2 * i], 1.f + __expf(-a[2 * i])));
+    const float s1 = bf16_round(__fdividef(a[2 * i + 1], 1.f + __expf(-a[2 * i + 1])));
+    __nv_bfloat162 p = __floats2bfloat162_rn(s0 * b[2 * i], s1 * b[2 * i + 1]);
+    h[i] = *reinterpret_cast<uint32_t*>(&p);
+  }
+  return make_uint4(h[0], h[1], h[2], h[3]);
+}
+
 // Byte offset of the scale factor of (row, block kb) in the 128x4-tiled layout; kt = K-tiles per row tile.
 __device__ __forceinline__ int64_t sf_swizzled(int64_t row, int kb, int64_t kt) {
   return ((row >> 7) * kt + (kb >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3);

@@ -99,7 +99,13 @@ struct GemmParams {
   int64_t sfb_groups;      // 128-row groups in the SF buffer of B
   const int32_t* tile_expert;   // grouped: expert of every 128-row tile of A; null otherwise
   const int32_t* num_tiles;     // grouped: device count of row tiles in use
+  GluOut glu;                   // EPI_GLU: where the SwiGLU + MXFP8 epilogue writes
 };
+
+enum { EPI_BF16 = 0, EPI_GLU = 1 };
+// Threads per CTA: producer warp, MMA warp and one (bf16 output) or two (SwiGLU epilogue) groups
+// of four epilogue warps.
+__host__ __device__ constexpr int gemm_threads(int epi) { return epi == EPI_GLU ? 320 : 192; }
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m, int& n) {
   constexpr int GM = 16;   // m-blocks per raster group: concurrent CTAs share A and B tiles through L2
@@ -112,8 +118,8 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m,
 }
 
 
-template <int KIND, int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int KIND, int BN, int EPI>
+__global__ void __launch_bounds__(gemm_threads(EPI), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ OutMaps outs, const GemmParams p) {
   using C = Cfg<KIND, BN>;
@@ -142,13 +148,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // loaded) multiply the zero-filled operand tail by a finite scale.
     for (int s = 0; s < C::STAGES; ++s) {
       uint32_t* sfz = reinterpret_cast<uint32_t*>(smem_gen + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
-      for (int i = threadIdx.x; i < (C::SFA_BYTES + C::SFB_BYTES) / 4; i += kGemmThreads) sfz[i] = 0;
+      for (int i = threadIdx.x; i < (C::SFA_BYTES + C::SFB_BYTES) / 4; i += gemm_threads(EPI)) sfz[i] = 0;
     }
     ptx::fence_proxy_async();
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 4); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), gemm_threads(EPI) / 32 - 2); }
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_a);
@@ -275,11 +281,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     uint8_t* epi_g = smem_gen + C::EPI_OFF + q * C::EPI_BUFS * EPI_BLOCK_BYTES;
     int buf = 0;
     int acc = 0; uint32_t acc_phase = 0;
+    int tile_iter = 0;
     bool ok = true;
     float alpha = 1.f;
     if (KIND == KIND_NV) alpha = __ldg(p.scale_a) * __ldg(p.scale_b);
     constexpr int NBLK = BN / EPI_COLS;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
       int m_blk, n_blk;
       tile_coords(t, num_m, p.num_n, m_blk, n_blk);
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase) || *abort_flag) { ok = false; break; }
@@ -296,13 +303,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       // strip has been read (overlapped) or after the last block has been read (otherwise).
       constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;
       const uint32_t release_bar = tempty_bar(acc);
-      epilogue_tile<KIND == KIND_F8, NBLK, C::EPI_BUFS, RELEASE_AFTER>(
-          taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
-          [&]() {
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(release_bar);
-          });
+      auto release = [&]() {
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(release_bar);
+      };
+      if (EPI == EPI_GLU)
+        // the two warp groups swap block sets from tile to tile, so an odd block count evens out
+        epilogue_tile_glu<NBLK, RELEASE_AFTER, 2>(taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, p.M,
+                                                  p.N, p.glu, release);
+      else
+        epilogue_tile<KIND == KIND_F8, NBLK, C::EPI_BUFS, RELEASE_AFTER>(
+            taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
+            release);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (lane == 0) ptx::bulk_wait<0>();           // all stores of this warp have landed
@@ -376,7 +389,7 @@ int make_out_maps(OutMaps* om, const OutSpec& outs, int64_t M, int64_t N, int64_
   return B200Q_OK;
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, int EPI = EPI_BF16>
 int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, GemmParams p, cudaStream_t st) {
   using C = Cfg<KIND, BN>;
   const int64_t row_bytes = KIND == KIND_NV ? p.K / 2 : p.K;
@@ -386,17 +399,22 @@ int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t 
   // operands: byte matrices [rows, row_bytes], box = 128 bytes x tile rows, 128-byte swizzle
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, p.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, b_rows, row_bytes, BKB, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = make_out_maps(&md, D, p.M, p.N, ldd))) return rc;
+  if (EPI == EPI_GLU) {
+    md.count = 0;                       // no bf16 output: the epilogue writes codes and scale bytes itself
+    for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
+  } else if ((rc = make_out_maps(&md, D, p.M, p.N, ldd))) {
+    return rc;
+  }
   p.num_m = (int)((p.M + BM - 1) / BM);
   p.num_n = (int)((p.N + BN - 1) / BN);
   p.num_k = (int)((row_bytes + BKB - 1) / BKB);
   const int64_t nblk = KIND == KIND_MX ? p.K / 32 : p.K / 16;
   p.sf_kt = (int)((nblk + 3) / 4);
   p.sfb_groups = (b_rows + 127) / 128;
-  B200Q_CUDA(cudaFuncSetAttribute(gemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  B200Q_CUDA(cudaFuncSetAttribute(gemm_kernel<KIND, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < kNumSMs ? tiles : kNumSMs;
-  gemm_kernel<KIND, BN><<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(ma, mb, md, p);
+  gemm_kernel<KIND, BN, EPI><<<grid, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, md, p);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -442,6 +460,40 @@ int dispatch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_
     case 256: return launch<KIND, 256>(A, B, D, ldd, b_rows, p, st);
     default: return B200Q_ERR_INVALID_ARG;
   }
+}
+
+// MXFP8 GEMM with the SwiGLU + MXFP8 epilogue (one-CTA kernel; every tile width is a whole number
+// of 64-column epilogue blocks).
+int dispatch_glu(const void* A, const void* B, int64_t b_rows, const GemmParams& p, cudaStream_t st) {
+  const int bn = g_force_bn ? g_force_bn : choose_bn<KIND_MX>(p.M, p.N, p.K);
+  const OutSpec none = {};
+  switch (bn) {
+    case 128: return launch<KIND_MX, 128, EPI_GLU>(A, B, none, 0, b_rows, p, st);
+    case 192: return launch<KIND_MX, 192, EPI_GLU>(A, B, none, 0, b_rows, p, st);
+    case 256: return launch<KIND_MX, 256, EPI_GLU>(A, B, none, 0, b_rows, p, st);
+    default: return B200Q_ERR_INVALID_ARG;
+  }
+}
+
+// Argument checks and the zeroing of scale-factor pad bytes shared by the two SwiGLU entry points.
+int prepare_glu(GemmParams* p, const void* A, const void* sfA, const void* B, const void* sfB, int a_fmt, int b_fmt, int64_t M,
+                int64_t N, int64_t K, void* H, int64_t ldh, void* sfH, bool zero_pads, cudaStream_t st) {
+  if (A == nullptr || B == nullptr || sfA == nullptr || sfB == nullptr || H == nullptr || sfH == nullptr || M <= 0 || N <= 0 ||
+      K <= 0 || ldh < N / 2 || ((a_fmt | b_fmt) & ~1))
+    return B200Q_ERR_INVALID_ARG;
+  if ((K & 31) || (N & 63) || (ldh & 15)) return B200Q_ERR_SHAPE;
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B200Q_ERR_SHAPE;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(H) || !aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  const int64_t hblk = N / 64;
+  if (zero_pads && ((M & 127) || (hblk & 3)))
+    B200Q_CUDA(cudaMemsetAsync(sfH, 0, (size_t)b200q_sf_bytes(M, hblk, B200Q_SF_SWIZZLE_128x4), st));
+  *p = GemmParams{};
+  p->sfa = (const uint8_t*)sfA; p->sfb = (const uint8_t*)sfB; p->a_fmt = a_fmt; p->b_fmt = b_fmt;
+  p->M = M; p->N = N; p->K = K;
+  p->glu.codes = (uint8_t*)H; p->glu.ldh = ldh; p->glu.sf = (uint8_t*)sfH; p->glu.kt = (hblk + 3) / 4;
+  return B200Q_OK;
 }
 
 // Destination list of a fused GEMM + all-gather: rows [rank*M, rank*M + M) of every rank's gathered
@@ -531,6 +583,26 @@ int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const vo
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   p.M = padded_rows; p.N = N; p.K = K; p.tile_expert = tile_expert; p.num_tiles = num_tiles;
   return dispatch<KIND_MX>(A, B, one_output(D), ldd, (int64_t)E * N, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
+                            int64_t N, int64_t K, void* H, int64_t ldh, void* sfH, void* stream) {
+  GemmParams p;
+  int rc = prepare_glu(&p, A, sfA, B, sfB, a_fmt, b_fmt, M, N, K, H, ldh, sfH, true, (cudaStream_t)stream);
+  if (rc) return rc;
+  return dispatch_glu(A, B, N, p, (cudaStream_t)stream);
+}
+
+int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB,
+                                    const int32_t* tile_expert, const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
+                                    int64_t K, void* H, int64_t ldh, void* sfH, void* stream) {
+  if (tile_expert == nullptr || num_tiles == nullptr || E <= 0) return B200Q_ERR_INVALID_ARG;
+  if ((padded_rows & 127) || (int64_t)E * N > INT32_MAX) return B200Q_ERR_SHAPE;
+  GemmParams p;
+  int rc = prepare_glu(&p, A, sfA, B, sfB, a_fmt, b_fmt, padded_rows, N, K, H, ldh, sfH, true, (cudaStream_t)stream);
+  if (rc) return rc;
+  p.tile_expert = tile_expert; p.num_tiles = num_tiles;
+  return dispatch_glu(A, B, (int64_t)E * N, p, (cudaStream_t)stream);
 }
 
 int b200q_gemm_fp8_allgather(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a, int a_scale_is_scalar,

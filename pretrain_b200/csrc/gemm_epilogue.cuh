@@ -93,3 +93,64 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t 
     }
   }
 }
+
+// ---- SwiGLU + MXFP8 epilogue ----------------------------------------------------------------------
+// For a GEMM whose B rows come in the order "32 gate rows, then the 32 up rows of the same 32
+// outputs": every 64-column accumulator block holds gate[0..32) | up[0..32) of one 32-wide block
+// of h = silu(gate) * up, and a thread (one accumulator row) holds that whole block - exactly one
+// MXFP8 block along the next GEMM's contraction dimension.  The thread rounds the accumulators to
+// bf16 (the reference's GEMM output dtype), applies the same SwiGLU arithmetic as the stand-alone
+// kernel, quantizes, and writes 32 code bytes and one scale byte straight to global memory: the
+// bf16 [M, 2I] intermediate never exists.
+struct GluOut {
+  uint8_t* codes;   // [M, N/2] E4M3 codes, pitch ldh bytes
+  int64_t ldh;
+  uint8_t* sf;      // 128x4-tiled E8M0 scale factors over (M, N/64)
+  int64_t kt;       // K-tiles per row tile of that layout
+};
+
+// Two warps share each tensor-memory lane quarter here (the arithmetic per block is long):
+// warp group `grp` of NGRP takes the blocks whose walking index i has i % NGRP == grp, and hands
+// the accumulator back once ITS blocks among the first RELEASE_AFTER + 1 have been read.
+template <int NBLK, int RELEASE_AFTER, int NGRP, class Release>
+__device__ __forceinline__ void epilogue_tile_glu(uint32_t taddr, bool rev, int grp, int64_t row, int64_t col0, int64_t M,
+                                                  int64_t N, const GluOut& out, Release release) {
+  auto emit = [&](int c, const uint32_t (&r)[64]) {
+    uint4 h[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint4 vg = make_uint4(pack_bf16(u2f(r[8 * u]), u2f(r[8 * u + 1])), pack_bf16(u2f(r[8 * u + 2]), u2f(r[8 * u + 3])),
+                                  pack_bf16(u2f(r[8 * u + 4]), u2f(r[8 * u + 5])), pack_bf16(u2f(r[8 * u + 6]), u2f(r[8 * u + 7])));
+      const uint4 vu = make_uint4(pack_bf16(u2f(r[32 + 8 * u]), u2f(r[33 + 8 * u])), pack_bf16(u2f(r[34 + 8 * u]), u2f(r[35 + 8 * u])),
+                                  pack_bf16(u2f(r[36 + 8 * u]), u2f(r[37 + 8 * u])), pack_bf16(u2f(r[38 + 8 * u]), u2f(r[39 + 8 * u])));
+      h[u] = swiglu8(vg, vu);
+    }
+    uint32_t o[8];
+    const int e = mx_quant_block32<FMT_E4M3>(h, o);
+    if (row < M) {
+      const int64_t hb = (col0 + c * EPI_COLS) >> 6;   // 32-wide block of h along the row
+      uint4* dst = reinterpret_cast<uint4*>(out.codes + row * out.ldh + hb * 32);
+      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      out.sf[sf_swizzled(row, (int)hb, out.kt)] = (uint8_t)(e + 127);
+    }
+  };
+
+  // last walking index <= RELEASE_AFTER that belongs to this group (-1: none)
+  const int my_last = RELEASE_AFTER - ((RELEASE_AFTER - grp) % NGRP + NGRP) % NGRP;
+  if (my_last < 0) release();
+  uint32_t r[64];
+  // not unrolled: one copy of the (long) block body keeps the epilogue inside the instruction cache
+#pragma unroll 1
+  for (int i = 0; i < NBLK; ++i) {
+    if (i % NGRP != grp) continue;                        // warp-uniform
+    const int c = rev ? NBLK - 1 - i : i;
+    const bool valid = col0 + c * EPI_COLS < N;           // warp-uniform
+    if (valid) {
+      tmem_ld64(taddr + c * EPI_COLS, r);
+      ptx::tmem_ld_wait();
+    }
+    if (i == my_last) release();
+    if (valid) emit(c, r);
+  }
+}

@@ -181,26 +181,6 @@ moe_gather_kernel(const uint16_t* __restrict__ x, int64_t D, int64_t ld, const i
   }
 }
 
-__device__ __forceinline__ float bf16_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
-
-// h = bf16(bf16(silu(gate)) * up) for 8 (gate, up) pairs packed as bf16: the roundings of the
-// reference's bf16 tensor ops.  silu(x) = x / (1 + e^-x) with the hardware exponential and
-// reciprocal: within 2 fp32 ulp, far inside the bf16 rounding that follows.
-__device__ __forceinline__ uint4 swiglu8(const uint4& vg, const uint4& vu) {
-  float a[8], b[8];
-  unpack8(vg, a);
-  unpack8(vu, b);
-  uint32_t h[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float s0 = bf16_round(__fdividef(a[2 * i], 1.f + __expf(-a[2 * i])));
-    const float s1 = bf16_round(__fdividef(a[2 * i + 1], 1.f + __expf(-a[2 * i + 1])));
-    __nv_bfloat162 p = __floats2bfloat162_rn(s0 * b[2 * i], s1 * b[2 * i + 1]);
-    h[i] = *reinterpret_cast<uint32_t*>(&p);
-  }
-  return make_uint4(h[0], h[1], h[2], h[3]);
-}
-
 // ---- SwiGLU (+ MXFP8) between the two grouped GEMMs -------------------------------------------------
 // Input rows are [gate (I) | up (I)]; work item = 32 consecutive outputs of one row, one thread.
 template <int QUANT, bool WIDE, int FMT>

@@ -84,7 +84,8 @@ template <int MODE, bool WIDE, int FMT>
 __global__ void __launch_bounds__(kThreads)
 rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                            uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, int swz,
-                           const float* __restrict__ tensor_amax, float* __restrict__ tensor_scale_out) {
+                           const float* __restrict__ tensor_amax, float* __restrict__ tensor_scale_out,
+                           const int32_t* __restrict__ dst_row) {
   constexpr int BS = MODE == MODE_MX ? 32 : 16;
   const int64_t nblk = cols / BS;
   float s_t = 0.f, rcp_st = 0.f;
@@ -96,12 +97,12 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
   const int runs = (int)(cols >> 5);            // 32-element runs per row
   const int64_t kt = (nblk + 3) >> 2;
   for (ItemWalker w((int64_t)blockIdx.x * kThreads + threadIdx.x, (int64_t)gridDim.x * kThreads, runs); w.row < rows; w.next()) {
-    const int64_t row = w.row;
     const int c = w.chunk << 5;
-    const uint16_t* xp = x + row * ld + c;
+    const uint16_t* xp = x + w.row * ld + c;
     uint4 v[4];
     ld_nc_32B<WIDE>(xp, v[0], v[1]);
     ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
+    const int64_t row = dst_row ? (int64_t)__ldg(dst_row + w.row) : w.row;   // output row (codes and scale factors)
     if (MODE == MODE_MX) {
       uint32_t o[8];
       const int e = mx_quant_block32<FMT>(v, o);
@@ -400,16 +401,18 @@ int zero_sf_pads(void* sf, int64_t outer, int64_t nblk, int layout, cudaStream_t
 // Launch helpers: the kernels take the fp8 format and the load width as template arguments.
 template <int MODE, bool WIDE, int FMT>
 void launch_rowwise_block(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, uint8_t* codes, uint8_t* sf, int swz,
-                          const float* tensor_amax, float* tensor_scale_out, cudaStream_t st) {
+                          const float* tensor_amax, float* tensor_scale_out, const int32_t* dst_row, cudaStream_t st) {
   auto kernel = rowwise_block_quant_kernel<MODE, WIDE, FMT>;
-  kernel<<<rowwise_grid(kernel, rows * (cols / 32), kThreads), kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, tensor_amax, tensor_scale_out);
+  kernel<<<rowwise_grid(kernel, rows * (cols / 32), kThreads), kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, tensor_amax,
+                                                                                 tensor_scale_out, dst_row);
 }
 template <int MODE>
 void launch_rowwise_block(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes, uint8_t* sf,
-                          int swz, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st) {
+                          int swz, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st,
+                          const int32_t* dst_row = nullptr) {
   // 256-bit loads and stores need 32-byte aligned rows on both sides
   const bool wide = aligned32(x) && aligned32(codes) && (ld & 15) == 0;
-#define B200Q_GO(W, F) launch_rowwise_block<MODE, W, F>(x, rows, cols, ld, codes, sf, swz, tensor_amax, tensor_scale_out, st)
+#define B200Q_GO(W, F) launch_rowwise_block<MODE, W, F>(x, rows, cols, ld, codes, sf, swz, tensor_amax, tensor_scale_out, dst_row, st)
   if (MODE == MODE_NV || fmt == FMT_E4M3) { if (wide) B200Q_GO(true, FMT_E4M3); else B200Q_GO(false, FMT_E4M3); }
   else { if (wide) B200Q_GO(true, FMT_E5M2); else B200Q_GO(false, FMT_E5M2); }
 #undef B200Q_GO
@@ -562,6 +565,24 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
     launch_rowwise_block<MODE_MX>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr, st);
   else
     launch_transpose<MODE_MX>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr, nullptr, st);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_quantize_mxfp8_rowmap(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt, const int32_t* dst_row,
+                                void* codes, void* sf, int sf_layout, void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes == nullptr || sf == nullptr || dst_row == nullptr || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2) ||
+      (sf_layout != B200Q_SF_NATURAL && sf_layout != B200Q_SF_SWIZZLE_128x4))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
+  if ((cols & 31) || rows > INT32_MAX) return B200Q_ERR_SHAPE;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((rc = zero_sf_pads(sf, rows, cols / 32, sf_layout, st))) return rc;
+  launch_rowwise_block<MODE_MX>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr, st,
+                                dst_row);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -52,20 +52,36 @@ def _expert_of_padded_row(plan) -> torch.Tensor:
     return plan.tile_expert.clamp_min(0).repeat_interleave(128).long()
 
 
+_ROW_MAPS: dict = {}
+
+
+def _glu_row_map(e: int, inter: int, device) -> torch.Tensor:
+    key = (e, inter, str(device))
+    if key not in _ROW_MAPS:
+        _ROW_MAPS[key] = ops.glu_row_map(e, inter, device)
+    return _ROW_MAPS[key]
+
+
 def _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in=None, b_down=None):
     """Both grouped GEMMs and the activation on the padded layout; returns (padded_rows, D_out) bf16."""
     n1, n2 = w_in.shape[1], w_down.shape[1]
-    wq1, wsf1 = _quantize_expert_weights(w_in)
     wq2, wsf2 = _quantize_expert_weights(w_down)
     e = w_in.shape[0]
-    h = ops.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, wq1.shape[0] // e)[:, :n1]
-    if b_in is not None:
-        h = h + b_in.to(h.dtype)[_expert_of_padded_row(plan)]
-    if gated and act_fn is silu_glu:
-        hq, hsf = ops.swiglu(h, True)                     # fused silu(gate)*up + MXFP8
+    if gated and act_fn is silu_glu and b_in is None and n1 % 128 == 0:
+        # SwiGLU and the re-quantization run in the first GEMM's epilogue: the weights are stored with
+        # gate and up rows interleaved so that a thread of the epilogue holds a whole block of h
+        wq1, wsf1 = ops.quantize_mxfp8_rowmap(w_in.reshape(-1, w_in.shape[2]), _glu_row_map(e, n1 // 2, w_in.device))
+        hq, hsf = ops.grouped_gemm_mxfp8_swiglu(a, sfa, wq1, wsf1, plan, n1)
     else:
-        act = act_fn(*h.chunk(2, dim=-1)) if gated else act_fn(h)
-        hq, hsf = ops.quantize_mxfp8(act.contiguous(), 1)
+        wq1, wsf1 = _quantize_expert_weights(w_in)
+        h = ops.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, wq1.shape[0] // e)[:, :n1]
+        if b_in is not None:
+            h = h + b_in.to(h.dtype)[_expert_of_padded_row(plan)]
+        if gated and act_fn is silu_glu:
+            hq, hsf = ops.swiglu(h, True)                     # fused silu(gate)*up + MXFP8
+        else:
+            act = act_fn(*h.chunk(2, dim=-1)) if gated else act_fn(h)
+            hq, hsf = ops.quantize_mxfp8(act.contiguous(), 1)
     out = ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, wq2.shape[0] // e)[:, :n2]
     if b_down is not None:
         out = out + b_down.to(out.dtype)[_expert_of_padded_row(plan)]

@@ -86,6 +86,33 @@ def quantize_mxfp8(x: torch.Tensor, axis: int = 1, fmt=E4M3, layout: int = SF_SW
     return codes, sf
 
 
+def glu_row_map(n_groups: int, inter: int, device) -> torch.Tensor:
+    """dst_row for weights stacked as n_groups x [gate (inter rows); up (inter rows)]: the
+    interleaved order the SwiGLU epilogue reads (32 gate rows, then the 32 up rows of the same
+    outputs).  inter % 32 == 0."""
+    if inter % 32:
+        raise ValueError("intermediate size must be a multiple of 32")
+    j = torch.arange(inter, device=device)
+    gate = (j // 32) * 64 + j % 32
+    one = torch.cat([gate, gate + 32])
+    base = torch.arange(n_groups, device=device).unsqueeze(1) * (2 * inter)
+    return (base + one.unsqueeze(0)).reshape(-1).to(torch.int32)
+
+
+def quantize_mxfp8_rowmap(x: torch.Tensor, dst_row: torch.Tensor, fmt=E4M3, layout: int = SF_SWIZZLED):
+    """Row-wise MXFP8 of x with input row r written as output row dst_row[r] (a permutation)."""
+    x = _mat(x)
+    rows, cols = x.shape
+    if dst_row.numel() != rows or dst_row.dtype != torch.int32 or not dst_row.is_cuda:
+        raise ValueError("dst_row: one int32 per row, on the GPU")
+    codes = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(rows, cols // 32, layout), dtype=torch.uint8, device=x.device)
+    _lib.check(_lib.load().b200q_quantize_mxfp8_rowmap(x.data_ptr(), rows, cols, x.stride(0), fmt_of(fmt), dst_row.data_ptr(),
+                                                       codes.data_ptr(), sf.data_ptr(), layout, _stream()),
+               "b200q_quantize_mxfp8_rowmap")
+    return codes, sf
+
+
 def quantize_nvfp4(x: torch.Tensor, axis: int = 1, tensor_amax: torch.Tensor | None = None, layout: int = SF_SWIZZLED):
     """Returns (packed uint8 [outer, C/2], sf uint8 flat buffer, tensor_scale fp32 [1])."""
     x = _mat(x)
@@ -250,6 +277,32 @@ def grouped_gemm_mxfp8(a_codes, a_sf, b_codes, b_sf, plan: MoEPlan, n: int, a_fm
                                                     plan.num_tiles.data_ptr(), rows, plan.n_experts, n, k, d.data_ptr(),
                                                     d.stride(0), _stream()), "b200q_grouped_gemm_mxfp8")
     return d
+
+
+def gemm_mxfp8_swiglu(a_codes, a_sf, b_codes, b_sf, a_fmt=E4M3, b_fmt=E4M3):
+    """MXFP8 (codes [M, N/2], sf) of silu(gate) * up where [gate | up] = A . B^T and B's rows are in
+    the interleaved order of glu_row_map: the GEMM, the activation and the quantization in one kernel."""
+    m, k = a_codes.shape
+    n = b_codes.shape[0]
+    h = torch.empty(m, n // 2, dtype=torch.uint8, device=a_codes.device)
+    sf = torch.empty(sf_bytes(m, n // 64), dtype=torch.uint8, device=a_codes.device)
+    _lib.check(_lib.load().b200q_gemm_mxfp8_swiglu(a_codes.data_ptr(), fmt_of(a_fmt), a_sf.data_ptr(), b_codes.data_ptr(),
+                                                   fmt_of(b_fmt), b_sf.data_ptr(), m, n, k, h.data_ptr(), h.stride(0),
+                                                   sf.data_ptr(), _stream()), "b200q_gemm_mxfp8_swiglu")
+    return h, sf
+
+
+def grouped_gemm_mxfp8_swiglu(a_codes, a_sf, b_codes, b_sf, plan: MoEPlan, n: int, a_fmt=E4M3, b_fmt=E4M3):
+    """Grouped form of gemm_mxfp8_swiglu: b_codes is (E * n, K) with every expert's n = 2I rows interleaved."""
+    rows, k = a_codes.shape
+    h = torch.empty(rows, n // 2, dtype=torch.uint8, device=a_codes.device)
+    sf = torch.empty(sf_bytes(rows, n // 64), dtype=torch.uint8, device=a_codes.device)
+    _lib.check(_lib.load().b200q_grouped_gemm_mxfp8_swiglu(a_codes.data_ptr(), fmt_of(a_fmt), a_sf.data_ptr(), b_codes.data_ptr(),
+                                                           fmt_of(b_fmt), b_sf.data_ptr(), plan.tile_expert.data_ptr(),
+                                                           plan.num_tiles.data_ptr(), rows, plan.n_experts, n, k, h.data_ptr(),
+                                                           h.stride(0), sf.data_ptr(), _stream()),
+               "b200q_grouped_gemm_mxfp8_swiglu")
+    return h, sf
 
 
 def swiglu(g: torch.Tensor, quantize: bool, fmt=E4M3):

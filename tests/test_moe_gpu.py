@@ -155,6 +155,72 @@ def test_grouped_gemm_with_empty_experts(ops, counts, d, n):
         s += c
 
 
+@pytest.mark.parametrize("counts", [[5, 0, 7, 4], [200, 0, 0, 131], [128, 256, 1, 0]])
+@pytest.mark.parametrize("d,inter", [(256, 64), (768, 384), (512, 192)])
+@pytest.mark.parametrize("bn", [0, 128, 192, 256])
+def test_swiglu_epilogue_equals_gemm_then_swiglu(ops, counts, d, inter, bn):
+    """Grouped GEMM with the SwiGLU + MXFP8 epilogue over interleaved weights == grouped GEMM to
+    bf16 followed by the stand-alone SwiGLU + MXFP8 kernel over the plain weights, byte for byte."""
+    from pretrain_b200 import _lib
+    g = torch.Generator().manual_seed(sum(counts) + d + inter)
+    r, e = sum(counts), len(counts)
+    x = torch.randn(r, d, generator=g).bfloat16().cuda()
+    w = (0.08 * torch.randn(e, 2 * inter, d, generator=g)).bfloat16().cuda()
+    offs = torch.tensor(counts).cumsum(0).int().cuda()
+    plan = ops.moe_pad_plan(offs, r)
+    a, sfa = ops.moe_gather(x, plan, True)
+    live = int(plan.num_tiles.item()) * 128
+    # plain chain (every expert's 2I rows padded to 128 so that scale-factor tiles do not straddle experts)
+    n_pad = (2 * inter + 127) // 128 * 128
+    wp = torch.cat([w, w.new_zeros(e, n_pad - 2 * inter, d)], 1) if n_pad != 2 * inter else w
+    wq, wsf = ops.quantize_mxfp8(wp.reshape(e * n_pad, d), 1)
+    hb = ops.grouped_gemm_mxfp8(a, sfa, wq, wsf, plan, n_pad)[:live, : 2 * inter].contiguous()
+    want_codes, want_sf = ops.swiglu(hb, True)
+    _lib.load().b200q_debug_set_gemm_bn(bn)
+    try:
+        wqi, wsfi = ops.quantize_mxfp8_rowmap(w.reshape(e * 2 * inter, d), ops.glu_row_map(e, inter, "cuda"))
+        got_codes, got_sf = ops.grouped_gemm_mxfp8_swiglu(a, sfa, wqi, wsfi, plan, 2 * inter)
+        ops.device_status()
+    finally:
+        _lib.load().b200q_debug_set_gemm_bn(0)
+    assert torch.equal(got_codes[:live], want_codes)
+    n_sf = live // 128 * ((inter // 32 + 3) // 4) * 512
+    assert torch.equal(got_sf[:n_sf], want_sf[:n_sf])
+
+
+def test_rowmap_quantizer_is_a_row_permutation(ops):
+    e, inter, d = 3, 96, 160
+    g = torch.Generator().manual_seed(9)
+    w = torch.randn(e * 2 * inter, d, generator=g).bfloat16().cuda()
+    m = ops.glu_row_map(e, inter, "cuda")
+    assert sorted(m.tolist()) == list(range(e * 2 * inter))
+    assert m[:32].tolist() == list(range(32)) and m[inter: inter + 32].tolist() == list(range(32, 64))   # gate block, then its up block
+    codes, sf = ops.quantize_mxfp8_rowmap(w, m, layout=0)
+    rc, rs = ops.quantize_mxfp8(w, 1, layout=0)
+    assert torch.equal(codes[m.long()], rc)
+    assert torch.equal(sf.view(-1, d // 32)[m.long()], rs.view(-1, d // 32))
+
+
+def test_dense_gemm_with_swiglu_epilogue(ops):
+    g = torch.Generator().manual_seed(4)
+    m_, d, inter = 300, 512, 256
+    x = torch.randn(m_, d, generator=g).bfloat16().cuda()
+    w = (0.06 * torch.randn(2 * inter, d, generator=g)).bfloat16().cuda()
+    xq, xsf = ops.quantize_mxfp8(x, 1)
+    wq, wsf = ops.quantize_mxfp8(w, 1)
+    want_codes, want_sf = ops.swiglu(ops.gemm_mxfp8(xq, xsf, wq, wsf), True)
+    wqi, wsfi = ops.quantize_mxfp8_rowmap(w, ops.glu_row_map(1, inter, "cuda"))
+    got_codes, got_sf = ops.gemm_mxfp8_swiglu(xq, xsf, wqi, wsfi)
+    ops.device_status()
+    assert torch.equal(got_codes, want_codes)
+    assert torch.equal(G.unswizzle(got_sf, m_, inter // 32), G.unswizzle(want_sf, m_, inter // 32))
+    # and against the oracle's arithmetic on the dequantized operands
+    h_ref = R.silu_glu(*(G.matmul_fp32(G.deq_mxfp8(xq, xsf), G.deq_mxfp8(wq, wsf)).bfloat16()).chunk(2, dim=-1))
+    h_got = G.deq_mxfp8(got_codes, got_sf)
+    mx, fro = G.rel_errors(h_got, h_ref.float())
+    assert mx <= 6e-2 and fro <= 4e-2, (mx, fro)      # one E4M3 rounding (2^-4 relative) on top of the GEMM tolerance
+
+
 def test_swiglu(ops):
     g = torch.Generator().manual_seed(0)
     h = (2.0 * torch.randn(384, 768, generator=g)).bfloat16().cuda()
