@@ -422,9 +422,11 @@ int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t 
 int g_force_bn = 0;   // test hook: 0 = choose by shape
 
 // Tile width by a small cost model (cycles per tile x waves): the main loop is bound by the
-// tensor pipe (2*BN cycles per K step) or by shared-memory reads ((128+BN)*128 bytes per K
-// step at ~100 B/clk, fitted to measurements); the epilogue hides behind the next main loop only when two
-// accumulators fit in tensor memory (every width but 256).
+// tensor pipe (2*BN cycles per K step) or by the operand bytes the SM pulls from L2 per K step,
+// (128+BN)*128, at ~45 B/clk per SM when all SMs load at once (about 12 TB/s in total, fitted to
+// grouped and small dense shapes: the widest tile won or tied on every one of them); the
+// epilogue hides behind the next main loop only when two accumulators fit in tensor memory
+// (every width but 256).
 template <int KIND>
 int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
   const int cands[3] = {256, 192, 128};
@@ -434,7 +436,7 @@ int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
   for (int bn : cands) {
     const int64_t tiles = num_m * ((N + bn - 1) / bn);
     const int64_t waves = (tiles + kNumSMs - 1) / kNumSMs;
-    const double kstep = std::max(2.0 * bn, (128.0 + bn) * 128.0 / 100.0);
+    const double kstep = std::max(2.0 * bn, (128.0 + bn) * 128.0 / 45.0);
     const double mainloop = num_k * kstep + 600.0, epi = 300.0 + (bn / 32) * 220.0;
     // the epilogue hides behind the next main loop; at width 256 with scale factors the MMA
     // still waits for the first epilogue block(s) of the previous tile

@@ -105,6 +105,102 @@ moe_scatter_kernel(const int64_t* __restrict__ top_idx, int64_t n, int k, int E,
   }
 }
 
+// ---- plan, steps 2 + 3 in one launch (up to kFusedPlanBlocks CTAs) ---------------------------------
+// Every CTA re-derives what step 2 would hand it from the per-CTA histograms (a few thousand
+// integers in L2): the experts' totals, hence the padded segment starts, and its own exclusive
+// prefix over the CTAs before it; then it places its pairs like moe_scatter_kernel.  CTA 0 also
+// writes the tables (offs, padded_offs, tile_expert, num_tiles) and marks the pad rows of every
+// segment with -1, so no separate scan launch and no clearing of src_of_row are needed.
+constexpr int kFusedPlanBlocks = 128;
+
+__global__ void __launch_bounds__(kPlanThreads)
+moe_scatter_tables_kernel(const int64_t* __restrict__ top_idx, int64_t n, int k, int E, const int32_t* __restrict__ block_counts,
+                          int nblocks, int32_t* __restrict__ offs, int32_t* __restrict__ padded_offs,
+                          int32_t* __restrict__ row_of, int32_t* __restrict__ src_of_row, int32_t* __restrict__ tile_expert,
+                          int32_t* __restrict__ num_tiles, int max_tiles, int64_t padded_rows) {
+  extern __shared__ int warp_counts[];      // [32 warps][E]
+  __shared__ int total[kMaxExperts], excl[kMaxExperts], pstart[kMaxExperts + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 32 * E; i += kPlanThreads) warp_counts[i] = 0;
+  for (int i = threadIdx.x; i < E; i += kPlanThreads) total[i] = excl[i] = 0;
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nblocks * E; idx += kPlanThreads) {
+    const int b = idx / E, e = idx - b * E;
+    const int c = block_counts[idx];
+    if (c) {
+      atomicAdd(&total[e], c);
+      if (b < (int)blockIdx.x) atomicAdd(&excl[e], c);
+    }
+  }
+  const int64_t i = (int64_t)blockIdx.x * kPlanThreads + threadIdx.x;
+  int e = -1;
+  if (i < n) {
+    e = (int)top_idx[i];
+    if (e < 0 || e >= E) e = -1;
+  }
+  const unsigned same = __match_any_sync(0xFFFFFFFFu, e);
+  const int rank_in_warp = __popc(same & ((1u << lane) - 1));
+  if (e >= 0 && rank_in_warp == 0) warp_counts[warp * E + e] = __popc(same);
+  __syncthreads();
+  if (warp == 0) {
+    // padded segment starts: exclusive scan of the totals rounded up to 128, 32 experts at a time
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int x = e0 + lane < E ? (total[e0 + lane] + 127) & ~127 : 0;
+      int inc = x;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += y;
+      }
+      if (e0 + lane < E) pstart[e0 + lane] = carry + inc - x;
+      carry += __shfl_sync(0xFFFFFFFFu, inc, 31);
+    }
+    if (lane == 0) pstart[E] = carry;
+  }
+  for (int x = threadIdx.x; x < E; x += kPlanThreads) {     // exclusive prefix over the 32 warps
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = warp_counts[w * E + x];
+      warp_counts[w * E + x] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  if (e >= 0) {
+    const int dest = pstart[e] + excl[e] + warp_counts[warp * E + e] + rank_in_warp;
+    row_of[i] = dest;
+    src_of_row[dest] = (int32_t)(i / k);
+  }
+  // rows past the last segment (the buffer is sized for the worst case): no source either
+  for (int64_t r = pstart[E] + (int64_t)blockIdx.x * kPlanThreads + threadIdx.x; r < padded_rows; r += (int64_t)gridDim.x * kPlanThreads)
+    src_of_row[r] = -1;
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) {
+      int end = 0;
+      for (int x = 0; x < E; ++x) { end += total[x]; offs[x] = end; }
+      *num_tiles = pstart[E] >> 7;
+    }
+    for (int x = threadIdx.x; x <= E; x += kPlanThreads) padded_offs[x] = pstart[x];
+    for (int t = threadIdx.x; t < max_tiles; t += kPlanThreads) {
+      // expert of tile t: the segment that contains row 128 t (segments are whole tiles)
+      int ex = -1;
+      if (t < (pstart[E] >> 7)) {
+        int lo = 0, hi = E - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (pstart[mid] <= (t << 7)) lo = mid; else hi = mid - 1;
+        }
+        ex = lo;   // the last expert that starts at or before the row: empty ones before it share its start
+      }
+      tile_expert[t] = ex;
+    }
+    // pad rows at the end of every segment
+    for (int x = warp; x < E; x += 32)
+      for (int r = pstart[x] + total[x] + lane; r < pstart[x + 1]; r += 32) src_of_row[r] = -1;
+  }
+}
+
 // ---- plan for rows that are already expert-sorted (grouped_mlp's input convention) ----------------
 __global__ void __launch_bounds__(kMaxExperts)
 moe_pad_plan_kernel(const int32_t* __restrict__ offs, int E, int32_t* __restrict__ padded_offs,
@@ -248,6 +344,31 @@ static __device__ __align__(256) int32_t g_static_plan_scratch[kStaticPlanInts];
 constexpr int kMaxDevices = 64;
 static int32_t* g_static_plan_ptr[kMaxDevices] = {};   // device address of the array, per device
 
+// The permute plan's launches, shared by the two entry points (workspace from the caller or built in).
+int run_permute_plan(const int64_t* top_idx, int64_t n_pairs, int k, int E, int32_t* block_counts, int32_t* offs,
+                     int32_t* padded_offs, int32_t* row_of, int32_t* src_of_row, int32_t* tile_expert, int32_t* num_tiles,
+                     cudaStream_t st) {
+  const int nblocks = (int)((n_pairs + kPlanThreads - 1) / kPlanThreads);
+  const int64_t padded_rows = b200q_moe_padded_rows(n_pairs, E);
+  moe_hist_kernel<<<nblocks, kPlanThreads, 0, st>>>(top_idx, n_pairs, E, block_counts);
+  B200Q_CUDA(cudaGetLastError());
+  if (nblocks <= kFusedPlanBlocks) {
+    moe_scatter_tables_kernel<<<nblocks, kPlanThreads, 32 * E * sizeof(int), st>>>(
+        top_idx, n_pairs, k, E, block_counts, nblocks, offs, padded_offs, row_of, src_of_row, tile_expert, num_tiles,
+        (int)(padded_rows / 128), padded_rows);
+    B200Q_CUDA(cudaGetLastError());
+    return B200Q_OK;
+  }
+  B200Q_CUDA(cudaMemsetAsync(src_of_row, 0xFF, (size_t)padded_rows * sizeof(int32_t), st));   // -1 = pad row
+  moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(block_counts, nblocks, E, offs, padded_offs, tile_expert, num_tiles,
+                                             (int)(padded_rows / 128));
+  B200Q_CUDA(cudaGetLastError());
+  moe_scatter_kernel<<<nblocks, kPlanThreads, 32 * E * sizeof(int), st>>>(top_idx, n_pairs, k, E, block_counts, padded_offs,
+                                                                           row_of, src_of_row);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
 // grid for kernels whose work items belong to single threads (256 per CTA), capped at one wave
 inline int thread_item_grid(int64_t items) {
   int64_t want = (items + 255) / 256, cap = (int64_t)kNumSMs * 5;
@@ -288,19 +409,8 @@ int b200q_moe_permute_plan(const int64_t* top_idx, int64_t n_pairs, int k, int E
   int rc = require_sm100();
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  const int nblocks = (int)((n_pairs + kPlanThreads - 1) / kPlanThreads);
-  const int64_t padded_rows = b200q_moe_padded_rows(n_pairs, E);
-  int32_t* block_counts = (int32_t*)workspace;
-  B200Q_CUDA(cudaMemsetAsync(src_of_row, 0xFF, (size_t)padded_rows * sizeof(int32_t), st));   // -1 = pad row
-  moe_hist_kernel<<<nblocks, kPlanThreads, 0, st>>>(top_idx, n_pairs, E, block_counts);
-  B200Q_CUDA(cudaGetLastError());
-  moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(block_counts, nblocks, E, offs, padded_offs, tile_expert, num_tiles,
-                                             (int)(padded_rows / 128));
-  B200Q_CUDA(cudaGetLastError());
-  moe_scatter_kernel<<<nblocks, kPlanThreads, 32 * E * sizeof(int), st>>>(top_idx, n_pairs, k, E, block_counts, padded_offs,
-                                                                           row_of, src_of_row);
-  B200Q_CUDA(cudaGetLastError());
-  return B200Q_OK;
+  return run_permute_plan(top_idx, n_pairs, k, E, (int32_t*)workspace, offs, padded_offs, row_of, src_of_row, tile_expert,
+                          num_tiles, st);
 }
 
 int b200q_moe_pad_plan(const int32_t* offs, int E, int64_t n_rows, int32_t* padded_offs, int32_t* src_of_row,
@@ -412,20 +522,8 @@ int b200q_moe_permute_plan_static(const int64_t* top_idx, int64_t n_pairs, int k
     B200Q_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_plan_scratch));
     g_static_plan_ptr[dev] = ptr;
   }
-  int32_t* block_counts = g_static_plan_ptr[dev];
-  cudaStream_t st = (cudaStream_t)stream;
-  const int nblocks = (int)nblocks64;
-  const int64_t padded_rows = b200q_moe_padded_rows(n_pairs, E);
-  B200Q_CUDA(cudaMemsetAsync(src_of_row, 0xFF, (size_t)padded_rows * sizeof(int32_t), st));   // -1 = pad row
-  moe_hist_kernel<<<nblocks, kPlanThreads, 0, st>>>(top_idx, n_pairs, E, block_counts);
-  B200Q_CUDA(cudaGetLastError());
-  moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(block_counts, nblocks, E, offs, padded_offs, tile_expert, num_tiles,
-                                             (int)(padded_rows / 128));
-  B200Q_CUDA(cudaGetLastError());
-  moe_scatter_kernel<<<nblocks, kPlanThreads, 32 * E * sizeof(int), st>>>(top_idx, n_pairs, k, E, block_counts, padded_offs,
-                                                                           row_of, src_of_row);
-  B200Q_CUDA(cudaGetLastError());
-  return B200Q_OK;
+  return run_permute_plan(top_idx, n_pairs, k, E, g_static_plan_ptr[dev], offs, padded_offs, row_of, src_of_row, tile_expert,
+                          num_tiles, (cudaStream_t)stream);
 }
 
 }  // extern "C"
