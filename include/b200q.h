@@ -76,6 +76,16 @@ int b200q_quantize_fp8_tensorwise(const void* x, int64_t rows, int64_t cols, int
 int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int fmt,
                          void* codes, void* sf, int sf_layout, void* stream);
 
+/* Both directions of b200q_quantize_mxfp8 from ONE read of x: (codes_row [rows, cols], sf_row) as
+ * axis = 1 would give and (codes_col [cols, rows], sf_col) as axis = 0 would give, byte for byte.
+ * A linear layer needs both of each tensor: the activation for fprop and wgrad
+ * (src/quant/linear.py:74,102), the weight for fprop and dgrad (:74,98), the output gradient for
+ * dgrad and wgrad (:98,102); the reference re-reads the bf16 tensor for each.  rows % 32 == 0 and
+ * cols % 32 == 0.  4.0625 bytes of traffic per element instead of 2 x 3.03125. */
+int b200q_quantize_mxfp8_dual(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt,
+                              void* codes_row, void* sf_row, void* codes_col, void* sf_col,
+                              int sf_layout, void* stream);
+
 /* Row-wise b200q_quantize_mxfp8 (axis = 1) that writes input row r as output row dst_row[r]
  * (codes and scale factors alike); dst_row is a permutation of 0 .. rows-1 in device memory.
  * Used to store gated-MLP weights (src/layers/mlp.py:404-411, expert_gate_up) in the interleaved

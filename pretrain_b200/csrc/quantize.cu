@@ -374,6 +374,115 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// MXFP8 in both directions from one read of the input: row-wise codes/scales (blocks along the
+// columns) for the GEMM that contracts over the columns, and transposed codes/scales (blocks
+// along the rows) for the GEMM that contracts over the rows - what a linear layer needs of an
+// activation (fprop + wgrad), of a weight (fprop + dgrad) and of an output gradient (dgrad +
+// wgrad).  Results equal the two single-direction kernels byte for byte.
+//
+// A CTA takes a 128 x 128 tile.  Phase 1: every thread loads two runs of 32 consecutive elements
+// of a row (64 bytes each), quantizes them row-wise straight from registers (BOTH) and parks the
+// bf16 values in shared memory (row pitch 272 bytes: 16-byte stores without bank conflicts).
+// Phase 2: a thread owns TWO adjacent columns and 32 rows: 32 four-byte shared-memory loads give
+// it both columns as packed bf16 pairs, the block maxima come from packed max instructions, and
+// the codes go to a staging tile.  Phase 3 writes that tile out as 128-byte rows of the
+// transposed matrix.  BOTH = false skips the row-wise outputs (the transposing quantizer).
+// ------------------------------------------------------------------------------------------
+constexpr int kDT = 128;                    // tile edge
+constexpr int kDPitch = kDT * 2 + 16;       // bytes per staged input row
+constexpr int kDOutPitch = kDT + 16;        // bytes per staged output row (= input column)
+constexpr int kDualSmem = kDT * kDPitch + kDT * kDOutPitch;
+
+template <int FMT, bool WIDE, bool BOTH>
+__global__ void __launch_bounds__(kThreads)
+mx_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, uint8_t* __restrict__ codes_r,
+                     uint8_t* __restrict__ sf_r, uint8_t* __restrict__ codes_c, uint8_t* __restrict__ sf_c, int swz) {
+  extern __shared__ __align__(16) uint8_t dual_smem[];
+  uint8_t* tin = dual_smem;
+  uint8_t* tout = dual_smem + kDT * kDPitch;
+  const int tid = threadIdx.x;
+  const int64_t c0 = (int64_t)blockIdx.x * kDT, r0 = (int64_t)blockIdx.y * kDT;
+  const int64_t nblk_r = cols >> 5, kt_r = (nblk_r + 3) >> 2;
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int item = i * kThreads + tid, r = item >> 2, q = item & 3;     // 4 runs of 32 per tile row
+    const int64_t gr = r0 + r, gc = c0 + q * 32;
+    const bool live = gr < rows && gc < cols;                             // cols % 32 == 0: a run is whole or absent
+    uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (live) {
+      const uint16_t* xp = x + gr * ld + gc;
+      ld_nc_32B<WIDE>(xp, v[0], v[1]);
+      ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(tin + r * kDPitch + q * 64);
+    dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; dst[3] = v[3];
+    if (BOTH && live) {
+      uint32_t o[8];
+      const int e = mx_quant_block32<FMT>(v, o);
+      st_32B<WIDE>(codes_r + gr * cols + gc, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+      sf_r[swz ? sf_swizzled(gr, (int)(gc >> 5), kt_r) : gr * nblk_r + (gc >> 5)] = (uint8_t)(e + 127);
+    }
+  }
+  __syncthreads();
+
+  {
+    const int cp = tid & 63, j = tid >> 6;            // column pair, block of 32 rows
+    const uint32_t* col = reinterpret_cast<const uint32_t*>(tin + (32 * j) * kDPitch) + cp;
+    uint32_t w[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) w[i] = col[i * (kDPitch / 4)];
+    uint32_t m = absmax_bf16x2(w[0], w[1]);
+#pragma unroll
+    for (int i = 2; i < 32; ++i) m = absmax_bf16x2(m, w[i]);
+    const int e0 = mx_scale_exp(bf16lo(m), FMT), e1 = mx_scale_exp(bf16hi(m), FMT);
+    const float inv0 = mx_inv_scale(e0), inv1 = mx_inv_scale(e1);
+    uint32_t o0[8], o1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o0[i] = cvt_fp8x4(bf16lo(w[4 * i]) * inv0, bf16lo(w[4 * i + 1]) * inv0, bf16lo(w[4 * i + 2]) * inv0, bf16lo(w[4 * i + 3]) * inv0, FMT);
+      o1[i] = cvt_fp8x4(bf16hi(w[4 * i]) * inv1, bf16hi(w[4 * i + 1]) * inv1, bf16hi(w[4 * i + 2]) * inv1, bf16hi(w[4 * i + 3]) * inv1, FMT);
+    }
+    uint4* d0 = reinterpret_cast<uint4*>(tout + (2 * cp) * kDOutPitch + 32 * j);
+    uint4* d1 = reinterpret_cast<uint4*>(tout + (2 * cp + 1) * kDOutPitch + 32 * j);
+    d0[0] = make_uint4(o0[0], o0[1], o0[2], o0[3]); d0[1] = make_uint4(o0[4], o0[5], o0[6], o0[7]);
+    d1[0] = make_uint4(o1[0], o1[1], o1[2], o1[3]); d1[1] = make_uint4(o1[4], o1[5], o1[6], o1[7]);
+    const int64_t gc = c0 + 2 * cp, gr = r0 + 32 * j;
+    if (gr < rows) {
+      if (gc < cols) sf_c[sf_offset(gc, gr >> 5, rows >> 5, swz)] = (uint8_t)(e0 + 127);
+      if (gc + 1 < cols) sf_c[sf_offset(gc + 1, gr >> 5, rows >> 5, swz)] = (uint8_t)(e1 + 127);
+    }
+  }
+  __syncthreads();
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int id = i * kThreads + tid, oc = id >> 3, ch = id & 7;
+    if (c0 + oc < cols && r0 + ch * 16 < rows)
+      *reinterpret_cast<uint4*>(codes_c + (c0 + oc) * rows + r0 + ch * 16) =
+          *reinterpret_cast<const uint4*>(tout + oc * kDOutPitch + ch * 16);
+  }
+}
+
+template <bool BOTH>
+int launch_mx_tile_quant(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes_r, uint8_t* sf_r,
+                         uint8_t* codes_c, uint8_t* sf_c, int swz, cudaStream_t st) {
+  const bool wide = aligned32(x) && (ld & 15) == 0 && (!BOTH || aligned32(codes_r));
+  dim3 grid((unsigned)((cols + kDT - 1) / kDT), (unsigned)((rows + kDT - 1) / kDT));
+#define B200Q_GO(F, W)                                                                                                  \
+  do {                                                                                                                  \
+    auto kernel = mx_tile_quant_kernel<F, W, BOTH>;                                                                     \
+    B200Q_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDualSmem));                   \
+    kernel<<<grid, kThreads, kDualSmem, st>>>(x, rows, cols, ld, codes_r, sf_r, codes_c, sf_c, swz);                    \
+  } while (0)
+  if (fmt == FMT_E4M3) { if (wide) B200Q_GO(FMT_E4M3, true); else B200Q_GO(FMT_E4M3, false); }
+  else { if (wide) B200Q_GO(FMT_E5M2, true); else B200Q_GO(FMT_E5M2, false); }
+#undef B200Q_GO
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
 int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
   if (x == nullptr || rows <= 0 || cols <= 0 || ld < cols) return B200Q_ERR_INVALID_ARG;
   if ((cols & 7) || (ld & 7)) return B200Q_ERR_SHAPE;
@@ -563,10 +672,29 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   if ((rc = zero_sf_pads(sf, outer, contraction / 32, sf_layout, st))) return rc;
   if (axis == 1)
     launch_rowwise_block<MODE_MX>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr, st);
+  else if ((cols & 31) == 0)   // whole 32-column runs: the 128 x 128 tile kernel with packed column pairs
+    return launch_mx_tile_quant<false>((const uint16_t*)x, rows, cols, ld, fmt, nullptr, nullptr, (uint8_t*)codes, (uint8_t*)sf, sf_layout, st);
   else
     launch_transpose<MODE_MX>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr, nullptr, st);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
+}
+
+int b200q_quantize_mxfp8_dual(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt, void* codes_row, void* sf_row,
+                              void* codes_col, void* sf_col, int sf_layout, void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes_row == nullptr || sf_row == nullptr || codes_col == nullptr || sf_col == nullptr ||
+      (fmt != B200Q_E4M3 && fmt != B200Q_E5M2) || (sf_layout != B200Q_SF_NATURAL && sf_layout != B200Q_SF_SWIZZLE_128x4))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes_row) || !aligned16(codes_col)) return B200Q_ERR_ALIGNMENT;
+  if ((rows & 31) || (cols & 31)) return B200Q_ERR_SHAPE;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((rc = zero_sf_pads(sf_row, rows, cols / 32, sf_layout, st))) return rc;
+  if ((rc = zero_sf_pads(sf_col, cols, rows / 32, sf_layout, st))) return rc;
+  return launch_mx_tile_quant<true>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row, (uint8_t*)codes_col,
+                                    (uint8_t*)sf_col, sf_layout, st);
 }
 
 int b200q_quantize_mxfp8_rowmap(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt, const int32_t* dst_row,

@@ -86,6 +86,20 @@ def quantize_mxfp8(x: torch.Tensor, axis: int = 1, fmt=E4M3, layout: int = SF_SW
     return codes, sf
 
 
+def quantize_mxfp8_dual(x: torch.Tensor, fmt=E4M3, layout: int = SF_SWIZZLED):
+    """One pass over x (rows, cols): returns (codes_row, sf_row, codes_col, sf_col), equal to
+    quantize_mxfp8(x, 1) + quantize_mxfp8(x, 0).  rows % 32 == 0 and cols % 32 == 0."""
+    x = _mat(x)
+    rows, cols = x.shape
+    cr = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
+    cc = torch.empty(cols, rows, dtype=torch.uint8, device=x.device)
+    sr = torch.empty(sf_bytes(rows, cols // 32, layout), dtype=torch.uint8, device=x.device)
+    sc = torch.empty(sf_bytes(cols, rows // 32, layout), dtype=torch.uint8, device=x.device)
+    _lib.check(_lib.load().b200q_quantize_mxfp8_dual(x.data_ptr(), rows, cols, x.stride(0), fmt_of(fmt), cr.data_ptr(), sr.data_ptr(),
+                                                     cc.data_ptr(), sc.data_ptr(), layout, _stream()), "b200q_quantize_mxfp8_dual")
+    return cr, sr, cc, sc
+
+
 def glu_row_map(n_groups: int, inter: int, device) -> torch.Tensor:
     """dst_row for weights stacked as n_groups x [gate (inter rows); up (inter rows)]: the
     interleaved order the SwiGLU epilogue reads (32 gate rows, then the 32 up rows of the same

@@ -69,6 +69,18 @@ def _(x, axis, fmt, layout):
     return x.new_empty(outer, c, dtype=torch.uint8), x.new_empty(_sf_numel(outer, c // 32, layout), dtype=torch.uint8)
 
 
+@_lib_def("b200q::quantize_mxfp8_dual", mutates_args=())
+def quantize_mxfp8_dual(x: torch.Tensor, fmt: int, layout: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    return ops.quantize_mxfp8_dual(x, fmt, layout)
+
+
+@quantize_mxfp8_dual.register_fake
+def _(x, fmt, layout):
+    rows, cols = x.shape
+    return (x.new_empty(rows, cols, dtype=torch.uint8), x.new_empty(_sf_numel(rows, cols // 32, layout), dtype=torch.uint8),
+            x.new_empty(cols, rows, dtype=torch.uint8), x.new_empty(_sf_numel(cols, rows // 32, layout), dtype=torch.uint8))
+
+
 @_lib_def("b200q::quantize_nvfp4", mutates_args=())
 def quantize_nvfp4(x: torch.Tensor, axis: int, layout: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     return ops.quantize_nvfp4(x, axis, None, layout)

@@ -101,6 +101,41 @@ def test_module_forward_backward(recipe, gran, kind):
     assert q.bias.grad is not None and torch.isfinite(q.weight.grad).all()
 
 
+def test_mxfp8_training_path_quantizes_once_and_equals_the_per_gemm_path():
+    """All-MXFP8 layers quantize x, w and g once each (both directions in one kernel) and save codes
+    for backward; y, dx and dw must equal what the three separate `_gemm` calls give, bit for bit."""
+    from pretrain_b200.quant.linear import QuantLinear, QuantizedLinearFn, _gemm
+    torch.manual_seed(1)
+    cfg = _cfg("mxfp8")
+    m, k, n = 256, 160, 96
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = nn.Parameter((0.05 * torch.randn(n, k, device="cuda")).bfloat16())
+    g = (1e-2 * torch.randn(m, n, device="cuda")).bfloat16()
+    y = QuantizedLinearFn.apply(x, w, None, cfg)
+    y.backward(g)
+    d = cfg.dtype
+    with torch.no_grad():
+        y_ref = _gemm(x, w.t(), d["act"], d["weight"], torch.bfloat16)
+        dx_ref = _gemm(g, w, d["input_grad"], d["weight"], torch.bfloat16)
+        dw_ref = _gemm(g.t(), x, d["weight_grad"], d["act"], torch.bfloat16)
+    assert torch.equal(y, y_ref) and torch.equal(x.grad, dx_ref) and torch.equal(w.grad, dw_ref)
+    # the weight's two MXFP8 copies are kept until the parameter is written again
+    cached = w._b200q_mx
+    QuantizedLinearFn.apply(x, w, None, cfg).sum().backward()
+    assert w._b200q_mx is cached
+    with torch.no_grad():
+        w.add_(1.0)                                    # what an optimizer step does
+    QuantizedLinearFn.apply(x, w, None, cfg)
+    assert w._b200q_mx is not cached
+    # no backward to come: the plain single-direction path runs and leaves no codes behind
+    q = QuantLinear(k, n, False, cfg).cuda().bfloat16()
+    with torch.no_grad():
+        y2 = q(x.detach())
+    assert not hasattr(q.weight, "_b200q_mx") and y2.shape == (m, n)
+    q(x.detach()).sum().backward()
+    assert hasattr(q.weight, "_b200q_mx") and q.weight.grad is not None
+
+
 def test_hp_weight_grad_differs_from_quantized():
     from pretrain_b200.quant.linear import QuantLinear
     torch.manual_seed(0)

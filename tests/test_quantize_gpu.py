@@ -16,6 +16,11 @@ pytestmark = pytest.mark.gpu
 E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
 
 
+def G_unswizzle(sf, outer, nblk):
+    import gpu_ref
+    return gpu_ref.unswizzle(sf, outer, nblk)
+
+
 @pytest.fixture(scope="module")
 def ops():
     from pretrain_b200 import build, ops
@@ -165,6 +170,22 @@ def test_strided_input_is_read_in_place(ops):
     codes, sf = ops.quantize_mxfp8(view, 1, E4, 0)
     rc, rs = R.quantize_mxfp8(x, -1, E4)
     assert torch.equal(codes.cpu(), rc) and torch.equal(sf.cpu(), rs.reshape(-1))
+
+
+@pytest.mark.parametrize("shape", [(512, 768), (96, 160), (32, 32), (160, 96), (384, 4352)])
+@pytest.mark.parametrize("dt", [E4, E5])
+@pytest.mark.parametrize("layout", [0, 1])
+def test_mxfp8_both_directions_in_one_pass(ops, shape, dt, layout):
+    g = torch.Generator().manual_seed(shape[0] + shape[1])
+    x = (torch.randn(*shape, generator=g) * torch.exp2(torch.randint(-6, 6, shape, generator=g).float())).bfloat16().cuda()
+    cr, sr, cc, sc = ops.quantize_mxfp8_dual(x, dt, layout)
+    r1, s1 = ops.quantize_mxfp8(x, 1, dt, layout)
+    r0, s0 = ops.quantize_mxfp8(x, 0, dt, layout)
+    assert torch.equal(cr, r1) and torch.equal(sr, s1) and torch.equal(cc, r0) and torch.equal(sc, s0)
+    # and against the oracle directly
+    oc, osf = R.quantize_mxfp8(x.cpu(), 0, dt)
+    assert torch.equal(cc.cpu(), oc)
+    assert torch.equal((G_unswizzle(sc, shape[1], shape[0] // 32) if layout else sc.view(shape[1], -1)).cpu(), osf)
 
 
 def test_rows_that_are_only_16_byte_aligned(ops):
