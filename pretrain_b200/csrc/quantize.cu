@@ -382,25 +382,26 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
 // wgrad).  Results equal the two single-direction kernels byte for byte.
 //
 // A CTA takes a 128 x 128 tile.  Phase 1: every thread loads two runs of 32 consecutive elements
-// of a row (64 bytes each), quantizes them row-wise straight from registers (BOTH) and parks the
+// of a row (64 bytes each), quantizes them row-wise straight from registers and parks the
 // bf16 values in shared memory (row pitch 272 bytes: 16-byte stores without bank conflicts).
 // Phase 2: a thread owns TWO adjacent columns and 32 rows: 32 four-byte shared-memory loads give
 // it both columns as packed bf16 pairs, the block maxima come from packed max instructions, and
-// the codes go to a staging tile.  Phase 3 writes that tile out as 128-byte rows of the
-// transposed matrix.  BOTH = false skips the row-wise outputs (the transposing quantizer).
+// the codes go to a staging tile (which reuses the input tile's memory once every thread holds
+// its columns in registers).  Phase 3 writes that tile out as 128-byte rows of the transposed
+// matrix.
 // ------------------------------------------------------------------------------------------
 constexpr int kDT = 128;                    // tile edge
 constexpr int kDPitch = kDT * 2 + 16;       // bytes per staged input row
 constexpr int kDOutPitch = kDT + 16;        // bytes per staged output row (= input column)
-constexpr int kDualSmem = kDT * kDPitch + kDT * kDOutPitch;
+constexpr int kDualSmem = kDT * kDPitch;     // the output staging tile reuses the input tile's memory
 
-template <int FMT, bool WIDE, bool BOTH>
+template <int FMT, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
 mx_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, uint8_t* __restrict__ codes_r,
                      uint8_t* __restrict__ sf_r, uint8_t* __restrict__ codes_c, uint8_t* __restrict__ sf_c, int swz) {
   extern __shared__ __align__(16) uint8_t dual_smem[];
   uint8_t* tin = dual_smem;
-  uint8_t* tout = dual_smem + kDT * kDPitch;
+  uint8_t* tout = dual_smem;                  // written only after every thread has read its columns (barrier below)
   const int tid = threadIdx.x;
   const int64_t c0 = (int64_t)blockIdx.x * kDT, r0 = (int64_t)blockIdx.y * kDT;
   const int64_t nblk_r = cols >> 5, kt_r = (nblk_r + 3) >> 2;
@@ -418,7 +419,7 @@ mx_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
     }
     uint4* dst = reinterpret_cast<uint4*>(tin + r * kDPitch + q * 64);
     dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; dst[3] = v[3];
-    if (BOTH && live) {
+    if (live) {
       uint32_t o[8];
       const int e = mx_quant_block32<FMT>(v, o);
       st_32B<WIDE>(codes_r + gr * cols + gc, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
@@ -433,6 +434,7 @@ mx_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
     uint32_t w[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) w[i] = col[i * (kDPitch / 4)];
+    __syncthreads();                            // all column reads done: the tile may be overwritten
     uint32_t m = absmax_bf16x2(w[0], w[1]);
 #pragma unroll
     for (int i = 2; i < 32; ++i) m = absmax_bf16x2(m, w[i]);
@@ -465,14 +467,13 @@ mx_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
   }
 }
 
-template <bool BOTH>
 int launch_mx_tile_quant(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes_r, uint8_t* sf_r,
                          uint8_t* codes_c, uint8_t* sf_c, int swz, cudaStream_t st) {
-  const bool wide = aligned32(x) && (ld & 15) == 0 && (!BOTH || aligned32(codes_r));
+  const bool wide = aligned32(x) && (ld & 15) == 0 && aligned32(codes_r);
   dim3 grid((unsigned)((cols + kDT - 1) / kDT), (unsigned)((rows + kDT - 1) / kDT));
 #define B200Q_GO(F, W)                                                                                                  \
   do {                                                                                                                  \
-    auto kernel = mx_tile_quant_kernel<F, W, BOTH>;                                                                     \
+    auto kernel = mx_tile_quant_kernel<F, W>;                                                                           \
     B200Q_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDualSmem));                   \
     kernel<<<grid, kThreads, kDualSmem, st>>>(x, rows, cols, ld, codes_r, sf_r, codes_c, sf_c, swz);                    \
   } while (0)
@@ -672,8 +673,6 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
   if ((rc = zero_sf_pads(sf, outer, contraction / 32, sf_layout, st))) return rc;
   if (axis == 1)
     launch_rowwise_block<MODE_MX>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr, st);
-  else if ((cols & 31) == 0)   // whole 32-column runs: the 128 x 128 tile kernel with packed column pairs
-    return launch_mx_tile_quant<false>((const uint16_t*)x, rows, cols, ld, fmt, nullptr, nullptr, (uint8_t*)codes, (uint8_t*)sf, sf_layout, st);
   else
     launch_transpose<MODE_MX>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, (uint8_t*)sf, sf_layout, nullptr, nullptr, nullptr, st);
   B200Q_CUDA(cudaGetLastError());
@@ -693,7 +692,7 @@ int b200q_quantize_mxfp8_dual(const void* x, int64_t rows, int64_t cols, int64_t
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf_row, rows, cols / 32, sf_layout, st))) return rc;
   if ((rc = zero_sf_pads(sf_col, cols, rows / 32, sf_layout, st))) return rc;
-  return launch_mx_tile_quant<true>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row, (uint8_t*)codes_col,
+  return launch_mx_tile_quant((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row, (uint8_t*)codes_col,
                                     (uint8_t*)sf_col, sf_layout, st);
 }
 
