@@ -47,7 +47,8 @@ MOE_EXPERTS, MOE_TOPK = 64, 4
 NOMINAL_TFLOPS = {"mxfp8": 4500.0, "fp8": 4500.0, "nvfp4": 9000.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the ncu captures summarised
 # under profiles/ (null until captured for that workload)
-GEMM_DRAM_TRAFFIC = {"mxfp8_square_8192": 462.7e6, "nvfp4_square_8192": 258.3e6}   # one-CTA kernel captures
+GEMM_DRAM_TRAFFIC = {"mxfp8_square_8192": 475.8e6, "nvfp4_square_8192": 273.4e6,
+                     "fp8_rowwise_linear_16384x2048x2048": 55.1e6}   # gemm_pair_kernel captures
 
 
 def measured_peaks():
