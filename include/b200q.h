@@ -68,6 +68,16 @@ int b200q_quantize_fp8_tensorwise(const void* x, int64_t rows, int64_t cols, int
                                   int fmt, const float* tensor_amax, void* codes, float* scale_out,
                                   void* stream);
 
+/* quantize_int8(x, qmax, dim) of src/quant/int8.py:9-19, the int8 series (int8 .. int4 in an int8
+ * container; qmax = 127, 63, 31, 15, 7 as in src/quant/utils.py:19): scale = max(amax/qmax, 1e-12),
+ * codes = clamp(round_half_even(x/scale), +-qmax).  Same axis / shape rules as b200q_quantize_fp8 and
+ * b200q_quantize_fp8_tensorwise; codes are int8. */
+int b200q_quantize_int8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int qmax,
+                        void* codes, float* scales, void* stream);
+int b200q_quantize_int8_tensorwise(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose,
+                                   int qmax, const float* tensor_amax, void* codes, float* scale_out,
+                                   void* stream);
+
 /* MXFP8: 32-element blocks along the contraction dimension, fp8 codes, one E8M0 byte per
  * block (2^e = smallest power of two >= max(amax/qmax, 1e-12)).  No counterpart in the
  * reference yet (TODO at src/quant/__init__.py:26); extends src/quant/fp8.py:16-32.
@@ -113,6 +123,14 @@ int b200q_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t ld, 
 int b200q_gemm_fp8(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a,
                    int a_scale_is_scalar, const float* scale_b, int b_scale_is_scalar, int64_t M,
                    int64_t N, int64_t K, void* D, int64_t ldd, void* stream);
+
+/* Stands for torch._int_mm and the scaling after it at src/quant/int8.py:49-53:
+ * D = bf16((float(A . B^T) * scale_a) * scale_b) with the integer product accumulated exactly in
+ * 32 bits (tcgen05.mma kind::i8), so the result equals the reference's bit for bit.  A, B: int8
+ * codes; scales as for b200q_gemm_fp8.  K % 16 == 0. */
+int b200q_gemm_int8(const void* A, const void* B, const float* scale_a, int a_scale_is_scalar,
+                    const float* scale_b, int b_scale_is_scalar, int64_t M, int64_t N, int64_t K,
+                    void* D, int64_t ldd, void* stream);
 
 /* Block-scaled MXFP8 GEMM (the `_gemm` seam, src/quant/linear.py:27-56, for MX formats).
  * K % 32 == 0. */

@@ -77,6 +77,50 @@ def fp8_gemm_ref(a, b, out_dtype, a_dtype, b_dtype, rowwise=False):
 
 
 # ---------------------------------------------------------------------------
+# int8 series: symmetric integers of 8..4 bits in an int8 container (reference code exists)
+# ---------------------------------------------------------------------------
+INT_QMAX = {"int8": 127, "int7": 63, "int6": 31, "int5": 15, "int4": 7}   # src/quant/utils.py:19
+
+
+def quantize_int8(x: torch.Tensor, qmax: int, dim: int | None = None):
+    """Restates ``quantize_int8`` (src/quant/int8.py:9-19): ``scale = max(amax / qmax, 1e-12)``
+    in fp32, ``codes = clamp(round(x.float() / scale), +-qmax)`` as int8 (``torch.round`` rounds
+    halves to even)."""
+    if dim is None:
+        amax = x.abs().max().float()
+    else:
+        amax = x.abs().amax(dim=dim, keepdim=True).float()
+    scale = (amax / qmax).clamp_min(EPS)
+    codes = torch.round(x.float() / scale).clamp(-qmax, qmax).to(torch.int8)
+    return codes, scale
+
+
+def fake_quantize_int8(x: torch.Tensor, qmax: int, dim: int | None = None):
+    """Restates ``fake_quantize_int8`` (src/quant/int8.py:22-26)."""
+    codes, scale = quantize_int8(x, qmax, dim)
+    return (codes.float() * scale).to(x.dtype)
+
+
+def int8_gemm_ref(a, b, out_dtype, a_qmax, b_qmax, rowwise=False):
+    """The reference's int8 GEMM with the real kernel's arithmetic (src/quant/int8.py:49-53):
+    integer codes, exact integer accumulation (what ``torch._int_mm`` returns; it lives in
+    torch 2.10 / cuBLAS, outside the reference checkout), then
+    ``(acc.float() * a_scale * b_scale).to(out_dtype)``."""
+    ca, sa = quantize_int8(a, a_qmax, dim=-1 if rowwise else None)
+    cb, sb = quantize_int8(b, b_qmax, dim=0 if rowwise else None)
+    acc = (ca.to(torch.int64) @ cb.to(torch.int64)).to(torch.int32)
+    return (acc.float() * sa * sb).to(out_dtype)
+
+
+def int8_gemm_fake_ref(a, b, out_dtype, a_qmax, b_qmax, rowwise=False):
+    """The reference's CPU / fallback form of the same GEMM (src/quant/int8.py:41-47):
+    fake-quantise both operands and matmul in their dtype."""
+    fa = fake_quantize_int8(a, a_qmax, dim=-1 if rowwise else None)
+    fb = fake_quantize_int8(b, b_qmax, dim=0 if rowwise else None)
+    return (fa @ fb).to(out_dtype)
+
+
+# ---------------------------------------------------------------------------
 # MXFP8: 32-element blocks, E4M3/E5M2 codes, E8M0 power-of-two scale
 # ---------------------------------------------------------------------------
 

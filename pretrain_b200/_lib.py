@@ -24,6 +24,9 @@ SIGNATURES = {
     "b200q_quantize_fp8_tensorwise": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp, _vp]),
     "b200q_quantize_mxfp8": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _int, _vp]),
     "b200q_quantize_nvfp4": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp, _vp]),
+    "b200q_quantize_int8": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]),
+    "b200q_quantize_int8_tensorwise": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp, _vp]),
+    "b200q_gemm_int8": (_int, [_vp, _vp, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_fp8": (_int, [_vp, _int, _vp, _int, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_mxfp8": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),

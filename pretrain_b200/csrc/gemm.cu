@@ -2,6 +2,10 @@
 //
 //   KIND_F8  : fp8 codes, fp32 scale per row of A and per row of B applied in the epilogue
 //              (stands for torch._scaled_mm, src/quant/fp8.py:59-65)
+//   KIND_I8  : int8-series codes, tcgen05.mma kind::i8 with 32-bit integer accumulators, the
+//              same fp32 row / column scales in the epilogue (stands for torch._int_mm and the
+//              scaling after it, src/quant/int8.py:49-53); integer accumulation is exact, so the
+//              result equals the reference's bit for bit
 //   KIND_MX  : MXFP8, tcgen05.mma kind::mxf8f6f4.block_scale (E8M0 scale per 32 elements)
 //   KIND_NV  : NVFP4, tcgen05.mma kind::mxf4nvf4.block_scale.block16 (E4M3 scale per 16
 //              elements), fp32 tensor scales applied in the epilogue
@@ -29,7 +33,9 @@
 namespace b200q {
 namespace {
 
-enum { KIND_F8 = 0, KIND_MX = 1, KIND_NV = 2 };
+enum { KIND_F8 = 0, KIND_MX = 1, KIND_NV = 2, KIND_I8 = 3 };
+// kinds whose scales are one fp32 per output row and column, applied in the epilogue
+__host__ __device__ constexpr bool row_scaled(int kind) { return kind == KIND_F8 || kind == KIND_I8; }
 
 constexpr int BM = 128;
 constexpr int BKB = 128;                 // bytes of K per stage (= one 128-byte swizzle row)
@@ -50,8 +56,8 @@ struct Cfg {
   static constexpr int K_ATOMS = KIND == KIND_NV ? 4 : 1;                  // 512-byte SF atoms per K step and row group
   static constexpr int A_BYTES = BM * BKB;
   static constexpr int B_BYTES = BN * BKB;
-  static constexpr int SFA_BYTES = KIND == KIND_F8 ? 0 : K_ATOMS * 512;
-  static constexpr int SFB_BYTES = KIND == KIND_F8 ? 0 : NB_ATOMS * K_ATOMS * 512;
+  static constexpr int SFA_BYTES = row_scaled(KIND) ? 0 : K_ATOMS * 512;
+  static constexpr int SFB_BYTES = row_scaled(KIND) ? 0 : NB_ATOMS * K_ATOMS * 512;
   static constexpr int STAGE_BYTES = ((A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024) * 1024;
   // Two staging blocks per epilogue warp unless giving one up buys another pipeline stage
   // (NVFP4 at width 256: 4 stages of 54 KB only fit beside 8 KB of staging).
@@ -61,8 +67,8 @@ struct Cfg {
   static constexpr int EPI_BYTES = EPI_BUFS * kEpiBytes1;
   static constexpr int STAGES_RAW = EPI_BUFS == 1 ? STAGES_1BUF : STAGES_2BUF;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int SFA_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS;
-  static constexpr int SFB_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS * NB_ATOMS;
+  static constexpr int SFA_COLS = row_scaled(KIND) ? 0 : 4 * K_ATOMS;
+  static constexpr int SFB_COLS = row_scaled(KIND) ? 0 : 4 * K_ATOMS * NB_ATOMS;
   // Two accumulators always.  When two whole ones and the scale factors do not fit in the 512
   // columns (width 256, block-scaled kinds) the second accumulator starts OVL columns early, so
   // the two share OVL columns: the epilogue reads that shared strip of a tile first and only
@@ -143,7 +149,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
   const int total_tiles = num_m * p.num_n;
 
-  if (KIND != KIND_F8) {
+  if (!row_scaled(KIND)) {
     // Scale-factor stage buffers start as zeros so that atoms beyond the end of K (never
     // loaded) multiply the zero-filled operand tail by a finite scale.
     for (int s = 0; s < C::STAGES; ++s) {
@@ -185,7 +191,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           const uint32_t fb = full_bar(stage);
           uint32_t tx = C::A_BYTES + C::B_BYTES;
-          if (KIND != KIND_F8) {
+          if (!row_scaled(KIND)) {
             // atoms of this K step that exist in the (padded) scale-factor buffers
             const int ka0 = k * C::K_ATOMS;
             const int ka = p.sf_kt - ka0 < C::K_ATOMS ? p.sf_kt - ka0 : C::K_ATOMS;
@@ -238,7 +244,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-          if (KIND != KIND_F8) {
+          if (!row_scaled(KIND)) {
             const uint32_t ssfa = sb + C::B_BYTES, ssfb = ssfa + C::SFA_BYTES;
 #pragma unroll
             for (int a = 0; a < C::K_ATOMS; ++a) {
@@ -254,7 +260,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int kk = 0; kk < 4; ++kk) {
             const uint32_t accum = (k | kk) != 0;
             const uint64_t adv = (uint64_t)(kk * 32 >> 4);   // 32 bytes of K per instruction
-            if (KIND == KIND_F8) {
+            if (KIND == KIND_I8) {
+              ptx::mma_i8(d_tmem, da + adv, db + adv, ptx::idesc_i8(BM, BN), accum);
+            } else if (KIND == KIND_F8) {
               ptx::mma_f8(d_tmem, da + adv, db + adv, ptx::idesc_f8(p.a_fmt, p.b_fmt, BM, BN), accum);
             } else if (KIND == KIND_MX) {
               ptx::mma_mxf8(d_tmem, da + adv, db + adv, ptx::idesc_block_scaled(p.a_fmt, p.b_fmt, 1, BM, BN, kk), accum,
@@ -294,7 +302,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int64_t row0 = (int64_t)m_blk * BM + q * 32, row = row0 + lane;
       const int64_t col0 = (int64_t)n_blk * BN;
       float row_scale = alpha;
-      if (KIND == KIND_F8) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
+      if (row_scaled(KIND)) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
       // Block order: natural, except that an overlapped accumulator 0 is read from its last
@@ -313,7 +321,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         epilogue_tile_glu<NBLK, RELEASE_AFTER, 2>(taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, p.M,
                                                   p.N, p.glu, release);
       else
-        epilogue_tile<KIND == KIND_F8, NBLK, C::EPI_BUFS, RELEASE_AFTER>(
+        epilogue_tile<row_scaled(KIND), KIND == KIND_I8, NBLK, C::EPI_BUFS, RELEASE_AFTER>(
             taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
             release);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
@@ -440,7 +448,7 @@ int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
     const double mainloop = num_k * kstep + 600.0, epi = 300.0 + (bn / 32) * 220.0;
     // the epilogue hides behind the next main loop; at width 256 with scale factors the MMA
     // still waits for the first epilogue block(s) of the previous tile
-    const double per_tile = std::max(mainloop + (bn == 256 && KIND != KIND_F8 ? 500.0 : 0.0), epi);
+    const double per_tile = std::max(mainloop + (bn == 256 && !row_scaled(KIND) ? 500.0 : 0.0), epi);
     const double cost = waves * per_tile;
     if (cost < best * 0.995) { best = cost; best_bn = bn; }
   }
@@ -546,6 +554,17 @@ int b200q_gemm_fp8(const void* A, int a_fmt, const void* B, int b_fmt, const flo
   p.scale_a = scale_a; p.scale_b = scale_b; p.a_scalar = a_scale_is_scalar; p.b_scalar = b_scale_is_scalar;
   p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.M = M; p.N = N; p.K = K;
   return dispatch<KIND_F8>(A, B, one_output(D), ldd, N, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_int8(const void* A, const void* B, const float* scale_a, int a_scale_is_scalar, const float* scale_b,
+                    int b_scale_is_scalar, int64_t M, int64_t N, int64_t K, void* D, int64_t ldd, void* stream) {
+  int rc = check_gemm(A, B, D, M, N, K, ldd, 16);
+  if (rc) return rc;
+  if (scale_a == nullptr || scale_b == nullptr) return B200Q_ERR_INVALID_ARG;
+  GemmParams p = {};
+  p.scale_a = scale_a; p.scale_b = scale_b; p.a_scalar = a_scale_is_scalar; p.b_scalar = b_scale_is_scalar;
+  p.M = M; p.N = N; p.K = K;
+  return dispatch<KIND_I8>(A, B, one_output(D), ldd, N, p, (cudaStream_t)stream);
 }
 
 int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,

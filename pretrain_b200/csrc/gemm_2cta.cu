@@ -28,15 +28,15 @@ template <int KIND>
 struct PCfg {
   static constexpr int K_ATOMS = KIND == KIND_NV ? 4 : 1;
   static constexpr int A_BYTES = BM * BKB, B_BYTES = HALF_N * BKB;
-  static constexpr int SFA_BYTES = KIND == KIND_F8 ? 0 : K_ATOMS * 512;
-  static constexpr int SFB_BYTES = KIND == KIND_F8 ? 0 : 2 * K_ATOMS * 512;       // both halves of B's columns
+  static constexpr int SFA_BYTES = row_scaled(KIND) ? 0 : K_ATOMS * 512;
+  static constexpr int SFB_BYTES = row_scaled(KIND) ? 0 : 2 * K_ATOMS * 512;       // both halves of B's columns
   static constexpr int TX_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;      // per CTA and K step
   static constexpr int STAGE_BYTES = ((TX_BYTES + 1023) / 1024) * 1024;
   static constexpr int EPI_BYTES = 2 * kEpiBytes1;
   static constexpr int STAGES_RAW = (kSmemBudget - 2048 - EPI_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int SFA_COLS = KIND == KIND_F8 ? 0 : 4 * K_ATOMS;
-  static constexpr int SFB_COLS = KIND == KIND_F8 ? 0 : 8 * K_ATOMS;
+  static constexpr int SFA_COLS = row_scaled(KIND) ? 0 : 4 * K_ATOMS;
+  static constexpr int SFB_COLS = row_scaled(KIND) ? 0 : 8 * K_ATOMS;
   static constexpr int SF_COLS = SFA_COLS + SFB_COLS;
   static constexpr bool OVERLAP = SF_COLS > 0;     // two 256-column accumulators + scale columns > 512
   static constexpr int OVL = OVERLAP ? ((SF_COLS + EPI_COLS - 1) / EPI_COLS) * EPI_COLS : 0;
@@ -132,7 +132,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           ptx::mbar_expect_tx_cluster(fb, C::TX_BYTES);
           ptx::tma_load_2d_pair(sa, &tmap_a, k * BKB, row0, fb);
           ptx::tma_load_2d_pair(sb, &tmap_b, k * BKB, brow0, fb);
-          if (KIND != KIND_F8) {
+          if (!row_scaled(KIND)) {
             // scale buffers viewed as rows of 256 bytes: a 512-byte atom is 2 rows, the K_ATOMS atoms of
             // one K step and row group are contiguous
             const uint32_t ssfa = sb + C::B_BYTES, ssfb = ssfa + C::SFA_BYTES;
@@ -167,7 +167,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-          if (KIND != KIND_F8) {
+          if (!row_scaled(KIND)) {
             const uint32_t ssfa = sb + C::B_BYTES, ssfb = ssfa + C::SFA_BYTES;
 #pragma unroll
             for (int a = 0; a < C::K_ATOMS; ++a) {
@@ -183,7 +183,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int kk = 0; kk < 4; ++kk) {
             const uint32_t accum = (k | kk) != 0;
             const uint64_t adv = (uint64_t)(kk * 32 >> 4);
-            if (KIND == KIND_F8) {
+            if (KIND == KIND_I8) {
+              ptx::mma_i8_pair(d_tmem, da + adv, db + adv, ptx::idesc_i8(256, BN), accum);
+            } else if (KIND == KIND_F8) {
               ptx::mma_f8_pair(d_tmem, da + adv, db + adv, ptx::idesc_f8(p.a_fmt, p.b_fmt, 256, BN), accum);
             } else if (KIND == KIND_MX) {
               ptx::mma_mxf8_pair(d_tmem, da + adv, db + adv, ptx::idesc_block_scaled(p.a_fmt, p.b_fmt, 1, 256, BN, kk), accum,
@@ -222,12 +224,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int64_t row0 = (int64_t)mp * 256 + cta * BM + q * 32, row = row0 + lane;
       const int64_t col0 = (int64_t)n_blk * BN;
       float row_scale = alpha;
-      if (KIND == KIND_F8) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
+      if (row_scaled(KIND)) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
       constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;
       const uint32_t release_bar = tempty_bar(acc) & ptx::kLeaderMask;       // the leader's barrier, from either CTA
-      epilogue_tile<KIND == KIND_F8, NBLK, 2, RELEASE_AFTER>(
+      epilogue_tile<row_scaled(KIND), KIND == KIND_I8, NBLK, 2, RELEASE_AFTER>(
           taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
           [&]() {
             ptx::tc_fence_before();
@@ -274,7 +276,7 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, gp.N, row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_out_maps(&md, D, gp.M, gp.N, ldd))) return rc;
   int sf_kt = 0;
-  if (KIND != KIND_F8) {
+  if (!row_scaled(KIND)) {
     // scale buffers as rows of 256 bytes (two rows per 512-byte atom); box = the atoms of one K step
     const int64_t nblk = KIND == KIND_MX ? gp.K / 32 : gp.K / 16;
     sf_kt = (int)((nblk + 3) / 4);

@@ -32,7 +32,9 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
 // `rev` walks the blocks from the last to the first (used when the tile's LAST columns are the ones
 // to hand back first); `release` is called once, after block number RELEASE_AFTER (in walking
 // order) has been read from tensor memory.
-template <bool COL_SCALE, int NBLK, int EPI_BUFS, int RELEASE_AFTER, class Release>
+// ACC_INT: the accumulators are 32-bit integers (kind::i8); they are converted to fp32 with
+// round-to-nearest, then scaled by the row's and the column's scale in that order.
+template <bool COL_SCALE, bool ACC_INT, int NBLK, int EPI_BUFS, int RELEASE_AFTER, class Release>
 __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t row0, int64_t col0, int64_t M, int64_t N,
                                               float row_scale, const float* __restrict__ scale_b, int b_scalar,
                                               const OutMaps* outs, uint32_t epi_s, uint8_t* epi_g, int& buf, int lane,
@@ -51,7 +53,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t 
     uint32_t o[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      float lo = u2f(r[2 * i]) * row_scale, hi = u2f(r[2 * i + 1]) * row_scale;
+      float lo = (ACC_INT ? __int2float_rn((int)r[2 * i]) : u2f(r[2 * i])) * row_scale;
+      float hi = (ACC_INT ? __int2float_rn((int)r[2 * i + 1]) : u2f(r[2 * i + 1])) * row_scale;
       if (COL_SCALE) {
         lo *= __shfl_sync(0xFFFFFFFFu, i < 16 ? sb0 : sb1, (2 * i) & 31);
         hi *= __shfl_sync(0xFFFFFFFFu, i < 16 ? sb0 : sb1, (2 * i + 1) & 31);

@@ -23,7 +23,7 @@
 
 namespace b200q {
 
-enum Fp8Fmt : int { FMT_E4M3 = 0, FMT_E5M2 = 1 };
+enum Fp8Fmt : int { FMT_E4M3 = 0, FMT_E5M2 = 1, FMT_I8 = 2 };   // FMT_I8: the int8 series (qmax is a run-time value)
 
 constexpr float kEps = 1e-12f;            // src/quant/fp8.py:6
 constexpr int kMxFloorExp = -39;          // 2^-39 is the smallest power of two >= 1e-12
@@ -141,6 +141,31 @@ B200Q_HD float e4m3_to_float(uint8_t b) {
 B200Q_HD uint8_t cvt_e2m1x2(float lo, float hi) {
   float2 v; v.x = lo; v.y = hi;
   return (uint8_t)__nv_cvt_float2_to_fp4x2(v, __NV_E2M1, cudaRoundNearest);
+}
+
+// ---- int8 series (src/quant/int8.py:9-19) ---------------------------------------------------------
+// scale = max(amax / qmax, 1e-12); codes = clamp(round_half_even(x / scale), +-qmax) as int8.
+B200Q_HD float int_scale_from_amax(float amax, float qmax) {
+  float s = div_rn(amax, qmax);
+  return s < kEps ? kEps : s;
+}
+B200Q_HD uint32_t cvt_i8(float q, float qmax) {
+#if defined(__CUDA_ARCH__)
+  float r = rintf(q);
+#else
+  float r = nearbyintf(q);
+#endif
+  r = r < -qmax ? -qmax : (r > qmax ? qmax : r);
+  return (uint32_t)(int)r & 0xFFu;
+}
+// Scale and four packed codes for any of the per-row / per-column / per-tensor formats; `fmt` is a
+// compile-time constant at every call site, so the branch folds.
+B200Q_HD float scale_from_amax(float amax, int fmt, float qmax) {
+  return fmt == FMT_I8 ? int_scale_from_amax(amax, qmax) : fp8_scale_from_amax(amax, fmt);
+}
+B200Q_HD uint32_t cvt_codes_x4(float a, float b, float c, float d, int fmt, float qmax) {
+  if (fmt == FMT_I8) return cvt_i8(a, qmax) | (cvt_i8(b, qmax) << 8) | (cvt_i8(c, qmax) << 16) | (cvt_i8(d, qmax) << 24);
+  return cvt_fp8x4(a, b, c, d, fmt);
 }
 
 // ---- MXFP8 block scale -------------------------------------------------------------

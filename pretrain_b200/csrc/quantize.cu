@@ -148,7 +148,7 @@ template <int NVEC, int FMT>
 __global__ void __launch_bounds__(kThreads)
 rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                    uint8_t* __restrict__ codes, float* __restrict__ scales, const float* __restrict__ tensor_amax,
-                   float* __restrict__ tensor_scale_out, int wpr) {
+                   float* __restrict__ tensor_scale_out, int wpr, float qmax) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int fmt = FMT;
   const int grp = warp / wpr, wig = warp - grp * wpr, rpc = kWarps / wpr;
@@ -185,7 +185,7 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
       for (int j = 0; j < wpr; ++j) amax = fmaxf(amax, smax[it & 1][grp * wpr + j]);
     }
     if (tensor_amax) amax = *tensor_amax;
-    const float scale = fp8_scale_from_amax(amax, fmt);
+    const float scale = scale_from_amax(amax, fmt, qmax);
     const float rcp = rcp_rn(scale);
     if (lane == 0 && wig == 0 && live) {
       if (tensor_amax == nullptr) scales[row] = scale;
@@ -201,8 +201,8 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = quot_for_cast(f[j], scale, rcp);
         uint2 o;
-        o.x = cvt_fp8x4(f[0], f[1], f[2], f[3], fmt);
-        o.y = cvt_fp8x4(f[4], f[5], f[6], f[7], fmt);
+        o.x = cvt_codes_x4(f[0], f[1], f[2], f[3], fmt, qmax);
+        o.y = cvt_codes_x4(f[4], f[5], f[6], f[7], fmt, qmax);
         if (live && c < cols) *reinterpret_cast<uint2*>(cr + c) = o;
       }
     } else if (live) {
@@ -212,8 +212,8 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = quot_for_cast(f[j], scale, rcp);
         uint2 o;
-        o.x = cvt_fp8x4(f[0], f[1], f[2], f[3], fmt);
-        o.y = cvt_fp8x4(f[4], f[5], f[6], f[7], fmt);
+        o.x = cvt_codes_x4(f[0], f[1], f[2], f[3], fmt, qmax);
+        o.y = cvt_codes_x4(f[4], f[5], f[6], f[7], fmt, qmax);
         *reinterpret_cast<uint2*>(cr + c) = o;
       }
     }
@@ -259,9 +259,9 @@ col_amax_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int6
   }
 }
 
-__global__ void amax_to_scale_kernel(float* __restrict__ scales, int64_t n, int fmt) {
+__global__ void amax_to_scale_kernel(float* __restrict__ scales, int64_t n, int fmt, float qmax) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) scales[i] = fp8_scale_from_amax(scales[i], fmt);
+  if (i < n) scales[i] = scale_from_amax(scales[i], fmt, qmax);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(kThreads)
 transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                        uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, int swz,
                        const float* __restrict__ col_scales, const float* __restrict__ tensor_amax,
-                       float* __restrict__ tensor_scale_out) {
+                       float* __restrict__ tensor_scale_out, float qmax) {
   __shared__ __align__(16) uint16_t tin[kTR * kTC];
   constexpr int OUT_PITCH = (MODE == MODE_NV ? kTR / 2 : kTR) + 16;
   __shared__ __align__(16) uint8_t tout[kTC * OUT_PITCH];
@@ -299,7 +299,7 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
     if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) *tensor_scale_out = s_t;
   }
   if (MODE == MODE_FP8 && tensor_amax != nullptr) {
-    t_scale = fp8_scale_from_amax(*tensor_amax, fmt);
+    t_scale = scale_from_amax(*tensor_amax, fmt, qmax);
     if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) *tensor_scale_out = t_scale;
   }
   __syncthreads();
@@ -350,8 +350,8 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
     uint32_t o[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      o[i] = cvt_fp8x4(quot_for_cast(f[4 * i], scale, rcp), quot_for_cast(f[4 * i + 1], scale, rcp),
-                       quot_for_cast(f[4 * i + 2], scale, rcp), quot_for_cast(f[4 * i + 3], scale, rcp), fmt);
+      o[i] = cvt_codes_x4(quot_for_cast(f[4 * i], scale, rcp), quot_for_cast(f[4 * i + 1], scale, rcp),
+                          quot_for_cast(f[4 * i + 2], scale, rcp), quot_for_cast(f[4 * i + 3], scale, rcp), fmt, qmax);
     uint4* dst = reinterpret_cast<uint4*>(&tout[c * OUT_PITCH + 32 * j]);
     dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
     dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
@@ -529,12 +529,15 @@ void launch_rowwise_block(const uint16_t* x, int64_t rows, int64_t cols, int64_t
 }
 template <int MODE>
 void launch_transpose(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes, uint8_t* sf, int swz,
-                      const float* col_scales, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st) {
+                      const float* col_scales, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st,
+                      float qmax = 0.f) {
   dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
-  if (MODE == MODE_NV || fmt == FMT_E4M3)
-    transpose_quant_kernel<MODE, FMT_E4M3><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out);
+  if (MODE == MODE_FP8 && fmt == FMT_I8)
+    transpose_quant_kernel<MODE_FP8, FMT_I8><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
+  else if (MODE == MODE_NV || fmt == FMT_E4M3)
+    transpose_quant_kernel<MODE, FMT_E4M3><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
   else
-    transpose_quant_kernel<MODE, FMT_E5M2><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out);
+    transpose_quant_kernel<MODE, FMT_E5M2><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
 }
 
 }  // namespace
@@ -588,7 +591,8 @@ int b200q_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, float* ama
 }
 
 static int launch_rowwise_fp8(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes,
-                              float* scales, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st) {
+                              float* scales, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st,
+                              float qmax = 0.f) {
   // warps per row: enough that a lane keeps at most 4 vectors (32 elements), up to the whole CTA
   const int64_t nv = cols / 8;
   int wpr = 1;
@@ -599,9 +603,11 @@ static int launch_rowwise_fp8(const uint16_t* x, int64_t rows, int64_t cols, int
 #define B200Q_LAUNCH(NV)                                                                                                   \
   do {                                                                                                                     \
     if (fmt == FMT_E4M3)                                                                                                   \
-      rowwise_fp8_kernel<NV, FMT_E4M3><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr); \
+      rowwise_fp8_kernel<NV, FMT_E4M3><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr, qmax); \
+    else if (fmt == FMT_E5M2)                                                                                              \
+      rowwise_fp8_kernel<NV, FMT_E5M2><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr, qmax); \
     else                                                                                                                   \
-      rowwise_fp8_kernel<NV, FMT_E5M2><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr); \
+      rowwise_fp8_kernel<NV, FMT_I8><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr, qmax); \
   } while (0)
   if (nvec <= 1) B200Q_LAUNCH(1);
   else if (nvec <= 2) B200Q_LAUNCH(2);
@@ -634,9 +640,56 @@ int b200q_quantize_fp8(const void* x, int64_t rows, int64_t cols, int64_t ld, in
     col_amax_kernel<<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, (unsigned int*)scales);
     B200Q_CUDA(cudaGetLastError());
   }
-  amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, fmt);
+  amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, fmt, 0.f);
   B200Q_CUDA(cudaGetLastError());
   launch_transpose<MODE_FP8>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, nullptr, 0, scales, nullptr, nullptr, st);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+// int8 series: the FP8 kernels with integer rounding and qmax = 2^(bits-1) - 1 (src/quant/int8.py:9-19)
+int b200q_quantize_int8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int qmax, void* codes, float* scales,
+                        void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes == nullptr || scales == nullptr || (axis != 0 && axis != 1) || qmax < 1 || qmax > 127) return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (axis == 1)
+    return launch_rowwise_fp8((const uint16_t*)x, rows, cols, ld, FMT_I8, (uint8_t*)codes, scales, nullptr, nullptr, st, (float)qmax);
+  if (rows & 15) return B200Q_ERR_SHAPE;
+  B200Q_CUDA(cudaMemsetAsync(scales, 0, (size_t)cols * sizeof(float), st));
+  {
+    dim3 grid((unsigned)((cols / 8 + 31) / 32), 1);
+    int64_t ymax = (rows + kWarps * 4 - 1) / (kWarps * 4);
+    int64_t want = (int64_t)kNumSMs * 4 / grid.x + 1;
+    grid.y = (unsigned)(want < ymax ? want : ymax);
+    col_amax_kernel<<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, (unsigned int*)scales);
+    B200Q_CUDA(cudaGetLastError());
+  }
+  amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, FMT_I8, (float)qmax);
+  B200Q_CUDA(cudaGetLastError());
+  launch_transpose<MODE_FP8>((const uint16_t*)x, rows, cols, ld, FMT_I8, (uint8_t*)codes, nullptr, 0, scales, nullptr, nullptr, st,
+                             (float)qmax);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_quantize_int8_tensorwise(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose, int qmax,
+                                   const float* tensor_amax, void* codes, float* scale_out, void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes == nullptr || tensor_amax == nullptr || scale_out == nullptr || qmax < 1 || qmax > 127) return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!transpose)
+    return launch_rowwise_fp8((const uint16_t*)x, rows, cols, ld, FMT_I8, (uint8_t*)codes, nullptr, tensor_amax, scale_out, st,
+                              (float)qmax);
+  if (rows & 15) return B200Q_ERR_SHAPE;
+  launch_transpose<MODE_FP8>((const uint16_t*)x, rows, cols, ld, FMT_I8, (uint8_t*)codes, nullptr, 0, nullptr, tensor_amax, scale_out, st,
+                             (float)qmax);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -158,6 +158,10 @@ __device__ __forceinline__ uint64_t smem_desc_sf(uint32_t saddr) { return smem_d
 __host__ __device__ constexpr uint32_t idesc_f8(int a_fmt, int b_fmt, int M, int N) {
   return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// kind::i8: signed 8-bit operands (format 1), 32-bit integer accumulator (format 2 in bits [4,6)).
+__host__ __device__ constexpr uint32_t idesc_i8(int M, int N) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
 // Instruction descriptor, block-scaled kinds.  Bits: [4,6) B scale-factor byte id; [7,10) A
 // format; [10,13) B format; [17,23) N >> 3; [23] scale format (0 = UE4M3, 1 = UE8M0);
 // [24,29) M >> 4; [29,31) A scale-factor byte id.
@@ -172,6 +176,14 @@ __device__ __forceinline__ void mma_f8(uint32_t d, uint64_t a, uint64_t b, uint3
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_i8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -246,6 +258,14 @@ __device__ __forceinline__ void mma_f8_pair(uint32_t d, uint64_t a, uint64_t b, 
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_i8_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }

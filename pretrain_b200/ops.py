@@ -74,6 +74,33 @@ def quantize_fp8_tensorwise(x: torch.Tensor, fmt, transpose: bool = False, tenso
     return codes, scale
 
 
+def quantize_int8(x: torch.Tensor, qmax: int, axis: int):
+    """Per-row (axis=1) or per-column (axis=0, codes transposed) int8-series codes.  Returns
+    (codes int8 [outer, C], scales fp32 [outer])."""
+    x = _mat(x)
+    rows, cols = x.shape
+    outer, c = (rows, cols) if axis == 1 else (cols, rows)
+    codes = torch.empty(outer, c, dtype=torch.int8, device=x.device)
+    scales = torch.empty(outer, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().b200q_quantize_int8(x.data_ptr(), rows, cols, x.stride(0), axis, int(qmax), codes.data_ptr(),
+                                               scales.data_ptr(), _stream()), "b200q_quantize_int8")
+    return codes, scales
+
+
+def quantize_int8_tensorwise(x: torch.Tensor, qmax: int, transpose: bool = False, tensor_amax: torch.Tensor | None = None):
+    x = _mat(x)
+    rows, cols = x.shape
+    if tensor_amax is None:
+        tensor_amax = amax(x)
+    shape = (cols, rows) if transpose else (rows, cols)
+    codes = torch.empty(shape, dtype=torch.int8, device=x.device)
+    scale = torch.empty(1, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().b200q_quantize_int8_tensorwise(x.data_ptr(), rows, cols, x.stride(0), int(transpose), int(qmax),
+                                                          tensor_amax.data_ptr(), codes.data_ptr(), scale.data_ptr(), _stream()),
+               "b200q_quantize_int8_tensorwise")
+    return codes, scale
+
+
 def quantize_mxfp8(x: torch.Tensor, axis: int = 1, fmt=E4M3, layout: int = SF_SWIZZLED):
     """Returns (codes uint8 [outer, C], sf uint8 flat buffer in `layout`)."""
     x = _mat(x)
@@ -160,6 +187,18 @@ def gemm_fp8(a_codes, a_fmt, b_codes, b_fmt, scale_a, scale_b, out=None):
                                           scale_a.data_ptr(), int(scale_a.numel() == 1), scale_b.data_ptr(),
                                           int(scale_b.numel() == 1), m, n, k, d.data_ptr(), d.stride(0), _stream()),
                "b200q_gemm_fp8")
+    return d
+
+
+def gemm_int8(a_codes, b_codes, scale_a, scale_b, out=None):
+    """D = bf16((float(A . B^T) * scale_a[:, None]) * scale_b[None, :]), int8 codes, exact integer
+    accumulation; scales may have one element."""
+    m, k = a_codes.shape
+    n = b_codes.shape[0]
+    d = _out(m, n, a_codes.device, out)
+    _lib.check(_lib.load().b200q_gemm_int8(a_codes.data_ptr(), b_codes.data_ptr(), scale_a.data_ptr(), int(scale_a.numel() == 1),
+                                           scale_b.data_ptr(), int(scale_b.numel() == 1), m, n, k, d.data_ptr(), d.stride(0),
+                                           _stream()), "b200q_gemm_int8")
     return d
 
 

@@ -9,7 +9,7 @@ import torch.nn as nn
 
 from . import QUANT_PASSTHROUGH, fp8
 from .linear import QuantLinear
-from .utils import is_int8s, resolve_rule
+from .utils import resolve_rule
 
 
 def _quantizes(rule) -> bool:
@@ -25,8 +25,6 @@ def _check_hardware(rules) -> None:
         for fmt in rule.dtype.values():
             if fmt in QUANT_PASSTHROUGH:
                 continue
-            if is_int8s(fmt):
-                raise RuntimeError(f"quant dtype {fmt!r} is not built in this library (FP8 / MXFP8 / NVFP4 only).")
             if not fp8.is_supported():
                 raise RuntimeError(f"quant dtype {fmt!r} requires {fp8.HARDWARE_REQUIREMENT}. "
                                    "Disable quant or run on supported hardware.")

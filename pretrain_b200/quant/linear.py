@@ -15,8 +15,9 @@ from .. import torch_ops as T
 from ..ops import SF_NATURAL, SF_SWIZZLED, fmt_of
 from .config import QuantConfig
 from .fp8 import _k_major, fake_quantize_fp8, fp8_gemm
+from .int8 import fake_quantize_int8, int8_gemm
 from .mx import mxfp8_gemm, nvfp4_gemm
-from .utils import is_fp8, is_int8s, is_mxfp8, is_nvfp4, is_quantized, str_to_dtype_fp8
+from .utils import is_fp8, is_int8s, is_mxfp8, is_nvfp4, is_quantized, str_to_dtype_fp8, str_to_qmax_int8s
 
 _E2M1_LUT = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
 
@@ -49,7 +50,7 @@ def _fake_quant(x, fmt, dim, contraction_dim):
     if is_mxfp8(fmt) or is_nvfp4(fmt):
         return _fake_quant_block(x, fmt, contraction_dim)
     if is_int8s(fmt):
-        raise NotImplementedError("the int8-series formats are outside this build's hot path")
+        return fake_quantize_int8(x, str_to_qmax_int8s(fmt), dim=dim)
     return x
 
 
@@ -61,8 +62,8 @@ def _gemm(a, b, a_fmt, b_fmt, out_dtype, rowwise=False):
         return mxfp8_gemm(a, b, out_dtype, str_to_dtype_fp8(a_fmt), str_to_dtype_fp8(b_fmt))
     if is_nvfp4(a_fmt) and is_nvfp4(b_fmt):
         return nvfp4_gemm(a, b, out_dtype)
-    if is_int8s(a_fmt) or is_int8s(b_fmt):
-        raise NotImplementedError("the int8-series formats are outside this build's hot path")
+    if is_int8s(a_fmt) and is_int8s(b_fmt):
+        return int8_gemm(a, b, out_dtype, str_to_qmax_int8s(a_fmt), str_to_qmax_int8s(b_fmt), rowwise=rowwise)
     if is_quantized(a_fmt):
         a = _fake_quant(a, a_fmt, -1 if rowwise else None, 1)
     if is_quantized(b_fmt):

@@ -58,6 +58,38 @@ def _(x, fmt, transpose):
     return x.new_empty(outer, c, dtype=torch.uint8), x.new_empty(1, dtype=torch.float32)
 
 
+@_lib_def("b200q::quantize_int8", mutates_args=())
+def quantize_int8(x: torch.Tensor, qmax: int, axis: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    return ops.quantize_int8(x, qmax, axis)
+
+
+@quantize_int8.register_fake
+def _(x, qmax, axis):
+    outer, c = _outer_c(x, axis)
+    return x.new_empty(outer, c, dtype=torch.int8), x.new_empty(outer, dtype=torch.float32)
+
+
+@_lib_def("b200q::quantize_int8_tensorwise", mutates_args=())
+def quantize_int8_tensorwise(x: torch.Tensor, qmax: int, transpose: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    return ops.quantize_int8_tensorwise(x, qmax, transpose)
+
+
+@quantize_int8_tensorwise.register_fake
+def _(x, qmax, transpose):
+    outer, c = _outer_c(x, 0 if transpose else 1)
+    return x.new_empty(outer, c, dtype=torch.int8), x.new_empty(1, dtype=torch.float32)
+
+
+@_lib_def("b200q::gemm_int8", mutates_args=())
+def gemm_int8(a: torch.Tensor, b: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor) -> torch.Tensor:
+    return ops.gemm_int8(a, b, scale_a, scale_b)
+
+
+@gemm_int8.register_fake
+def _(a, b, scale_a, scale_b):
+    return a.new_empty(a.shape[0], b.shape[0], dtype=torch.bfloat16)
+
+
 @_lib_def("b200q::quantize_mxfp8", mutates_args=())
 def quantize_mxfp8(x: torch.Tensor, axis: int, fmt: int, layout: int) -> Tuple[torch.Tensor, torch.Tensor]:
     return ops.quantize_mxfp8(x, axis, fmt, layout)

@@ -29,5 +29,10 @@ def golden():
     return dict(np.load(path))
 
 
+@pytest.fixture(scope="session")
+def golden_int8():
+    return dict(np.load(os.path.join(ROOT, "tests", "golden", "ref_int8.npz")))
+
+
 def bf16_from_bits(arr) -> torch.Tensor:
     return torch.from_numpy(np.ascontiguousarray(arr)).view(torch.bfloat16)

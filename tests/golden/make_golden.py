@@ -6,7 +6,8 @@ Run once, in a container that has the reference checkout, as
 
 It imports ``src.quant.fp8`` and ``src.layers.mlp`` from that checkout, feeds them
 seeded inputs and stores what they return (``ref_small.npz``: whole small tensors;
-``ref_digests.json``: sha256 of codes and scales at benchmark sizes).  The tests
+``ref_int8.npz``: the int8-series quantizer of ``src.quant.int8``; ``ref_digests.json``:
+sha256 of codes and scales at benchmark sizes).  The tests
 never need the checkout again: they compare the oracle and the CUDA kernels with
 these files.
 """
@@ -120,6 +121,21 @@ def main(ref_root: str) -> None:
     )
     np.savez_compressed(os.path.join(HERE, "ref_small.npz"), **out)
 
+    # int8 series (src/quant/int8.py:9-26): codes, scales and the fake-quant round trip for every
+    # width and granularity, plus the reference's CPU form of its int8 GEMM (:41-47).
+    from src.quant.int8 import fake_quantize_int8, quantize_int8  # noqa: E402
+    i8: dict[str, np.ndarray] = {}
+    for name, t in (("a", a), ("b", b), ("grad", grad), ("edge", edge)):
+        for qmax in (127, 63, 31, 15, 7):
+            for dimname, dim in (("tensor", None), ("row", -1), ("col", 0)):
+                codes, scale = quantize_int8(t, qmax, dim)
+                i8[f"q_{name}_{qmax}_{dimname}_codes"] = codes.numpy()
+                i8[f"q_{name}_{qmax}_{dimname}_scale"] = scale.reshape(-1).numpy()
+        i8[f"fq_{name}_127_row"] = _bf16_bits(fake_quantize_int8(t, 127, dim=-1))
+    i8["gemm_rowwise_127"] = _bf16_bits(fake_quantize_int8(a, 127, dim=-1) @ fake_quantize_int8(b, 127, dim=0))
+    i8["gemm_tensor_127_7"] = _bf16_bits(fake_quantize_int8(a, 127) @ fake_quantize_int8(b, 7))
+    np.savez_compressed(os.path.join(HERE, "ref_int8.npz"), **i8)
+
     # Digests at benchmark sizes (FP8 training triple: M=16384, K=N=2048).
     x3, w3, dy3 = restate.inputs_fp8_triple()
     dig = {}
@@ -132,7 +148,7 @@ def main(ref_root: str) -> None:
         dig[name] = {"codes": _sha(codes), "scale": _sha(scale), "shape": list(codes.shape)}
     with open(os.path.join(HERE, "ref_digests.json"), "w") as f:
         json.dump(dig, f, indent=1, sort_keys=True)
-    print("wrote", len(out), "arrays and", len(dig), "digests")
+    print("wrote", len(out), "+", len(i8), "arrays and", len(dig), "digests")
 
 
 if __name__ == "__main__":

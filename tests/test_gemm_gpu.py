@@ -188,6 +188,36 @@ def test_cta_pair_kernel(ops, kind, m, n, k):
     _check(out, ref)
 
 
+def _int8_ref(ca, cb, sa, sb):
+    """The reference's formula (src/quant/int8.py:52-53) with an exact integer product."""
+    acc = (ca.double() @ cb.double().t()).to(torch.int32)            # |acc| < 2^31: exact in fp64
+    return (acc.float() * sa.view(-1, 1) * sb.view(1, -1)).bfloat16()
+
+
+@pytest.mark.parametrize("bn,pair", [(0, 0), (128, 0), (192, 0), (256, 0), (0, 1)])
+@pytest.mark.parametrize("m,n,k", [(512, 768, 1024), (300, 520, 256), (128, 256, 96), (2048, 1024, 4096)])
+def test_int8_gemm_is_bit_exact(ops, bn, pair, m, n, k):
+    """kind::i8 accumulates exactly, so every tile width and both kernels must give the reference's
+    bits; per-row scales and one-per-tensor scales."""
+    from pretrain_b200 import _lib
+    a, b = _rand(m, k, 21), _rand(n, k, 22)
+    ca, sa = ops.quantize_int8(a, 127, 1)
+    cb, sb = ops.quantize_int8(b, 31, 1)
+    ta, tsa = ops.quantize_int8_tensorwise(a, 127)
+    tb, tsb = ops.quantize_int8_tensorwise(b, 127)
+    _lib.load().b200q_debug_set_gemm_bn(bn)
+    _lib.load().b200q_debug_set_gemm_pair(1 if pair else -1)       # always / never the CTA-pair kernel
+    try:
+        out = ops.gemm_int8(ca, cb, sa, sb)
+        out_t = ops.gemm_int8(ta, tb, tsa, tsb)
+        ops.device_status()
+    finally:
+        _lib.load().b200q_debug_set_gemm_bn(0)
+        _lib.load().b200q_debug_set_gemm_pair(0)
+    assert torch.equal(out, _int8_ref(ca, cb, sa, sb))
+    assert torch.equal(out_t, _int8_ref(ta, tb, tsa.expand(m), tsb.expand(n)))
+
+
 def test_mxfp8_linear_config_against_cpu_oracle(ops):
     """GPT-2 MLP up-projection (X[8192,768] . W[3072,768]^T, seed 0): the full path against
     the CPU oracle's dequantize-then-matmul on a row sample."""

@@ -77,8 +77,41 @@ def test_mixed_formats_fall_to_fake_quant_matmul():
     cb, sb = R.quantize_mxfp8(b, 0)
     ref = (a.float() @ R.dequantize_mxfp8(cb, sb).t()).bfloat16()
     assert _rel(out.cpu(), ref) < 0.01
-    with pytest.raises(NotImplementedError):
-        _gemm(a.cuda(), b.cuda(), "int8", "int8", torch.bfloat16)
+    out = _gemm(a.cuda(), b.cuda(), "int8", "fp8_e4m3", torch.bfloat16, rowwise=True)      # mixed families
+    ref = (R.fake_quantize_int8(a, 127, dim=-1).float() @ R.fake_quantize_fp8(b, E4, dim=0).float()).bfloat16()
+    assert _rel(out.cpu(), ref) < 0.01
+
+
+@pytest.mark.parametrize("a_fmt,b_fmt", [("int8", "int8"), ("int8", "int4"), ("int6", "int7")])
+@pytest.mark.parametrize("rowwise", [True, False])
+def test_int8_series_gemm_seam_is_bit_exact(a_fmt, b_fmt, rowwise):
+    """Integer accumulation is exact, so the tensor-core GEMM must reproduce the reference's
+    `torch._int_mm` formula (src/quant/int8.py:49-53) bit for bit, in all three layouts."""
+    from pretrain_b200.quant.linear import _gemm
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(256, 192, generator=g).bfloat16()
+    w = (0.05 * torch.randn(128, 192, generator=g)).bfloat16()
+    gr = (1e-2 * torch.randn(256, 128, generator=g)).bfloat16()
+    qa, qb = R.INT_QMAX[a_fmt], R.INT_QMAX[b_fmt]
+    for a, b in ((x, w.t()), (gr, w), (gr.t(), x)):                       # fprop, dgrad, wgrad
+        out = _gemm(a.cuda(), b.cuda(), a_fmt, b_fmt, torch.bfloat16, rowwise=rowwise)
+        ref = R.int8_gemm_ref(a, b, torch.bfloat16, qa, qb, rowwise=rowwise)
+        assert torch.equal(out.cpu(), ref)
+
+
+def test_int8_recipe_module_trains():
+    from pretrain_b200.quant.linear import QuantLinear
+    torch.manual_seed(0)
+    lin = nn.Linear(128, 96, bias=True)
+    q = QuantLinear.from_linear(lin, _cfg("int8", "rowwise")).cuda()
+    x = torch.randn(4, 16, 128)
+    xd = x.cuda().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = q(xd)
+    ref = R.int8_gemm_ref(x.reshape(-1, 128).bfloat16(), lin.weight.detach().bfloat16().t(), torch.bfloat16, 127, 127, True)
+    assert torch.equal(y.reshape(-1, 96).cpu(), (ref + lin.bias.detach().bfloat16()))
+    y.float().square().mean().backward()
+    assert torch.isfinite(xd.grad).all() and torch.isfinite(q.weight.grad).all()
 
 
 @pytest.mark.parametrize("recipe,gran,kind", CASES)

@@ -42,6 +42,31 @@ def test_fake_quant_and_gemm_forms_match_reference_vectors(golden):
     assert np.array_equal(out2.view(torch.int16).numpy(), golden["gemm_rowwise_e5m2_e4m3"])
 
 
+@pytest.mark.parametrize("name", ["a", "b", "grad", "edge"])
+@pytest.mark.parametrize("qmax", [127, 63, 31, 15, 7])
+@pytest.mark.parametrize("dimname,dim", [("tensor", None), ("row", -1), ("col", 0)])
+def test_quantize_int8_matches_reference_vectors(golden, golden_int8, name, qmax, dimname, dim):
+    x = bf16_from_bits(golden[f"in_{name}"])
+    codes, scale = R.quantize_int8(x, qmax, dim)
+    assert np.array_equal(codes.numpy(), golden_int8[f"q_{name}_{qmax}_{dimname}_codes"])
+    assert np.array_equal(scale.reshape(-1).numpy().view(np.uint32),
+                          golden_int8[f"q_{name}_{qmax}_{dimname}_scale"].view(np.uint32))
+
+
+def test_int8_fake_quant_and_gemm_forms_match_reference_vectors(golden, golden_int8):
+    a, b = (bf16_from_bits(golden[f"in_{n}"]) for n in ("a", "b"))
+    assert np.array_equal(R.fake_quantize_int8(a, 127, dim=-1).view(torch.int16).numpy(), golden_int8["fq_a_127_row"])
+    out = R.int8_gemm_fake_ref(a, b, torch.bfloat16, 127, 127, rowwise=True)
+    assert np.array_equal(out.view(torch.int16).numpy(), golden_int8["gemm_rowwise_127"])
+    out = R.int8_gemm_fake_ref(a, b, torch.bfloat16, 127, 7, rowwise=False)
+    assert np.array_equal(out.view(torch.int16).numpy(), golden_int8["gemm_tensor_127_7"])
+    # the real kernel's form (exact integer accumulation, scales applied in fp32) stays within bf16
+    # rounding of the fallback form the reference runs on a CPU
+    exact = R.int8_gemm_ref(a, b, torch.bfloat16, 127, 127, rowwise=True).float()
+    gold = bf16_from_bits(golden_int8["gemm_rowwise_127"]).float()
+    assert (exact - gold).abs().max() / gold.abs().max() < 1e-2
+
+
 def test_digests_at_benchmark_size():
     with open(os.path.join(ROOT, "tests", "golden", "ref_digests.json")) as f:
         dig = json.load(f)

@@ -91,6 +91,41 @@ def test_fp8_matches_reference_golden(ops, golden):
             assert np.array_equal(codes.cpu().numpy(), golden[f"q_{name}_{dname}_tensor_codes"])
 
 
+@pytest.mark.parametrize("name", ["x", "w", "outlier", "wide", "tiny", "zeros", "long", "odd"])
+@pytest.mark.parametrize("qmax", [127, 31, 7])
+def test_int8_series_row_col_tensor(ops, name, qmax):
+    x = CASES[name]
+    xc = x.cuda()
+    codes, scales = ops.quantize_int8(xc, qmax, 1)
+    rc, rs = R.quantize_int8(x, qmax, dim=-1)
+    assert torch.equal(codes.cpu(), rc) and torch.equal(scales.cpu().view(torch.int32), rs.reshape(-1).view(torch.int32))
+    if x.shape[0] % 16 == 0:
+        codes, scales = ops.quantize_int8(xc, qmax, 0)
+        rc, rs = R.quantize_int8(x, qmax, dim=0)
+        assert torch.equal(codes.cpu(), rc.t()) and torch.equal(scales.cpu().view(torch.int32), rs.reshape(-1).view(torch.int32))
+        codes, scale = ops.quantize_int8_tensorwise(xc, qmax, True)
+        rc, rs = R.quantize_int8(x, qmax, None)
+        assert torch.equal(codes.cpu(), rc.t()) and scale.item() == rs.item()
+    codes, scale = ops.quantize_int8_tensorwise(xc, qmax, False)
+    rc, rs = R.quantize_int8(x, qmax, None)
+    assert torch.equal(codes.cpu(), rc) and scale.item() == rs.item()
+
+
+def test_int8_matches_reference_golden(ops, golden, golden_int8):
+    for name in ("a", "b", "grad", "edge"):
+        x = bf16_from_bits(golden[f"in_{name}"]).cuda()
+        for qmax in (127, 63, 31, 15, 7):
+            codes, scales = ops.quantize_int8(x, qmax, 1)
+            assert np.array_equal(codes.cpu().numpy(), golden_int8[f"q_{name}_{qmax}_row_codes"])
+            assert np.array_equal(scales.cpu().numpy().view(np.uint32), golden_int8[f"q_{name}_{qmax}_row_scale"].view(np.uint32))
+            codes, scales = ops.quantize_int8(x, qmax, 0)
+            assert np.array_equal(codes.cpu().numpy(), golden_int8[f"q_{name}_{qmax}_col_codes"].T)
+            assert np.array_equal(scales.cpu().numpy().view(np.uint32), golden_int8[f"q_{name}_{qmax}_col_scale"].view(np.uint32))
+            codes, scale = ops.quantize_int8_tensorwise(x, qmax)
+            assert np.array_equal(codes.cpu().numpy(), golden_int8[f"q_{name}_{qmax}_tensor_codes"])
+            assert np.array_equal(scale.cpu().numpy().view(np.uint32), golden_int8[f"q_{name}_{qmax}_tensor_scale"].view(np.uint32))
+
+
 def test_fp8_digests_at_benchmark_size(ops):
     """FP8 training triple (M=16384, K=N=2048): sha256 of codes and scales equals what the
     reference's quantize_fp8 produced for the same seeded inputs."""
