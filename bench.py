@@ -40,11 +40,12 @@ WORKLOADS = {
     "mxfp8_square_4096": ("mxfp8", 4096, 4096, 4096),
     "mxfp8_gpt2_mlp_up": ("mxfp8", 8192, 3072, 768),
     "fp8_rowwise_linear_16384x2048x2048": ("fp8", 16384, 2048, 2048),
+    "int8_rowwise_linear_16384x2048x2048": ("int8", 16384, 2048, 2048),
     # MoE block: (kind, tokens, hidden, intermediate); 64 experts, top-4
     "moe_mxfp8_16384x768_e64_top4": ("moe", 16384, 768, 384),
 }
 MOE_EXPERTS, MOE_TOPK = 64, 4
-NOMINAL_TFLOPS = {"mxfp8": 4500.0, "fp8": 4500.0, "nvfp4": 9000.0}
+NOMINAL_TFLOPS = {"mxfp8": 4500.0, "fp8": 4500.0, "int8": 4500.0, "nvfp4": 9000.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the ncu captures summarised
 # under profiles/ (null until captured for that workload)
 GEMM_DRAM_TRAFFIC = {"mxfp8_square_8192": 475.8e6, "nvfp4_square_8192": 273.4e6,
@@ -119,6 +120,8 @@ def cpu_step(kind, a, b):
         pa, sa, ta = R.quantize_nvfp4(a, -1)
         pb, sb, tb = R.quantize_nvfp4(b, -1)
         fa, fb = R.dequantize_nvfp4(pa, sa, ta).bfloat16(), R.dequantize_nvfp4(pb, sb, tb).bfloat16()
+    elif kind == "int8":
+        fa, fb = R.fake_quantize_int8(a, 127, dim=-1), R.fake_quantize_int8(b, 127, dim=-1)
     else:
         fa, fb = R.fake_quantize_fp8(a, torch.float8_e4m3fn, dim=-1), R.fake_quantize_fp8(b, torch.float8_e4m3fn, dim=-1)
     return fa @ fb.t()
@@ -177,6 +180,11 @@ def make_step(kind, a, b, out):
             pb, sfb, tb = ops.quantize_nvfp4(b, 1, ab)
             ev()
             ops.gemm_nvfp4(pa, sfa, ta, pb, sfb, tb, out=out)
+        elif kind == "int8":
+            ca, sa = ops.quantize_int8(a, 127, 1)
+            cb, sb = ops.quantize_int8(b, 127, 1)
+            ev()
+            ops.gemm_int8(ca, cb, sa, sb, out=out)
         else:
             ca, sa = ops.quantize_fp8(a, E4, 1)
             cb, sb = ops.quantize_fp8(b, E4, 1)
@@ -185,7 +193,7 @@ def make_step(kind, a, b, out):
         ev()                                        # end of the GEMM
         return out
 
-    launches = {"mxfp8": 3, "nvfp4": 5, "fp8": 3}[kind]
+    launches = {"mxfp8": 3, "nvfp4": 5, "fp8": 3, "int8": 3}[kind]
     return step, launches
 
 
@@ -398,7 +406,7 @@ def main():
 
     # ---- end to end through the public call, host buffers --------------------------------
     from pretrain_b200.quant.linear import _gemm
-    fmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3"}[kind]
+    fmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3", "int8": "int8"}[kind]
     ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
     hout = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
 
@@ -446,7 +454,7 @@ def main():
         try:
             from pretrain_b200 import dist as D
             gout = D.GatheredOutput(m, n)
-            ffmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3"}[kind]
+            ffmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3", "int8": "int8"}[kind]
             for _ in range(3):
                 D.sharded_gemm_fused(a, b, ffmt, gout)
             barrier()
@@ -471,7 +479,7 @@ def main():
     peaks = measured_peaks()
     # fp8 / fp4 tensor peak is not measured directly: the driver's measured bf16 cuBLAS rate,
     # sustained (this kernel is timed inside a seconds-long loop), times the format's rate ratio
-    ratio = {"mxfp8": 2.0, "fp8": 2.0, "nvfp4": 4.0}[kind]
+    ratio = {"mxfp8": 2.0, "fp8": 2.0, "int8": 2.0, "nvfp4": 4.0}[kind]
     peak = peaks["bf16_tflops_sustained"] * ratio
     achieved = flops / (gemm_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": f"gemm_pair_kernel<{kind}> / gemm_kernel<{kind}> (chosen by shape)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
@@ -480,7 +488,7 @@ def main():
                 "traffic": GEMM_DRAM_TRAFFIC.get(args.workload), "kernel_ms": gemm_ms}
     # the quantize kernels of the step against the measured HBM copy bandwidth (algorithmic bytes:
     # bf16 in, codes + scale bytes out; NVFP4 also reads each operand once more for its amax)
-    bpe = {"mxfp8": 3.03125, "fp8": 3.0, "nvfp4": 2.0 + 2.5625}[kind]
+    bpe = {"mxfp8": 3.03125, "fp8": 3.0, "int8": 3.0, "nvfp4": 2.0 + 2.5625}[kind]
     q_bytes = (m * k + n * k) * bpe
     quantize = {"bound": "hbm", "achieved": q_bytes / (quant_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": q_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": f"hbm_gbs, {peaks['source']}",
