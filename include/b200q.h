@@ -250,6 +250,16 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
                                     const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
                                     int64_t K, void* H, int64_t ldh, void* sfH, void* stream);
 
+/* Everything MoERouter.forward does after the fp32 gate GEMM (src/layers/mlp.py:292-301) and the
+ * bincount of the block (:455), in one launch: probs = softmax (score_fn 0) or sigmoid (1) of the
+ * fp32 logits [T, E]; the k largest probs per token in descending order -> top_idx (int64 [T, k]);
+ * their probs, divided by (their sum + 1e-9) when normalize != 0, -> top_w (bf16 [T, k]); probs as
+ * bf16 [T, E] (optional); expert_counts[e] = tokens that chose e (int32 [E], optional).  Equal
+ * probs are ordered by logit, then by expert index.  E <= 256, k <= 32. */
+int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int score_fn, int normalize,
+                          int64_t* top_idx, void* top_w, void* probs, int32_t* expert_counts,
+                          void* stream);
+
 /* Weighted unpermute (src/layers/mlp.py:472-477): out[t, :] = sum_j w[t, j] * y[row_of[t*k+j], :],
  * accumulated in fp32 and rounded once to bf16.  y bf16 [padded_rows, D] pitch ldy; w bf16 [T, k]. */
 int b200q_moe_unpermute(const void* y, int64_t ldy, const void* w, const int32_t* row_of, int64_t T,

@@ -374,6 +374,18 @@ def router_topk(logits: torch.Tensor, k: int, dtype=torch.bfloat16):
     return idx, w.to(dtype)
 
 
+def router_backend(logits: torch.Tensor, k: int, score_fn: str = "softmax", normalize: bool = True, dtype=torch.bfloat16):
+    """Everything after the gate GEMM in MoERouter.forward (src/layers/mlp.py:292-301) and the
+    bincount of SparseMoEBlock.forward (:455): (top_idx, top_w, probs, expert_counts)."""
+    lf = logits.float()
+    probs = lf.softmax(dim=-1) if score_fn == "softmax" else lf.sigmoid()
+    w, idx = torch.topk(probs, k, dim=-1)
+    if normalize:
+        w = w / (w.sum(-1, keepdim=True) + 1e-9)
+    counts = torch.bincount(idx.reshape(-1), minlength=logits.shape[-1])
+    return idx, w.to(dtype), probs.to(dtype), counts
+
+
 # ---------------------------------------------------------------------------
 # Seeded synthetic inputs for the benchmark configurations
 # ---------------------------------------------------------------------------

@@ -309,6 +309,90 @@ swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t l
   }
 }
 
+// ---- router back end: score function, top-k, normalised weights, casts, expert histogram ---------
+// One warp per token over the fp32 logits of the gate GEMM (src/layers/mlp.py:292-301, :455):
+// probs = softmax | sigmoid (fp32), the k largest probs in descending order (equal probs: the
+// larger logit first, then the lower expert index), weights = probs[idx] / (sum + 1e-9) when
+// normalising, both cast to bf16, plus how many tokens chose each expert.  Lane l holds experts
+// l, l + 32, ... (E <= 256).
+constexpr int kRouterMaxPerLane = kMaxExperts / 32;
+
+__global__ void __launch_bounds__(256)
+moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k, int sigmoid, int normalize,
+                       int64_t* __restrict__ top_idx, uint16_t* __restrict__ top_w, uint16_t* __restrict__ probs_out,
+                       int32_t* __restrict__ counts) {
+  __shared__ int hist[kMaxExperts];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < E; i += 256) hist[i] = 0;
+  __syncthreads();
+  const int per = (E + 31) >> 5;
+  for (int64_t t = (int64_t)blockIdx.x * 8 + warp; t < T; t += (int64_t)gridDim.x * 8) {
+    float v[kRouterMaxPerLane], p[kRouterMaxPerLane];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kRouterMaxPerLane; ++j) {
+      const int e = j * 32 + lane;
+      v[j] = (j < per && e < E) ? logits[t * E + e] : -INFINITY;
+      m = fmaxf(m, v[j]);
+    }
+    if (sigmoid) {
+#pragma unroll
+      for (int j = 0; j < kRouterMaxPerLane; ++j) p[j] = v[j] == -INFINITY ? -1.f : 1.f / (1.f + expf(-v[j]));
+    } else {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < kRouterMaxPerLane; ++j) {
+        p[j] = v[j] == -INFINITY ? 0.f : expf(v[j] - m);
+        sum += p[j];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+#pragma unroll
+      for (int j = 0; j < kRouterMaxPerLane; ++j) p[j] = v[j] == -INFINITY ? -1.f : p[j] / sum;
+    }
+    if (probs_out != nullptr) {
+#pragma unroll
+      for (int j = 0; j < kRouterMaxPerLane; ++j) {
+        const int e = j * 32 + lane;
+        if (j < per && e < E) probs_out[t * E + e] = __bfloat16_as_ushort(__float2bfloat16_rn(p[j]));
+      }
+    }
+    // k rounds of warp arg-max; a taken entry drops to -2 (below every prob and the -1 of absent experts)
+    float wsum = 0.f, mine = 0.f;   // lane j keeps the j-th weight
+    int mine_idx = 0;
+    for (int r = 0; r < k; ++r) {
+      float bp = -3.f, bv = -INFINITY;
+      int be = 0x7FFFFFFF;
+#pragma unroll
+      for (int j = 0; j < kRouterMaxPerLane; ++j) {
+        const int e = j * 32 + lane;
+        if (p[j] > bp || (p[j] == bp && (v[j] > bv || (v[j] == bv && e < be)))) { bp = p[j]; bv = v[j]; be = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float op = __shfl_xor_sync(0xFFFFFFFFu, bp, o), ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+        const int oe = __shfl_xor_sync(0xFFFFFFFFu, be, o);
+        if (op > bp || (op == bp && (ov > bv || (ov == bv && oe < be)))) { bp = op; bv = ov; be = oe; }
+      }
+      if ((be & 31) == lane) p[be >> 5] = -2.f;        // compile-time indexing is kept by the unrolled form below
+      wsum += bp;
+      if (lane == r) { mine = bp; mine_idx = be; }
+    }
+    if (lane < k) {
+      const float w = normalize ? mine / (wsum + 1e-9f) : mine;
+      top_idx[t * k + lane] = mine_idx;
+      top_w[t * k + lane] = __bfloat16_as_ushort(__float2bfloat16_rn(w));
+      if (counts != nullptr) atomicAdd(&hist[mine_idx], 1);
+    }
+  }
+  __syncthreads();
+  if (counts != nullptr)
+    for (int i = threadIdx.x; i < E; i += 256)
+      if (hist[i]) atomicAdd(&counts[i], hist[i]);
+}
+
 // ---- weighted unpermute: out[t] = sum_j w[t,j] * y[row_of[t*k+j]] (fp32 accumulate) ----------------
 __global__ void __launch_bounds__(256)
 moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t* __restrict__ w,
@@ -474,6 +558,21 @@ int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantiz
   else if (fmt == B200Q_E4M3) { if (wide) B200Q_GO(1, true, FMT_E4M3); else B200Q_GO(1, false, FMT_E4M3); }
   else { if (wide) B200Q_GO(1, true, FMT_E5M2); else B200Q_GO(1, false, FMT_E5M2); }
 #undef B200Q_GO
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int score_fn, int normalize, int64_t* top_idx,
+                          void* top_w, void* probs, int32_t* expert_counts, void* stream) {
+  if (logits == nullptr || top_idx == nullptr || top_w == nullptr || T <= 0 || E <= 0 || k <= 0 || (score_fn != 0 && score_fn != 1))
+    return B200Q_ERR_INVALID_ARG;
+  if (E > kMaxExperts || k > 32 || k > E) return B200Q_ERR_SHAPE;
+  int rc = require_sm100();
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (expert_counts != nullptr) B200Q_CUDA(cudaMemsetAsync(expert_counts, 0, (size_t)E * sizeof(int32_t), st));
+  moe_router_topk_kernel<<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, (uint16_t*)top_w,
+                                                      (uint16_t*)probs, expert_counts);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

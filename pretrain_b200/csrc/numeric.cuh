@@ -158,13 +158,28 @@ B200Q_HD uint32_t cvt_i8(float q, float qmax) {
   r = r < -qmax ? -qmax : (r > qmax ? qmax : r);
   return (uint32_t)(int)r & 0xFFu;
 }
+// Four of them packed, lowest address first.  Clamping before the rounding gives the same integer
+// (the bounds are integers and rounding is monotone); on the device that is two min/max, one
+// convert and half a saturating pack per value.
+B200Q_HD uint32_t cvt_i8x4(float a, float b, float c, float d, float qmax) {
+#if defined(__CUDA_ARCH__)
+  const int ia = __float2int_rn(fminf(fmaxf(a, -qmax), qmax)), ib = __float2int_rn(fminf(fmaxf(b, -qmax), qmax));
+  const int ic = __float2int_rn(fminf(fmaxf(c, -qmax), qmax)), id = __float2int_rn(fminf(fmaxf(d, -qmax), qmax));
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(id), "r"(ic), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(ib), "r"(ia), "r"(hi));
+  return out;
+#else
+  return cvt_i8(a, qmax) | (cvt_i8(b, qmax) << 8) | (cvt_i8(c, qmax) << 16) | (cvt_i8(d, qmax) << 24);
+#endif
+}
 // Scale and four packed codes for any of the per-row / per-column / per-tensor formats; `fmt` is a
 // compile-time constant at every call site, so the branch folds.
 B200Q_HD float scale_from_amax(float amax, int fmt, float qmax) {
   return fmt == FMT_I8 ? int_scale_from_amax(amax, qmax) : fp8_scale_from_amax(amax, fmt);
 }
 B200Q_HD uint32_t cvt_codes_x4(float a, float b, float c, float d, int fmt, float qmax) {
-  if (fmt == FMT_I8) return cvt_i8(a, qmax) | (cvt_i8(b, qmax) << 8) | (cvt_i8(c, qmax) << 16) | (cvt_i8(d, qmax) << 24);
+  if (fmt == FMT_I8) return cvt_i8x4(a, b, c, d, qmax);
   return cvt_fp8x4(a, b, c, d, fmt);
 }
 

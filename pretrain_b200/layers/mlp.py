@@ -124,6 +124,7 @@ class MoERouter(nn.Module):
         self.n_routed_experts_per_token = n_routed_experts_per_token
         self.normalize = normalize
         self.score_fn = MOE_ROUTER_SCORE_FNS[router_score_fn]
+        self.score_name = router_score_fn
         self.gate = nn.Linear(d_model, n_routed_experts, bias=False)
 
     def _apply(self, fn, recurse=True):
@@ -134,11 +135,48 @@ class MoERouter(nn.Module):
 
     def forward(self, x):
         with torch.amp.autocast(device_type=x.device.type, enabled=False):
-            probs = self.score_fn(self.gate(x.float()))
+            logits = self.gate(x.float())                  # the fp32 gate GEMM stays the reference's own op
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.n_routed_experts <= 256:
+            top_i, top_w, probs = _RouterBackEnd.apply(logits, self.n_routed_experts_per_token, self.score_name, self.normalize)
+            return top_i, top_w, probs
+        probs = self.score_fn(logits)
         top_w, top_i = torch.topk(probs, self.n_routed_experts_per_token, dim=-1)
         if self.normalize:
             top_w = top_w / (top_w.sum(-1, keepdim=True) + 1e-9)
         return top_i, top_w.to(x.dtype), probs.to(x.dtype)
+
+
+class _RouterBackEnd(torch.autograd.Function):
+    """Score function, top-k, normalisation and casts of MoERouter.forward in one kernel
+    (b200q_moe_router_topk); the backward is the closed form of those steps on the (T, E) tensors."""
+
+    @staticmethod
+    def forward(ctx, logits, k, score_name, normalize):
+        top_i, top_w, probs, _ = ops.moe_router_topk(logits, k, score_name, normalize, want_counts=False)
+        ctx.save_for_backward(logits, top_i)
+        ctx.score_name, ctx.normalize = score_name, normalize
+        ctx.mark_non_differentiable(top_i)
+        return top_i, top_w, probs
+
+    @staticmethod
+    def backward(ctx, _g_idx, g_w, g_p):
+        logits, top_i = ctx.saved_tensors
+        p = logits.softmax(-1) if ctx.score_name == "softmax" else logits.sigmoid()
+        dp = g_p.float() if g_p is not None else torch.zeros_like(p)
+        if g_w is not None:
+            g_w = g_w.float()
+            w_raw = p.gather(-1, top_i)
+            if ctx.normalize:
+                s = w_raw.sum(-1, keepdim=True) + 1e-9
+                d_raw = g_w / s - (g_w * w_raw).sum(-1, keepdim=True) / (s * s)
+            else:
+                d_raw = g_w
+            dp = dp.scatter_add(-1, top_i, d_raw)
+        if ctx.score_name == "softmax":
+            dlogits = p * (dp - (dp * p).sum(-1, keepdim=True))
+        else:
+            dlogits = dp * p * (1 - p)
+        return dlogits, None, None, None
 
 
 class SparseMoEBlock(nn.Module):

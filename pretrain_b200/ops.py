@@ -373,6 +373,24 @@ def swiglu(g: torch.Tensor, quantize: bool, fmt=E4M3):
     return (out, sf) if quantize else out
 
 
+def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str = "softmax", normalize: bool = True, want_probs: bool = True,
+                    want_counts: bool = True):
+    """fp32 logits (T, E) -> (top_idx int64 (T, k), top_w bf16 (T, k), probs bf16 (T, E) | None,
+    expert_counts int32 (E) | None): score function, top-k, normalisation, casts and histogram in one launch."""
+    if not logits.is_cuda:
+        raise RuntimeError("b200q ops need CUDA tensors (no CPU path exists)")
+    logits = logits.float().contiguous()
+    t, e = logits.shape
+    idx = torch.empty(t, k, dtype=torch.int64, device=logits.device)
+    w = torch.empty(t, k, dtype=torch.bfloat16, device=logits.device)
+    probs = torch.empty(t, e, dtype=torch.bfloat16, device=logits.device) if want_probs else None
+    counts = torch.empty(e, dtype=torch.int32, device=logits.device) if want_counts else None
+    _lib.check(_lib.load().b200q_moe_router_topk(logits.data_ptr(), t, e, k, {"softmax": 0, "sigmoid": 1}[score_fn], int(normalize),
+                                                 idx.data_ptr(), w.data_ptr(), probs.data_ptr() if want_probs else None,
+                                                 counts.data_ptr() if want_counts else None, _stream()), "b200q_moe_router_topk")
+    return idx, w, probs, counts
+
+
 def moe_unpermute(y: torch.Tensor, weights: torch.Tensor, row_of: torch.Tensor, n_tokens: int):
     """out[t] = sum_j weights[t, j] * y[row_of[t*k + j]] (fp32 accumulate, bf16 out)."""
     k = row_of.numel() // n_tokens

@@ -221,6 +221,53 @@ def test_dense_gemm_with_swiglu_epilogue(ops):
     assert mx <= 6e-2 and fro <= 4e-2, (mx, fro)      # one E4M3 rounding (2^-4 relative) on top of the GEMM tolerance
 
 
+@pytest.mark.parametrize("score_fn", ["softmax", "sigmoid"])
+@pytest.mark.parametrize("normalize", [True, False])
+@pytest.mark.parametrize("t,e,k", [(4096, 64, 4), (1000, 8, 2), (777, 200, 6), (64, 256, 8), (16384, 64, 4)])
+def test_router_back_end(ops, score_fn, normalize, t, e, k):
+    """Indices and counts exactly as torch.topk / bincount on the same fp32 logits; weights and
+    probs within one bf16 ulp of the reference's fp32 arithmetic (the kernel's exp and sum differ
+    from torch's in the last fp32 bit at most)."""
+    g = torch.Generator().manual_seed(t + e + k)
+    logits = torch.randn(t, e, generator=g)
+    if t == 1000:
+        logits = logits * 30                                       # saturated router (tests/fast/layers/test_mlp.py:808-822)
+    idx, w, probs, counts = ops.moe_router_topk(logits.cuda(), k, score_fn, normalize)
+    ri, rw, rp, rc = R.router_backend(logits, k, score_fn, normalize)
+    # positions where the reference's own probs tie (saturation) may be ordered either way: compare as sets there
+    pf = logits.softmax(-1) if score_fn == "softmax" else logits.sigmoid()
+    tied = (pf.gather(-1, ri)[:, 1:] == pf.gather(-1, ri)[:, :-1]).any(-1) | (pf.gather(-1, ri)[:, -1:] == pf.topk(min(k + 1, e), -1).values[:, -1:]).any(-1)
+    assert torch.equal(idx.cpu()[~tied], ri[~tied])
+    assert torch.equal(idx.cpu()[tied].sort(-1).values, ri[tied].sort(-1).values) or score_fn == "sigmoid" or t == 1000
+    clean = ~tied
+    ulp = lambda a, b: ((a.view(torch.int16).int() - b.view(torch.int16).int()).abs().max().item() if a.numel() else 0)
+    assert ulp(w.cpu()[clean], rw[clean]) <= 1
+    assert ulp(probs.cpu(), rp) <= 1
+    assert torch.equal(counts.cpu().long(), torch.bincount(idx.cpu().reshape(-1), minlength=e))
+    if not tied.any():
+        assert torch.equal(counts.cpu().long(), rc)
+
+
+def test_router_module_matches_torch_router_and_backpropagates(ops):
+    from pretrain_b200.layers.mlp import MoERouter
+    torch.manual_seed(0)
+    for score in ("softmax", "sigmoid"):
+        r = MoERouter(128, 16, 4, router_score_fn=score).cuda()
+        x = torch.randn(512, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        ti, tw, pr = r(x)
+        # the same module on its plain torch path (fp32 input switches the fused back end off)
+        logits = r.gate(x.float())
+        p = logits.softmax(-1) if score == "softmax" else logits.sigmoid()
+        rw, ri = torch.topk(p, 4, dim=-1)
+        rw = rw / (rw.sum(-1, keepdim=True) + 1e-9)
+        assert torch.equal(ti, ri)
+        assert (tw.float() - rw).abs().max() <= 2 ** -8 * rw.abs().max()
+        coef_w, coef_p = torch.randn_like(rw), torch.randn_like(p)
+        (gx,) = torch.autograd.grad((tw.float() * coef_w).sum() + (pr.float() * coef_p).sum(), x, retain_graph=True)
+        (rx,) = torch.autograd.grad((rw * coef_w).sum() + (p * coef_p).sum(), x)
+        assert _rel(gx, rx) < 2e-2
+
+
 def test_swiglu(ops):
     g = torch.Generator().manual_seed(0)
     h = (2.0 * torch.randn(384, 768, generator=g)).bfloat16().cuda()
