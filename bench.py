@@ -43,6 +43,11 @@ WORKLOADS = {
     "int8_rowwise_linear_16384x2048x2048": ("int8", 16384, 2048, 2048),
     # MoE block: (kind, tokens, hidden, intermediate); 64 experts, top-4
     "moe_mxfp8_16384x768_e64_top4": ("moe", 16384, 768, 384),
+    # gated MLP in NVFP4: (kind, tokens, hidden, intermediate): gate_up GEMM, SwiGLU, re-quantize, down GEMM
+    "nvfp4_mlp_16384x1024x3072": ("nvfp4_mlp", 16384, 1024, 3072),
+    # the three GEMMs of one linear layer and step (fprop, dgrad, wgrad): (kind, M, N, K)
+    "fp8_training_triple_16384x2048x2048": ("fp8_triple", 16384, 2048, 2048),
+    "mxfp8_training_triple_16384x2048x2048": ("mxfp8_triple", 16384, 2048, 2048),
 }
 MOE_EXPERTS, MOE_TOPK = 64, 4
 NOMINAL_TFLOPS = {"mxfp8": 4500.0, "fp8": 4500.0, "int8": 4500.0, "nvfp4": 9000.0}
@@ -321,6 +326,218 @@ def run_moe(args, t, d, inter, rank, world, local):
         print(json.dumps(line))
 
 
+def run_composite(args, kind, d0, d1, d2, rank, world, local):
+    """Workloads made of several quantize / GEMM / elementwise launches: the NVFP4 gated MLP
+    (tokens d0, hidden d1, intermediate d2) and the three GEMMs of a linear layer's step in FP8
+    row-wise or MXFP8 (M d0, N d1, K d2).  Every phase is event-timed; `value` counts the GEMMs' FLOP
+    over the whole step."""
+    from oracle import restate as R
+    from pretrain_b200 import build, ops
+    if rank == 0:
+        build.build()
+    E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
+    g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    rnd = lambda *shape, scale=1.0: (scale * torch.randn(*shape, generator=g, device="cuda")).to(torch.bfloat16)
+    phases = []            # (label, kind, work) in execution order; work = FLOP for gemm, bytes otherwise
+
+    if kind == "nvfp4_mlp":
+        t, h, inter = d0, d1, d2
+        x, w_gu, w_d = rnd(t, h), rnd(2 * inter, h, scale=0.02), rnd(h, inter, scale=0.02)
+        flops = 2.0 * t * (2 * inter * h + h * inter)
+
+        row_map = ops.glu_row_map(1, inter, x.device)       # gate / up rows interleaved for the SwiGLU epilogue
+
+        def step(ev):
+            ev("quantize", (t * h + 2 * inter * h) * (2 + 2.5625))
+            px, sx, tx = ops.quantize_nvfp4(x, 1)
+            pw, sw, tw = ops.quantize_nvfp4_rowmap(w_gu, row_map)
+            ev("gemm", 2.0 * t * 2 * inter * h)
+            hh, h_amax = ops.gemm_nvfp4_swiglu(px, sx, tx, pw, sw, tw)       # GEMM + SwiGLU + max|h| in one kernel
+            ev("quantize", t * inter * 2.5625 + h * inter * (2 + 2.5625))
+            ph, sh, th = ops.quantize_nvfp4(hh, 1, h_amax)
+            pd, sd, td = ops.quantize_nvfp4(w_d, 1)
+            ev("gemm", 2.0 * t * h * inter)
+            out = ops.gemm_nvfp4(ph, sh, th, pd, sd, td)
+            ev(None, 0)
+            return out
+        launches, dtype, peak_ratio, nominal = 11, "nvfp4", 4.0, 9000.0
+        desc = {"tokens_per_gpu": t, "hidden": h, "intermediate": inter}
+    else:
+        m, n, k = d0, d1, d2
+        x, w, dy = rnd(m, k), rnd(n, k, scale=0.02), rnd(m, n, scale=1e-3)
+        flops = 3 * 2.0 * m * n * k
+        if kind == "fp8_triple":
+            def step(ev):
+                ev("quantize", (m * k + n * k) * 3.0)
+                cx, sx = ops.quantize_fp8(x, E4, 1); cw, sw = ops.quantize_fp8(w, E4, 1)
+                ev("gemm", 2.0 * m * n * k)
+                y = ops.gemm_fp8(cx, E4, cw, E4, sx, sw)                         # fprop  (M,K).(N,K)^T
+                ev("quantize", m * n * 3.0 + n * k * 5.0)
+                cg, sg = ops.quantize_fp8(dy, E5, 1); cwt, swt = ops.quantize_fp8(w, E4, 0)
+                ev("gemm", 2.0 * m * n * k)
+                dx = ops.gemm_fp8(cg, E5, cwt, E4, sg, swt)                      # dgrad  (M,N).(K,N)^T
+                ev("quantize", m * n * 5.0 + m * k * 5.0)
+                cgt, sgt = ops.quantize_fp8(dy, E5, 0); cxt, sxt = ops.quantize_fp8(x, E4, 0)
+                ev("gemm", 2.0 * m * n * k)
+                dw = ops.gemm_fp8(cgt, E5, cxt, E4, sgt, sxt)                    # wgrad  (N,M).(K,M)^T
+                ev(None, 0)
+                return y, dx, dw
+            launches, dtype = 6 + 3 * 4 + 3, "fp8"
+        else:
+            def step(ev):
+                ev("quantize", (m * k + n * k) * 4.0625)
+                xr, xsr, xc, xsc = ops.quantize_mxfp8_dual(x, E4); wr, wsr, wc, wsc = ops.quantize_mxfp8_dual(w, E4)
+                ev("gemm", 2.0 * m * n * k)
+                y = ops.gemm_mxfp8(xr, xsr, wr, wsr)
+                ev("quantize", m * n * 4.0625)
+                gr, gsr, gc, gsc = ops.quantize_mxfp8_dual(dy, E5)
+                ev("gemm", 2.0 * m * n * k)
+                dx = ops.gemm_mxfp8(gr, gsr, wc, wsc, E5, E4)
+                ev("gemm", 2.0 * m * n * k)
+                dw = ops.gemm_mxfp8(gc, gsc, xc, xsc, E5, E4)
+                ev(None, 0)
+                return y, dx, dw
+            launches, dtype = 6, "mxfp8"
+        peak_ratio, nominal = 2.0, 4500.0
+        desc = {"M_per_gpu": m, "N": n, "K": k, "gemms": "fprop, dgrad, wgrad"}
+
+    def run(record):
+        marks = []
+
+        def ev(label, work):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            marks.append((label, work, e))
+        step(ev if record else (lambda *_: None))
+        return marks
+
+    for _ in range(max(args.warmup, 3)):
+        run(False)
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    all_marks = []
+    with ClockSampler(local) as clk:
+        torch.cuda.synchronize()
+        t0.record()
+        for _ in range(args.steps):
+            all_marks.append(run(True))
+        t1.record()
+        torch.cuda.synchronize()
+    ops.device_status()
+    ms_step = t0.elapsed_time(t1) / args.steps
+    acc = {}
+    for marks in all_marks:
+        for (label, work, e0), (_, _, e1) in zip(marks[:-1], marks[1:]):
+            a = acc.setdefault(label, [0.0, 0.0])
+            a[0] += e0.elapsed_time(e1)
+            a[1] += work
+    per = {lab: (ms / args.steps, work / args.steps) for lab, (ms, work) in acc.items()}
+
+    # end to end through the public seam, host buffers in and out
+    from pretrain_b200.quant.linear import QuantizedLinearFn, _gemm
+    from pretrain_b200.quant.config import TrainingConfig
+    import torch.nn.functional as F
+    if kind == "nvfp4_mlp":
+        hx = x.cpu().pin_memory()
+        hout = torch.empty(d0, d1, dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            dxm = hx.to("cuda", non_blocking=True)
+            gu = _gemm(dxm, w_gu.t(), "nvfp4", "nvfp4", torch.bfloat16)
+            gate, up = gu.chunk(2, dim=-1)
+            hout.copy_(_gemm(F.silu(gate) * up, w_d.t(), "nvfp4", "nvfp4", torch.bfloat16), non_blocking=True)
+        h2d, d2h = hx.numel() * 2, hout.numel() * 2
+    else:
+        recipe = "fp8" if kind == "fp8_triple" else "mxfp8"
+        q = {"enabled": True, "dtype_recipe": recipe}
+        if recipe == "fp8":
+            q["scaling"] = {"granularity": "rowwise"}
+        cfg = TrainingConfig(quant=q).quant[0]
+        hx, hg = x.cpu().pin_memory(), dy.cpu().pin_memory()
+        hdx, hdw = torch.empty_like(hx).pin_memory(), torch.empty(d1, d2, dtype=torch.bfloat16).pin_memory()
+        wp = torch.nn.Parameter(w.clone())
+
+        def e2e_step():
+            dxm = hx.to("cuda", non_blocking=True).requires_grad_(True)
+            y = QuantizedLinearFn.apply(dxm, wp, None, cfg)
+            gx, gw = torch.autograd.grad(y, (dxm, wp), hg.to("cuda", non_blocking=True))
+            hdx.copy_(gx, non_blocking=True)
+            hdw.copy_(gw, non_blocking=True)
+        h2d, d2h = (hx.numel() + hg.numel()) * 2, (hdx.numel() + hdw.numel()) * 2
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    n_e2e = max(3, min(args.steps, 10))
+    t0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / n_e2e
+
+    peaks = measured_peaks()
+    peak = peaks["bf16_tflops_sustained"] * peak_ratio
+    gemm_ms, gemm_flops = per["gemm"]
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    q_ms, q_bytes = per["quantize"]
+    line = {"metric": METRIC.replace("linear step: quantize A + quantize B + GEMM", "all quantize + GEMM launches of the workload"),
+            "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": dtype, "data": "synthetic",
+            "config": dict(workload=args.workload, l2="tensors of a step total > 126 MB (larger than L2); no flush needed", **desc),
+            "clocks": clk.summary(),
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "all GEMM launches of the step", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_ratio:g} x bf16_tflops_sustained, {peaks['source']}",
+                         "frac_of_nominal": achieved / nominal, "nominal_peak": nominal, "traffic": None, "kernel_ms": gemm_ms},
+            "quantize": {"bound": "hbm", "achieved": q_bytes / (q_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": q_bytes / (q_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "kernels_ms": q_ms, "bytes": q_bytes}}
+    if "elementwise" in per:
+        e_ms, e_bytes = per["elementwise"]
+        line["swiglu"] = {"bound": "hbm", "achieved": e_bytes / (e_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                          "frac": e_bytes / (e_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "kernels_ms": e_ms, "bytes": e_bytes}
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_composite_sample(kind, d0, d1, d2)
+        print(json.dumps(line))
+
+
+def cpu_composite_sample(kind, d0, d1, d2, rows=1024):
+    """The oracle's form of the composite workloads on the host cores, on a slice of `rows` tokens / rows."""
+    from oracle import restate as R
+    g = torch.Generator().manual_seed(0)
+    E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
+    if kind == "nvfp4_mlp":
+        x = torch.randn(rows, d1, generator=g).bfloat16()
+        w_gu, w_d = (0.02 * torch.randn(2 * d2, d1, generator=g)).bfloat16(), (0.02 * torch.randn(d1, d2, generator=g)).bfloat16()
+        tc = time.perf_counter()
+        gu = R.nvfp4_gemm_ref(x, w_gu.t())
+        gate, up = gu.chunk(2, dim=-1)
+        R.nvfp4_gemm_ref(R.silu_glu(gate, up), w_d.t())
+        dt = time.perf_counter() - tc
+        fl = 2.0 * rows * (2 * d2 * d1 + d1 * d2)
+        what = f"{rows} of {d0} tokens through the oracle's NVFP4 fake-quant MLP, 1 pass"
+    else:
+        n, k = d1, d2
+        x, w, dy = torch.randn(rows, k, generator=g).bfloat16(), (0.02 * torch.randn(n, k, generator=g)).bfloat16(), (1e-3 * torch.randn(rows, n, generator=g)).bfloat16()
+        tc = time.perf_counter()
+        if kind == "fp8_triple":
+            R.fp8_gemm_ref(x, w.t(), torch.bfloat16, E4, E4, rowwise=True)
+            R.fp8_gemm_ref(dy, w, torch.bfloat16, E5, E4, rowwise=True)
+            R.fp8_gemm_ref(dy.t(), x, torch.bfloat16, E5, E4, rowwise=True)
+        else:
+            R.mxfp8_gemm_ref(x, w.t(), torch.bfloat16, E4, E4)
+            R.mxfp8_gemm_ref(dy, w, torch.bfloat16, E5, E4)
+            R.mxfp8_gemm_ref(dy.t(), x, torch.bfloat16, E5, E4)
+        dt = time.perf_counter() - tc
+        fl = 3 * 2.0 * rows * n * k
+        what = f"{rows} of {d0} rows through the oracle's fake-quant fprop + dgrad + wgrad, 1 pass"
+    return {"value": fl / dt / 1e12, "unit": "TFLOPS", "cores": torch.get_num_threads(), "kind": "port", "sample": what,
+            "ms_per_step": dt * 1e3}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -343,7 +560,12 @@ def main():
             return
         torch.set_num_threads(len(os.sched_getaffinity(0)))     # torchrun pins OMP_NUM_THREADS=1
         steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
-        cb = cpu_moe_sample(m, n, k) if kind == "moe" else run_cpu(kind, m, n, k, steps, warm)
+        if kind == "moe":
+            cb = cpu_moe_sample(m, n, k)
+        elif kind in ("nvfp4_mlp", "fp8_triple", "mxfp8_triple"):
+            cb = cpu_composite_sample(kind, m, n, k)
+        else:
+            cb = run_cpu(kind, m, n, k, steps, warm)
         print(json.dumps({"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOPS", "n_gpus": args.gpus,
                           "steps": steps, "warmup": warm, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
                           "scaling": "weak", "vs_baseline": None, "dtype": "bf16 matmul of fake-quantized operands (CPU)",
@@ -357,6 +579,8 @@ def main():
     torch.cuda.set_device(local)
     if kind == "moe":
         return run_moe(args, m, n, k, rank, world, local)
+    if kind in ("nvfp4_mlp", "fp8_triple", "mxfp8_triple"):
+        return run_composite(args, kind, m, n, k, rank, world, local)
     dist = None
     if world > 1:
         import torch.distributed as dist

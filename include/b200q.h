@@ -245,6 +245,18 @@ int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantiz
 int b200q_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
                             const void* sfB, int64_t M, int64_t N, int64_t K, void* H, int64_t ldh,
                             void* sfH, void* stream);
+/* The same for NVFP4 operands, as far as NVFP4 allows: h cannot be quantized where it is produced
+ * (its tensor scale needs max|h| over the whole tensor first), so the epilogue writes h as bf16
+ * [M, N/2] (pitch ldh elements) and that maximum to *amax_out - the two things b200q_quantize_nvfp4
+ * of h needs - and the bf16 [M, 2I] gate/up tensor, twice the size of h, is never written.  B rows
+ * in the interleaved order (b200q_quantize_nvfp4_rowmap).  Bit-identical to b200q_gemm_nvfp4 ->
+ * b200q_swiglu(quantize = 0) -> b200q_amax. */
+int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const void* sfB,
+                            const float* tsA, const float* tsB, int64_t M, int64_t N, int64_t K,
+                            void* H, int64_t ldh, float* amax_out, void* stream);
+int b200q_quantize_nvfp4_rowmap(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                                const float* tensor_amax, const int32_t* dst_row, void* codes,
+                                void* sf, int sf_layout, float* tensor_scale_out, void* stream);
 int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
                                     const void* sfB, const int32_t* tile_expert,
                                     const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,

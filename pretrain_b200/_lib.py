@@ -45,6 +45,8 @@ SIGNATURES = {
     "b200q_grouped_gemm_mxfp8_swiglu": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _i64, _int, _i64, _i64, _vp, _i64,
                                                _vp, _vp]),
     "b200q_quantize_mxfp8_dual": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _int, _vp]),
+    "b200q_gemm_nvfp4_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
+    "b200q_quantize_nvfp4_rowmap": (_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp]),
     "b200q_quantize_mxfp8_rowmap": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp]),
     "b200q_moe_router_topk": (_int, [_vp, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_unpermute": (_int, [_vp, _i64, _vp, _vp, _i64, _int, _i64, _vp, _vp]),

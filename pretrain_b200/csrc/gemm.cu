@@ -108,10 +108,10 @@ struct GemmParams {
   GluOut glu;                   // EPI_GLU: where the SwiGLU + MXFP8 epilogue writes
 };
 
-enum { EPI_BF16 = 0, EPI_GLU = 1 };
+enum { EPI_BF16 = 0, EPI_GLU = 1, EPI_GLU_BF16 = 2 };   // plain output; SwiGLU -> MXFP8 codes; SwiGLU -> bf16 + amax
 // Threads per CTA: producer warp, MMA warp and one (bf16 output) or two (SwiGLU epilogue) groups
 // of four epilogue warps.
-__host__ __device__ constexpr int gemm_threads(int epi) { return epi == EPI_GLU ? 320 : 192; }
+__host__ __device__ constexpr int gemm_threads(int epi) { return epi == EPI_BF16 ? 192 : 320; }
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m, int& n) {
   constexpr int GM = 16;   // m-blocks per raster group: concurrent CTAs share A and B tiles through L2
@@ -316,10 +316,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(release_bar);
       };
-      if (EPI == EPI_GLU)
+      if (EPI != EPI_BF16)
         // the two warp groups swap block sets from tile to tile, so an odd block count evens out
-        epilogue_tile_glu<NBLK, RELEASE_AFTER, 2>(taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, p.M,
-                                                  p.N, p.glu, release);
+        epilogue_tile_glu<EPI == EPI_GLU ? GLU_MX : GLU_BF16, NBLK, RELEASE_AFTER, 2>(
+            taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, p.M, p.N, alpha, p.glu, release);
       else
         epilogue_tile<row_scaled(KIND), KIND == KIND_I8, NBLK, C::EPI_BUFS, RELEASE_AFTER>(
             taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
@@ -407,8 +407,8 @@ int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t 
   // operands: byte matrices [rows, row_bytes], box = 128 bytes x tile rows, 128-byte swizzle
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, p.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, b_rows, row_bytes, BKB, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if (EPI == EPI_GLU) {
-    md.count = 0;                       // no bf16 output: the epilogue writes codes and scale bytes itself
+  if (EPI != EPI_BF16) {
+    md.count = 0;                       // no TMA-stored output: the epilogue writes its results itself
     for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
   } else if ((rc = make_out_maps(&md, D, p.M, p.N, ldd))) {
     return rc;
@@ -457,7 +457,7 @@ int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
 
 // CTA-pair form of the dense GEMMs (gemm_2cta.cu, same translation unit)
 bool pair_eligible(int64_t M, int64_t N, int64_t row_bytes, bool grouped);
-template <int KIND>
+template <int KIND, int EPI = 0>
 int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, const GemmParams& gp, cudaStream_t st);
 
 template <int KIND>
@@ -475,12 +475,26 @@ int dispatch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_
 // MXFP8 GEMM with the SwiGLU + MXFP8 epilogue (one-CTA kernel; every tile width is a whole number
 // of 64-column epilogue blocks).
 int dispatch_glu(const void* A, const void* B, int64_t b_rows, const GemmParams& p, cudaStream_t st) {
+  if (pair_eligible(p.M, p.N, p.K, p.tile_expert != nullptr)) return launch_pair<KIND_MX, EPI_GLU>(A, B, OutSpec{}, 0, p, st);
   const int bn = g_force_bn ? g_force_bn : choose_bn<KIND_MX>(p.M, p.N, p.K);
   const OutSpec none = {};
   switch (bn) {
     case 128: return launch<KIND_MX, 128, EPI_GLU>(A, B, none, 0, b_rows, p, st);
     case 192: return launch<KIND_MX, 192, EPI_GLU>(A, B, none, 0, b_rows, p, st);
     case 256: return launch<KIND_MX, 256, EPI_GLU>(A, B, none, 0, b_rows, p, st);
+    default: return B200Q_ERR_INVALID_ARG;
+  }
+}
+
+// NVFP4 GEMM with the SwiGLU -> bf16 + amax epilogue.
+int dispatch_glu_nv(const void* A, const void* B, int64_t b_rows, const GemmParams& p, cudaStream_t st) {
+  if (pair_eligible(p.M, p.N, p.K / 2, false)) return launch_pair<KIND_NV, EPI_GLU_BF16>(A, B, OutSpec{}, 0, p, st);
+  const int bn = g_force_bn ? g_force_bn : choose_bn<KIND_NV>(p.M, p.N, p.K / 2);
+  const OutSpec none = {};
+  switch (bn) {
+    case 128: return launch<KIND_NV, 128, EPI_GLU_BF16>(A, B, none, 0, b_rows, p, st);
+    case 192: return launch<KIND_NV, 192, EPI_GLU_BF16>(A, B, none, 0, b_rows, p, st);
+    case 256: return launch<KIND_NV, 256, EPI_GLU_BF16>(A, B, none, 0, b_rows, p, st);
     default: return B200Q_ERR_INVALID_ARG;
   }
 }
@@ -624,6 +638,25 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
   if (rc) return rc;
   p.tile_expert = tile_expert; p.num_tiles = num_tiles;
   return dispatch_glu(A, B, (int64_t)E * N, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,
+                            int64_t M, int64_t N, int64_t K, void* H, int64_t ldh, float* amax_out, void* stream) {
+  if (A == nullptr || B == nullptr || sfA == nullptr || sfB == nullptr || tsA == nullptr || tsB == nullptr || H == nullptr ||
+      amax_out == nullptr || M <= 0 || N <= 0 || K <= 0 || ldh < N / 2)
+    return B200Q_ERR_INVALID_ARG;
+  if ((K & 31) || (N & 63) || (ldh & 7)) return B200Q_ERR_SHAPE;
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B200Q_ERR_SHAPE;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(H) || !aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  B200Q_CUDA(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.scale_a = tsA; p.scale_b = tsB;
+  p.M = M; p.N = N; p.K = K;
+  p.glu.codes = (uint8_t*)H; p.glu.ldh = ldh * 2; p.glu.amax = amax_out;
+  return dispatch_glu_nv(A, B, N, p, st);
 }
 
 int b200q_gemm_fp8_allgather(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a, int a_scale_is_scalar,

@@ -57,6 +57,7 @@ struct PairParams {
   int64_t M, N;
   int num_mp, num_n, num_k;      // pair tiles (256 rows), column tiles, K steps
   int sf_kt;                     // 512-byte scale atoms per 128-row group along K
+  GluOut glu;                    // SwiGLU epilogues: where they write
 };
 
 __device__ __forceinline__ void pair_tile_coords(int t, int num_mp, int num_n, int& mp, int& n) {
@@ -71,8 +72,8 @@ __device__ __forceinline__ void pair_tile_coords(int t, int num_mp, int num_n, i
 
 }  // namespace pair
 
-template <int KIND>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+template <int KIND, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm_threads(EPI), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                  const __grid_constant__ OutMaps outs, const pair::PairParams p) {
@@ -96,9 +97,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (threadIdx.x == 0) {
     // full: one arrival (with its byte count) per producer of the pair; empty / accumulator-full: the
-    // leader's commit; accumulator-free: 4 epilogue warps of each CTA
+    // leader's commit; accumulator-free: every epilogue warp (4 or 8) of each CTA
     for (int s = 0; s < C::STAGES; ++s) { ptx::mbar_init(full_bar(s), 2); ptx::mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 8); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 2 * (gemm_threads(EPI) / 32 - 2)); }
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tmap_a);
@@ -212,11 +213,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* epi_g = smem_gen + C::EPI_OFF + q * 2 * EPI_BLOCK_BYTES;
     int buf = 0;
     int acc = 0; uint32_t acc_phase = 0;
+    int tile_iter = 0;
     bool ok = true;
     float alpha = 1.f;
     if (KIND == KIND_NV) alpha = __ldg(p.scale_a) * __ldg(p.scale_b);
     constexpr int NBLK = BN / EPI_COLS;
-    for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
+    for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++tile_iter) {
       int mp, n_blk;
       pair::pair_tile_coords(t, p.num_mp, p.num_n, mp, n_blk);
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase) || *abort_flag) { ok = false; break; }
@@ -229,13 +231,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
       constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;
       const uint32_t release_bar = tempty_bar(acc) & ptx::kLeaderMask;       // the leader's barrier, from either CTA
-      epilogue_tile<row_scaled(KIND), KIND == KIND_I8, NBLK, 2, RELEASE_AFTER>(
-          taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
-          [&]() {
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(release_bar);
-          });
+      auto release = [&]() {
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(release_bar);
+      };
+      if (EPI != EPI_BF16)
+        epilogue_tile_glu<EPI == EPI_GLU ? GLU_MX : GLU_BF16, NBLK, RELEASE_AFTER, 2>(
+            taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, p.M, p.N, alpha, p.glu, release);
+      else
+        epilogue_tile<row_scaled(KIND), KIND == KIND_I8, NBLK, 2, RELEASE_AFTER>(
+            taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
+            release);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (lane == 0) ptx::bulk_wait<0>();
@@ -265,7 +272,7 @@ bool pair_eligible(int64_t M, int64_t N, int64_t row_bytes, bool grouped) {
   return tiles >= kNumSMs / 2;     // measured faster than the one-CTA kernel from K = 384 up once the pairs are busy
 }
 
-template <int KIND>
+template <int KIND, int EPI>
 int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, const GemmParams& gp, cudaStream_t st) {
   using C = pair::PCfg<KIND>;
   const int64_t row_bytes = KIND == KIND_NV ? gp.K / 2 : gp.K;
@@ -274,7 +281,12 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   int rc;
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, gp.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, gp.N, row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = make_out_maps(&md, D, gp.M, gp.N, ldd))) return rc;
+  if (EPI != EPI_BF16) {
+    md.count = 0;                       // the SwiGLU epilogues write their results themselves
+    for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
+  } else if ((rc = make_out_maps(&md, D, gp.M, gp.N, ldd))) {
+    return rc;
+  }
   int sf_kt = 0;
   if (!row_scaled(KIND)) {
     // scale buffers as rows of 256 bytes (two rows per 512-byte atom); box = the atoms of one K step
@@ -293,9 +305,10 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   p.num_n = (int)((gp.N + pair::PBN - 1) / pair::PBN);
   p.num_k = (int)((row_bytes + BKB - 1) / BKB);
   p.sf_kt = sf_kt;
-  B200Q_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  p.glu = gp.glu;
+  B200Q_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   const int tiles = p.num_mp * p.num_n, pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
-  gemm_pair_kernel<KIND><<<2 * pairs, kGemmThreads, C::SMEM_BYTES, st>>>(ma, mb, msa, msb, md, p);
+  gemm_pair_kernel<KIND, EPI><<<2 * pairs, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, msa, msb, md, p);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -97,45 +97,65 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t 
   }
 }
 
-// ---- SwiGLU + MXFP8 epilogue ----------------------------------------------------------------------
+// ---- SwiGLU epilogues ------------------------------------------------------------------------------
 // For a GEMM whose B rows come in the order "32 gate rows, then the 32 up rows of the same 32
 // outputs": every 64-column accumulator block holds gate[0..32) | up[0..32) of one 32-wide block
-// of h = silu(gate) * up, and a thread (one accumulator row) holds that whole block - exactly one
-// MXFP8 block along the next GEMM's contraction dimension.  The thread rounds the accumulators to
-// bf16 (the reference's GEMM output dtype), applies the same SwiGLU arithmetic as the stand-alone
-// kernel, quantizes, and writes 32 code bytes and one scale byte straight to global memory: the
-// bf16 [M, 2I] intermediate never exists.
+// of h = silu(gate) * up, and a thread (one accumulator row) holds that whole block.  The thread
+// rounds the scaled accumulators to bf16 (the reference's GEMM output dtype) and applies the same
+// SwiGLU arithmetic as the stand-alone kernel; the bf16 [M, 2I] intermediate never exists.  Then
+//   GLU_MX   : the block is exactly one MXFP8 block along the next GEMM's contraction dimension:
+//              quantize, write 32 code bytes and one scale byte;
+//   GLU_BF16 : write the 32 bf16 values and fold them into the tensor's absolute maximum (what an
+//              NVFP4 quantization of h needs before it can start), one atomic per warp and tile.
+enum { GLU_MX = 0, GLU_BF16 = 1 };
+
 struct GluOut {
-  uint8_t* codes;   // [M, N/2] E4M3 codes, pitch ldh bytes
+  uint8_t* codes;   // GLU_MX: [M, N/2] E4M3 codes; GLU_BF16: [M, N/2] bf16; pitch ldh BYTES
   int64_t ldh;
-  uint8_t* sf;      // 128x4-tiled E8M0 scale factors over (M, N/64)
+  uint8_t* sf;      // GLU_MX: 128x4-tiled E8M0 scale factors over (M, N/64)
   int64_t kt;       // K-tiles per row tile of that layout
+  float* amax;      // GLU_BF16: max |h| over the tensor (zeroed before the launch)
 };
 
 // Two warps share each tensor-memory lane quarter here (the arithmetic per block is long):
 // warp group `grp` of NGRP takes the blocks whose walking index i has i % NGRP == grp, and hands
 // the accumulator back once ITS blocks among the first RELEASE_AFTER + 1 have been read.
-template <int NBLK, int RELEASE_AFTER, int NGRP, class Release>
+template <int OUT, int NBLK, int RELEASE_AFTER, int NGRP, class Release>
 __device__ __forceinline__ void epilogue_tile_glu(uint32_t taddr, bool rev, int grp, int64_t row, int64_t col0, int64_t M,
-                                                  int64_t N, const GluOut& out, Release release) {
+                                                  int64_t N, float alpha, const GluOut& out, Release release) {
+  uint32_t hmax = 0;   // packed |bf16| maxima of this thread's h values (GLU_BF16)
   auto emit = [&](int c, const uint32_t (&r)[64]) {
     uint4 h[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const uint4 vg = make_uint4(pack_bf16(u2f(r[8 * u]), u2f(r[8 * u + 1])), pack_bf16(u2f(r[8 * u + 2]), u2f(r[8 * u + 3])),
-                                  pack_bf16(u2f(r[8 * u + 4]), u2f(r[8 * u + 5])), pack_bf16(u2f(r[8 * u + 6]), u2f(r[8 * u + 7])));
-      const uint4 vu = make_uint4(pack_bf16(u2f(r[32 + 8 * u]), u2f(r[33 + 8 * u])), pack_bf16(u2f(r[34 + 8 * u]), u2f(r[35 + 8 * u])),
-                                  pack_bf16(u2f(r[36 + 8 * u]), u2f(r[37 + 8 * u])), pack_bf16(u2f(r[38 + 8 * u]), u2f(r[39 + 8 * u])));
+      const uint4 vg = make_uint4(pack_bf16(u2f(r[8 * u]) * alpha, u2f(r[8 * u + 1]) * alpha),
+                                  pack_bf16(u2f(r[8 * u + 2]) * alpha, u2f(r[8 * u + 3]) * alpha),
+                                  pack_bf16(u2f(r[8 * u + 4]) * alpha, u2f(r[8 * u + 5]) * alpha),
+                                  pack_bf16(u2f(r[8 * u + 6]) * alpha, u2f(r[8 * u + 7]) * alpha));
+      const uint4 vu = make_uint4(pack_bf16(u2f(r[32 + 8 * u]) * alpha, u2f(r[33 + 8 * u]) * alpha),
+                                  pack_bf16(u2f(r[34 + 8 * u]) * alpha, u2f(r[35 + 8 * u]) * alpha),
+                                  pack_bf16(u2f(r[36 + 8 * u]) * alpha, u2f(r[37 + 8 * u]) * alpha),
+                                  pack_bf16(u2f(r[38 + 8 * u]) * alpha, u2f(r[39 + 8 * u]) * alpha));
       h[u] = swiglu8(vg, vu);
     }
-    uint32_t o[8];
-    const int e = mx_quant_block32<FMT_E4M3>(h, o);
-    if (row < M) {
-      const int64_t hb = (col0 + c * EPI_COLS) >> 6;   // 32-wide block of h along the row
-      uint4* dst = reinterpret_cast<uint4*>(out.codes + row * out.ldh + hb * 32);
-      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-      out.sf[sf_swizzled(row, (int)hb, out.kt)] = (uint8_t)(e + 127);
+    const int64_t hb = (col0 + c * EPI_COLS) >> 6;   // 32-wide block of h along the row
+    if (OUT == GLU_MX) {
+      uint32_t o[8];
+      const int e = mx_quant_block32<FMT_E4M3>(h, o);
+      if (row < M) {
+        uint4* dst = reinterpret_cast<uint4*>(out.codes + row * out.ldh + hb * 32);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        out.sf[sf_swizzled(row, (int)hb, out.kt)] = (uint8_t)(e + 127);
+      }
+    } else if (row < M) {
+      uint4* dst = reinterpret_cast<uint4*>(out.codes + row * out.ldh + hb * 64);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        dst[u] = h[u];
+        hmax = absmax_bf16x2(hmax, absmax_bf16x2(h[u].x, h[u].y));
+        hmax = absmax_bf16x2(hmax, absmax_bf16x2(h[u].z, h[u].w));
+      }
     }
   };
 
@@ -155,5 +175,11 @@ __device__ __forceinline__ void epilogue_tile_glu(uint32_t taddr, bool rev, int 
     }
     if (i == my_last) release();
     if (valid) emit(c, r);
+  }
+  if (OUT == GLU_BF16) {
+    float a = fmaxf(bf16lo(hmax), bf16hi(hmax));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+    if ((threadIdx.x & 31) == 0 && a > 0.f) atomicMax(reinterpret_cast<unsigned int*>(out.amax), f2u(a));   // a >= 0: uint order == float order
   }
 }

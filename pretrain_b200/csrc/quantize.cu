@@ -767,6 +767,25 @@ int b200q_quantize_mxfp8_rowmap(const void* x, int64_t rows, int64_t cols, int64
   return B200Q_OK;
 }
 
+int b200q_quantize_nvfp4_rowmap(const void* x, int64_t rows, int64_t cols, int64_t ld, const float* tensor_amax,
+                                const int32_t* dst_row, void* codes, void* sf, int sf_layout, float* tensor_scale_out,
+                                void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes == nullptr || sf == nullptr || tensor_amax == nullptr || tensor_scale_out == nullptr || dst_row == nullptr ||
+      (sf_layout != B200Q_SF_NATURAL && sf_layout != B200Q_SF_SWIZZLE_128x4))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
+  if ((cols & 31) || rows > INT32_MAX) return B200Q_ERR_SHAPE;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((rc = zero_sf_pads(sf, rows, cols / 16, sf_layout, st))) return rc;
+  launch_rowwise_block<MODE_NV>((const uint16_t*)x, rows, cols, ld, 0, (uint8_t*)codes, (uint8_t*)sf, sf_layout, tensor_amax,
+                                tensor_scale_out, st, dst_row);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
 int b200q_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, const float* tensor_amax,
                          void* codes, void* sf, int sf_layout, float* tensor_scale_out, void* stream) {
   int rc = check_matrix(x, rows, cols, ld);

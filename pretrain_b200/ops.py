@@ -154,6 +154,23 @@ def quantize_mxfp8_rowmap(x: torch.Tensor, dst_row: torch.Tensor, fmt=E4M3, layo
     return codes, sf
 
 
+def quantize_nvfp4_rowmap(x: torch.Tensor, dst_row: torch.Tensor, tensor_amax: torch.Tensor | None = None, layout: int = SF_SWIZZLED):
+    """Row-wise NVFP4 of x with input row r written as output row dst_row[r] (a permutation)."""
+    x = _mat(x)
+    rows, cols = x.shape
+    if dst_row.numel() != rows or dst_row.dtype != torch.int32 or not dst_row.is_cuda:
+        raise ValueError("dst_row: one int32 per row, on the GPU")
+    if tensor_amax is None:
+        tensor_amax = amax(x)
+    codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(rows, cols // 16, layout), dtype=torch.uint8, device=x.device)
+    ts = torch.empty(1, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().b200q_quantize_nvfp4_rowmap(x.data_ptr(), rows, cols, x.stride(0), tensor_amax.data_ptr(), dst_row.data_ptr(),
+                                                       codes.data_ptr(), sf.data_ptr(), layout, ts.data_ptr(), _stream()),
+               "b200q_quantize_nvfp4_rowmap")
+    return codes, sf, ts
+
+
 def quantize_nvfp4(x: torch.Tensor, axis: int = 1, tensor_amax: torch.Tensor | None = None, layout: int = SF_SWIZZLED):
     """Returns (packed uint8 [outer, C/2], sf uint8 flat buffer, tensor_scale fp32 [1])."""
     x = _mat(x)
@@ -343,6 +360,20 @@ def gemm_mxfp8_swiglu(a_codes, a_sf, b_codes, b_sf, a_fmt=E4M3, b_fmt=E4M3):
                                                    fmt_of(b_fmt), b_sf.data_ptr(), m, n, k, h.data_ptr(), h.stride(0),
                                                    sf.data_ptr(), _stream()), "b200q_gemm_mxfp8_swiglu")
     return h, sf
+
+
+def gemm_nvfp4_swiglu(a_codes, a_sf, a_ts, b_codes, b_sf, b_ts):
+    """(h bf16 [M, N/2], max|h| fp32 [1]) with h = silu(gate) * up, [gate | up] = A . B^T in NVFP4 and B's
+    rows in the interleaved order of glu_row_map: GEMM, activation and the amax pass in one kernel."""
+    m = a_codes.shape[0]
+    k = a_codes.shape[1] * 2
+    n = b_codes.shape[0]
+    h = torch.empty(m, n // 2, dtype=torch.bfloat16, device=a_codes.device)
+    am = torch.empty(1, dtype=torch.float32, device=a_codes.device)
+    _lib.check(_lib.load().b200q_gemm_nvfp4_swiglu(a_codes.data_ptr(), a_sf.data_ptr(), b_codes.data_ptr(), b_sf.data_ptr(),
+                                                   a_ts.data_ptr(), b_ts.data_ptr(), m, n, k, h.data_ptr(), h.stride(0), am.data_ptr(),
+                                                   _stream()), "b200q_gemm_nvfp4_swiglu")
+    return h, am
 
 
 def grouped_gemm_mxfp8_swiglu(a_codes, a_sf, b_codes, b_sf, plan: MoEPlan, n: int, a_fmt=E4M3, b_fmt=E4M3):

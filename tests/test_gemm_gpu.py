@@ -188,6 +188,30 @@ def test_cta_pair_kernel(ops, kind, m, n, k):
     _check(out, ref)
 
 
+@pytest.mark.parametrize("bn,pair", [(0, -1), (128, -1), (192, -1), (256, -1), (0, 1)])
+@pytest.mark.parametrize("m,d,inter", [(300, 512, 256), (1024, 1024, 384)])
+def test_nvfp4_gemm_with_swiglu_epilogue(ops, bn, pair, m, d, inter):
+    """GEMM with the SwiGLU -> bf16 + amax epilogue over interleaved NVFP4 weights == GEMM to bf16,
+    stand-alone SwiGLU, amax kernel: the same bits."""
+    from pretrain_b200 import _lib
+    x, w = _rand(m, d, 31), _rand(2 * inter, d, 32) * 0.05
+    px, sx, tx = ops.quantize_nvfp4(x)
+    pw, sw, tw = ops.quantize_nvfp4(w)
+    want = ops.swiglu(ops.gemm_nvfp4(px, sx, tx, pw, sw, tw), False)
+    pwi, swi, twi = ops.quantize_nvfp4_rowmap(w, ops.glu_row_map(1, inter, "cuda"))
+    assert torch.equal(twi, tw)
+    _lib.load().b200q_debug_set_gemm_bn(bn)
+    _lib.load().b200q_debug_set_gemm_pair(pair)                   # never / always the CTA-pair kernel
+    try:
+        h, am = ops.gemm_nvfp4_swiglu(px, sx, tx, pwi, swi, twi)
+        ops.device_status()
+    finally:
+        _lib.load().b200q_debug_set_gemm_bn(0)
+        _lib.load().b200q_debug_set_gemm_pair(0)
+    assert torch.equal(h, want)
+    assert am.item() == ops.amax(want).item() == want.float().abs().max().item()
+
+
 def _int8_ref(ca, cb, sa, sb):
     """The reference's formula (src/quant/int8.py:52-53) with an exact integer product."""
     acc = (ca.double() @ cb.double().t()).to(torch.int32)            # |acc| < 2^31: exact in fp64

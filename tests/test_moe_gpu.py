@@ -201,17 +201,23 @@ def test_rowmap_quantizer_is_a_row_permutation(ops):
     assert torch.equal(sf.view(-1, d // 32)[m.long()], rs.view(-1, d // 32))
 
 
-def test_dense_gemm_with_swiglu_epilogue(ops):
+@pytest.mark.parametrize("pair", [-1, 1])
+@pytest.mark.parametrize("m_,d,inter", [(300, 512, 256), (1024, 768, 384)])
+def test_dense_gemm_with_swiglu_epilogue(ops, pair, m_, d, inter):
+    from pretrain_b200 import _lib
     g = torch.Generator().manual_seed(4)
-    m_, d, inter = 300, 512, 256
     x = torch.randn(m_, d, generator=g).bfloat16().cuda()
     w = (0.06 * torch.randn(2 * inter, d, generator=g)).bfloat16().cuda()
     xq, xsf = ops.quantize_mxfp8(x, 1)
     wq, wsf = ops.quantize_mxfp8(w, 1)
     want_codes, want_sf = ops.swiglu(ops.gemm_mxfp8(xq, xsf, wq, wsf), True)
     wqi, wsfi = ops.quantize_mxfp8_rowmap(w, ops.glu_row_map(1, inter, "cuda"))
-    got_codes, got_sf = ops.gemm_mxfp8_swiglu(xq, xsf, wqi, wsfi)
-    ops.device_status()
+    _lib.load().b200q_debug_set_gemm_pair(pair)                   # never / always the CTA-pair kernel
+    try:
+        got_codes, got_sf = ops.gemm_mxfp8_swiglu(xq, xsf, wqi, wsfi)
+        ops.device_status()
+    finally:
+        _lib.load().b200q_debug_set_gemm_pair(0)
     assert torch.equal(got_codes, want_codes)
     assert torch.equal(G.unswizzle(got_sf, m_, inter // 32), G.unswizzle(want_sf, m_, inter // 32))
     # and against the oracle's arithmetic on the dequantized operands
