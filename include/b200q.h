@@ -223,6 +223,28 @@ int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const vo
                              int64_t padded_rows, int E, int64_t N, int64_t K, void* D, int64_t ldd,
                              void* stream);
 
+/* The two backward GEMMs of a grouped (per-expert) linear layer y_e = x_e . W_e^T over the padded
+ * expert-sorted layout; the reference gets them from autograd through torch._grouped_mm
+ * (src/layers/mlp.py:89,97).  MXFP8 operands, bf16 outputs, K % 128 == 0.
+ *
+ * dgrad: D[r, :] = A[r, :] . Bt[:, e(r)*K : (e(r)+1)*K]^T.  A: codes [padded_rows, K] + sfA (the
+ * output gradient, quantized along its columns); Bt: codes [N, E*K] + sfBt = the weight stack
+ * [E*K, N] quantized along axis 0 (b200q_quantize_mxfp8 transposes it as a whole, which puts expert
+ * e's operand at column offset e*K).  D: bf16 [padded_rows, N].
+ *
+ * wgrad: D[e*M + m, n] = sum over the rows r of expert e of At[m, r] * Bt[n, r].  At: codes
+ * [M, padded_rows] + sfAt and Bt: codes [N, padded_rows] + sfBt (output gradient and layer input,
+ * both quantized along the row dimension, i.e. axis 0 of the [padded_rows, .] tensors);
+ * padded_offs[E+1] from the permute plan gives every expert's row range.  D: bf16 [E*M, N],
+ * zeros for experts without rows.  M % 128 == 0. */
+int b200q_grouped_gemm_mxfp8_dgrad(const void* A, int a_fmt, const void* sfA, const void* Bt, int b_fmt,
+                                   const void* sfBt, const int32_t* tile_expert,
+                                   const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
+                                   int64_t K, void* D, int64_t ldd, void* stream);
+int b200q_grouped_gemm_mxfp8_wgrad(const void* At, int a_fmt, const void* sfAt, const void* Bt, int b_fmt,
+                                   const void* sfBt, const int32_t* padded_offs, int E, int64_t M,
+                                   int64_t N, int64_t padded_rows, void* D, int64_t ldd, void* stream);
+
 /* h[r, 0:I] = silu(gate) * up with gate = g[r, 0:I], up = g[r, I:2I] (src/layers/activation.py:80-81,
  * the step between the two grouped GEMMs, src/layers/mlp.py:92-94), rounded to bf16 as the
  * reference does, then (quantize = 1) MXFP8-quantized along I into `out` + swizzled `sf`, or
@@ -261,6 +283,21 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
                                     const void* sfB, const int32_t* tile_expert,
                                     const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
                                     int64_t K, void* H, int64_t ldh, void* sfH, void* stream);
+
+/* Backward of b200q_swiglu(quantize = 0): dg[r] = [dh * up * silu'(gate) | dh * silu(gate)] for
+ * g[r] = [gate | up]; bf16 in and out, fp32 arithmetic (the reference gets this from autograd through
+ * src/layers/activation.py:80-81).  I % 8 == 0. */
+int b200q_swiglu_backward(const void* g, int64_t rows, int64_t I, int64_t ldg, const void* dh,
+                          int64_t lddh, void* dg, int64_t lddg, void* stream);
+
+/* Backward of b200q_moe_unpermute (src/layers/mlp.py:472-477 under autograd): from the block's
+ * output gradient dout (bf16 [T, D]) it writes dy (bf16 [padded_rows, D]) with
+ * dy[row_of[t*k+j]] = w[t,j] * dout[t] and zero rows wherever src_of_row < 0, and, when y (the
+ * forward's expert outputs, bf16 [padded_rows, D], pitch ldy) and dw are given, the router-weight
+ * gradient dw[t*k+j] = <dout[t], y[row_of[t*k+j]]> in fp32. */
+int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y, int64_t ldy,
+                                 const int32_t* row_of, const int32_t* src_of_row, int64_t T, int k,
+                                 int64_t D, int64_t padded_rows, void* dy, float* dw, void* stream);
 
 /* Everything MoERouter.forward does after the fp32 gate GEMM (src/layers/mlp.py:292-301) and the
  * bincount of the block (:455), in one launch: probs = softmax (score_fn 0) or sigmoid (1) of the

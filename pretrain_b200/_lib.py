@@ -40,6 +40,8 @@ SIGNATURES = {
     "b200q_moe_pad_plan": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_gather": (_int, [_vp, _i64, _i64, _vp, _vp, _i64, _int, _int, _vp, _vp, _vp]),
     "b200q_grouped_gemm_mxfp8": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _i64, _int, _i64, _i64, _vp, _i64, _vp]),
+    "b200q_grouped_gemm_mxfp8_dgrad": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _i64, _int, _i64, _i64, _vp, _i64, _vp]),
+    "b200q_grouped_gemm_mxfp8_wgrad": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_swiglu": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]),
     "b200q_gemm_mxfp8_swiglu": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "b200q_grouped_gemm_mxfp8_swiglu": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _i64, _int, _i64, _i64, _vp, _i64,
@@ -48,6 +50,8 @@ SIGNATURES = {
     "b200q_gemm_nvfp4_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "b200q_quantize_nvfp4_rowmap": (_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp]),
     "b200q_quantize_mxfp8_rowmap": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp]),
+    "b200q_swiglu_backward": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "b200q_moe_unpermute_backward": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _int, _i64, _i64, _vp, _vp, _vp]),
     "b200q_moe_router_topk": (_int, [_vp, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_unpermute": (_int, [_vp, _i64, _vp, _vp, _i64, _int, _i64, _vp, _vp]),
 }

@@ -106,6 +106,11 @@ struct GemmParams {
   const int32_t* tile_expert;   // grouped: expert of every 128-row tile of A; null otherwise
   const int32_t* num_tiles;     // grouped: device count of row tiles in use
   GluOut glu;                   // EPI_GLU: where the SwiGLU + MXFP8 epilogue writes
+  // Grouped backward forms (MXFP8, K % 128 == 0):
+  int b_along_k;                // dgrad: B is [N, E*K], expert e's operand at K offset e*K (a transposed weight stack)
+  int sf_kt_b;                  // 512-byte atoms per row group along K in B's scale buffer (== sf_kt unless b_along_k)
+  const int32_t* ragged_offs;   // wgrad: padded_offs[E+1]; expert e contracts over rows [offs[e], offs[e+1]) of both operands
+  int n_experts;                //        and writes rows [e*M, (e+1)*M) of the output
 };
 
 enum { EPI_BF16 = 0, EPI_GLU = 1, EPI_GLU_BF16 = 2 };   // plain output; SwiGLU -> MXFP8 codes; SwiGLU -> bf16 + amax
@@ -123,6 +128,50 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m,
   n = r / gm;
 }
 
+
+// Everything the three roles need to know about tile t.
+struct Tile {
+  int m_blk, n_blk;
+  int k0, nk;          // first K step and number of K steps (128 bytes each)
+  int sfb_k0;          // first scale atom of B along K
+  int64_t brow0;       // first row of the B tile
+  int64_t bk0;         // K offset (bytes) of the B operand
+  int64_t drow_off;    // row offset of the output tile
+  float keep;          // 0 for an expert without rows (its single dummy K step is multiplied away), else 1
+};
+
+template <int BN>
+__device__ __forceinline__ Tile get_tile(const GemmParams& p, int t, int num_m) {
+  Tile ti;
+  int local = t, e = 0;
+  if (p.ragged_offs != nullptr) {
+    const int per = num_m * p.num_n;
+    e = t / per;
+    local = t - e * per;
+  }
+  tile_coords(local, num_m, p.num_n, ti.m_blk, ti.n_blk);
+  if (p.tile_expert != nullptr) e = __ldg(p.tile_expert + ti.m_blk);
+  ti.k0 = 0; ti.nk = p.num_k; ti.sfb_k0 = 0; ti.bk0 = 0; ti.drow_off = 0; ti.keep = 1.f;
+  ti.brow0 = (int64_t)ti.n_blk * BN;
+  if (p.ragged_offs != nullptr) {
+    const int r0 = __ldg(p.ragged_offs + e), r1 = __ldg(p.ragged_offs + e + 1);
+    ti.k0 = r0 >> 7;
+    ti.nk = (r1 - r0) >> 7;
+    if (ti.nk <= 0) {                      // no rows: run one in-range K step and scale it to zero
+      ti.nk = 1;
+      ti.k0 = ti.k0 < p.num_k ? ti.k0 : p.num_k - 1;
+      ti.keep = 0.f;
+    }
+    ti.sfb_k0 = 0;
+    ti.drow_off = (int64_t)e * p.M;
+  } else if (p.b_along_k) {
+    ti.bk0 = (int64_t)e * p.K;
+    ti.sfb_k0 = e * (int)(p.K >> 7);
+  } else {
+    ti.brow0 += (int64_t)e * p.N;
+  }
+  return ti;
+}
 
 template <int KIND, int BN, int EPI>
 __global__ void __launch_bounds__(gemm_threads(EPI), 1)
@@ -147,7 +196,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int live = __ldg(p.num_tiles);
     num_m = live < num_m ? live : num_m;
   }
-  const int total_tiles = num_m * p.num_n;
+  const int total_tiles = num_m * p.num_n * (p.ragged_offs != nullptr ? p.n_experts : 1);
 
   if (!row_scaled(KIND)) {
     // Scale-factor stage buffers start as zeros so that atoms beyond the end of K (never
@@ -182,11 +231,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int m_blk, n_blk;
-        tile_coords(t, num_m, p.num_n, m_blk, n_blk);
-        const int expert = p.tile_expert ? __ldg(p.tile_expert + m_blk) : 0;
-        const int64_t brow0 = (int64_t)expert * p.N + (int64_t)n_blk * BN;   // first row of the B tile
-        for (int k = 0; k < p.num_k; ++k) {
+        const Tile ti = get_tile<BN>(p, t, num_m);
+        const int m_blk = ti.m_blk;
+        const int64_t brow0 = ti.brow0;
+        for (int kl = 0; kl < ti.nk; ++kl) {
+          const int k = ti.k0 + kl;
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1) || *abort_flag) { ok = false; break; }
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           const uint32_t fb = full_bar(stage);
@@ -203,13 +252,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < C::NB_ATOMS; ++j) {
               const int64_t rg = g0 + j < p.sfb_groups ? g0 + j : g0;     // past the end: any valid group
-              ptx::bulk_load(ssfb + j * C::K_ATOMS * 512, p.sfb + (rg * p.sf_kt + ka0) * 512, ka * 512, fb);
+              ptx::bulk_load(ssfb + j * C::K_ATOMS * 512, p.sfb + (rg * p.sf_kt_b + ti.sfb_k0 + ka0) * 512, ka * 512, fb);
             }
           } else {
             ptx::mbar_expect_tx(fb, tx);
           }
           ptx::tma_load_2d(sa, &tmap_a, k * BKB, m_blk * BM, fb);
-          ptx::tma_load_2d(sb, &tmap_b, k * BKB, (int32_t)brow0, fb);
+          ptx::tma_load_2d(sb, &tmap_b, (int32_t)(k * BKB + ti.bk0), (int32_t)brow0, fb);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -224,10 +273,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t tile_iter = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-        int m_blk, n_blk;
-        tile_coords(t, num_m, p.num_n, m_blk, n_blk);
-        const int expert = p.tile_expert ? __ldg(p.tile_expert + m_blk) : 0;
-        const int64_t brow0 = (int64_t)expert * p.N + (int64_t)n_blk * BN;
+        const Tile ti = get_tile<BN>(p, t, num_m);
+        const int64_t brow0 = ti.brow0;
         const uint32_t sfb_off = (uint32_t)(brow0 & 127) >> 5;   // B tile starts this many 32-row columns into its first SF group
         // Plain double buffering: wait until this accumulator's previous tile has been read.
         // Overlapped: wait until the PREVIOUS tile's epilogue (other accumulator) has read the
@@ -240,7 +287,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (acc ? C::ACC1_COL0 : 0);
-        for (int k = 0; k < p.num_k; ++k) {
+        for (int k = 0; k < ti.nk; ++k) {
           if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
@@ -294,14 +341,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     float alpha = 1.f;
     if (KIND == KIND_NV) alpha = __ldg(p.scale_a) * __ldg(p.scale_b);
     constexpr int NBLK = BN / EPI_COLS;
+    const int64_t m_out = p.ragged_offs != nullptr ? p.M * p.n_experts : p.M;    // rows of the output
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-      int m_blk, n_blk;
-      tile_coords(t, num_m, p.num_n, m_blk, n_blk);
+      const Tile ti = get_tile<BN>(p, t, num_m);
+      const int m_blk = ti.m_blk, n_blk = ti.n_blk;
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase) || *abort_flag) { ok = false; break; }
       ptx::tc_fence_after();
-      const int64_t row0 = (int64_t)m_blk * BM + q * 32, row = row0 + lane;
+      const int64_t row0 = ti.drow_off + (int64_t)m_blk * BM + q * 32, row = row0 + lane;
       const int64_t col0 = (int64_t)n_blk * BN;
-      float row_scale = alpha;
+      float row_scale = alpha * ti.keep;
       if (row_scaled(KIND)) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
@@ -322,7 +370,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, p.M, p.N, alpha, p.glu, release);
       else
         epilogue_tile<row_scaled(KIND), KIND == KIND_I8, NBLK, C::EPI_BUFS, RELEASE_AFTER>(
-            taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
+            taddr, C::OVERLAP && acc == 0, row0, col0, m_out, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
             release);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
@@ -401,16 +449,18 @@ template <int KIND, int BN, int EPI = EPI_BF16>
 int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, GemmParams p, cudaStream_t st) {
   using C = Cfg<KIND, BN>;
   const int64_t row_bytes = KIND == KIND_NV ? p.K / 2 : p.K;
+  const int64_t b_row_bytes = p.b_along_k ? row_bytes * p.n_experts : row_bytes;      // a transposed weight stack is [N, E*K]
+  const int64_t m_out = p.ragged_offs != nullptr ? p.M * p.n_experts : p.M;
   CUtensorMap ma, mb;
   OutMaps md;
   int rc;
   // operands: byte matrices [rows, row_bytes], box = 128 bytes x tile rows, 128-byte swizzle
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, p.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, b_rows, row_bytes, BKB, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, b_row_bytes, b_rows, b_row_bytes, BKB, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if (EPI != EPI_BF16) {
     md.count = 0;                       // no TMA-stored output: the epilogue writes its results itself
     for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
-  } else if ((rc = make_out_maps(&md, D, p.M, p.N, ldd))) {
+  } else if ((rc = make_out_maps(&md, D, m_out, p.N, ldd))) {
     return rc;
   }
   p.num_m = (int)((p.M + BM - 1) / BM);
@@ -418,10 +468,11 @@ int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t 
   p.num_k = (int)((row_bytes + BKB - 1) / BKB);
   const int64_t nblk = KIND == KIND_MX ? p.K / 32 : p.K / 16;
   p.sf_kt = (int)((nblk + 3) / 4);
+  p.sf_kt_b = p.b_along_k ? p.sf_kt * p.n_experts : p.sf_kt;
   p.sfb_groups = (b_rows + 127) / 128;
   B200Q_CUDA(cudaFuncSetAttribute(gemm_kernel<KIND, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-  const int tiles = p.num_m * p.num_n;
-  const int grid = tiles < kNumSMs ? tiles : kNumSMs;
+  const int64_t tiles = (int64_t)p.num_m * p.num_n * (p.ragged_offs != nullptr ? p.n_experts : 1);
+  const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
   gemm_kernel<KIND, BN, EPI><<<grid, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, md, p);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -657,6 +708,48 @@ int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const
   p.M = M; p.N = N; p.K = K;
   p.glu.codes = (uint8_t*)H; p.glu.ldh = ldh * 2; p.glu.amax = amax_out;
   return dispatch_glu_nv(A, B, N, p, st);
+}
+
+// one-CTA kernel, tile width by the cost model (the grouped backward forms have no pair variant)
+static int dispatch_one_cta_mx(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, const GemmParams& p,
+                               cudaStream_t st) {
+  const int bn = g_force_bn ? g_force_bn : choose_bn<KIND_MX>(p.M, p.N, p.K);
+  switch (bn) {
+    case 128: return launch<KIND_MX, 128>(A, B, one_output(D), ldd, b_rows, p, st);
+    case 192: return launch<KIND_MX, 192>(A, B, one_output(D), ldd, b_rows, p, st);
+    case 256: return launch<KIND_MX, 256>(A, B, one_output(D), ldd, b_rows, p, st);
+    default: return B200Q_ERR_INVALID_ARG;
+  }
+}
+
+int b200q_grouped_gemm_mxfp8_dgrad(const void* A, int a_fmt, const void* sfA, const void* Bt, int b_fmt, const void* sfBt,
+                                   const int32_t* tile_expert, const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
+                                   int64_t K, void* D, int64_t ldd, void* stream) {
+  int rc = check_gemm(A, Bt, D, padded_rows, N, K, ldd, 128);
+  if (rc) return rc;
+  if (sfA == nullptr || sfBt == nullptr || tile_expert == nullptr || num_tiles == nullptr || E <= 0 || (a_fmt | b_fmt) & ~1)
+    return B200Q_ERR_INVALID_ARG;
+  if ((padded_rows & 127) || (int64_t)E * K > INT32_MAX) return B200Q_ERR_SHAPE;
+  if (!aligned16(sfA) || !aligned16(sfBt)) return B200Q_ERR_ALIGNMENT;
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfBt; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.M = padded_rows; p.N = N; p.K = K; p.tile_expert = tile_expert; p.num_tiles = num_tiles;
+  p.b_along_k = 1; p.n_experts = E;
+  return dispatch_one_cta_mx(A, Bt, D, ldd, N, p, (cudaStream_t)stream);
+}
+
+int b200q_grouped_gemm_mxfp8_wgrad(const void* At, int a_fmt, const void* sfAt, const void* Bt, int b_fmt, const void* sfBt,
+                                   const int32_t* padded_offs, int E, int64_t M, int64_t N, int64_t padded_rows, void* D,
+                                   int64_t ldd, void* stream) {
+  int rc = check_gemm(At, Bt, D, M, N, padded_rows, ldd, 128);
+  if (rc) return rc;
+  if (sfAt == nullptr || sfBt == nullptr || padded_offs == nullptr || E <= 0 || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
+  if ((M & 127) || (int64_t)E * M > INT32_MAX) return B200Q_ERR_SHAPE;
+  if (!aligned16(sfAt) || !aligned16(sfBt)) return B200Q_ERR_ALIGNMENT;
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfAt; p.sfb = (const uint8_t*)sfBt; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.M = M; p.N = N; p.K = padded_rows; p.ragged_offs = padded_offs; p.n_experts = E;
+  return dispatch_one_cta_mx(At, Bt, D, ldd, N, p, (cudaStream_t)stream);
 }
 
 int b200q_gemm_fp8_allgather(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a, int a_scale_is_scalar,

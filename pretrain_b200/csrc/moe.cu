@@ -420,6 +420,86 @@ moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t
   }
 }
 
+// ---- backward of SwiGLU: dg = [dh * up * silu'(gate) | dh * silu(gate)] -------------------------
+// silu'(x) = s (1 + x (1 - s)), s = 1 / (1 + e^-x); fp32 arithmetic on the bf16 inputs, one rounding.
+__global__ void __launch_bounds__(256)
+swiglu_backward_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t ldg, const uint16_t* __restrict__ dh,
+                       int64_t lddh, uint16_t* __restrict__ dg, int64_t lddg) {
+  const int runs = (int)(I >> 3);
+  for (ItemWalker w((int64_t)blockIdx.x * 256 + threadIdx.x, (int64_t)gridDim.x * 256, runs); w.row < rows; w.next()) {
+    const int64_t r = w.row;
+    const int c = w.chunk << 3;
+    float a[8], b[8], d[8];
+    unpack8(ld_nc_v4(g + r * ldg + c), a);
+    unpack8(ld_nc_v4(g + r * ldg + I + c), b);
+    unpack8(ld_nc_v4(dh + r * lddh + c), d);
+    uint32_t og[4], ou[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float dgate[2], dup[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float x = a[2 * i + j];
+        const float sg = __fdividef(1.f, 1.f + __expf(-x));
+        dup[j] = d[2 * i + j] * x * sg;
+        dgate[j] = d[2 * i + j] * b[2 * i + j] * sg * (1.f + x * (1.f - sg));
+      }
+      __nv_bfloat162 pg = __floats2bfloat162_rn(dgate[0], dgate[1]), pu = __floats2bfloat162_rn(dup[0], dup[1]);
+      og[i] = *reinterpret_cast<uint32_t*>(&pg);
+      ou[i] = *reinterpret_cast<uint32_t*>(&pu);
+    }
+    *reinterpret_cast<uint4*>(dg + r * lddg + c) = make_uint4(og[0], og[1], og[2], og[3]);
+    *reinterpret_cast<uint4*>(dg + r * lddg + I + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+  }
+}
+
+// ---- backward of the weighted unpermute ------------------------------------------------------------
+// out[t] = sum_j w[t,j] y[row_of[t,j]]  =>  dy[row_of[t,j]] = w[t,j] dout[t],  dw[t,j] = <dout[t], y[row_of[t,j]]>.
+// One warp per routed pair; a second range of warp items zeroes the rows of dy that no pair owns
+// (the pad rows of every segment and everything past the last one).
+__global__ void __launch_bounds__(256)
+moe_unpermute_backward_kernel(const uint16_t* __restrict__ dout, const uint16_t* __restrict__ w, const uint16_t* __restrict__ y,
+                              int64_t ldy, const int32_t* __restrict__ row_of, const int32_t* __restrict__ src_of_row,
+                              int64_t n_pairs, int k, int64_t D, int64_t padded_rows, uint16_t* __restrict__ dy,
+                              float* __restrict__ dw) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t total = n_pairs + padded_rows;
+  for (int64_t it = (int64_t)blockIdx.x * 8 + warp; it < total; it += (int64_t)gridDim.x * 8) {
+    if (it < n_pairs) {
+      const int64_t t = it / k;
+      const int row = row_of[it];
+      const float wj = u2f((uint32_t)w[it] << 16);
+      float dot = 0.f;
+      for (int64_t c = lane * 8; c < D; c += 256) {
+        float f[8];
+        unpack8(ld_nc_v4(dout + t * D + c), f);
+        if (y != nullptr) {
+          float yy[8];
+          unpack8(ld_nc_v4(y + (int64_t)row * ldy + c), yy);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dot = fmaf(f[i], yy[i], dot);
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 pk = __floats2bfloat162_rn(wj * f[2 * i], wj * f[2 * i + 1]);
+          o[i] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+        *reinterpret_cast<uint4*>(dy + (int64_t)row * D + c) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      if (dw != nullptr) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
+        if (lane == 0) dw[it] = dot;
+      }
+    } else {
+      const int64_t r = it - n_pairs;
+      if (src_of_row[r] < 0)
+        for (int64_t c = lane * 8; c < D; c += 256) *reinterpret_cast<uint4*>(dy + r * D + c) = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
 // Scratch of b200q_moe_permute_plan_static: the per-CTA expert histograms of the plan kernels
 // ([CTAs][E] int32).  It lives in the library image, so every GPU that loads the library holds
 // these 1 MiB until the process exits.
@@ -558,6 +638,37 @@ int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantiz
   else if (fmt == B200Q_E4M3) { if (wide) B200Q_GO(1, true, FMT_E4M3); else B200Q_GO(1, false, FMT_E4M3); }
   else { if (wide) B200Q_GO(1, true, FMT_E5M2); else B200Q_GO(1, false, FMT_E5M2); }
 #undef B200Q_GO
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_swiglu_backward(const void* g, int64_t rows, int64_t I, int64_t ldg, const void* dh, int64_t lddh, void* dg, int64_t lddg,
+                          void* stream) {
+  if (g == nullptr || dh == nullptr || dg == nullptr || rows <= 0 || I <= 0 || ldg < 2 * I || lddh < I || lddg < 2 * I)
+    return B200Q_ERR_INVALID_ARG;
+  if ((I & 7) || (ldg & 7) || (lddh & 7) || (lddg & 7)) return B200Q_ERR_SHAPE;
+  if (!aligned16(g) || !aligned16(dh) || !aligned16(dg)) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  swiglu_backward_kernel<<<thread_item_grid(rows * (I >> 3)), 256, 0, (cudaStream_t)stream>>>(
+      (const uint16_t*)g, rows, I, ldg, (const uint16_t*)dh, lddh, (uint16_t*)dg, lddg);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y, int64_t ldy, const int32_t* row_of,
+                                 const int32_t* src_of_row, int64_t T, int k, int64_t D, int64_t padded_rows, void* dy, float* dw,
+                                 void* stream) {
+  if (dout == nullptr || w == nullptr || row_of == nullptr || src_of_row == nullptr || dy == nullptr || T <= 0 || k <= 0 ||
+      D <= 0 || padded_rows <= 0 || (y != nullptr && ldy < D) || (dw != nullptr && y == nullptr))
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 7) || (y != nullptr && (ldy & 7))) return B200Q_ERR_SHAPE;
+  if (!aligned16(dout) || !aligned16(dy) || (y != nullptr && !aligned16(y))) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  moe_unpermute_backward_kernel<<<row_grid(T * k + padded_rows), 256, 0, (cudaStream_t)stream>>>(
+      (const uint16_t*)dout, (const uint16_t*)w, (const uint16_t*)y, ldy, row_of, src_of_row, T * k, k, D, padded_rows, (uint16_t*)dy,
+      dw);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

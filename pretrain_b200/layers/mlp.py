@@ -6,8 +6,8 @@ The two bf16 ``torch._grouped_mm`` calls of the reference become ragged MXFP8 gr
 the tensor cores; the permute is a stable counting sort (same row order as the reference's
 ``sort(stable=True)``) whose gather is fused with the MXFP8 quantization; SwiGLU is fused with
 the re-quantization of the hidden activations; the unpermute is a gather-reduce in fp32.
-Forward (fprop) only: the backward of the expert path is not built yet, so tensors that require
-grad are rejected instead of silently detaching them.
+``SparseMoEBlock`` is trainable (bias-free SwiGLU experts): its backward runs the four grouped
+backward GEMMs in MXFP8 as well.  ``grouped_mlp`` on its own is forward-only.
 """
 
 from __future__ import annotations
@@ -34,9 +34,65 @@ MOE_ROUTER_SCORE_FNS = {
 }
 
 
-def _no_grad_only(*tensors):
-    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
-        raise NotImplementedError("the MXFP8 expert path is forward-only in this build; call it under torch.no_grad()")
+def _wants_grad(*tensors) -> bool:
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+
+
+def _trainable_shapes(d: int, inter: int) -> bool:
+    """The grouped backward GEMMs contract over D, 2I and the rows; their K must be a multiple of 128."""
+    return d % 128 == 0 and (2 * inter) % 128 == 0 and inter % 32 == 0
+
+
+E4M3, E5M2 = torch.float8_e4m3fn, torch.float8_e5m2
+
+
+class _ExpertFFN(torch.autograd.Function):
+    """Permuted SwiGLU expert FFN + weighted unpermute with a backward pass, all GEMMs in MXFP8 on
+    the padded expert-sorted layout (the reference differentiates src/layers/mlp.py:446-477 through
+    torch._grouped_mm with autograd).
+
+    forward : gather -> quantize x both ways -> GEMM 1 -> SwiGLU -> quantize h both ways -> GEMM 2
+              -> weighted unpermute; the weights are quantized both ways too (row-wise for fprop,
+              transposed for dgrad).
+    backward: dy = w * dout (and dw = <dout, y>) -> dgrad 2 / wgrad 2 -> SwiGLU backward -> dgrad 1 /
+              wgrad 1 -> sum over the k slots.  Activations and weights E4M3, gradients E5M2, as in
+              the `mxfp8` recipe."""
+
+    @staticmethod
+    def forward(ctx, x, top_w, w_in, w_down, plan):
+        t, d = x.shape
+        e, n1, _ = w_in.shape
+        inter = n1 // 2
+        a = ops.moe_gather(x, plan, False)                                             # (R, D) bf16, pad rows zero
+        ar, asr, ac, asc = ops.quantize_mxfp8_dual(a, E4M3)
+        w1r, w1sr, w1c, w1sc = ops.quantize_mxfp8_dual(w_in.reshape(e * n1, d), E4M3)       # (E*2I, D) | (D, E*2I)
+        w2r, w2sr, w2c, w2sc = ops.quantize_mxfp8_dual(w_down.reshape(e * d, inter), E4M3)  # (E*D, I)  | (I, E*D)
+        g = ops.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, n1)                       # (R, 2I) bf16
+        h = ops.swiglu(g, False)
+        hr, hsr, hc, hsc = ops.quantize_mxfp8_dual(h, E4M3)
+        y = ops.grouped_gemm_mxfp8(hr, hsr, w2r, w2sr, plan, d)                        # (R, D) bf16
+        out = ops.moe_unpermute(y, top_w, plan.row_of, t)
+        ctx.save_for_backward(top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, y)
+        ctx.plan, ctx.shapes = plan, (t, d, e, inter, top_w.shape[1])
+        ctx.dtypes = (x.dtype, top_w.dtype, w_in.dtype, w_down.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, y = ctx.saved_tensors
+        plan = ctx.plan
+        t, d, e, inter, k = ctx.shapes
+        dy, dw = ops.moe_unpermute_backward(dout.reshape(t, d).to(torch.bfloat16), top_w, y, plan)
+        dyr, dysr, dyc, dysc = ops.quantize_mxfp8_dual(dy, E5M2)
+        dh = ops.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, plan, inter, E5M2, E4M3)       # (R, I)
+        dw2 = ops.grouped_gemm_mxfp8_wgrad(dyc, dysc, hc, hsc, plan, E5M2, E4M3)               # (E, D, I)
+        dg = ops.swiglu_backward(g, dh)                                                        # (R, 2I)
+        dgr, dgsr, dgc, dgsc = ops.quantize_mxfp8_dual(dg, E5M2)
+        da = ops.grouped_gemm_mxfp8_dgrad(dgr, dgsr, w1c, w1sc, plan, d, E5M2, E4M3)           # (R, D)
+        dw1 = ops.grouped_gemm_mxfp8_wgrad(dgc, dgsc, ac, asc, plan, E5M2, E4M3)               # (E, 2I, D)
+        dx = ops.moe_unpermute(da, torch.ones(t, k, dtype=torch.bfloat16, device=da.device), plan.row_of, t)
+        xd, twd, w1d, w2d = ctx.dtypes
+        return dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d), None
 
 
 def _quantize_expert_weights(w: torch.Tensor):
@@ -95,7 +151,8 @@ def grouped_mlp(x, w_in, w_down, act_fn, offs, gated, row_expert_ids=None, b_in=
     (offs[-1] == R); weights are (E, out, in); empty groups are fine; biases, when given, are
     (E, out) and are added per row.  Returns (R, D_out) in bf16, rows in the input order.
     """
-    _no_grad_only(x, w_in, w_down, b_in, b_down)
+    if _wants_grad(x, w_in, w_down, b_in, b_down):
+        raise NotImplementedError("grouped_mlp is forward-only here; SparseMoEBlock carries the backward of the expert path")
     if not x.is_cuda:
         raise RuntimeError("grouped_mlp runs on the B200 kernels only (no CPU path)")
     r = x.shape[0]
@@ -213,13 +270,19 @@ class SparseMoEBlock(nn.Module):
         top_indices, top_weights, router_probs = self.router(x_flat)
         w_in = self.expert_gate_up if self.gated else self.expert_up
         b_in = self.expert_gate_up_bias if self.gated else self.expert_up_bias
-        _no_grad_only(x, w_in, self.expert_down)
-
         plan = ops.moe_permute_plan(top_indices, e)                        # stable sort by expert
-        a, sfa = ops.moe_gather(x_flat.to(torch.bfloat16), plan, True)    # permute fused with MXFP8
-        y = _grouped_ffn_padded(a, sfa, plan, w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
-                                self.act_fn, self.gated, b_in, self.expert_down_bias)
-        out = ops.moe_unpermute(y, top_weights, plan.row_of, b * s).to(x.dtype)
+        if _wants_grad(x, top_weights, w_in, self.expert_down, b_in, self.expert_down_bias):
+            if not (self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None
+                    and _trainable_shapes(d, w_in.shape[1] // 2)):
+                raise NotImplementedError("the backward of the MXFP8 expert path covers bias-free SwiGLU experts with "
+                                          "d_model % 128 == 0 and intermediate_size % 64 == 0")
+            out = _ExpertFFN.apply(x_flat.to(torch.bfloat16), top_weights, w_in.to(torch.bfloat16),
+                                   self.expert_down.to(torch.bfloat16), plan).to(x.dtype)
+        else:
+            a, sfa = ops.moe_gather(x_flat.to(torch.bfloat16), plan, True)    # permute fused with MXFP8
+            y = _grouped_ffn_padded(a, sfa, plan, w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
+                                    self.act_fn, self.gated, b_in, self.expert_down_bias)
+            out = ops.moe_unpermute(y, top_weights, plan.row_of, b * s).to(x.dtype)
 
         aux = None
         if self.aux_loss:

@@ -362,6 +362,31 @@ def gemm_mxfp8_swiglu(a_codes, a_sf, b_codes, b_sf, a_fmt=E4M3, b_fmt=E4M3):
     return h, sf
 
 
+def grouped_gemm_mxfp8_dgrad(a_codes, a_sf, bt_codes, bt_sf, plan: MoEPlan, n: int, a_fmt=E4M3, b_fmt=E4M3):
+    """D[r] = A[r] . W_e(r) for the padded layout, where the weight stack (E*K, n) was quantized along
+    axis 0 as a whole: bt_codes is (n, E*K).  A is (padded_rows, K)."""
+    rows, k = a_codes.shape
+    d = torch.empty(rows, n, dtype=torch.bfloat16, device=a_codes.device)
+    _lib.check(_lib.load().b200q_grouped_gemm_mxfp8_dgrad(a_codes.data_ptr(), fmt_of(a_fmt), a_sf.data_ptr(), bt_codes.data_ptr(),
+                                                          fmt_of(b_fmt), bt_sf.data_ptr(), plan.tile_expert.data_ptr(),
+                                                          plan.num_tiles.data_ptr(), rows, plan.n_experts, n, k, d.data_ptr(),
+                                                          d.stride(0), _stream()), "b200q_grouped_gemm_mxfp8_dgrad")
+    return d
+
+
+def grouped_gemm_mxfp8_wgrad(at_codes, at_sf, bt_codes, bt_sf, plan: MoEPlan, a_fmt=E4M3, b_fmt=E4M3):
+    """D[e] = At[:, rows of e] . Bt[:, rows of e]^T for every expert: at_codes (M, padded_rows), bt_codes
+    (N, padded_rows), both quantized along the row dimension of the padded layout.  Returns (E, M, N) bf16."""
+    m, rows = at_codes.shape
+    n = bt_codes.shape[0]
+    e = plan.n_experts
+    d = torch.empty(e * m, n, dtype=torch.bfloat16, device=at_codes.device)
+    _lib.check(_lib.load().b200q_grouped_gemm_mxfp8_wgrad(at_codes.data_ptr(), fmt_of(a_fmt), at_sf.data_ptr(), bt_codes.data_ptr(),
+                                                          fmt_of(b_fmt), bt_sf.data_ptr(), plan.padded_offs.data_ptr(), e, m, n, rows,
+                                                          d.data_ptr(), d.stride(0), _stream()), "b200q_grouped_gemm_mxfp8_wgrad")
+    return d.view(e, m, n)
+
+
 def gemm_nvfp4_swiglu(a_codes, a_sf, a_ts, b_codes, b_sf, b_ts):
     """(h bf16 [M, N/2], max|h| fp32 [1]) with h = silu(gate) * up, [gate | up] = A . B^T in NVFP4 and B's
     rows in the interleaved order of glu_row_map: GEMM, activation and the amax pass in one kernel."""
@@ -402,6 +427,33 @@ def swiglu(g: torch.Tensor, quantize: bool, fmt=E4M3):
     _lib.check(_lib.load().b200q_swiglu(g.data_ptr(), rows, i, g.stride(0), int(quantize), fmt_of(fmt), out.data_ptr(),
                                         sf.data_ptr() if quantize else None, _stream()), "b200q_swiglu")
     return (out, sf) if quantize else out
+
+
+def swiglu_backward(g: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
+    """dg (rows, 2I) bf16 from g = [gate | up] (rows, 2I) and dh (rows, I)."""
+    g, dh = _mat(g), _mat(dh)
+    rows, i2 = g.shape
+    dg = torch.empty(rows, i2, dtype=torch.bfloat16, device=g.device)
+    _lib.check(_lib.load().b200q_swiglu_backward(g.data_ptr(), rows, i2 // 2, g.stride(0), dh.data_ptr(), dh.stride(0), dg.data_ptr(),
+                                                 dg.stride(0), _stream()), "b200q_swiglu_backward")
+    return dg
+
+
+def moe_unpermute_backward(dout: torch.Tensor, weights: torch.Tensor, y: torch.Tensor | None, plan: MoEPlan):
+    """(dy bf16 (padded_rows, D), dw fp32 (T, k) | None): gradients of moe_unpermute w.r.t. the expert
+    outputs and, when y is given, the routing weights."""
+    dout = _mat(dout)
+    t, d = dout.shape
+    w = weights.to(torch.bfloat16).contiguous()
+    k = w.shape[1]
+    dy = torch.empty(plan.padded_rows, d, dtype=torch.bfloat16, device=dout.device)
+    dw = torch.empty(t, k, dtype=torch.float32, device=dout.device) if y is not None else None
+    _lib.check(_lib.load().b200q_moe_unpermute_backward(dout.data_ptr(), w.data_ptr(), y.data_ptr() if y is not None else None,
+                                                        y.stride(0) if y is not None else 0, plan.row_of.data_ptr(),
+                                                        plan.src_of_row.data_ptr(), t, k, d, plan.padded_rows, dy.data_ptr(),
+                                                        dw.data_ptr() if dw is not None else None, _stream()),
+               "b200q_moe_unpermute_backward")
+    return dy, dw
 
 
 def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str = "softmax", normalize: bool = True, want_probs: bool = True,
