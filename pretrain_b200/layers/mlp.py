@@ -168,6 +168,90 @@ def grouped_mlp(x, w_in, w_down, act_fn, offs, gated, row_expert_ids=None, b_in=
     return out_p[plan.padded_offs.long()[expert] + rows - starts[expert]]
 
 
+def _cached(param: torch.Tensor, slot: str, key, make):
+    """Quantized copies of a weight, kept on the parameter until it is written again."""
+    key = (param._version, param.data_ptr(), key)
+    hit = getattr(param, slot, None)
+    if hit is None or hit[0] != key:
+        with torch.no_grad():
+            hit = (key, make())
+        setattr(param, slot, hit)
+    return hit[1]
+
+
+class DenseMLPBlock(nn.Module):
+    """Dense feed-forward block with the reference's constructor and (out, None) contract
+    (src/layers/mlp.py:103-150): ``down_proj(act(gate, up))`` with ``(gate, up) =
+    chunk(gate_up_proj(x))`` when gated, ``down_proj(act(up_proj(x)))`` otherwise.  Its Linears are
+    plain ``nn.Linear`` that ``apply_quantization`` swaps for ``QuantLinear`` like any other.
+
+    When both projections carry an all-MXFP8 or all-NVFP4 rule, the block is SwiGLU without biases
+    and no gradient is being recorded, the forward is three launches shorter than the composition:
+    the gate/up GEMM applies SwiGLU in its epilogue and hands the down projection MXFP8 codes, or
+    bf16 h plus its absolute maximum for NVFP4 (b200q_gemm_{mxfp8,nvfp4}_swiglu)."""
+
+    def __init__(self, d_model, *, intermediate_size, activation="silu", gated=True, bias=False, dropout=0.0):
+        super().__init__()
+        registry = GATED_ACTIVATIONS if gated else UNGATED_ACTIVATIONS
+        self.gated = gated
+        self.act_fn = registry[activation]
+        if gated:
+            self.gate_up_proj = nn.Linear(d_model, 2 * intermediate_size, bias=bias)
+        else:
+            self.up_proj = nn.Linear(d_model, intermediate_size, bias=bias)
+        self.down_proj = nn.Linear(intermediate_size, d_model, bias=bias)
+        self.dropout = nn.Dropout(dropout)
+
+    def _fused_kind(self, x):
+        """'mxfp8' / 'nvfp4' when the epilogue form applies to this call, else None."""
+        from ..quant.linear import QuantLinear
+        from ..quant.utils import is_mxfp8, is_nvfp4
+        if not (self.gated and self.act_fn is silu_glu and x.is_cuda and x.dtype == torch.bfloat16):
+            return None
+        up, down = self.gate_up_proj, self.down_proj
+        if not (isinstance(up, QuantLinear) and isinstance(down, QuantLinear)) or up.bias is not None or down.bias is not None:
+            return None
+        if _wants_grad(x, up.weight, down.weight) or up.weight.dtype != torch.bfloat16 and not torch.is_autocast_enabled("cuda"):
+            return None
+        inter, d = down.in_features, up.in_features
+        if inter % 64 or d % 32:
+            return None
+        fmts = [m.cfg.dtype[o] for m in (up, down) for o in ("act", "weight")]
+        if all(is_mxfp8(f) and not f.endswith("e5m2") for f in fmts):
+            return "mxfp8"
+        if all(is_nvfp4(f) for f in fmts):
+            return "nvfp4"
+        return None
+
+    def forward(self, x):
+        kind = self._fused_kind(x)
+        if kind is None:
+            if self.gated:
+                gate, up = self.gate_up_proj(x).chunk(2, dim=-1)
+                hidden = self.act_fn(gate, up)
+            else:
+                hidden = self.act_fn(self.up_proj(x))
+            return self.dropout(self.down_proj(hidden)), None
+        w_gu, w_d = self.gate_up_proj.weight, self.down_proj.weight
+        inter = self.down_proj.in_features
+        x2 = x.reshape(-1, x.shape[-1])
+        row_map = _glu_row_map(1, inter, x.device)
+        if kind == "mxfp8":
+            gq = _cached(w_gu, "_b200q_glu", "mx", lambda: ops.quantize_mxfp8_rowmap(w_gu.detach().to(torch.bfloat16), row_map))
+            dq = _cached(w_d, "_b200q_row", "mx", lambda: ops.quantize_mxfp8(w_d.detach().to(torch.bfloat16), 1))
+            xq, xsf = ops.quantize_mxfp8(x2, 1)
+            hq, hsf = ops.gemm_mxfp8_swiglu(xq, xsf, *gq)
+            out = ops.gemm_mxfp8(hq, hsf, *dq)
+        else:
+            gq = _cached(w_gu, "_b200q_glu", "nv", lambda: ops.quantize_nvfp4_rowmap(w_gu.detach().to(torch.bfloat16), row_map))
+            dq = _cached(w_d, "_b200q_row", "nv", lambda: ops.quantize_nvfp4(w_d.detach().to(torch.bfloat16), 1))
+            px, sx, tx = ops.quantize_nvfp4(x2, 1)
+            h, h_amax = ops.gemm_nvfp4_swiglu(px, sx, tx, *gq)
+            ph, sh, th = ops.quantize_nvfp4(h, 1, h_amax)
+            out = ops.gemm_nvfp4(ph, sh, th, *dq)
+        return self.dropout(out.reshape(*x.shape[:-1], out.shape[-1])), None
+
+
 class MoERouter(nn.Module):
     """Top-k router with an fp32-pinned gate (src/layers/mlp.py:248-302): fp32 logits, score
     function, top-k, weights normalised by their sum + 1e-9."""

@@ -183,6 +183,36 @@ def test_hp_weight_grad_differs_from_quantized():
     assert not torch.equal(grads[0], grads[1]) and _rel(grads[0], grads[1]) < 0.1
 
 
+@pytest.mark.parametrize("recipe", ["mxfp8", "nvfp4"])
+def test_dense_mlp_block_fused_forward_equals_the_composition(recipe):
+    """DenseMLPBlock (src/layers/mlp.py:103-150) after the module swap: without grad the gate/up GEMM does
+    SwiGLU in its epilogue; with grad it is the plain composition of two QuantLinears.  Same result up to the
+    bf16 rounding of silu(gate) * up (the epilogue follows the reference's bf16 steps; torch fuses differently)."""
+    from types import SimpleNamespace
+    from pretrain_b200.layers.mlp import DenseMLPBlock
+    from pretrain_b200.quant.config import TrainingConfig
+    from pretrain_b200.quant.convert import apply_quantization
+    from pretrain_b200.quant.linear import QuantLinear
+    torch.manual_seed(0)
+    blk = DenseMLPBlock(256, intermediate_size=384).cuda().bfloat16()
+    apply_quantization(blk, SimpleNamespace(training=TrainingConfig(quant={"enabled": True, "dtype_recipe": recipe, "exclude": []})))
+    assert isinstance(blk.gate_up_proj, QuantLinear) and isinstance(blk.down_proj, QuantLinear)
+    x = torch.randn(4, 96, 256, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        assert blk._fused_kind(x) == recipe
+        fused, none = blk(x)
+        gate, up = blk.gate_up_proj(x).chunk(2, dim=-1)
+        comp = blk.down_proj(torch.nn.functional.silu(gate) * up)
+    assert none is None and fused.shape == x.shape
+    assert _rel(fused, comp) < 2e-2
+    xg = x.clone().requires_grad_(True)
+    assert blk._fused_kind(xg) is None
+    out, _ = blk(xg)
+    out.float().square().mean().backward()
+    assert torch.isfinite(xg.grad).all() and blk.gate_up_proj.weight.grad is not None
+    assert _rel(out, comp) < 1e-3                    # the recorded path IS the composition
+
+
 def test_swapped_model_trains_one_step_and_compiles():
     from types import SimpleNamespace
     from pretrain_b200.quant.config import TrainingConfig
