@@ -43,6 +43,8 @@ WORKLOADS = {
     "int8_rowwise_linear_16384x2048x2048": ("int8", 16384, 2048, 2048),
     # MoE block: (kind, tokens, hidden, intermediate); 64 experts, top-4
     "moe_mxfp8_16384x768_e64_top4": ("moe", 16384, 768, 384),
+    # the same block, forward + backward (autograd function of SparseMoEBlock, 4 more grouped GEMMs)
+    "moe_mxfp8_training_16384x768_e64_top4": ("moe_train", 16384, 768, 384),
     # gated MLP in NVFP4: (kind, tokens, hidden, intermediate): gate_up GEMM, SwiGLU, re-quantize, down GEMM
     "nvfp4_mlp_16384x1024x3072": ("nvfp4_mlp", 16384, 1024, 3072),
     # the three GEMMs of one linear layer and step (fprop, dgrad, wgrad): (kind, M, N, K)
@@ -326,6 +328,82 @@ def run_moe(args, t, d, inter, rank, world, local):
         print(json.dumps(line))
 
 
+def run_moe_training(args, t, d, inter, rank, world, local):
+    """Forward + backward of the expert path of SparseMoEBlock (after the router): every tensor quantized
+    both ways once, 2 + 4 grouped MXFP8 GEMMs, SwiGLU forward and backward, unpermute forward and backward.
+    FLOP = 3 x the forward's GEMM FLOP (fprop, dgrad, wgrad of both layers)."""
+    from oracle import restate as R
+    from pretrain_b200 import build, ops
+    from pretrain_b200.layers.mlp import _ExpertFFN
+    if rank == 0:
+        build.build()
+    e, k = MOE_EXPERTS, MOE_TOPK
+    x, logits, w_gu, w_d = R.inputs_moe(t, d, e, k, inter, seed=rank)
+    top_i, top_w = R.router_topk(logits, k)
+    x, top_i, top_w, w_gu, w_d = (v.cuda() for v in (x, top_i, top_w, w_gu, w_d))
+    flops = 3 * 2.0 * t * k * (2 * inter * d + d * inter)
+    x.requires_grad_(True); top_w.requires_grad_(True); w_gu.requires_grad_(True); w_d.requires_grad_(True)
+    dout = torch.randn(t, d, device="cuda", dtype=torch.bfloat16)
+
+    def step():
+        plan = ops.moe_permute_plan(top_i, e)
+        out = _ExpertFFN.apply(x, top_w, w_gu, w_d, plan)
+        return torch.autograd.grad(out, (x, top_w, w_gu, w_d), dout)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        torch.cuda.synchronize()
+        t0.record()
+        for _ in range(args.steps):
+            step()
+        t1.record()
+        torch.cuda.synchronize()
+    ops.device_status()
+    ms_step = t0.elapsed_time(t1) / args.steps
+    hx, hd = x.detach().cpu().pin_memory(), dout.cpu().pin_memory()
+    hgx = torch.empty_like(hx).pin_memory()
+
+    def e2e_step():
+        xx = hx.to("cuda", non_blocking=True).requires_grad_(True)
+        out = _ExpertFFN.apply(xx, top_w, w_gu, w_d, ops.moe_permute_plan(top_i, e))
+        (gx,) = torch.autograd.grad(out, (xx,), hd.to("cuda", non_blocking=True))
+        hgx.copy_(gx, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    n_e2e = max(3, min(args.steps, 10))
+    t0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / n_e2e
+    peaks = measured_peaks()
+    peak = peaks["bf16_tflops_sustained"] * 2.0
+    achieved = flops / (ms_step * 1e-3) / 1e12
+    line = {"metric": "MoE block grouped-GEMM TFLOPS/GPU (forward + backward of the expert path)",
+            "value": world * achieved, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens_per_gpu": t, "hidden": d, "intermediate": inter, "experts": e, "top_k": k,
+                       "l2": "weights and permuted activations exceed L2; no flush needed"},
+            "clocks": clk.summary(),
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": (hx.numel() + hd.numel()) * 2, "d2h_bytes_per_step": hgx.numel() * 2},
+            "gpu_launches": 24 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "whole step (6 grouped GEMMs and the HBM-bound kernels between them)",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_source": f"2 x bf16_tflops_sustained, {peaks['source']}", "frac_of_nominal": achieved / 4500.0,
+                         "nominal_peak": 4500.0, "traffic": None, "kernel_ms": ms_step}}
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_moe_sample(t, d, inter)
+        print(json.dumps(line))
+
+
 def run_composite(args, kind, d0, d1, d2, rank, world, local):
     """Workloads made of several quantize / GEMM / elementwise launches: the NVFP4 gated MLP
     (tokens d0, hidden d1, intermediate d2) and the three GEMMs of a linear layer's step in FP8
@@ -560,7 +638,7 @@ def main():
             return
         torch.set_num_threads(len(os.sched_getaffinity(0)))     # torchrun pins OMP_NUM_THREADS=1
         steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
-        if kind == "moe":
+        if kind in ("moe", "moe_train"):
             cb = cpu_moe_sample(m, n, k)
         elif kind in ("nvfp4_mlp", "fp8_triple", "mxfp8_triple"):
             cb = cpu_composite_sample(kind, m, n, k)
@@ -579,6 +657,8 @@ def main():
     torch.cuda.set_device(local)
     if kind == "moe":
         return run_moe(args, m, n, k, rank, world, local)
+    if kind == "moe_train":
+        return run_moe_training(args, m, n, k, rank, world, local)
     if kind in ("nvfp4_mlp", "fp8_triple", "mxfp8_triple"):
         return run_composite(args, kind, m, n, k, rank, world, local)
     dist = None
