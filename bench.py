@@ -229,8 +229,14 @@ def run_moe(args, t, d, inter, rank, world, local):
     from oracle import restate as R
     from pretrain_b200 import build, ops
     from pretrain_b200.layers.mlp import SparseMoEBlock
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     if rank == 0:
         build.build()
+    if dist is not None:
+        dist.barrier()
     e, k = MOE_EXPERTS, MOE_TOPK
     x, logits, w_gu, w_d = R.inputs_moe(t, d, e, k, inter, seed=rank)
     top_i, top_w = R.router_topk(logits, k)
@@ -261,15 +267,24 @@ def run_moe(args, t, d, inter, rank, world, local):
     torch.cuda.synchronize()
     marks = []
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clk:
+    def barrier():
+        if dist is not None:
+            dist.barrier()
         torch.cuda.synchronize()
+
+    with ClockSampler(local) as clk:
+        barrier()
         t0.record()
         for _ in range(args.steps):
             step(marks)
         t1.record()
-        torch.cuda.synchronize()
+        barrier()
     ops.device_status()
     ms_step = t0.elapsed_time(t1) / args.steps
+    if dist is not None:
+        tt = torch.tensor([ms_step], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_step = tt.item()
     seg = [marks[i:i + 6] for i in range(0, len(marks), 6)]
     avg = lambda i: sum(sg[i].elapsed_time(sg[i + 1]) for sg in seg) / len(seg)
     permute_ms, wquant_ms, gemm1_ms, gemm2_ms, unperm_ms = (avg(i) for i in range(5))
@@ -298,6 +313,39 @@ def run_moe(args, t, d, inter, rank, world, local):
     torch.cuda.synchronize()
     e2e_ms = t0.elapsed_time(t1) / n_e2e
 
+    # ---- expert parallelism over the ranks (tokens stay sharded, experts split): the exchange by NCCL
+    # all-to-all, and by the kernels themselves over peer-mapped memory; reported beside `value`
+    expert_parallel = None
+    if dist is not None and e % world == 0:
+        from pretrain_b200 import dist as D
+        el = e // world
+        w1l, w2l = w_gu[rank * el:(rank + 1) * el].contiguous(), w_d[rank * el:(rank + 1) * el].contiguous()
+
+        def timed(fn, n=20):
+            for _ in range(3):
+                fn()
+            dist.barrier(); torch.cuda.synchronize()
+            t0.record()
+            for _ in range(n):
+                fn()
+            t1.record()
+            dist.barrier(); torch.cuda.synchronize()
+            tt = torch.tensor([t0.elapsed_time(t1) / n], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return tt.item()
+
+        with torch.no_grad():
+            nccl_ms = timed(lambda: D.expert_parallel_moe(x, top_i, top_w, w1l, w2l, e))
+            expert_parallel = {"nccl_all_to_all_ms": nccl_ms, "nccl_tflops": world * flops / (nccl_ms * 1e-3) / 1e12}
+            try:
+                ep = D.FusedExpertParallel(t, k, d, e)
+                fused_ms = timed(lambda: ep.forward(x, top_i, top_w, w1l, w2l))
+                expert_parallel.update(fused_ms=fused_ms, fused_tflops=world * flops / (fused_ms * 1e-3) / 1e12,
+                                       fused="dispatch = gather + MXFP8 kernel storing into the owners' buffers, combine = "
+                                             "unpermute kernel loading from them (symmetric memory, NVLink)")
+            except Exception as ex:                       # symmetric memory not available on this system
+                expert_parallel["fused_error"] = str(ex)[:200]
+
     peaks = measured_peaks()
     peak = peaks["bf16_tflops_sustained"] * 2.0
     gemm_ms = gemm1_ms + gemm2_ms
@@ -322,10 +370,14 @@ def run_moe(args, t, d, inter, rank, world, local):
             "permute": dict(bound="hbm", **hbm(n_pairs * d * 3.03125, permute_ms), note="plan kernels + gather fused with MXFP8"),
             "weight_quantize": dict(bound="hbm", **hbm((w_gu.numel() + w_d.numel()) * 3.03125, wquant_ms)),
             "unpermute": dict(bound="hbm", **hbm(n_pairs * d * 2 + t * d * 2, unperm_ms))}
+    if expert_parallel is not None:
+        line["expert_parallel"] = expert_parallel
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_moe_sample(t, d, inter)
         print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 def run_moe_training(args, t, d, inter, rank, world, local):

@@ -284,6 +284,32 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
                                     const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
                                     int64_t K, void* H, int64_t ldh, void* sfH, void* stream);
 
+/* Expert parallelism inside one NVLink domain without a collective on the data path: ranks own
+ * contiguous ranges of experts_per_rank experts and expose their buffers to each other (peer-mapped
+ * device memory; the reference is single-GPU and has no counterpart).
+ *
+ * dispatch: the sender walks ITS padded expert-sorted plan over all E experts (src_of_row,
+ * tile_expert, padded_offs, num_tiles from b200q_moe_permute_plan) and writes every routed row,
+ * MXFP8-quantized along D, into the owner's buffers: row row_base[e] + (rank of the row inside the
+ * sender's segment of e) of peer_codes[e / experts_per_rank] ([rows, D] codes) and peer_sf[...]
+ * (128x4-tiled scale factors).  row_base[E] comes from the exchanged counts.  Stores only.
+ * zero_pad_rows: the owner clears the rows of its own buffers that no sender writes (src_of_row < 0
+ * in the owner's b200q_moe_pad_plan).
+ * combine: out[t] = sum_j w[t,j] * peer_y[pair_peer[t*k+j]][pair_row[t*k+j]] with the expert
+ * outputs (bf16, pitch ldy) loaded in place from their owners; fp32 accumulation, one rounding.
+ * The caller orders dispatch -> (all ranks) -> owner's GEMMs -> (all ranks) -> combine.
+ * D % 128 == 0, world <= 8. */
+int b200q_moe_dispatch_peers(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row,
+                             const int32_t* tile_expert, const int32_t* padded_offs,
+                             const int32_t* num_tiles, int64_t padded_rows, const int32_t* row_base,
+                             int experts_per_rank, int world, void* const* peer_codes,
+                             void* const* peer_sf, void* stream);
+int b200q_moe_zero_pad_rows(const int32_t* src_of_row, const int32_t* num_tiles, int64_t padded_rows,
+                            int64_t D, void* codes, void* sf, void* stream);
+int b200q_moe_combine_peers(void* const* peer_y, int world, int64_t ldy, const void* w,
+                            const int32_t* pair_peer, const int32_t* pair_row, int64_t T, int k,
+                            int64_t D, void* out, void* stream);
+
 /* Backward of b200q_swiglu(quantize = 0): dg[r] = [dh * up * silu'(gate) | dh * silu(gate)] for
  * g[r] = [gate | up]; bf16 in and out, fp32 arithmetic (the reference gets this from autograd through
  * src/layers/activation.py:80-81).  I % 8 == 0. */

@@ -10,6 +10,7 @@ namespace b200q {
 namespace {
 
 constexpr int kPlanThreads = 1024;       // pairs per CTA in the plan kernels
+constexpr int kMaxPeers = 8;             // ranks of one NVLink domain
 constexpr int kMaxExperts = 256;
 
 // ---- plan, step 1: per-CTA histogram of expert ids -------------------------------------------
@@ -420,6 +421,95 @@ moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t
   }
 }
 
+// ---- expert-parallel dispatch / combine over peer-mapped memory -----------------------------------
+// Dispatch: the sender's gather + MXFP8 kernel writes every routed row straight into the padded
+// expert-sorted buffer of the rank that owns its expert (plain stores to peer-mapped memory over
+// NVLink; nothing is loaded from a peer here).  The sender walks its OWN padded layout (row r ->
+// token src_of_row[r], expert tile_expert[r / 128]); row_base[e] is where this rank's rows of
+// global expert e start in the owner's buffer, so the destination row keeps the sender's stable
+// order inside the expert.
+struct PeerBufs {
+  uint8_t* codes[kMaxPeers];
+  uint8_t* sf[kMaxPeers];
+};
+
+__global__ void __launch_bounds__(256)
+moe_dispatch_kernel(const uint16_t* __restrict__ x, int64_t D, int64_t ld, const int32_t* __restrict__ src_of_row,
+                    const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ padded_offs,
+                    const int32_t* __restrict__ num_tiles, int64_t padded_rows, const int32_t* __restrict__ row_base,
+                    int experts_per_rank, const PeerBufs peers) {
+  int64_t live_rows = (int64_t)(*num_tiles) << 7;
+  if (live_rows > padded_rows) live_rows = padded_rows;
+  const int runs = (int)(D >> 5);
+  const int64_t kt = ((D >> 5) + 3) >> 2;
+  for (ItemWalker w((int64_t)blockIdx.x * 256 + threadIdx.x, (int64_t)gridDim.x * 256, runs); w.row < live_rows; w.next()) {
+    const int64_t r = w.row;
+    const int src = src_of_row[r];
+    if (src < 0) continue;                               // the sender's own pad rows are not sent
+    const int e = tile_expert[r >> 7];
+    const int dst = e / experts_per_rank;
+    const int64_t drow = (int64_t)row_base[e] + (r - padded_offs[e]);
+    const int c = w.chunk << 5;
+    uint4 v[4];
+    const uint16_t* xp = x + (int64_t)src * ld + c;
+    ld_nc_32B<false>(xp, v[0], v[1]);
+    ld_nc_32B<false>(xp + 16, v[2], v[3]);
+    uint32_t o[8];
+    const int ex = mx_quant_block32<FMT_E4M3>(v, o);
+    st_32B<false>(peers.codes[dst] + drow * D + c, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+    peers.sf[dst][sf_swizzled(drow, w.chunk, kt)] = (uint8_t)(ex + 127);
+  }
+}
+
+// The receiver clears the pad rows of its own buffer (rows no sender writes): zero codes, scale 2^0.
+__global__ void __launch_bounds__(256)
+moe_zero_pad_rows_kernel(const int32_t* __restrict__ src_of_row, const int32_t* __restrict__ num_tiles, int64_t padded_rows,
+                         int64_t D, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf) {
+  int64_t live_rows = (int64_t)(*num_tiles) << 7;
+  if (live_rows > padded_rows) live_rows = padded_rows;
+  const int runs = (int)(D >> 5);
+  const int64_t kt = ((D >> 5) + 3) >> 2;
+  for (ItemWalker w((int64_t)blockIdx.x * 256 + threadIdx.x, (int64_t)gridDim.x * 256, runs); w.row < live_rows; w.next()) {
+    if (src_of_row[w.row] >= 0) continue;
+    st_32B<false>(codes + w.row * D + (w.chunk << 5), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0));
+    sf[sf_swizzled(w.row, w.chunk, kt)] = 127;
+  }
+}
+
+// Combine: out[t] = sum_j w[t,j] * y_{peer[t,j]}[row[t,j]] with the expert outputs read in place from
+// the owners' buffers (plain loads from peer-mapped memory), fp32 accumulation in slot order, one
+// rounding - the arithmetic of moe_unpermute_kernel.
+struct PeerRows {
+  const uint16_t* y[kMaxPeers];
+};
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const PeerRows peers, int64_t ldy, const uint16_t* __restrict__ w, const int32_t* __restrict__ pair_peer,
+                   const int32_t* __restrict__ pair_row, int64_t T, int k, int64_t D, uint16_t* __restrict__ out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (ItemWalker it((int64_t)blockIdx.x * 8 + warp, (int64_t)gridDim.x * 8, (int)((D + 255) >> 8)); it.row < T; it.next()) {
+    const int64_t t = it.row, c = (int64_t)it.chunk * 256 + lane * 8;
+    if (c >= D) continue;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < k; ++j) {
+      const uint16_t* base = peers.y[pair_peer[t * k + j]];
+      const float wj = u2f((uint32_t)w[t * k + j] << 16);
+      float f[8];
+      const uint4 v = *reinterpret_cast<const uint4*>(base + (int64_t)pair_row[t * k + j] * ldy + c);
+      unpack8(v, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(wj, f[i], acc[i]);
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      o[i] = *reinterpret_cast<uint32_t*>(&p);
+    }
+    *reinterpret_cast<uint4*>(out + t * D + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // ---- backward of SwiGLU: dg = [dh * up * silu'(gate) | dh * silu(gate)] -------------------------
 // silu'(x) = s (1 + x (1 - s)), s = 1 / (1 + e^-x); fp32 arithmetic on the bf16 inputs, one rounding.
 __global__ void __launch_bounds__(256)
@@ -638,6 +728,65 @@ int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantiz
   else if (fmt == B200Q_E4M3) { if (wide) B200Q_GO(1, true, FMT_E4M3); else B200Q_GO(1, false, FMT_E4M3); }
   else { if (wide) B200Q_GO(1, true, FMT_E5M2); else B200Q_GO(1, false, FMT_E5M2); }
 #undef B200Q_GO
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_dispatch_peers(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row, const int32_t* tile_expert,
+                             const int32_t* padded_offs, const int32_t* num_tiles, int64_t padded_rows, const int32_t* row_base,
+                             int experts_per_rank, int world, void* const* peer_codes, void* const* peer_sf, void* stream) {
+  if (x == nullptr || src_of_row == nullptr || tile_expert == nullptr || padded_offs == nullptr || num_tiles == nullptr ||
+      row_base == nullptr || peer_codes == nullptr || peer_sf == nullptr || D <= 0 || ld < D || padded_rows <= 0 ||
+      experts_per_rank <= 0 || world < 1 || world > kMaxPeers)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 127) || (ld & 7) || (padded_rows & 127)) return B200Q_ERR_SHAPE;      // whole scale-factor tiles along D
+  if (!aligned16(x)) return B200Q_ERR_ALIGNMENT;
+  PeerBufs peers = {};
+  for (int i = 0; i < world; ++i) {
+    if (peer_codes[i] == nullptr || peer_sf[i] == nullptr) return B200Q_ERR_INVALID_ARG;
+    if (!aligned16(peer_codes[i])) return B200Q_ERR_ALIGNMENT;
+    peers.codes[i] = (uint8_t*)peer_codes[i];
+    peers.sf[i] = (uint8_t*)peer_sf[i];
+  }
+  int rc = require_sm100();
+  if (rc) return rc;
+  moe_dispatch_kernel<<<thread_item_grid(padded_rows * (D >> 5)), 256, 0, (cudaStream_t)stream>>>(
+      (const uint16_t*)x, D, ld, src_of_row, tile_expert, padded_offs, num_tiles, padded_rows, row_base, experts_per_rank, peers);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_zero_pad_rows(const int32_t* src_of_row, const int32_t* num_tiles, int64_t padded_rows, int64_t D, void* codes,
+                            void* sf, void* stream) {
+  if (src_of_row == nullptr || num_tiles == nullptr || codes == nullptr || sf == nullptr || padded_rows <= 0 || D <= 0)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 127) || (padded_rows & 127)) return B200Q_ERR_SHAPE;
+  if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  moe_zero_pad_rows_kernel<<<thread_item_grid(padded_rows * (D >> 5)), 256, 0, (cudaStream_t)stream>>>(
+      src_of_row, num_tiles, padded_rows, D, (uint8_t*)codes, (uint8_t*)sf);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_combine_peers(void* const* peer_y, int world, int64_t ldy, const void* w, const int32_t* pair_peer,
+                            const int32_t* pair_row, int64_t T, int k, int64_t D, void* out, void* stream) {
+  if (peer_y == nullptr || w == nullptr || pair_peer == nullptr || pair_row == nullptr || out == nullptr || T <= 0 || k <= 0 ||
+      D <= 0 || ldy < D || world < 1 || world > kMaxPeers)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 7) || (ldy & 7)) return B200Q_ERR_SHAPE;
+  if (!aligned16(out)) return B200Q_ERR_ALIGNMENT;
+  PeerRows peers = {};
+  for (int i = 0; i < world; ++i) {
+    if (peer_y[i] == nullptr) return B200Q_ERR_INVALID_ARG;
+    if (!aligned16(peer_y[i])) return B200Q_ERR_ALIGNMENT;
+    peers.y[i] = (const uint16_t*)peer_y[i];
+  }
+  int rc = require_sm100();
+  if (rc) return rc;
+  moe_combine_kernel<<<row_grid(T * ((D + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(peers, ldy, (const uint16_t*)w, pair_peer,
+                                                                                      pair_row, T, k, D, (uint16_t*)out);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

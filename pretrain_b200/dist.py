@@ -162,6 +162,76 @@ def ep_combine(y: torch.Tensor, state: DispatchState, top_weights: torch.Tensor,
     return (per_pair.view(t, k, -1).float() * w).sum(1).to(y.dtype)
 
 
+class FusedExpertParallel:
+    """Expert-parallel MoE forward inside one NVLink domain with the exchange done by the kernels
+    themselves: the dispatch is the permute's gather + MXFP8 kernel storing each routed row straight
+    into the buffer of the rank that owns its expert, the combine is the unpermute kernel loading the
+    expert outputs in place from their owners.  The only collectives left are one all-gather of the
+    per-expert counts (E integers per rank) and two stream-ordered rendezvous.
+
+    Buffers are symmetric memory sized for `capacity_rows` received rows per rank (default: every
+    routed row of every rank).  Results equal the single-GPU block on the concatenated tokens bit
+    for bit when the ranks hold consecutive token ranges."""
+
+    def __init__(self, tokens_per_rank: int, top_k: int, d_model: int, n_experts: int, group=None, capacity_rows: int | None = None):
+        import torch.distributed._symmetric_memory as symm
+        from . import ops
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if n_experts % self.world or d_model % 128:
+            raise ValueError("experts must split evenly over the ranks and d_model must be a multiple of 128")
+        self.e, self.e_local, self.d, self.k, self.t = n_experts, n_experts // self.world, d_model, top_k, tokens_per_rank
+        rows = capacity_rows if capacity_rows is not None else self.world * tokens_per_rank * top_k
+        self.rows, self.check_capacity = rows, capacity_rows is not None       # the default capacity cannot overflow
+        self.cap = ops.moe_padded_rows(rows, self.e_local)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.codes = symm.empty((self.cap, d_model), dtype=torch.uint8, device=dev)
+        self.sf = symm.empty((ops.sf_bytes(self.cap, d_model // 32),), dtype=torch.uint8, device=dev)
+        self.y = symm.empty((self.cap, d_model), dtype=torch.bfloat16, device=dev)
+        hs = [symm.rendezvous(b, self.group) for b in (self.codes, self.sf, self.y)]
+        self.codes_ptrs, self.sf_ptrs, self.y_ptrs = ([int(p) for p in h.buffer_ptrs] for h in hs)
+        self._handles = hs
+        self._flag = torch.zeros(1, device=dev)
+
+    def _rendezvous(self):
+        dist.all_reduce(self._flag, group=self.group)      # stream-ordered: every rank's stores before it have landed
+
+    def forward(self, x: torch.Tensor, top_indices: torch.Tensor, top_weights: torch.Tensor, w_in_local: torch.Tensor,
+                w_down_local: torch.Tensor) -> torch.Tensor:
+        from . import ops
+        from .layers.mlp import _grouped_ffn_padded, silu_glu
+        t, k = top_indices.shape
+        counts = torch.bincount(top_indices.reshape(-1), minlength=self.e).to(torch.int32)
+        all_counts = torch.empty(self.world, self.e, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(all_counts, counts, group=self.group)                       # [src rank][global expert]
+        # layout of every owner's buffer: experts' segments padded to 128 rows, senders in rank order inside a segment
+        totals = all_counts.sum(0)
+        padded = (totals + 127) // 128 * 128
+        seg_start = (padded.view(self.world, self.e_local).cumsum(1) - padded.view(self.world, self.e_local)).reshape(-1)
+        before_me = all_counts[: self.rank].sum(0)
+        row_base = (seg_start + before_me).to(torch.int32)
+        if self.check_capacity and int(padded.view(self.world, self.e_local).sum(1).max()) > self.cap:     # host sync
+            raise RuntimeError("received rows exceed the capacity of the expert-parallel buffers")
+        # my rows leave in my own stable expert order
+        plan = ops.moe_permute_plan(top_indices, self.e)
+        # what I own: segment table of my experts
+        my_totals = totals.view(self.world, self.e_local)[self.rank]
+        own = ops.moe_pad_plan(my_totals.cumsum(0).to(torch.int32), self.rows)
+        ops.moe_zero_pad_rows(own, self.d, self.codes, self.sf)
+        ops.moe_dispatch_peers(x.to(torch.bfloat16), plan, row_base, self.e_local, self.codes_ptrs, self.sf_ptrs)
+        self._rendezvous()
+        _grouped_ffn_padded(self.codes, self.sf, own, w_in_local.to(torch.bfloat16), w_down_local.to(torch.bfloat16), silu_glu, True,
+                            out=self.y)                        # the second GEMM writes where the peers will read
+        self._rendezvous()
+        # where every (token, slot) pair's output row lives
+        flat_e = top_indices.reshape(-1)
+        pair_peer = (flat_e // self.e_local).to(torch.int32)
+        pair_row = (row_base.long()[flat_e] + plan.row_of.long() - plan.padded_offs.long()[flat_e]).to(torch.int32)
+        out = ops.moe_combine_peers(self.y_ptrs, self.d, top_weights, pair_peer, pair_row, self.d)
+        self._rendezvous()                                   # nobody overwrites y or the codes while a peer still reads them
+        return out.to(x.dtype)
+
+
 def expert_ffn_local(rows: torch.Tensor, expert_ids: torch.Tensor, w_in: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
     """Gated-SwiGLU expert FFN for rows in ARBITRARY order with their local expert ids, on the
     MXFP8 kernels: local permute plan, fused gather+quantize, two grouped GEMMs with the fused

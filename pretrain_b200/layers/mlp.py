@@ -118,8 +118,9 @@ def _glu_row_map(e: int, inter: int, device) -> torch.Tensor:
     return _ROW_MAPS[key]
 
 
-def _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in=None, b_down=None):
-    """Both grouped GEMMs and the activation on the padded layout; returns (padded_rows, D_out) bf16."""
+def _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in=None, b_down=None, out=None):
+    """Both grouped GEMMs and the activation on the padded layout; returns (padded_rows, D_out) bf16
+    (written into `out` when given and the expert width needs no padding)."""
     n1, n2 = w_in.shape[1], w_down.shape[1]
     wq2, wsf2 = _quantize_expert_weights(w_down)
     e = w_in.shape[0]
@@ -138,7 +139,7 @@ def _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in=None, b_
         else:
             act = act_fn(*h.chunk(2, dim=-1)) if gated else act_fn(h)
             hq, hsf = ops.quantize_mxfp8(act.contiguous(), 1)
-    out = ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, wq2.shape[0] // e)[:, :n2]
+    out = ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, wq2.shape[0] // e, out=out if n2 % 128 == 0 else None)[:, :n2]
     if b_down is not None:
         out = out + b_down.to(out.dtype)[_expert_of_padded_row(plan)]
     return out

@@ -429,6 +429,31 @@ def swiglu(g: torch.Tensor, quantize: bool, fmt=E4M3):
     return (out, sf) if quantize else out
 
 
+def moe_dispatch_peers(x: torch.Tensor, plan: MoEPlan, row_base: torch.Tensor, experts_per_rank: int, peer_codes, peer_sf):
+    """Quantize this rank's routed rows (plan over ALL experts) to MXFP8 and store them into their owners'
+    buffers; peer_codes / peer_sf are the device pointers of every rank's buffers (own and peer-mapped)."""
+    x = _mat(x)
+    _lib.check(_lib.load().b200q_moe_dispatch_peers(x.data_ptr(), x.shape[1], x.stride(0), plan.src_of_row.data_ptr(),
+                                                    plan.tile_expert.data_ptr(), plan.padded_offs.data_ptr(), plan.num_tiles.data_ptr(),
+                                                    plan.padded_rows, row_base.data_ptr(), experts_per_rank, len(peer_codes),
+                                                    _ptr_array(peer_codes), _ptr_array(peer_sf), _stream()), "b200q_moe_dispatch_peers")
+
+
+def moe_zero_pad_rows(plan: MoEPlan, d: int, codes: torch.Tensor, sf: torch.Tensor):
+    _lib.check(_lib.load().b200q_moe_zero_pad_rows(plan.src_of_row.data_ptr(), plan.num_tiles.data_ptr(), plan.padded_rows, d,
+                                                   codes.data_ptr(), sf.data_ptr(), _stream()), "b200q_moe_zero_pad_rows")
+
+
+def moe_combine_peers(peer_y, ldy: int, weights: torch.Tensor, pair_peer: torch.Tensor, pair_row: torch.Tensor, d: int):
+    """out[t] = sum_j weights[t, j] * y_{pair_peer[t, j]}[pair_row[t, j]], the rows read from their owners' buffers."""
+    t, k = weights.shape
+    w = weights.to(torch.bfloat16).contiguous()
+    out = torch.empty(t, d, dtype=torch.bfloat16, device=w.device)
+    _lib.check(_lib.load().b200q_moe_combine_peers(_ptr_array(peer_y), len(peer_y), ldy, w.data_ptr(), pair_peer.data_ptr(),
+                                                   pair_row.data_ptr(), t, k, d, out.data_ptr(), _stream()), "b200q_moe_combine_peers")
+    return out
+
+
 def swiglu_backward(g: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
     """dg (rows, 2I) bf16 from g = [gate | up] (rows, 2I) and dh (rows, I)."""
     g, dh = _mat(g), _mat(dh)

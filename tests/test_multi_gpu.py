@@ -110,3 +110,31 @@ def _ep_rank(rank, world):
 
 def test_expert_parallel_moe_matches_single_gpu():
     _run(_ep_rank, 2)
+
+
+def _fused_ep_rank(rank, world):
+    from pretrain_b200 import dist as D, ops
+    from pretrain_b200.layers.mlp import _grouped_ffn_padded, silu_glu
+    t, d, e, k, i = 1024, 256, 16, 4, 128
+    x, logits, w_gu, w_d = R.inputs_moe(world * t, d, e, k, i, seed=6)
+    logits[:, 5] = -1e9                                                 # an expert nobody picks
+    logits[: world * t // 2, 9] += 4.0                                  # and one that the first rank's tokens crowd
+    top_i, top_w = R.router_topk(logits, k)
+    x, top_i, top_w, w_gu, w_d = (v.cuda() for v in (x, top_i, top_w, w_gu, w_d))
+    lo, hi, el = rank * t, (rank + 1) * t, e // world
+    ep = D.FusedExpertParallel(t, k, d, e)
+    with torch.no_grad():
+        outs = [ep.forward(x[lo:hi], top_i[lo:hi], top_w[lo:hi], w_gu[rank * el:(rank + 1) * el].contiguous(),
+                           w_d[rank * el:(rank + 1) * el].contiguous()) for _ in range(2)]      # buffers are reused
+        plan = ops.moe_permute_plan(top_i, e)
+        a, sfa = ops.moe_gather(x, plan, True)
+        y = _grouped_ffn_padded(a, sfa, plan, w_gu, w_d, silu_glu, True)
+        ref = ops.moe_unpermute(y, top_w, plan.row_of, world * t)[lo:hi]
+    ops.device_status()
+    # same rows, same kernels, same order of the k additions: the same bits as one GPU over all tokens
+    assert torch.equal(outs[0], ref) and torch.equal(outs[1], ref)
+
+
+def test_fused_expert_parallel_equals_single_gpu_bit_for_bit():
+    """Dispatch by stores into the owners' buffers, combine by loads from them (no all-to-all)."""
+    _run(_fused_ep_rank, 2)
