@@ -254,6 +254,26 @@ def test_mxfp8_linear_config_against_cpu_oracle(ops):
     _check(out[rows], ref)
 
 
+def test_largest_square_16384(ops):
+    """16384^3, the largest benchmark size (8.8 TFLOP, tile and K-step counts at their maxima for the
+    configurations of record): sampled rows against the fp32 reference, and the GEMM of the row-reversed
+    operand equals the row-reversed GEMM (the output rows are independent), bit for bit."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    n = 16384
+    a = torch.randn(n, n, generator=g, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(n, n, generator=g, device="cuda", dtype=torch.bfloat16)
+    ca, sfa = ops.quantize_mxfp8(a); cb, sfb = ops.quantize_mxfp8(b)
+    out = ops.gemm_mxfp8(ca, sfa, cb, sfb)
+    ops.device_status()
+    rows = torch.arange(5, n, 331, device="cuda")
+    _check(out[rows], G.matmul_fp32(G.deq_mxfp8(ca, sfa)[rows], G.deq_mxfp8(cb, sfb)))
+    del cb, sfb
+    ca2, sfa2 = ops.quantize_mxfp8(a.flip(0).contiguous())
+    cb, sfb = ops.quantize_mxfp8(b)
+    out2 = ops.gemm_mxfp8(ca2, sfa2, cb, sfb)
+    assert torch.equal(out2.flip(0), out)
+
+
 def test_large_square_linearity(ops):
     """8192^3 (the headline size): compared on sampled rows with an fp32 reference, plus
     linearity in the scale factors (doubling every A scale doubles D exactly)."""
