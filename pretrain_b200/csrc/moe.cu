@@ -316,8 +316,9 @@ swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t l
 // larger logit first, then the lower expert index), weights = probs[idx] / (sum + 1e-9) when
 // normalising, both cast to bf16, plus how many tokens chose each expert.  Lane l holds experts
 // l, l + 32, ... (E <= 256).
-constexpr int kRouterMaxPerLane = kMaxExperts / 32;
-
+// PER = experts per lane (1, 2, 4 or 8: the smallest that covers E), a template argument so that the
+// loops over a lane's experts have no idle iterations.
+template <int PER>
 __global__ void __launch_bounds__(256)
 moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k, int sigmoid, int normalize,
                        int64_t* __restrict__ top_idx, uint16_t* __restrict__ top_w, uint16_t* __restrict__ probs_out,
@@ -326,7 +327,8 @@ moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < E; i += 256) hist[i] = 0;
   __syncthreads();
-  const int per = (E + 31) >> 5;
+  constexpr int kRouterMaxPerLane = PER;
+  const int per = PER;
   for (int64_t t = (int64_t)blockIdx.x * 8 + warp; t < T; t += (int64_t)gridDim.x * 8) {
     float v[kRouterMaxPerLane], p[kRouterMaxPerLane];
     float m = -INFINITY;
@@ -377,7 +379,11 @@ moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k
         const int oe = __shfl_xor_sync(0xFFFFFFFFu, be, o);
         if (op > bp || (op == bp && (ov > bv || (ov == bv && oe < be)))) { bp = op; bv = ov; be = oe; }
       }
-      if ((be & 31) == lane) p[be >> 5] = -2.f;        // compile-time indexing is kept by the unrolled form below
+      if ((be & 31) == lane) {                         // selects over the PER registers, no local memory
+#pragma unroll
+        for (int j = 0; j < kRouterMaxPerLane; ++j)
+          if (j == (be >> 5)) p[j] = -2.f;
+      }
       wsum += bp;
       if (lane == r) { mine = bp; mine_idx = be; }
     }
@@ -831,8 +837,14 @@ int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int scor
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (expert_counts != nullptr) B200Q_CUDA(cudaMemsetAsync(expert_counts, 0, (size_t)E * sizeof(int32_t), st));
-  moe_router_topk_kernel<<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, (uint16_t*)top_w,
-                                                      (uint16_t*)probs, expert_counts);
+#define B200Q_GO(P) \
+  moe_router_topk_kernel<P><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, (uint16_t*)top_w, \
+                                                         (uint16_t*)probs, expert_counts)
+  if (E <= 32) B200Q_GO(1);
+  else if (E <= 64) B200Q_GO(2);
+  else if (E <= 128) B200Q_GO(4);
+  else B200Q_GO(8);
+#undef B200Q_GO
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
