@@ -68,6 +68,18 @@ int b200q_quantize_fp8_tensorwise(const void* x, int64_t rows, int64_t cols, int
                                   int fmt, const float* tensor_amax, void* codes, float* scale_out,
                                   void* stream);
 
+/* Both per-row and per-column FP8 copies of one tensor, i.e. quantize_fp8(x, dtype, dim=-1) and
+ * quantize_fp8(x, dtype, dim=0) of src/quant/fp8.py:16-32 (a linear layer's step needs both of x, w
+ * and the output gradient: src/quant/linear.py:74,98,102), in two reads of x instead of three: the
+ * row-wise pass also reduces |x| down the columns, so the column direction needs no amax pass of
+ * its own.  Outputs as b200q_quantize_fp8 with axis = 1 (codes_row [rows, cols], scales_row[rows])
+ * and axis = 0 (codes_col [cols, rows], scales_col[cols]), bit for bit.  workspace:
+ * b200q_quantize_fp8_both_workspace_bytes(cols) bytes.  rows % 16 == 0, cols <= 8192. */
+int64_t b200q_quantize_fp8_both_workspace_bytes(int64_t cols);
+int b200q_quantize_fp8_both(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt,
+                            void* codes_row, float* scales_row, void* codes_col, float* scales_col,
+                            void* workspace, void* stream);
+
 /* quantize_int8(x, qmax, dim) of src/quant/int8.py:9-19, the int8 series (int8 .. int4 in an int8
  * container; qmax = 127, 63, 31, 15, 7 as in src/quant/utils.py:19): scale = max(amax/qmax, 1e-12),
  * codes = clamp(round_half_even(x/scale), +-qmax).  Same axis / shape rules as b200q_quantize_fp8 and

@@ -24,6 +24,8 @@ SIGNATURES = {
     "b200q_quantize_fp8_tensorwise": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp, _vp]),
     "b200q_quantize_mxfp8": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _int, _vp]),
     "b200q_quantize_nvfp4": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp, _vp]),
+    "b200q_quantize_fp8_both_workspace_bytes": (_i64, [_i64]),
+    "b200q_quantize_fp8_both": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_quantize_int8": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]),
     "b200q_quantize_int8_tensorwise": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp, _vp]),
     "b200q_gemm_int8": (_int, [_vp, _vp, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp]),

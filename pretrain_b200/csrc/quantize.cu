@@ -144,15 +144,20 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
 // 16-byte vectors per lane; partial maxima meet in shared memory).  NVEC == 0 re-reads the row
 // (it is still in L2) for rows too long for that.
 // ------------------------------------------------------------------------------------------
-template <int NVEC, int FMT>
+// COLMAX: the same pass also reduces |x| down the columns (for the per-column scales of the transposed
+// copy of the same tensor): every thread keeps the maxima of its columns over the rows it visits, the
+// CTA merges its row groups in shared memory and writes one row of partial maxima (packed bf16) per CTA.
+template <int NVEC, int FMT, bool COLMAX = false>
 __global__ void __launch_bounds__(kThreads)
 rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                    uint8_t* __restrict__ codes, float* __restrict__ scales, const float* __restrict__ tensor_amax,
-                   float* __restrict__ tensor_scale_out, int wpr, float qmax) {
+                   float* __restrict__ tensor_scale_out, int wpr, float qmax, unsigned int* __restrict__ col_partials = nullptr) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int fmt = FMT;
   const int grp = warp / wpr, wig = warp - grp * wpr, rpc = kWarps / wpr;
   __shared__ float smax[2][kWarps];
+  extern __shared__ unsigned int colmax_s[];            // COLMAX: [row groups of the CTA][cols / 2] packed bf16 pairs
+  uint32_t cm[COLMAX && NVEC > 0 ? NVEC * 4 : 1] = {};
   int it = 0;
   for (int64_t base = (int64_t)blockIdx.x * rpc; base < rows; base += (int64_t)gridDim.x * rpc, ++it) {
     const int64_t row = base + grp;
@@ -170,6 +175,12 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
       for (int i = 0; i < NVEC; ++i) {
         m = absmax_bf16x2(m, absmax_bf16x2(v[i].x, v[i].y));
         m = absmax_bf16x2(m, absmax_bf16x2(v[i].z, v[i].w));
+        if (COLMAX) {
+          cm[4 * i] = absmax_bf16x2(cm[4 * i], v[i].x);
+          cm[4 * i + 1] = absmax_bf16x2(cm[4 * i + 1], v[i].y);
+          cm[4 * i + 2] = absmax_bf16x2(cm[4 * i + 2], v[i].z);
+          cm[4 * i + 3] = absmax_bf16x2(cm[4 * i + 3], v[i].w);
+        }
       }
     } else if (tensor_amax == nullptr && live) {
       for (int64_t c = (wig * 32 + lane) * 8; c < cols; c += 256 * wpr) {
@@ -217,6 +228,42 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
         *reinterpret_cast<uint2*>(cr + c) = o;
       }
     }
+  }
+  if (COLMAX && NVEC > 0) {
+    const int64_t half = cols >> 1;                    // words per row group
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int64_t c = (int64_t)((i * wpr + wig) * 32 + lane) * 8;
+      if (c < cols)
+        *reinterpret_cast<uint4*>(&colmax_s[grp * half + (c >> 1)]) = make_uint4(cm[4 * i], cm[4 * i + 1], cm[4 * i + 2], cm[4 * i + 3]);
+    }
+    __syncthreads();
+    for (int64_t wi = threadIdx.x; wi < half; wi += kThreads) {
+      uint32_t m = colmax_s[wi];
+      for (int g2 = 1; g2 < rpc; ++g2) m = absmax_bf16x2(m, colmax_s[g2 * half + wi]);
+      col_partials[(int64_t)blockIdx.x * half + wi] = m;
+    }
+  }
+}
+
+// scales[c] = scale(max over the CTAs' partial column maxima)
+__global__ void __launch_bounds__(1024)
+col_partials_to_scale_kernel(const unsigned int* __restrict__ partials, int nparts, int64_t cols, int fmt, float qmax,
+                             float* __restrict__ scales) {
+  // 32 packed column pairs x 32 slices of the partial rows per CTA: enough loads in flight to hide their latency
+  __shared__ uint32_t red[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t wi = (int64_t)blockIdx.x * 32 + tx, half = cols >> 1;
+  uint32_t m = 0;
+  if (wi < half)
+    for (int p = ty; p < nparts; p += 32) m = absmax_bf16x2(m, partials[(int64_t)p * half + wi]);
+  red[ty][tx] = m;
+  __syncthreads();
+  if (ty == 0 && wi < half) {
+#pragma unroll
+    for (int j = 1; j < 32; ++j) m = absmax_bf16x2(m, red[j][tx]);
+    scales[2 * wi] = scale_from_amax(bf16lo(m), fmt, qmax);
+    scales[2 * wi + 1] = scale_from_amax(bf16hi(m), fmt, qmax);
   }
 }
 
@@ -643,6 +690,51 @@ int b200q_quantize_fp8(const void* x, int64_t rows, int64_t cols, int64_t ld, in
   amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, fmt, 0.f);
   B200Q_CUDA(cudaGetLastError());
   launch_transpose<MODE_FP8>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, nullptr, 0, scales, nullptr, nullptr, st);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+// Rows of partial column maxima the COLMAX pass writes (one per CTA of a grid that is capped at this)
+constexpr int kColmaxParts = kNumSMs * 8;
+
+int64_t b200q_quantize_fp8_both_workspace_bytes(int64_t cols) { return cols > 0 ? (int64_t)kColmaxParts * cols * 2 : 0; }
+
+int b200q_quantize_fp8_both(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt, void* codes_row, float* scales_row,
+                            void* codes_col, float* scales_col, void* workspace, void* stream) {
+  int rc = check_matrix(x, rows, cols, ld);
+  if (rc) return rc;
+  if (codes_row == nullptr || scales_row == nullptr || codes_col == nullptr || scales_col == nullptr || workspace == nullptr ||
+      (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes_row) || !aligned16(codes_col)) return B200Q_ERR_ALIGNMENT;
+  if ((rows & 15) || cols > 8192) return B200Q_ERR_SHAPE;       // the column maxima of a CTA live in 32 KB of shared memory
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const uint16_t* xp = (const uint16_t*)x;
+  unsigned int* parts = (unsigned int*)workspace;
+  // pass 1: row-wise codes and scales + partial column maxima
+  const int64_t nv = cols / 8;
+  int wpr = 1;
+  while (wpr < kWarps && nv > (int64_t)wpr * 32 * 4) wpr *= 2;
+  const int64_t nvec = (nv + wpr * 32 - 1) / (wpr * 32);
+  const int64_t rpc = kWarps / wpr, want = (rows + rpc - 1) / rpc;
+  const int grid = (int)(want < kColmaxParts ? want : kColmaxParts);
+  const size_t smem = (size_t)rpc * cols * 2;          // packed bf16 column maxima of every row group
+#define B200Q_GO(NV, F)                                                                                                      \
+  rowwise_fp8_kernel<NV, F, true><<<grid, kThreads, smem, st>>>(xp, rows, cols, ld, (uint8_t*)codes_row, scales_row, nullptr, nullptr, \
+                                                                wpr, 0.f, parts)
+#define B200Q_PICK(NV) do { if (fmt == FMT_E4M3) B200Q_GO(NV, FMT_E4M3); else B200Q_GO(NV, FMT_E5M2); } while (0)
+  if (nvec <= 1) B200Q_PICK(1);
+  else if (nvec <= 2) B200Q_PICK(2);
+  else if (nvec <= 4) B200Q_PICK(4);
+  else B200Q_PICK(8);                                            // cols <= 8192: at most 4 vectors per lane with 8 warps per row
+#undef B200Q_PICK
+#undef B200Q_GO
+  B200Q_CUDA(cudaGetLastError());
+  // pass 2: column scales, then the transposed codes
+  col_partials_to_scale_kernel<<<(unsigned)((cols / 2 + 31) / 32), 1024, 0, st>>>(parts, grid, cols, fmt, 0.f, scales_col);
+  B200Q_CUDA(cudaGetLastError());
+  launch_transpose<MODE_FP8>(xp, rows, cols, ld, fmt, (uint8_t*)codes_col, nullptr, 0, scales_col, nullptr, nullptr, st);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

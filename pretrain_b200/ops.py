@@ -60,6 +60,23 @@ def quantize_fp8(x: torch.Tensor, fmt, axis: int):
     return codes, scales
 
 
+def quantize_fp8_both(x: torch.Tensor, fmt):
+    """Per-row and per-column FP8 of x (rows, cols) in two reads: returns (codes_row (rows, cols),
+    scales_row (rows), codes_col (cols, rows), scales_col (cols)), equal to quantize_fp8(x, fmt, 1) +
+    quantize_fp8(x, fmt, 0).  rows % 16 == 0, cols <= 8192."""
+    x = _mat(x)
+    rows, cols = x.shape
+    lib = _lib.load()
+    cr = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
+    sr = torch.empty(rows, dtype=torch.float32, device=x.device)
+    cc = torch.empty(cols, rows, dtype=torch.uint8, device=x.device)
+    sc = torch.empty(cols, dtype=torch.float32, device=x.device)
+    ws = torch.empty(lib.b200q_quantize_fp8_both_workspace_bytes(cols), dtype=torch.uint8, device=x.device)
+    _lib.check(lib.b200q_quantize_fp8_both(x.data_ptr(), rows, cols, x.stride(0), fmt_of(fmt), cr.data_ptr(), sr.data_ptr(),
+                                           cc.data_ptr(), sc.data_ptr(), ws.data_ptr(), _stream()), "b200q_quantize_fp8_both")
+    return cr, sr, cc, sc
+
+
 def quantize_fp8_tensorwise(x: torch.Tensor, fmt, transpose: bool = False, tensor_amax: torch.Tensor | None = None):
     x = _mat(x)
     rows, cols = x.shape

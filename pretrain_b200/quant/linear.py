@@ -82,6 +82,34 @@ def _mx_training_formats(cfg: QuantConfig):
     return str_to_dtype_fp8(d["act"]), str_to_dtype_fp8(d["weight"]), str_to_dtype_fp8(d["input_grad"])
 
 
+def _fp8_training_formats(cfg: QuantConfig):
+    """(act, weight, grad) fp8 dtypes when the three GEMMs are row-wise-scaled FP8 and both uses of the
+    output gradient share a format (the ``fp8`` recipe with ``granularity: rowwise``); None otherwise."""
+    d = cfg.dtype
+    if cfg.scaling["granularity"] != "rowwise" or not all(is_fp8(d[k]) for k in ("act", "weight", "input_grad", "weight_grad")):
+        return None
+    if d["input_grad"] != d["weight_grad"]:
+        return None
+    fa, fw, fg = (str_to_dtype_fp8(d[k]) for k in ("act", "weight", "input_grad"))
+    e5 = torch.float8_e5m2
+    if (fa == e5 and fw == e5) or (fg == e5 and fw == e5) or (fg == e5 and fa == e5):
+        return None                       # fp8_gemm wants at least one e4m3 operand in every GEMM
+    return fa, fw, fg
+
+
+def _both_fp8_weight(weight: torch.Tensor, w: torch.Tensor, fmt: torch.dtype):
+    """Per-row and per-column FP8 copies of the weight, kept on the parameter until it is written again."""
+    if torch.compiler.is_compiling() or not isinstance(weight, nn.Parameter):
+        return T.quantize_fp8_both(w, fmt_of(fmt))
+    key = (weight._version, weight.data_ptr(), w.dtype, fmt)
+    cached = getattr(weight, "_b200q_fp8", None)
+    if cached is None or cached[0] != key:
+        with torch.no_grad():
+            cached = (key, T.quantize_fp8_both(w.detach(), fmt_of(fmt)))
+        weight._b200q_fp8 = cached
+    return cached[1]
+
+
 def _dual_mx_weight(weight: torch.Tensor, w: torch.Tensor, fmt: torch.dtype):
     """Both MXFP8 copies of the weight (along in_features for fprop, along out_features for
     dgrad).  Outside torch.compile they are kept on the parameter until it is next written, so a
@@ -122,11 +150,29 @@ class QuantizedLinearFn(torch.autograd.Function):
         mx = _mx_training_formats(cfg)
         ctx.mx = (mx is not None and compute_dtype == torch.bfloat16 and any(ctx.needs_input_grad[:2]) and recording is not False
                   and x2d.shape[0] % 32 == 0 and x2d.shape[1] % 32 == 0 and w.shape[0] % 32 == 0)
+        ctx.f8 = False
         if ctx.mx:
             fa, fw, _ = mx
             xr, xsr, xc, xsc = T.quantize_mxfp8_dual(x2d, fmt_of(fa), SF_SWIZZLED)
             wr, wsr, wc, wsc = _dual_mx_weight(weight, w, fw)
             y = T.gemm_mxfp8(xr, xsr, wr, wsr, fmt_of(fa), fmt_of(fw))
+            if bias is not None:
+                y = y + bias.to(compute_dtype)
+            ctx.save_for_backward(xc, xsc, wc, wsc)
+            ctx.cfg, ctx.has_bias = cfg, bias is not None
+            ctx.x_shape, ctx.x_dtype, ctx.w_dtype = x.shape, x.dtype, weight.dtype
+            return y.reshape(*x.shape[:-1], weight.shape[0])
+        f8 = _fp8_training_formats(cfg)
+        ctx.f8 = (f8 is not None and compute_dtype == torch.bfloat16 and any(ctx.needs_input_grad[:2]) and recording is not False
+                  and x2d.shape[0] % 16 == 0 and w.shape[0] % 16 == 0 and x2d.shape[1] % 16 == 0
+                  and max(x2d.shape[1], w.shape[0]) <= 8192)
+        if ctx.f8:
+            # the same idea for row-wise FP8: each tensor quantized per row and per column in two reads
+            # (not three), codes and scales saved for backward, the weight's copies kept on the parameter
+            fa, fw, _ = f8
+            xr, xsr, xc, xsc = T.quantize_fp8_both(x2d, fmt_of(fa))            # (M, K) | (K, M)
+            wr, wsr, wc, wsc = _both_fp8_weight(weight, w, fw)                 # (N, K) | (K, N)
+            y = T.gemm_fp8(xr, fmt_of(fa), wr, fmt_of(fw), xsr, wsr)
             if bias is not None:
                 y = y + bias.to(compute_dtype)
             ctx.save_for_backward(xc, xsc, wc, wsc)
@@ -150,6 +196,16 @@ class QuantizedLinearFn(torch.autograd.Function):
             gr, gsr, gc, gsc = T.quantize_mxfp8_dual(g, fg, SF_SWIZZLED)
             dx = T.gemm_mxfp8(gr, gsr, wc, wsc, fg, fw) if ctx.needs_input_grad[0] else None    # (M, N) . (K, N)^T
             dw = T.gemm_mxfp8(gc, gsc, xc, xsc, fg, fa) if ctx.needs_input_grad[1] else None    # (N, M) . (K, M)^T
+            db = g.sum(dim=0).to(ctx.w_dtype) if ctx.has_bias else None
+            return (dx.reshape(*ctx.x_shape).to(ctx.x_dtype) if dx is not None else None,
+                    dw.to(ctx.w_dtype) if dw is not None else None, db, None, None)[:ctx.n_inputs]
+        if ctx.f8:
+            xc, xsc, wc, wsc = ctx.saved_tensors          # x^T codes (K, M) + per-column scales, w^T codes (K, N)
+            fa, fw, fg = (fmt_of(t) for t in _fp8_training_formats(ctx.cfg))
+            g = grad_out.reshape(-1, grad_out.shape[-1]).to(torch.bfloat16)             # (M, N)
+            gr, gsr, gc, gsc = T.quantize_fp8_both(g, fg)                                # (M, N) | (N, M)
+            dx = T.gemm_fp8(gr, fg, wc, fw, gsr, wsc) if ctx.needs_input_grad[0] else None      # (M, N) . (K, N)^T
+            dw = T.gemm_fp8(gc, fg, xc, fa, gsc, xsc) if ctx.needs_input_grad[1] else None      # (N, M) . (K, M)^T
             db = g.sum(dim=0).to(ctx.w_dtype) if ctx.has_bias else None
             return (dx.reshape(*ctx.x_shape).to(ctx.x_dtype) if dx is not None else None,
                     dw.to(ctx.w_dtype) if dw is not None else None, db, None, None)[:ctx.n_inputs]

@@ -47,6 +47,18 @@ def _(x, fmt, axis):
     return x.new_empty(outer, c, dtype=torch.uint8), x.new_empty(outer, dtype=torch.float32)
 
 
+@_lib_def("b200q::quantize_fp8_both", mutates_args=())
+def quantize_fp8_both(x: torch.Tensor, fmt: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    return ops.quantize_fp8_both(x, fmt)
+
+
+@quantize_fp8_both.register_fake
+def _(x, fmt):
+    rows, cols = x.shape
+    return (x.new_empty(rows, cols, dtype=torch.uint8), x.new_empty(rows, dtype=torch.float32),
+            x.new_empty(cols, rows, dtype=torch.uint8), x.new_empty(cols, dtype=torch.float32))
+
+
 @_lib_def("b200q::quantize_fp8_tensorwise", mutates_args=())
 def quantize_fp8_tensorwise(x: torch.Tensor, fmt: int, transpose: bool) -> Tuple[torch.Tensor, torch.Tensor]:
     return ops.quantize_fp8_tensorwise(x, fmt, transpose)

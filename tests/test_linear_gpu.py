@@ -169,6 +169,27 @@ def test_mxfp8_training_path_quantizes_once_and_equals_the_per_gemm_path():
     assert hasattr(q.weight, "_b200q_mx") and q.weight.grad is not None
 
 
+def test_fp8_rowwise_training_path_equals_the_per_gemm_path():
+    """Row-wise FP8 layers quantize x, w and g per row and per column in two reads each and save codes;
+    y, dx and dw must equal the three separate `_gemm` calls bit for bit."""
+    from pretrain_b200.quant.linear import QuantizedLinearFn, _gemm
+    torch.manual_seed(2)
+    cfg = _cfg("fp8", "rowwise")
+    m, k, n = 256, 160, 96
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = nn.Parameter((0.05 * torch.randn(n, k, device="cuda")).bfloat16())
+    g = (1e-2 * torch.randn(m, n, device="cuda")).bfloat16()
+    y = QuantizedLinearFn.apply(x, w, None, cfg)
+    y.backward(g)
+    assert hasattr(w, "_b200q_fp8")
+    d = cfg.dtype
+    with torch.no_grad():
+        y_ref = _gemm(x, w.t(), d["act"], d["weight"], torch.bfloat16, rowwise=True)
+        dx_ref = _gemm(g, w, d["input_grad"], d["weight"], torch.bfloat16, rowwise=True)
+        dw_ref = _gemm(g.t(), x, d["weight_grad"], d["act"], torch.bfloat16, rowwise=True)
+    assert torch.equal(y, y_ref) and torch.equal(x.grad, dx_ref) and torch.equal(w.grad, dw_ref)
+
+
 def test_hp_weight_grad_differs_from_quantized():
     from pretrain_b200.quant.linear import QuantLinear
     torch.manual_seed(0)

@@ -223,6 +223,19 @@ def test_mxfp8_both_directions_in_one_pass(ops, shape, dt, layout):
     assert torch.equal((G_unswizzle(sc, shape[1], shape[0] // 32) if layout else sc.view(shape[1], -1)).cpu(), osf)
 
 
+@pytest.mark.parametrize("shape", [(512, 768), (96, 160), (16, 8), (160, 96), (64, 4352), (2048, 8192)])
+@pytest.mark.parametrize("dt", [E4, E5])
+def test_fp8_rows_and_columns_in_two_reads(ops, shape, dt):
+    g = torch.Generator().manual_seed(shape[0] * 7 + shape[1])
+    x = (torch.randn(*shape, generator=g) * torch.exp2(torch.randint(-8, 8, shape, generator=g).float())).bfloat16().cuda()
+    cr, sr, cc, sc = ops.quantize_fp8_both(x, dt)
+    r1, s1 = ops.quantize_fp8(x, dt, 1)
+    r0, s0 = ops.quantize_fp8(x, dt, 0)
+    assert torch.equal(cr, r1) and torch.equal(sr, s1) and torch.equal(cc, r0) and torch.equal(sc, s0)
+    oc, osc = R.quantize_fp8(x.cpu(), dt, dim=0)
+    assert torch.equal(cc.cpu(), oc.view(torch.uint8).t()) and torch.equal(sc.cpu(), osc.reshape(-1))
+
+
 def test_rows_that_are_only_16_byte_aligned(ops):
     """Pitch and start that rule out the 256-bit loads: the 128-bit path must give the same bytes."""
     x = CASES["x"]
