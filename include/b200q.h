@@ -296,6 +296,30 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
                                     const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
                                     int64_t K, void* H, int64_t ldh, void* sfH, void* stream);
 
+/* Four element-wise steps of the trainable expert path, each fused with b200q_quantize_mxfp8_dual so that
+ * the bf16 tensor between the step and its two MXFP8 copies is never written: the outputs are what
+ * b200q_quantize_mxfp8_dual gives on the step's result (codes_row [rows, cols] + sf_row, codes_col
+ * [cols, rows] + sf_col, 128x4-tiled scale factors), bit for bit.
+ *   gather:              rows of x picked by src_of_row (b200q_moe_gather with quantize = 0; -1 = zero row)
+ *   unpermute backward:  row r = w[p] * dout[p / k] for p = pair_of_row[r] (-1 = zero row), the dy of
+ *                        b200q_moe_unpermute_backward (pair_of_row is the inverse of the plan's row_of)
+ *   swiglu:              silu(gate) * up of g = [gate | up]  (b200q_swiglu with quantize = 0)
+ *   swiglu backward:     [d_gate | d_up] of b200q_swiglu_backward
+ * Row counts are multiples of 128; D % 128 == 0; I % 128 == 0 (swiglu) / I % 64 == 0 (swiglu backward). */
+int b200q_moe_gather_quantize_dual(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row,
+                                   int64_t padded_rows, int fmt, void* codes_row, void* sf_row,
+                                   void* codes_col, void* sf_col, void* stream);
+int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, const void* w,
+                                               const int32_t* pair_of_row, int k, int64_t padded_rows,
+                                               int64_t D, int fmt, void* codes_row, void* sf_row,
+                                               void* codes_col, void* sf_col, void* stream);
+int b200q_swiglu_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, int fmt,
+                               void* codes_row, void* sf_row, void* codes_col, void* sf_col,
+                               void* stream);
+int b200q_swiglu_backward_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg,
+                                        const void* dh, int64_t lddh, int fmt, void* codes_row,
+                                        void* sf_row, void* codes_col, void* sf_col, void* stream);
+
 /* Expert parallelism inside one NVLink domain without a collective on the data path: ranks own
  * contiguous ranges of experts_per_rank experts and expose their buffers to each other (peer-mapped
  * device memory; the reference is single-GPU and has no counterpart).
@@ -332,7 +356,7 @@ int b200q_swiglu_backward(const void* g, int64_t rows, int64_t I, int64_t ldg, c
  * output gradient dout (bf16 [T, D]) it writes dy (bf16 [padded_rows, D]) with
  * dy[row_of[t*k+j]] = w[t,j] * dout[t] and zero rows wherever src_of_row < 0, and, when y (the
  * forward's expert outputs, bf16 [padded_rows, D], pitch ldy) and dw are given, the router-weight
- * gradient dw[t*k+j] = <dout[t], y[row_of[t*k+j]]> in fp32. */
+ * gradient dw[t*k+j] = <dout[t], y[row_of[t*k+j]]> in fp32.  dy may be NULL when only dw is wanted. */
 int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y, int64_t ldy,
                                  const int32_t* row_of, const int32_t* src_of_row, int64_t T, int k,
                                  int64_t D, int64_t padded_rows, void* dy, float* dw, void* stream);

@@ -129,6 +129,32 @@ __device__ __forceinline__ uint4 swiglu8(const uint4& vg, const uint4& vu) {
   return make_uint4(h[0], h[1], h[2], h[3]);
 }
 
+// Backward of swiglu8 for 8 (gate, up, dh) triples: d_gate = dh * up * silu'(gate), d_up = dh * silu(gate),
+// silu'(x) = s (1 + x (1 - s)), s = 1 / (1 + e^-x); fp32 arithmetic, one rounding to bf16.
+__device__ __forceinline__ void swiglu_bwd8(const uint4& vg, const uint4& vu, const uint4& vd, uint4& dgate, uint4& dup) {
+  float a[8], b[8], d[8];
+  unpack8(vg, a);
+  unpack8(vu, b);
+  unpack8(vd, d);
+  uint32_t og[4], ou[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float pg[2], pu[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float x = a[2 * i + j];
+      const float sg = __fdividef(1.f, 1.f + __expf(-x));
+      pu[j] = d[2 * i + j] * x * sg;
+      pg[j] = d[2 * i + j] * b[2 * i + j] * sg * (1.f + x * (1.f - sg));
+    }
+    __nv_bfloat162 qg = __floats2bfloat162_rn(pg[0], pg[1]), qu = __floats2bfloat162_rn(pu[0], pu[1]);
+    og[i] = *reinterpret_cast<uint32_t*>(&qg);
+    ou[i] = *reinterpret_cast<uint32_t*>(&qu);
+  }
+  dgate = make_uint4(og[0], og[1], og[2], og[3]);
+  dup = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+}
+
 // Byte offset of the scale factor of (row, block kb) in the 128x4-tiled layout; kt = K-tiles per row tile.
 __device__ __forceinline__ int64_t sf_swizzled(int64_t row, int kb, int64_t kt) {
   return ((row >> 7) * kt + (kb >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3);

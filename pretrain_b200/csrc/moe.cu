@@ -1,9 +1,12 @@
-// MoE data movement around the ragged grouped GEMM: permute plan (stable counting sort of the
-// routed (token, slot) pairs by expert, in the reference's order, src/layers/mlp.py:446-457),
-// gather into the padded expert-sorted layout (optionally fused with MXFP8 quantization), SwiGLU
-// between the two GEMMs (src/layers/activation.py:80-81), and the weighted unpermute
-// (src/layers/mlp.py:472-477).  Index work is integer and bit-exact; the row movers are
-// HBM-bound: 16-byte coalesced accesses, one warp per row.
+// MoE data movement around the ragged grouped GEMM: router back end (score function, top-k,
+// src/layers/mlp.py:292-301), permute plan (stable counting sort of the routed (token, slot) pairs
+// by expert, in the reference's order, src/layers/mlp.py:446-457), gather into the padded
+// expert-sorted layout (optionally fused with MXFP8 quantization), SwiGLU between the two GEMMs
+// (src/layers/activation.py:80-81) and its backward, the weighted unpermute
+// (src/layers/mlp.py:472-477) and its backward, and the expert-parallel dispatch / combine over
+// peer-mapped memory.  Index work is integer and bit-exact; the row movers are HBM-bound: a thread
+// owns a run of 32 elements (64 bytes in, two sectors) or a warp owns a row chunk, 16-byte or
+// 32-byte accesses.
 #include "common.cuh"
 
 namespace b200q {
@@ -525,27 +528,10 @@ swiglu_backward_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, 
   for (ItemWalker w((int64_t)blockIdx.x * 256 + threadIdx.x, (int64_t)gridDim.x * 256, runs); w.row < rows; w.next()) {
     const int64_t r = w.row;
     const int c = w.chunk << 3;
-    float a[8], b[8], d[8];
-    unpack8(ld_nc_v4(g + r * ldg + c), a);
-    unpack8(ld_nc_v4(g + r * ldg + I + c), b);
-    unpack8(ld_nc_v4(dh + r * lddh + c), d);
-    uint32_t og[4], ou[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float dgate[2], dup[2];
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const float x = a[2 * i + j];
-        const float sg = __fdividef(1.f, 1.f + __expf(-x));
-        dup[j] = d[2 * i + j] * x * sg;
-        dgate[j] = d[2 * i + j] * b[2 * i + j] * sg * (1.f + x * (1.f - sg));
-      }
-      __nv_bfloat162 pg = __floats2bfloat162_rn(dgate[0], dgate[1]), pu = __floats2bfloat162_rn(dup[0], dup[1]);
-      og[i] = *reinterpret_cast<uint32_t*>(&pg);
-      ou[i] = *reinterpret_cast<uint32_t*>(&pu);
-    }
-    *reinterpret_cast<uint4*>(dg + r * lddg + c) = make_uint4(og[0], og[1], og[2], og[3]);
-    *reinterpret_cast<uint4*>(dg + r * lddg + I + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+    uint4 og4, ou4;
+    swiglu_bwd8(ld_nc_v4(g + r * ldg + c), ld_nc_v4(g + r * ldg + I + c), ld_nc_v4(dh + r * lddh + c), og4, ou4);
+    *reinterpret_cast<uint4*>(dg + r * lddg + c) = og4;
+    *reinterpret_cast<uint4*>(dg + r * lddg + I + c) = ou4;
   }
 }
 
@@ -581,7 +567,7 @@ moe_unpermute_backward_kernel(const uint16_t* __restrict__ dout, const uint16_t*
           __nv_bfloat162 pk = __floats2bfloat162_rn(wj * f[2 * i], wj * f[2 * i + 1]);
           o[i] = *reinterpret_cast<uint32_t*>(&pk);
         }
-        *reinterpret_cast<uint4*>(dy + (int64_t)row * D + c) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (dy != nullptr) *reinterpret_cast<uint4*>(dy + (int64_t)row * D + c) = make_uint4(o[0], o[1], o[2], o[3]);
       }
       if (dw != nullptr) {
 #pragma unroll
@@ -590,7 +576,7 @@ moe_unpermute_backward_kernel(const uint16_t* __restrict__ dout, const uint16_t*
       }
     } else {
       const int64_t r = it - n_pairs;
-      if (src_of_row[r] < 0)
+      if (dy != nullptr && src_of_row[r] < 0)
         for (int64_t c = lane * 8; c < D; c += 256) *reinterpret_cast<uint4*>(dy + r * D + c) = make_uint4(0, 0, 0, 0);
     }
   }
@@ -814,16 +800,16 @@ int b200q_swiglu_backward(const void* g, int64_t rows, int64_t I, int64_t ldg, c
 int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y, int64_t ldy, const int32_t* row_of,
                                  const int32_t* src_of_row, int64_t T, int k, int64_t D, int64_t padded_rows, void* dy, float* dw,
                                  void* stream) {
-  if (dout == nullptr || w == nullptr || row_of == nullptr || src_of_row == nullptr || dy == nullptr || T <= 0 || k <= 0 ||
-      D <= 0 || padded_rows <= 0 || (y != nullptr && ldy < D) || (dw != nullptr && y == nullptr))
+  if (dout == nullptr || w == nullptr || row_of == nullptr || src_of_row == nullptr || (dy == nullptr && dw == nullptr) || T <= 0 ||
+      k <= 0 || D <= 0 || padded_rows <= 0 || (y != nullptr && ldy < D) || (dw != nullptr && y == nullptr))
     return B200Q_ERR_INVALID_ARG;
   if ((D & 7) || (y != nullptr && (ldy & 7))) return B200Q_ERR_SHAPE;
-  if (!aligned16(dout) || !aligned16(dy) || (y != nullptr && !aligned16(y))) return B200Q_ERR_ALIGNMENT;
+  if (!aligned16(dout) || (dy != nullptr && !aligned16(dy)) || (y != nullptr && !aligned16(y))) return B200Q_ERR_ALIGNMENT;
   int rc = require_sm100();
   if (rc) return rc;
-  moe_unpermute_backward_kernel<<<row_grid(T * k + padded_rows), 256, 0, (cudaStream_t)stream>>>(
-      (const uint16_t*)dout, (const uint16_t*)w, (const uint16_t*)y, ldy, row_of, src_of_row, T * k, k, D, padded_rows, (uint16_t*)dy,
-      dw);
+  moe_unpermute_backward_kernel<<<row_grid(T * k + (dy != nullptr ? padded_rows : 0)), 256, 0, (cudaStream_t)stream>>>(
+      (const uint16_t*)dout, (const uint16_t*)w, (const uint16_t*)y, ldy, row_of, src_of_row, T * k, k, D,
+      dy != nullptr ? padded_rows : 0, (uint16_t*)dy, dw);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -1,12 +1,14 @@
-// Quantize kernels: amax, FP8 (per-row / per-column / per-tensor fp32 scales), MXFP8
-// (32-element blocks, E8M0 scales) and NVFP4 (16-element blocks, E4M3 scales + fp32 tensor
-// scale), each in a row-wise form (contraction dimension contiguous in the input) and a
-// transposing form (contraction dimension = input rows; output written transposed).
+// Quantize kernels: amax, FP8 and the int8 series (per-row / per-column / per-tensor fp32
+// scales), MXFP8 (32-element blocks, E8M0 scales) and NVFP4 (16-element blocks, E4M3 scales +
+// fp32 tensor scale), each in a row-wise form (contraction dimension contiguous in the input)
+// and a transposing form (contraction dimension = input rows; output written transposed), plus
+// the forms that produce both directions of one tensor (MXFP8 in one read, FP8 in two).
 //
-// All of them are HBM-bound streaming kernels: 16-byte coalesced loads with several loads in
-// flight per thread, warp-shuffle reductions for the block / row maxima, hardware fp8 / fp4
-// conversion instructions, 8- or 16-byte coalesced stores.  Arithmetic is the bit-exact core
-// in numeric.cuh (reference formula: src/quant/fp8.py:16-32).
+// All of them are HBM-bound streaming kernels: 16- or 32-byte loads with several in flight per
+// thread, block maxima inside one thread (block-scaled formats) or warp-shuffle reductions
+// (row maxima), hardware fp8 / fp4 conversion instructions, 8- to 32-byte stores.  Arithmetic is
+// the bit-exact core in numeric.cuh (reference formulas: src/quant/fp8.py:16-32,
+// src/quant/int8.py:9-19).
 #include "common.cuh"
 
 namespace b200q {
@@ -442,9 +444,88 @@ constexpr int kDPitch = kDT * 2 + 16;       // bytes per staged input row
 constexpr int kDOutPitch = kDT + 16;        // bytes per staged output row (= input column)
 constexpr int kDualSmem = kDT * kDPitch;     // the output staging tile reuses the input tile's memory
 
-template <int FMT, bool WIDE>
+// Where the tile kernel gets its values from: a matrix in memory, or one of the element-wise steps of
+// the MoE expert path computed on the fly, so that the bf16 tensor between that step and its two
+// MXFP8 copies never exists.
+enum { SRC_PLAIN = 0, SRC_GATHER = 1, SRC_SCALED_GATHER = 2, SRC_SWIGLU = 3, SRC_SWIGLU_BWD = 4 };
+struct TileSrc {
+  const uint16_t* x;       // PLAIN / GATHER: the matrix; SCALED_GATHER: dout [T, cols]; SWIGLU(_BWD): g = [gate | up] [rows, 2I]
+  int64_t ld;
+  const int32_t* index;    // GATHER: source row of every output row (-1: zero row); SCALED_GATHER: routed pair of every row (-1: zero row)
+  const uint16_t* w;       // SCALED_GATHER: routing weight of every pair (bf16)
+  int k;                   //                slots per token (token = pair / k)
+  const uint16_t* dh;      // SWIGLU_BWD: gradient of h [rows, I]
+  int64_t lddh;
+  int64_t I;               // SWIGLU: cols == I; SWIGLU_BWD: cols == 2 I (gate half, then up half)
+};
+
+template <int SRC, bool WIDE>
+__device__ __forceinline__ void load_run(const TileSrc& s, int64_t gr, int64_t gc, uint4 (&v)[4]) {
+  if (SRC == SRC_PLAIN) {
+    const uint16_t* xp = s.x + gr * s.ld + gc;
+    ld_nc_32B<WIDE>(xp, v[0], v[1]);
+    ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
+  } else if (SRC == SRC_GATHER) {
+    const int src = s.index[gr];
+    if (src >= 0) {
+      const uint16_t* xp = s.x + (int64_t)src * s.ld + gc;
+      ld_nc_32B<WIDE>(xp, v[0], v[1]);
+      ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
+    }
+  } else if (SRC == SRC_SCALED_GATHER) {
+    const int pair = s.index[gr];
+    if (pair >= 0) {
+      const float wj = u2f((uint32_t)s.w[pair] << 16);
+      const uint16_t* xp = s.x + (int64_t)(pair / s.k) * s.ld + gc;
+      uint4 t[4];
+      ld_nc_32B<WIDE>(xp, t[0], t[1]);
+      ld_nc_32B<WIDE>(xp + 16, t[2], t[3]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        unpack8(t[u], f);
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 pk = __floats2bfloat162_rn(wj * f[2 * i], wj * f[2 * i + 1]);
+          o[i] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+        v[u] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  } else if (SRC == SRC_SWIGLU) {
+    const uint16_t* gp = s.x + gr * s.ld + gc;
+    uint4 vg[4], vu[4];
+    ld_nc_32B<WIDE>(gp, vg[0], vg[1]);
+    ld_nc_32B<WIDE>(gp + 16, vg[2], vg[3]);
+    ld_nc_32B<WIDE>(gp + s.I, vu[0], vu[1]);
+    ld_nc_32B<WIDE>(gp + s.I + 16, vu[2], vu[3]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = swiglu8(vg[u], vu[u]);
+  } else {
+    const bool up_half = gc >= s.I;                    // I % 32 == 0: a run lies in one half
+    const int64_t cc = up_half ? gc - s.I : gc;
+    const uint16_t* gp = s.x + gr * s.ld + cc;
+    const uint16_t* dp = s.dh + gr * s.lddh + cc;
+    uint4 vg[4], vu[4], vd[4];
+    ld_nc_32B<WIDE>(gp, vg[0], vg[1]);
+    ld_nc_32B<WIDE>(gp + 16, vg[2], vg[3]);
+    ld_nc_32B<WIDE>(gp + s.I, vu[0], vu[1]);
+    ld_nc_32B<WIDE>(gp + s.I + 16, vu[2], vu[3]);
+    ld_nc_32B<WIDE>(dp, vd[0], vd[1]);
+    ld_nc_32B<WIDE>(dp + 16, vd[2], vd[3]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint4 dgate, dup;
+      swiglu_bwd8(vg[u], vu[u], vd[u], dgate, dup);
+      v[u] = up_half ? dup : dgate;
+    }
+  }
+}
+
+template <int FMT, bool WIDE, int SRC = SRC_PLAIN>
 __global__ void __launch_bounds__(kThreads)
-mx_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, uint8_t* __restrict__ codes_r,
+mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __restrict__ codes_r,
                      uint8_t* __restrict__ sf_r, uint8_t* __restrict__ codes_c, uint8_t* __restrict__ sf_c, int swz) {
   extern __shared__ __align__(16) uint8_t dual_smem[];
   uint8_t* tin = dual_smem;
@@ -459,11 +540,7 @@ mx_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
     const int64_t gr = r0 + r, gc = c0 + q * 32;
     const bool live = gr < rows && gc < cols;                             // cols % 32 == 0: a run is whole or absent
     uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-    if (live) {
-      const uint16_t* xp = x + gr * ld + gc;
-      ld_nc_32B<WIDE>(xp, v[0], v[1]);
-      ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
-    }
+    if (live) load_run<SRC, WIDE>(src, gr, gc, v);
     uint4* dst = reinterpret_cast<uint4*>(tin + r * kDPitch + q * 64);
     dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; dst[3] = v[3];
     if (live) {
@@ -514,15 +591,16 @@ mx_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
   }
 }
 
-int launch_mx_tile_quant(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes_r, uint8_t* sf_r,
+template <int SRC>
+int launch_mx_tile_quant(const TileSrc& src, bool aligned_src, int64_t rows, int64_t cols, int fmt, uint8_t* codes_r, uint8_t* sf_r,
                          uint8_t* codes_c, uint8_t* sf_c, int swz, cudaStream_t st) {
-  const bool wide = aligned32(x) && (ld & 15) == 0 && aligned32(codes_r);
+  const bool wide = aligned_src && aligned32(codes_r);
   dim3 grid((unsigned)((cols + kDT - 1) / kDT), (unsigned)((rows + kDT - 1) / kDT));
 #define B200Q_GO(F, W)                                                                                                  \
   do {                                                                                                                  \
-    auto kernel = mx_tile_quant_kernel<F, W>;                                                                           \
+    auto kernel = mx_tile_quant_kernel<F, W, SRC>;                                                                      \
     B200Q_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDualSmem));                   \
-    kernel<<<grid, kThreads, kDualSmem, st>>>(x, rows, cols, ld, codes_r, sf_r, codes_c, sf_c, swz);                    \
+    kernel<<<grid, kThreads, kDualSmem, st>>>(src, rows, cols, codes_r, sf_r, codes_c, sf_c, swz);                      \
   } while (0)
   if (fmt == FMT_E4M3) { if (wide) B200Q_GO(FMT_E4M3, true); else B200Q_GO(FMT_E4M3, false); }
   else { if (wide) B200Q_GO(FMT_E5M2, true); else B200Q_GO(FMT_E5M2, false); }
@@ -530,6 +608,8 @@ int launch_mx_tile_quant(const uint16_t* x, int64_t rows, int64_t cols, int64_t 
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
+
+inline bool rows_32B_aligned(const void* p, int64_t ld) { return aligned32(p) && (ld & 15) == 0; }
 
 int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
   if (x == nullptr || rows <= 0 || cols <= 0 || ld < cols) return B200Q_ERR_INVALID_ARG;
@@ -837,8 +917,79 @@ int b200q_quantize_mxfp8_dual(const void* x, int64_t rows, int64_t cols, int64_t
   cudaStream_t st = (cudaStream_t)stream;
   if ((rc = zero_sf_pads(sf_row, rows, cols / 32, sf_layout, st))) return rc;
   if ((rc = zero_sf_pads(sf_col, cols, rows / 32, sf_layout, st))) return rc;
-  return launch_mx_tile_quant((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row, (uint8_t*)codes_col,
-                                    (uint8_t*)sf_col, sf_layout, st);
+  TileSrc src = {};
+  src.x = (const uint16_t*)x; src.ld = ld;
+  return launch_mx_tile_quant<SRC_PLAIN>(src, rows_32B_aligned(x, ld), rows, cols, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row,
+                                         (uint8_t*)codes_col, (uint8_t*)sf_col, sf_layout, st);
+}
+
+// ---- the element-wise steps of the MoE expert path, fused with the both-directions quantizer ----
+static int check_dual_out(void* codes_row, void* sf_row, void* codes_col, void* sf_col, int fmt) {
+  if (codes_row == nullptr || sf_row == nullptr || codes_col == nullptr || sf_col == nullptr || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes_row) || !aligned16(codes_col)) return B200Q_ERR_ALIGNMENT;
+  return B200Q_OK;
+}
+
+int b200q_moe_gather_quantize_dual(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row, int64_t padded_rows, int fmt,
+                                   void* codes_row, void* sf_row, void* codes_col, void* sf_col, void* stream) {
+  int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
+  if (rc) return rc;
+  if (x == nullptr || src_of_row == nullptr || D <= 0 || ld < D || padded_rows <= 0) return B200Q_ERR_INVALID_ARG;
+  if ((D & 127) || (ld & 7) || (padded_rows & 127)) return B200Q_ERR_SHAPE;
+  if (!aligned16(x)) return B200Q_ERR_ALIGNMENT;
+  if ((rc = require_sm100())) return rc;
+  TileSrc src = {};
+  src.x = (const uint16_t*)x; src.ld = ld; src.index = src_of_row;
+  return launch_mx_tile_quant<SRC_GATHER>(src, rows_32B_aligned(x, ld), padded_rows, D, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row,
+                                          (uint8_t*)codes_col, (uint8_t*)sf_col, B200Q_SF_SWIZZLE_128x4, (cudaStream_t)stream);
+}
+
+int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, const void* w, const int32_t* pair_of_row, int k,
+                                               int64_t padded_rows, int64_t D, int fmt, void* codes_row, void* sf_row,
+                                               void* codes_col, void* sf_col, void* stream) {
+  int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
+  if (rc) return rc;
+  if (dout == nullptr || w == nullptr || pair_of_row == nullptr || k <= 0 || D <= 0 || ld < D || padded_rows <= 0)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 127) || (ld & 7) || (padded_rows & 127)) return B200Q_ERR_SHAPE;
+  if (!aligned16(dout)) return B200Q_ERR_ALIGNMENT;
+  if ((rc = require_sm100())) return rc;
+  TileSrc src = {};
+  src.x = (const uint16_t*)dout; src.ld = ld; src.index = pair_of_row; src.w = (const uint16_t*)w; src.k = k;
+  return launch_mx_tile_quant<SRC_SCALED_GATHER>(src, rows_32B_aligned(dout, ld), padded_rows, D, fmt, (uint8_t*)codes_row,
+                                                 (uint8_t*)sf_row, (uint8_t*)codes_col, (uint8_t*)sf_col, B200Q_SF_SWIZZLE_128x4,
+                                                 (cudaStream_t)stream);
+}
+
+int b200q_swiglu_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, int fmt, void* codes_row, void* sf_row,
+                               void* codes_col, void* sf_col, void* stream) {
+  int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
+  if (rc) return rc;
+  if (g == nullptr || rows <= 0 || I <= 0 || ldg < 2 * I) return B200Q_ERR_INVALID_ARG;
+  if ((I & 127) || (ldg & 7) || (rows & 127)) return B200Q_ERR_SHAPE;
+  if (!aligned16(g)) return B200Q_ERR_ALIGNMENT;
+  if ((rc = require_sm100())) return rc;
+  TileSrc src = {};
+  src.x = (const uint16_t*)g; src.ld = ldg; src.I = I;
+  return launch_mx_tile_quant<SRC_SWIGLU>(src, rows_32B_aligned(g, ldg) && (I & 15) == 0, rows, I, fmt, (uint8_t*)codes_row,
+                                          (uint8_t*)sf_row, (uint8_t*)codes_col, (uint8_t*)sf_col, B200Q_SF_SWIZZLE_128x4,
+                                          (cudaStream_t)stream);
+}
+
+int b200q_swiglu_backward_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, const void* dh, int64_t lddh, int fmt,
+                                        void* codes_row, void* sf_row, void* codes_col, void* sf_col, void* stream) {
+  int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
+  if (rc) return rc;
+  if (g == nullptr || dh == nullptr || rows <= 0 || I <= 0 || ldg < 2 * I || lddh < I) return B200Q_ERR_INVALID_ARG;
+  if ((I & 63) || (ldg & 7) || (lddh & 7) || (rows & 127)) return B200Q_ERR_SHAPE;       // 2 I % 128 == 0: whole scale tiles
+  if (!aligned16(g) || !aligned16(dh)) return B200Q_ERR_ALIGNMENT;
+  if ((rc = require_sm100())) return rc;
+  TileSrc src = {};
+  src.x = (const uint16_t*)g; src.ld = ldg; src.I = I; src.dh = (const uint16_t*)dh; src.lddh = lddh;
+  return launch_mx_tile_quant<SRC_SWIGLU_BWD>(src, rows_32B_aligned(g, ldg) && rows_32B_aligned(dh, lddh) && (I & 15) == 0, rows, 2 * I,
+                                              fmt, (uint8_t*)codes_row, (uint8_t*)sf_row, (uint8_t*)codes_col, (uint8_t*)sf_col,
+                                              B200Q_SF_SWIZZLE_128x4, (cudaStream_t)stream);
 }
 
 int b200q_quantize_mxfp8_rowmap(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt, const int32_t* dst_row,

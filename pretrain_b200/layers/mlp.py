@@ -63,13 +63,15 @@ class _ExpertFFN(torch.autograd.Function):
         t, d = x.shape
         e, n1, _ = w_in.shape
         inter = n1 // 2
-        a = ops.moe_gather(x, plan, False)                                             # (R, D) bf16, pad rows zero
-        ar, asr, ac, asc = ops.quantize_mxfp8_dual(a, E4M3)
+        # every element-wise step hands its result to the both-directions quantizer inside one kernel
+        ar, asr, ac, asc = ops.moe_gather_quantize_dual(x, plan, E4M3)                         # (R, D) | (D, R), pad rows zero
         w1r, w1sr, w1c, w1sc = ops.quantize_mxfp8_dual(w_in.reshape(e * n1, d), E4M3)       # (E*2I, D) | (D, E*2I)
         w2r, w2sr, w2c, w2sc = ops.quantize_mxfp8_dual(w_down.reshape(e * d, inter), E4M3)  # (E*D, I)  | (I, E*D)
-        g = ops.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, n1)                       # (R, 2I) bf16
-        h = ops.swiglu(g, False)
-        hr, hsr, hc, hsc = ops.quantize_mxfp8_dual(h, E4M3)
+        g = ops.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, n1)                       # (R, 2I) bf16, kept for backward
+        if inter % 128 == 0:
+            hr, hsr, hc, hsc = ops.swiglu_quantize_dual(g, E4M3)
+        else:
+            hr, hsr, hc, hsc = ops.quantize_mxfp8_dual(ops.swiglu(g, False), E4M3)
         y = ops.grouped_gemm_mxfp8(hr, hsr, w2r, w2sr, plan, d)                        # (R, D) bf16
         out = ops.moe_unpermute(y, top_w, plan.row_of, t)
         ctx.save_for_backward(top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, y)
@@ -82,12 +84,12 @@ class _ExpertFFN(torch.autograd.Function):
         top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, y = ctx.saved_tensors
         plan = ctx.plan
         t, d, e, inter, k = ctx.shapes
-        dy, dw = ops.moe_unpermute_backward(dout.reshape(t, d).to(torch.bfloat16), top_w, y, plan)
-        dyr, dysr, dyc, dysc = ops.quantize_mxfp8_dual(dy, E5M2)
+        dout = dout.reshape(t, d).to(torch.bfloat16)
+        dw = ops.moe_unpermute_backward(dout, top_w, y, plan, want_dy=False)                   # (T, k) fp32
+        dyr, dysr, dyc, dysc = ops.moe_unpermute_backward_quantize_dual(dout, top_w, ops.moe_pair_of_row(plan), E5M2)
         dh = ops.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, plan, inter, E5M2, E4M3)       # (R, I)
         dw2 = ops.grouped_gemm_mxfp8_wgrad(dyc, dysc, hc, hsc, plan, E5M2, E4M3)               # (E, D, I)
-        dg = ops.swiglu_backward(g, dh)                                                        # (R, 2I)
-        dgr, dgsr, dgc, dgsc = ops.quantize_mxfp8_dual(dg, E5M2)
+        dgr, dgsr, dgc, dgsc = ops.swiglu_backward_quantize_dual(g, dh, E5M2)                  # of dg (R, 2I)
         da = ops.grouped_gemm_mxfp8_dgrad(dgr, dgsr, w1c, w1sc, plan, d, E5M2, E4M3)           # (R, D)
         dw1 = ops.grouped_gemm_mxfp8_wgrad(dgc, dgsc, ac, asc, plan, E5M2, E4M3)               # (E, 2I, D)
         dx = ops.moe_unpermute(da, torch.ones(t, k, dtype=torch.bfloat16, device=da.device), plan.row_of, t)

@@ -446,6 +446,65 @@ def swiglu(g: torch.Tensor, quantize: bool, fmt=E4M3):
     return (out, sf) if quantize else out
 
 
+def _dual_outputs(rows: int, cols: int, device):
+    return (torch.empty(rows, cols, dtype=torch.uint8, device=device), torch.empty(sf_bytes(rows, cols // 32), dtype=torch.uint8, device=device),
+            torch.empty(cols, rows, dtype=torch.uint8, device=device), torch.empty(sf_bytes(cols, rows // 32), dtype=torch.uint8, device=device))
+
+
+def moe_gather_quantize_dual(x: torch.Tensor, plan: MoEPlan, fmt=E4M3):
+    """quantize_mxfp8_dual(moe_gather(x, plan, False)) without the bf16 copy of the gathered rows (all
+    padded_rows rows are defined: rows without a source are zero)."""
+    x = _mat(x)
+    d = x.shape[1]
+    cr, sr, cc, sc = _dual_outputs(plan.padded_rows, d, x.device)
+    _lib.check(_lib.load().b200q_moe_gather_quantize_dual(x.data_ptr(), d, x.stride(0), plan.src_of_row.data_ptr(), plan.padded_rows,
+                                                          fmt_of(fmt), cr.data_ptr(), sr.data_ptr(), cc.data_ptr(), sc.data_ptr(),
+                                                          _stream()), "b200q_moe_gather_quantize_dual")
+    return cr, sr, cc, sc
+
+
+def moe_pair_of_row(plan: MoEPlan) -> torch.Tensor:
+    """Inverse of plan.row_of: the routed pair that owns every padded row, -1 for rows nobody owns."""
+    inv = torch.full((plan.padded_rows,), -1, dtype=torch.int32, device=plan.row_of.device)
+    inv[plan.row_of.long()] = torch.arange(plan.row_of.numel(), dtype=torch.int32, device=plan.row_of.device)
+    return inv
+
+
+def moe_unpermute_backward_quantize_dual(dout: torch.Tensor, weights: torch.Tensor, pair_of_row: torch.Tensor, fmt=E5M2):
+    """quantize_mxfp8_dual of dy[row] = weights[pair] * dout[pair // k] without writing dy."""
+    dout = _mat(dout)
+    d = dout.shape[1]
+    w = weights.to(torch.bfloat16).contiguous()
+    rows = pair_of_row.numel()
+    cr, sr, cc, sc = _dual_outputs(rows, d, dout.device)
+    _lib.check(_lib.load().b200q_moe_unpermute_backward_quantize_dual(dout.data_ptr(), dout.stride(0), w.data_ptr(), pair_of_row.data_ptr(),
+                                                                      w.shape[1], rows, d, fmt_of(fmt), cr.data_ptr(), sr.data_ptr(),
+                                                                      cc.data_ptr(), sc.data_ptr(), _stream()),
+               "b200q_moe_unpermute_backward_quantize_dual")
+    return cr, sr, cc, sc
+
+
+def swiglu_quantize_dual(g: torch.Tensor, fmt=E4M3):
+    """quantize_mxfp8_dual(swiglu(g, False)) without the bf16 h."""
+    g = _mat(g)
+    rows, i2 = g.shape
+    cr, sr, cc, sc = _dual_outputs(rows, i2 // 2, g.device)
+    _lib.check(_lib.load().b200q_swiglu_quantize_dual(g.data_ptr(), rows, i2 // 2, g.stride(0), fmt_of(fmt), cr.data_ptr(), sr.data_ptr(),
+                                                      cc.data_ptr(), sc.data_ptr(), _stream()), "b200q_swiglu_quantize_dual")
+    return cr, sr, cc, sc
+
+
+def swiglu_backward_quantize_dual(g: torch.Tensor, dh: torch.Tensor, fmt=E5M2):
+    """quantize_mxfp8_dual(swiglu_backward(g, dh)) without the bf16 dg."""
+    g, dh = _mat(g), _mat(dh)
+    rows, i2 = g.shape
+    cr, sr, cc, sc = _dual_outputs(rows, i2, g.device)
+    _lib.check(_lib.load().b200q_swiglu_backward_quantize_dual(g.data_ptr(), rows, i2 // 2, g.stride(0), dh.data_ptr(), dh.stride(0),
+                                                               fmt_of(fmt), cr.data_ptr(), sr.data_ptr(), cc.data_ptr(), sc.data_ptr(),
+                                                               _stream()), "b200q_swiglu_backward_quantize_dual")
+    return cr, sr, cc, sc
+
+
 def moe_dispatch_peers(x: torch.Tensor, plan: MoEPlan, row_base: torch.Tensor, experts_per_rank: int, peer_codes, peer_sf):
     """Quantize this rank's routed rows (plan over ALL experts) to MXFP8 and store them into their owners'
     buffers; peer_codes / peer_sf are the device pointers of every rank's buffers (own and peer-mapped)."""
@@ -481,15 +540,20 @@ def swiglu_backward(g: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
     return dg
 
 
-def moe_unpermute_backward(dout: torch.Tensor, weights: torch.Tensor, y: torch.Tensor | None, plan: MoEPlan):
+def moe_unpermute_backward(dout: torch.Tensor, weights: torch.Tensor, y: torch.Tensor | None, plan: MoEPlan, want_dy: bool = True):
     """(dy bf16 (padded_rows, D), dw fp32 (T, k) | None): gradients of moe_unpermute w.r.t. the expert
-    outputs and, when y is given, the routing weights."""
+    outputs and, when y is given, the routing weights.  want_dy=False returns dw alone."""
     dout = _mat(dout)
     t, d = dout.shape
     w = weights.to(torch.bfloat16).contiguous()
     k = w.shape[1]
-    dy = torch.empty(plan.padded_rows, d, dtype=torch.bfloat16, device=dout.device)
     dw = torch.empty(t, k, dtype=torch.float32, device=dout.device) if y is not None else None
+    if not want_dy:
+        _lib.check(_lib.load().b200q_moe_unpermute_backward(dout.data_ptr(), w.data_ptr(), y.data_ptr(), y.stride(0), plan.row_of.data_ptr(),
+                                                            plan.src_of_row.data_ptr(), t, k, d, plan.padded_rows, None, dw.data_ptr(),
+                                                            _stream()), "b200q_moe_unpermute_backward")
+        return dw
+    dy = torch.empty(plan.padded_rows, d, dtype=torch.bfloat16, device=dout.device)
     _lib.check(_lib.load().b200q_moe_unpermute_backward(dout.data_ptr(), w.data_ptr(), y.data_ptr() if y is not None else None,
                                                         y.stride(0) if y is not None else 0, plan.row_of.data_ptr(),
                                                         plan.src_of_row.data_ptr(), t, k, d, plan.padded_rows, dy.data_ptr(),

@@ -342,6 +342,35 @@ def test_swiglu_backward_and_unpermute_backward(ops):
     assert (dy[plan.src_of_row < 0] == 0).all()
 
 
+def test_elementwise_steps_fused_with_the_dual_quantizer(ops):
+    """gather / swiglu / unpermute-backward / swiglu-backward feeding the both-directions MXFP8 quantizer inside
+    one kernel == the step's own kernel followed by quantize_mxfp8_dual, byte for byte."""
+    g = torch.Generator().manual_seed(11)
+    t, k, d, e, inter = 640, 2, 256, 8, 128
+    x = torch.randn(t, d, generator=g).bfloat16().cuda()
+    logits = torch.randn(t, e, generator=g)
+    logits[:, 2] = -1e9
+    top_i, top_w = R.router_topk(logits, k)
+    plan = ops.moe_permute_plan(top_i.cuda(), e)
+    live = int(plan.num_tiles.item()) * 128
+    eq = lambda a, b: all(torch.equal(u, v) for u, v in zip(a, b))
+    # gather (rows past the live tiles are zero rows in the fused form; the plain gather leaves them unwritten)
+    a = ops.moe_gather(x, plan, False)
+    a[live:] = 0
+    assert eq(ops.moe_gather_quantize_dual(x, plan), ops.quantize_mxfp8_dual(a))
+    # swiglu
+    gu = (1.5 * torch.randn(plan.padded_rows, 2 * inter, generator=g)).bfloat16().cuda()
+    assert eq(ops.swiglu_quantize_dual(gu), ops.quantize_mxfp8_dual(ops.swiglu(gu, False)))
+    # unpermute backward
+    dout = torch.randn(t, d, generator=g).bfloat16().cuda()
+    dy, _ = ops.moe_unpermute_backward(dout, top_w.cuda(), torch.zeros(plan.padded_rows, d, dtype=torch.bfloat16, device="cuda"), plan)
+    E5 = torch.float8_e5m2
+    assert eq(ops.moe_unpermute_backward_quantize_dual(dout, top_w.cuda(), ops.moe_pair_of_row(plan), E5), ops.quantize_mxfp8_dual(dy, E5))
+    # swiglu backward
+    dh = torch.randn(plan.padded_rows, inter, generator=g).bfloat16().cuda()
+    assert eq(ops.swiglu_backward_quantize_dual(gu, dh, E5), ops.quantize_mxfp8_dual(ops.swiglu_backward(gu, dh), E5))
+
+
 def _moe_block_reference(x, gate_w, w_gu, w_d, k):
     """SparseMoEBlock.forward of the reference (src/layers/mlp.py:432-494, softmax router, SwiGLU experts,
     no aux loss) written as a per-expert loop in fp32."""
