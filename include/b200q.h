@@ -302,7 +302,10 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
  * [cols, rows] + sf_col, 128x4-tiled scale factors), bit for bit.
  *   gather:              rows of x picked by src_of_row (b200q_moe_gather with quantize = 0; -1 = zero row)
  *   unpermute backward:  row r = w[p] * dout[p / k] for p = pair_of_row[r] (-1 = zero row), the dy of
- *                        b200q_moe_unpermute_backward (pair_of_row is the inverse of the plan's row_of)
+ *                        b200q_moe_unpermute_backward (pair_of_row is the inverse of the plan's row_of).
+ *                        With dw != NULL the same pass also gives that function's dw: dw[p] =
+ *                        <dout[p / k], y[row_of[p]]> (fp32, 0 for a dropped pair), summed per 128-column
+ *                        tile into dot_workspace ((D / 128) * padded_rows floats) and then per pair.
  *   swiglu:              silu(gate) * up of g = [gate | up]  (b200q_swiglu with quantize = 0)
  *   swiglu backward:     [d_gate | d_up] of b200q_swiglu_backward
  * Row counts are multiples of 128; D % 128 == 0; I % 128 == 0 (swiglu) / I % 64 == 0 (swiglu backward). */
@@ -312,7 +315,9 @@ int b200q_moe_gather_quantize_dual(const void* x, int64_t D, int64_t ld, const i
 int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, const void* w,
                                                const int32_t* pair_of_row, int k, int64_t padded_rows,
                                                int64_t D, int fmt, void* codes_row, void* sf_row,
-                                               void* codes_col, void* sf_col, void* stream);
+                                               void* codes_col, void* sf_col, const void* y, int64_t ldy,
+                                               const int32_t* row_of, int64_t n_pairs,
+                                               float* dot_workspace, float* dw, void* stream);
 int b200q_swiglu_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, int fmt,
                                void* codes_row, void* sf_row, void* codes_col, void* sf_col,
                                void* stream);

@@ -53,7 +53,8 @@ SIGNATURES = {
     "b200q_quantize_nvfp4_rowmap": (_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp]),
     "b200q_quantize_mxfp8_rowmap": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp]),
     "b200q_moe_gather_quantize_dual": (_int, [_vp, _i64, _i64, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
-    "b200q_moe_unpermute_backward_quantize_dual": (_int, [_vp, _i64, _vp, _vp, _int, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_moe_unpermute_backward_quantize_dual": (_int, [_vp, _i64, _vp, _vp, _int, _i64, _i64, _int, _vp, _vp, _vp, _vp,
+                                                         _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
     "b200q_swiglu_quantize_dual": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
     "b200q_swiglu_backward_quantize_dual": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_dispatch_peers": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _int, _int, _vp, _vp, _vp]),

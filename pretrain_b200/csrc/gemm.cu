@@ -487,9 +487,9 @@ int g_force_bn = 0;   // test hook: 0 = choose by shape
 // epilogue hides behind the next main loop only when two accumulators fit in tensor memory
 // (every width but 256).
 template <int KIND>
-int choose_bn(int64_t M, int64_t N, int64_t row_bytes) {
+int choose_bn(int64_t M, int64_t N, int64_t row_bytes, int64_t groups = 1) {
   const int cands[3] = {256, 192, 128};
-  const int64_t num_k = (row_bytes + BKB - 1) / BKB, num_m = (M + BM - 1) / BM;
+  const int64_t num_k = (row_bytes + BKB - 1) / BKB, num_m = groups * ((M + BM - 1) / BM);
   double best = 1e30;
   int best_bn = 256;
   for (int bn : cands) {
@@ -713,7 +713,9 @@ int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const
 // one-CTA kernel, tile width by the cost model (the grouped backward forms have no pair variant)
 static int dispatch_one_cta_mx(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, const GemmParams& p,
                                cudaStream_t st) {
-  const int bn = g_force_bn ? g_force_bn : choose_bn<KIND_MX>(p.M, p.N, p.K);
+  // ragged form: every expert has its own output tiles and (on average) its share of the K range
+  const int64_t groups = p.ragged_offs ? p.n_experts : 1;
+  const int bn = g_force_bn ? g_force_bn : choose_bn<KIND_MX>(p.M, p.N, p.K / groups, groups);
   switch (bn) {
     case 128: return launch<KIND_MX, 128>(A, B, one_output(D), ldd, b_rows, p, st);
     case 192: return launch<KIND_MX, 192>(A, B, one_output(D), ldd, b_rows, p, st);

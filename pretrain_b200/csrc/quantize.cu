@@ -457,10 +457,13 @@ struct TileSrc {
   const uint16_t* dh;      // SWIGLU_BWD: gradient of h [rows, I]
   int64_t lddh;
   int64_t I;               // SWIGLU: cols == I; SWIGLU_BWD: cols == 2 I (gate half, then up half)
+  const uint16_t* y;       // SCALED_GATHER, optional: expert outputs [rows, cols]; <dout[token], y[row]> per row and
+  int64_t ldy;             //                column tile goes to dot_partial[column tile][row] (the routing weights' gradient)
+  float* dot_partial;
 };
 
 template <int SRC, bool WIDE>
-__device__ __forceinline__ void load_run(const TileSrc& s, int64_t gr, int64_t gc, uint4 (&v)[4]) {
+__device__ __forceinline__ void load_run(const TileSrc& s, int64_t gr, int64_t gc, uint4 (&v)[4], float& dot) {
   if (SRC == SRC_PLAIN) {
     const uint16_t* xp = s.x + gr * s.ld + gc;
     ld_nc_32B<WIDE>(xp, v[0], v[1]);
@@ -477,13 +480,21 @@ __device__ __forceinline__ void load_run(const TileSrc& s, int64_t gr, int64_t g
     if (pair >= 0) {
       const float wj = u2f((uint32_t)s.w[pair] << 16);
       const uint16_t* xp = s.x + (int64_t)(pair / s.k) * s.ld + gc;
-      uint4 t[4];
+      uint4 t[4], ty[4] = {};
       ld_nc_32B<WIDE>(xp, t[0], t[1]);
       ld_nc_32B<WIDE>(xp + 16, t[2], t[3]);
+      if (s.y != nullptr) {
+        const uint16_t* yp = s.y + gr * s.ldy + gc;
+        ld_nc_32B<WIDE>(yp, ty[0], ty[1]);
+        ld_nc_32B<WIDE>(yp + 16, ty[2], ty[3]);
+      }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        float f[8];
+        float f[8], fy[8];
         unpack8(t[u], f);
+        unpack8(ty[u], fy);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(f[i], fy[i], dot);
         uint32_t o[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -502,34 +513,38 @@ __device__ __forceinline__ void load_run(const TileSrc& s, int64_t gr, int64_t g
     ld_nc_32B<WIDE>(gp + s.I + 16, vu[2], vu[3]);
 #pragma unroll
     for (int u = 0; u < 4; ++u) v[u] = swiglu8(vg[u], vu[u]);
-  } else {
-    const bool up_half = gc >= s.I;                    // I % 32 == 0: a run lies in one half
-    const int64_t cc = up_half ? gc - s.I : gc;
-    const uint16_t* gp = s.x + gr * s.ld + cc;
-    const uint16_t* dp = s.dh + gr * s.lddh + cc;
-    uint4 vg[4], vu[4], vd[4];
-    ld_nc_32B<WIDE>(gp, vg[0], vg[1]);
-    ld_nc_32B<WIDE>(gp + 16, vg[2], vg[3]);
-    ld_nc_32B<WIDE>(gp + s.I, vu[0], vu[1]);
-    ld_nc_32B<WIDE>(gp + s.I + 16, vu[2], vu[3]);
-    ld_nc_32B<WIDE>(dp, vd[0], vd[1]);
-    ld_nc_32B<WIDE>(dp + 16, vd[2], vd[3]);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      uint4 dgate, dup;
-      swiglu_bwd8(vg[u], vu[u], vd[u], dgate, dup);
-      v[u] = up_half ? dup : dgate;
-    }
   }
 }
+
+// SWIGLU_BWD: one evaluation of the backward gives the run of the gate half (columns lc .. lc+31)
+// and the run of the up half (columns I + lc ..) together.
+template <bool WIDE>
+__device__ __forceinline__ void load_run_swiglu_bwd(const TileSrc& s, int64_t gr, int64_t lc, uint4 (&dgate)[4], uint4 (&dup)[4]) {
+  const uint16_t* gp = s.x + gr * s.ld + lc;
+  const uint16_t* dp = s.dh + gr * s.lddh + lc;
+  uint4 vg[4], vu[4], vd[4];
+  ld_nc_32B<WIDE>(gp, vg[0], vg[1]);
+  ld_nc_32B<WIDE>(gp + 16, vg[2], vg[3]);
+  ld_nc_32B<WIDE>(gp + s.I, vu[0], vu[1]);
+  ld_nc_32B<WIDE>(gp + s.I + 16, vu[2], vu[3]);
+  ld_nc_32B<WIDE>(dp, vd[0], vd[1]);
+  ld_nc_32B<WIDE>(dp + 16, vd[2], vd[3]);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) swiglu_bwd8(vg[u], vu[u], vd[u], dgate[u], dup[u]);
+}
+
+// SWIGLU_BWD tiles come in pairs: the CTA at column tile c takes columns [c, c + 128) of the gate half
+// and of the up half (two staged tiles), so the backward is evaluated once per element.
+template <int SRC> __host__ __device__ constexpr int tile_parts() { return SRC == SRC_SWIGLU_BWD ? 2 : 1; }
 
 template <int FMT, bool WIDE, int SRC = SRC_PLAIN>
 __global__ void __launch_bounds__(kThreads)
 mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __restrict__ codes_r,
                      uint8_t* __restrict__ sf_r, uint8_t* __restrict__ codes_c, uint8_t* __restrict__ sf_c, int swz) {
   extern __shared__ __align__(16) uint8_t dual_smem[];
-  uint8_t* tin = dual_smem;
-  uint8_t* tout = dual_smem;                  // written only after every thread has read its columns (barrier below)
+  constexpr int NT = tile_parts<SRC>();
+  // part t covers columns [t * width + c0, ...) below (t + 1) * width of the output matrix
+  const int64_t width = NT == 2 ? src.I : cols;
   const int tid = threadIdx.x;
   const int64_t c0 = (int64_t)blockIdx.x * kDT, r0 = (int64_t)blockIdx.y * kDT;
   const int64_t nblk_r = cols >> 5, kt_r = (nblk_r + 3) >> 2;
@@ -537,22 +552,44 @@ mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __r
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int item = i * kThreads + tid, r = item >> 2, q = item & 3;     // 4 runs of 32 per tile row
-    const int64_t gr = r0 + r, gc = c0 + q * 32;
-    const bool live = gr < rows && gc < cols;                             // cols % 32 == 0: a run is whole or absent
-    uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-    if (live) load_run<SRC, WIDE>(src, gr, gc, v);
-    uint4* dst = reinterpret_cast<uint4*>(tin + r * kDPitch + q * 64);
-    dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; dst[3] = v[3];
+    const int64_t gr = r0 + r, lc = c0 + q * 32;
+    const bool live = gr < rows && lc < width;                            // width % 32 == 0: a run is whole or absent
+    uint4 v[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[t][u] = make_uint4(0, 0, 0, 0);
+    float dot = 0.f;
     if (live) {
-      uint32_t o[8];
-      const int e = mx_quant_block32<FMT>(v, o);
-      st_32B<WIDE>(codes_r + gr * cols + gc, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
-      sf_r[swz ? sf_swizzled(gr, (int)(gc >> 5), kt_r) : gr * nblk_r + (gc >> 5)] = (uint8_t)(e + 127);
+      if constexpr (NT == 2) load_run_swiglu_bwd<WIDE>(src, gr, lc, v[0], v[1]);
+      else load_run<SRC, WIDE>(src, gr, lc, v[0], dot);
+    }
+    if constexpr (SRC == SRC_SCALED_GATHER) {
+      if (src.dot_partial != nullptr) {                 // the four lanes q = 0..3 of a row are neighbours
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        if (q == 0 && gr < rows) src.dot_partial[(int64_t)blockIdx.x * rows + gr] = dot;
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      uint4* dst = reinterpret_cast<uint4*>(dual_smem + t * kDualSmem + r * kDPitch + q * 64);
+      dst[0] = v[t][0]; dst[1] = v[t][1]; dst[2] = v[t][2]; dst[3] = v[t][3];
+      if (live) {
+        const int64_t gc = t * width + lc;
+        uint32_t o[8];
+        const int e = mx_quant_block32<FMT>(v[t], o);
+        st_32B<WIDE>(codes_r + gr * cols + gc, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+        sf_r[swz ? sf_swizzled(gr, (int)(gc >> 5), kt_r) : gr * nblk_r + (gc >> 5)] = (uint8_t)(e + 127);
+      }
     }
   }
   __syncthreads();
 
-  {
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    uint8_t* tin = dual_smem + t * kDualSmem;
+    uint8_t* tout = tin;                              // written only after every thread has read its columns (barrier below)
     const int cp = tid & 63, j = tid >> 6;            // column pair, block of 32 rows
     const uint32_t* col = reinterpret_cast<const uint32_t*>(tin + (32 * j) * kDPitch) + cp;
     uint32_t w[32];
@@ -574,33 +611,50 @@ mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __r
     uint4* d1 = reinterpret_cast<uint4*>(tout + (2 * cp + 1) * kDOutPitch + 32 * j);
     d0[0] = make_uint4(o0[0], o0[1], o0[2], o0[3]); d0[1] = make_uint4(o0[4], o0[5], o0[6], o0[7]);
     d1[0] = make_uint4(o1[0], o1[1], o1[2], o1[3]); d1[1] = make_uint4(o1[4], o1[5], o1[6], o1[7]);
-    const int64_t gc = c0 + 2 * cp, gr = r0 + 32 * j;
+    const int64_t lc = c0 + 2 * cp, gc = t * width + lc, gr = r0 + 32 * j;
     if (gr < rows) {
-      if (gc < cols) sf_c[sf_offset(gc, gr >> 5, rows >> 5, swz)] = (uint8_t)(e0 + 127);
-      if (gc + 1 < cols) sf_c[sf_offset(gc + 1, gr >> 5, rows >> 5, swz)] = (uint8_t)(e1 + 127);
+      if (lc < width) sf_c[sf_offset(gc, gr >> 5, rows >> 5, swz)] = (uint8_t)(e0 + 127);
+      if (lc + 1 < width) sf_c[sf_offset(gc + 1, gr >> 5, rows >> 5, swz)] = (uint8_t)(e1 + 127);
     }
   }
   __syncthreads();
 
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int id = i * kThreads + tid, oc = id >> 3, ch = id & 7;
-    if (c0 + oc < cols && r0 + ch * 16 < rows)
-      *reinterpret_cast<uint4*>(codes_c + (c0 + oc) * rows + r0 + ch * 16) =
-          *reinterpret_cast<const uint4*>(tout + oc * kDOutPitch + ch * 16);
+  for (int t = 0; t < NT; ++t) {
+    const uint8_t* tout = dual_smem + t * kDualSmem;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int id = i * kThreads + tid, oc = id >> 3, ch = id & 7;
+      if (c0 + oc < width && r0 + ch * 16 < rows)
+        *reinterpret_cast<uint4*>(codes_c + (t * width + c0 + oc) * rows + r0 + ch * 16) =
+            *reinterpret_cast<const uint4*>(tout + oc * kDOutPitch + ch * 16);
+    }
   }
+}
+
+// dw[pair] = sum over the column tiles of the partial dot products of the pair's row (0 for a dropped pair).
+__global__ void dot_partials_to_pairs_kernel(const float* __restrict__ partial, int parts, int64_t rows,
+                                             const int32_t* __restrict__ row_of, int64_t n_pairs, float* __restrict__ dw) {
+  const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n_pairs) return;
+  const int r = row_of[p];
+  float acc = 0.f;
+  if (r >= 0)
+    for (int c = 0; c < parts; ++c) acc += partial[(int64_t)c * rows + r];
+  dw[p] = acc;
 }
 
 template <int SRC>
 int launch_mx_tile_quant(const TileSrc& src, bool aligned_src, int64_t rows, int64_t cols, int fmt, uint8_t* codes_r, uint8_t* sf_r,
                          uint8_t* codes_c, uint8_t* sf_c, int swz, cudaStream_t st) {
   const bool wide = aligned_src && aligned32(codes_r);
-  dim3 grid((unsigned)((cols + kDT - 1) / kDT), (unsigned)((rows + kDT - 1) / kDT));
+  constexpr int NT = tile_parts<SRC>();
+  dim3 grid((unsigned)((cols / NT + kDT - 1) / kDT), (unsigned)((rows + kDT - 1) / kDT));
 #define B200Q_GO(F, W)                                                                                                  \
   do {                                                                                                                  \
     auto kernel = mx_tile_quant_kernel<F, W, SRC>;                                                                      \
-    B200Q_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDualSmem));                   \
-    kernel<<<grid, kThreads, kDualSmem, st>>>(src, rows, cols, codes_r, sf_r, codes_c, sf_c, swz);                      \
+    B200Q_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, NT * kDualSmem));              \
+    kernel<<<grid, kThreads, NT * kDualSmem, st>>>(src, rows, cols, codes_r, sf_r, codes_c, sf_c, swz);                 \
   } while (0)
   if (fmt == FMT_E4M3) { if (wide) B200Q_GO(FMT_E4M3, true); else B200Q_GO(FMT_E4M3, false); }
   else { if (wide) B200Q_GO(FMT_E5M2, true); else B200Q_GO(FMT_E5M2, false); }
@@ -947,19 +1001,36 @@ int b200q_moe_gather_quantize_dual(const void* x, int64_t D, int64_t ld, const i
 
 int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, const void* w, const int32_t* pair_of_row, int k,
                                                int64_t padded_rows, int64_t D, int fmt, void* codes_row, void* sf_row,
-                                               void* codes_col, void* sf_col, void* stream) {
+                                               void* codes_col, void* sf_col, const void* y, int64_t ldy,
+                                               const int32_t* row_of, int64_t n_pairs, float* dot_workspace, float* dw,
+                                               void* stream) {
   int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
   if (rc) return rc;
   if (dout == nullptr || w == nullptr || pair_of_row == nullptr || k <= 0 || D <= 0 || ld < D || padded_rows <= 0)
     return B200Q_ERR_INVALID_ARG;
   if ((D & 127) || (ld & 7) || (padded_rows & 127)) return B200Q_ERR_SHAPE;
   if (!aligned16(dout)) return B200Q_ERR_ALIGNMENT;
+  if (dw != nullptr) {
+    if (y == nullptr || row_of == nullptr || dot_workspace == nullptr || n_pairs <= 0 || ldy < D) return B200Q_ERR_INVALID_ARG;
+    if (ldy & 7) return B200Q_ERR_SHAPE;
+    if (!aligned16(y)) return B200Q_ERR_ALIGNMENT;
+  }
   if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
   TileSrc src = {};
   src.x = (const uint16_t*)dout; src.ld = ld; src.index = pair_of_row; src.w = (const uint16_t*)w; src.k = k;
-  return launch_mx_tile_quant<SRC_SCALED_GATHER>(src, rows_32B_aligned(dout, ld), padded_rows, D, fmt, (uint8_t*)codes_row,
-                                                 (uint8_t*)sf_row, (uint8_t*)codes_col, (uint8_t*)sf_col, B200Q_SF_SWIZZLE_128x4,
-                                                 (cudaStream_t)stream);
+  bool wide = rows_32B_aligned(dout, ld);
+  if (dw != nullptr) {
+    src.y = (const uint16_t*)y; src.ldy = ldy; src.dot_partial = dot_workspace;
+    wide = wide && rows_32B_aligned(y, ldy);
+  }
+  rc = launch_mx_tile_quant<SRC_SCALED_GATHER>(src, wide, padded_rows, D, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row,
+                                               (uint8_t*)codes_col, (uint8_t*)sf_col, B200Q_SF_SWIZZLE_128x4, st);
+  if (rc || dw == nullptr) return rc;
+  dot_partials_to_pairs_kernel<<<(unsigned)((n_pairs + kThreads - 1) / kThreads), kThreads, 0, st>>>(
+      dot_workspace, (int)(D / kDT), padded_rows, row_of, n_pairs, dw);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
 }
 
 int b200q_swiglu_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, int fmt, void* codes_row, void* sf_row,

@@ -85,8 +85,8 @@ class _ExpertFFN(torch.autograd.Function):
         plan = ctx.plan
         t, d, e, inter, k = ctx.shapes
         dout = dout.reshape(t, d).to(torch.bfloat16)
-        dw = ops.moe_unpermute_backward(dout, top_w, y, plan, want_dy=False)                   # (T, k) fp32
-        dyr, dysr, dyc, dysc = ops.moe_unpermute_backward_quantize_dual(dout, top_w, ops.moe_pair_of_row(plan), E5M2)
+        dyr, dysr, dyc, dysc, dw = ops.moe_unpermute_backward_quantize_dual(                   # dw (T, k) fp32
+            dout, top_w, ops.moe_pair_of_row(plan), E5M2, y=y, row_of=plan.row_of)
         dh = ops.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, plan, inter, E5M2, E4M3)       # (R, I)
         dw2 = ops.grouped_gemm_mxfp8_wgrad(dyc, dysc, hc, hsc, plan, E5M2, E4M3)               # (E, D, I)
         dgr, dgsr, dgc, dgsc = ops.swiglu_backward_quantize_dual(g, dh, E5M2)                  # of dg (R, 2I)

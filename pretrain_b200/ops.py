@@ -470,18 +470,29 @@ def moe_pair_of_row(plan: MoEPlan) -> torch.Tensor:
     return inv
 
 
-def moe_unpermute_backward_quantize_dual(dout: torch.Tensor, weights: torch.Tensor, pair_of_row: torch.Tensor, fmt=E5M2):
-    """quantize_mxfp8_dual of dy[row] = weights[pair] * dout[pair // k] without writing dy."""
+def moe_unpermute_backward_quantize_dual(dout: torch.Tensor, weights: torch.Tensor, pair_of_row: torch.Tensor, fmt=E5M2,
+                                         y: torch.Tensor | None = None, row_of: torch.Tensor | None = None):
+    """quantize_mxfp8_dual of dy[row] = weights[pair] * dout[pair // k] without writing dy.  With the
+    expert outputs `y` (padded rows) and the plan's `row_of`, the same pass also returns the routing
+    weights' gradient dw (T, k) fp32 = <dout[token], y[row of the pair]> as a fifth result."""
     dout = _mat(dout)
     d = dout.shape[1]
     w = weights.to(torch.bfloat16).contiguous()
     rows = pair_of_row.numel()
     cr, sr, cc, sc = _dual_outputs(rows, d, dout.device)
-    _lib.check(_lib.load().b200q_moe_unpermute_backward_quantize_dual(dout.data_ptr(), dout.stride(0), w.data_ptr(), pair_of_row.data_ptr(),
-                                                                      w.shape[1], rows, d, fmt_of(fmt), cr.data_ptr(), sr.data_ptr(),
-                                                                      cc.data_ptr(), sc.data_ptr(), _stream()),
-               "b200q_moe_unpermute_backward_quantize_dual")
-    return cr, sr, cc, sc
+    dw = ws = None
+    if y is not None:
+        y = _mat(y)
+        if row_of is None or y.shape != (rows, d):
+            raise ValueError("dw needs row_of and y of shape (padded_rows, D)")
+        dw = torch.empty(w.shape, dtype=torch.float32, device=dout.device)
+        ws = torch.empty(d // 128, rows, dtype=torch.float32, device=dout.device)
+    _lib.check(_lib.load().b200q_moe_unpermute_backward_quantize_dual(
+        dout.data_ptr(), dout.stride(0), w.data_ptr(), pair_of_row.data_ptr(), w.shape[1], rows, d, fmt_of(fmt), cr.data_ptr(),
+        sr.data_ptr(), cc.data_ptr(), sc.data_ptr(), y.data_ptr() if y is not None else None, y.stride(0) if y is not None else 0,
+        row_of.data_ptr() if y is not None else None, w.numel(), ws.data_ptr() if ws is not None else None,
+        dw.data_ptr() if dw is not None else None, _stream()), "b200q_moe_unpermute_backward_quantize_dual")
+    return (cr, sr, cc, sc) if dw is None else (cr, sr, cc, sc, dw)
 
 
 def swiglu_quantize_dual(g: torch.Tensor, fmt=E4M3):

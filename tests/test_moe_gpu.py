@@ -366,9 +366,19 @@ def test_elementwise_steps_fused_with_the_dual_quantizer(ops):
     dy, _ = ops.moe_unpermute_backward(dout, top_w.cuda(), torch.zeros(plan.padded_rows, d, dtype=torch.bfloat16, device="cuda"), plan)
     E5 = torch.float8_e5m2
     assert eq(ops.moe_unpermute_backward_quantize_dual(dout, top_w.cuda(), ops.moe_pair_of_row(plan), E5), ops.quantize_mxfp8_dual(dy, E5))
-    # swiglu backward
-    dh = torch.randn(plan.padded_rows, inter, generator=g).bfloat16().cuda()
-    assert eq(ops.swiglu_backward_quantize_dual(gu, dh, E5), ops.quantize_mxfp8_dual(ops.swiglu_backward(gu, dh), E5))
+    # ... and with the routing weights' gradient from the same pass
+    y = torch.randn(plan.padded_rows, d, generator=g).bfloat16().cuda()
+    _, dw = ops.moe_unpermute_backward(dout, top_w.cuda(), y, plan)
+    *codes, dw_fused = ops.moe_unpermute_backward_quantize_dual(dout, top_w.cuda(), ops.moe_pair_of_row(plan), E5, y=y, row_of=plan.row_of)
+    assert eq(codes, ops.quantize_mxfp8_dual(dy, E5))
+    ref_dw = (dout.float().unsqueeze(1) * y.float()[plan.row_of.long()].view(t, k, d)).sum(-1)
+    assert dw_fused.shape == (t, k) and dw_fused.dtype == torch.float32
+    assert _rel(dw_fused, ref_dw) < 1e-5 and _rel(dw_fused, dw) < 1e-5
+    # swiglu backward (expert widths of one tile, and of one and a half tiles)
+    for width in (inter, 192):
+        gu = (1.5 * torch.randn(plan.padded_rows, 2 * width, generator=g)).bfloat16().cuda()
+        dh = torch.randn(plan.padded_rows, width, generator=g).bfloat16().cuda()
+        assert eq(ops.swiglu_backward_quantize_dual(gu, dh, E5), ops.quantize_mxfp8_dual(ops.swiglu_backward(gu, dh), E5))
 
 
 def _moe_block_reference(x, gate_w, w_gu, w_d, k):
