@@ -377,9 +377,16 @@ int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int scor
                           void* stream);
 
 /* Weighted unpermute (src/layers/mlp.py:472-477): out[t, :] = sum_j w[t, j] * y[row_of[t*k+j], :],
- * accumulated in fp32 and rounded once to bf16.  y bf16 [padded_rows, D] pitch ldy; w bf16 [T, k]. */
+ * accumulated in fp32 and rounded once to bf16.  y bf16 [padded_rows, D] pitch ldy; w bf16 [T, k], or
+ * NULL for unit weights (the sum over the k slots: the backward of the gather). */
 int b200q_moe_unpermute(const void* y, int64_t ldy, const void* w, const int32_t* row_of, int64_t T,
                         int k, int64_t D, void* out, void* stream);
+
+/* Inverse of the plan's row_of (int32 [n_pairs], pair -> padded row, negative = dropped): pair_of_row
+ * [padded_rows] = the routed pair t*k+j that owns the row, -1 for pad rows (the reference keeps this as
+ * token_ids_sorted / weights_sorted, src/layers/mlp.py:446-458). */
+int b200q_moe_pair_of_row(const int32_t* row_of, int64_t n_pairs, int64_t padded_rows,
+                          int32_t* pair_of_row, void* stream);
 
 #ifdef __cplusplus
 }

@@ -67,18 +67,22 @@ __device__ __forceinline__ void st_32B(void* p, const uint4& a, const uint4& b) 
 }
 __host__ __device__ inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; }
 
-// |bf16x2| max of two packed words, as packed bf16x2 (exact: comparisons only).
-__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t v) {
-  __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&acc);
-  __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&v);
-  __nv_bfloat162 r = __hmax2(__habs2(a), __habs2(b));
-  return *reinterpret_cast<uint32_t*>(&r);
+// max(|a|, |b|) of two packed bf16 pairs in ONE instruction; the sign bits of the result are
+// unspecified (the xor of the operands' signs): chain freely, then clear them with abs_bf16x2.
+// Exact (comparisons only); a NaN operand loses against a number, as with fmaxf.
+__device__ __forceinline__ uint32_t absmax_raw_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
 }
+__device__ __forceinline__ uint32_t abs_bf16x2(uint32_t m) { return m & 0x7fff7fffu; }
+// |bf16x2| max of two packed words, as packed non-negative bf16x2.
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t v) { return abs_bf16x2(absmax_raw_bf16x2(acc, v)); }
+// max magnitude over the two halves of a packed word -> float
+__device__ __forceinline__ float absmax_halves(uint32_t m) { return fmaxf(fabsf(bf16lo(m)), fabsf(bf16hi(m))); }
 // max over the 8 bf16 of a uint4 -> float
 __device__ __forceinline__ float absmax8(uint4 v) {
-  uint32_t m = absmax_bf16x2(v.x, v.y);
-  m = absmax_bf16x2(m, absmax_bf16x2(v.z, v.w));
-  return fmaxf(bf16lo(m), bf16hi(m));
+  return absmax_halves(absmax_raw_bf16x2(absmax_raw_bf16x2(v.x, v.y), absmax_raw_bf16x2(v.z, v.w)));
 }
 
 // bf16 x 8 in a 16-byte word -> floats (exact)
@@ -87,24 +91,37 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
 }
 
+// Packed bf16 pair (2^-e_lo, 2^-e_hi) for block exponents in [-39, 126], and the packed product.  Scaling a
+// bf16 value by a power of two is exact in bf16 unless the result falls below 2^-126, far under the
+// smallest fp8 subnormal, where it rounds to a (signed) zero code either way - so the packed multiply
+// gives the codes of the fp32 multiply at half the instructions.
+__device__ __forceinline__ uint32_t mx_inv_scale_bf16x2(int e_lo, int e_hi) {
+  return ((uint32_t)(127 - e_lo) << 7) | ((uint32_t)(127 - e_hi) << 23);
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 // One MXFP8 block held by one thread: 32 bf16 in four 16-byte words -> 32 code bytes in o[0..7];
 // returns the block's unbiased scale exponent.
 template <int FMT>
 __device__ __forceinline__ int mx_quant_block32(const uint4 (&v)[4], uint32_t (&o)[8]) {
-  uint32_t m = absmax_bf16x2(absmax_bf16x2(v[0].x, v[0].y), absmax_bf16x2(v[0].z, v[0].w));
+  uint32_t m = absmax_raw_bf16x2(absmax_raw_bf16x2(v[0].x, v[0].y), absmax_raw_bf16x2(v[0].z, v[0].w));
 #pragma unroll
   for (int u = 1; u < 4; ++u) {
-    m = absmax_bf16x2(m, absmax_bf16x2(v[u].x, v[u].y));
-    m = absmax_bf16x2(m, absmax_bf16x2(v[u].z, v[u].w));
+    m = absmax_raw_bf16x2(m, absmax_raw_bf16x2(v[u].x, v[u].y));
+    m = absmax_raw_bf16x2(m, absmax_raw_bf16x2(v[u].z, v[u].w));
   }
-  const int e = mx_scale_exp(fmaxf(bf16lo(m), bf16hi(m)), FMT);
-  const float inv = mx_inv_scale(e);
+  const int e = mx_scale_exp(absmax_halves(m), FMT);
+  const uint32_t inv2 = mx_inv_scale_bf16x2(e, e);
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
-    float f[8];
-    unpack8(v[u], f);
-    o[2 * u] = cvt_fp8x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv, FMT);
-    o[2 * u + 1] = cvt_fp8x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv, FMT);
+    const uint32_t a = mul_bf16x2(v[u].x, inv2), b = mul_bf16x2(v[u].y, inv2), c = mul_bf16x2(v[u].z, inv2),
+                   d = mul_bf16x2(v[u].w, inv2);
+    o[2 * u] = cvt_fp8x4(bf16lo(a), bf16hi(a), bf16lo(b), bf16hi(b), FMT);
+    o[2 * u + 1] = cvt_fp8x4(bf16lo(c), bf16hi(c), bf16lo(d), bf16hi(d), FMT);
   }
   return e;
 }

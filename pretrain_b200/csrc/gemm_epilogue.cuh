@@ -153,8 +153,8 @@ __device__ __forceinline__ void epilogue_tile_glu(uint32_t taddr, bool rev, int 
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         dst[u] = h[u];
-        hmax = absmax_bf16x2(hmax, absmax_bf16x2(h[u].x, h[u].y));
-        hmax = absmax_bf16x2(hmax, absmax_bf16x2(h[u].z, h[u].w));
+        hmax = absmax_raw_bf16x2(hmax, absmax_raw_bf16x2(h[u].x, h[u].y));
+        hmax = absmax_raw_bf16x2(hmax, absmax_raw_bf16x2(h[u].z, h[u].w));
       }
     }
   };
@@ -177,7 +177,7 @@ __device__ __forceinline__ void epilogue_tile_glu(uint32_t taddr, bool rev, int 
     if (valid) emit(c, r);
   }
   if (OUT == GLU_BF16) {
-    float a = fmaxf(bf16lo(hmax), bf16hi(hmax));
+    float a = absmax_halves(hmax);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
     if ((threadIdx.x & 31) == 0 && a > 0.f) atomicMax(reinterpret_cast<unsigned int*>(out.amax), f2u(a));   // a >= 0: uint order == float order

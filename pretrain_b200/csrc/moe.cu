@@ -403,6 +403,15 @@ moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k
       if (hist[i]) atomicAdd(&counts[i], hist[i]);
 }
 
+// ---- inverse of row_of: the pair that owns every padded row (the array is preset to -1) -------------
+__global__ void moe_pair_of_row_kernel(const int32_t* __restrict__ row_of, int64_t n_pairs, int64_t padded_rows,
+                                       int32_t* __restrict__ pair_of_row) {
+  const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n_pairs) return;
+  const int r = row_of[p];
+  if (r >= 0 && r < padded_rows) pair_of_row[r] = (int32_t)p;
+}
+
 // ---- weighted unpermute: out[t] = sum_j w[t,j] * y[row_of[t*k+j]] (fp32 accumulate) ----------------
 __global__ void __launch_bounds__(256)
 moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t* __restrict__ w,
@@ -414,7 +423,7 @@ moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < k; ++j) {
       const int row = row_of[t * k + j];
-      const float wj = u2f((uint32_t)w[t * k + j] << 16);
+      const float wj = w != nullptr ? u2f((uint32_t)w[t * k + j] << 16) : 1.f;
       float f[8];
       unpack8(ld_nc_v4(y + (int64_t)row * ldy + c), f);
 #pragma unroll
@@ -835,9 +844,20 @@ int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int scor
   return B200Q_OK;
 }
 
+int b200q_moe_pair_of_row(const int32_t* row_of, int64_t n_pairs, int64_t padded_rows, int32_t* pair_of_row, void* stream) {
+  if (row_of == nullptr || pair_of_row == nullptr || n_pairs <= 0 || padded_rows <= 0 || n_pairs > INT32_MAX) return B200Q_ERR_INVALID_ARG;
+  int rc = require_sm100();
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  B200Q_CUDA(cudaMemsetAsync(pair_of_row, 0xff, (size_t)padded_rows * sizeof(int32_t), st));      // -1 everywhere
+  moe_pair_of_row_kernel<<<(unsigned)((n_pairs + 255) / 256), 256, 0, st>>>(row_of, n_pairs, padded_rows, pair_of_row);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
 int b200q_moe_unpermute(const void* y, int64_t ldy, const void* w, const int32_t* row_of, int64_t T, int k, int64_t D, void* out,
                         void* stream) {
-  if (y == nullptr || w == nullptr || row_of == nullptr || out == nullptr || T <= 0 || k <= 0 || D <= 0 || ldy < D)
+  if (y == nullptr || row_of == nullptr || out == nullptr || T <= 0 || k <= 0 || D <= 0 || ldy < D)
     return B200Q_ERR_INVALID_ARG;
   if ((D & 7) || (ldy & 7)) return B200Q_ERR_SHAPE;
   if (!aligned16(y) || !aligned16(out)) return B200Q_ERR_ALIGNMENT;

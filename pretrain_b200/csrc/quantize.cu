@@ -58,11 +58,11 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const uint16_t* __restri
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      m = absmax_bf16x2(m, absmax_bf16x2(v[u].x, v[u].y));
-      m = absmax_bf16x2(m, absmax_bf16x2(v[u].z, v[u].w));
+      m = absmax_raw_bf16x2(m, absmax_raw_bf16x2(v[u].x, v[u].y));
+      m = absmax_raw_bf16x2(m, absmax_raw_bf16x2(v[u].z, v[u].w));
     }
   }
-  float a = warp_max(fmaxf(bf16lo(m), bf16hi(m)));
+  float a = warp_max(absmax_halves(m));
   __shared__ float s[kWarps];
   if (lane == 0) s[warp] = a;
   __syncthreads();
@@ -175,23 +175,23 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
       }
 #pragma unroll
       for (int i = 0; i < NVEC; ++i) {
-        m = absmax_bf16x2(m, absmax_bf16x2(v[i].x, v[i].y));
-        m = absmax_bf16x2(m, absmax_bf16x2(v[i].z, v[i].w));
-        if (COLMAX) {
-          cm[4 * i] = absmax_bf16x2(cm[4 * i], v[i].x);
-          cm[4 * i + 1] = absmax_bf16x2(cm[4 * i + 1], v[i].y);
-          cm[4 * i + 2] = absmax_bf16x2(cm[4 * i + 2], v[i].z);
-          cm[4 * i + 3] = absmax_bf16x2(cm[4 * i + 3], v[i].w);
+        m = absmax_raw_bf16x2(m, absmax_raw_bf16x2(v[i].x, v[i].y));
+        m = absmax_raw_bf16x2(m, absmax_raw_bf16x2(v[i].z, v[i].w));
+        if (COLMAX) {                                   // signs cleared when the maxima are parked below
+          cm[4 * i] = absmax_raw_bf16x2(cm[4 * i], v[i].x);
+          cm[4 * i + 1] = absmax_raw_bf16x2(cm[4 * i + 1], v[i].y);
+          cm[4 * i + 2] = absmax_raw_bf16x2(cm[4 * i + 2], v[i].z);
+          cm[4 * i + 3] = absmax_raw_bf16x2(cm[4 * i + 3], v[i].w);
         }
       }
     } else if (tensor_amax == nullptr && live) {
       for (int64_t c = (wig * 32 + lane) * 8; c < cols; c += 256 * wpr) {
         uint4 t = ld_nc_v4(xr + c);
-        m = absmax_bf16x2(m, absmax_bf16x2(t.x, t.y));
-        m = absmax_bf16x2(m, absmax_bf16x2(t.z, t.w));
+        m = absmax_raw_bf16x2(m, absmax_raw_bf16x2(t.x, t.y));
+        m = absmax_raw_bf16x2(m, absmax_raw_bf16x2(t.z, t.w));
       }
     }
-    float amax = warp_max(fmaxf(bf16lo(m), bf16hi(m)));
+    float amax = warp_max(absmax_halves(m));
     if (wpr > 1) {
       if (lane == 0) smax[it & 1][warp] = amax;
       __syncthreads();
@@ -237,7 +237,8 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
     for (int i = 0; i < NVEC; ++i) {
       const int64_t c = (int64_t)((i * wpr + wig) * 32 + lane) * 8;
       if (c < cols)
-        *reinterpret_cast<uint4*>(&colmax_s[grp * half + (c >> 1)]) = make_uint4(cm[4 * i], cm[4 * i + 1], cm[4 * i + 2], cm[4 * i + 3]);
+        *reinterpret_cast<uint4*>(&colmax_s[grp * half + (c >> 1)]) =
+            make_uint4(abs_bf16x2(cm[4 * i]), abs_bf16x2(cm[4 * i + 1]), abs_bf16x2(cm[4 * i + 2]), abs_bf16x2(cm[4 * i + 3]));
     }
     __syncthreads();
     for (int64_t wi = threadIdx.x; wi < half; wi += kThreads) {
@@ -287,14 +288,14 @@ col_amax_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int6
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        m[0] = absmax_bf16x2(m[0], v[u].x); m[1] = absmax_bf16x2(m[1], v[u].y);
-        m[2] = absmax_bf16x2(m[2], v[u].z); m[3] = absmax_bf16x2(m[3], v[u].w);
+        m[0] = absmax_raw_bf16x2(m[0], v[u].x); m[1] = absmax_raw_bf16x2(m[1], v[u].y);
+        m[2] = absmax_raw_bf16x2(m[2], v[u].z); m[3] = absmax_raw_bf16x2(m[3], v[u].w);
       }
     }
   }
   __shared__ uint32_t s[kWarps][32][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) s[ty][tx][i] = m[i];
+  for (int i = 0; i < 4; ++i) s[ty][tx][i] = abs_bf16x2(m[i]);
   __syncthreads();
   if (ty == 0 && c < cols) {
 #pragma unroll
@@ -596,16 +597,19 @@ mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __r
 #pragma unroll
     for (int i = 0; i < 32; ++i) w[i] = col[i * (kDPitch / 4)];
     __syncthreads();                            // all column reads done: the tile may be overwritten
-    uint32_t m = absmax_bf16x2(w[0], w[1]);
+    uint32_t m = absmax_raw_bf16x2(w[0], w[1]);
 #pragma unroll
-    for (int i = 2; i < 32; ++i) m = absmax_bf16x2(m, w[i]);
+    for (int i = 2; i < 32; ++i) m = absmax_raw_bf16x2(m, w[i]);
+    m = abs_bf16x2(m);
     const int e0 = mx_scale_exp(bf16lo(m), FMT), e1 = mx_scale_exp(bf16hi(m), FMT);
-    const float inv0 = mx_inv_scale(e0), inv1 = mx_inv_scale(e1);
+    const uint32_t inv2 = mx_inv_scale_bf16x2(e0, e1);        // one packed multiply scales both columns
     uint32_t o0[8], o1[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      o0[i] = cvt_fp8x4(bf16lo(w[4 * i]) * inv0, bf16lo(w[4 * i + 1]) * inv0, bf16lo(w[4 * i + 2]) * inv0, bf16lo(w[4 * i + 3]) * inv0, FMT);
-      o1[i] = cvt_fp8x4(bf16hi(w[4 * i]) * inv1, bf16hi(w[4 * i + 1]) * inv1, bf16hi(w[4 * i + 2]) * inv1, bf16hi(w[4 * i + 3]) * inv1, FMT);
+      const uint32_t a = mul_bf16x2(w[4 * i], inv2), b = mul_bf16x2(w[4 * i + 1], inv2), c = mul_bf16x2(w[4 * i + 2], inv2),
+                     d = mul_bf16x2(w[4 * i + 3], inv2);
+      o0[i] = cvt_fp8x4(bf16lo(a), bf16lo(b), bf16lo(c), bf16lo(d), FMT);
+      o1[i] = cvt_fp8x4(bf16hi(a), bf16hi(b), bf16hi(c), bf16hi(d), FMT);
     }
     uint4* d0 = reinterpret_cast<uint4*>(tout + (2 * cp) * kDOutPitch + 32 * j);
     uint4* d1 = reinterpret_cast<uint4*>(tout + (2 * cp + 1) * kDOutPitch + 32 * j);

@@ -92,7 +92,7 @@ class _ExpertFFN(torch.autograd.Function):
         dgr, dgsr, dgc, dgsc = ops.swiglu_backward_quantize_dual(g, dh, E5M2)                  # of dg (R, 2I)
         da = ops.grouped_gemm_mxfp8_dgrad(dgr, dgsr, w1c, w1sc, plan, d, E5M2, E4M3)           # (R, D)
         dw1 = ops.grouped_gemm_mxfp8_wgrad(dgc, dgsc, ac, asc, plan, E5M2, E4M3)               # (E, 2I, D)
-        dx = ops.moe_unpermute(da, torch.ones(t, k, dtype=torch.bfloat16, device=da.device), plan.row_of, t)
+        dx = ops.moe_unpermute(da, None, plan.row_of, t)                                         # sum over the k slots
         xd, twd, w1d, w2d = ctx.dtypes
         return dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d), None
 

@@ -465,8 +465,9 @@ def moe_gather_quantize_dual(x: torch.Tensor, plan: MoEPlan, fmt=E4M3):
 
 def moe_pair_of_row(plan: MoEPlan) -> torch.Tensor:
     """Inverse of plan.row_of: the routed pair that owns every padded row, -1 for rows nobody owns."""
-    inv = torch.full((plan.padded_rows,), -1, dtype=torch.int32, device=plan.row_of.device)
-    inv[plan.row_of.long()] = torch.arange(plan.row_of.numel(), dtype=torch.int32, device=plan.row_of.device)
+    inv = torch.empty(plan.padded_rows, dtype=torch.int32, device=plan.row_of.device)
+    _lib.check(_lib.load().b200q_moe_pair_of_row(plan.row_of.data_ptr(), plan.row_of.numel(), plan.padded_rows, inv.data_ptr(), _stream()),
+               "b200q_moe_pair_of_row")
     return inv
 
 
@@ -591,13 +592,13 @@ def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str = "softmax", nor
     return idx, w, probs, counts
 
 
-def moe_unpermute(y: torch.Tensor, weights: torch.Tensor, row_of: torch.Tensor, n_tokens: int):
-    """out[t] = sum_j weights[t, j] * y[row_of[t*k + j]] (fp32 accumulate, bf16 out)."""
+def moe_unpermute(y: torch.Tensor, weights: torch.Tensor | None, row_of: torch.Tensor, n_tokens: int):
+    """out[t] = sum_j weights[t, j] * y[row_of[t*k + j]] (fp32 accumulate, bf16 out); weights None = all ones."""
     k = row_of.numel() // n_tokens
-    w = weights.to(torch.bfloat16).contiguous()
+    w = weights.to(torch.bfloat16).contiguous() if weights is not None else None
     d = y.shape[1]
     out = torch.empty(n_tokens, d, dtype=torch.bfloat16, device=y.device)
-    _lib.check(_lib.load().b200q_moe_unpermute(y.data_ptr(), y.stride(0), w.data_ptr(), row_of.data_ptr(), n_tokens, k, d,
+    _lib.check(_lib.load().b200q_moe_unpermute(y.data_ptr(), y.stride(0), w.data_ptr() if w is not None else None, row_of.data_ptr(), n_tokens, k, d,
                                                out.data_ptr(), _stream()), "b200q_moe_unpermute")
     return out
 

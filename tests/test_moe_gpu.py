@@ -459,6 +459,14 @@ def test_unpermute(ops, golden):
     assert (out.float() - ref32.float()).abs().max() <= 2 ** -7 * ref32.float().abs().max()
     gold = bf16_from_bits(golden["moe_y"])                            # the reference's bf16 index_add_
     assert (out.float() - gold.float()).abs().max() <= 2e-2 * gold.float().abs().max()
+    # no weights = unit weights; pair_of_row is the inverse of row_of with -1 on pad rows
+    ones = torch.ones_like(top_w).cuda()
+    assert torch.equal(ops.moe_unpermute(y_pad.cuda(), None, plan.row_of, top_i.shape[0]),
+                       ops.moe_unpermute(y_pad.cuda(), ones, plan.row_of, top_i.shape[0]))
+    inv = ops.moe_pair_of_row(plan).cpu()
+    want = torch.full((plan.padded_rows,), -1, dtype=torch.int32)
+    want[plan.row_of.cpu().long()] = torch.arange(top_i.numel(), dtype=torch.int32)
+    assert torch.equal(inv, want)
 
 
 def _mx_fake(t):

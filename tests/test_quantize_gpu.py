@@ -37,7 +37,15 @@ def _cases():
     zeros = torch.zeros(32, 32)
     big = torch.randn(64, 4352, generator=g) * 3        # > 4096 columns: re-read path of the per-row kernel
     odd = torch.randn(160, 96, generator=g)             # partial tiles in both directions
-    return {"x": x, "w": w, "outlier": xo, "wgu": wgu, "wide": wide.bfloat16(), "tiny": tiny.bfloat16(),
+    # one huge element per 32-block next to tiny, subnormal and signed-zero ones: the scaled values fall
+    # below every format's smallest subnormal and must come out as zeros that keep their sign
+    span = torch.randn(64, 128, generator=g) * 1e-30
+    span[:, ::32] = 3.0e38 * torch.sign(torch.randn(64, 4, generator=g))
+    span[:, 1::32] = -0.0
+    span[:, 2::32] = -1e-39
+    span[:, 3::32] = 2.0 ** -126
+    span[1::2, 4::32] = -(2.0 ** -133)
+    return {"span": span.bfloat16(), "x": x, "w": w, "outlier": xo, "wgu": wgu, "wide": wide.bfloat16(), "tiny": tiny.bfloat16(),
             "zeros": zeros.bfloat16(), "long": big.bfloat16(), "odd": odd.bfloat16()}
 
 
@@ -221,6 +229,15 @@ def test_mxfp8_both_directions_in_one_pass(ops, shape, dt, layout):
     oc, osf = R.quantize_mxfp8(x.cpu(), 0, dt)
     assert torch.equal(cc.cpu(), oc)
     assert torch.equal((G_unswizzle(sc, shape[1], shape[0] // 32) if layout else sc.view(shape[1], -1)).cpu(), osf)
+
+
+@pytest.mark.parametrize("dt", [E4, E5])
+def test_mxfp8_both_directions_on_blocks_that_span_the_exponent_range(ops, dt):
+    x = CASES["span"].cuda()
+    cr, sr, cc, sc = ops.quantize_mxfp8_dual(x, dt, 0)
+    for axis, codes, sf in ((-1, cr, sr), (0, cc, sc)):
+        oc, osf = R.quantize_mxfp8(x.cpu(), axis, dt)
+        assert torch.equal(codes.cpu(), oc) and torch.equal(sf.cpu().reshape(-1), osf.reshape(-1))
 
 
 @pytest.mark.parametrize("shape", [(512, 768), (96, 160), (16, 8), (160, 96), (64, 4352), (2048, 8192)])
