@@ -510,6 +510,11 @@ int choose_bn(int64_t M, int64_t N, int64_t row_bytes, int64_t groups = 1) {
 bool pair_eligible(int64_t M, int64_t N, int64_t row_bytes, bool grouped);
 template <int KIND, int EPI = 0>
 int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, const GemmParams& gp, cudaStream_t st);
+// ... and of the grouped MXFP8 forms
+bool pair_grouped_eligible(const GemmParams& gp);
+template <int EPI>
+int launch_pair_grouped(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, const GemmParams& gp,
+                        cudaStream_t st);
 
 template <int KIND>
 int dispatch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, const GemmParams& p, cudaStream_t st) {
@@ -667,7 +672,8 @@ int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const vo
   if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
-  p.M = padded_rows; p.N = N; p.K = K; p.tile_expert = tile_expert; p.num_tiles = num_tiles;
+  p.M = padded_rows; p.N = N; p.K = K; p.tile_expert = tile_expert; p.num_tiles = num_tiles; p.n_experts = E;
+  if (pair_grouped_eligible(p)) return launch_pair_grouped<EPI_BF16>(A, B, one_output(D), ldd, (int64_t)E * N, p, (cudaStream_t)stream);
   return dispatch<KIND_MX>(A, B, one_output(D), ldd, (int64_t)E * N, p, (cudaStream_t)stream);
 }
 
@@ -687,7 +693,8 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
   GemmParams p;
   int rc = prepare_glu(&p, A, sfA, B, sfB, a_fmt, b_fmt, padded_rows, N, K, H, ldh, sfH, true, (cudaStream_t)stream);
   if (rc) return rc;
-  p.tile_expert = tile_expert; p.num_tiles = num_tiles;
+  p.tile_expert = tile_expert; p.num_tiles = num_tiles; p.n_experts = E;
+  if (pair_grouped_eligible(p)) return launch_pair_grouped<EPI_GLU>(A, B, OutSpec{}, 0, (int64_t)E * N, p, (cudaStream_t)stream);
   return dispatch_glu(A, B, (int64_t)E * N, p, (cudaStream_t)stream);
 }
 
@@ -710,9 +717,10 @@ int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const
   return dispatch_glu_nv(A, B, N, p, st);
 }
 
-// one-CTA kernel, tile width by the cost model (the grouped backward forms have no pair variant)
+// the grouped backward forms: CTA pairs when the shape allows, else the one-CTA kernel with the tile width of the cost model
 static int dispatch_one_cta_mx(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, const GemmParams& p,
                                cudaStream_t st) {
+  if (pair_grouped_eligible(p)) return launch_pair_grouped<EPI_BF16>(A, B, one_output(D), ldd, b_rows, p, st);
   // ragged form: every expert has its own output tiles and (on average) its share of the K range
   const int64_t groups = p.ragged_offs ? p.n_experts : 1;
   const int bn = g_force_bn ? g_force_bn : choose_bn<KIND_MX>(p.M, p.N, p.K / groups, groups);

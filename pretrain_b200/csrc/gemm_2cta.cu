@@ -13,6 +13,13 @@
 //   * the peer's epilogue warps arrive remotely on the leader's "accumulator free" barrier;
 //   * the pair synchronizes as a cluster after barrier set-up and before tear-down.
 // No TMA multicast is used.
+//
+// GROUPED: the three ragged MoE forms of gemm.cu (rows of A grouped by expert; the transposed weight
+// stack along K; per-expert K ranges) on the same pairs.  Expert segments are whole 128-row tiles,
+// not 256-row ones, so the pair tiles are formed INSIDE each expert: expert e with n tiles gets
+// ceil(n / 2) pair tiles, and when n is odd the second CTA of the last pair has no rows of its own -
+// it still stages its half of B (the first CTA's MMA reads it) but stores nothing.  Every CTA builds
+// the (first tile, pair-tile prefix) table of the experts in shared memory from tile_expert at start.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -24,7 +31,10 @@ namespace pair {
 constexpr int PBN = 256;                          // columns of the pair's tile
 constexpr int HALF_N = PBN / 2;                   // B rows each CTA stages
 
-template <int KIND>
+constexpr int kPairMaxExperts = 256;
+constexpr int kGroupTableBytes = 2 * (kPairMaxExperts + 1) * 4 + 248;     // first tile + pair prefix per expert, 256-aligned
+
+template <int KIND, bool GROUPED = false>
 struct PCfg {
   static constexpr int K_ATOMS = KIND == KIND_NV ? 4 : 1;
   static constexpr int A_BYTES = BM * BKB, B_BYTES = HALF_N * BKB;
@@ -33,7 +43,8 @@ struct PCfg {
   static constexpr int TX_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;      // per CTA and K step
   static constexpr int STAGE_BYTES = ((TX_BYTES + 1023) / 1024) * 1024;
   static constexpr int EPI_BYTES = 2 * kEpiBytes1;
-  static constexpr int STAGES_RAW = (kSmemBudget - 2048 - EPI_BYTES) / STAGE_BYTES;
+  static constexpr int GRP_BYTES = GROUPED ? kGroupTableBytes : 0;
+  static constexpr int STAGES_RAW = (kSmemBudget - 2048 - GRP_BYTES - EPI_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SFA_COLS = row_scaled(KIND) ? 0 : 4 * K_ATOMS;
   static constexpr int SFB_COLS = row_scaled(KIND) ? 0 : 8 * K_ATOMS;
@@ -45,7 +56,8 @@ struct PCfg {
   static constexpr int SFB_COL0 = SFA_COL0 + SFA_COLS;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFF = EPI_OFF + EPI_BYTES;
-  static constexpr int SMEM_BYTES = BAR_OFF + 256 + 1024;
+  static constexpr int GRP_OFF = BAR_OFF + 256;
+  static constexpr int SMEM_BYTES = BAR_OFF + 256 + GRP_BYTES + 1024;
   static_assert(SFB_COL0 + SFB_COLS <= 512, "tensor memory overflow");
   static_assert(SMEM_BYTES <= kSmemBudget, "shared memory overflow");
 };
@@ -58,6 +70,29 @@ struct PairParams {
   int num_mp, num_n, num_k;      // pair tiles (256 rows), column tiles, K steps
   int sf_kt;                     // 512-byte scale atoms per 128-row group along K
   GluOut glu;                    // SwiGLU epilogues: where they write
+  // GROUPED only (see GemmParams): M = padded rows (fprop, dgrad) or rows per expert (wgrad); N per expert
+  const int32_t* tile_expert;    // fprop / dgrad: expert of every 128-row tile of A
+  const int32_t* num_tiles;      //                128-row tiles in use (device)
+  int num_m128;                  //                upper bound of that count
+  const int32_t* ragged_offs;    // wgrad: K range of every expert
+  int n_experts;
+  int b_along_k;                 // dgrad: B is [N, E*K]
+  int sf_kt_b;                   // scale atoms per row group of B
+  int64_t K;                     // contraction length per expert (bytes), dgrad's K offset unit
+};
+
+// Everything the roles of one CTA need to know about pair tile t.
+struct PTile {
+  int row0;            // this CTA's first row of A
+  int n_blk;
+  int k0, nk;          // first K step, number of K steps
+  int brow0;           // this CTA's first row of B
+  int bgroup;          // first 128-row scale group of the pair's B tile
+  int bk0;             // K offset of B (bytes)
+  int sfb_k0;          // first scale atom of B along K
+  int64_t drow_off;    // row offset of the output
+  float keep;          // 0: expert without rows (wgrad), the dummy K step is multiplied away
+  bool live;           // this CTA owns output rows
 };
 
 __device__ __forceinline__ void pair_tile_coords(int t, int num_mp, int num_n, int& mp, int& n) {
@@ -70,14 +105,66 @@ __device__ __forceinline__ void pair_tile_coords(int t, int num_mp, int num_n, i
   n = r / gm;
 }
 
+template <bool GROUPED>
+__device__ __forceinline__ PTile get_ptile(const PairParams& p, int t, int total_pt, int cta, const int* g_first, const int* g_pairs) {
+  PTile ti;
+  ti.k0 = 0; ti.nk = p.num_k; ti.bk0 = 0; ti.sfb_k0 = 0; ti.drow_off = 0; ti.keep = 1.f;
+  int mp;
+  if (!GROUPED) {
+    pair_tile_coords(t, p.num_mp, p.num_n, mp, ti.n_blk);
+    ti.row0 = mp * 256 + cta * BM;
+    ti.live = true;                                   // rows beyond M are clipped by the epilogue
+    ti.brow0 = ti.n_blk * PBN + cta * HALF_N;
+    ti.bgroup = ti.n_blk * 2;
+  } else if (p.ragged_offs != nullptr) {
+    const int per = p.num_mp * p.num_n;
+    const int e = t / per;
+    pair_tile_coords(t - e * per, p.num_mp, p.num_n, mp, ti.n_blk);
+    ti.row0 = mp * 256 + cta * BM;
+    ti.live = ti.row0 < p.M;
+    ti.brow0 = ti.n_blk * PBN + cta * HALF_N;
+    ti.bgroup = ti.n_blk * 2;
+    const int r0 = __ldg(p.ragged_offs + e), r1 = __ldg(p.ragged_offs + e + 1);
+    ti.k0 = r0 >> 7;
+    ti.nk = (r1 - r0) >> 7;
+    if (ti.nk <= 0) {                                 // no rows: one in-range K step, scaled to zero
+      ti.nk = 1;
+      ti.k0 = ti.k0 < p.num_k ? ti.k0 : p.num_k - 1;
+      ti.keep = 0.f;
+    }
+    ti.drow_off = (int64_t)e * p.M;
+  } else {
+    int pt;
+    pair_tile_coords(t, total_pt, p.num_n, pt, ti.n_blk);
+    int lo = 0, hi = p.n_experts - 1;                 // last expert whose first pair tile is <= pt
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (g_pairs[mid] <= pt) lo = mid; else hi = mid - 1;
+    }
+    const int e = lo, tile0 = g_first[e] + 2 * (pt - g_pairs[e]);
+    ti.row0 = (tile0 + cta) * BM;
+    ti.live = cta == 0 || tile0 + 1 < g_first[e + 1];
+    ti.brow0 = ti.n_blk * PBN + cta * HALF_N;
+    ti.bgroup = ti.n_blk * 2;
+    if (p.b_along_k) {
+      ti.bk0 = (int)(e * p.K);
+      ti.sfb_k0 = e * p.sf_kt;
+    } else {
+      ti.brow0 += e * (int)p.N;
+      ti.bgroup += (int)((e * p.N) >> 7);
+    }
+  }
+  return ti;
+}
+
 }  // namespace pair
 
-template <int KIND, int EPI>
+template <int KIND, int EPI, bool GROUPED = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm_threads(EPI), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                  const __grid_constant__ OutMaps outs, const pair::PairParams p) {
-  using C = pair::PCfg<KIND>;
+  using C = pair::PCfg<KIND, GROUPED>;
   constexpr int BN = pair::PBN;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -93,7 +180,67 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = ptx::cluster_ctarank();       // 0 = leader
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int total_tiles = p.num_mp * p.num_n;
+  int* g_first = reinterpret_cast<int*>(smem_gen + C::GRP_OFF);        // GROUPED: first 128-row tile of every expert (+ end)
+  int* g_pairs = g_first + pair::kPairMaxExperts + 1;                   //          pair tiles before every expert (+ total)
+  const bool by_expert = GROUPED && p.tile_expert != nullptr;
+  int live_tiles = 0;
+  if (by_expert) {
+    live_tiles = __ldg(p.num_tiles);
+    live_tiles = live_tiles < p.num_m128 ? live_tiles : p.num_m128;
+    for (int e = threadIdx.x; e <= p.n_experts; e += gemm_threads(EPI)) g_first[e] = e == p.n_experts ? live_tiles : 0x7fffffff;
+    __syncthreads();
+    for (int t = threadIdx.x; t < live_tiles; t += gemm_threads(EPI)) {
+      const int e = __ldg(p.tile_expert + t), prev = t > 0 ? __ldg(p.tile_expert + t - 1) : -1;
+      if (e != prev && e >= 0 && e < p.n_experts) g_first[e] = t;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // suffix minimum (an expert without tiles starts where the next one does), pair-tile counts, their prefix sums
+      constexpr int PER = pair::kPairMaxExperts / 32;
+      const int E = p.n_experts, base = lane * PER;
+      int v[PER];
+#pragma unroll
+      for (int i = 0; i < PER; ++i) v[i] = base + i < E ? g_first[base + i] : live_tiles;
+#pragma unroll
+      for (int i = PER - 2; i >= 0; --i) v[i] = v[i] < v[i + 1] ? v[i] : v[i + 1];
+      int suf = v[0];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int x = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32 && x < suf) suf = x;
+      }
+      int later = __shfl_down_sync(0xffffffffu, suf, 1);       // minimum over all later lanes
+      if (lane == 31) later = live_tiles;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) v[i] = v[i] < later ? v[i] : later;
+      int next0 = __shfl_down_sync(0xffffffffu, v[0], 1);
+      if (lane == 31) next0 = live_tiles;
+      int cnt[PER], sum = 0;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int end = i + 1 < PER ? v[i + 1] : next0;
+        cnt[i] = base + i < E ? (end - v[i] + 1) >> 1 : 0;
+        sum += cnt[i];
+      }
+      int inc = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int x = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += x;
+      }
+      int run = inc - sum;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        if (base + i < E) { g_first[base + i] = v[i]; g_pairs[base + i] = run; }
+        run += cnt[i];
+      }
+      if (lane == 31) g_pairs[E] = inc;
+    }
+    __syncthreads();
+  }
+  const int total_pt = by_expert ? g_pairs[p.n_experts] : 0;
+  const int total_tiles = by_expert ? total_pt * p.num_n
+                                    : p.num_mp * p.num_n * (GROUPED && p.ragged_offs != nullptr ? p.n_experts : 1);
 
   if (threadIdx.x == 0) {
     // full: one arrival (with its byte count) per producer of the pair; empty / accumulator-full: the
@@ -122,26 +269,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
-        int mp, n_blk;
-        pair::pair_tile_coords(t, p.num_mp, p.num_n, mp, n_blk);
-        const int row0 = mp * 256 + (int)cta * BM;                   // this CTA's rows of A
-        const int brow0 = n_blk * BN + (int)cta * pair::HALF_N;      // this CTA's rows of B
-        for (int k = 0; k < p.num_k; ++k) {
+        const pair::PTile ti = pair::get_ptile<GROUPED>(p, t, total_pt, (int)cta, g_first, g_pairs);
+        const int row0 = ti.row0;                                    // this CTA's rows of A
+        const int brow0 = ti.brow0;                                  // this CTA's rows of B
+        for (int kl = 0; kl < ti.nk; ++kl) {
+          const int k = ti.k0 + kl;
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1) || *abort_flag) { ok = false; break; }
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           const uint32_t fb = full_bar(stage) & ptx::kLeaderMask;    // the leader's barrier, from either CTA
           ptx::mbar_expect_tx_cluster(fb, C::TX_BYTES);
           ptx::tma_load_2d_pair(sa, &tmap_a, k * BKB, row0, fb);
-          ptx::tma_load_2d_pair(sb, &tmap_b, k * BKB, brow0, fb);
+          ptx::tma_load_2d_pair(sb, &tmap_b, k * BKB + ti.bk0, brow0, fb);
           if (!row_scaled(KIND)) {
             // scale buffers viewed as rows of 256 bytes: a 512-byte atom is 2 rows, the K_ATOMS atoms of
             // one K step and row group are contiguous
             const uint32_t ssfa = sb + C::B_BYTES, ssfb = ssfa + C::SFA_BYTES;
-            const int sf_kt = p.sf_kt;
+            const int sf_kt = p.sf_kt, sf_kt_b = GROUPED ? p.sf_kt_b : p.sf_kt;
             ptx::tma_load_2d_pair(ssfa, &tmap_sfa, 0, 2 * ((row0 >> 7) * sf_kt + k * C::K_ATOMS), fb);
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              ptx::tma_load_2d_pair(ssfb + j * C::K_ATOMS * 512, &tmap_sfb, 0, 2 * ((n_blk * 2 + j) * sf_kt + k * C::K_ATOMS), fb);
+              ptx::tma_load_2d_pair(ssfb + j * C::K_ATOMS * 512, &tmap_sfb, 0,
+                                    2 * ((ti.bgroup + j) * sf_kt_b + ti.sfb_k0 + k * C::K_ATOMS), fb);
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
@@ -164,7 +312,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (acc ? C::ACC1_COL0 : 0);
-        for (int k = 0; k < p.num_k; ++k) {
+        // only the ragged form has a K range per tile; the others need no tile lookup here
+        const int nk = GROUPED && p.ragged_offs != nullptr ? pair::get_ptile<GROUPED>(p, t, total_pt, 0, g_first, g_pairs).nk : p.num_k;
+        for (int k = 0; k < nk; ++k) {
           if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
@@ -219,13 +369,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (KIND == KIND_NV) alpha = __ldg(p.scale_a) * __ldg(p.scale_b);
     constexpr int NBLK = BN / EPI_COLS;
     for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++tile_iter) {
-      int mp, n_blk;
-      pair::pair_tile_coords(t, p.num_mp, p.num_n, mp, n_blk);
+      const pair::PTile ti = pair::get_ptile<GROUPED>(p, t, total_pt, (int)cta, g_first, g_pairs);
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase) || *abort_flag) { ok = false; break; }
       ptx::tc_fence_after();
-      const int64_t row0 = (int64_t)mp * 256 + cta * BM + q * 32, row = row0 + lane;
-      const int64_t col0 = (int64_t)n_blk * BN;
-      float row_scale = alpha;
+      const int64_t row0 = ti.drow_off + ti.row0 + q * 32, row = row0 + lane;
+      const int64_t col0 = (int64_t)ti.n_blk * BN;
+      // rows this CTA may store: none for the idle half of an expert's odd last pair
+      const int64_t m_lim = !ti.live ? 0 : (GROUPED && p.ragged_offs != nullptr ? ti.drow_off + p.M : p.M);
+      float row_scale = alpha * ti.keep;
       if (row_scaled(KIND)) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
@@ -238,10 +389,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       };
       if (EPI != EPI_BF16)
         epilogue_tile_glu<EPI == EPI_GLU ? GLU_MX : GLU_BF16, NBLK, RELEASE_AFTER, 2>(
-            taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, p.M, p.N, alpha, p.glu, release);
+            taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, m_lim, p.N, alpha, p.glu, release);
       else
         epilogue_tile<row_scaled(KIND), KIND == KIND_I8, NBLK, 2, RELEASE_AFTER>(
-            taddr, C::OVERLAP && acc == 0, row0, col0, p.M, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
+            taddr, C::OVERLAP && acc == 0, row0, col0, m_lim, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
             release);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
@@ -309,6 +460,61 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   B200Q_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   const int tiles = p.num_mp * p.num_n, pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
   gemm_pair_kernel<KIND, EPI><<<2 * pairs, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, msa, msb, md, p);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+// The grouped MXFP8 forms on pairs.  gp as for the one-CTA kernel: tile_expert / num_tiles (fprop, and dgrad
+// with b_along_k) or ragged_offs (wgrad); b_rows = rows of the B matrix as stored.
+// Opt-in (b200q_debug_set_gemm_pair(1)): at T = 16384, E = 64, k = 4, D = 768 the pairs move a third
+// fewer operand bytes but lose it again to the idle halves of odd experts (6 % more tiles), the
+// table build at the start of every CTA and the per-tile expert search: 54 / 46 us against 54 / 40 us
+// for the one-CTA kernel on the two forward GEMMs (the dense pair kernel on the same shapes: 46 / 34 us).
+// The wgrad form has neither table nor idle halves and still only ties (44 / 32 us against 46 / 32 us).
+bool pair_grouped_eligible(const GemmParams& gp) {
+  // a forced tile width (test hook) means the one-CTA kernel
+  if (g_pair_mode <= 0 || g_force_bn != 0 || gp.n_experts > pair::kPairMaxExperts || (gp.K & 127)) return false;
+  if (gp.ragged_offs != nullptr) return (gp.M & 127) == 0;
+  return gp.tile_expert != nullptr && (gp.N & 127) == 0;     // an expert's B rows start on a scale-group boundary
+}
+
+template <int EPI>
+int launch_pair_grouped(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, const GemmParams& gp,
+                        cudaStream_t st) {
+  using C = pair::PCfg<KIND_MX, true>;
+  const bool ragged = gp.ragged_offs != nullptr;
+  const int64_t row_bytes = gp.K;                                              // per expert for the dgrad form
+  const int64_t b_row_bytes = gp.b_along_k ? row_bytes * gp.n_experts : row_bytes;
+  const int64_t m_out = ragged ? gp.M * gp.n_experts : gp.M;
+  CUtensorMap ma, mb, msa, msb;
+  OutMaps md;
+  int rc;
+  if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, gp.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, b_row_bytes, b_rows, b_row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if (EPI != EPI_BF16) {
+    md.count = 0;
+    for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
+  } else if ((rc = make_out_maps(&md, D, m_out, gp.N, ldd))) {
+    return rc;
+  }
+  const int sf_kt = (int)(row_bytes / 128), sf_kt_b = gp.b_along_k ? sf_kt * gp.n_experts : sf_kt;
+  const uint64_t rows_a = (uint64_t)((gp.M + 127) / 128) * sf_kt * 2, rows_b = (uint64_t)((b_rows + 127) / 128) * sf_kt_b * 2;
+  if ((rc = encode_2d(&msa, CU_TENSOR_MAP_DATA_TYPE_UINT8, gp.sfa, 256, rows_a, 256, 256, 2, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+  if ((rc = encode_2d(&msb, CU_TENSOR_MAP_DATA_TYPE_UINT8, gp.sfb, 256, rows_b, 256, 256, 2, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+  pair::PairParams p = {};
+  p.a_fmt = gp.a_fmt; p.b_fmt = gp.b_fmt; p.M = gp.M; p.N = gp.N;
+  p.num_mp = (int)((gp.M + 255) / 256);
+  p.num_n = (int)((gp.N + pair::PBN - 1) / pair::PBN);
+  p.num_k = (int)(row_bytes / BKB);
+  p.sf_kt = sf_kt; p.sf_kt_b = sf_kt_b;
+  p.glu = gp.glu;
+  p.tile_expert = gp.tile_expert; p.num_tiles = gp.num_tiles; p.num_m128 = (int)((gp.M + 127) / 128);
+  p.ragged_offs = gp.ragged_offs; p.n_experts = gp.n_experts; p.b_along_k = gp.b_along_k; p.K = gp.K;
+  B200Q_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<KIND_MX, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  // the pair-tile count of the expert forms is only known on the device: every pair of the GPU starts
+  const int64_t tiles = ragged ? (int64_t)p.num_mp * p.num_n * gp.n_experts : (int64_t)(p.num_m128 + 1) / 2 * p.num_n;
+  const int pairs = (int)(tiles < kNumSMs / 2 ? tiles : kNumSMs / 2);
+  gemm_pair_kernel<KIND_MX, EPI, true><<<2 * pairs, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, msa, msb, md, p);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -90,13 +90,18 @@ def test_fused_permute_quantize_is_bit_exact(ops):
     assert torch.equal(sf_nat[want_rows], rs)
 
 
-@pytest.mark.parametrize("counts", [[5, 0, 7, 4], [200, 0, 0, 131], [128, 256, 1, 0], [0, 0, 300, 0]])
+# 37 experts, every fifth one empty, up to 6 row tiles each: odd and even tile counts in a row
+_MANY = [int(c) for c in torch.randint(0, 700, (37,), generator=torch.Generator().manual_seed(3)) * (torch.arange(37) % 5 != 2)]
+
+
+@pytest.mark.parametrize("counts", [[5, 0, 7, 4], [200, 0, 0, 131], [128, 256, 1, 0], [0, 0, 300, 0], "many"])
 @pytest.mark.parametrize("k,n", [(256, 384), (768, 384), (384, 768)])
-@pytest.mark.parametrize("bn", [0, 128, 192, 256])
+@pytest.mark.parametrize("bn", [0, 128, 192, 256, "pair"])        # tile width of the one-CTA kernel (0 = by shape) / CTA pairs
 def test_grouped_backward_gemms(ops, counts, k, n, bn):
     """dgrad (operand = transposed weight stack, expert offset along K) and wgrad (ragged K range per
     expert, one output matrix per expert, zeros for experts without rows) against dequantize-then-matmul."""
     from pretrain_b200 import _lib
+    counts = _MANY if counts == "many" else counts
     g = torch.Generator().manual_seed(sum(counts) + k + n)
     r, e = sum(counts), len(counts)
     gy = torch.randn(r, k, generator=g).bfloat16().cuda()               # "output gradient" rows, K = the layer's out features
@@ -112,13 +117,15 @@ def test_grouped_backward_gemms(ops, counts, k, n, bn):
     gy_pad[live:] = 0; x_pad[live:] = 0
     gt, gtsf = ops.quantize_mxfp8(gy_pad, 0)                             # (k, padded_rows)
     xt, xtsf = ops.quantize_mxfp8(x_pad, 0)                              # (n, padded_rows)
-    _lib.load().b200q_debug_set_gemm_bn(bn)
+    _lib.load().b200q_debug_set_gemm_pair(1 if bn == "pair" else 0)
+    _lib.load().b200q_debug_set_gemm_bn(0 if bn == "pair" else bn)
     try:
         dx = ops.grouped_gemm_mxfp8_dgrad(a, sfa, wt, wtsf, plan, n)     # (padded_rows, n)
         dw = ops.grouped_gemm_mxfp8_wgrad(gt, gtsf, xt, xtsf, plan)      # (E, k, n)
         ops.device_status()
     finally:
         _lib.load().b200q_debug_set_gemm_bn(0)
+        _lib.load().b200q_debug_set_gemm_pair(0)
     a_deq = G.deq_mxfp8(a, sfa)
     wt_deq = G.deq_mxfp8(wt, wtsf)                                       # (n, E*k)
     gt_deq, xt_deq = G.deq_mxfp8(gt, gtsf), G.deq_mxfp8(xt, xtsf)
@@ -174,9 +181,11 @@ def _grouped_ref(a_deq, w_deq, counts):
     return out
 
 
-@pytest.mark.parametrize("counts", [[5, 0, 7, 4], [0, 5, 7, 4], [5, 7, 4, 0], [200, 0, 0, 131], [128, 256, 1, 0]])
+@pytest.mark.parametrize("pair", [1, -1])          # CTA pairs formed inside every expert (opt-in) / the one-CTA kernel
+@pytest.mark.parametrize("counts", [[5, 0, 7, 4], [0, 5, 7, 4], [5, 7, 4, 0], [200, 0, 0, 131], [128, 256, 1, 0], [300, 129, 0, 513, 1], _MANY])
 @pytest.mark.parametrize("d,n", [(256, 384), (768, 768)])
-def test_grouped_gemm_with_empty_experts(ops, counts, d, n):
+def test_grouped_gemm_with_empty_experts(ops, counts, d, n, pair):
+    from pretrain_b200 import _lib
     g = torch.Generator().manual_seed(sum(counts) + d)
     r, e = sum(counts), len(counts)
     x = torch.randn(r, d, generator=g).bfloat16().cuda()
@@ -185,8 +194,12 @@ def test_grouped_gemm_with_empty_experts(ops, counts, d, n):
     plan = ops.moe_pad_plan(offs, r)
     a, sfa = ops.moe_gather(x, plan, True)
     wq, wsf = ops.quantize_mxfp8(w.reshape(e * n, d), 1)
-    out = ops.grouped_gemm_mxfp8(a, sfa, wq, wsf, plan, n)
-    ops.device_status()
+    _lib.load().b200q_debug_set_gemm_pair(pair)
+    try:
+        out = ops.grouped_gemm_mxfp8(a, sfa, wq, wsf, plan, n)
+        ops.device_status()
+    finally:
+        _lib.load().b200q_debug_set_gemm_pair(0)
     xq, xsf = ops.quantize_mxfp8(x, 1)
     ref = _grouped_ref(G.deq_mxfp8(xq, xsf), G.deq_mxfp8(wq, wsf).view(e, n, d), counts)
     pstart = plan.padded_offs.cpu().tolist()
@@ -202,7 +215,7 @@ def test_grouped_gemm_with_empty_experts(ops, counts, d, n):
 
 @pytest.mark.parametrize("counts", [[5, 0, 7, 4], [200, 0, 0, 131], [128, 256, 1, 0]])
 @pytest.mark.parametrize("d,inter", [(256, 64), (768, 384), (512, 192)])
-@pytest.mark.parametrize("bn", [0, 128, 192, 256])
+@pytest.mark.parametrize("bn", [0, 128, 192, 256, "pair"])
 def test_swiglu_epilogue_equals_gemm_then_swiglu(ops, counts, d, inter, bn):
     """Grouped GEMM with the SwiGLU + MXFP8 epilogue over interleaved weights == grouped GEMM to
     bf16 followed by the stand-alone SwiGLU + MXFP8 kernel over the plain weights, byte for byte."""
@@ -221,13 +234,15 @@ def test_swiglu_epilogue_equals_gemm_then_swiglu(ops, counts, d, inter, bn):
     wq, wsf = ops.quantize_mxfp8(wp.reshape(e * n_pad, d), 1)
     hb = ops.grouped_gemm_mxfp8(a, sfa, wq, wsf, plan, n_pad)[:live, : 2 * inter].contiguous()
     want_codes, want_sf = ops.swiglu(hb, True)
-    _lib.load().b200q_debug_set_gemm_bn(bn)
+    _lib.load().b200q_debug_set_gemm_pair(1 if bn == "pair" else 0)
+    _lib.load().b200q_debug_set_gemm_bn(0 if bn == "pair" else bn)
     try:
         wqi, wsfi = ops.quantize_mxfp8_rowmap(w.reshape(e * 2 * inter, d), ops.glu_row_map(e, inter, "cuda"))
         got_codes, got_sf = ops.grouped_gemm_mxfp8_swiglu(a, sfa, wqi, wsfi, plan, 2 * inter)
         ops.device_status()
     finally:
         _lib.load().b200q_debug_set_gemm_bn(0)
+        _lib.load().b200q_debug_set_gemm_pair(0)
     assert torch.equal(got_codes[:live], want_codes)
     n_sf = live // 128 * ((inter // 32 + 3) // 4) * 512
     assert torch.equal(got_sf[:n_sf], want_sf[:n_sf])
