@@ -667,6 +667,73 @@ int launch_mx_tile_quant(const TileSrc& src, bool aligned_src, int64_t rows, int
   return B200Q_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Per-column FP8 codes (transposed output) given the column scales, on the tile structure of
+// mx_tile_quant_kernel: 128 x 128 tile staged with 32-byte loads, a thread takes two adjacent
+// columns x 32 rows as packed bf16 pairs (32 four-byte shared-memory loads), the codes go back
+// through the same memory as 128-byte rows of the transposed matrix.  The arithmetic is the
+// scaled-FP8 one (a division by the fp32 scale: hoisted reciprocal + one correction).
+// rows % 32 == 0, cols % 32 == 0; other shapes use transpose_quant_kernel.
+// ------------------------------------------------------------------------------------------
+template <int FMT, bool WIDE>
+__global__ void __launch_bounds__(kThreads)
+fp8_col_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
+                          const float* __restrict__ col_scales, uint8_t* __restrict__ codes_c, float qmax) {
+  extern __shared__ __align__(16) uint8_t dual_smem[];
+  uint8_t* tin = dual_smem;
+  uint8_t* tout = dual_smem;                  // written only after every thread has read its columns (barrier below)
+  const int tid = threadIdx.x;
+  const int64_t c0 = (int64_t)blockIdx.x * kDT, r0 = (int64_t)blockIdx.y * kDT;
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int item = i * kThreads + tid, r = item >> 2, q = item & 3;     // 4 runs of 32 per tile row
+    const int64_t gr = r0 + r, gc = c0 + q * 32;
+    uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (gr < rows && gc < cols) {
+      const uint16_t* xp = x + gr * ld + gc;
+      ld_nc_32B<WIDE>(xp, v[0], v[1]);
+      ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(tin + r * kDPitch + q * 64);
+    dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; dst[3] = v[3];
+  }
+  __syncthreads();
+
+  {
+    const int cp = tid & 63, j = tid >> 6;            // column pair, block of 32 rows
+    const uint32_t* col = reinterpret_cast<const uint32_t*>(tin + (32 * j) * kDPitch) + cp;
+    uint32_t w[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) w[i] = col[i * (kDPitch / 4)];
+    __syncthreads();                            // all column reads done: the tile may be overwritten
+    const int64_t gc = c0 + 2 * cp;
+    const float s0 = gc < cols ? __ldg(col_scales + gc) : 1.f, s1 = gc + 1 < cols ? __ldg(col_scales + gc + 1) : 1.f;
+    const float rc0 = rcp_rn(s0), rc1 = rcp_rn(s1);
+    uint32_t o0[8], o1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o0[i] = cvt_codes_x4(quot_for_cast(bf16lo(w[4 * i]), s0, rc0), quot_for_cast(bf16lo(w[4 * i + 1]), s0, rc0),
+                           quot_for_cast(bf16lo(w[4 * i + 2]), s0, rc0), quot_for_cast(bf16lo(w[4 * i + 3]), s0, rc0), FMT, qmax);
+      o1[i] = cvt_codes_x4(quot_for_cast(bf16hi(w[4 * i]), s1, rc1), quot_for_cast(bf16hi(w[4 * i + 1]), s1, rc1),
+                           quot_for_cast(bf16hi(w[4 * i + 2]), s1, rc1), quot_for_cast(bf16hi(w[4 * i + 3]), s1, rc1), FMT, qmax);
+    }
+    uint4* d0 = reinterpret_cast<uint4*>(tout + (2 * cp) * kDOutPitch + 32 * j);
+    uint4* d1 = reinterpret_cast<uint4*>(tout + (2 * cp + 1) * kDOutPitch + 32 * j);
+    d0[0] = make_uint4(o0[0], o0[1], o0[2], o0[3]); d0[1] = make_uint4(o0[4], o0[5], o0[6], o0[7]);
+    d1[0] = make_uint4(o1[0], o1[1], o1[2], o1[3]); d1[1] = make_uint4(o1[4], o1[5], o1[6], o1[7]);
+  }
+  __syncthreads();
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int id = i * kThreads + tid, oc = id >> 3, ch = id & 7;
+    if (c0 + oc < cols && r0 + ch * 16 < rows)
+      *reinterpret_cast<uint4*>(codes_c + (c0 + oc) * rows + r0 + ch * 16) =
+          *reinterpret_cast<const uint4*>(tout + oc * kDOutPitch + ch * 16);
+  }
+}
+
 inline bool rows_32B_aligned(const void* p, int64_t ld) { return aligned32(p) && (ld & 15) == 0; }
 
 int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
@@ -723,6 +790,26 @@ void launch_transpose(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld,
     transpose_quant_kernel<MODE, FMT_E4M3><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
   else
     transpose_quant_kernel<MODE, FMT_E5M2><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
+}
+
+// Per-column codes from given column scales: the tile kernel on whole 32 x 32 blocks, else the general transposing kernel.
+void launch_fp8_cols(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes, const float* col_scales,
+                     cudaStream_t st, float qmax = 0.f) {
+  if ((rows & 31) || (cols & 31)) {
+    launch_transpose<MODE_FP8>(x, rows, cols, ld, fmt, codes, nullptr, 0, col_scales, nullptr, nullptr, st, qmax);
+    return;
+  }
+  dim3 grid((unsigned)((cols + kDT - 1) / kDT), (unsigned)((rows + kDT - 1) / kDT));
+  const bool wide = rows_32B_aligned(x, ld);
+#define B200Q_TILE(F)                                                                                                        \
+  do {                                                                                                                       \
+    if (wide) fp8_col_tile_quant_kernel<F, true><<<grid, kThreads, kDualSmem, st>>>(x, rows, cols, ld, col_scales, codes, qmax);      \
+    else fp8_col_tile_quant_kernel<F, false><<<grid, kThreads, kDualSmem, st>>>(x, rows, cols, ld, col_scales, codes, qmax);          \
+  } while (0)
+  if (fmt == FMT_I8) B200Q_TILE(FMT_I8);
+  else if (fmt == FMT_E4M3) B200Q_TILE(FMT_E4M3);
+  else B200Q_TILE(FMT_E5M2);
+#undef B200Q_TILE
 }
 
 }  // namespace
@@ -827,7 +914,7 @@ int b200q_quantize_fp8(const void* x, int64_t rows, int64_t cols, int64_t ld, in
   }
   amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, fmt, 0.f);
   B200Q_CUDA(cudaGetLastError());
-  launch_transpose<MODE_FP8>((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, nullptr, 0, scales, nullptr, nullptr, st);
+  launch_fp8_cols((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, scales, st);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -872,7 +959,7 @@ int b200q_quantize_fp8_both(const void* x, int64_t rows, int64_t cols, int64_t l
   // pass 2: column scales, then the transposed codes
   col_partials_to_scale_kernel<<<(unsigned)((cols / 2 + 31) / 32), 1024, 0, st>>>(parts, grid, cols, fmt, 0.f, scales_col);
   B200Q_CUDA(cudaGetLastError());
-  launch_transpose<MODE_FP8>(xp, rows, cols, ld, fmt, (uint8_t*)codes_col, nullptr, 0, scales_col, nullptr, nullptr, st);
+  launch_fp8_cols(xp, rows, cols, ld, fmt, (uint8_t*)codes_col, scales_col, st);     // the second read comes mostly from L2
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -900,8 +987,7 @@ int b200q_quantize_int8(const void* x, int64_t rows, int64_t cols, int64_t ld, i
   }
   amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, FMT_I8, (float)qmax);
   B200Q_CUDA(cudaGetLastError());
-  launch_transpose<MODE_FP8>((const uint16_t*)x, rows, cols, ld, FMT_I8, (uint8_t*)codes, nullptr, 0, scales, nullptr, nullptr, st,
-                             (float)qmax);
+  launch_fp8_cols((const uint16_t*)x, rows, cols, ld, FMT_I8, (uint8_t*)codes, scales, st, (float)qmax);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
