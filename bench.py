@@ -389,6 +389,7 @@ def run_moe_training(args, t, d, inter, rank, world, local):
     from oracle import restate as R
     from pretrain_b200 import build, ops
     from pretrain_b200.layers.mlp import _ExpertFFN
+    from pretrain_b200 import torch_ops as T
     if rank == 0:
         build.build()
     e, k = MOE_EXPERTS, MOE_TOPK
@@ -400,8 +401,7 @@ def run_moe_training(args, t, d, inter, rank, world, local):
     dout = torch.randn(t, d, device="cuda", dtype=torch.bfloat16)
 
     def step():
-        plan = ops.moe_permute_plan(top_i, e)
-        out = _ExpertFFN.apply(x, top_w, w_gu, w_d, plan)
+        out = _ExpertFFN.apply(x, top_w, w_gu, w_d, *T.moe_permute_plan(top_i, e))
         return torch.autograd.grad(out, (x, top_w, w_gu, w_d), dout)
 
     for _ in range(max(args.warmup, 3)):
@@ -447,7 +447,7 @@ def run_moe_training(args, t, d, inter, rank, world, local):
 
     def e2e_step():
         xx = hx.to("cuda", non_blocking=True).requires_grad_(True)
-        out = _ExpertFFN.apply(xx, top_w, w_gu, w_d, ops.moe_permute_plan(top_i, e))
+        out = _ExpertFFN.apply(xx, top_w, w_gu, w_d, *T.moe_permute_plan(top_i, e))
         (gx,) = torch.autograd.grad(out, (xx,), hd.to("cuda", non_blocking=True))
         hgx.copy_(gx, non_blocking=True)
 

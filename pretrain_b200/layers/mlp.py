@@ -17,6 +17,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from .. import torch_ops as T
 
 
 def silu_glu(gate, up):
@@ -43,7 +44,7 @@ def _trainable_shapes(d: int, inter: int) -> bool:
     return d % 128 == 0 and (2 * inter) % 128 == 0 and inter % 32 == 0
 
 
-E4M3, E5M2 = torch.float8_e4m3fn, torch.float8_e5m2
+E4M3, E5M2, SWZ = ops.E4M3, ops.E5M2, ops.SF_SWIZZLED
 
 
 class _ExpertFFN(torch.autograd.Function):
@@ -59,42 +60,43 @@ class _ExpertFFN(torch.autograd.Function):
               the `mxfp8` recipe."""
 
     @staticmethod
-    def forward(ctx, x, top_w, w_in, w_down, plan):
+    def forward(ctx, x, top_w, w_in, w_down, *plan_tensors):
+        plan = T.MoEPlan(*plan_tensors)
         t, d = x.shape
         e, n1, _ = w_in.shape
         inter = n1 // 2
         # every element-wise step hands its result to the both-directions quantizer inside one kernel
-        ar, asr, ac, asc = ops.moe_gather_quantize_dual(x, plan, E4M3)                         # (R, D) | (D, R), pad rows zero
-        w1r, w1sr, w1c, w1sc = ops.quantize_mxfp8_dual(w_in.reshape(e * n1, d), E4M3)       # (E*2I, D) | (D, E*2I)
-        w2r, w2sr, w2c, w2sc = ops.quantize_mxfp8_dual(w_down.reshape(e * d, inter), E4M3)  # (E*D, I)  | (I, E*D)
-        g = ops.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, n1)                       # (R, 2I) bf16, kept for backward
+        ar, asr, ac, asc = T.moe_gather_quantize_dual(x, plan, E4M3)                          # (R, D) | (D, R), pad rows zero
+        w1r, w1sr, w1c, w1sc = T.quantize_mxfp8_dual(w_in.reshape(e * n1, d), E4M3, SWZ)       # (E*2I, D) | (D, E*2I)
+        w2r, w2sr, w2c, w2sc = T.quantize_mxfp8_dual(w_down.reshape(e * d, inter), E4M3, SWZ)  # (E*D, I)  | (I, E*D)
+        g = T.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, n1)                        # (R, 2I) bf16, kept for backward
         if inter % 128 == 0:
-            hr, hsr, hc, hsc = ops.swiglu_quantize_dual(g, E4M3)
+            hr, hsr, hc, hsc = T.swiglu_quantize_dual(g, E4M3)
         else:
-            hr, hsr, hc, hsc = ops.quantize_mxfp8_dual(ops.swiglu(g, False), E4M3)
-        y = ops.grouped_gemm_mxfp8(hr, hsr, w2r, w2sr, plan, d)                        # (R, D) bf16
-        out = ops.moe_unpermute(y, top_w, plan.row_of, t)
-        ctx.save_for_backward(top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, y)
-        ctx.plan, ctx.shapes = plan, (t, d, e, inter, top_w.shape[1])
+            hr, hsr, hc, hsc = T.quantize_mxfp8_dual(T.swiglu(g), E4M3, SWZ)
+        y = T.grouped_gemm_mxfp8(hr, hsr, w2r, w2sr, plan, d)                         # (R, D) bf16
+        out = T.moe_unpermute(y, top_w, plan.row_of, t)
+        ctx.save_for_backward(top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, y, *plan_tensors)
+        ctx.shapes = (t, d, e, inter, top_w.shape[1])
         ctx.dtypes = (x.dtype, top_w.dtype, w_in.dtype, w_down.dtype)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, y = ctx.saved_tensors
-        plan = ctx.plan
+        top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, y, *plan_tensors = ctx.saved_tensors
+        plan = T.MoEPlan(*plan_tensors)
         t, d, e, inter, k = ctx.shapes
         dout = dout.reshape(t, d).to(torch.bfloat16)
-        dyr, dysr, dyc, dysc, dw = ops.moe_unpermute_backward_quantize_dual(                   # dw (T, k) fp32
-            dout, top_w, ops.moe_pair_of_row(plan), E5M2, y=y, row_of=plan.row_of)
-        dh = ops.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, plan, inter, E5M2, E4M3)       # (R, I)
-        dw2 = ops.grouped_gemm_mxfp8_wgrad(dyc, dysc, hc, hsc, plan, E5M2, E4M3)               # (E, D, I)
-        dgr, dgsr, dgc, dgsc = ops.swiglu_backward_quantize_dual(g, dh, E5M2)                  # of dg (R, 2I)
-        da = ops.grouped_gemm_mxfp8_dgrad(dgr, dgsr, w1c, w1sc, plan, d, E5M2, E4M3)           # (R, D)
-        dw1 = ops.grouped_gemm_mxfp8_wgrad(dgc, dgsc, ac, asc, plan, E5M2, E4M3)               # (E, 2I, D)
-        dx = ops.moe_unpermute(da, None, plan.row_of, t)                                         # sum over the k slots
+        dyr, dysr, dyc, dysc, dw = T.moe_unpermute_backward_quantize_dual(                      # dw (T, k) fp32
+            dout, top_w.to(torch.bfloat16), plan.row_of, plan.padded_rows, E5M2, y)
+        dh = T.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, plan, inter, E5M2, E4M3)         # (R, I)
+        dw2 = T.grouped_gemm_mxfp8_wgrad(dyc, dysc, hc, hsc, plan, E5M2, E4M3)                 # (E, D, I)
+        dgr, dgsr, dgc, dgsc = T.swiglu_backward_quantize_dual(g, dh, E5M2)                    # of dg (R, 2I)
+        da = T.grouped_gemm_mxfp8_dgrad(dgr, dgsr, w1c, w1sc, plan, d, E5M2, E4M3)             # (R, D)
+        dw1 = T.grouped_gemm_mxfp8_wgrad(dgc, dgsc, ac, asc, plan, E5M2, E4M3)                 # (E, 2I, D)
+        dx = T.moe_unpermute(da, None, plan.row_of, t)                                           # sum over the k slots
         xd, twd, w1d, w2d = ctx.dtypes
-        return dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d), None
+        return (dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d)) + (None,) * len(plan_tensors)
 
 
 def _quantize_expert_weights(w: torch.Tensor):
@@ -103,7 +105,7 @@ def _quantize_expert_weights(w: torch.Tensor):
     if n % 128:
         # scale-factor tiles hold 128 rows and must not straddle experts: pad every expert's rows
         w = torch.cat([w, w.new_zeros(e, 128 - n % 128, k)], dim=1)
-    return ops.quantize_mxfp8(w.reshape(-1, k), 1)
+    return T.quantize_mxfp8(w.reshape(-1, k), 1, E4M3, SWZ)
 
 
 def _expert_of_padded_row(plan) -> torch.Tensor:
@@ -129,19 +131,21 @@ def _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in=None, b_
     if gated and act_fn is silu_glu and b_in is None and n1 % 128 == 0:
         # SwiGLU and the re-quantization run in the first GEMM's epilogue: the weights are stored with
         # gate and up rows interleaved so that a thread of the epilogue holds a whole block of h
-        wq1, wsf1 = ops.quantize_mxfp8_rowmap(w_in.reshape(-1, w_in.shape[2]), _glu_row_map(e, n1 // 2, w_in.device))
-        hq, hsf = ops.grouped_gemm_mxfp8_swiglu(a, sfa, wq1, wsf1, plan, n1)
+        wq1, wsf1 = T.quantize_mxfp8_glu_rows(w_in.reshape(-1, w_in.shape[2]), e, n1 // 2)
+        hq, hsf = T.grouped_gemm_mxfp8_swiglu(a, sfa, wq1, wsf1, plan, n1)
     else:
         wq1, wsf1 = _quantize_expert_weights(w_in)
-        h = ops.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, wq1.shape[0] // e)[:, :n1]
+        h = T.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, wq1.shape[0] // e)[:, :n1]
         if b_in is not None:
             h = h + b_in.to(h.dtype)[_expert_of_padded_row(plan)]
         if gated and act_fn is silu_glu:
-            hq, hsf = ops.swiglu(h, True)                     # fused silu(gate)*up + MXFP8
+            hq, hsf = T.swiglu_mxfp8(h, E4M3)                 # fused silu(gate)*up + MXFP8
         else:
             act = act_fn(*h.chunk(2, dim=-1)) if gated else act_fn(h)
-            hq, hsf = ops.quantize_mxfp8(act.contiguous(), 1)
-    out = ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, wq2.shape[0] // e, out=out if n2 % 128 == 0 else None)[:, :n2]
+            hq, hsf = T.quantize_mxfp8(act.contiguous(), 1, E4M3, SWZ)
+    if out is not None and n2 % 128 == 0:       # straight into the caller's buffer (expert-parallel combine reads it in place)
+        return ops.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, wq2.shape[0] // e, out=out)
+    out = T.grouped_gemm_mxfp8(hq, hsf, wq2, wsf2, plan, wq2.shape[0] // e)[:, :n2]
     if b_down is not None:
         out = out + b_down.to(out.dtype)[_expert_of_padded_row(plan)]
     return out
@@ -161,8 +165,8 @@ def grouped_mlp(x, w_in, w_down, act_fn, offs, gated, row_expert_ids=None, b_in=
     r = x.shape[0]
     e = w_in.shape[0]
     x, w_in, w_down = x.to(torch.bfloat16), w_in.to(torch.bfloat16), w_down.to(torch.bfloat16)
-    plan = ops.moe_pad_plan(offs, r)
-    a, sfa = ops.moe_gather(x, plan, True)
+    plan = T.moe_pad_plan(offs, r)
+    a, sfa = T.moe_gather_mxfp8(x, plan)
     out_p = _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in, b_down)
     # back to the caller's unpadded row order
     rows = torch.arange(r, device=x.device)
@@ -210,6 +214,8 @@ class DenseMLPBlock(nn.Module):
         from ..quant.linear import QuantLinear
         from ..quant.utils import is_mxfp8, is_nvfp4
         if not (self.gated and self.act_fn is silu_glu and x.is_cuda and x.dtype == torch.bfloat16):
+            return None
+        if torch.compiler.is_compiling():        # the cached weight copies are Python-side state: the composition traces cleanly
             return None
         up, down = self.gate_up_proj, self.down_proj
         if not (isinstance(up, QuantLinear) and isinstance(down, QuantLinear)) or up.bias is not None or down.bias is not None:
@@ -296,7 +302,7 @@ class _RouterBackEnd(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, logits, k, score_name, normalize):
-        top_i, top_w, probs, _ = ops.moe_router_topk(logits, k, score_name, normalize, want_counts=False)
+        top_i, top_w, probs = T.moe_router_topk(logits.float().contiguous(), k, score_name, normalize)
         ctx.save_for_backward(logits, top_i)
         ctx.score_name, ctx.normalize = score_name, normalize
         ctx.mark_non_differentiable(top_i)
@@ -357,19 +363,19 @@ class SparseMoEBlock(nn.Module):
         top_indices, top_weights, router_probs = self.router(x_flat)
         w_in = self.expert_gate_up if self.gated else self.expert_up
         b_in = self.expert_gate_up_bias if self.gated else self.expert_up_bias
-        plan = ops.moe_permute_plan(top_indices, e)                        # stable sort by expert
+        plan = T.moe_permute_plan(top_indices, e)                          # stable sort by expert
         if _wants_grad(x, top_weights, w_in, self.expert_down, b_in, self.expert_down_bias):
             if not (self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None
                     and _trainable_shapes(d, w_in.shape[1] // 2)):
                 raise NotImplementedError("the backward of the MXFP8 expert path covers bias-free SwiGLU experts with "
                                           "d_model % 128 == 0 and intermediate_size % 64 == 0")
             out = _ExpertFFN.apply(x_flat.to(torch.bfloat16), top_weights, w_in.to(torch.bfloat16),
-                                   self.expert_down.to(torch.bfloat16), plan).to(x.dtype)
+                                   self.expert_down.to(torch.bfloat16), *plan).to(x.dtype)
         else:
-            a, sfa = ops.moe_gather(x_flat.to(torch.bfloat16), plan, True)    # permute fused with MXFP8
+            a, sfa = T.moe_gather_mxfp8(x_flat.to(torch.bfloat16), plan)      # permute fused with MXFP8
             y = _grouped_ffn_padded(a, sfa, plan, w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
                                     self.act_fn, self.gated, b_in, self.expert_down_bias)
-            out = ops.moe_unpermute(y, top_weights, plan.row_of, b * s).to(x.dtype)
+            out = T.moe_unpermute(y, top_weights.to(torch.bfloat16), plan.row_of, b * s).to(x.dtype)
 
         aux = None
         if self.aux_loss:

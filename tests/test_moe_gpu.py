@@ -448,6 +448,40 @@ def test_sparse_moe_block_trains(ops):
     assert all(torch.isfinite(p).all() for p in blk.parameters())
 
 
+@pytest.mark.parametrize("train", [True, False])
+def test_sparse_moe_block_traces_with_torch_compile(ops, train):
+    """The reference compiles the whole model (src/training/trainer.py:176-177): the block must trace without a
+    graph break, forward and backward, and give what it gives eagerly: the same kernels run, so the expert path is
+    bit-identical; the router's torch arithmetic is re-fused by the compiler and may round differently."""
+    from pretrain_b200.layers.mlp import SparseMoEBlock
+    torch.manual_seed(1)
+    d, inter, e, k, t = 256, 128, 8, 2, 512
+    blk = SparseMoEBlock(d, intermediate_size=inter, n_routed_experts=e, n_routed_experts_per_token=k, router_score_fn="sigmoid",
+                         aux_loss=True).cuda()
+    with torch.no_grad():
+        blk.expert_gate_up.normal_(std=0.05)
+        blk.expert_down.normal_(std=0.05)
+    compiled = torch.compile(blk, fullgraph=True)
+    coef = torch.randn(2, t // 2, d, device="cuda")
+
+    def run(fn):
+        x = torch.randn(2, t // 2, d, device="cuda", dtype=torch.bfloat16, generator=torch.Generator("cuda").manual_seed(5))
+        if not train:
+            with torch.no_grad():
+                out, aux = fn(x)
+            return out, aux
+        x.requires_grad_(True)
+        blk.zero_grad()
+        out, aux = fn(x)
+        ((out.float() * coef).sum() + aux.float()).backward()
+        return out, aux, x.grad, blk.expert_gate_up.grad.clone(), blk.expert_down.grad.clone(), blk.router.gate.weight.grad.clone()
+
+    eager, traced = run(blk), run(compiled)
+    assert torch.equal(eager[0], traced[0])
+    for a, b in zip(eager[1:], traced[1:]):
+        assert _rel(a.reshape(1, -1), b.reshape(1, -1)) < 2e-3
+
+
 def test_swiglu(ops):
     g = torch.Generator().manual_seed(0)
     h = (2.0 * torch.randn(384, 768, generator=g)).bfloat16().cuda()

@@ -292,3 +292,29 @@ def test_full_size_properties(ops):
     c1, sc1 = ops.quantize_fp8(x, E4, 1)
     c2, sc2 = ops.quantize_fp8(x.t().contiguous(), E4, 0)
     assert torch.equal(c1, c2) and torch.equal(sc1, sc2)
+
+
+def test_a_nan_stays_where_it_is(ops):
+    """Non-finite inputs are outside the reference's tests; what the kernels do with them is pinned here: a NaN
+    becomes a NaN code in place and takes part in no maximum, so every other code and every scale are those of the
+    same tensor with the NaN replaced by zero."""
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(64, 256, generator=g).bfloat16()
+    clean = x.clone()
+    x[3, 5] = float("nan")
+    clean[3, 5] = 0.0
+    is_nan = lambda codes, dt: codes.view(dt).float().isnan()
+    for dt in (E4, E5):
+        for fn in (lambda t: ops.quantize_fp8(t, dt, 1), lambda t: ops.quantize_mxfp8(t, 1, dt, 0)):
+            codes, scales = fn(x.cuda())
+            want, want_scales = fn(clean.cuda())
+            assert is_nan(codes[3, 5].cpu(), dt)
+            codes = codes.clone()
+            codes[3, 5] = want[3, 5]
+            assert torch.equal(codes, want) and torch.equal(scales.view(torch.uint8), want_scales.view(torch.uint8))
+        cr, sr, cc, sc = ops.quantize_mxfp8_dual(x.cuda(), dt, 0)
+        wr, wsr, wc, wsc = ops.quantize_mxfp8_dual(clean.cuda(), dt, 0)
+        assert is_nan(cr[3, 5].cpu(), dt) and is_nan(cc[5, 3].cpu(), dt)
+        cr, cc = cr.clone(), cc.clone()
+        cr[3, 5], cc[5, 3] = wr[3, 5], wc[5, 3]
+        assert torch.equal(cr, wr) and torch.equal(cc, wc) and torch.equal(sr, wsr) and torch.equal(sc, wsc)
