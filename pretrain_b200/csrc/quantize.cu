@@ -445,6 +445,26 @@ constexpr int kDPitch = kDT * 2 + 16;       // bytes per staged input row
 constexpr int kDOutPitch = kDT + 16;        // bytes per staged output row (= input column)
 constexpr int kDualSmem = kDT * kDPitch;     // the output staging tile reuses the input tile's memory
 
+// Steps the tile kernels share.  A thread's two columns x 32 rows of codes go to the staging tile
+// (row = column of the input), then the tile leaves as 128-byte rows of the transposed matrix.
+__device__ __forceinline__ void tile_park_columns(uint8_t* tout, int cp, int j, const uint32_t (&o0)[8], const uint32_t (&o1)[8]) {
+  uint4* d0 = reinterpret_cast<uint4*>(tout + (2 * cp) * kDOutPitch + 32 * j);
+  uint4* d1 = reinterpret_cast<uint4*>(tout + (2 * cp + 1) * kDOutPitch + 32 * j);
+  d0[0] = make_uint4(o0[0], o0[1], o0[2], o0[3]); d0[1] = make_uint4(o0[4], o0[5], o0[6], o0[7]);
+  d1[0] = make_uint4(o1[0], o1[1], o1[2], o1[3]); d1[1] = make_uint4(o1[4], o1[5], o1[6], o1[7]);
+}
+// `first_col` = the tile's first column in the output, `c0` / `width` = its position and limit in the part it belongs to
+__device__ __forceinline__ void tile_store_transposed(const uint8_t* tout, int tid, int64_t first_col, int64_t c0, int64_t width,
+                                                      int64_t r0, int64_t rows, uint8_t* __restrict__ codes_c) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int id = i * kThreads + tid, oc = id >> 3, ch = id & 7;
+    if (c0 + oc < width && r0 + ch * 16 < rows)
+      *reinterpret_cast<uint4*>(codes_c + (first_col + oc) * rows + r0 + ch * 16) =
+          *reinterpret_cast<const uint4*>(tout + oc * kDOutPitch + ch * 16);
+  }
+}
+
 // Where the tile kernel gets its values from: a matrix in memory, or one of the element-wise steps of
 // the MoE expert path computed on the fly, so that the bf16 tensor between that step and its two
 // MXFP8 copies never exists.
@@ -611,10 +631,7 @@ mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __r
       o0[i] = cvt_fp8x4(bf16lo(a), bf16lo(b), bf16lo(c), bf16lo(d), FMT);
       o1[i] = cvt_fp8x4(bf16hi(a), bf16hi(b), bf16hi(c), bf16hi(d), FMT);
     }
-    uint4* d0 = reinterpret_cast<uint4*>(tout + (2 * cp) * kDOutPitch + 32 * j);
-    uint4* d1 = reinterpret_cast<uint4*>(tout + (2 * cp + 1) * kDOutPitch + 32 * j);
-    d0[0] = make_uint4(o0[0], o0[1], o0[2], o0[3]); d0[1] = make_uint4(o0[4], o0[5], o0[6], o0[7]);
-    d1[0] = make_uint4(o1[0], o1[1], o1[2], o1[3]); d1[1] = make_uint4(o1[4], o1[5], o1[6], o1[7]);
+    tile_park_columns(tout, cp, j, o0, o1);
     const int64_t lc = c0 + 2 * cp, gc = t * width + lc, gr = r0 + 32 * j;
     if (gr < rows) {
       if (lc < width) sf_c[sf_offset(gc, gr >> 5, rows >> 5, swz)] = (uint8_t)(e0 + 127);
@@ -624,16 +641,7 @@ mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __r
   __syncthreads();
 
 #pragma unroll
-  for (int t = 0; t < NT; ++t) {
-    const uint8_t* tout = dual_smem + t * kDualSmem;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int id = i * kThreads + tid, oc = id >> 3, ch = id & 7;
-      if (c0 + oc < width && r0 + ch * 16 < rows)
-        *reinterpret_cast<uint4*>(codes_c + (t * width + c0 + oc) * rows + r0 + ch * 16) =
-            *reinterpret_cast<const uint4*>(tout + oc * kDOutPitch + ch * 16);
-    }
-  }
+  for (int t = 0; t < NT; ++t) tile_store_transposed(dual_smem + t * kDualSmem, tid, t * width + c0, c0, width, r0, rows, codes_c);
 }
 
 // dw[pair] = sum over the column tiles of the partial dot products of the pair's row (0 for a dropped pair).
@@ -718,20 +726,11 @@ fp8_col_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t 
       o1[i] = cvt_codes_x4(quot_for_cast(bf16hi(w[4 * i]), s1, rc1), quot_for_cast(bf16hi(w[4 * i + 1]), s1, rc1),
                            quot_for_cast(bf16hi(w[4 * i + 2]), s1, rc1), quot_for_cast(bf16hi(w[4 * i + 3]), s1, rc1), FMT, qmax);
     }
-    uint4* d0 = reinterpret_cast<uint4*>(tout + (2 * cp) * kDOutPitch + 32 * j);
-    uint4* d1 = reinterpret_cast<uint4*>(tout + (2 * cp + 1) * kDOutPitch + 32 * j);
-    d0[0] = make_uint4(o0[0], o0[1], o0[2], o0[3]); d0[1] = make_uint4(o0[4], o0[5], o0[6], o0[7]);
-    d1[0] = make_uint4(o1[0], o1[1], o1[2], o1[3]); d1[1] = make_uint4(o1[4], o1[5], o1[6], o1[7]);
+    tile_park_columns(tout, cp, j, o0, o1);
   }
   __syncthreads();
 
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int id = i * kThreads + tid, oc = id >> 3, ch = id & 7;
-    if (c0 + oc < cols && r0 + ch * 16 < rows)
-      *reinterpret_cast<uint4*>(codes_c + (c0 + oc) * rows + r0 + ch * 16) =
-          *reinterpret_cast<const uint4*>(tout + oc * kDOutPitch + ch * 16);
-  }
+  tile_store_transposed(tout, tid, c0, c0, cols, r0, rows, codes_c);
 }
 
 inline bool rows_32B_aligned(const void* p, int64_t ld) { return aligned32(p) && (ld & 15) == 0; }
