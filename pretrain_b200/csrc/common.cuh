@@ -34,6 +34,41 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Checks the current device is sm_10x (cached per device).
 int require_sm100();
 
+// Per-launch runtime queries that never change for a (kernel, device) pair, remembered per host thread:
+// the opt-in to more than 48 KB of dynamic shared memory and the occupancy of a kernel at a block size.
+struct KernelFact { const void* fn; int dev; int key; int value; };
+inline KernelFact* kernel_fact(const void* fn, int dev, int key) {
+  static thread_local KernelFact facts[128];
+  static thread_local int n = 0;
+  for (int i = 0; i < n; ++i)
+    if (facts[i].fn == fn && facts[i].dev == dev && facts[i].key == key) return &facts[i];
+  KernelFact* f = &facts[n < 128 ? n++ : 127];       // a full table recycles its last slot
+  *f = KernelFact{fn, dev, key, -1};
+  return f;
+}
+template <typename Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  KernelFact* f = kernel_fact(reinterpret_cast<const void*>(kernel), dev, -bytes);
+  if (f->value == 1) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) f->value = 1;
+  return e;
+}
+template <typename Kernel>
+inline int blocks_per_sm(Kernel kernel, int threads, int fallback) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fallback;
+  KernelFact* f = kernel_fact(reinterpret_cast<const void*>(kernel), dev, threads);
+  if (f->value < 1) {
+    int per_sm = 0;
+    f->value = (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) == cudaSuccess && per_sm >= 1) ? per_sm : fallback;
+  }
+  return f->value;
+}
+
 __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -470,7 +470,7 @@ int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t 
   p.sf_kt = (int)((nblk + 3) / 4);
   p.sf_kt_b = p.b_along_k ? p.sf_kt * p.n_experts : p.sf_kt;
   p.sfb_groups = (b_rows + 127) / 128;
-  B200Q_CUDA(cudaFuncSetAttribute(gemm_kernel<KIND, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  B200Q_CUDA(ensure_dynamic_smem(gemm_kernel<KIND, BN, EPI>, C::SMEM_BYTES));
   const int64_t tiles = (int64_t)p.num_m * p.num_n * (p.ragged_offs != nullptr ? p.n_experts : 1);
   const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
   gemm_kernel<KIND, BN, EPI><<<grid, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, md, p);

@@ -457,7 +457,7 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   p.num_k = (int)((row_bytes + BKB - 1) / BKB);
   p.sf_kt = sf_kt;
   p.glu = gp.glu;
-  B200Q_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  B200Q_CUDA(ensure_dynamic_smem(gemm_pair_kernel<KIND, EPI>, C::SMEM_BYTES));
   const int tiles = p.num_mp * p.num_n, pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
   gemm_pair_kernel<KIND, EPI><<<2 * pairs, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, msa, msb, md, p);
   B200Q_CUDA(cudaGetLastError());
@@ -510,7 +510,7 @@ int launch_pair_grouped(const void* A, const void* B, const OutSpec& D, int64_t 
   p.glu = gp.glu;
   p.tile_expert = gp.tile_expert; p.num_tiles = gp.num_tiles; p.num_m128 = (int)((gp.M + 127) / 128);
   p.ragged_offs = gp.ragged_offs; p.n_experts = gp.n_experts; p.b_along_k = gp.b_along_k; p.K = gp.K;
-  B200Q_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<KIND_MX, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  B200Q_CUDA(ensure_dynamic_smem(gemm_pair_kernel<KIND_MX, EPI, true>, C::SMEM_BYTES));
   // the pair-tile count of the expert forms is only known on the device: every pair of the GPU starts
   const int64_t tiles = ragged ? (int64_t)p.num_mp * p.num_n * gp.n_experts : (int64_t)(p.num_m128 + 1) / 2 * p.num_n;
   const int pairs = (int)(tiles < kNumSMs / 2 ? tiles : kNumSMs / 2);

@@ -665,7 +665,7 @@ int launch_mx_tile_quant(const TileSrc& src, bool aligned_src, int64_t rows, int
 #define B200Q_GO(F, W)                                                                                                  \
   do {                                                                                                                  \
     auto kernel = mx_tile_quant_kernel<F, W, SRC>;                                                                      \
-    B200Q_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, NT * kDualSmem));              \
+    B200Q_CUDA(ensure_dynamic_smem(kernel, NT * kDualSmem));                                                           \
     kernel<<<grid, kThreads, NT * kDualSmem, st>>>(src, rows, cols, codes_r, sf_r, codes_c, sf_c, swz);                 \
   } while (0)
   if (fmt == FMT_E4M3) { if (wide) B200Q_GO(FMT_E4M3, true); else B200Q_GO(FMT_E4M3, false); }
@@ -747,8 +747,7 @@ int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
 // warp gets the same share and there is no tail wave.  `per_cta` = items one CTA takes per pass.
 template <typename Kernel>
 int rowwise_grid(Kernel kernel, int64_t items, int per_cta) {
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+  const int per_sm = blocks_per_sm(kernel, kThreads, 4);
   const int64_t want = (items + per_cta - 1) / per_cta, cap = (int64_t)kNumSMs * per_sm;
   return (int)(want < cap ? want : cap);
 }

@@ -18,7 +18,13 @@ def fmt_of(dtype_or_fmt) -> int:
     return _FMT_OF_DTYPE.get(dtype_or_fmt, dtype_or_fmt)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """Handle of the current CUDA stream (the raw-handle query skips building a Stream object per launch)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -37,7 +43,10 @@ def _mat(x: torch.Tensor) -> torch.Tensor:
 
 
 def sf_bytes(outer: int, nblk: int, layout: int = SF_SWIZZLED) -> int:
-    return _lib.load().b200q_sf_bytes(outer, nblk, layout)
+    """b200q_sf_bytes without the foreign call: 512-byte tiles of 128 rows x 4 blocks, or one byte per block."""
+    if layout == SF_SWIZZLED:
+        return ((outer + 127) // 128) * ((nblk + 3) // 4) * 512
+    return outer * nblk
 
 
 def amax(x: torch.Tensor) -> torch.Tensor:

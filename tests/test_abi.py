@@ -43,6 +43,11 @@ def test_host_only_entry_points(lib_path):
     assert lib.b200q_sf_bytes(128, 4, 1) == 512
     assert lib.b200q_sf_bytes(129, 5, 1) == 2 * 2 * 512
     assert lib.b200q_sf_bytes(129, 5, 0) == 129 * 5
+    from pretrain_b200 import ops                       # the Python-side size formula is the library's
+    for outer in (1, 127, 128, 129, 4096):
+        for nblk in (1, 3, 4, 5, 257):
+            for layout in (0, 1):
+                assert ops.sf_bytes(outer, nblk, layout) == lib.b200q_sf_bytes(outer, nblk, layout)
     # argument validation happens before any CUDA call
     assert lib.b200q_amax(None, 4, 8, 8, None, None) == -1
     assert lib.b200q_quantize_mxfp8(ctypes.c_void_p(16), 4, 12, 16, 1, 0, ctypes.c_void_p(16), ctypes.c_void_p(16), 1, None) == -2
