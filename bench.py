@@ -223,6 +223,7 @@ def cpu_moe_sample(t, d, inter, ts=1024):
             "ms_per_step": dt * 1e3}
 
 
+
 def run_moe(args, t, d, inter, rank, world, local):
     """MoE block workload: one step = permute plan, gather fused with MXFP8, quantize both expert
     weight stacks, grouped GEMM with the SwiGLU + MXFP8 epilogue, grouped GEMM, weighted unpermute
@@ -822,7 +823,13 @@ def main():
     # ---- end to end through the public call, host buffers --------------------------------
     from pretrain_b200.quant.linear import _gemm
     fmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3", "int8": "int8"}[kind]
-    ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
+    # B is replicated over the ranks: with more than one rank each copies only ITS 1/world of B's rows from its
+    # host buffer and the ranks all-gather the rest over NVLink (NCCL), so the host link carries every input
+    # byte of the job once per step instead of B once per rank.
+    shard_b = dist is not None and n % world == 0
+    nb = n // world if shard_b else n
+    b_lo = rank * nb if shard_b else 0
+    ha, hb = a.cpu().pin_memory(), b[b_lo:b_lo + nb].cpu().pin_memory()
     hout = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
 
     # Three streams and two sets of device buffers: step i's host->device copy, step i-1's quantize + GEMM and
@@ -844,12 +851,14 @@ def main():
             ev_in[j].record()
         with torch.cuda.stream(s_in2):                  # the two operands travel on two streams
             s_in2.wait_event(ev_c[j])
-            db.copy_(hb, non_blocking=True)
+            db[b_lo:b_lo + nb].copy_(hb, non_blocking=True)
             ev_in2[j].record()
         with torch.cuda.stream(s_c):
             s_c.wait_event(ev_in[j])
             s_c.wait_event(ev_in2[j])
             s_c.wait_event(ev_out[j])                   # the result buffer has been read back
+            if shard_b:
+                dist.all_gather_into_tensor(db, db[b_lo:b_lo + nb])
             dd.copy_(_gemm(da, db.t(), fmt, fmt, torch.bfloat16, rowwise=True))
             ev_c[j].record()
         with torch.cuda.stream(s_out):
@@ -879,6 +888,8 @@ def main():
         e2e_ms = t.item()
     e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": ha.numel() * 2 + hb.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2}
+    if shard_b:
+        e2e["replicated_operand"] = "each rank copies 1/%d of B from host; ncclAllGather over NVLink completes it" % world
 
     # ---- output all-gather of the M-sharded layout (not on the data path; reported beside) --
     allgather = None
