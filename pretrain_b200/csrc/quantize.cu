@@ -941,7 +941,9 @@ int b200q_quantize_fp8_both(const void* x, int64_t rows, int64_t cols, int64_t l
   while (wpr < kWarps && nv > (int64_t)wpr * 32 * 4) wpr *= 2;
   const int64_t nvec = (nv + wpr * 32 - 1) / (wpr * 32);
   const int64_t rpc = kWarps / wpr, want = (rows + rpc - 1) / rpc;
-  const int grid = (int)(want < kColmaxParts ? want : kColmaxParts);
+  // one resident wave of the COLMAX kernel (64 registers: four CTAs per SM): half the partial rows to reduce afterwards
+  const int64_t wave = (int64_t)kNumSMs * 4;
+  const int grid = (int)(want < wave ? want : wave);
   const size_t smem = (size_t)rpc * cols * 2;          // packed bf16 column maxima of every row group
 #define B200Q_GO(NV, F)                                                                                                      \
   rowwise_fp8_kernel<NV, F, true><<<grid, kThreads, smem, st>>>(xp, rows, cols, ld, (uint8_t*)codes_row, scales_row, nullptr, nullptr, \
