@@ -930,6 +930,43 @@ def main():
         except Exception as ex:                       # symmetric memory not available on this system
             allgather["fused_error"] = str(ex)[:200]
 
+    # ---- data-parallel wgrad: dW = sum over ranks of dY_r^T . X_r, reduce-scattered by rows (not on the data path) ----
+    reduce_scatter = None
+    if dist is not None and kind == "mxfp8" and n % (32 * world) == 0:
+        try:
+            from pretrain_b200 import dist as D
+            e5, e4 = torch.float8_e5m2, torch.float8_e4m3fn
+            dy = (1e-2 * torch.randn(m, n, generator=g, device="cuda")).to(torch.bfloat16)
+            shard = torch.empty(n // world, k, device="cuda", dtype=torch.bfloat16)
+
+            def nccl_step():
+                gt, gtsf = ops.quantize_mxfp8(dy, 0, e5)
+                xt, xtsf = ops.quantize_mxfp8(a, 0, e4)
+                dist.reduce_scatter_tensor(shard, ops.gemm_mxfp8(gt, gtsf, xt, xtsf, e5, e4))
+
+            sc = D.ScatteredSum(n, k)
+            times = []
+            for fn in (nccl_step, lambda: D.wgrad_reduce_scatter_fused(dy, a, sc)):
+                for _ in range(3):
+                    fn()
+                barrier()
+                t0.record()
+                for _ in range(10):
+                    fn()
+                t1.record()
+                barrier()
+                t = torch.tensor([t0.elapsed_time(t1) / 10], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                times.append(t.item())
+            reduce_scatter = {"workload": "wgrad of the same shape per rank (2 transposing quantizations + GEMM), dW summed over ranks",
+                              "nccl_ms_per_step": times[0], "nccl_tflops": world * flops / (times[0] * 1e-3) / 1e12,
+                              "fused_ms_per_step": times[1], "fused_tflops": world * flops / (times[1] * 1e-3) / 1e12,
+                              "bytes_sent_per_rank": (world - 1) * (n // world) * k * 2,
+                              "fused": "GEMM epilogue stores each block into its owner's staging slot (symmetric memory, NVLink); "
+                                       "one kernel adds the slots"}
+        except Exception as ex:
+            reduce_scatter = {"error": str(ex)[:200]}
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -960,6 +997,8 @@ def main():
         line["cuda_graph"] = graph
     if allgather is not None:
         line["allgather"] = allgather
+    if reduce_scatter is not None:
+        line["reduce_scatter"] = reduce_scatter
     if world == 1 and not args.no_cpu_baseline:
         cb = run_cpu(kind, m, n, k, 2, 1)
         line["cpu_baseline"] = {k2: cb[k2] for k2 in ("value", "unit", "cores", "kind", "sample")}

@@ -175,6 +175,22 @@ int b200q_gemm_nvfp4_allgather(const void* A, const void* sfA, const void* B, co
                                const float* tsA, const float* tsB, int64_t M, int64_t N, int64_t K,
                                void* const* D_all, int world, int rank, int64_t ldd, void* stream);
 
+/* Fused GEMM + reduce-scatter, first half (new functionality: the data-parallel wgrad the reference, being
+ * single-GPU, never needs; src/quant/linear.py:102-109 is the GEMM).  Every rank computes its own [M, N]
+ * partial result (e.g. dW from its shard of the tokens); the sum over the ranks is wanted scattered by
+ * rows, rank g owning rows [g*M/world, (g+1)*M/world).  The epilogue stores every block (bf16) into THIS
+ * rank's slot of the OWNER's staging buffer: stage_all[g] is rank g's buffer, bf16 [world][M/world, N]
+ * with pitch ldd (local memory for g == rank, peer-mapped otherwise), slot = sender.  Only stores cross
+ * NVLink, tile by tile while the main loop runs.  After the ranks have synchronized, each owner adds
+ * its slots with b200q_sum_slots.  world <= 8, M % world == 0, (M / world) % 32 == 0. */
+int b200q_gemm_mxfp8_scatter(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
+                             const void* sfB, int64_t M, int64_t N, int64_t K, void* const* stage_all,
+                             int world, int rank, int64_t ldd, void* stream);
+/* out[r, c] = bf16(sum_s float(stage[s][r][c])), slots added in order in fp32, one rounding.
+ * stage bf16 [slots][rows, cols] pitch ld (slot stride rows * ld); cols % 8 == 0. */
+int b200q_sum_slots(const void* stage, int slots, int64_t rows, int64_t cols, int64_t ld, void* out,
+                    int64_t ldo, void* stream);
+
 /* ---- MoE: top-k permute, ragged grouped GEMM, SwiGLU, weighted unpermute ------------------
  * Layout used between these calls ("padded expert-sorted"): rows sorted by expert in the
  * reference's order (stable sort of the flattened (token, slot) pairs by expert id,

@@ -34,6 +34,8 @@ SIGNATURES = {
     "b200q_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_fp8_allgather": (_int, [_vp, _int, _vp, _int, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),
     "b200q_gemm_mxfp8_allgather": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),
+    "b200q_gemm_mxfp8_scatter": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),
+    "b200q_sum_slots": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_nvfp4_allgather": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),
     "b200q_moe_padded_rows": (_i64, [_i64, _int]),
     "b200q_moe_plan_workspace_bytes": (_i64, [_i64, _int]),

@@ -427,6 +427,7 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64
 struct OutSpec {
   void* ptr[kMaxOutputs];
   int count;
+  int64_t scatter_rows;    // > 0: output g is [scatter_rows, N] and receives the rows g * scatter_rows ... of the result
 };
 inline OutSpec one_output(void* D) {
   OutSpec o = {};
@@ -437,8 +438,10 @@ inline OutSpec one_output(void* D) {
 // output maps: bf16 [M, N] pitch ldd, box = 64 columns x 32 rows, 128-byte swizzle
 int make_out_maps(OutMaps* om, const OutSpec& outs, int64_t M, int64_t N, int64_t ldd) {
   om->count = outs.count;
+  om->scatter_rows = (int)outs.scatter_rows;
+  const int64_t map_rows = outs.scatter_rows > 0 ? outs.scatter_rows : M;
   for (int g = 0; g < outs.count; ++g) {
-    int rc = encode_2d(&om->m[g], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, outs.ptr[g], N, M, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    int rc = encode_2d(&om->m[g], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, outs.ptr[g], N, map_rows, ldd * 2, EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
   for (int g = outs.count; g < kMaxOutputs; ++g) om->m[g] = om->m[0];
@@ -458,7 +461,7 @@ int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t 
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, p.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, b_row_bytes, b_rows, b_row_bytes, BKB, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if (EPI != EPI_BF16) {
-    md.count = 0;                       // no TMA-stored output: the epilogue writes its results itself
+    md.count = 0; md.scatter_rows = 0;                       // no TMA-stored output: the epilogue writes its results itself
     for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
   } else if ((rc = make_out_maps(&md, D, m_out, p.N, ldd))) {
     return rc;
@@ -590,6 +593,41 @@ int gathered_outputs(OutSpec* o, void* const* d_all, int world, int rank, int64_
     o->ptr[i] = static_cast<uint8_t*>(base) + (size_t)rank * M * ldd * 2;
   }
   return B200Q_OK;
+}
+
+// Outputs of a GEMM whose result is summed over the ranks and scattered by rows: output g is this rank's slot
+// (rank-th block of rows_per_owner rows) in the staging buffer of rank g, which owns rows [g * rows_per_owner, ...).
+int scattered_outputs(OutSpec* o, void* const* stage_all, int world, int rank, int64_t M, int64_t ldd) {
+  if (stage_all == nullptr || world < 1 || world > kMaxOutputs || rank < 0 || rank >= world) return B200Q_ERR_INVALID_ARG;
+  if (M % world || (M / world) % 32) return B200Q_ERR_SHAPE;
+  *o = OutSpec{};
+  o->count = world;
+  o->scatter_rows = M / world;
+  for (int g = 0; g < world; ++g) {
+    if (stage_all[g] == nullptr) return B200Q_ERR_INVALID_ARG;
+    if (!aligned16(stage_all[g])) return B200Q_ERR_ALIGNMENT;
+    o->ptr[g] = static_cast<uint8_t*>(stage_all[g]) + (size_t)rank * o->scatter_rows * ldd * 2;
+  }
+  return B200Q_OK;
+}
+
+// out[r, c] = bf16(sum over the slots of float(stage[slot][r][c])), slots in order
+__global__ void __launch_bounds__(256)
+sum_slots_kernel(const uint16_t* __restrict__ stage, int slots, int64_t rows, int64_t cols, int64_t ld, uint16_t* __restrict__ out,
+                 int64_t ldo) {
+  const int64_t chunks = cols >> 3, total = rows * chunks;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / chunks, c = (i - r * chunks) << 3;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < slots; ++s) {
+      float f[8];
+      unpack8(ld_nc_v4(stage + ((int64_t)s * rows + r) * ld + c), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    *reinterpret_cast<uint4*>(out + r * ldo + c) =
+        make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+  }
 }
 
 int check_gemm(const void* A, const void* B, const void* D, int64_t M, int64_t N, int64_t K, int64_t ldd, int kmult) {
@@ -788,6 +826,33 @@ int b200q_gemm_mxfp8_allgather(const void* A, int a_fmt, const void* sfA, const 
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   p.M = M; p.N = N; p.K = K;
   return dispatch<KIND_MX>(A, B, outs, ldd, N, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_mxfp8_scatter(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
+                             int64_t N, int64_t K, void* const* stage_all, int world, int rank, int64_t ldd, void* stream) {
+  OutSpec outs;
+  int rc = scattered_outputs(&outs, stage_all, world, rank, M, ldd);
+  if (rc) return rc;
+  if ((rc = check_gemm(A, B, outs.ptr[0], M, N, K, ldd, 32))) return rc;
+  if (sfA == nullptr || sfB == nullptr || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.M = M; p.N = N; p.K = K;
+  return dispatch<KIND_MX>(A, B, outs, ldd, N, p, (cudaStream_t)stream);
+}
+
+int b200q_sum_slots(const void* stage, int slots, int64_t rows, int64_t cols, int64_t ld, void* out, int64_t ldo, void* stream) {
+  if (stage == nullptr || out == nullptr || slots < 1 || rows <= 0 || cols <= 0 || ld < cols || ldo < cols) return B200Q_ERR_INVALID_ARG;
+  if ((cols & 7) || (ld & 7) || (ldo & 7)) return B200Q_ERR_SHAPE;
+  if (!aligned16(stage) || !aligned16(out)) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  const int64_t want = (rows * (cols >> 3) + 255) / 256, cap = (int64_t)kNumSMs * 8;
+  sum_slots_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, (cudaStream_t)stream>>>(
+      (const uint16_t*)stage, slots, rows, cols, ld, (uint16_t*)out, ldo);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
 }
 
 int b200q_gemm_nvfp4_allgather(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,

@@ -433,7 +433,7 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, gp.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, gp.N, row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if (EPI != EPI_BF16) {
-    md.count = 0;                       // the SwiGLU epilogues write their results themselves
+    md.count = 0; md.scatter_rows = 0;                       // the SwiGLU epilogues write their results themselves
     for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
   } else if ((rc = make_out_maps(&md, D, gp.M, gp.N, ldd))) {
     return rc;
@@ -492,7 +492,7 @@ int launch_pair_grouped(const void* A, const void* B, const OutSpec& D, int64_t 
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, gp.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, b_row_bytes, b_rows, b_row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if (EPI != EPI_BF16) {
-    md.count = 0;
+    md.count = 0; md.scatter_rows = 0;
     for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
   } else if ((rc = make_out_maps(&md, D, m_out, gp.N, ldd))) {
     return rc;

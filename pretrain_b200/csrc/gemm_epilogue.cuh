@@ -12,10 +12,14 @@ constexpr int kEpiBytes1 = 4 * EPI_BLOCK_BYTES;      // one staging block per ep
 // Where a tile's blocks are stored: this GPU's output and, for the fused GEMM + all-gather, the
 // same rows of every peer's copy of the gathered output (peer-mapped device memory, written by
 // TMA stores over NVLink; stores only — nothing is ever loaded from a peer).
+// Scatter form (GEMM + reduce-scatter): output g holds only the rows [g * scatter_rows, (g + 1) * scatter_rows) of
+// the result - this rank's slot in the staging buffer of the rank that owns those rows - so every block goes to
+// exactly one output, the owner of its rows.
 constexpr int kMaxOutputs = 8;
 struct OutMaps {
   CUtensorMap m[kMaxOutputs];
   int count;
+  int scatter_rows;    // 0: every output receives every block; else a multiple of 32
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -71,8 +75,14 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t 
     ptx::fence_proxy_async();
     __syncwarp();
     if (lane == 0) {
-      for (int g = 0; g < outs->count; ++g)
-        ptx::tma_store_2d(&outs->m[g], (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
+      if (outs->scatter_rows > 0) {
+        const int owner = (int)(row0 / outs->scatter_rows);
+        ptx::tma_store_2d(&outs->m[owner], (int32_t)colg, (int32_t)(row0 - (int64_t)owner * outs->scatter_rows),
+                          epi_s + buf * EPI_BLOCK_BYTES);
+      } else {
+        for (int g = 0; g < outs->count; ++g)
+          ptx::tma_store_2d(&outs->m[g], (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
+      }
       ptx::bulk_commit();
     }
     buf = (buf + 1) % EPI_BUFS;

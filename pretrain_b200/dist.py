@@ -110,6 +110,52 @@ def sharded_gemm_fused(a_shard: torch.Tensor, w: torch.Tensor, fmt: str, out: Ga
     return out.buf
 
 
+class ScatteredSum:
+    """Staging for a GEMM whose (rows, cols) result is summed over the ranks and scattered by rows
+    (reduce-scatter), as symmetric memory: rank g owns rows [g * rows / world, ...) and keeps one slot
+    per sender; the senders' GEMM epilogues store their blocks of those rows straight into their slot
+    over NVLink.  Two staging buffers alternate, so a rank that runs ahead writes the buffer its
+    peers are not reading; one rendezvous per call orders everything else."""
+
+    def __init__(self, rows: int, cols: int, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if rows % self.world or (rows // self.world) % 32 or cols % 8:
+            raise ValueError("rows must split into multiples of 32 per rank and cols be a multiple of 8")
+        self.rows, self.cols = rows, cols
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.bufs, self.ptrs = [], []
+        for _ in range(2):
+            buf = symm.empty((self.world, rows // self.world, cols), dtype=torch.bfloat16, device=dev)
+            handle = symm.rendezvous(buf, self.group)
+            self.bufs.append(buf)
+            self.ptrs.append([int(p) for p in handle.buffer_ptrs])
+        self._flag = torch.zeros(1, device=dev)
+        self._turn = 0
+
+    def sync(self) -> None:
+        dist.all_reduce(self._flag, group=self.group)
+
+
+def wgrad_reduce_scatter_fused(dy_shard: torch.Tensor, x_shard: torch.Tensor, out: ScatteredSum) -> torch.Tensor:
+    """Data-parallel weight gradient of a linear layer in MXFP8: every rank holds its shard of the tokens
+    (dy_shard (m, n) output gradients, x_shard (m, k) inputs, m % 32 == 0); returns this rank's rows
+    [rank * n / world, ...) of dW = sum over ranks of dy_shard.T @ x_shard, bf16 (n / world, k).  The GEMM is the
+    wgrad of QuantizedLinearFn (E5M2 gradients x E4M3 activations, blocks along the tokens,
+    src/quant/linear.py:102-109); its epilogue does the scatter, a small kernel the sum."""
+    from . import ops
+    if dy_shard.shape[1] != out.rows or x_shard.shape[1] != out.cols or dy_shard.shape[0] != x_shard.shape[0]:
+        raise ValueError("shards do not match the staged (n, k) result")
+    gt, gtsf = ops.quantize_mxfp8(dy_shard, 0, torch.float8_e5m2)           # (n, m): blocks along the tokens
+    xt, xtsf = ops.quantize_mxfp8(x_shard, 0, torch.float8_e4m3fn)          # (k, m)
+    turn = out._turn
+    out._turn ^= 1
+    ops.gemm_mxfp8_scatter(gt, gtsf, xt, xtsf, out.ptrs[turn], out.rank, out.cols, out.cols, torch.float8_e5m2, torch.float8_e4m3fn)
+    out.sync()
+    return ops.sum_slots(out.bufs[turn])
+
+
 # ---- expert parallelism ---------------------------------------------------------------------
 
 @dataclass

@@ -279,6 +279,25 @@ def gemm_mxfp8_allgather(a_codes, a_sf, b_codes, b_sf, out_ptrs, rank: int, n: i
                                                       len(out_ptrs), rank, ldd, _stream()), "b200q_gemm_mxfp8_allgather")
 
 
+def gemm_mxfp8_scatter(a_codes, a_sf, b_codes, b_sf, stage_ptrs, rank: int, n: int, ldd: int, a_fmt=E4M3, b_fmt=E4M3):
+    """First half of a fused GEMM + reduce-scatter: block rows [g*M/world, ...) of this rank's (M, n) partial result go
+    to slot `rank` of rank g's staging buffer (`stage_ptrs`: device pointers of the ranks' [world, M/world, n] buffers)."""
+    m, k = a_codes.shape
+    _lib.check(_lib.load().b200q_gemm_mxfp8_scatter(a_codes.data_ptr(), fmt_of(a_fmt), a_sf.data_ptr(), b_codes.data_ptr(),
+                                                    fmt_of(b_fmt), b_sf.data_ptr(), m, n, k, _ptr_array(stage_ptrs),
+                                                    len(stage_ptrs), rank, ldd, _stream()), "b200q_gemm_mxfp8_scatter")
+
+
+def sum_slots(stage: torch.Tensor) -> torch.Tensor:
+    """(slots, rows, cols) bf16 -> (rows, cols) bf16: the slots added in order in fp32, one rounding."""
+    slots, rows, cols = stage.shape
+    if stage.dtype != torch.bfloat16 or not stage.is_contiguous():
+        raise ValueError("expected a contiguous bf16 (slots, rows, cols) tensor")
+    out = torch.empty(rows, cols, dtype=torch.bfloat16, device=stage.device)
+    _lib.check(_lib.load().b200q_sum_slots(stage.data_ptr(), slots, rows, cols, cols, out.data_ptr(), cols, _stream()), "b200q_sum_slots")
+    return out
+
+
 def gemm_nvfp4_allgather(a_packed, a_sf, a_ts, b_packed, b_sf, b_ts, out_ptrs, rank: int, n: int, ldd: int):
     m, k2 = a_packed.shape
     _lib.check(_lib.load().b200q_gemm_nvfp4_allgather(a_packed.data_ptr(), a_sf.data_ptr(), b_packed.data_ptr(), b_sf.data_ptr(),

@@ -292,3 +292,34 @@ def test_large_square_linearity(ops):
     out4 = ops.gemm_nvfp4(pa, sa4, ta, pb, sb4, tb)
     ref4 = G.matmul_fp32(G.deq_nvfp4(pa, sa4, ta)[rows], G.deq_nvfp4(pb, sb4, tb))
     _check(out4[rows], ref4)
+
+
+@pytest.mark.parametrize("pair", [-1, 1])
+def test_scatter_epilogue_and_slot_sum_on_one_gpu(ops, pair):
+    """The reduce-scatter form with both "ranks" played in turn on one GPU (no kernel waits on another): every rank's
+    partial product lands in its slot of the owner's staging buffer, and the slot sum is the fp32 sum of the bf16
+    partials rounded once."""
+    from pretrain_b200 import _lib
+    world, m, n, k = 2, 512, 384, 256            # result (m, n), contraction k; owner g holds rows [g * 256, ...)
+    g = torch.Generator().manual_seed(3)
+    stage = [torch.full((world, m // world, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ptrs = [t.data_ptr() for t in stage]
+    parts = []
+    _lib.load().b200q_debug_set_gemm_pair(pair)
+    try:
+        for rank in range(world):
+            a = torch.randn(m, k, generator=g).bfloat16().cuda()
+            b = torch.randn(n, k, generator=g).bfloat16().cuda()
+            ca, sa = ops.quantize_mxfp8(a, 1)
+            cb, sb = ops.quantize_mxfp8(b, 1)
+            ops.gemm_mxfp8_scatter(ca, sa, cb, sb, ptrs, rank, n, n)
+            parts.append(ops.gemm_mxfp8(ca, sa, cb, sb))
+        ops.device_status()
+    finally:
+        _lib.load().b200q_debug_set_gemm_pair(0)
+    for owner in range(world):
+        rows = slice(owner * (m // world), (owner + 1) * (m // world))
+        for rank in range(world):
+            assert torch.equal(stage[owner][rank], parts[rank][rows])
+        want = torch.stack([p[rows].float() for p in parts]).sum(0).bfloat16()
+        assert torch.equal(ops.sum_slots(stage[owner]), want)

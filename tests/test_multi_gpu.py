@@ -87,6 +87,38 @@ def test_fused_gemm_allgather_equals_nccl_allgather(fmt):
     _run(_fused_rank, 2, fmt)
 
 
+def _wgrad_rs_rank(rank, world):
+    from pretrain_b200 import dist as D, ops
+    m, n, k = 1024, 1536, 1024                  # tokens per rank, out features, in features
+    g = torch.Generator().manual_seed(10 + rank)
+    dy = (1e-2 * torch.randn(m, n, generator=g)).bfloat16().cuda()
+    x = torch.randn(m, k, generator=g).bfloat16().cuda()
+    out = D.ScatteredSum(n, k)
+    for _ in range(3):                          # the staging buffers alternate and are reused
+        dw = D.wgrad_reduce_scatter_fused(dy, x, out)
+    # the same partial GEMM without the scatter, then the ranks' partials added in fp32 in rank order
+    gt, gtsf = ops.quantize_mxfp8(dy, 0, torch.float8_e5m2)
+    xt, xtsf = ops.quantize_mxfp8(x, 0, torch.float8_e4m3fn)
+    part = ops.gemm_mxfp8(gt, gtsf, xt, xtsf, torch.float8_e5m2, torch.float8_e4m3fn)      # (n, k) bf16
+    parts = [torch.empty_like(part) for _ in range(world)]
+    dist.all_gather(parts, part)
+    rows = n // world
+    want = torch.stack([p[rank * rows:(rank + 1) * rows].float() for p in parts]).sum(0).bfloat16()
+    torch.cuda.synchronize()
+    assert dw.shape == (rows, k) and torch.equal(dw, want)
+    # ... and against the unquantized gradient of the whole batch
+    full_dy, full_x = [torch.empty_like(dy) for _ in range(world)], [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(full_dy, dy)
+    dist.all_gather(full_x, x)
+    ref = (torch.cat(full_dy).float().t() @ torch.cat(full_x).float())[rank * rows:(rank + 1) * rows]
+    assert ((dw.float() - ref).norm() / ref.norm()).item() < 6e-2        # E5M2 gradients x E4M3 activations
+    ops.device_status()
+
+
+def test_fused_wgrad_reduce_scatter_equals_sum_of_partials():
+    _run(_wgrad_rs_rank, 2)
+
+
 def _ep_rank(rank, world):
     from pretrain_b200 import dist as D, ops
     from pretrain_b200.layers.mlp import _grouped_ffn_padded, silu_glu
