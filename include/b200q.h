@@ -387,10 +387,12 @@ int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y,
  * fp32 logits [T, E]; the k largest probs per token in descending order -> top_idx (int64 [T, k]);
  * their probs, divided by (their sum + 1e-9) when normalize != 0, -> top_w (bf16 [T, k]); probs as
  * bf16 [T, E] (optional); expert_counts[e] = tokens that chose e (int32 [E], optional).  Equal
- * probs are ordered by logit, then by expert index.  E <= 256, k <= 32. */
+ * probs are ordered by logit, then by expert index.  select_bias (fp32 [E], optional): the experts are
+ * chosen by prob + select_bias, the load-balancing bias of src/layers/mlp.py:182-216,295-297, while the
+ * weights stay the chosen experts' probs.  E <= 256, k <= 32. */
 int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int score_fn, int normalize,
                           int64_t* top_idx, void* top_w, void* probs, int32_t* expert_counts,
-                          void* stream);
+                          const float* select_bias, void* stream);
 
 /* Weighted unpermute (src/layers/mlp.py:472-477): out[t, :] = sum_j w[t, j] * y[row_of[t*k+j], :],
  * accumulated in fp32 and rounded once to bf16.  y bf16 [padded_rows, D] pitch ldy; w bf16 [T, k], or

@@ -64,7 +64,7 @@ SIGNATURES = {
     "b200q_moe_combine_peers": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _i64, _int, _i64, _vp, _vp]),
     "b200q_swiglu_backward": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
     "b200q_moe_unpermute_backward": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _int, _i64, _i64, _vp, _vp, _vp]),
-    "b200q_moe_router_topk": (_int, [_vp, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_moe_router_topk": (_int, [_vp, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_unpermute": (_int, [_vp, _i64, _vp, _vp, _i64, _int, _i64, _vp, _vp]),
     "b200q_moe_pair_of_row": (_int, [_vp, _i64, _i64, _vp, _vp]),
 }

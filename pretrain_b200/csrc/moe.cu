@@ -321,11 +321,13 @@ swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t l
 // l, l + 32, ... (E <= 256).
 // PER = experts per lane (1, 2, 4 or 8: the smallest that covers E), a template argument so that the
 // loops over a lane's experts have no idle iterations.
-template <int PER>
+// BIAS: the k experts are chosen by prob + select_bias[e] (load-balancing bias, selection only); the
+// weights are still the probs of the chosen experts.
+template <int PER, bool BIAS>
 __global__ void __launch_bounds__(256)
 moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k, int sigmoid, int normalize,
                        int64_t* __restrict__ top_idx, uint16_t* __restrict__ top_w, uint16_t* __restrict__ probs_out,
-                       int32_t* __restrict__ counts) {
+                       int32_t* __restrict__ counts, const float* __restrict__ select_bias) {
   __shared__ int hist[kMaxExperts];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < E; i += 256) hist[i] = 0;
@@ -365,16 +367,27 @@ moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k
         if (j < per && e < E) probs_out[t * E + e] = __bfloat16_as_ushort(__float2bfloat16_rn(p[j]));
       }
     }
-    // k rounds of warp arg-max; a taken entry drops to -2 (below every prob and the -1 of absent experts)
+    // selection key: the prob, or prob + bias; absent experts stay below every key
+    float key[BIAS ? kRouterMaxPerLane : 1];
+    if (BIAS) {
+#pragma unroll
+      for (int j = 0; j < kRouterMaxPerLane; ++j) {
+        const int e = j * 32 + lane;
+        key[j] = (j < per && e < E) ? p[j] + select_bias[e] : -INFINITY;
+      }
+    }
+    // k rounds of warp arg-max; a taken entry drops below every key (-2 under the probs and the -1 of absent
+    // experts; -infinity under biased keys)
     float wsum = 0.f, mine = 0.f;   // lane j keeps the j-th weight
     int mine_idx = 0;
     for (int r = 0; r < k; ++r) {
-      float bp = -3.f, bv = -INFINITY;
+      float bp = BIAS ? -INFINITY : -3.f, bv = -INFINITY;
       int be = 0x7FFFFFFF;
 #pragma unroll
       for (int j = 0; j < kRouterMaxPerLane; ++j) {
         const int e = j * 32 + lane;
-        if (p[j] > bp || (p[j] == bp && (v[j] > bv || (v[j] == bv && e < be)))) { bp = p[j]; bv = v[j]; be = e; }
+        const float kj = BIAS ? key[j] : p[j];
+        if (kj > bp || (kj == bp && (v[j] > bv || (v[j] == bv && e < be)))) { bp = kj; bv = v[j]; be = e; }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
@@ -382,13 +395,23 @@ moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k
         const int oe = __shfl_xor_sync(0xFFFFFFFFu, be, o);
         if (op > bp || (op == bp && (ov > bv || (ov == bv && oe < be)))) { bp = op; bv = ov; be = oe; }
       }
+      float wp = bp;                                   // the weight: the chosen expert's prob
+      if (BIAS) {
+        float own = 0.f;
+#pragma unroll
+        for (int j = 0; j < kRouterMaxPerLane; ++j)
+          if (j == (be >> 5)) own = p[j];
+        wp = __shfl_sync(0xFFFFFFFFu, own, be & 31);
+      }
       if ((be & 31) == lane) {                         // selects over the PER registers, no local memory
 #pragma unroll
         for (int j = 0; j < kRouterMaxPerLane; ++j)
-          if (j == (be >> 5)) p[j] = -2.f;
+          if (j == (be >> 5)) {
+            if (BIAS) key[j] = -INFINITY; else p[j] = -2.f;
+          }
       }
-      wsum += bp;
-      if (lane == r) { mine = bp; mine_idx = be; }
+      wsum += wp;
+      if (lane == r) { mine = wp; mine_idx = be; }
     }
     if (lane < k) {
       const float w = normalize ? mine / (wsum + 1e-9f) : mine;
@@ -824,7 +847,7 @@ int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y,
 }
 
 int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int score_fn, int normalize, int64_t* top_idx,
-                          void* top_w, void* probs, int32_t* expert_counts, void* stream) {
+                          void* top_w, void* probs, int32_t* expert_counts, const float* select_bias, void* stream) {
   if (logits == nullptr || top_idx == nullptr || top_w == nullptr || T <= 0 || E <= 0 || k <= 0 || (score_fn != 0 && score_fn != 1))
     return B200Q_ERR_INVALID_ARG;
   if (E > kMaxExperts || k > 32 || k > E) return B200Q_ERR_SHAPE;
@@ -832,9 +855,15 @@ int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int scor
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (expert_counts != nullptr) B200Q_CUDA(cudaMemsetAsync(expert_counts, 0, (size_t)E * sizeof(int32_t), st));
-#define B200Q_GO(P) \
-  moe_router_topk_kernel<P><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, (uint16_t*)top_w, \
-                                                         (uint16_t*)probs, expert_counts)
+#define B200Q_GO(P)                                                                                                          \
+  do {                                                                                                                       \
+    if (select_bias != nullptr)                                                                                              \
+      moe_router_topk_kernel<P, true><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, (uint16_t*)top_w,   \
+                                                                   (uint16_t*)probs, expert_counts, select_bias);            \
+    else                                                                                                                     \
+      moe_router_topk_kernel<P, false><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, (uint16_t*)top_w,  \
+                                                                    (uint16_t*)probs, expert_counts, nullptr);               \
+  } while (0)
   if (E <= 32) B200Q_GO(1);
   else if (E <= 64) B200Q_GO(2);
   else if (E <= 128) B200Q_GO(4);

@@ -261,6 +261,51 @@ class DenseMLPBlock(nn.Module):
         return self.dropout(out.reshape(*x.shape[:-1], out.shape[-1])), None
 
 
+class ExpertBias(nn.Module):
+    """Auxiliary-loss-free load-balancing bias (src/layers/mlp.py:182-216): added to the gating scores for the
+    top-k selection only, nudged toward uniform load by a fixed-rate sign rule; an fp32 buffer, not a parameter."""
+
+    def __init__(self, n_experts: int, update_rate: float = 0.001):
+        super().__init__()
+        self.update_rate = update_rate
+        self.register_buffer("bias", torch.zeros(n_experts))
+
+    def _apply(self, fn, recurse=True):
+        result = super()._apply(fn, recurse)
+        if self.bias.dtype != torch.float32:
+            self.bias = self.bias.float()
+        return result
+
+    def forward(self, scores):
+        return scores + self.bias
+
+    @torch.no_grad()
+    def update(self, expert_counts):
+        err = expert_counts.float().mean() - expert_counts.float()
+        self.bias += self.update_rate * err.sign()
+
+
+class ExpertLoad(nn.Module):
+    """Tokens per expert seen in training (accumulated) and in the last evaluation pass (src/layers/mlp.py:219-239)."""
+
+    def __init__(self, n_experts: int):
+        super().__init__()
+        self.register_buffer("train_load", torch.zeros(n_experts, dtype=torch.long), persistent=False)
+        self.register_buffer("eval_load", torch.zeros(n_experts, dtype=torch.long), persistent=False)
+
+    def record_load(self, counts, training: bool) -> None:
+        if training:
+            self.train_load += counts
+        else:
+            self.eval_load.copy_(counts)
+
+    def reset_train_load(self) -> None:
+        self.train_load.zero_()
+
+    def reset_eval_load(self) -> None:
+        self.eval_load.zero_()
+
+
 class MoERouter(nn.Module):
     """Top-k router with an fp32-pinned gate (src/layers/mlp.py:248-302): fp32 logits, score
     function, top-k, weights normalised by their sum + 1e-9."""
@@ -268,14 +313,18 @@ class MoERouter(nn.Module):
     def __init__(self, d_model, n_routed_experts, n_routed_experts_per_token, normalize=True, expert_bias=False,
                  expert_bias_update_rate=0.001, router_score_fn="sigmoid"):
         super().__init__()
-        if expert_bias:
-            raise NotImplementedError("expert-bias load balancing is not part of this build's path")
         self.n_routed_experts = n_routed_experts
         self.n_routed_experts_per_token = n_routed_experts_per_token
         self.normalize = normalize
         self.score_fn = MOE_ROUTER_SCORE_FNS[router_score_fn]
         self.score_name = router_score_fn
         self.gate = nn.Linear(d_model, n_routed_experts, bias=False)
+        self.expert_bias = ExpertBias(n_routed_experts, expert_bias_update_rate) if expert_bias else None
+
+    def update_expert_bias(self, expert_counts):
+        """Nudge the load-balancing bias toward uniform load; no-op without one."""
+        if self.expert_bias is not None:
+            self.expert_bias.update(expert_counts)
 
     def _apply(self, fn, recurse=True):
         result = super()._apply(fn, recurse)
@@ -287,10 +336,15 @@ class MoERouter(nn.Module):
         with torch.amp.autocast(device_type=x.device.type, enabled=False):
             logits = self.gate(x.float())                  # the fp32 gate GEMM stays the reference's own op
         if x.is_cuda and x.dtype == torch.bfloat16 and self.n_routed_experts <= 256:
-            top_i, top_w, probs = _RouterBackEnd.apply(logits, self.n_routed_experts_per_token, self.score_name, self.normalize)
+            bias = self.expert_bias.bias if self.expert_bias is not None else None
+            top_i, top_w, probs = _RouterBackEnd.apply(logits, self.n_routed_experts_per_token, self.score_name, self.normalize, bias)
             return top_i, top_w, probs
         probs = self.score_fn(logits)
-        top_w, top_i = torch.topk(probs, self.n_routed_experts_per_token, dim=-1)
+        if self.expert_bias is not None:
+            top_i = torch.topk(self.expert_bias(probs), self.n_routed_experts_per_token, dim=-1).indices
+            top_w = probs.gather(-1, top_i)
+        else:
+            top_w, top_i = torch.topk(probs, self.n_routed_experts_per_token, dim=-1)
         if self.normalize:
             top_w = top_w / (top_w.sum(-1, keepdim=True) + 1e-9)
         return top_i, top_w.to(x.dtype), probs.to(x.dtype)
@@ -301,8 +355,8 @@ class _RouterBackEnd(torch.autograd.Function):
     (b200q_moe_router_topk); the backward is the closed form of those steps on the (T, E) tensors."""
 
     @staticmethod
-    def forward(ctx, logits, k, score_name, normalize):
-        top_i, top_w, probs = T.moe_router_topk(logits.float().contiguous(), k, score_name, normalize)
+    def forward(ctx, logits, k, score_name, normalize, select_bias=None):
+        top_i, top_w, probs = T.moe_router_topk(logits.float().contiguous(), k, score_name, normalize, select_bias)
         ctx.save_for_backward(logits, top_i)
         ctx.score_name, ctx.normalize = score_name, normalize
         ctx.mark_non_differentiable(top_i)
@@ -326,7 +380,7 @@ class _RouterBackEnd(torch.autograd.Function):
             dlogits = p * (dp - (dp * p).sum(-1, keepdim=True))
         else:
             dlogits = dp * p * (1 - p)
-        return dlogits, None, None, None
+        return dlogits, None, None, None, None
 
 
 class SparseMoEBlock(nn.Module):
@@ -340,9 +394,11 @@ class SparseMoEBlock(nn.Module):
         super().__init__()
         if aux_loss and expert_bias:
             raise ValueError("aux_loss and expert_bias are mutually exclusive MoE balancing strategies")
-        if n_shared_experts or dropout:
-            raise NotImplementedError("shared experts and expert dropout are outside this build's path")
+        if dropout:
+            raise NotImplementedError("expert dropout is outside this build's path (the unpermute kernel applies the weights)")
         self.n_routed_experts = n_routed_experts
+        self.n_shared_experts = n_shared_experts
+        self.expert_bias, self.expert_bias_update_rate = expert_bias, expert_bias_update_rate
         self.n_routed_experts_per_token = n_routed_experts_per_token
         self.aux_loss, self.aux_loss_coef = aux_loss, aux_loss_coef
         self.router_score_fn, self.gated = router_score_fn, gated
@@ -355,6 +411,16 @@ class SparseMoEBlock(nn.Module):
         setattr(self, name + "_bias", nn.Parameter(torch.zeros(n_routed_experts, width)) if bias else None)
         self.expert_down = nn.Parameter(torch.empty(n_routed_experts, d_model, intermediate_size))
         self.expert_down_bias = nn.Parameter(torch.zeros(n_routed_experts, d_model)) if bias else None
+        # DeepSeekMoE shared experts: one always-on dense block of width n_shared_experts * intermediate_size
+        self.shared_expert = (DenseMLPBlock(d_model, intermediate_size=n_shared_experts * intermediate_size, activation=activation,
+                                            gated=gated, bias=bias) if n_shared_experts > 0 else None)
+        self.expert_load = ExpertLoad(n_routed_experts)
+
+    @torch.no_grad()
+    def post_step(self):
+        if self.expert_bias:
+            self.router.update_expert_bias(self.expert_load.train_load)
+            self.expert_load.reset_train_load()
 
     def forward(self, x):
         b, s, d = x.shape
@@ -377,12 +443,16 @@ class SparseMoEBlock(nn.Module):
                                     self.act_fn, self.gated, b_in, self.expert_down_bias)
             out = T.moe_unpermute(y, top_weights.to(torch.bfloat16), plan.row_of, b * s).to(x.dtype)
 
+        counts = torch.diff(plan.offs, prepend=plan.offs.new_zeros(1))
+        self.expert_load.record_load(counts.detach(), self.training)
         aux = None
         if self.aux_loss:
-            counts = torch.diff(plan.offs, prepend=plan.offs.new_zeros(1))
             f = counts.to(x.dtype) / (b * s)
             probs = router_probs
             if self.router_score_fn == "sigmoid":
                 probs = probs / (probs.sum(-1, keepdim=True) + 1e-9)
             aux = self.aux_loss_coef * e * (f * probs.mean(0)).sum()
-        return out.view(b, s, d), aux
+        out = out.view(b, s, d)
+        if self.shared_expert is not None:
+            out = out + self.shared_expert(x)[0]
+        return out, aux

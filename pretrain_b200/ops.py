@@ -603,7 +603,7 @@ def moe_unpermute_backward(dout: torch.Tensor, weights: torch.Tensor, y: torch.T
 
 
 def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str = "softmax", normalize: bool = True, want_probs: bool = True,
-                    want_counts: bool = True):
+                    want_counts: bool = True, select_bias: torch.Tensor | None = None):
     """fp32 logits (T, E) -> (top_idx int64 (T, k), top_w bf16 (T, k), probs bf16 (T, E) | None,
     expert_counts int32 (E) | None): score function, top-k, normalisation, casts and histogram in one launch."""
     if not logits.is_cuda:
@@ -614,9 +614,13 @@ def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str = "softmax", nor
     w = torch.empty(t, k, dtype=torch.bfloat16, device=logits.device)
     probs = torch.empty(t, e, dtype=torch.bfloat16, device=logits.device) if want_probs else None
     counts = torch.empty(e, dtype=torch.int32, device=logits.device) if want_counts else None
+    bias = select_bias.float().contiguous() if select_bias is not None else None      # chosen by score + bias, weighted by score
+    if bias is not None and bias.shape != (e,):
+        raise ValueError("select_bias must have one entry per expert")
     _lib.check(_lib.load().b200q_moe_router_topk(logits.data_ptr(), t, e, k, {"softmax": 0, "sigmoid": 1}[score_fn], int(normalize),
                                                  idx.data_ptr(), w.data_ptr(), probs.data_ptr() if want_probs else None,
-                                                 counts.data_ptr() if want_counts else None, _stream()), "b200q_moe_router_topk")
+                                                 counts.data_ptr() if want_counts else None,
+                                                 bias.data_ptr() if bias is not None else None, _stream()), "b200q_moe_router_topk")
     return idx, w, probs, counts
 
 

@@ -419,13 +419,14 @@ def _(dout, weights, row_of, padded_rows, fmt, y):
 
 
 @_lib_def("b200q::moe_router_topk", mutates_args=())
-def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str, normalize: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    idx, w, probs, _ = ops.moe_router_topk(logits, k, score_fn, normalize, want_counts=False)
+def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str, normalize: bool,
+                    select_bias: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    idx, w, probs, _ = ops.moe_router_topk(logits, k, score_fn, normalize, want_counts=False, select_bias=select_bias)
     return idx, w, probs
 
 
 @moe_router_topk.register_fake
-def _(logits, k, score_fn, normalize):
+def _(logits, k, score_fn, normalize, select_bias):
     t, e = logits.shape
     return (logits.new_empty(t, k, dtype=torch.int64), logits.new_empty(t, k, dtype=torch.bfloat16),
             logits.new_empty(t, e, dtype=torch.bfloat16))

@@ -314,6 +314,63 @@ def test_router_back_end(ops, score_fn, normalize, t, e, k):
         assert torch.equal(counts.cpu().long(), rc)
 
 
+@pytest.mark.parametrize("score_fn", ["softmax", "sigmoid"])
+def test_router_back_end_with_selection_bias(ops, score_fn):
+    """Experts chosen by prob + bias (src/layers/mlp.py:295-297), weights from the unbiased probs."""
+    g = torch.Generator().manual_seed(21)
+    t, e, k = 2048, 64, 4
+    logits = torch.randn(t, e, generator=g)
+    bias = 0.05 * torch.randn(e, generator=g)
+    bias[7] = 5.0                                                   # always chosen
+    bias[9] = -5.0                                                  # never chosen
+    idx, w, probs, counts = ops.moe_router_topk(logits.cuda(), k, score_fn, True, select_bias=bias.cuda())
+    p = logits.softmax(-1) if score_fn == "softmax" else logits.sigmoid()
+    biased = p + bias
+    ri = torch.topk(biased, k, dim=-1).indices
+    # rows where the k-th and (k+1)-th biased scores are within rounding of each other may legitimately differ
+    top = biased.topk(k + 1, -1).values
+    clear = (top[:, :-1] - top[:, 1:]).min(-1).values > 1e-6
+    assert clear.float().mean() > 0.99
+    assert torch.equal(idx.cpu()[clear], ri[clear])
+    assert (idx.cpu() == 7).any(-1).all() and not (idx.cpu() == 9).any()
+    raw = p.gather(-1, idx.cpu())
+    rw = (raw / (raw.sum(-1, keepdim=True) + 1e-9)).bfloat16()
+    ulp = (w.cpu().view(torch.int16).int() - rw.view(torch.int16).int()).abs().max().item()
+    assert ulp <= 1
+    assert torch.equal(counts.cpu().long(), torch.bincount(idx.cpu().reshape(-1), minlength=e))
+
+
+@pytest.mark.parametrize("compiled", [False, True])
+def test_block_with_shared_experts_and_expert_bias(ops, compiled):
+    from pretrain_b200.layers.mlp import SparseMoEBlock
+    torch.manual_seed(3)
+    d, inter, e, k, t = 256, 128, 8, 2, 512
+    blk = SparseMoEBlock(d, intermediate_size=inter, n_routed_experts=e, n_routed_experts_per_token=k, n_shared_experts=2,
+                         router_score_fn="sigmoid", aux_loss=False, expert_bias=True, expert_bias_update_rate=0.01).cuda().bfloat16()
+    with torch.no_grad():
+        blk.expert_gate_up.normal_(std=0.05)
+        blk.expert_down.normal_(std=0.05)
+        blk.router.expert_bias.bias[5] = 3.0                        # every token is routed to expert 5
+    assert blk.router.gate.weight.dtype == torch.float32 and blk.router.expert_bias.bias.dtype == torch.float32
+    fn = torch.compile(blk, fullgraph=True) if compiled else blk
+    x = torch.randn(2, t // 2, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out, aux = fn(x)
+    assert aux is None and out.shape == x.shape
+    out.float().square().mean().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in blk.parameters())
+    load = blk.expert_load.train_load
+    assert load.sum().item() == t * k and load[5].item() == t
+    # routed part + shared part: the shared block alone gives the difference to a block without it
+    with torch.no_grad():
+        shared = blk.shared_expert(x)[0]
+        blk_shared, blk.shared_expert = blk.shared_expert, None
+        routed = blk(x)[0]
+        blk.shared_expert = blk_shared
+    assert _rel(out.detach(), routed + shared) < 1e-2
+    blk.post_step()                                                  # expert 5 is overloaded: its bias drops by the rate
+    assert abs(blk.router.expert_bias.bias[5].item() - 2.99) < 1e-6 and blk.expert_load.train_load.sum().item() == 0
+
+
 def test_router_module_matches_torch_router_and_backpropagates(ops):
     from pretrain_b200.layers.mlp import MoERouter
     torch.manual_seed(0)

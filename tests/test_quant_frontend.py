@@ -154,3 +154,43 @@ def test_converter_swaps_by_rule(monkeypatch):
     assert type(m.lm_head) is nn.Linear                    # default exclude
     assert type(m.proj_tied) is nn.Linear                  # tie guard
     assert set(mlp0.state_dict()) == {"weight", "bias"}    # state-dict compatible with nn.Linear
+
+
+def test_moe_block_host_state_matches_the_reference_layout():
+    """Buffers, parameter names and the load-balancing bookkeeping of the MoE block (src/layers/mlp.py:182-239,
+    324-500; the reference's tests/fast/layers/test_mlp.py checks the same names and the sign rule)."""
+    from pretrain_b200.layers.mlp import ExpertBias, ExpertLoad, MoERouter, SparseMoEBlock
+    blk = SparseMoEBlock(64, intermediate_size=32, n_routed_experts=4, n_routed_experts_per_token=2, n_shared_experts=2,
+                         aux_loss=False, expert_bias=True, expert_bias_update_rate=0.01)
+    assert sorted(n for n, _ in blk.named_buffers()) == ["expert_load.eval_load", "expert_load.train_load", "router.expert_bias.bias"]
+    assert sorted(n for n, _ in blk.named_parameters()) == ["expert_down", "expert_gate_up", "router.gate.weight",
+                                                            "shared_expert.down_proj.weight", "shared_expert.gate_up_proj.weight"]
+    assert blk.shared_expert.down_proj.in_features == 2 * 32
+    assert "expert_load.train_load" not in blk.state_dict() and "router.expert_bias.bias" in blk.state_dict()
+    with pytest.raises(ValueError):
+        SparseMoEBlock(64, intermediate_size=32, n_routed_experts=4, n_routed_experts_per_token=2, aux_loss=True, expert_bias=True)
+    # sign rule: overloaded experts go down, underloaded ones up, by exactly the rate
+    eb = ExpertBias(4, 0.01)
+    eb.update(torch.tensor([10, 0, 5, 5]))
+    assert torch.allclose(eb.bias, torch.tensor([-0.01, 0.01, 0.0, 0.0]))
+    assert eb.half().bias.dtype == torch.float32                       # pinned to fp32 through casts
+    load = ExpertLoad(4)
+    load.record_load(torch.tensor([1, 2, 3, 4]), True)
+    load.record_load(torch.tensor([1, 0, 0, 0]), True)
+    load.record_load(torch.tensor([9, 9, 9, 9]), False)
+    assert load.train_load.tolist() == [2, 2, 3, 4] and load.eval_load.tolist() == [9, 9, 9, 9]
+    # post_step feeds the accumulated load to the bias and clears it
+    blk.expert_load.record_load(torch.tensor([8, 0, 4, 4]), True)
+    blk.post_step()
+    assert torch.allclose(blk.router.expert_bias.bias, torch.tensor([-0.01, 0.01, 0.0, 0.0]))
+    assert blk.expert_load.train_load.sum().item() == 0
+    # the bias moves the selection, never the weights (fp32 CPU input: the module's torch path)
+    torch.manual_seed(0)
+    r = MoERouter(16, 4, 2, expert_bias=True, router_score_fn="softmax")
+    x = torch.randn(32, 16)
+    i0, w0, p0 = r(x)
+    r.expert_bias.bias[3] = 10.0
+    i1, w1, p1 = r(x)
+    assert (i1 == 3).any(-1).all() and torch.equal(p0, p1)
+    raw = p1.gather(-1, i1)
+    assert torch.allclose(w1, raw / (raw.sum(-1, keepdim=True) + 1e-9))
