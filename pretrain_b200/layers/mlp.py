@@ -186,6 +186,20 @@ def _cached(param: torch.Tensor, slot: str, key, make):
     return hit[1]
 
 
+def _ffn_flops(d_model: int, d_ff: int, gated: bool, bias: bool) -> int:
+    """Forward FLOPs per token of one feed-forward network: 2 FLOPs per weight (three d x d_ff matrices when gated,
+    two otherwise) plus one add per bias entry - the accounting of src/layers/mlp.py:152-162."""
+    return (6 if gated else 4) * d_model * d_ff + _ffn_bias_terms(d_model, d_ff, gated, bias)
+
+
+def _ffn_bias_terms(d_model: int, d_ff: int, gated: bool, bias: bool) -> int:
+    return ((2 if gated else 1) * d_ff + d_model) if bias else 0
+
+
+def _ffn_parameters(d_model: int, d_ff: int, gated: bool, bias: bool) -> int:
+    return (3 if gated else 2) * d_model * d_ff + _ffn_bias_terms(d_model, d_ff, gated, bias)
+
+
 class DenseMLPBlock(nn.Module):
     """Dense feed-forward block with the reference's constructor and (out, None) contract
     (src/layers/mlp.py:103-150): ``down_proj(act(gate, up))`` with ``(gate, up) =
@@ -208,6 +222,14 @@ class DenseMLPBlock(nn.Module):
             self.up_proj = nn.Linear(d_model, intermediate_size, bias=bias)
         self.down_proj = nn.Linear(intermediate_size, d_model, bias=bias)
         self.dropout = nn.Dropout(dropout)
+
+    @classmethod
+    def compute_flops(cls, d_model, *, intermediate_size, gated=True, bias=False, **_):
+        return _ffn_flops(d_model, intermediate_size, gated, bias)
+
+    @classmethod
+    def compute_parameters(cls, d_model, *, intermediate_size, gated=True, bias=False, active=False, **_):
+        return _ffn_parameters(d_model, intermediate_size, gated, bias)
 
     def _fused_kind(self, x):
         """'mxfp8' / 'nvfp4' when the epilogue form applies to this call, else None."""
@@ -284,6 +306,14 @@ class ExpertBias(nn.Module):
         err = expert_counts.float().mean() - expert_counts.float()
         self.bias += self.update_rate * err.sign()
 
+    @classmethod
+    def compute_flops(cls, n_experts: int) -> int:
+        return n_experts                   # one add per expert score
+
+    @classmethod
+    def compute_parameters(cls, n_experts: int) -> int:
+        return 0                           # a buffer, not a parameter
+
 
 class ExpertLoad(nn.Module):
     """Tokens per expert seen in training (accumulated) and in the last evaluation pass (src/layers/mlp.py:219-239)."""
@@ -320,6 +350,14 @@ class MoERouter(nn.Module):
         self.score_name = router_score_fn
         self.gate = nn.Linear(d_model, n_routed_experts, bias=False)
         self.expert_bias = ExpertBias(n_routed_experts, expert_bias_update_rate) if expert_bias else None
+
+    @classmethod
+    def compute_flops(cls, d_model: int, n_experts: int, *, expert_bias=False) -> int:
+        return 2 * d_model * n_experts + (ExpertBias.compute_flops(n_experts) if expert_bias else 0)
+
+    @classmethod
+    def compute_parameters(cls, d_model: int, n_experts: int, *, expert_bias=False) -> int:
+        return d_model * n_experts + (ExpertBias.compute_parameters(n_experts) if expert_bias else 0)
 
     def update_expert_bias(self, expert_counts):
         """Nudge the load-balancing bias toward uniform load; no-op without one."""
@@ -422,6 +460,27 @@ class SparseMoEBlock(nn.Module):
             self.router.update_expert_bias(self.expert_load.train_load)
             self.expert_load.reset_train_load()
 
+    def forward_meta(self) -> dict:
+        """Routing metadata of the last forward: accumulated counts in training, the batch's counts in evaluation."""
+        return {"expert_load": self.expert_load.train_load if self.training else self.expert_load.eval_load}
+
+    @classmethod
+    def compute_flops(cls, d_model, *, intermediate_size, n_routed_experts, n_routed_experts_per_token=2, n_shared_experts=0,
+                      gated=True, bias=False, expert_bias=False, **_):
+        """Per token: the router, k routed experts and the always-on shared block (src/layers/mlp.py:510-545)."""
+        shared = _ffn_flops(d_model, n_shared_experts * intermediate_size, gated, bias) if n_shared_experts > 0 else 0
+        return (MoERouter.compute_flops(d_model, n_routed_experts, expert_bias=expert_bias)
+                + n_routed_experts_per_token * _ffn_flops(d_model, intermediate_size, gated, bias) + shared)
+
+    @classmethod
+    def compute_parameters(cls, d_model, *, intermediate_size, n_routed_experts, n_routed_experts_per_token=2, n_shared_experts=0,
+                           gated=True, bias=False, expert_bias=False, active=False, **_):
+        """All experts, or with `active` only the k that run per token; shared experts count either way."""
+        n = n_routed_experts_per_token if active else n_routed_experts
+        shared = _ffn_parameters(d_model, n_shared_experts * intermediate_size, gated, bias) if n_shared_experts > 0 else 0
+        return (MoERouter.compute_parameters(d_model, n_routed_experts, expert_bias=expert_bias)
+                + n * _ffn_parameters(d_model, intermediate_size, gated, bias) + shared)
+
     def forward(self, x):
         b, s, d = x.shape
         e = self.n_routed_experts
@@ -456,3 +515,6 @@ class SparseMoEBlock(nn.Module):
         if self.shared_expert is not None:
             out = out + self.shared_expert(x)[0]
         return out, aux
+
+
+MLP_REGISTRY = {"dense": DenseMLPBlock, "moe": SparseMoEBlock}

@@ -194,3 +194,23 @@ def test_moe_block_host_state_matches_the_reference_layout():
     assert (i1 == 3).any(-1).all() and torch.equal(p0, p1)
     raw = p1.gather(-1, i1)
     assert torch.allclose(w1, raw / (raw.sum(-1, keepdim=True) + 1e-9))
+
+
+def test_flop_and_parameter_accounting_of_the_mlp_blocks():
+    """The class methods the reference's model statistics call (src/layers/mlp.py:152-176, 309-322, 510-587); the
+    expected numbers were produced by the reference's own methods for the same arguments."""
+    from pretrain_b200.layers.mlp import MLP_REGISTRY, DenseMLPBlock, MoERouter, SparseMoEBlock
+    assert MLP_REGISTRY == {"dense": DenseMLPBlock, "moe": SparseMoEBlock}
+    assert DenseMLPBlock.compute_flops(64, intermediate_size=96) == 6 * 64 * 96
+    assert DenseMLPBlock.compute_flops(64, intermediate_size=96, gated=False, bias=True) == 4 * 64 * 96 + 96 + 64
+    assert DenseMLPBlock.compute_parameters(64, intermediate_size=96, bias=True) == 3 * 64 * 96 + 2 * 96 + 64
+    assert MoERouter.compute_flops(64, 8, expert_bias=True) == 2 * 64 * 8 + 8 and MoERouter.compute_parameters(64, 8, expert_bias=True) == 64 * 8
+    kw = dict(intermediate_size=96, n_routed_experts=8)
+    assert SparseMoEBlock.compute_flops(64, n_shared_experts=2, expert_bias=True, bias=True, **kw) == 149448
+    assert SparseMoEBlock.compute_parameters(64, active=True, **kw) == 37376
+    assert SparseMoEBlock.compute_parameters(64, **kw) == 64 * 8 + 8 * 3 * 64 * 96
+    blk = SparseMoEBlock(64, intermediate_size=32, n_routed_experts=4, n_routed_experts_per_token=2, aux_loss=False)
+    blk.expert_load.record_load(torch.tensor([1, 2, 3, 4]), True)
+    blk.expert_load.record_load(torch.tensor([5, 5, 5, 5]), False)
+    assert blk.forward_meta()["expert_load"].tolist() == [1, 2, 3, 4]
+    assert blk.eval().forward_meta()["expert_load"].tolist() == [5, 5, 5, 5]
