@@ -25,9 +25,40 @@ def silu_glu(gate, up):
     return F.silu(gate) * up
 
 
-GATED_ACTIVATIONS = {"silu": silu_glu, "relu": lambda g, u: F.relu(g) * u, "gelu": lambda g, u: F.gelu(g) * u,
-                     "bilinear": lambda g, u: g * u}
-UNGATED_ACTIVATIONS = {"silu": F.silu, "relu": F.relu, "gelu": F.gelu}
+def _powlu(x, m: float = 3.0):
+    """PowLU with m = 3: x * x^(m / (sqrt(x) + 1)) * sigmoid(x) for x > 0 and x^2 * sigmoid(x) otherwise.  The positive
+    branch is evaluated on max(x, 1-where-negative) so that the unselected side stays finite for autograd."""
+    base = torch.where(x > 0, x, torch.ones_like(x))
+    pos = x * base ** (m / (base.sqrt() + 1.0)) * torch.sigmoid(x)
+    return torch.where(x > 0, pos, x * x * torch.sigmoid(x))
+
+
+# The reference's activation registries (src/layers/activation.py): unary activations, their squares
+# ("relu2", ...), and for gated blocks unary(gate) * up, plus the gate-only forms.  Only SwiGLU has a
+# fused kernel here; the others run as torch element-wise ops between the two quantized GEMMs.
+_UNARY = {"relu": F.relu, "gelu": F.gelu, "silu": F.silu, "leaky_relu": lambda x: F.leaky_relu(x, 0.01)}
+UNGATED_ACTIVATIONS = dict(_UNARY)
+UNGATED_ACTIVATIONS.update({name + "2": (lambda x, f=f: f(x) ** 2) for name, f in _UNARY.items()})
+GATED_ACTIVATIONS = {name: (lambda g, u, f=f: f(g) * u) for name, f in UNGATED_ACTIVATIONS.items()}
+GATED_ACTIVATIONS.update({"silu": silu_glu, "bilinear": lambda g, u: g * u, "bilinear2": lambda g, u: g ** 2 * u,
+                          "powlu": lambda g, u: _powlu(g) * u})
+
+
+def _add_bias(y, b):
+    return y if b is None else y + (b if b.ndim == 1 else b.unsqueeze(-2))
+
+
+def gated_mlp(x, w_gate_up, w_down, act_fn, b_gate_up=None, b_down=None):
+    """down(act(gate, up)) with (gate, up) = chunk(x @ w_gate_up^T): the reference's unquantized helper
+    (src/layers/mlp.py:7-30), kept as plain matmuls."""
+    gate, up = _add_bias(x @ w_gate_up.mT, b_gate_up).chunk(2, dim=-1)
+    return _add_bias(act_fn(gate, up) @ w_down.mT, b_down)
+
+
+def ungated_mlp(x, w_up, w_down, act_fn, b_up=None, b_down=None):
+    """down(act(x @ w_up^T)), the ungated counterpart (src/layers/mlp.py:33-52)."""
+    return _add_bias(act_fn(_add_bias(x @ w_up.mT, b_up)) @ w_down.mT, b_down)
+
 
 MOE_ROUTER_SCORE_FNS = {
     "softmax": lambda logits: logits.softmax(dim=-1),

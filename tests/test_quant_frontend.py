@@ -214,3 +214,24 @@ def test_flop_and_parameter_accounting_of_the_mlp_blocks():
     blk.expert_load.record_load(torch.tensor([5, 5, 5, 5]), False)
     assert blk.forward_meta()["expert_load"].tolist() == [1, 2, 3, 4]
     assert blk.eval().forward_meta()["expert_load"].tolist() == [5, 5, 5, 5]
+
+
+def test_activation_registries_cover_the_reference_names():
+    """Names of src/layers/activation.py:130-158 and the rule that a squared variant squares the unary activation
+    before the gate multiplies in."""
+    import torch.nn.functional as F
+    from pretrain_b200.layers.mlp import GATED_ACTIVATIONS, UNGATED_ACTIVATIONS, gated_mlp, silu_glu, ungated_mlp
+    assert set(UNGATED_ACTIVATIONS) == {"relu", "gelu", "silu", "leaky_relu", "relu2", "gelu2", "silu2", "leaky_relu2"}
+    assert set(GATED_ACTIVATIONS) == set(UNGATED_ACTIVATIONS) | {"bilinear", "bilinear2", "powlu"}
+    assert GATED_ACTIVATIONS["silu"] is silu_glu                    # the one with a fused kernel
+    g, u = torch.randn(8, 16), torch.randn(8, 16)
+    assert torch.equal(UNGATED_ACTIVATIONS["leaky_relu2"](g), F.leaky_relu(g, 0.01) ** 2)
+    assert torch.equal(GATED_ACTIVATIONS["silu2"](g, u), F.silu(g) ** 2 * u)
+    assert torch.equal(GATED_ACTIVATIONS["bilinear2"](g, u), g ** 2 * u)
+    p = GATED_ACTIVATIONS["powlu"](g, torch.ones_like(g))
+    neg = g <= 0
+    assert torch.allclose(p[neg], (g * g * torch.sigmoid(g))[neg]) and torch.isfinite(p).all()
+    x, wgu, wd = torch.randn(2, 3, 16), torch.randn(24, 16), torch.randn(16, 12)
+    gate, up = (x @ wgu.t()).chunk(2, -1)
+    assert torch.allclose(gated_mlp(x, wgu, wd, silu_glu), (F.silu(gate) * up) @ wd.t())
+    assert torch.allclose(ungated_mlp(x, wgu[:12], wd, F.relu, torch.ones(12)), F.relu(x @ wgu[:12].t() + 1) @ wd.t())
