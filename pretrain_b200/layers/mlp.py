@@ -70,11 +70,6 @@ def _wants_grad(*tensors) -> bool:
     return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
 
 
-def _trainable_shapes(d: int, inter: int) -> bool:
-    """The grouped backward GEMMs contract over D, 2I and the rows; their K must be a multiple of 128."""
-    return d % 128 == 0 and (2 * inter) % 128 == 0 and inter % 32 == 0
-
-
 E4M3, E5M2, SWZ = ops.E4M3, ops.E5M2, ops.SF_SWIZZLED
 
 
@@ -128,6 +123,75 @@ class _ExpertFFN(torch.autograd.Function):
         dx = T.moe_unpermute(da, None, plan.row_of, t)                                           # sum over the k slots
         xd, twd, w1d, w2d = ctx.dtypes
         return (dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d)) + (None,) * len(plan_tensors)
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+    """y[r] = a[r] @ w[expert of r]^T on the padded expert-sorted layout, MXFP8 forward and backward: one piece of
+    the general trainable expert path (any activation, biases), which keeps the element-wise steps between its two
+    grouped linears in plain torch under autograd.  With `gather` the input is the (T, D) token matrix and the
+    permute is fused into the quantizer; otherwise it is a (padded_rows, K) matrix."""
+
+    @staticmethod
+    def forward(ctx, a, w, gather, *plan_tensors):
+        plan = T.MoEPlan(*plan_tensors)
+        e, n, k = w.shape
+        if gather:
+            ar, asr, ac, asc = T.moe_gather_quantize_dual(a, plan, E4M3)
+        else:
+            ar, asr, ac, asc = T.quantize_mxfp8_dual(a, E4M3, SWZ)
+        wr, wsr, wc, wsc = T.quantize_mxfp8_dual(w.reshape(e * n, k), E4M3, SWZ)
+        ctx.save_for_backward(ac, asc, wc, wsc, *plan_tensors)
+        ctx.gather, ctx.tokens, ctx.k = gather, a.shape[0], k
+        ctx.dtypes = (a.dtype, w.dtype)
+        return T.grouped_gemm_mxfp8(ar, asr, wr, wsr, plan, n)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ac, asc, wc, wsc, *plan_tensors = ctx.saved_tensors
+        plan = T.MoEPlan(*plan_tensors)
+        gr, gsr, gc, gsc = T.quantize_mxfp8_dual(dy.to(torch.bfloat16).contiguous(), E5M2, SWZ)
+        da = T.grouped_gemm_mxfp8_dgrad(gr, gsr, wc, wsc, plan, ctx.k, E5M2, E4M3)            # (R, K)
+        dw = T.grouped_gemm_mxfp8_wgrad(gc, gsc, ac, asc, plan, E5M2, E4M3)                  # (E, N, K)
+        if ctx.gather:
+            da = T.moe_unpermute(da, None, plan.row_of, ctx.tokens)                           # sum over the k slots
+        return (da.to(ctx.dtypes[0]), dw.to(ctx.dtypes[1]), None) + (None,) * len(plan_tensors)
+
+
+class _UnpermuteFn(torch.autograd.Function):
+    """out[t] = sum_j w[t, j] * y[row of (t, j)] with its backward (dy scattered into the padded layout, pad rows
+    zero; dw = <dout, y>)."""
+
+    @staticmethod
+    def forward(ctx, y, top_w, tokens, *plan_tensors):
+        plan = T.MoEPlan(*plan_tensors)
+        ctx.save_for_backward(y, top_w, *plan_tensors)
+        return T.moe_unpermute(y, top_w.to(torch.bfloat16), plan.row_of, tokens)
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, top_w, *plan_tensors = ctx.saved_tensors
+        dy, dw = T.moe_unpermute_backward(dout.to(torch.bfloat16).contiguous(), top_w.to(torch.bfloat16), y, T.MoEPlan(*plan_tensors))
+        return (dy.to(y.dtype), dw.to(top_w.dtype), None) + (None,) * len(plan_tensors)
+
+
+def _expert_ffn_general(x, top_w, w_in, w_down, b_in, b_down, act_fn, gated, plan):
+    """The trainable expert path for any activation and optional biases: grouped linear -> (+ bias, activation in
+    torch) -> grouped linear -> (+ bias) -> weighted unpermute.  Pad rows carry no gradient: their output
+    gradient is zero, so whatever the biases put there never reaches a weight."""
+    t = x.shape[0]
+    g = _GroupedLinearFn.apply(x, w_in, True, *plan)
+    rows = _expert_of_padded_row(plan)
+    if b_in is not None:
+        g = g + b_in.to(g.dtype)[rows]
+    # rows past the live tiles are never written by the grouped GEMMs (forward or backward): select them away, so
+    # that neither their contents nor the gradients that come back for them reach a weight or a bias
+    live = (plan.tile_expert >= 0).repeat_interleave(128).unsqueeze(-1)
+    g = torch.where(live, g, torch.zeros((), dtype=g.dtype, device=g.device))
+    h = act_fn(*g.chunk(2, dim=-1)) if gated else act_fn(g)
+    y = _GroupedLinearFn.apply(h.contiguous(), w_down, False, *plan)
+    if b_down is not None:
+        y = y + b_down.to(y.dtype)[rows]
+    return _UnpermuteFn.apply(y, top_w, t, *plan)
 
 
 def _quantize_expert_weights(w: torch.Tensor):
@@ -521,12 +585,19 @@ class SparseMoEBlock(nn.Module):
         b_in = self.expert_gate_up_bias if self.gated else self.expert_up_bias
         plan = T.moe_permute_plan(top_indices, e)                          # stable sort by expert
         if _wants_grad(x, top_weights, w_in, self.expert_down, b_in, self.expert_down_bias):
-            if not (self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None
-                    and _trainable_shapes(d, w_in.shape[1] // 2)):
-                raise NotImplementedError("the backward of the MXFP8 expert path covers bias-free SwiGLU experts with "
-                                          "d_model % 128 == 0 and intermediate_size % 64 == 0")
-            out = _ExpertFFN.apply(x_flat.to(torch.bfloat16), top_weights, w_in.to(torch.bfloat16),
-                                   self.expert_down.to(torch.bfloat16), *plan).to(x.dtype)
+            inter = self.expert_down.shape[2]
+            if d % 128 or w_in.shape[1] % 128 or inter % 32:
+                raise NotImplementedError("the backward of the MXFP8 expert path needs d_model and the first layer's width "
+                                          "(2 * intermediate_size when gated) to be multiples of 128 and intermediate_size "
+                                          "a multiple of 32")
+            if self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None:
+                # SwiGLU without biases: every element-wise step runs inside a quantizer kernel
+                out = _ExpertFFN.apply(x_flat.to(torch.bfloat16), top_weights, w_in.to(torch.bfloat16),
+                                       self.expert_down.to(torch.bfloat16), *plan).to(x.dtype)
+            else:
+                out = _expert_ffn_general(x_flat.to(torch.bfloat16), top_weights, w_in.to(torch.bfloat16),
+                                          self.expert_down.to(torch.bfloat16), b_in, self.expert_down_bias, self.act_fn,
+                                          self.gated, plan).to(x.dtype)
         else:
             a, sfa = T.moe_gather_mxfp8(x_flat.to(torch.bfloat16), plan)      # permute fused with MXFP8
             y = _grouped_ffn_padded(a, sfa, plan, w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),

@@ -449,3 +449,20 @@ def quantize_mxfp8_glu_rows(w: torch.Tensor, n_groups: int, inter: int) -> Tuple
 def _(w, n_groups, inter):
     rows, k = w.shape
     return w.new_empty(rows, k, dtype=torch.uint8), w.new_empty(_sf_numel(rows, k // 32, ops.SF_SWIZZLED), dtype=torch.uint8)
+
+
+@_lib_def("b200q::moe_unpermute_backward", mutates_args=())
+def _moe_unpermute_backward(dout: torch.Tensor, weights: torch.Tensor, y: torch.Tensor, row_of: torch.Tensor,
+                            src_of_row: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    plan = _plan(0, row_of=row_of, src_of_row=src_of_row)
+    return ops.moe_unpermute_backward(dout, weights, y, plan)
+
+
+@_moe_unpermute_backward.register_fake
+def _(dout, weights, y, row_of, src_of_row):
+    return dout.new_empty(src_of_row.shape[0], dout.shape[1], dtype=torch.bfloat16), dout.new_empty(weights.shape, dtype=torch.float32)
+
+
+def moe_unpermute_backward(dout, weights, y, plan: MoEPlan):
+    """(dy bf16 (padded_rows, D) with zero pad rows, dw fp32 (T, k)): the gradients of moe_unpermute."""
+    return _moe_unpermute_backward(dout, weights, y, plan.row_of, plan.src_of_row)

@@ -505,6 +505,55 @@ def test_sparse_moe_block_trains(ops):
     assert all(torch.isfinite(p).all() for p in blk.parameters())
 
 
+@pytest.mark.parametrize("gated,activation,bias", [(False, "relu2", True), (True, "gelu", True), (True, "silu", True), (False, "silu", False)])
+@pytest.mark.parametrize("compiled", [False, True])
+def test_block_trains_with_any_activation_and_biases(ops, gated, activation, bias, compiled):
+    """The general trainable path (grouped linears with MXFP8 forward and backward, element-wise steps in torch)
+    against the same block written as a per-expert fp32 loop under autograd."""
+    from pretrain_b200.layers.mlp import GATED_ACTIVATIONS, UNGATED_ACTIVATIONS, SparseMoEBlock
+    torch.manual_seed(4)
+    d, inter, e, k, t = 256, 128, 8, 2, 1024
+    blk = SparseMoEBlock(d, intermediate_size=inter, n_routed_experts=e, n_routed_experts_per_token=k, router_score_fn="softmax",
+                         aux_loss=False, activation=activation, gated=gated, bias=bias).cuda()
+    w_in = blk.expert_gate_up if gated else blk.expert_up
+    b_in = blk.expert_gate_up_bias if gated else blk.expert_up_bias
+    with torch.no_grad():
+        w_in.normal_(std=0.05)
+        blk.expert_down.normal_(std=0.05)
+        blk.router.gate.weight.normal_(std=0.5)
+        if bias:
+            b_in.normal_(std=0.1)
+            blk.expert_down_bias.normal_(std=0.1)
+    fn = torch.compile(blk, fullgraph=True) if compiled else blk
+    x = torch.randn(2, t // 2, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    coef = torch.randn(2, t // 2, d, device="cuda")
+    out, _ = fn(x)
+    (out.float() * coef).sum().backward()
+    # fp32 loop form
+    act = (GATED_ACTIVATIONS if gated else UNGATED_ACTIVATIONS)[activation]
+    xr = x.detach().float().reshape(t, d).requires_grad_(True)
+    params = [p.detach().float().clone().requires_grad_(True) for p in ([w_in, blk.expert_down] + ([b_in, blk.expert_down_bias] if bias else []))]
+    probs = (xr @ blk.router.gate.weight.detach().float().t()).softmax(-1)
+    tw, ti = torch.topk(probs, k, dim=-1)
+    tw = tw / (tw.sum(-1, keepdim=True) + 1e-9)
+    ref = torch.zeros(t, d, device="cuda")
+    for ei in range(e):
+        tok, slot = (ti == ei).nonzero(as_tuple=True)
+        if tok.numel():
+            pre = xr[tok].bfloat16().float() @ params[0][ei].bfloat16().float().t() + (params[2][ei] if bias else 0)
+            hid = act(*pre.chunk(2, -1)) if gated else act(pre)
+            y = hid @ params[1][ei].bfloat16().float().t() + (params[3][ei] if bias else 0)
+            ref = ref.index_add(0, tok, y * tw[tok, slot].unsqueeze(-1))
+    (ref * coef.reshape(t, d)).sum().backward()
+    got = [w_in.grad, blk.expert_down.grad] + ([b_in.grad, blk.expert_down_bias.grad] if bias else [])
+    errs = [_rel(out.reshape(t, d), ref)] + [_rel(a_, b_.grad) for a_, b_ in zip(got, params)]
+    # MXFP8 noise of two chained GEMMs with E5M2 gradients; the first layer's bias gradient is a sum of signed
+    # per-row terms that largely cancel, which amplifies that noise relative to the sum (a wiring error gives >= 1)
+    limits = [1.3e-1, 1.3e-1, 1.3e-1, 3.5e-1, 1.3e-1]
+    assert all(err < lim for err, lim in zip(errs, limits)), errs
+    assert _rel(x.grad.reshape(t, d), xr.grad) < 1.5e-1
+
+
 @pytest.mark.parametrize("train", [True, False])
 def test_sparse_moe_block_traces_with_torch_compile(ops, train):
     """The reference compiles the whole model (src/training/trainer.py:176-177): the block must trace without a
