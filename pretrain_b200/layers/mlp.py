@@ -174,11 +174,17 @@ class _UnpermuteFn(torch.autograd.Function):
         return (dy.to(y.dtype), dw.to(top_w.dtype), None) + (None,) * len(plan_tensors)
 
 
-def _expert_ffn_general(x, top_w, w_in, w_down, b_in, b_down, act_fn, gated, plan):
-    """The trainable expert path for any activation and optional biases: grouped linear -> (+ bias, activation in
-    torch) -> grouped linear -> (+ bias) -> weighted unpermute.  Pad rows carry no gradient: their output
-    gradient is zero, so whatever the biases put there never reaches a weight."""
-    t = x.shape[0]
+def _trainable_widths(d: int, width: int, inter: int) -> None:
+    if d % 128 or width % 128 or inter % 32:
+        raise NotImplementedError("the backward of the MXFP8 expert path needs d_model and the first layer's width "
+                                  "(2 * intermediate_size when gated) to be multiples of 128 and intermediate_size "
+                                  "a multiple of 32")
+
+
+def _expert_ffn_general(x, w_in, w_down, b_in, b_down, act_fn, gated, plan):
+    """The trainable expert path for any activation and optional biases, up to the expert outputs in the padded
+    layout: grouped linear (permute fused) -> (+ bias, activation in torch) -> grouped linear -> (+ bias).  Pad rows
+    carry no gradient: their output gradient is zero, so whatever the biases put there never reaches a weight."""
     g = _GroupedLinearFn.apply(x, w_in, True, *plan)
     rows = _expert_of_padded_row(plan)
     if b_in is not None:
@@ -191,7 +197,7 @@ def _expert_ffn_general(x, top_w, w_in, w_down, b_in, b_down, act_fn, gated, pla
     y = _GroupedLinearFn.apply(h.contiguous(), w_down, False, *plan)
     if b_down is not None:
         y = y + b_down.to(y.dtype)[rows]
-    return _UnpermuteFn.apply(y, top_w, t, *plan)
+    return y
 
 
 def _quantize_expert_weights(w: torch.Tensor):
@@ -251,23 +257,29 @@ def grouped_mlp(x, w_in, w_down, act_fn, offs, gated, row_expert_ids=None, b_in=
 
     x is (R, D) with rows grouped by expert and ``offs`` the (E,) int32 cumulative end offsets
     (offs[-1] == R); weights are (E, out, in); empty groups are fine; biases, when given, are
-    (E, out) and are added per row.  Returns (R, D_out) in bf16, rows in the input order.
+    (E, out) and are added per row.  Returns (R, D_out) in bf16, rows in the input order.  With inputs that
+    require grad the general trainable path runs (MXFP8 backward GEMMs; widths as _trainable_widths says).
     """
-    if _wants_grad(x, w_in, w_down, b_in, b_down):
-        raise NotImplementedError("grouped_mlp is forward-only here; SparseMoEBlock carries the backward of the expert path")
     if not x.is_cuda:
         raise RuntimeError("grouped_mlp runs on the B200 kernels only (no CPU path)")
     r = x.shape[0]
     e = w_in.shape[0]
-    x, w_in, w_down = x.to(torch.bfloat16), w_in.to(torch.bfloat16), w_down.to(torch.bfloat16)
     plan = T.moe_pad_plan(offs, r)
-    a, sfa = T.moe_gather_mxfp8(x, plan)
-    out_p = _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in, b_down)
-    # back to the caller's unpadded row order
+    # padded row of every input row (the inverse of the plan's src_of_row): its expert's padded start + its rank there
     rows = torch.arange(r, device=x.device)
     expert = torch.searchsorted(plan.offs.long(), rows, right=True).clamp_max(e - 1)
     starts = torch.cat([plan.offs.new_zeros(1), plan.offs[:-1]]).long()
-    return out_p[plan.padded_offs.long()[expert] + rows - starts[expert]]
+    row_of = plan.padded_offs.long()[expert] + rows - starts[expert]
+    if _wants_grad(x, w_in, w_down, b_in, b_down):
+        _trainable_widths(x.shape[1], w_in.shape[1], w_down.shape[2])
+        plan = plan._replace(row_of=row_of.to(torch.int32))          # one "slot" per row: the backward of the gather sums over it
+        out_p = _expert_ffn_general(x.to(torch.bfloat16), w_in.to(torch.bfloat16), w_down.to(torch.bfloat16), b_in, b_down,
+                                    act_fn, gated, plan)
+    else:
+        x, w_in, w_down = x.to(torch.bfloat16), w_in.to(torch.bfloat16), w_down.to(torch.bfloat16)
+        a, sfa = T.moe_gather_mxfp8(x, plan)
+        out_p = _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in, b_down)
+    return out_p[row_of]                                                # back to the caller's unpadded row order
 
 
 def _cached(param: torch.Tensor, slot: str, key, make):
@@ -585,19 +597,15 @@ class SparseMoEBlock(nn.Module):
         b_in = self.expert_gate_up_bias if self.gated else self.expert_up_bias
         plan = T.moe_permute_plan(top_indices, e)                          # stable sort by expert
         if _wants_grad(x, top_weights, w_in, self.expert_down, b_in, self.expert_down_bias):
-            inter = self.expert_down.shape[2]
-            if d % 128 or w_in.shape[1] % 128 or inter % 32:
-                raise NotImplementedError("the backward of the MXFP8 expert path needs d_model and the first layer's width "
-                                          "(2 * intermediate_size when gated) to be multiples of 128 and intermediate_size "
-                                          "a multiple of 32")
+            _trainable_widths(d, w_in.shape[1], self.expert_down.shape[2])
             if self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None:
                 # SwiGLU without biases: every element-wise step runs inside a quantizer kernel
                 out = _ExpertFFN.apply(x_flat.to(torch.bfloat16), top_weights, w_in.to(torch.bfloat16),
                                        self.expert_down.to(torch.bfloat16), *plan).to(x.dtype)
             else:
-                out = _expert_ffn_general(x_flat.to(torch.bfloat16), top_weights, w_in.to(torch.bfloat16),
-                                          self.expert_down.to(torch.bfloat16), b_in, self.expert_down_bias, self.act_fn,
-                                          self.gated, plan).to(x.dtype)
+                y = _expert_ffn_general(x_flat.to(torch.bfloat16), w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
+                                        b_in, self.expert_down_bias, self.act_fn, self.gated, plan)
+                out = _UnpermuteFn.apply(y, top_weights, b * s, *plan).to(x.dtype)
         else:
             a, sfa = T.moe_gather_mxfp8(x_flat.to(torch.bfloat16), plan)      # permute fused with MXFP8
             y = _grouped_ffn_padded(a, sfa, plan, w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),

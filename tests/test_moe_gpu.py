@@ -645,8 +645,25 @@ def test_grouped_mlp_drop_in(ops, counts):
     assert _rel(out, ref) < 2e-2
     plain = R.grouped_mlp_ref(x, w_in, w_down, offs)                   # unquantized reference: only quantization noise apart
     assert _rel(out, plain) < 0.08
-    with pytest.raises(NotImplementedError):
-        grouped_mlp(x.cuda().requires_grad_(True), w_in.cuda(), w_down.cuda(), silu_glu, offs.cuda(), True)
+    # with gradients: the same function under autograd against the plain loop form in fp32
+    xg, wi, wd = (t.cuda().requires_grad_(True) for t in (x, w_in, w_down))
+    coef = torch.randn(r, d, generator=g).cuda()
+    (grouped_mlp(xg, wi, wd, silu_glu, offs.cuda(), True).float() * coef).sum().backward()
+    xr, wir, wdr = (t.cuda().float().requires_grad_(True) for t in (x, w_in, w_down))
+    starts = [0] + offs.tolist()
+    ref_rows = []
+    for ei in range(e):
+        seg = xr[starts[ei]:starts[ei + 1]]
+        gate, up = (seg @ wir[ei].t()).chunk(2, -1)
+        ref_rows.append((F.silu(gate) * up) @ wdr[ei].t())
+    (torch.cat(ref_rows) * coef).sum().backward()
+    assert _rel(xg.grad, xr.grad) < 1.5e-1
+    live = [ei for ei, c in enumerate(counts) if c]
+    assert _rel(wi.grad[live], wir.grad[live]) < 1.5e-1 and _rel(wd.grad[live], wdr.grad[live]) < 1.5e-1
+    dead = [ei for ei, c in enumerate(counts) if not c]
+    assert (wi.grad[dead] == 0).all() and (wd.grad[dead] == 0).all()      # experts without rows get exact zeros
+    with pytest.raises(NotImplementedError):                               # widths the backward GEMMs cannot tile
+        grouped_mlp(x.cuda()[:, :192].requires_grad_(True), w_in.cuda()[:, :, :192], w_down.cuda()[:, :192], silu_glu, offs.cuda(), True)
 
 
 def test_grouped_mlp_against_reference_golden(ops, golden):
