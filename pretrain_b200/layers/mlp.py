@@ -539,8 +539,6 @@ class SparseMoEBlock(nn.Module):
         super().__init__()
         if aux_loss and expert_bias:
             raise ValueError("aux_loss and expert_bias are mutually exclusive MoE balancing strategies")
-        if dropout:
-            raise NotImplementedError("expert dropout is outside this build's path (the unpermute kernel applies the weights)")
         self.n_routed_experts = n_routed_experts
         self.n_shared_experts = n_shared_experts
         self.expert_bias, self.expert_bias_update_rate = expert_bias, expert_bias_update_rate
@@ -559,6 +557,9 @@ class SparseMoEBlock(nn.Module):
         # DeepSeekMoE shared experts: one always-on dense block of width n_shared_experts * intermediate_size
         self.shared_expert = (DenseMLPBlock(d_model, intermediate_size=n_shared_experts * intermediate_size, activation=activation,
                                             gated=gated, bias=bias) if n_shared_experts > 0 else None)
+        # the reference drops elements of weight * expert_out (src/layers/mlp.py:472-473); the weights multiply
+        # element-wise, so dropping the expert outputs before the weighted unpermute is the same operation
+        self.expert_dropout = nn.Dropout(dropout)
         self.expert_load = ExpertLoad(n_routed_experts)
 
     @torch.no_grad()
@@ -598,19 +599,20 @@ class SparseMoEBlock(nn.Module):
         plan = T.moe_permute_plan(top_indices, e)                          # stable sort by expert
         if _wants_grad(x, top_weights, w_in, self.expert_down, b_in, self.expert_down_bias):
             _trainable_widths(d, w_in.shape[1], self.expert_down.shape[2])
-            if self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None:
+            dropping = self.training and self.expert_dropout.p > 0
+            if self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None and not dropping:
                 # SwiGLU without biases: every element-wise step runs inside a quantizer kernel
                 out = _ExpertFFN.apply(x_flat.to(torch.bfloat16), top_weights, w_in.to(torch.bfloat16),
                                        self.expert_down.to(torch.bfloat16), *plan).to(x.dtype)
             else:
                 y = _expert_ffn_general(x_flat.to(torch.bfloat16), w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
                                         b_in, self.expert_down_bias, self.act_fn, self.gated, plan)
-                out = _UnpermuteFn.apply(y, top_weights, b * s, *plan).to(x.dtype)
+                out = _UnpermuteFn.apply(self.expert_dropout(y), top_weights, b * s, *plan).to(x.dtype)
         else:
             a, sfa = T.moe_gather_mxfp8(x_flat.to(torch.bfloat16), plan)      # permute fused with MXFP8
             y = _grouped_ffn_padded(a, sfa, plan, w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
                                     self.act_fn, self.gated, b_in, self.expert_down_bias)
-            out = T.moe_unpermute(y, top_weights.to(torch.bfloat16), plan.row_of, b * s).to(x.dtype)
+            out = T.moe_unpermute(self.expert_dropout(y), top_weights.to(torch.bfloat16), plan.row_of, b * s).to(x.dtype)
 
         counts = torch.diff(plan.offs, prepend=plan.offs.new_zeros(1))
         self.expert_load.record_load(counts.detach(), self.training)

@@ -554,6 +554,29 @@ def test_block_trains_with_any_activation_and_biases(ops, gated, activation, bia
     assert _rel(x.grad.reshape(t, d), xr.grad) < 1.5e-1
 
 
+def test_expert_dropout(ops):
+    from pretrain_b200.layers.mlp import SparseMoEBlock
+    torch.manual_seed(6)
+    d, inter, e, k, t = 256, 128, 8, 2, 1024
+    kw = dict(intermediate_size=inter, n_routed_experts=e, n_routed_experts_per_token=k, router_score_fn="softmax", aux_loss=False)
+    plain, drop = SparseMoEBlock(d, **kw).cuda(), SparseMoEBlock(d, dropout=0.5, **kw).cuda()
+    with torch.no_grad():
+        plain.expert_gate_up.normal_(std=0.05)
+        plain.expert_down.normal_(std=0.05)
+    drop.load_state_dict(plain.state_dict())
+    x = torch.randn(1, t, d, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        want = plain.eval()(x)[0]
+        assert torch.equal(drop.eval()(x)[0], want)                       # identity outside training
+    xg = x.clone().requires_grad_(True)
+    out = drop.train()(xg)[0]
+    out.float().square().mean().backward()
+    assert torch.isfinite(xg.grad).all() and torch.isfinite(drop.expert_down.grad).all()
+    # each expert output element survives with probability 1/2 and is doubled: same mean, about twice the energy
+    ratio = (out.float().norm() / want.float().norm()).item()
+    assert 1.1 < ratio < 1.8 and _rel(out, want) > 0.5
+
+
 @pytest.mark.parametrize("train", [True, False])
 def test_sparse_moe_block_traces_with_torch_compile(ops, train):
     """The reference compiles the whole model (src/training/trainer.py:176-177): the block must trace without a

@@ -166,6 +166,7 @@ def test_moe_block_host_state_matches_the_reference_layout():
     assert sorted(n for n, _ in blk.named_parameters()) == ["expert_down", "expert_gate_up", "router.gate.weight",
                                                             "shared_expert.down_proj.weight", "shared_expert.gate_up_proj.weight"]
     assert blk.shared_expert.down_proj.in_features == 2 * 32
+    assert SparseMoEBlock(64, intermediate_size=32, n_routed_experts=4, n_routed_experts_per_token=2, dropout=0.25).expert_dropout.p == 0.25
     assert "expert_load.train_load" not in blk.state_dict() and "router.expert_bias.bias" in blk.state_dict()
     with pytest.raises(ValueError):
         SparseMoEBlock(64, intermediate_size=32, n_routed_experts=4, n_routed_experts_per_token=2, aux_loss=True, expert_bias=True)
