@@ -257,13 +257,15 @@ def grouped_mlp(x, w_in, w_down, act_fn, offs, gated, row_expert_ids=None, b_in=
 
     x is (R, D) with rows grouped by expert and ``offs`` the (E,) int32 cumulative end offsets
     (offs[-1] == R); weights are (E, out, in); empty groups are fine; biases, when given, are
-    (E, out) and are added per row.  Returns (R, D_out) in bf16, rows in the input order.  With inputs that
+    (E, out) and are added per row.  Returns (R, D_out), rows in the input order (computed in MXFP8 with bf16
+    outputs, returned in the autocast dtype or else x's dtype).  With inputs that
     require grad the general trainable path runs (MXFP8 backward GEMMs; widths as _trainable_widths says).
     """
     if not x.is_cuda:
         raise RuntimeError("grouped_mlp runs on the B200 kernels only (no CPU path)")
     r = x.shape[0]
     e = w_in.shape[0]
+    in_dtype = x.dtype
     plan = T.moe_pad_plan(offs, r)
     # padded row of every input row (the inverse of the plan's src_of_row): its expert's padded start + its rank there
     rows = torch.arange(r, device=x.device)
@@ -279,7 +281,10 @@ def grouped_mlp(x, w_in, w_down, act_fn, offs, gated, row_expert_ids=None, b_in=
         x, w_in, w_down = x.to(torch.bfloat16), w_in.to(torch.bfloat16), w_down.to(torch.bfloat16)
         a, sfa = T.moe_gather_mxfp8(x, plan)
         out_p = _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in, b_down)
-    return out_p[row_of]                                                # back to the caller's unpadded row order
+    # back to the caller's unpadded row order, in the dtype the reference's matmuls would return: the autocast
+    # dtype when autocast is on, else the input's (tests/fast/layers/test_mlp.py:1065-1084)
+    out_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else in_dtype
+    return out_p[row_of].to(out_dtype)
 
 
 def _cached(param: torch.Tensor, slot: str, key, make):
