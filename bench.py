@@ -389,7 +389,7 @@ def run_moe_training(args, t, d, inter, rank, world, local):
     FLOP = 3 x the forward's GEMM FLOP (fprop, dgrad, wgrad of both layers)."""
     from oracle import restate as R
     from pretrain_b200 import build, ops
-    from pretrain_b200.layers.mlp import _ExpertFFN
+    from pretrain_b200.layers.mlp import _ExpertFFN, _expert_weight_copies      # plain tensors: quantized every step
     from pretrain_b200 import torch_ops as T
     if rank == 0:
         build.build()
@@ -402,7 +402,8 @@ def run_moe_training(args, t, d, inter, rank, world, local):
     dout = torch.randn(t, d, device="cuda", dtype=torch.bfloat16)
 
     def step():
-        out = _ExpertFFN.apply(x, top_w, w_gu, w_d, *T.moe_permute_plan(top_i, e))
+        out = _ExpertFFN.apply(x, top_w, w_gu, w_d, *_expert_weight_copies(w_gu, "dual"), *_expert_weight_copies(w_d, "dual"),
+                               *T.moe_permute_plan(top_i, e))
         return torch.autograd.grad(out, (x, top_w, w_gu, w_d), dout)
 
     for _ in range(max(args.warmup, 3)):
@@ -448,7 +449,8 @@ def run_moe_training(args, t, d, inter, rank, world, local):
 
     def e2e_step():
         xx = hx.to("cuda", non_blocking=True).requires_grad_(True)
-        out = _ExpertFFN.apply(xx, top_w, w_gu, w_d, *T.moe_permute_plan(top_i, e))
+        out = _ExpertFFN.apply(xx, top_w, w_gu, w_d, *_expert_weight_copies(w_gu, "dual"), *_expert_weight_copies(w_d, "dual"),
+                               *T.moe_permute_plan(top_i, e))
         (gx,) = torch.autograd.grad(out, (xx,), hd.to("cuda", non_blocking=True))
         hgx.copy_(gx, non_blocking=True)
 

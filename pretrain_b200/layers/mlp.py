@@ -86,15 +86,14 @@ class _ExpertFFN(torch.autograd.Function):
               the `mxfp8` recipe."""
 
     @staticmethod
-    def forward(ctx, x, top_w, w_in, w_down, *plan_tensors):
+    def forward(ctx, x, top_w, w_in, w_down, w1r, w1sr, w1c, w1sc, w2r, w2sr, w2c, w2sc, *plan_tensors):
+        # w1* / w2*: both MXFP8 copies of the weight stacks, (E*2I, D) | (D, E*2I) and (E*D, I) | (I, E*D)
         plan = T.MoEPlan(*plan_tensors)
         t, d = x.shape
         e, n1, _ = w_in.shape
         inter = n1 // 2
         # every element-wise step hands its result to the both-directions quantizer inside one kernel
         ar, asr, ac, asc = T.moe_gather_quantize_dual(x, plan, E4M3)                          # (R, D) | (D, R), pad rows zero
-        w1r, w1sr, w1c, w1sc = T.quantize_mxfp8_dual(w_in.reshape(e * n1, d), E4M3, SWZ)       # (E*2I, D) | (D, E*2I)
-        w2r, w2sr, w2c, w2sc = T.quantize_mxfp8_dual(w_down.reshape(e * d, inter), E4M3, SWZ)  # (E*D, I)  | (I, E*D)
         g = T.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, n1)                        # (R, 2I) bf16, kept for backward
         if inter % 128 == 0:
             hr, hsr, hc, hsc = T.swiglu_quantize_dual(g, E4M3)
@@ -122,7 +121,7 @@ class _ExpertFFN(torch.autograd.Function):
         dw1 = T.grouped_gemm_mxfp8_wgrad(dgc, dgsc, ac, asc, plan, E5M2, E4M3)                 # (E, 2I, D)
         dx = T.moe_unpermute(da, None, plan.row_of, t)                                           # sum over the k slots
         xd, twd, w1d, w2d = ctx.dtypes
-        return (dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d)) + (None,) * len(plan_tensors)
+        return (dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d)) + (None,) * (8 + len(plan_tensors))
 
 
 class _GroupedLinearFn(torch.autograd.Function):
@@ -227,15 +226,15 @@ def _grouped_ffn_padded(a, sfa, plan, w_in, w_down, act_fn, gated, b_in=None, b_
     """Both grouped GEMMs and the activation on the padded layout; returns (padded_rows, D_out) bf16
     (written into `out` when given and the expert width needs no padding)."""
     n1, n2 = w_in.shape[1], w_down.shape[1]
-    wq2, wsf2 = _quantize_expert_weights(w_down)
+    wq2, wsf2 = _expert_weight_copies(w_down, "rows")
     e = w_in.shape[0]
     if gated and act_fn is silu_glu and b_in is None and n1 % 128 == 0:
         # SwiGLU and the re-quantization run in the first GEMM's epilogue: the weights are stored with
         # gate and up rows interleaved so that a thread of the epilogue holds a whole block of h
-        wq1, wsf1 = T.quantize_mxfp8_glu_rows(w_in.reshape(-1, w_in.shape[2]), e, n1 // 2)
+        wq1, wsf1 = _expert_weight_copies(w_in, "glu")
         hq, hsf = T.grouped_gemm_mxfp8_swiglu(a, sfa, wq1, wsf1, plan, n1)
     else:
-        wq1, wsf1 = _quantize_expert_weights(w_in)
+        wq1, wsf1 = _expert_weight_copies(w_in, "rows")
         h = T.grouped_gemm_mxfp8(a, sfa, wq1, wsf1, plan, wq1.shape[0] // e)[:, :n1]
         if b_in is not None:
             h = h + b_in.to(h.dtype)[_expert_of_padded_row(plan)]
@@ -296,6 +295,26 @@ def _cached(param: torch.Tensor, slot: str, key, make):
             hit = (key, make())
         setattr(param, slot, hit)
     return hit[1]
+
+
+def _expert_weight_copies(param: torch.Tensor, kind: str):
+    """Quantized copies of an expert weight stack (E, out, in), kept on the parameter until it is next written
+    (a step made of several micro-batches, or evaluation, quantizes each stack once; under torch.compile they are
+    recomputed in the graph).  kind "dual": (codes, sf) along `in` and along `out` of the (E*out, in) matrix, for
+    fprop / dgrad; "glu": row-wise with gate / up rows interleaved for the SwiGLU epilogue; "rows": row-wise."""
+    e, n, k = param.shape
+
+    def make():
+        w = param.detach().to(torch.bfloat16)
+        if kind == "dual":
+            return T.quantize_mxfp8_dual(w.reshape(e * n, k), E4M3, SWZ)
+        if kind == "glu":
+            return T.quantize_mxfp8_glu_rows(w.reshape(e * n, k), e, n // 2)
+        return _quantize_expert_weights(w)
+
+    if torch.compiler.is_compiling() or not isinstance(param, nn.Parameter):
+        return make()
+    return _cached(param, "_b200q_" + kind, kind, make)
 
 
 def _ffn_flops(d_model: int, d_ff: int, gated: bool, bias: bool) -> int:
@@ -607,16 +626,16 @@ class SparseMoEBlock(nn.Module):
             dropping = self.training and self.expert_dropout.p > 0
             if self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None and not dropping:
                 # SwiGLU without biases: every element-wise step runs inside a quantizer kernel
-                out = _ExpertFFN.apply(x_flat.to(torch.bfloat16), top_weights, w_in.to(torch.bfloat16),
-                                       self.expert_down.to(torch.bfloat16), *plan).to(x.dtype)
+                out = _ExpertFFN.apply(x_flat.to(torch.bfloat16), top_weights, w_in, self.expert_down,
+                                       *_expert_weight_copies(w_in, "dual"), *_expert_weight_copies(self.expert_down, "dual"),
+                                       *plan).to(x.dtype)
             else:
                 y = _expert_ffn_general(x_flat.to(torch.bfloat16), w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
                                         b_in, self.expert_down_bias, self.act_fn, self.gated, plan)
                 out = _UnpermuteFn.apply(self.expert_dropout(y), top_weights, b * s, *plan).to(x.dtype)
         else:
             a, sfa = T.moe_gather_mxfp8(x_flat.to(torch.bfloat16), plan)      # permute fused with MXFP8
-            y = _grouped_ffn_padded(a, sfa, plan, w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
-                                    self.act_fn, self.gated, b_in, self.expert_down_bias)
+            y = _grouped_ffn_padded(a, sfa, plan, w_in, self.expert_down, self.act_fn, self.gated, b_in, self.expert_down_bias)
             out = T.moe_unpermute(self.expert_dropout(y), top_weights.to(torch.bfloat16), plan.row_of, b * s).to(x.dtype)
 
         counts = torch.diff(plan.offs, prepend=plan.offs.new_zeros(1))

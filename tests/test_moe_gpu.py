@@ -554,6 +554,33 @@ def test_block_trains_with_any_activation_and_biases(ops, gated, activation, bia
     assert _rel(x.grad.reshape(t, d), xr.grad) < 1.5e-1
 
 
+def test_expert_weight_copies_are_kept_until_the_weights_change(ops):
+    from pretrain_b200.layers.mlp import SparseMoEBlock
+    torch.manual_seed(8)
+    blk = SparseMoEBlock(256, intermediate_size=128, n_routed_experts=8, n_routed_experts_per_token=2, router_score_fn="softmax",
+                         aux_loss=False).cuda()
+    with torch.no_grad():
+        blk.expert_gate_up.normal_(std=0.05)
+        blk.expert_down.normal_(std=0.05)
+    x = torch.randn(1, 512, 256, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        first = blk(x)[0]
+        kept = blk.expert_gate_up._b200q_glu[1][0]
+        assert blk(x)[0].equal(first) and blk.expert_gate_up._b200q_glu[1][0] is kept          # evaluation: quantized once
+        blk.expert_gate_up.mul_(2.0)                                                            # what an optimizer step does
+        second = blk(x)[0]
+        assert blk.expert_gate_up._b200q_glu[1][0] is not kept and not second.equal(first)
+    # training: two micro-batches share the copies, the optimizer step invalidates them
+    xg = x.clone().requires_grad_(True)
+    blk(xg)[0].float().sum().backward()
+    dual = blk.expert_down._b200q_dual[1][0]
+    blk(xg)[0].float().sum().backward()
+    assert blk.expert_down._b200q_dual[1][0] is dual
+    torch.optim.SGD(blk.parameters(), lr=1e-3).step()
+    blk(xg)[0].float().sum().backward()
+    assert blk.expert_down._b200q_dual[1][0] is not dual
+
+
 def test_expert_dropout(ops):
     from pretrain_b200.layers.mlp import SparseMoEBlock
     torch.manual_seed(6)
