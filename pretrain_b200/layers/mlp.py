@@ -131,14 +131,14 @@ class _GroupedLinearFn(torch.autograd.Function):
     permute is fused into the quantizer; otherwise it is a (padded_rows, K) matrix."""
 
     @staticmethod
-    def forward(ctx, a, w, gather, *plan_tensors):
+    def forward(ctx, a, w, gather, wr, wsr, wc, wsc, *plan_tensors):
+        # wr .. wsc: both MXFP8 copies of the (E*N, K) weight matrix (_expert_weight_copies)
         plan = T.MoEPlan(*plan_tensors)
         e, n, k = w.shape
         if gather:
             ar, asr, ac, asc = T.moe_gather_quantize_dual(a, plan, E4M3)
         else:
             ar, asr, ac, asc = T.quantize_mxfp8_dual(a, E4M3, SWZ)
-        wr, wsr, wc, wsc = T.quantize_mxfp8_dual(w.reshape(e * n, k), E4M3, SWZ)
         ctx.save_for_backward(ac, asc, wc, wsc, *plan_tensors)
         ctx.gather, ctx.tokens, ctx.k = gather, a.shape[0], k
         ctx.dtypes = (a.dtype, w.dtype)
@@ -153,7 +153,7 @@ class _GroupedLinearFn(torch.autograd.Function):
         dw = T.grouped_gemm_mxfp8_wgrad(gc, gsc, ac, asc, plan, E5M2, E4M3)                  # (E, N, K)
         if ctx.gather:
             da = T.moe_unpermute(da, None, plan.row_of, ctx.tokens)                           # sum over the k slots
-        return (da.to(ctx.dtypes[0]), dw.to(ctx.dtypes[1]), None) + (None,) * len(plan_tensors)
+        return (da.to(ctx.dtypes[0]), dw.to(ctx.dtypes[1]), None) + (None,) * (4 + len(plan_tensors))
 
 
 class _UnpermuteFn(torch.autograd.Function):
@@ -184,7 +184,7 @@ def _expert_ffn_general(x, w_in, w_down, b_in, b_down, act_fn, gated, plan):
     """The trainable expert path for any activation and optional biases, up to the expert outputs in the padded
     layout: grouped linear (permute fused) -> (+ bias, activation in torch) -> grouped linear -> (+ bias).  Pad rows
     carry no gradient: their output gradient is zero, so whatever the biases put there never reaches a weight."""
-    g = _GroupedLinearFn.apply(x, w_in, True, *plan)
+    g = _GroupedLinearFn.apply(x, w_in, True, *_expert_weight_copies(w_in, "dual"), *plan)
     rows = _expert_of_padded_row(plan)
     if b_in is not None:
         g = g + b_in.to(g.dtype)[rows]
@@ -193,7 +193,7 @@ def _expert_ffn_general(x, w_in, w_down, b_in, b_down, act_fn, gated, plan):
     live = (plan.tile_expert >= 0).repeat_interleave(128).unsqueeze(-1)
     g = torch.where(live, g, torch.zeros((), dtype=g.dtype, device=g.device))
     h = act_fn(*g.chunk(2, dim=-1)) if gated else act_fn(g)
-    y = _GroupedLinearFn.apply(h.contiguous(), w_down, False, *plan)
+    y = _GroupedLinearFn.apply(h.contiguous(), w_down, False, *_expert_weight_copies(w_down, "dual"), *plan)
     if b_down is not None:
         y = y + b_down.to(y.dtype)[rows]
     return y
@@ -274,8 +274,7 @@ def grouped_mlp(x, w_in, w_down, act_fn, offs, gated, row_expert_ids=None, b_in=
     if _wants_grad(x, w_in, w_down, b_in, b_down):
         _trainable_widths(x.shape[1], w_in.shape[1], w_down.shape[2])
         plan = plan._replace(row_of=row_of.to(torch.int32))          # one "slot" per row: the backward of the gather sums over it
-        out_p = _expert_ffn_general(x.to(torch.bfloat16), w_in.to(torch.bfloat16), w_down.to(torch.bfloat16), b_in, b_down,
-                                    act_fn, gated, plan)
+        out_p = _expert_ffn_general(x.to(torch.bfloat16), w_in, w_down, b_in, b_down, act_fn, gated, plan)
     else:
         x, w_in, w_down = x.to(torch.bfloat16), w_in.to(torch.bfloat16), w_down.to(torch.bfloat16)
         a, sfa = T.moe_gather_mxfp8(x, plan)
@@ -630,8 +629,8 @@ class SparseMoEBlock(nn.Module):
                                        *_expert_weight_copies(w_in, "dual"), *_expert_weight_copies(self.expert_down, "dual"),
                                        *plan).to(x.dtype)
             else:
-                y = _expert_ffn_general(x_flat.to(torch.bfloat16), w_in.to(torch.bfloat16), self.expert_down.to(torch.bfloat16),
-                                        b_in, self.expert_down_bias, self.act_fn, self.gated, plan)
+                y = _expert_ffn_general(x_flat.to(torch.bfloat16), w_in, self.expert_down, b_in, self.expert_down_bias,
+                                        self.act_fn, self.gated, plan)
                 out = _UnpermuteFn.apply(self.expert_dropout(y), top_weights, b * s, *plan).to(x.dtype)
         else:
             a, sfa = T.moe_gather_mxfp8(x_flat.to(torch.bfloat16), plan)      # permute fused with MXFP8
