@@ -753,3 +753,47 @@ def test_sparse_moe_block_full_config(ops):
             y = (_mx_fake(h).float() @ _mx_fake(w_d[e]).float().t()).bfloat16()
             ref[n] += top_w[t, j].float() * y[0].float()
     assert _rel(out.view(-1, 768)[sample], ref) < 2e-2
+
+
+def test_fake_kernels_of_the_moe_ops_describe_the_real_outputs(ops):
+    """torch.compile trusts every custom op's fake kernel for shapes, dtypes and strides: check them against what the
+    real kernels return (torch.library.opcheck, fake-tensor test) on one routed batch."""
+    from pretrain_b200 import torch_ops as T
+    g = torch.Generator().manual_seed(12)
+    t, k, d, e, inter = 384, 2, 256, 8, 128
+    x = torch.randn(t, d, generator=g).bfloat16().cuda()
+    logits = torch.randn(t, e, generator=g).cuda()
+    check = lambda fn, *args: torch.library.opcheck(fn.op, args, test_utils="test_faketensor")
+    check(T.moe_router_topk, logits, k, "softmax", True, None)
+    check(T.moe_router_topk, logits, k, "sigmoid", False, torch.zeros(e, device="cuda"))
+    top_i, top_w, _ = T.moe_router_topk(logits, k, "softmax", True, None)
+    check(T._moe_permute_plan, top_i, e)
+    plan = T.moe_permute_plan(top_i, e)
+    check(T._moe_pad_plan, plan.offs, t * k)
+    check(T._moe_gather_mxfp8, x, plan.src_of_row, plan.num_tiles, 0)
+    check(T._moe_gather_quantize_dual, x, plan.src_of_row, 0)
+    w_in = (0.05 * torch.randn(e, 2 * inter, d, generator=g)).bfloat16().cuda()
+    w_down = (0.05 * torch.randn(e, d, inter, generator=g)).bfloat16().cuda()
+    ar, asr, ac, asc = T.moe_gather_quantize_dual(x, plan, 0)
+    w1r, w1sr, w1c, w1sc = T.quantize_mxfp8_dual(w_in.reshape(-1, d), 0, 1)
+    check(T._grouped_gemm_mxfp8, ar, asr, w1r, w1sr, plan.tile_expert, plan.num_tiles, e, 2 * inter, 0, 0, 0)
+    check(T.quantize_mxfp8_glu_rows, w_in.reshape(-1, d), e, inter)
+    wg, wgs = T.quantize_mxfp8_glu_rows(w_in.reshape(-1, d), e, inter)
+    check(T._grouped_gemm_mxfp8_swiglu, ar, asr, wg, wgs, plan.tile_expert, plan.num_tiles, e, 2 * inter)
+    gu = T.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, 2 * inter)
+    check(T.swiglu, gu)
+    check(T.swiglu_mxfp8, gu, 0)
+    check(T.swiglu_quantize_dual, gu, 0)
+    hr, hsr, hc, hsc = T.swiglu_quantize_dual(gu, 0)
+    w2r, w2sr, w2c, w2sc = T.quantize_mxfp8_dual(w_down.reshape(-1, inter), 0, 1)
+    y = T.grouped_gemm_mxfp8(hr, hsr, w2r, w2sr, plan, d)
+    check(T.moe_unpermute, y, top_w, plan.row_of, t)
+    check(T.moe_unpermute, y, None, plan.row_of, t)
+    dout = torch.randn(t, d, generator=g).bfloat16().cuda()
+    check(T.moe_unpermute_backward_quantize_dual, dout, top_w, plan.row_of, plan.padded_rows, 1, y)
+    check(T._moe_unpermute_backward, dout, top_w, y, plan.row_of, plan.src_of_row)
+    dyr, dysr, dyc, dysc, _ = T.moe_unpermute_backward_quantize_dual(dout, top_w, plan.row_of, plan.padded_rows, 1, y)
+    check(T._grouped_gemm_mxfp8, dyr, dysr, w2c, w2sc, plan.tile_expert, plan.num_tiles, e, inter, 1, 0, 1)
+    check(T._grouped_gemm_mxfp8_wgrad, dyc, dysc, hc, hsc, plan.padded_offs, 1, 0)
+    dh = T.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, plan, inter, 1, 0)
+    check(T.swiglu_backward_quantize_dual, gu, dh, 1)
