@@ -256,3 +256,39 @@ def test_swapped_model_trains_one_step_and_compiles():
     with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
         a, b = model(x), compiled(x)
     assert _rel(a, b) < 5e-2          # Inductor fuses bias add and SiLU with other roundings; requantization amplifies them
+
+
+def test_fake_kernels_of_the_linear_ops_describe_the_real_outputs():
+    """Shapes, dtypes and strides the compiler assumes for every custom op of the linear path against what the kernels
+    return (torch.library.opcheck, fake-tensor test)."""
+    from pretrain_b200 import build, torch_ops as T
+    build.build()
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(256, 384, generator=g).bfloat16().cuda()
+    w = torch.randn(512, 384, generator=g).bfloat16().cuda()
+    check = lambda fn, *args: torch.library.opcheck(fn.op, args, test_utils="test_faketensor")
+    check(T.amax, x)
+    for axis in (1, 0):
+        check(T.quantize_fp8, x, 0, axis)
+        check(T.quantize_int8, x, 127, axis)
+        for layout in (0, 1):
+            check(T.quantize_mxfp8, x, axis, 1, layout)
+            check(T.quantize_nvfp4, x, axis, layout)
+    check(T.quantize_fp8_both, x, 1)
+    for transpose in (False, True):
+        check(T.quantize_fp8_tensorwise, x, 0, transpose)
+        check(T.quantize_int8_tensorwise, x, 31, transpose)
+    for layout in (0, 1):
+        check(T.quantize_mxfp8_dual, x, 0, layout)
+    xq, xs = T.quantize_fp8(x, 0, 1)
+    wq, ws = T.quantize_fp8(w, 0, 1)
+    check(T.gemm_fp8, xq, 0, wq, 0, xs, ws)
+    xi, xis = T.quantize_int8(x, 127, 1)
+    wi, wis = T.quantize_int8(w, 127, 1)
+    check(T.gemm_int8, xi, wi, xis, wis)
+    xm, xms = T.quantize_mxfp8(x, 1, 0, 1)
+    wm, wms = T.quantize_mxfp8(w, 1, 0, 1)
+    check(T.gemm_mxfp8, xm, xms, wm, wms, 0, 0)
+    xn, xns, xnt = T.quantize_nvfp4(x, 1, 1)
+    wn, wns, wnt = T.quantize_nvfp4(w, 1, 1)
+    check(T.gemm_nvfp4, xn, xns, xnt, wn, wns, wnt)
