@@ -250,21 +250,27 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
 }
 
 // scales[c] = scale(max over the CTAs' partial column maxima)
-__global__ void __launch_bounds__(1024)
+constexpr int kRedWords = 8, kRedSlices = 128;        // a CTA: 8 packed column pairs (one 32-byte sector per row) x 128 row slices
+__global__ void __launch_bounds__(kRedWords * kRedSlices)
 col_partials_to_scale_kernel(const unsigned int* __restrict__ partials, int nparts, int64_t cols, int fmt, float qmax,
                              float* __restrict__ scales) {
-  // 32 packed column pairs x 32 slices of the partial rows per CTA: enough loads in flight to hide their latency
-  __shared__ uint32_t red[32][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int64_t wi = (int64_t)blockIdx.x * 32 + tx, half = cols >> 1;
+  // few loads per thread (nparts / 128), many CTAs: the reduction is a chain of load latencies, not of bytes
+  __shared__ uint32_t red[kRedSlices][kRedWords + 1];
+  const int tx = threadIdx.x & (kRedWords - 1), ty = threadIdx.x / kRedWords;
+  const int64_t wi = (int64_t)blockIdx.x * kRedWords + tx, half = cols >> 1;
   uint32_t m = 0;
   if (wi < half)
-    for (int p = ty; p < nparts; p += 32) m = absmax_bf16x2(m, partials[(int64_t)p * half + wi]);
+    for (int p = ty; p < nparts; p += kRedSlices) m = absmax_bf16x2(m, partials[(int64_t)p * half + wi]);
   red[ty][tx] = m;
+  __syncthreads();
+  if (ty < 8) {                                        // 128 slices -> 8 -> 1
+    for (int j = ty + 8; j < kRedSlices; j += 8) m = absmax_bf16x2(m, red[j][tx]);
+    red[ty][tx] = m;
+  }
   __syncthreads();
   if (ty == 0 && wi < half) {
 #pragma unroll
-    for (int j = 1; j < 32; ++j) m = absmax_bf16x2(m, red[j][tx]);
+    for (int j = 1; j < 8; ++j) m = absmax_bf16x2(m, red[j][tx]);
     scales[2 * wi] = scale_from_amax(bf16lo(m), fmt, qmax);
     scales[2 * wi + 1] = scale_from_amax(bf16hi(m), fmt, qmax);
   }
@@ -957,7 +963,8 @@ int b200q_quantize_fp8_both(const void* x, int64_t rows, int64_t cols, int64_t l
 #undef B200Q_GO
   B200Q_CUDA(cudaGetLastError());
   // pass 2: column scales, then the transposed codes
-  col_partials_to_scale_kernel<<<(unsigned)((cols / 2 + 31) / 32), 1024, 0, st>>>(parts, grid, cols, fmt, 0.f, scales_col);
+  col_partials_to_scale_kernel<<<(unsigned)((cols / 2 + kRedWords - 1) / kRedWords), kRedWords * kRedSlices, 0, st>>>(parts, grid, cols, fmt,
+                                                                                                                0.f, scales_col);
   B200Q_CUDA(cudaGetLastError());
   launch_fp8_cols(xp, rows, cols, ld, fmt, (uint8_t*)codes_col, scales_col, st);     // the second read comes mostly from L2
   B200Q_CUDA(cudaGetLastError());
