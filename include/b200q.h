@@ -4,7 +4,9 @@
  *   - returns an int status (0 = ok, < 0 = B200Q_ERR_*), never throws, aborts or traps;
  *   - is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy stream);
  *   - works on buffers the caller owns, on the current device;
- *   - allocates nothing.
+ *   - allocates nothing;
+ *   - may be called from several host threads at once (no shared host state), with the two
+ *     b200q_debug_* hooks at the end of this file as the only exception.
  *
  * The path these replace is the quantized-linear path of gongyisheng/pretrain, which is
  * Python calling torch library kernels; each entry names the reference lines it stands for.
@@ -175,6 +177,19 @@ int b200q_gemm_nvfp4_allgather(const void* A, const void* sfA, const void* B, co
                                const float* tsA, const float* tsB, int64_t M, int64_t N, int64_t K,
                                void* const* D_all, int world, int rank, int64_t ldd, void* stream);
 
+/* The same fused GEMM + all-gather with the output leaving as MXFP8 instead of bf16, for the case where the
+ * consumer of the gathered matrix is the next block-scaled GEMM (which would quantize the bf16 matrix along its
+ * columns first thing, src/quant/linear.py:72-76): every accumulator is rounded to bf16 and then quantized as
+ * b200q_quantize_mxfp8(axis = 1, B200Q_E4M3, B200Q_SF_SWIZZLE_128x4) quantizes that bf16 matrix, bit for bit, and
+ * what crosses NVLink is 1 code byte per element plus 1 scale byte per 32 - 1.03 bytes instead of 2.
+ * C_all[g]: codes [world*M, N] of rank g (pitch ldc bytes, ldc % 16 == 0); SF_all[g]: its scale factors,
+ * b200q_sf_bytes(world*M, N/32, B200Q_SF_SWIZZLE_128x4) bytes.  The pair (C_all[g], SF_all[g]) is directly the A
+ * operand of b200q_gemm_mxfp8 with K = N.  M % 128 == 0, N % 128 == 0.  world = 1 (C_all = {C}, SF_all = {SF},
+ * rank 0) is a plain GEMM with MXFP8 output.  New functionality: the reference is single-GPU. */
+int b200q_gemm_mxfp8_allgather_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
+                                     const void* sfB, int64_t M, int64_t N, int64_t K, void* const* C_all,
+                                     void* const* SF_all, int world, int rank, int64_t ldc, void* stream);
+
 /* Fused GEMM + reduce-scatter, first half (new functionality: the data-parallel wgrad the reference, being
  * single-GPU, never needs; src/quant/linear.py:102-109 is the GEMM).  Every rank computes its own [M, N]
  * partial result (e.g. dW from its shard of the tokens); the sum over the ranks is wanted scattered by
@@ -289,7 +304,8 @@ int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantiz
  *
  * B must hold the N = 2I weight rows (per expert) in GLU-INTERLEAVED order: rows 64j .. 64j+31 are
  * gate rows 32j .. 32j+31 and rows 64j+32 .. 64j+63 are the up rows of the same outputs
- * (b200q_quantize_mxfp8_rowmap writes them so).  N % 64 == 0.
+ * (b200q_quantize_mxfp8_rowmap writes them so).  N % 64 == 0; grouped form: N % 128 == 0, so that
+ * every expert's rows of B start a 128-row scale-factor group.
  * H: E4M3 codes [M, N/2], pitch ldh bytes (ldh % 16 == 0); sfH: 128x4-tiled scale factors over
  * (M, N/64), b200q_sf_bytes(M, N/64, B200Q_SF_SWIZZLE_128x4) bytes. */
 int b200q_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt,
@@ -389,10 +405,11 @@ int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y,
  * bf16 [T, E] (optional); expert_counts[e] = tokens that chose e (int32 [E], optional).  Equal
  * probs are ordered by logit, then by expert index.  select_bias (fp32 [E], optional): the experts are
  * chosen by prob + select_bias, the load-balancing bias of src/layers/mlp.py:182-216,295-297, while the
- * weights stay the chosen experts' probs.  E <= 256, k <= 32. */
+ * weights stay the chosen experts' probs.  out_fp32 != 0: top_w and probs are written as fp32 instead
+ * of bf16 (the reference returns them in the activations' dtype, :302).  E <= 256, k <= 32. */
 int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int score_fn, int normalize,
                           int64_t* top_idx, void* top_w, void* probs, int32_t* expert_counts,
-                          const float* select_bias, void* stream);
+                          const float* select_bias, int out_fp32, void* stream);
 
 /* Weighted unpermute (src/layers/mlp.py:472-477): out[t, :] = sum_j w[t, j] * y[row_of[t*k+j], :],
  * accumulated in fp32 and rounded once to bf16.  y bf16 [padded_rows, D] pitch ldy; w bf16 [T, k], or
@@ -405,6 +422,16 @@ int b200q_moe_unpermute(const void* y, int64_t ldy, const void* w, const int32_t
  * token_ids_sorted / weights_sorted, src/layers/mlp.py:446-458). */
 int b200q_moe_pair_of_row(const int32_t* row_of, int64_t n_pairs, int64_t padded_rows,
                           int32_t* pair_of_row, void* stream);
+
+/* ---- test hooks ------------------------------------------------------------------------------
+ * Process-wide switches that override the kernel choice every later GEMM call makes, for tests that
+ * want to run one shape through every kernel form.  They are plain global variables: not thread-safe,
+ * not per device, and not meant for production callers (which never need them: 0 = choose by shape
+ * is the default).  No counterpart in the reference.
+ *   b200q_debug_set_gemm_bn(bn):    N tile width of the one-CTA kernel, 128 / 192 / 256; 0 = by shape.
+ *   b200q_debug_set_gemm_pair(mode): 1 = CTA-pair kernel whenever the shape allows, -1 = never, 0 = by shape. */
+int b200q_debug_set_gemm_bn(int bn);
+int b200q_debug_set_gemm_pair(int mode);
 
 #ifdef __cplusplus
 }

@@ -34,6 +34,7 @@ SIGNATURES = {
     "b200q_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_fp8_allgather": (_int, [_vp, _int, _vp, _int, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),
     "b200q_gemm_mxfp8_allgather": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),
+    "b200q_gemm_mxfp8_allgather_mxfp8": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _vp, _int, _int, _i64, _vp]),
     "b200q_gemm_mxfp8_scatter": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),
     "b200q_sum_slots": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_nvfp4_allgather": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),
@@ -64,11 +65,10 @@ SIGNATURES = {
     "b200q_moe_combine_peers": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _i64, _int, _i64, _vp, _vp]),
     "b200q_swiglu_backward": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
     "b200q_moe_unpermute_backward": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _int, _i64, _i64, _vp, _vp, _vp]),
-    "b200q_moe_router_topk": (_int, [_vp, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_moe_router_topk": (_int, [_vp, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "b200q_moe_unpermute": (_int, [_vp, _i64, _vp, _vp, _i64, _int, _i64, _vp, _vp]),
     "b200q_moe_pair_of_row": (_int, [_vp, _i64, _i64, _vp, _vp]),
-}
-DEBUG_SIGNATURES = {
+    # test hooks (process-wide kernel-choice overrides; see the end of include/b200q.h)
     "b200q_debug_set_gemm_bn": (_int, [_int]),
     "b200q_debug_set_gemm_pair": (_int, [_int]),
 }
@@ -84,7 +84,7 @@ def load() -> ctypes.CDLL:
                 f"{LIB_PATH} is missing: build it with `python -m pretrain_b200.build` "
                 "(there is no CPU or PyTorch fallback for this path)")
         lib = ctypes.CDLL(LIB_PATH)
-        for name, (res, args) in {**SIGNATURES, **DEBUG_SIGNATURES}.items():
+        for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
         _lib = lib

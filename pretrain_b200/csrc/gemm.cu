@@ -113,10 +113,11 @@ struct GemmParams {
   int n_experts;                //        and writes rows [e*M, (e+1)*M) of the output
 };
 
-enum { EPI_BF16 = 0, EPI_GLU = 1, EPI_GLU_BF16 = 2 };   // plain output; SwiGLU -> MXFP8 codes; SwiGLU -> bf16 + amax
-// Threads per CTA: producer warp, MMA warp and one (bf16 output) or two (SwiGLU epilogue) groups
+// plain output; SwiGLU -> MXFP8 codes; SwiGLU -> bf16 + amax; output quantized to MXFP8 (codes + scale bytes)
+enum { EPI_BF16 = 0, EPI_GLU = 1, EPI_GLU_BF16 = 2, EPI_MXQ = 3 };
+// Threads per CTA: producer warp, MMA warp and one (bf16 or MXFP8 output) or two (SwiGLU epilogue) groups
 // of four epilogue warps.
-__host__ __device__ constexpr int gemm_threads(int epi) { return epi == EPI_BF16 ? 192 : 320; }
+__host__ __device__ constexpr int gemm_threads(int epi) { return epi == EPI_BF16 || epi == EPI_MXQ ? 192 : 320; }
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m, int& n) {
   constexpr int GM = 16;   // m-blocks per raster group: concurrent CTAs share A and B tiles through L2
@@ -137,7 +138,7 @@ struct Tile {
   int64_t brow0;       // first row of the B tile
   int64_t bk0;         // K offset (bytes) of the B operand
   int64_t drow_off;    // row offset of the output tile
-  float keep;          // 0 for an expert without rows (its single dummy K step is multiplied away), else 1
+  bool zero;           // expert without rows: no K step runs, the epilogue stores zeros
 };
 
 template <int BN>
@@ -151,16 +152,15 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, int t, int num_m) 
   }
   tile_coords(local, num_m, p.num_n, ti.m_blk, ti.n_blk);
   if (p.tile_expert != nullptr) e = __ldg(p.tile_expert + ti.m_blk);
-  ti.k0 = 0; ti.nk = p.num_k; ti.sfb_k0 = 0; ti.bk0 = 0; ti.drow_off = 0; ti.keep = 1.f;
+  ti.k0 = 0; ti.nk = p.num_k; ti.sfb_k0 = 0; ti.bk0 = 0; ti.drow_off = 0; ti.zero = false;
   ti.brow0 = (int64_t)ti.n_blk * BN;
   if (p.ragged_offs != nullptr) {
     const int r0 = __ldg(p.ragged_offs + e), r1 = __ldg(p.ragged_offs + e + 1);
     ti.k0 = r0 >> 7;
     ti.nk = (r1 - r0) >> 7;
-    if (ti.nk <= 0) {                      // no rows: run one in-range K step and scale it to zero
-      ti.nk = 1;
-      ti.k0 = ti.k0 < p.num_k ? ti.k0 : p.num_k - 1;
-      ti.keep = 0.f;
+    if (ti.nk <= 0) {                      // no rows: nothing is loaded or multiplied (the operands there may hold
+      ti.nk = 0;                           // anything, NaN included); the epilogue writes zeros
+      ti.zero = true;
     }
     ti.sfb_k0 = 0;
     ti.drow_off = (int64_t)e * p.M;
@@ -349,7 +349,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       ptx::tc_fence_after();
       const int64_t row0 = ti.drow_off + (int64_t)m_blk * BM + q * 32, row = row0 + lane;
       const int64_t col0 = (int64_t)n_blk * BN;
-      float row_scale = alpha * ti.keep;
+      float row_scale = alpha;
       if (row_scaled(KIND)) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
@@ -364,14 +364,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(release_bar);
       };
-      if (EPI != EPI_BF16)
+      if constexpr (EPI == EPI_MXQ)
+        epilogue_tile_mxq<NBLK, C::EPI_BUFS, RELEASE_AFTER>(taddr, C::OVERLAP && acc == 0, row0, col0, m_out, p.N, alpha, &outs, epi_s,
+                                                            epi_g, buf, lane, release);
+      else if constexpr (EPI != EPI_BF16)
         // the two warp groups swap block sets from tile to tile, so an odd block count evens out
         epilogue_tile_glu<EPI == EPI_GLU ? GLU_MX : GLU_BF16, NBLK, RELEASE_AFTER, 2>(
             taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, p.M, p.N, alpha, p.glu, release);
       else
         epilogue_tile<row_scaled(KIND), KIND == KIND_I8, NBLK, C::EPI_BUFS, RELEASE_AFTER>(
-            taddr, C::OVERLAP && acc == 0, row0, col0, m_out, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
-            release);
+            taddr, C::OVERLAP && acc == 0, ti.zero, row0, col0, m_out, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf,
+            lane, release);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (lane == 0) ptx::bulk_wait<0>();           // all stores of this warp have landed
@@ -428,6 +431,7 @@ struct OutSpec {
   void* ptr[kMaxOutputs];
   int count;
   int64_t scatter_rows;    // > 0: output g is [scatter_rows, N] and receives the rows g * scatter_rows ... of the result
+  void* sf[kMaxOutputs];   // MXFP8-quantized output: this rank's first scale-factor tile in output g (ptr[g] are codes)
 };
 inline OutSpec one_output(void* D) {
   OutSpec o = {};
@@ -448,6 +452,20 @@ int make_out_maps(OutMaps* om, const OutSpec& outs, int64_t M, int64_t N, int64_
   return B200Q_OK;
 }
 
+// the same for an MXFP8-quantized output: byte matrices of codes [M, N] pitch ldc, box = 128 columns x 32 rows
+int make_code_maps(OutMaps* om, const OutSpec& outs, int64_t M, int64_t N, int64_t ldc) {
+  om->count = outs.count;
+  om->scatter_rows = 0;
+  om->sf_kt = (N / 32 + 3) / 4;
+  for (int g = 0; g < outs.count; ++g) {
+    int rc = encode_2d(&om->m[g], CU_TENSOR_MAP_DATA_TYPE_UINT8, outs.ptr[g], N, M, ldc, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    om->sf[g] = static_cast<uint8_t*>(outs.sf[g]);
+  }
+  for (int g = outs.count; g < kMaxOutputs; ++g) { om->m[g] = om->m[0]; om->sf[g] = om->sf[0]; }
+  return B200Q_OK;
+}
+
 template <int KIND, int BN, int EPI = EPI_BF16>
 int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, GemmParams p, cudaStream_t st) {
   using C = Cfg<KIND, BN>;
@@ -455,12 +473,14 @@ int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t 
   const int64_t b_row_bytes = p.b_along_k ? row_bytes * p.n_experts : row_bytes;      // a transposed weight stack is [N, E*K]
   const int64_t m_out = p.ragged_offs != nullptr ? p.M * p.n_experts : p.M;
   CUtensorMap ma, mb;
-  OutMaps md;
+  OutMaps md = {};
   int rc;
   // operands: byte matrices [rows, row_bytes], box = 128 bytes x tile rows, 128-byte swizzle
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, p.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, b_row_bytes, b_rows, b_row_bytes, BKB, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if (EPI != EPI_BF16) {
+  if (EPI == EPI_MXQ) {
+    if ((rc = make_code_maps(&md, D, m_out, p.N, ldd))) return rc;
+  } else if (EPI != EPI_BF16) {
     md.count = 0; md.scatter_rows = 0;                       // no TMA-stored output: the epilogue writes its results itself
     for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
   } else if ((rc = make_out_maps(&md, D, m_out, p.N, ldd))) {
@@ -541,6 +561,18 @@ int dispatch_glu(const void* A, const void* B, int64_t b_rows, const GemmParams&
     case 128: return launch<KIND_MX, 128, EPI_GLU>(A, B, none, 0, b_rows, p, st);
     case 192: return launch<KIND_MX, 192, EPI_GLU>(A, B, none, 0, b_rows, p, st);
     case 256: return launch<KIND_MX, 256, EPI_GLU>(A, B, none, 0, b_rows, p, st);
+    default: return B200Q_ERR_INVALID_ARG;
+  }
+}
+
+// MXFP8 GEMM whose output leaves as MXFP8 codes + scale bytes (tile widths with an even number of 64-column blocks).
+int dispatch_mxq(const void* A, const void* B, const OutSpec& D, int64_t ldc, const GemmParams& p, cudaStream_t st) {
+  if (pair_eligible(p.M, p.N, p.K, false)) return launch_pair<KIND_MX, EPI_MXQ>(A, B, D, ldc, p, st);
+  int bn = g_force_bn ? g_force_bn : choose_bn<KIND_MX>(p.M, p.N, p.K);
+  if (bn == 192) bn = 256;
+  switch (bn) {
+    case 128: return launch<KIND_MX, 128, EPI_MXQ>(A, B, D, ldc, p.N, p, st);
+    case 256: return launch<KIND_MX, 256, EPI_MXQ>(A, B, D, ldc, p.N, p, st);
     default: return B200Q_ERR_INVALID_ARG;
   }
 }
@@ -706,7 +738,8 @@ int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const vo
   if (rc) return rc;
   if (sfA == nullptr || sfB == nullptr || tile_expert == nullptr || num_tiles == nullptr || E <= 0 || (a_fmt | b_fmt) & ~1)
     return B200Q_ERR_INVALID_ARG;
-  if ((padded_rows & 127) || (N & 31) || (int64_t)E * N > INT32_MAX) return B200Q_ERR_SHAPE;
+  // N % 128: expert e's rows of B start at e*N, which must be the start of a 128-row scale-factor group
+  if ((padded_rows & 127) || (N & 127) || (int64_t)E * N > INT32_MAX) return B200Q_ERR_SHAPE;
   if (!aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
@@ -727,7 +760,7 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
                                     const int32_t* tile_expert, const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
                                     int64_t K, void* H, int64_t ldh, void* sfH, void* stream) {
   if (tile_expert == nullptr || num_tiles == nullptr || E <= 0) return B200Q_ERR_INVALID_ARG;
-  if ((padded_rows & 127) || (int64_t)E * N > INT32_MAX) return B200Q_ERR_SHAPE;
+  if ((padded_rows & 127) || (N & 127) || (int64_t)E * N > INT32_MAX) return B200Q_ERR_SHAPE;
   GemmParams p;
   int rc = prepare_glu(&p, A, sfA, B, sfB, a_fmt, b_fmt, padded_rows, N, K, H, ldh, sfH, true, (cudaStream_t)stream);
   if (rc) return rc;
@@ -826,6 +859,34 @@ int b200q_gemm_mxfp8_allgather(const void* A, int a_fmt, const void* sfA, const 
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   p.M = M; p.N = N; p.K = K;
   return dispatch<KIND_MX>(A, B, outs, ldd, N, p, (cudaStream_t)stream);
+}
+
+int b200q_gemm_mxfp8_allgather_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
+                                     int64_t N, int64_t K, void* const* C_all, void* const* SF_all, int world, int rank,
+                                     int64_t ldc, void* stream) {
+  if (A == nullptr || B == nullptr || sfA == nullptr || sfB == nullptr || C_all == nullptr || SF_all == nullptr || M <= 0 || N <= 0 ||
+      K <= 0 || ldc < N || world < 1 || world > kMaxOutputs || rank < 0 || rank >= world || ((a_fmt | b_fmt) & ~1))
+    return B200Q_ERR_INVALID_ARG;
+  // whole 128-row scale-factor tiles per rank, whole 128-column chunks (4 scale bytes) per row
+  if ((M & 127) || (N & 127) || (K & 31) || (ldc & 15)) return B200Q_ERR_SHAPE;
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || (int64_t)world * M > INT32_MAX) return B200Q_ERR_SHAPE;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(sfA) || !aligned16(sfB)) return B200Q_ERR_ALIGNMENT;
+  OutSpec outs = {};
+  outs.count = world;
+  const int64_t sf_kt = (N / 32 + 3) / 4;
+  for (int i = 0; i < world; ++i) {                     // the local copy first, then the peers starting with the next rank
+    const int g = (rank + i) % world;
+    if (C_all[g] == nullptr || SF_all[g] == nullptr) return B200Q_ERR_INVALID_ARG;
+    if (!aligned16(C_all[g]) || !aligned16(SF_all[g])) return B200Q_ERR_ALIGNMENT;
+    outs.ptr[i] = static_cast<uint8_t*>(C_all[g]) + (size_t)rank * M * ldc;
+    outs.sf[i] = static_cast<uint8_t*>(SF_all[g]) + (size_t)rank * (M / 128) * sf_kt * 512;
+  }
+  int rc = require_sm100();
+  if (rc) return rc;
+  GemmParams p = {};
+  p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.M = M; p.N = N; p.K = K;
+  return dispatch_mxq(A, B, outs, ldc, p, (cudaStream_t)stream);
 }
 
 int b200q_gemm_mxfp8_scatter(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,

@@ -91,7 +91,7 @@ struct PTile {
   int bk0;             // K offset of B (bytes)
   int sfb_k0;          // first scale atom of B along K
   int64_t drow_off;    // row offset of the output
-  float keep;          // 0: expert without rows (wgrad), the dummy K step is multiplied away
+  bool zero;           // expert without rows (wgrad): no K step runs, the epilogue stores zeros
   bool live;           // this CTA owns output rows
 };
 
@@ -108,7 +108,7 @@ __device__ __forceinline__ void pair_tile_coords(int t, int num_mp, int num_n, i
 template <bool GROUPED>
 __device__ __forceinline__ PTile get_ptile(const PairParams& p, int t, int total_pt, int cta, const int* g_first, const int* g_pairs) {
   PTile ti;
-  ti.k0 = 0; ti.nk = p.num_k; ti.bk0 = 0; ti.sfb_k0 = 0; ti.drow_off = 0; ti.keep = 1.f;
+  ti.k0 = 0; ti.nk = p.num_k; ti.bk0 = 0; ti.sfb_k0 = 0; ti.drow_off = 0; ti.zero = false;
   int mp;
   if (!GROUPED) {
     pair_tile_coords(t, p.num_mp, p.num_n, mp, ti.n_blk);
@@ -127,10 +127,9 @@ __device__ __forceinline__ PTile get_ptile(const PairParams& p, int t, int total
     const int r0 = __ldg(p.ragged_offs + e), r1 = __ldg(p.ragged_offs + e + 1);
     ti.k0 = r0 >> 7;
     ti.nk = (r1 - r0) >> 7;
-    if (ti.nk <= 0) {                                 // no rows: one in-range K step, scaled to zero
-      ti.nk = 1;
-      ti.k0 = ti.k0 < p.num_k ? ti.k0 : p.num_k - 1;
-      ti.keep = 0.f;
+    if (ti.nk <= 0) {                                 // no rows: nothing is loaded or multiplied, zeros are stored
+      ti.nk = 0;
+      ti.zero = true;
     }
     ti.drow_off = (int64_t)e * p.M;
   } else {
@@ -376,7 +375,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int64_t col0 = (int64_t)ti.n_blk * BN;
       // rows this CTA may store: none for the idle half of an expert's odd last pair
       const int64_t m_lim = !ti.live ? 0 : (GROUPED && p.ragged_offs != nullptr ? ti.drow_off + p.M : p.M);
-      float row_scale = alpha * ti.keep;
+      float row_scale = alpha;
       if (row_scaled(KIND)) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
@@ -387,13 +386,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(release_bar);
       };
-      if (EPI != EPI_BF16)
+      if constexpr (EPI == EPI_MXQ)
+        epilogue_tile_mxq<NBLK, 2, RELEASE_AFTER>(taddr, C::OVERLAP && acc == 0, row0, col0, m_lim, p.N, alpha, &outs, epi_s, epi_g, buf,
+                                                  lane, release);
+      else if constexpr (EPI != EPI_BF16)
         epilogue_tile_glu<EPI == EPI_GLU ? GLU_MX : GLU_BF16, NBLK, RELEASE_AFTER, 2>(
             taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, m_lim, p.N, alpha, p.glu, release);
       else
         epilogue_tile<row_scaled(KIND), KIND == KIND_I8, NBLK, 2, RELEASE_AFTER>(
-            taddr, C::OVERLAP && acc == 0, row0, col0, m_lim, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf, lane,
-            release);
+            taddr, C::OVERLAP && acc == 0, ti.zero, row0, col0, m_lim, p.N, row_scale, p.scale_b, p.b_scalar, &outs, epi_s, epi_g, buf,
+            lane, release);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (lane == 0) ptx::bulk_wait<0>();
@@ -428,11 +430,13 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   using C = pair::PCfg<KIND>;
   const int64_t row_bytes = KIND == KIND_NV ? gp.K / 2 : gp.K;
   CUtensorMap ma, mb, msa, msb;
-  OutMaps md;
+  OutMaps md = {};
   int rc;
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, gp.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, row_bytes, gp.N, row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if (EPI != EPI_BF16) {
+  if (EPI == EPI_MXQ) {
+    if ((rc = make_code_maps(&md, D, gp.M, gp.N, ldd))) return rc;
+  } else if (EPI != EPI_BF16) {
     md.count = 0; md.scatter_rows = 0;                       // the SwiGLU epilogues write their results themselves
     for (int g = 0; g < kMaxOutputs; ++g) md.m[g] = ma;
   } else if ((rc = make_out_maps(&md, D, gp.M, gp.N, ldd))) {
@@ -487,7 +491,7 @@ int launch_pair_grouped(const void* A, const void* B, const OutSpec& D, int64_t 
   const int64_t b_row_bytes = gp.b_along_k ? row_bytes * gp.n_experts : row_bytes;
   const int64_t m_out = ragged ? gp.M * gp.n_experts : gp.M;
   CUtensorMap ma, mb, msa, msb;
-  OutMaps md;
+  OutMaps md = {};
   int rc;
   if ((rc = encode_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, row_bytes, gp.M, row_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, B, b_row_bytes, b_rows, b_row_bytes, BKB, pair::HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;

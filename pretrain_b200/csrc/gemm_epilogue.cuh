@@ -20,6 +20,10 @@ struct OutMaps {
   CUtensorMap m[kMaxOutputs];
   int count;
   int scatter_rows;    // 0: every output receives every block; else a multiple of 32
+  // MXFP8-quantized output (epilogue_tile_mxq): the maps above are byte matrices of codes, and sf[g] is where this
+  // rank's rows start in output g's 128x4-tiled scale-factor buffer, which has sf_kt K-tiles per row tile
+  uint8_t* sf[kMaxOutputs];
+  int64_t sf_kt;
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -38,8 +42,10 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
 // order) has been read from tensor memory.
 // ACC_INT: the accumulators are 32-bit integers (kind::i8); they are converted to fp32 with
 // round-to-nearest, then scaled by the row's and the column's scale in that order.
+// `zero` (warp-uniform): the accumulator was never written (a tile without K steps); zeros are stored
+// whatever tensor memory holds.
 template <bool COL_SCALE, bool ACC_INT, int NBLK, int EPI_BUFS, int RELEASE_AFTER, class Release>
-__device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t row0, int64_t col0, int64_t M, int64_t N,
+__device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, bool zero, int64_t row0, int64_t col0, int64_t M, int64_t N,
                                               float row_scale, const float* __restrict__ scale_b, int b_scalar,
                                               const OutMaps* outs, uint32_t epi_s, uint8_t* epi_g, int& buf, int lane,
                                               Release release) {
@@ -94,6 +100,13 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t 
   for (int i = 0; i < NBLK; ++i) {
     const int c = rev ? NBLK - 1 - i : i;
     ptx::tmem_ld_wait();
+    if (zero) {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        if (i & 1) rb[j] = 0;
+        else ra[j] = 0;
+      }
+    }
     if (i == RELEASE_AFTER) release();
     if (i + 1 < NBLK) {
       const int cn = rev ? c - 1 : c + 1;
@@ -101,6 +114,83 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, int64_t 
       else tmem_ld64(taddr + cn * EPI_COLS, rb);
     }
     if (col0 + c * EPI_COLS < N && row0 < M) {            // warp-uniform
+      if (i & 1) emit(c, rb);
+      else emit(c, ra);
+    }
+  }
+}
+
+// ---- MXFP8-quantized output ------------------------------------------------------------------------
+// The tile leaves the kernel as what the NEXT block-scaled GEMM wants for its A operand: every
+// accumulator is scaled, rounded to bf16 (the GEMM's output dtype) and then quantized exactly as
+// b200q_quantize_mxfp8(axis = 1) would quantize that bf16 matrix - E4M3 codes, one E8M0 scale per 32
+// columns - so 1.03 bytes per element leave the SM instead of 2.  A thread owns a row, so it owns whole
+// 32-column blocks.  Two 64-column blocks make one 128-byte row of codes in the (128-byte-swizzled)
+// staging block, stored by TMA to every output; the four scale bytes of those 128 columns are one
+// aligned 32-bit word of the 128x4-tiled layout, stored by the lane itself to every output.
+// NBLK must be even; rows [row0, row0 + 32) and columns [col0, col0 + 64 * NBLK).
+template <int NBLK, int EPI_BUFS, int RELEASE_AFTER, class Release>
+__device__ __forceinline__ void epilogue_tile_mxq(uint32_t taddr, bool rev, int64_t row0, int64_t col0, int64_t M, int64_t N,
+                                                  float alpha, const OutMaps* outs, uint32_t epi_s, uint8_t* epi_g, int& buf,
+                                                  int lane, Release release) {
+  static_assert(NBLK % 2 == 0, "the quantized-output epilogue stores 128-column chunks");
+  uint32_t sfw = 0;                                        // the chunk's four scale bytes, lowest block first
+  auto emit = [&](int c, const uint32_t (&r)[64]) {
+    const int half = c & 1;
+    if (half == (rev ? 1 : 0)) {                           // first half of a chunk in walking order: claim the staging block
+      if (lane == 0) ptx::bulk_wait_read<EPI_BUFS - 1>();
+      __syncwarp();
+      sfw = 0;
+    }
+    uint8_t* dst = epi_g + buf * EPI_BLOCK_BYTES + lane * 128;
+    const int sw = lane & 7;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {                          // the two 32-column blocks of this 64-column block
+      uint4 h[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i0 = 32 * b + 8 * u;
+        h[u] = make_uint4(pack_bf16(u2f(r[i0]) * alpha, u2f(r[i0 + 1]) * alpha), pack_bf16(u2f(r[i0 + 2]) * alpha, u2f(r[i0 + 3]) * alpha),
+                          pack_bf16(u2f(r[i0 + 4]) * alpha, u2f(r[i0 + 5]) * alpha), pack_bf16(u2f(r[i0 + 6]) * alpha, u2f(r[i0 + 7]) * alpha));
+      }
+      uint32_t o[8];
+      const int e = mx_quant_block32<FMT_E4M3>(h, o);
+      sfw |= (uint32_t)((e + 127) & 0xFF) << (8 * (2 * half + b));
+      const int j0 = 4 * half + 2 * b;                      // 16-byte chunk of the 128-byte row
+      *reinterpret_cast<uint4*>(dst + (((j0) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(dst + (((j0 + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+    if (half == (rev ? 0 : 1)) {                           // chunk complete
+      const int64_t colg = col0 + (int64_t)(c >> 1) * 128;
+      ptx::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        for (int g = 0; g < outs->count; ++g)
+          ptx::tma_store_2d(&outs->m[g], (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
+        ptx::bulk_commit();
+      }
+      const int64_t row = row0 + lane;
+      if (row < M) {
+        const int64_t off = sf_swizzled(row, (int)(colg >> 5), outs->sf_kt);      // a multiple of 4: colg % 128 == 0
+        for (int g = 0; g < outs->count; ++g) *reinterpret_cast<uint32_t*>(outs->sf[g] + off) = sfw;
+      }
+      buf = (buf + 1) % EPI_BUFS;
+    }
+  };
+
+  uint32_t ra[64], rb[64];
+  tmem_ld64(taddr + (rev ? NBLK - 1 : 0) * EPI_COLS, ra);
+#pragma unroll
+  for (int i = 0; i < NBLK; ++i) {
+    const int c = rev ? NBLK - 1 - i : i;
+    ptx::tmem_ld_wait();
+    if (i == RELEASE_AFTER) release();
+    if (i + 1 < NBLK) {
+      const int cn = rev ? c - 1 : c + 1;
+      if (i & 1) tmem_ld64(taddr + cn * EPI_COLS, ra);
+      else tmem_ld64(taddr + cn * EPI_COLS, rb);
+    }
+    if (col0 + (int64_t)(c >> 1) * 128 < N && row0 < M) {  // warp-uniform; N % 128 == 0, so a chunk is in range or not as a whole
       if (i & 1) emit(c, rb);
       else emit(c, ra);
     }

@@ -9,6 +9,8 @@
 // 32-byte accesses.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace b200q {
 namespace {
 
@@ -317,7 +319,8 @@ swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t l
 // One warp per token over the fp32 logits of the gate GEMM (src/layers/mlp.py:292-301, :455):
 // probs = softmax | sigmoid (fp32), the k largest probs in descending order (equal probs: the
 // larger logit first, then the lower expert index), weights = probs[idx] / (sum + 1e-9) when
-// normalising, both cast to bf16, plus how many tokens chose each expert.  Lane l holds experts
+// normalising, both cast to bf16 (or left in fp32 when the caller's activations are not bf16), plus how
+// many tokens chose each expert.  Lane l holds experts
 // l, l + 32, ... (E <= 256).
 // PER = experts per lane (1, 2, 4 or 8: the smallest that covers E), a template argument so that the
 // loops over a lane's experts have no idle iterations.
@@ -326,8 +329,8 @@ swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t l
 template <int PER, bool BIAS>
 __global__ void __launch_bounds__(256)
 moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k, int sigmoid, int normalize,
-                       int64_t* __restrict__ top_idx, uint16_t* __restrict__ top_w, uint16_t* __restrict__ probs_out,
-                       int32_t* __restrict__ counts, const float* __restrict__ select_bias) {
+                       int64_t* __restrict__ top_idx, void* __restrict__ top_w, void* __restrict__ probs_out,
+                       int32_t* __restrict__ counts, const float* __restrict__ select_bias, int out_fp32) {
   __shared__ int hist[kMaxExperts];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < E; i += 256) hist[i] = 0;
@@ -364,7 +367,10 @@ moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k
 #pragma unroll
       for (int j = 0; j < kRouterMaxPerLane; ++j) {
         const int e = j * 32 + lane;
-        if (j < per && e < E) probs_out[t * E + e] = __bfloat16_as_ushort(__float2bfloat16_rn(p[j]));
+        if (j < per && e < E) {
+          if (out_fp32) static_cast<float*>(probs_out)[t * E + e] = p[j];
+          else static_cast<uint16_t*>(probs_out)[t * E + e] = __bfloat16_as_ushort(__float2bfloat16_rn(p[j]));
+        }
       }
     }
     // selection key: the prob, or prob + bias; absent experts stay below every key
@@ -416,7 +422,8 @@ moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k
     if (lane < k) {
       const float w = normalize ? mine / (wsum + 1e-9f) : mine;
       top_idx[t * k + lane] = mine_idx;
-      top_w[t * k + lane] = __bfloat16_as_ushort(__float2bfloat16_rn(w));
+      if (out_fp32) static_cast<float*>(top_w)[t * k + lane] = w;
+      else static_cast<uint16_t*>(top_w)[t * k + lane] = __bfloat16_as_ushort(__float2bfloat16_rn(w));
       if (counts != nullptr) atomicAdd(&hist[mine_idx], 1);
     }
   }
@@ -620,7 +627,8 @@ moe_unpermute_backward_kernel(const uint16_t* __restrict__ dout, const uint16_t*
 constexpr int64_t kStaticPlanInts = 262144;
 static __device__ __align__(256) int32_t g_static_plan_scratch[kStaticPlanInts];
 constexpr int kMaxDevices = 64;
-static int32_t* g_static_plan_ptr[kMaxDevices] = {};   // device address of the array, per device
+// device address of the array, per device; filled on first use (every thread that gets there stores the same value)
+static std::atomic<int32_t*> g_static_plan_ptr[kMaxDevices] = {};
 
 // The permute plan's launches, shared by the two entry points (workspace from the caller or built in).
 int run_permute_plan(const int64_t* top_idx, int64_t n_pairs, int k, int E, int32_t* block_counts, int32_t* offs,
@@ -847,7 +855,8 @@ int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y,
 }
 
 int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int score_fn, int normalize, int64_t* top_idx,
-                          void* top_w, void* probs, int32_t* expert_counts, const float* select_bias, void* stream) {
+                          void* top_w, void* probs, int32_t* expert_counts, const float* select_bias, int out_fp32,
+                          void* stream) {
   if (logits == nullptr || top_idx == nullptr || top_w == nullptr || T <= 0 || E <= 0 || k <= 0 || (score_fn != 0 && score_fn != 1))
     return B200Q_ERR_INVALID_ARG;
   if (E > kMaxExperts || k > 32 || k > E) return B200Q_ERR_SHAPE;
@@ -858,11 +867,11 @@ int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int scor
 #define B200Q_GO(P)                                                                                                          \
   do {                                                                                                                       \
     if (select_bias != nullptr)                                                                                              \
-      moe_router_topk_kernel<P, true><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, (uint16_t*)top_w,   \
-                                                                   (uint16_t*)probs, expert_counts, select_bias);            \
+      moe_router_topk_kernel<P, true><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, top_w, probs,       \
+                                                                   expert_counts, select_bias, out_fp32);                    \
     else                                                                                                                     \
-      moe_router_topk_kernel<P, false><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, (uint16_t*)top_w,  \
-                                                                    (uint16_t*)probs, expert_counts, nullptr);               \
+      moe_router_topk_kernel<P, false><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, top_w, probs,      \
+                                                                    expert_counts, nullptr, out_fp32);                       \
   } while (0)
   if (E <= 32) B200Q_GO(1);
   else if (E <= 64) B200Q_GO(2);
@@ -923,12 +932,13 @@ int b200q_moe_permute_plan_static(const int64_t* top_idx, int64_t n_pairs, int k
   int dev = -1;
   B200Q_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return B200Q_ERR_INVALID_ARG;
-  if (g_static_plan_ptr[dev] == nullptr) {
-    int32_t* ptr = nullptr;
+  int32_t* ptr = g_static_plan_ptr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     B200Q_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_plan_scratch));
-    g_static_plan_ptr[dev] = ptr;
+    if (ptr == nullptr) return B200Q_ERR_CUDA;
+    g_static_plan_ptr[dev].store(ptr, std::memory_order_release);
   }
-  return run_permute_plan(top_idx, n_pairs, k, E, g_static_plan_ptr[dev], offs, padded_offs, row_of, src_of_row, tile_expert,
+  return run_permute_plan(top_idx, n_pairs, k, E, ptr, offs, padded_offs, row_of, src_of_row, tile_expert,
                           num_tiles, (cudaStream_t)stream);
 }
 

@@ -64,50 +64,93 @@ def sharded_gemm(a_shard: torch.Tensor, b: torch.Tensor, a_fmt: str, b_fmt: str,
 
 
 class GatheredOutput:
-    """The gathered (world * m, n) bf16 output of an M-sharded GEMM as symmetric memory: every rank
-    owns one copy and has its peers' copies mapped, so that the GEMM's epilogue can store each tile
-    straight into all of them over NVLink (fused GEMM + all-gather, no separate collective)."""
+    """The gathered (world * m, n) output of an M-sharded GEMM as symmetric memory: every rank owns one
+    copy and has its peers' copies mapped, so that the GEMM's epilogue can store each tile straight into
+    all of them over NVLink (fused GEMM + all-gather, no separate collective).
 
-    def __init__(self, m: int, n: int, group=None):
+    payload "bf16": the result itself.  payload "mxfp8": E4M3 codes + swizzled E8M0 scale factors of the
+    result quantized along its columns - what the next block-scaled GEMM would make of the bf16 matrix
+    anyway (src/quant/linear.py:72-76) at 1.03 instead of 2 bytes per element on the link.
+
+    Two sets of buffers alternate from call to call: a rank that runs ahead into its next call stores into
+    the set its peers are not reading (their reads of the previous result are ordered before their own next
+    GEMM on the stream, and a rank cannot get two calls ahead of a peer past the per-call rendezvous)."""
+
+    def __init__(self, m: int, n: int, group=None, payload: str = "bf16"):
         import torch.distributed._symmetric_memory as symm
+        from . import ops
+        if payload not in ("bf16", "mxfp8"):
+            raise ValueError(f"unknown payload {payload!r}")
+        if payload == "mxfp8" and (m % 128 or n % 128):
+            raise ValueError("the MXFP8 payload needs m % 128 == 0 and n % 128 == 0")
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
-        self.m, self.n = m, n
-        self.buf = symm.empty((self.world * m, n), dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
-        self.handle = symm.rendezvous(self.buf, self.group)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        self._flag = torch.zeros(1, device=self.buf.device)
+        self.m, self.n, self.payload = m, n, payload
+        dev = torch.device("cuda", torch.cuda.current_device())
+        rows = self.world * m
+        self.bufs, self.ptrs, self.sfs, self.sf_ptrs = [], [], [], []
+        for _ in range(2):
+            buf = symm.empty((rows, n), dtype=torch.bfloat16 if payload == "bf16" else torch.uint8, device=dev)
+            self.bufs.append(buf)
+            self.ptrs.append([int(p) for p in symm.rendezvous(buf, self.group).buffer_ptrs])
+            if payload == "mxfp8":
+                sf = symm.empty((ops.sf_bytes(rows, n // 32),), dtype=torch.uint8, device=dev)
+                self.sfs.append(sf)
+                self.sf_ptrs.append([int(p) for p in symm.rendezvous(sf, self.group).buffer_ptrs])
+        self._flag = torch.zeros(1, device=dev)
+        self._turn = 0
+
+    @property
+    def buf(self) -> torch.Tensor:
+        """The set the last call filled."""
+        return self.bufs[self._turn ^ 1]
+
+    def take(self) -> int:
+        turn = self._turn
+        self._turn ^= 1
+        return turn
 
     def sync(self) -> None:
         """Stream-ordered rendezvous of the ranks: once it has run, every rank's stores have landed."""
         dist.all_reduce(self._flag, group=self.group)
 
 
-def sharded_gemm_fused(a_shard: torch.Tensor, w: torch.Tensor, fmt: str, out: GatheredOutput) -> torch.Tensor:
+def sharded_gemm_fused(a_shard: torch.Tensor, w: torch.Tensor, fmt: str, out: GatheredOutput):
     """`a_shard @ w.T` for this rank's rows of A (w is the (n, k) weight, replicated), quantized to
     `fmt` ("mxfp8", "nvfp4" or "fp8_e4m3" with per-row scales), with the output all-gather fused
-    into the GEMM's epilogue.  Returns the gathered (world * m, n) matrix (valid after `out.sync()`,
-    which this function calls)."""
+    into the GEMM's epilogue.  Returns the gathered (world * m, n) bf16 matrix, or for an "mxfp8"
+    payload the gathered (codes, scale factors); complete on return (this function runs the
+    rendezvous) and valid until the call after the next one reuses the buffers."""
     from . import ops
     if a_shard.shape[0] != out.m or w.shape[0] != out.n:
         raise ValueError("shard / weight shape does not match the gathered output")
+    turn = out.take()
+    ptrs = out.ptrs[turn]
+    if out.payload == "mxfp8":
+        if fmt not in ("mxfp8", "mxfp8_e4m3"):
+            raise ValueError("the MXFP8 payload is produced by the MXFP8 GEMM")
+        ca, sfa = ops.quantize_mxfp8(a_shard, 1)
+        cb, sfb = ops.quantize_mxfp8(w, 1)
+        ops.gemm_mxfp8_allgather_mxfp8(ca, sfa, cb, sfb, ptrs, out.sf_ptrs[turn], out.rank, out.n, out.n)
+        out.sync()
+        return out.bufs[turn], out.sfs[turn]
     if fmt in ("mxfp8", "mxfp8_e4m3"):
         ca, sfa = ops.quantize_mxfp8(a_shard, 1)
         cb, sfb = ops.quantize_mxfp8(w, 1)
-        ops.gemm_mxfp8_allgather(ca, sfa, cb, sfb, out.ptrs, out.rank, out.n, out.n)
+        ops.gemm_mxfp8_allgather(ca, sfa, cb, sfb, ptrs, out.rank, out.n, out.n)
     elif fmt in ("nvfp4", "fp4_nv"):
         pa, sfa, ta = ops.quantize_nvfp4(a_shard, 1)
         pb, sfb, tb = ops.quantize_nvfp4(w, 1)
-        ops.gemm_nvfp4_allgather(pa, sfa, ta, pb, sfb, tb, out.ptrs, out.rank, out.n, out.n)
+        ops.gemm_nvfp4_allgather(pa, sfa, ta, pb, sfb, tb, ptrs, out.rank, out.n, out.n)
     elif fmt in ("fp8", "fp8_e4m3"):
         e4 = torch.float8_e4m3fn
         ca, sa = ops.quantize_fp8(a_shard, e4, 1)
         cb, sb = ops.quantize_fp8(w, e4, 1)
-        ops.gemm_fp8_allgather(ca, e4, cb, e4, sa, sb, out.ptrs, out.rank, out.n, out.n)
+        ops.gemm_fp8_allgather(ca, e4, cb, e4, sa, sb, ptrs, out.rank, out.n, out.n)
     else:
         raise ValueError(f"unsupported format for the fused GEMM + all-gather: {fmt!r}")
     out.sync()
-    return out.buf
+    return out.bufs[turn]
 
 
 class ScatteredSum:

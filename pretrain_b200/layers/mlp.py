@@ -18,6 +18,7 @@ import torch.nn.functional as F
 
 from .. import ops
 from .. import torch_ops as T
+from ..quant import cache as weight_cache
 
 
 def silu_glu(gate, up):
@@ -286,14 +287,8 @@ def grouped_mlp(x, w_in, w_down, act_fn, offs, gated, row_expert_ids=None, b_in=
 
 
 def _cached(param: torch.Tensor, slot: str, key, make):
-    """Quantized copies of a weight, kept on the parameter until it is written again."""
-    key = (param._version, param.data_ptr(), key)
-    hit = getattr(param, slot, None)
-    if hit is None or hit[0] != key:
-        with torch.no_grad():
-            hit = (key, make())
-        setattr(param, slot, hit)
-    return hit[1]
+    """Quantized copies of a weight, kept on the parameter until it is written again (pretrain_b200.quant.cache)."""
+    return weight_cache.cached(param, slot[len("_b200q_"):] if slot.startswith("_b200q_") else slot, key, make)
 
 
 def _expert_weight_copies(param: torch.Tensor, kind: str):
@@ -311,9 +306,7 @@ def _expert_weight_copies(param: torch.Tensor, kind: str):
             return T.quantize_mxfp8_glu_rows(w.reshape(e * n, k), e, n // 2)
         return _quantize_expert_weights(w)
 
-    if torch.compiler.is_compiling() or not isinstance(param, nn.Parameter):
-        return make()
-    return _cached(param, "_b200q_" + kind, kind, make)
+    return _cached(param, kind, kind, make)
 
 
 def _ffn_flops(d_model: int, d_ff: int, gated: bool, bias: bool) -> int:
@@ -503,19 +496,17 @@ class MoERouter(nn.Module):
     def forward(self, x):
         with torch.amp.autocast(device_type=x.device.type, enabled=False):
             logits = self.gate(x.float())                  # the fp32 gate GEMM stays the reference's own op
-        if x.is_cuda and x.dtype == torch.bfloat16 and self.n_routed_experts <= 256:
-            bias = self.expert_bias.bias if self.expert_bias is not None else None
-            top_i, top_w, probs = _RouterBackEnd.apply(logits, self.n_routed_experts_per_token, self.score_name, self.normalize, bias)
-            return top_i, top_w, probs
-        probs = self.score_fn(logits)
-        if self.expert_bias is not None:
-            top_i = torch.topk(self.expert_bias(probs), self.n_routed_experts_per_token, dim=-1).indices
-            top_w = probs.gather(-1, top_i)
-        else:
-            top_w, top_i = torch.topk(probs, self.n_routed_experts_per_token, dim=-1)
-        if self.normalize:
-            top_w = top_w / (top_w.sum(-1, keepdim=True) + 1e-9)
-        return top_i, top_w.to(x.dtype), probs.to(x.dtype)
+        if not x.is_cuda:
+            raise RuntimeError("MoERouter runs on the B200 kernels only (no CPU path)")
+        if self.n_routed_experts > 256:
+            raise NotImplementedError("the router kernel handles at most 256 experts")
+        bias = self.expert_bias.bias if self.expert_bias is not None else None
+        # weights and probs come back in the activations' dtype (src/layers/mlp.py:302): bf16 straight from the
+        # kernel, anything else from its fp32 results
+        fp32_out = x.dtype != torch.bfloat16
+        top_i, top_w, probs = _RouterBackEnd.apply(logits, self.n_routed_experts_per_token, self.score_name, self.normalize, bias,
+                                                   fp32_out)
+        return (top_i, top_w.to(x.dtype), probs.to(x.dtype)) if fp32_out else (top_i, top_w, probs)
 
 
 class _RouterBackEnd(torch.autograd.Function):
@@ -523,8 +514,8 @@ class _RouterBackEnd(torch.autograd.Function):
     (b200q_moe_router_topk); the backward is the closed form of those steps on the (T, E) tensors."""
 
     @staticmethod
-    def forward(ctx, logits, k, score_name, normalize, select_bias=None):
-        top_i, top_w, probs = T.moe_router_topk(logits.float().contiguous(), k, score_name, normalize, select_bias)
+    def forward(ctx, logits, k, score_name, normalize, select_bias=None, fp32_out=False):
+        top_i, top_w, probs = T.moe_router_topk(logits.float().contiguous(), k, score_name, normalize, select_bias, fp32_out)
         ctx.save_for_backward(logits, top_i)
         ctx.score_name, ctx.normalize = score_name, normalize
         ctx.mark_non_differentiable(top_i)
@@ -548,7 +539,7 @@ class _RouterBackEnd(torch.autograd.Function):
             dlogits = p * (dp - (dp * p).sum(-1, keepdim=True))
         else:
             dlogits = dp * p * (1 - p)
-        return dlogits, None, None, None, None
+        return dlogits, None, None, None, None, None
 
 
 class SparseMoEBlock(nn.Module):
@@ -587,6 +578,7 @@ class SparseMoEBlock(nn.Module):
 
     @torch.no_grad()
     def post_step(self):
+        weight_cache.invalidate(self)      # the optimizer has just written the experts: their quantized copies go
         if self.expert_bias:
             self.router.update_expert_bias(self.expert_load.train_load)
             self.expert_load.reset_train_load()

@@ -279,6 +279,27 @@ def gemm_mxfp8_allgather(a_codes, a_sf, b_codes, b_sf, out_ptrs, rank: int, n: i
                                                       len(out_ptrs), rank, ldd, _stream()), "b200q_gemm_mxfp8_allgather")
 
 
+def gemm_mxfp8_allgather_mxfp8(a_codes, a_sf, b_codes, b_sf, code_ptrs, sf_ptrs, rank: int, n: int, ldc: int, a_fmt=E4M3, b_fmt=E4M3):
+    """Fused GEMM + all-gather with an MXFP8 output: this rank's (M, n) block, rounded to bf16 and quantized
+    along its columns, goes to rows [rank*M, rank*M+M) of every rank's gathered codes and swizzled scale
+    factors (`code_ptrs` / `sf_ptrs`: device pointers of those buffers, own and peer-mapped)."""
+    m, k = a_codes.shape
+    _lib.check(_lib.load().b200q_gemm_mxfp8_allgather_mxfp8(a_codes.data_ptr(), fmt_of(a_fmt), a_sf.data_ptr(), b_codes.data_ptr(),
+                                                            fmt_of(b_fmt), b_sf.data_ptr(), m, n, k, _ptr_array(code_ptrs),
+                                                            _ptr_array(sf_ptrs), len(code_ptrs), rank, ldc, _stream()),
+               "b200q_gemm_mxfp8_allgather_mxfp8")
+
+
+def gemm_mxfp8_quantized(a_codes, a_sf, b_codes, b_sf, a_fmt=E4M3, b_fmt=E4M3):
+    """(codes uint8 (M, N), swizzled sf) = quantize_mxfp8(gemm_mxfp8(...)) in one kernel: the GEMM's epilogue
+    quantizes its bf16 result along the columns.  M % 128 == 0, N % 128 == 0."""
+    m, n = a_codes.shape[0], b_codes.shape[0]
+    codes = torch.empty(m, n, dtype=torch.uint8, device=a_codes.device)
+    sf = torch.empty(sf_bytes(m, n // 32), dtype=torch.uint8, device=a_codes.device)
+    gemm_mxfp8_allgather_mxfp8(a_codes, a_sf, b_codes, b_sf, [codes.data_ptr()], [sf.data_ptr()], 0, n, codes.stride(0), a_fmt, b_fmt)
+    return codes, sf
+
+
 def gemm_mxfp8_scatter(a_codes, a_sf, b_codes, b_sf, stage_ptrs, rank: int, n: int, ldd: int, a_fmt=E4M3, b_fmt=E4M3):
     """First half of a fused GEMM + reduce-scatter: block rows [g*M/world, ...) of this rank's (M, n) partial result go
     to slot `rank` of rank g's staging buffer (`stage_ptrs`: device pointers of the ranks' [world, M/world, n] buffers)."""
@@ -603,16 +624,18 @@ def moe_unpermute_backward(dout: torch.Tensor, weights: torch.Tensor, y: torch.T
 
 
 def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str = "softmax", normalize: bool = True, want_probs: bool = True,
-                    want_counts: bool = True, select_bias: torch.Tensor | None = None):
-    """fp32 logits (T, E) -> (top_idx int64 (T, k), top_w bf16 (T, k), probs bf16 (T, E) | None,
-    expert_counts int32 (E) | None): score function, top-k, normalisation, casts and histogram in one launch."""
+                    want_counts: bool = True, select_bias: torch.Tensor | None = None, fp32_out: bool = False):
+    """fp32 logits (T, E) -> (top_idx int64 (T, k), top_w (T, k), probs (T, E) | None, expert_counts int32 (E) | None):
+    score function, top-k, normalisation, casts and histogram in one launch.  top_w and probs are bf16, or fp32
+    when `fp32_out`."""
     if not logits.is_cuda:
         raise RuntimeError("b200q ops need CUDA tensors (no CPU path exists)")
     logits = logits.float().contiguous()
     t, e = logits.shape
     idx = torch.empty(t, k, dtype=torch.int64, device=logits.device)
-    w = torch.empty(t, k, dtype=torch.bfloat16, device=logits.device)
-    probs = torch.empty(t, e, dtype=torch.bfloat16, device=logits.device) if want_probs else None
+    odt = torch.float32 if fp32_out else torch.bfloat16
+    w = torch.empty(t, k, dtype=odt, device=logits.device)
+    probs = torch.empty(t, e, dtype=odt, device=logits.device) if want_probs else None
     counts = torch.empty(e, dtype=torch.int32, device=logits.device) if want_counts else None
     bias = select_bias.float().contiguous() if select_bias is not None else None      # chosen by score + bias, weighted by score
     if bias is not None and bias.shape != (e,):
@@ -620,7 +643,8 @@ def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str = "softmax", nor
     _lib.check(_lib.load().b200q_moe_router_topk(logits.data_ptr(), t, e, k, {"softmax": 0, "sigmoid": 1}[score_fn], int(normalize),
                                                  idx.data_ptr(), w.data_ptr(), probs.data_ptr() if want_probs else None,
                                                  counts.data_ptr() if want_counts else None,
-                                                 bias.data_ptr() if bias is not None else None, _stream()), "b200q_moe_router_topk")
+                                                 bias.data_ptr() if bias is not None else None, int(fp32_out), _stream()),
+               "b200q_moe_router_topk")
     return idx, w, probs, counts
 
 

@@ -36,14 +36,17 @@ def fake_quantize_int8(x: torch.Tensor, qmax: int, dim: int | None = None) -> to
 
 def int8_gemm(a, b, out_dtype, a_qmax, b_qmax, rowwise: bool = False):
     """`a @ b` for a (M, K), b (K, N) high precision, both quantized along K to the int8 series
-    (src/quant/int8.py:29-53).  Shapes the tensor-core kernel does not take (K % 16 or N % 8)
-    go through the fake-quantize-then-matmul form, which is also what the reference does for the
-    shapes its own kernel rejects (src/quant/int8.py:35-47)."""
+    (src/quant/int8.py:29-53).  The tensor-core kernel wants K % 16 == 0 and N % 8 == 0; other shapes
+    are padded with zeros (which change neither a maximum nor the integer product) and the result is
+    cut back, so every shape runs on the kernel - there is no matmul fallback like the reference's
+    (src/quant/int8.py:35-47)."""
+    if not (a.is_cuda and b.is_cuda):
+        raise RuntimeError("int8_gemm runs on the B200 kernels only (no CPU path)")
     k, n = b.shape
-    if k % 16 or n % 8:
-        fa = fake_quantize_int8(a, a_qmax, dim=-1 if rowwise else None)
-        fb = fake_quantize_int8(b, b_qmax, dim=0 if rowwise else None)
-        return (fa @ fb).to(out_dtype)
+    pad_k, pad_n = (-k) % 16, (-n) % 8
+    if pad_k or pad_n:
+        a = torch.nn.functional.pad(a, (0, pad_k))
+        b = torch.nn.functional.pad(b, (0, pad_n, 0, pad_k))
     am, a_axis = _k_major(a, 1)
     bm, b_axis = _k_major(b, 0)
     if rowwise:
@@ -53,4 +56,6 @@ def int8_gemm(a, b, out_dtype, a_qmax, b_qmax, rowwise: bool = False):
         ca, sa = T.quantize_int8_tensorwise(am, int(a_qmax), a_axis == 0)
         cb, sb = T.quantize_int8_tensorwise(bm, int(b_qmax), b_axis == 0)
     out = T.gemm_int8(ca, cb, sa, sb)
+    if pad_n:
+        out = out[:, :n]
     return out if out_dtype == torch.bfloat16 else out.to(out_dtype)

@@ -13,6 +13,7 @@ import torch.nn as nn
 
 from .. import torch_ops as T
 from ..ops import SF_NATURAL, SF_SWIZZLED, fmt_of
+from . import cache as weight_cache
 from .config import QuantConfig
 from .fp8 import _k_major, fake_quantize_fp8, fp8_gemm
 from .int8 import fake_quantize_int8, int8_gemm
@@ -98,16 +99,9 @@ def _fp8_training_formats(cfg: QuantConfig):
 
 
 def _both_fp8_weight(weight: torch.Tensor, w: torch.Tensor, fmt: torch.dtype):
-    """Per-row and per-column FP8 copies of the weight, kept on the parameter until it is written again."""
-    if torch.compiler.is_compiling() or not isinstance(weight, nn.Parameter):
-        return T.quantize_fp8_both(w, fmt_of(fmt))
-    key = (weight._version, weight.data_ptr(), w.dtype, fmt)
-    cached = getattr(weight, "_b200q_fp8", None)
-    if cached is None or cached[0] != key:
-        with torch.no_grad():
-            cached = (key, T.quantize_fp8_both(w.detach(), fmt_of(fmt)))
-        weight._b200q_fp8 = cached
-    return cached[1]
+    """Per-row and per-column FP8 copies of the weight, kept on the parameter until it is written again
+    (see ``pretrain_b200.quant.cache`` for what "written" covers)."""
+    return weight_cache.cached(weight, "fp8", (w.dtype, fmt), lambda: T.quantize_fp8_both(w.detach(), fmt_of(fmt)))
 
 
 def _dual_mx_weight(weight: torch.Tensor, w: torch.Tensor, fmt: torch.dtype):
@@ -115,15 +109,7 @@ def _dual_mx_weight(weight: torch.Tensor, w: torch.Tensor, fmt: torch.dtype):
     dgrad).  Outside torch.compile they are kept on the parameter until it is next written, so a
     step made of several micro-batches quantizes each weight once (the reference re-quantizes in
     every forward and again in every backward, src/quant/linear.py:73-76,98)."""
-    if torch.compiler.is_compiling() or not isinstance(weight, nn.Parameter):
-        return T.quantize_mxfp8_dual(w, fmt_of(fmt), SF_SWIZZLED)
-    key = (weight._version, weight.data_ptr(), w.dtype, fmt)
-    cached = getattr(weight, "_b200q_mx", None)
-    if cached is None or cached[0] != key:
-        with torch.no_grad():
-            cached = (key, T.quantize_mxfp8_dual(w.detach(), fmt_of(fmt), SF_SWIZZLED))
-        weight._b200q_mx = cached
-    return cached[1]
+    return weight_cache.cached(weight, "mx", (w.dtype, fmt), lambda: T.quantize_mxfp8_dual(w.detach(), fmt_of(fmt), SF_SWIZZLED))
 
 
 class QuantizedLinearFn(torch.autograd.Function):
@@ -241,6 +227,13 @@ class QuantLinear(nn.Module):
 
     def forward(self, x):
         return QuantizedLinearFn.apply(x, self.weight, self.bias, self.cfg, torch.is_grad_enabled())
+
+    @torch.no_grad()
+    def post_step(self):
+        """Called by the training loop after every optimizer step (src/training/trainer.py:367 through
+        src/model/transformer.py:144-147): the weight has just been written, so its cached quantized copies go -
+        also when the optimizer wrote through ``.data``, which the version counter does not see."""
+        weight_cache.invalidate(self.weight)
 
     def extra_repr(self):
         return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}"

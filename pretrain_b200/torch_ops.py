@@ -419,17 +419,18 @@ def _(dout, weights, row_of, padded_rows, fmt, y):
 
 
 @_lib_def("b200q::moe_router_topk", mutates_args=())
-def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str, normalize: bool,
-                    select_bias: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    idx, w, probs, _ = ops.moe_router_topk(logits, k, score_fn, normalize, want_counts=False, select_bias=select_bias)
+def moe_router_topk(logits: torch.Tensor, k: int, score_fn: str, normalize: bool, select_bias: Optional[torch.Tensor],
+                    fp32_out: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    idx, w, probs, _ = ops.moe_router_topk(logits, k, score_fn, normalize, want_counts=False, select_bias=select_bias,
+                                           fp32_out=fp32_out)
     return idx, w, probs
 
 
 @moe_router_topk.register_fake
-def _(logits, k, score_fn, normalize, select_bias):
+def _(logits, k, score_fn, normalize, select_bias, fp32_out=False):
     t, e = logits.shape
-    return (logits.new_empty(t, k, dtype=torch.int64), logits.new_empty(t, k, dtype=torch.bfloat16),
-            logits.new_empty(t, e, dtype=torch.bfloat16))
+    odt = torch.float32 if fp32_out else torch.bfloat16
+    return (logits.new_empty(t, k, dtype=torch.int64), logits.new_empty(t, k, dtype=odt), logits.new_empty(t, e, dtype=odt))
 
 
 _GLU_ROW_MAPS: dict = {}

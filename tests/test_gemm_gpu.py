@@ -212,6 +212,41 @@ def test_nvfp4_gemm_with_swiglu_epilogue(ops, bn, pair, m, d, inter):
     assert am.item() == ops.amax(want).item() == want.float().abs().max().item()
 
 
+@pytest.mark.parametrize("bn,pair", [(0, -1), (128, -1), (256, -1), (0, 1)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (1024, 768, 768), (2048, 2048, 1024), (384, 1280, 96)])
+def test_gemm_with_mxfp8_quantized_output(ops, bn, pair, m, n, k):
+    """The GEMM whose epilogue quantizes its own bf16 result along the columns == the plain GEMM followed by
+    the row-wise MXFP8 quantizer: the same codes and the same swizzled scale bytes."""
+    from pretrain_b200 import _lib
+    a, b = _rand(m, k, 41), _rand(n, k, 42, 0.05)
+    ca, sfa = ops.quantize_mxfp8(a); cb, sfb = ops.quantize_mxfp8(b)
+    want_c, want_sf = ops.quantize_mxfp8(ops.gemm_mxfp8(ca, sfa, cb, sfb), 1)
+    _lib.load().b200q_debug_set_gemm_bn(bn)
+    _lib.load().b200q_debug_set_gemm_pair(pair)
+    try:
+        got_c, got_sf = ops.gemm_mxfp8_quantized(ca, sfa, cb, sfb)
+        ops.device_status()
+    finally:
+        _lib.load().b200q_debug_set_gemm_bn(0)
+        _lib.load().b200q_debug_set_gemm_pair(0)
+    assert torch.equal(got_c, want_c)
+    assert torch.equal(got_sf, want_sf)
+    # and it is a valid A operand for the next GEMM
+    w2 = _rand(256, n, 43, 0.05)
+    c2, sf2 = ops.quantize_mxfp8(w2)
+    assert torch.equal(ops.gemm_mxfp8(got_c, got_sf, c2, sf2), ops.gemm_mxfp8(want_c, want_sf, c2, sf2))
+
+
+def test_quantized_output_refuses_partial_tiles(ops):
+    from pretrain_b200 import _lib
+    import ctypes
+    z = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    one = (ctypes.c_void_p * 1)(z.data_ptr())
+    for m, n in ((96, 128), (128, 96), (128, 192 + 32)):
+        assert _lib.load().b200q_gemm_mxfp8_allgather_mxfp8(z.data_ptr(), 0, z.data_ptr(), z.data_ptr(), 0, z.data_ptr(), m, n, 128,
+                                                            one, one, 1, 0, 256, None) == -2
+
+
 def _int8_ref(ca, cb, sa, sb):
     """The reference's formula (src/quant/int8.py:52-53) with an exact integer product."""
     acc = (ca.double() @ cb.double().t()).to(torch.int32)            # |acc| < 2^31: exact in fp64

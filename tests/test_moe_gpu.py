@@ -114,7 +114,9 @@ def test_grouped_backward_gemms(ops, counts, k, n, bn):
     wt, wtsf = ops.quantize_mxfp8(w.reshape(e * k, n), 0)                # (n, E*k): every expert's operand at column e*k
     gy_pad, x_pad = ops.moe_gather(gy, plan, False), ops.moe_gather(xin, plan, False)
     live = int(plan.num_tiles.item()) * 128
-    gy_pad[live:] = 0; x_pad[live:] = 0
+    # rows past the live tiles are never written by the forward's kernels and may hold anything: an expert
+    # without rows must not read them (a product with them "scaled to zero" would be NaN)
+    gy_pad[live:] = float("nan"); x_pad[live:] = float("nan")
     gt, gtsf = ops.quantize_mxfp8(gy_pad, 0)                             # (k, padded_rows)
     xt, xtsf = ops.quantize_mxfp8(x_pad, 0)                              # (n, padded_rows)
     _lib.load().b200q_debug_set_gemm_pair(1 if bn == "pair" else 0)
@@ -140,6 +142,58 @@ def test_grouped_backward_gemms(ops, counts, k, n, bn):
             assert mx <= 1e-2 and fro <= 1e-2, ("wgrad", ei, mx, fro)
         else:
             assert (dw[ei] == 0).all()
+
+
+def test_grouped_entry_points_want_whole_scale_groups_per_expert(ops):
+    """N % 128 != 0 would start an expert's weight rows inside a 128-row scale-factor group: refused, not mis-computed."""
+    from pretrain_b200 import _lib
+    lib = _lib.load()
+    z = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    i32 = torch.zeros(8, dtype=torch.int32, device="cuda")
+    for n in (64, 96, 160, 320):
+        rc = lib.b200q_grouped_gemm_mxfp8(z.data_ptr(), 0, z.data_ptr(), z.data_ptr(), 0, z.data_ptr(), i32.data_ptr(), i32.data_ptr(),
+                                          128, 2, n, 128, z.data_ptr(), n, None)
+        assert rc == -2, (n, rc)
+        if n % 64 == 0:
+            rc = lib.b200q_grouped_gemm_mxfp8_swiglu(z.data_ptr(), 0, z.data_ptr(), z.data_ptr(), 0, z.data_ptr(), i32.data_ptr(),
+                                                     i32.data_ptr(), 128, 2, n, 128, z.data_ptr(), n // 2, z.data_ptr(), None)
+            assert rc == -2, (n, rc)
+
+
+def test_expert_ffn_backward_with_trailing_empty_experts_and_poisoned_scratch(ops, monkeypatch):
+    """Every buffer the layer allocates starts as 0xFF bytes (bf16 / fp32 NaN): rows past the live tiles, which no
+    grouped GEMM writes, then hold NaN when the both-directions quantizers and the wgrad GEMMs pass over them.
+    Experts without tokens - trailing ones, whose K range lies past the live tiles, included - must still get
+    exactly zero weight gradients, and every other gradient must be finite."""
+    from pretrain_b200.layers.mlp import _ExpertFFN, _expert_weight_copies
+    from pretrain_b200 import torch_ops as T
+    real_empty = torch.empty
+
+    def poisoned_empty(*args, **kwargs):
+        t = real_empty(*args, **kwargs)
+        if t.is_cuda and t.numel() and t.is_contiguous():
+            t.view(-1).view(torch.uint8).fill_(0xFF)
+        return t
+
+    t_, d, e, k, inter = 512, 256, 16, 2, 128
+    x, logits, w_gu, w_d = R.inputs_moe(t_, d, e, k, inter, seed=3)
+    logits[:, 3] = -1e9                      # an empty expert in the middle
+    logits[:, e - 3:] = -1e9                 # and three trailing ones
+    top_i, top_w = R.router_topk(logits, k)
+    x, top_i, top_w, w_gu, w_d = (v.cuda() for v in (x, top_i, top_w, w_gu, w_d))
+    x.requires_grad_(True); top_w.requires_grad_(True); w_gu.requires_grad_(True); w_d.requires_grad_(True)
+    dout = torch.randn(t_, d, device="cuda", dtype=torch.bfloat16)
+    monkeypatch.setattr(torch, "empty", poisoned_empty)
+    out = _ExpertFFN.apply(x, top_w, w_gu, w_d, *_expert_weight_copies(w_gu, "dual"), *_expert_weight_copies(w_d, "dual"),
+                           *T.moe_permute_plan(top_i, e))
+    gx, gtw, g1, g2 = torch.autograd.grad(out, (x, top_w, w_gu, w_d), dout)
+    monkeypatch.undo()
+    ops.device_status()
+    for g in (out, gx, gtw, g1, g2):
+        assert torch.isfinite(g.float()).all()
+    for ei in (3, e - 3, e - 2, e - 1):
+        assert (g1[ei] == 0).all() and (g2[ei] == 0).all()
+    assert (g1[0] != 0).any() and (g2[e - 4] != 0).any()
 
 
 def test_gather_and_swiglu_from_rows_that_are_only_16_byte_aligned(ops):

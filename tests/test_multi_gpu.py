@@ -67,12 +67,17 @@ def _fused_rank(rank, world, fmt):
     a = torch.randn(m, k, generator=g).bfloat16().cuda()
     w = (0.05 * torch.randn(n, k, generator=torch.Generator().manual_seed(77))).bfloat16().cuda()
     out = D.GatheredOutput(m, n)
-    for _ in range(2):                          # the second pass overwrites the first in place
-        full = D.sharded_gemm_fused(a, w, fmt, out)
-    local = _gemm(a, w.t(), fmt, fmt, torch.bfloat16, rowwise=True)
-    ref = D.all_gather_rows(local, world * m)   # the NCCL all-gather of the same shards
+    # three passes over different inputs: the two buffer sets alternate, and a result stays valid while the next call runs
+    inputs = [a, (a * 0.5 + 1.0).bfloat16(), a.flip(0).contiguous()]
+    fulls = [D.sharded_gemm_fused(ai, w, fmt, out) for ai in inputs]
     torch.cuda.synchronize()
-    assert torch.equal(full, ref)
+    for i, ai in enumerate(inputs):
+        local = _gemm(ai, w.t(), fmt, fmt, torch.bfloat16, rowwise=True)
+        ref = D.all_gather_rows(local, world * m)   # the NCCL all-gather of the same shards
+        if i > 0:                                # pass 0's buffer set was reused by pass 2
+            assert torch.equal(fulls[i], ref)
+    assert fulls[0].data_ptr() == fulls[2].data_ptr() != fulls[1].data_ptr()
+    full = fulls[2]
     ops.device_status()
     for small_m in (128, 96):                   # one-CTA kernel path, ragged rows
         o2 = D.GatheredOutput(small_m, n)
@@ -85,6 +90,35 @@ def _fused_rank(rank, world, fmt):
 @pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4", "fp8_e4m3"])
 def test_fused_gemm_allgather_equals_nccl_allgather(fmt):
     _run(_fused_rank, 2, fmt)
+
+
+def _fused_codes_rank(rank, world):
+    from pretrain_b200 import dist as D, ops
+    m, k, n = 2048, 1024, 1536
+    g = torch.Generator().manual_seed(rank)
+    a = torch.randn(m, k, generator=g).bfloat16().cuda()
+    w = (0.05 * torch.randn(n, k, generator=torch.Generator().manual_seed(77))).bfloat16().cuda()
+    bf = D.GatheredOutput(m, n)
+    mx = D.GatheredOutput(m, n, payload="mxfp8")
+    for ai in (a, (a * 0.25).bfloat16()):
+        full = D.sharded_gemm_fused(ai, w, "mxfp8", bf)
+        codes, sf = D.sharded_gemm_fused(ai, w, "mxfp8", mx)
+        torch.cuda.synchronize()
+        # the gathered codes and scale bytes are the row-wise MXFP8 quantization of the gathered bf16 output
+        want_c, want_sf = ops.quantize_mxfp8(full, 1)
+        assert torch.equal(codes, want_c) and torch.equal(sf, want_sf)
+    ops.device_status()
+    for small_m in (128, 256):                  # one-CTA kernel path
+        o2 = D.GatheredOutput(small_m, n, payload="mxfp8")
+        c2, s2 = D.sharded_gemm_fused(a[:small_m], w, "mxfp8", o2)
+        f2 = D.sharded_gemm_fused(a[:small_m], w, "mxfp8", D.GatheredOutput(small_m, n))
+        torch.cuda.synchronize()
+        wc, ws = ops.quantize_mxfp8(f2, 1)
+        assert torch.equal(c2, wc) and torch.equal(s2, ws)
+
+
+def test_fused_gemm_allgather_with_mxfp8_payload_equals_quantized_bf16_gather():
+    _run(_fused_codes_rank, 2)
 
 
 def _wgrad_rs_rank(rank, world):

@@ -185,16 +185,10 @@ def test_moe_block_host_state_matches_the_reference_layout():
     blk.post_step()
     assert torch.allclose(blk.router.expert_bias.bias, torch.tensor([-0.01, 0.01, 0.0, 0.0]))
     assert blk.expert_load.train_load.sum().item() == 0
-    # the bias moves the selection, never the weights (fp32 CPU input: the module's torch path)
-    torch.manual_seed(0)
+    # the router has no torch path: on a CPU tensor it raises instead of switching implementation
     r = MoERouter(16, 4, 2, expert_bias=True, router_score_fn="softmax")
-    x = torch.randn(32, 16)
-    i0, w0, p0 = r(x)
-    r.expert_bias.bias[3] = 10.0
-    i1, w1, p1 = r(x)
-    assert (i1 == 3).any(-1).all() and torch.equal(p0, p1)
-    raw = p1.gather(-1, i1)
-    assert torch.allclose(w1, raw / (raw.sum(-1, keepdim=True) + 1e-9))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        r(torch.randn(32, 16))
 
 
 def test_flop_and_parameter_accounting_of_the_mlp_blocks():
@@ -236,3 +230,50 @@ def test_activation_registries_cover_the_reference_names():
     gate, up = (x @ wgu.t()).chunk(2, -1)
     assert torch.allclose(gated_mlp(x, wgu, wd, silu_glu), (F.silu(gate) * up) @ wd.t())
     assert torch.allclose(ungated_mlp(x, wgu[:12], wd, F.relu, torch.ones(12)), F.relu(x @ wgu[:12].t() + 1) @ wd.t())
+
+
+def test_weight_cache_sees_version_bumps_and_can_be_invalidated(monkeypatch):
+    """The quantized-weight cache: reused while the parameter is untouched, rebuilt after an in-place op; a write
+    through ``.data`` is invisible to it (no version bump), which is what ``invalidate`` / ``post_step`` and the
+    B200Q_WEIGHT_CACHE=0 switch are for."""
+    import torch.nn as nn
+    from pretrain_b200.quant import cache
+    monkeypatch.delenv("B200Q_WEIGHT_CACHE", raising=False)
+    p = nn.Parameter(torch.ones(4, 4))
+    made = []
+
+    def make():
+        made.append(p.detach().clone())
+        return made[-1]
+
+    assert cache.cached(p, "mx", "k", make) is made[0] and cache.cached(p, "mx", "k", make) is made[0]
+    with torch.no_grad():
+        p.add_(1.0)                                           # bumps the version: seen
+    assert cache.cached(p, "mx", "k", make) is made[1] and made[1][0, 0] == 2
+    p.data.add_(1.0)                                          # does not: the stale copy is served
+    assert cache.cached(p, "mx", "k", make) is made[1]
+    assert cache.invalidate(p) == 1
+    assert cache.cached(p, "mx", "k", make) is made[2] and made[2][0, 0] == 3
+    assert cache.cached(p, "mx", "other key", make) is made[3]
+    lin = nn.Linear(4, 4)
+    cache.cached(lin.weight, "fp8", 0, make)
+    cache.cached(lin.weight, "mx", 0, make)
+    assert cache.invalidate(lin) == 2 and cache.invalidate(lin) == 0
+    monkeypatch.setenv("B200Q_WEIGHT_CACHE", "0")             # switch: every call re-quantizes
+    n = len(made)
+    cache.cached(p, "mx", "k", make); cache.cached(p, "mx", "k", make)
+    assert len(made) == n + 2
+    assert cache.cached(torch.ones(2), "mx", "k", lambda: 7) == 7      # plain tensors are never cached
+
+
+def test_quant_linear_post_step_drops_the_cached_weight_copies():
+    """QuantLinear.post_step is what the reference's loop calls after optimizer.step() (src/training/trainer.py:367)."""
+    from pretrain_b200.quant import cache
+    from pretrain_b200.quant.config import TrainingConfig
+    from pretrain_b200.quant.linear import QuantLinear
+    cfg = TrainingConfig(quant={"enabled": True, "dtype_recipe": "mxfp8"}).quant[0]
+    q = QuantLinear(32, 32, False, cfg)
+    cache.cached(q.weight, "mx", 0, lambda: 1)
+    assert hasattr(q.weight, "_b200q_mx")
+    q.post_step()
+    assert not hasattr(q.weight, "_b200q_mx")
