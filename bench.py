@@ -6,16 +6,25 @@ One "step" is one pass of the path over one batch of synthetic operands already 
 quantize A (bf16 -> MXFP8), quantize B, block-scaled GEMM D = A . B^T (bf16 out) — what
 `_gemm(a, b, "mxfp8", "mxfp8", ...)` does for one linear layer.  The default workload is the
 square 8192^3 case the GEMM targets are quoted on.  With N > 1 (launched by torchrun, one rank
-per GPU) every rank runs the same step on its own M-shard of a problem that is N times taller
-(weak scaling, B replicated, no collective on the data path); the output all-gather the
-M-sharded layout would need for a replicated result is timed separately and reported under
-"allgather".
+per GPU) A is sharded by rows over the ranks (B replicated) and the step ends with the all-gather
+of the bf16 output shards - fused into the GEMM's epilogue, which stores every tile into all ranks'
+gathered buffers over NVLink - and the rendezvous after which the gathered matrix may be read:
+`value` includes both.  `--scaling weak` (default): every rank brings the workload's M rows;
+`--scaling strong`: the workload's M rows are split over the ranks.  The same step without the
+gather ("compute_only"), with `ncclAllGather` after the GEMM and with an MXFP8 payload are reported
+beside it under "allgather".
+
+The --steps-long block is repeated (each block bracketed by barrier + synchronize and timed with CUDA
+events) until at least --min-seconds of device time have been timed; the median block is reported and
+the SM clock is sampled throughout.
 
 Prints ONE JSON line (rank 0).  `value` is device-timed whole-job TFLOPS; `e2e` is the same
 metric through the public `_gemm` call with host buffers (H2D of both operands and D2H of the
 result inside the timed region); `roofline` is the GEMM kernel against the measured tensor
-peak; `cpu_baseline` is the oracle's fake-quantize-then-matmul on this box's host cores.
-`--impl reference` times that CPU path alone.
+peak (burst or sustained according to how long the kernel's loop ran); the default line also carries
+the NVFP4 GEMM and the quantizers on 8192-sized operands, and `incumbent`: torch's scaled matmul
+(cuBLASLt, the reference's own GPU call) on the same codes; `cpu_baseline` is the oracle's
+fake-quantize-then-matmul on this box's host cores.  `--impl reference` times that CPU path alone.
 """
 
 from __future__ import annotations
@@ -144,12 +153,20 @@ def cpu_sample_shape(kind, m, n, k):
     return ms, ns, k
 
 
-def run_cpu(kind, m, n, k, steps, warmup):
+def run_cpu(kind, m, n, k, steps, warmup, budget_s=150.0):
+    """`steps` timed passes after `warmup` untimed ones, as asked - cut short only if the host is so slow that the whole
+    run would pass `budget_s` seconds (the counts actually run are returned and reported)."""
     ms, ns, ks = cpu_sample_shape(kind, m, n, k)
     g = torch.Generator().manual_seed(0)
     a = torch.randn(ms, ks, generator=g).bfloat16()
     b = torch.randn(ns, ks, generator=g).bfloat16()
-    for _ in range(warmup):
+    start = time.perf_counter()
+    cpu_step(kind, a, b)                                    # first pass: also tells how many more fit the budget
+    per = time.perf_counter() - start
+    fit = max(2, int(budget_s / max(per, 1e-3)))
+    warmup = max(1, min(warmup, fit // 4))
+    steps = max(1, min(steps, fit - warmup))
+    for _ in range(warmup - 1):
         cpu_step(kind, a, b)
     t0 = time.perf_counter()
     for _ in range(steps):
@@ -157,7 +174,7 @@ def run_cpu(kind, m, n, k, steps, warmup):
     dt = (time.perf_counter() - t0) / steps
     return {"value": 2.0 * ms * ns * ks / dt / 1e12, "unit": "TFLOPS", "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"{ms}x{ns}x{ks} slice of the {m}x{n}x{k} workload, {steps} step(s) after {warmup} warm-up",
-            "ms_per_step": dt * 1e3}
+            "ms_per_step": dt * 1e3, "steps": steps, "warmup": warmup}
 
 
 # ------------------------------------------------------------------------------------------
@@ -349,32 +366,77 @@ def run_moe(args, t, d, inter, rank, world, local):
             except Exception as ex:                       # symmetric memory not available on this system
                 expert_parallel["fused_error"] = str(ex)[:200]
 
+    # ---- incumbent: the reference's own expert path on this GPU - sort / bincount / gather, two bf16 torch._grouped_mm with
+    # SwiGLU between (src/layers/mlp.py:446-477, :89,97), index_add_ - on the same tokens and weights
+    incumbent = None
+    if world == 1:
+        try:
+            import torch.nn.functional as F
+
+            def ref_block(marks=None):
+                ev(marks)
+                expert_ids = top_i.reshape(-1)
+                token_ids = torch.arange(t, device="cuda").repeat_interleave(k)
+                ids_sorted, order = expert_ids.sort(stable=True)
+                tok_sorted, w_sorted = token_ids[order], top_w.reshape(-1, 1)[order]
+                offs = torch.bincount(ids_sorted, minlength=e).cumsum(0).to(torch.int32)
+                xs = x[tok_sorted]
+                ev(marks)
+                h = torch._grouped_mm(xs, w_gu.mT, offs=offs)
+                ev(marks)
+                gate, up = h.chunk(2, dim=-1)
+                h = F.silu(gate) * up
+                ev(marks)
+                y = torch._grouped_mm(h, w_d.mT, offs=offs)
+                ev(marks)
+                o = torch.zeros_like(x).index_add_(0, tok_sorted, y * w_sorted)
+                ev(marks)
+                return o
+
+            for _ in range(3):
+                ref_block()
+            torch.cuda.synchronize()
+            rm = []
+            t0.record()
+            for _ in range(20):
+                ref_block(rm)
+            t1.record()
+            torch.cuda.synchronize()
+            ref_ms = t0.elapsed_time(t1) / 20
+            rseg = [rm[i:i + 6] for i in range(0, len(rm), 6)]
+            ravg = lambda i: sum(sg[i].elapsed_time(sg[i + 1]) for sg in rseg) / len(rseg)
+            incumbent = {"call": "the reference's expert path in bf16: sort / bincount / gather, torch._grouped_mm x 2 with SwiGLU between, index_add_ "
+                                 "(src/layers/mlp.py:446-477)", "block_ms": ref_ms, "permute_ms": ravg(0), "grouped_mm1_ms": ravg(1), "swiglu_ms": ravg(2),
+                         "grouped_mm2_ms": ravg(3), "unpermute_ms": ravg(4), "grouped_mm_tflops": flops / ((ravg(1) + ravg(3)) * 1e-3) / 1e12,
+                         "ours_block_ms": ms_step, "speedup_block": ref_ms / ms_step,
+                         "speedup_gemms": (ravg(1) + ravg(2) + ravg(3)) / (gemm1_ms + gemm2_ms),
+                         "note": "speedup_gemms compares grouped_mm1 + SwiGLU + grouped_mm2 with this library's two grouped GEMMs (SwiGLU in the first one's epilogue)"}
+        except Exception as ex:
+            incumbent = {"error": f"{type(ex).__name__}: {str(ex)[:200]}"}
+
     peaks = measured_peaks()
-    peak = peaks["bf16_tflops_sustained"] * 2.0
     gemm_ms = gemm1_ms + gemm2_ms
-    achieved = flops / (gemm_ms * 1e-3) / 1e12
-    hbm = lambda nbytes, ms: {"achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                              "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "kernels_ms": ms, "bytes": nbytes}
+    clocks = clk.summary()
+    hbm = lambda nbytes, ms: {k2: v for k2, v in hbm_record(nbytes, ms, peaks).items() if k2 != "bound"}
     line = {"metric": "MoE block grouped-GEMM TFLOPS/GPU (permute + MXFP8 grouped GEMMs + SwiGLU + unpermute)",
             "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "mxfp8", "data": "synthetic",
             "config": {"workload": args.workload, "tokens_per_gpu": t, "hidden": d, "intermediate": inter, "experts": e, "top_k": k,
                        "l2": "weights (108 MB bf16) + permuted activations exceed L2; no flush needed"},
-            "clocks": clk.summary(),
+            "clocks": clocks,
             "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2},
             "gpu_launches": 9 * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<mxfp8> (grouped, 2 launches; the first one's epilogue does "
-                                                       "SwiGLU + MXFP8)", "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"2 x bf16_tflops_sustained, {peaks['source']}",
-                         "frac_of_nominal": achieved / 4500.0, "nominal_peak": 4500.0, "traffic": None, "kernel_ms": gemm_ms,
-                         "gemm1_swiglu_ms": gemm1_ms, "gemm2_ms": gemm2_ms},
+            "roofline": roofline_tensor("grouped MXFP8 GEMMs (2 launches; the first one's epilogue does SwiGLU + MXFP8)", flops, gemm_ms, 2.0,
+                                        4500.0, gemm_ms * args.steps * 1e-3, clocks, peaks, gemm1_swiglu_ms=gemm1_ms, gemm2_ms=gemm2_ms),
             "permute": dict(bound="hbm", **hbm(n_pairs * d * 3.03125, permute_ms), note="plan kernels + gather fused with MXFP8"),
             "weight_quantize": dict(bound="hbm", **hbm((w_gu.numel() + w_d.numel()) * 3.03125, wquant_ms)),
             "unpermute": dict(bound="hbm", **hbm(n_pairs * d * 2 + t * d * 2, unperm_ms))}
     if expert_parallel is not None:
         line["expert_parallel"] = expert_parallel
+    if incumbent is not None:
+        line["incumbent"] = incumbent
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_moe_sample(t, d, inter)
@@ -465,21 +527,19 @@ def run_moe_training(args, t, d, inter, rank, world, local):
     torch.cuda.synchronize()
     e2e_ms = t0.elapsed_time(t1) / n_e2e
     peaks = measured_peaks()
-    peak = peaks["bf16_tflops_sustained"] * 2.0
     achieved = flops / (ms_step * 1e-3) / 1e12
+    clocks = clk.summary()
     line = {"metric": "MoE block grouped-GEMM TFLOPS/GPU (forward + backward of the expert path)",
             "value": world * achieved, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8", "data": "synthetic",
             "config": {"workload": args.workload, "tokens_per_gpu": t, "hidden": d, "intermediate": inter, "experts": e, "top_k": k,
                        "l2": "weights and permuted activations exceed L2; no flush needed"},
-            "clocks": clk.summary(),
+            "clocks": clocks,
             "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": (hx.numel() + hd.numel()) * 2, "d2h_bytes_per_step": hgx.numel() * 2},
             "gpu_launches": 24 * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "whole step (6 grouped GEMMs and the HBM-bound kernels between them)",
-                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "peak_source": f"2 x bf16_tflops_sustained, {peaks['source']}", "frac_of_nominal": achieved / 4500.0,
-                         "nominal_peak": 4500.0, "traffic": None, "kernel_ms": ms_step}}
+            "roofline": roofline_tensor("whole step (6 grouped GEMMs and the HBM-bound kernels between them)", flops, ms_step, 2.0, 4500.0,
+                                        ms_step * args.steps * 1e-3, clocks, peaks)}
     if graph is not None:
         line["cuda_graph"] = graph
     if rank == 0:
@@ -637,28 +697,60 @@ def run_composite(args, kind, d0, d1, d2, rank, world, local):
     e2e_ms = t0.elapsed_time(t1) / n_e2e
 
     peaks = measured_peaks()
-    peak = peaks["bf16_tflops_sustained"] * peak_ratio
     gemm_ms, gemm_flops = per["gemm"]
-    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
     q_ms, q_bytes = per["quantize"]
+    clocks = clk.summary()
+    incumbent = None
+    if kind == "fp8_triple" and world == 1:
+        # the reference's own GPU path for the same three GEMMs: fp8_gemm(rowwise=True) = two quantize_fp8 passes in torch +
+        # torch._scaled_mm each (src/quant/fp8.py:35-65, src/quant/linear.py:74,98,102), here written with torch ops on the GPU
+        try:
+            fmax = {E4: 448.0, E5: 57344.0}
+
+            def q_ref(t_, dt, dim):
+                amax = t_.abs().amax(dim=dim, keepdim=True).float()
+                sc = (amax / fmax[dt]).clamp_min(1e-12)
+                return (t_.float() / sc).clamp(-fmax[dt], fmax[dt]).to(dt), sc
+
+            def ref_gemm(a_, b_, adt, bdt):                      # a_ (M, C), b_ (C, N)
+                qa, sa_ = q_ref(a_, adt, -1)
+                qb, sb_ = q_ref(b_, bdt, 0)
+                return torch._scaled_mm(qa, qb.t().contiguous().t(), scale_a=sa_, scale_b=sb_, out_dtype=torch.bfloat16)
+
+            def ref_step():
+                ref_gemm(x, w.t(), E4, E4)
+                ref_gemm(dy, w, E5, E4)
+                ref_gemm(dy.t(), x, E5, E4)
+
+            ref_ms = time_loop(ref_step, reps=10, warm=3)
+            cx, sx, cxt, sxt = ops.quantize_fp8_both(x, E4); cw, sw, cwt, swt = ops.quantize_fp8_both(w, E4)
+            cg, sg, cgt, sgt = ops.quantize_fp8_both(dy, E5)
+            mm = lambda a_, b_, sa_, sb_: torch._scaled_mm(a_, b_.t(), scale_a=sa_.view(-1, 1), scale_b=sb_.view(1, -1), out_dtype=torch.bfloat16)
+            gemms_only = time_loop(lambda: (mm(cx.view(E4), cw.view(E4), sx, sw), mm(cg.view(E5), cwt.view(E4), sg, swt),
+                                            mm(cgt.view(E5), cxt.view(E4), sgt, sxt)), reps=20)
+            incumbent = {"call": "the reference's GPU path for the three GEMMs: quantize_fp8 (torch ops) x 2 + torch._scaled_mm each "
+                                 "(src/quant/fp8.py:16-65)", "step_ms": ref_ms, "ours_step_ms": ms_step, "speedup_step": ref_ms / ms_step,
+                         "scaled_mm_x3_ms": gemms_only, "ours_gemms_ms": gemm_ms, "speedup_gemms": gemms_only / gemm_ms,
+                         "scaled_mm_tflops": flops / (gemms_only * 1e-3) / 1e12}
+        except Exception as ex:
+            incumbent = {"error": f"{type(ex).__name__}: {str(ex)[:200]}"}
     line = {"metric": METRIC.replace("linear step: quantize A + quantize B + GEMM", "all quantize + GEMM launches of the workload"),
             "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": dtype, "data": "synthetic",
             "config": dict(workload=args.workload, l2="tensors of a step total > 126 MB (larger than L2); no flush needed", **desc),
-            "clocks": clk.summary(),
+            "clocks": clocks,
             "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "all GEMM launches of the step", "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_ratio:g} x bf16_tflops_sustained, {peaks['source']}",
-                         "frac_of_nominal": achieved / nominal, "nominal_peak": nominal, "traffic": None, "kernel_ms": gemm_ms},
-            "quantize": {"bound": "hbm", "achieved": q_bytes / (q_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": q_bytes / (q_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "kernels_ms": q_ms, "bytes": q_bytes}}
+            "roofline": roofline_tensor("all GEMM launches of the step", gemm_flops, gemm_ms, peak_ratio, nominal, gemm_ms * args.steps * 1e-3,
+                                        clocks, peaks),
+            "quantize": hbm_record(q_bytes, q_ms, peaks)}
     if "elementwise" in per:
         e_ms, e_bytes = per["elementwise"]
-        line["swiglu"] = {"bound": "hbm", "achieved": e_bytes / (e_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                          "frac": e_bytes / (e_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "kernels_ms": e_ms, "bytes": e_bytes}
+        line["swiglu"] = hbm_record(e_bytes, e_ms, peaks)
+    if incumbent is not None:
+        line["incumbent"] = incumbent
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_composite_sample(kind, d0, d1, d2)
@@ -699,51 +791,180 @@ def cpu_composite_sample(kind, d0, d1, d2, rows=1024):
             "ms_per_step": dt * 1e3}
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
-    ap.add_argument("--workload", default="mxfp8_square_8192", choices=sorted(WORKLOADS))
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    args = ap.parse_args()
-    kind, m, n, k = WORKLOADS[args.workload]
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    config = {"workload": args.workload, "kind": kind, "M_per_gpu": m, "N": n, "K": k,
-              "sharding": "rows of A (M) across ranks, B replicated" if world > 1 else "single GPU",
-              "l2": "operands, codes and output of a step total > 126 MB (larger than L2); no flush needed"}
+# ------------------------------------------------------------------------------------------
+# Timing helpers
+# ------------------------------------------------------------------------------------------
+MIN_TIMED_SECONDS = 2.0          # the headline loop repeats its --steps-long block until this much device time is timed
 
-    if args.impl == "reference":
-        if rank != 0:
-            return
-        torch.set_num_threads(len(os.sched_getaffinity(0)))     # torchrun pins OMP_NUM_THREADS=1
-        steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
-        if kind in ("moe", "moe_train"):
-            cb = cpu_moe_sample(m, n, k)
-        elif kind in ("nvfp4_mlp", "fp8_triple", "mxfp8_triple"):
-            cb = cpu_composite_sample(kind, m, n, k)
-        else:
-            cb = run_cpu(kind, m, n, k, steps, warm)
-        print(json.dumps({"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOPS", "n_gpus": args.gpus,
-                          "steps": steps, "warmup": warm, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
-                          "scaling": "weak", "vs_baseline": None, "dtype": "bf16 matmul of fake-quantized operands (CPU)",
-                          "data": "synthetic", "config": config,
-                          "cpu_baseline": {k2: cb[k2] for k2 in ("value", "unit", "cores", "kind", "sample")},
-                          "e2e": {"value": cb["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
-        return
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path for the product arm")
-    torch.cuda.set_device(local)
-    if kind == "moe":
-        return run_moe(args, m, n, k, rank, world, local)
-    if kind == "moe_train":
-        return run_moe_training(args, m, n, k, rank, world, local)
-    if kind in ("nvfp4_mlp", "fp8_triple", "mxfp8_triple"):
-        return run_composite(args, kind, m, n, k, rank, world, local)
+def tensor_peak(ratio, region_s, peaks):
+    """Tensor-pipe denominator for a kernel timed over `region_s` seconds: `ratio` x the driver-measured bf16 cuBLAS
+    rate (FP8 = 2 x, FP4 = 4 x) - the burst figure for a region that ends before the power cap settles the clock
+    (under ~1 s), the sustained figure for a longer one.  Both are returned so that either fraction can be read."""
+    burst, sustained = ratio * peaks["bf16_tflops"], ratio * peaks["bf16_tflops_sustained"]
+    use_sustained = region_s >= 1.0
+    return {"peak": sustained if use_sustained else burst, "peak_burst": burst, "peak_sustained": sustained,
+            "peak_source": f"{ratio:g} x bf16_tflops{'_sustained' if use_sustained else ''} ({peaks['source']}); timed region {region_s:.2f} s"}
+
+
+def roofline_tensor(kernel, flops, kernel_ms, ratio, nominal, region_s, clocks, peaks, traffic=None, **extra):
+    achieved = flops / (kernel_ms * 1e-3) / 1e12
+    pk = tensor_peak(ratio, region_s, peaks)
+    out = {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": pk["peak"], "unit": "TFLOP/s", "frac": achieved / pk["peak"],
+           "frac_of_burst": achieved / pk["peak_burst"], "frac_of_sustained": achieved / pk["peak_sustained"], "peak_source": pk["peak_source"],
+           "frac_of_nominal": achieved / nominal, "nominal_peak": nominal, "traffic": traffic, "kernel_ms": kernel_ms}
+    mhz, mx = (clocks or {}).get("sm_mhz"), (clocks or {}).get("sm_max_mhz")
+    if mhz and mx:
+        # the same kernel time expressed at the maximum SM clock: separates what the kernel loses from what the
+        # power cap takes (no GPU setting is touched: the clock is only sampled)
+        out["clock_normalized"] = {"sm_mhz_median": mhz, "sm_max_mhz": mx, "kernel_ms_x_mhz_over_max": kernel_ms * mhz / mx,
+                                   "achieved_at_max_clock": achieved * mx / mhz, "frac_of_nominal_at_max_clock": achieved * mx / mhz / nominal}
+    out.update(extra)
+    return out
+
+
+def hbm_record(nbytes, ms, peaks, **extra):
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return dict({"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                 "peak_source": f"hbm_gbs, {peaks['source']}", "kernels_ms": ms, "bytes": nbytes}, **extra)
+
+
+def time_loop(fn, reps=20, warm=5):
+    """Mean CUDA-event time of fn() over `reps` back-to-back calls after `warm` warm-ups (ms)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(reps):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / reps
+
+
+def timed_blocks(run_block, min_seconds, barrier, dist=None, max_blocks=5000):
+    """run_block() enqueues exactly --steps steps.  Each block is bracketed by barrier + synchronize on both sides
+    and timed with CUDA events; blocks repeat until `min_seconds` of device time have been timed (the count is
+    agreed over the ranks after the first block).  Returns the per-block times in ms, max over ranks."""
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def one():
+        barrier()
+        t0.record()
+        run_block()
+        t1.record()
+        barrier()
+        return t0.elapsed_time(t1)
+
+    first = one()
+    if dist is not None:
+        t = torch.tensor([first], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        first = t.item()
+    n_more = max(0, min(max_blocks, int(min_seconds * 1e3 / max(first, 1e-3)) + 1) - 1)
+    times = [first] + [one() for _ in range(n_more)]
+    if dist is not None:
+        t = torch.tensor(times, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times = t.tolist()
+        times[0] = first
+    return times
+
+
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2] if len(xs) % 2 else 0.5 * (xs[len(xs) // 2 - 1] + xs[len(xs) // 2])
+
+
+# ------------------------------------------------------------------------------------------
+# Incumbents: the library kernels the reference itself calls on a GPU, timed on the same box
+# ------------------------------------------------------------------------------------------
+def incumbent_scaled_mm(ops, kinds, shapes, seed=7):
+    """torch's scaled matmul (cuBLASLt) - `torch._scaled_mm`, the reference's GPU call at src/quant/fp8.py:59-65, and
+    its block-scaled modes - on this library's own codes and scale factors, beside this library's GEMM on the same
+    operands.  GEMM kernels only (operands quantized beforehand), 20 launches after 5 warm-ups each."""
+    import torch.nn.functional as F
+    E4, e8, f4 = torch.float8_e4m3fn, torch.float8_e8m0fnu, torch.float4_e2m1fn_x2
+    S, Z = F.ScalingType, F.SwizzleType
+    out = {}
+    for kind, (m, n, k) in zip(kinds, shapes):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        a = torch.randn(m, k, generator=g, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(n, k, generator=g, device="cuda", dtype=torch.bfloat16)
+        d = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        rec = {"shape": f"{m}x{n}x{k}"}
+        try:
+            if kind == "fp8":
+                ca, sa = ops.quantize_fp8(a, E4, 1); cb, sb = ops.quantize_fp8(b, E4, 1)
+                ours = lambda: ops.gemm_fp8(ca, E4, cb, E4, sa, sb, out=d)
+                av, bv, sav, sbv = ca.view(E4), cb.view(E4).t(), sa.view(-1, 1), sb.view(1, -1)
+                theirs = lambda: torch._scaled_mm(av, bv, scale_a=sav, scale_b=sbv, out_dtype=torch.bfloat16)
+                rec["call"] = "torch._scaled_mm, per-row scales (src/quant/fp8.py:59-65)"
+            elif kind == "mxfp8":
+                ca, sfa = ops.quantize_mxfp8(a, 1); cb, sfb = ops.quantize_mxfp8(b, 1)
+                ours = lambda: ops.gemm_mxfp8(ca, sfa, cb, sfb, out=d)
+                av, bv, sav, sbv = ca.view(E4), cb.view(E4).t(), sfa.view(e8), sfb.view(e8)
+                theirs = lambda: F.scaled_mm(av, bv, sav, S.BlockWise1x32, sbv, S.BlockWise1x32, swizzle_a=Z.SWIZZLE_32_4_4,
+                                             swizzle_b=Z.SWIZZLE_32_4_4, output_dtype=torch.bfloat16)
+                rec["call"] = "torch.nn.functional.scaled_mm, BlockWise1x32 E8M0 scales, SWIZZLE_32_4_4 (cuBLASLt)"
+            else:
+                pa, sfa, ta = ops.quantize_nvfp4(a, 1); pb, sfb, tb = ops.quantize_nvfp4(b, 1)
+                ours = lambda: ops.gemm_nvfp4(pa, sfa, ta, pb, sfb, tb, out=d)
+                av, bv, sav, sbv = pa.view(f4), pb.view(f4).t(), sfa.view(E4), sfb.view(E4)
+                theirs = lambda: F.scaled_mm(av, bv, sav, S.BlockWise1x16, sbv, S.BlockWise1x16, swizzle_a=Z.SWIZZLE_32_4_4,
+                                             swizzle_b=Z.SWIZZLE_32_4_4, output_dtype=torch.bfloat16)
+                rec["call"] = ("torch.nn.functional.scaled_mm, BlockWise1x16 E4M3 scales, SWIZZLE_32_4_4 (cuBLASLt); the fp32 tensor "
+                               "scales, which this library applies in its epilogue, are left out of torch's launch")
+            ours_ms = time_loop(ours)
+            rec.update(ours_ms=ours_ms, ours_tflops=2.0 * m * n * k / (ours_ms * 1e-3) / 1e12)
+            theirs()
+            torch.cuda.synchronize()
+            their_ms = time_loop(theirs)
+            rec.update(incumbent_ms=their_ms, incumbent_tflops=2.0 * m * n * k / (their_ms * 1e-3) / 1e12, speedup=their_ms / ours_ms)
+        except Exception as ex:                                   # torch refused this mode on this build: say so
+            rec["error"] = f"{type(ex).__name__}: {str(ex).splitlines()[0][:200]}" if str(ex) else type(ex).__name__
+        out[f"{kind}_{m}x{n}x{k}"] = rec
+    return out
+
+
+def secondary_kernels(ops, peaks, clocks):
+    """The other targets quoted on the 8192-sized problem, each with its own short event-timed loop: the NVFP4 GEMM, and
+    the NVFP4 / FP8 / MXFP8 quantizers on 8192 x 8192 and 16384 x 2048 bf16 operands (inputs of 128 and 64 MiB; with
+    their outputs every call moves more than the 126 MB L2 holds)."""
+    E4 = torch.float8_e4m3fn
+    g = torch.Generator(device="cuda").manual_seed(4321)
+    a = torch.randn(8192, 8192, generator=g, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(8192, 8192, generator=g, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(16384, 2048, generator=g, device="cuda", dtype=torch.bfloat16)
+    d = torch.empty(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    pa, sfa, ta = ops.quantize_nvfp4(a, 1); pb, sfb, tb = ops.quantize_nvfp4(b, 1)
+    reps = 60
+    nv_ms = time_loop(lambda: ops.gemm_nvfp4(pa, sfa, ta, pb, sfb, tb, out=d), reps=reps)
+    flops = 2.0 * 8192 ** 3
+    out = {"roofline_nvfp4": roofline_tensor("gemm_pair_kernel<nvfp4> 8192^3", flops, nv_ms, 4.0, NOMINAL_TFLOPS["nvfp4"], reps * nv_ms * 1e-3,
+                                             clocks, peaks, traffic=GEMM_DRAM_TRAFFIC.get("nvfp4_square_8192"))}
+    am = ops.amax(a)
+    n_el = a.numel()
+    out["quantize_nvfp4"] = hbm_record(n_el * 2.5625, time_loop(lambda: ops.quantize_nvfp4(a, 1, am)), peaks, shape="8192x8192",
+                                       note="quantize kernel alone (tensor amax given): 2 + 0.5 + 1/16 B per element")
+    out["amax"] = hbm_record(n_el * 2.0, time_loop(lambda: ops.amax(a)), peaks, shape="8192x8192")
+    out["quantize_mxfp8"] = hbm_record(n_el * 3.03125, time_loop(lambda: ops.quantize_mxfp8(a, 1)), peaks, shape="8192x8192")
+    out["quantize_fp8"] = hbm_record(n_el * (3.0 + 4.0 / 8192), time_loop(lambda: ops.quantize_fp8(a, E4, 1)), peaks, shape="8192x8192",
+                                     note="per-row FP8 (src/quant/fp8.py:16-32 with dim=-1)")
+    nx = x.numel()
+    out["quantize_fp8_16384x2048"] = hbm_record(nx * (3.0 + 4.0 / 2048), time_loop(lambda: ops.quantize_fp8(x, E4, 1)), peaks, shape="16384x2048")
+    out["quantize_fp8_both_16384x2048"] = hbm_record(nx * 4.0, time_loop(lambda: ops.quantize_fp8_both(x, E4)), peaks, shape="16384x2048",
+                                                     note="per row and per column from one call; algorithmic bytes: one read, two sets of codes")
+    out["quantize_mxfp8_dual_16384x2048"] = hbm_record(nx * 4.0625, time_loop(lambda: ops.quantize_mxfp8_dual(x, E4)), peaks, shape="16384x2048")
+    return out
+
+
+def run_dense(args, kind, m, n, k, rank, world, local, config):
+    """Square / linear-layer workloads: quantize A, quantize B, GEMM.  One GPU: that step.  N GPUs: M sharded over the
+    ranks (weak: every rank brings `m` rows; strong: `m` rows in total), B replicated, and the step ends with the
+    all-gather of the output shards, fused into the GEMM's epilogue (TMA stores into the peers' gathered buffers over
+    NVLink), plus the rendezvous that makes the gathered matrix readable - all inside `value`."""
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -759,64 +980,88 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def rank_max(*vals):
+        if dist is None:
+            return vals if len(vals) > 1 else vals[0]
+        t = torch.tensor(vals, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist() if len(vals) > 1 else t.item()
+
+    strong = args.scaling == "strong" and world > 1
+    m_rank = m // world if strong else m                 # rows of A (and of the output) this rank computes
+    if strong and (m % (128 * world)):
+        raise SystemExit("--scaling strong needs M to split into 128-row tiles per rank")
+    peaks = measured_peaks()
+    fmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3", "int8": "int8"}[kind]
+    ratio = {"mxfp8": 2.0, "fp8": 2.0, "int8": 2.0, "nvfp4": 4.0}[kind]
     g = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    a = torch.randn(m, k, generator=g, device="cuda", dtype=torch.bfloat16)
+    a = torch.randn(m_rank, k, generator=g, device="cuda", dtype=torch.bfloat16)
     gb = torch.Generator(device="cuda").manual_seed(99)
     b = torch.randn(n, k, generator=gb, device="cuda", dtype=torch.bfloat16)
-    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-    step, launches = make_step(kind, a, b, out)
+    out = torch.empty(m_rank, n, device="cuda", dtype=torch.bfloat16)
+    compute_step, launches = make_step(kind, a, b, out)
+    flops = 2.0 * m_rank * n * k                         # per rank and step
+    warm = max(args.warmup, 3)
 
-    for _ in range(max(args.warmup, 3)):
+    gathered = None
+    if dist is not None and kind != "int8":
+        from pretrain_b200 import dist as D
+        gathered = D.GatheredOutput(m_rank, n)
+        step = lambda marks=None: D.sharded_gemm_fused(a, b, fmt, gathered)      # the product call: quantize x 2, GEMM + gather, rendezvous
+    else:
+        step = compute_step
+
+    # ---- headline: blocks of --steps steps until MIN_TIMED_SECONDS of device time -------------
+    for _ in range(warm):
         step()
     barrier()
     marks = []
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
+        block_ms = timed_blocks(lambda: [step(marks) for _ in range(args.steps)], args.min_seconds, barrier, dist)
+    ops.device_status()
+    clocks = clk.summary()
+    timed_region_s = sum(block_ms) * 1e-3
+    ms_step = median(block_ms) / args.steps
+    value = world * flops / (ms_step * 1e-3) / 1e12
+
+    # ---- the compute-only step (no gather), with its quantize / GEMM split from events ---------
+    if step is compute_step:
+        trip = [marks[i:i + 3] for i in range(0, len(marks), 3)]
+        co_ms = ms_step
+        co_region_s = timed_region_s
+    else:
+        marks = []
+        for _ in range(3):
+            compute_step()
         barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_co = max(args.steps, 20)
         t0.record()
-        for _ in range(args.steps):
-            step(marks)
+        for _ in range(n_co):
+            compute_step(marks)
         t1.record()
         barrier()
-    ops.device_status()
-    ms_total = t0.elapsed_time(t1)
-    trip = [marks[i:i + 3] for i in range(0, len(marks), 3)]       # (quantize start, GEMM start, GEMM end) per step
+        co_ms = rank_max(t0.elapsed_time(t1) / n_co)
+        co_region_s = co_ms * n_co * 1e-3
+        trip = [marks[i:i + 3] for i in range(0, len(marks), 3)]
     quant_ms = sum(q.elapsed_time(g0) for q, g0, _ in trip) / len(trip)
     gemm_ms = sum(g0.elapsed_time(g1) for _, g0, g1 in trip) / len(trip)
-    if dist is not None:
-        t = torch.tensor([ms_total, gemm_ms, quant_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, gemm_ms, quant_ms = t.tolist()
-    ms_step = ms_total / args.steps
-    flops = 2.0 * m * n * k
-    value = world * flops / (ms_step * 1e-3) / 1e12
+    gemm_ms, quant_ms = rank_max(gemm_ms, quant_ms)
 
     # Short steps are bound by the host's launch rate, not by the GPU: replay the same step from a CUDA graph
     # (what a training loop that cares would do) and report it beside the eager number.
     graph = None
-    if ms_step < 0.25:
+    if co_ms < 0.25 and dist is None:
         try:
             cg = torch.cuda.CUDAGraph()
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                step()
+                compute_step()
                 with torch.cuda.graph(cg, stream=side):
-                    step()
+                    compute_step()
             torch.cuda.current_stream().wait_stream(side)
-            for _ in range(3):
-                cg.replay()
-            barrier()
-            t0.record()
-            for _ in range(args.steps):
-                cg.replay()
-            t1.record()
-            barrier()
-            g_ms = t0.elapsed_time(t1) / args.steps
-            if dist is not None:
-                t = torch.tensor([g_ms], device="cuda", dtype=torch.float64)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                g_ms = t.item()
+            g_ms = time_loop(cg.replay, reps=max(args.steps, 20), warm=3)
             graph = {"ms_per_step": g_ms, "value": world * flops / (g_ms * 1e-3) / 1e12, "unit": "TFLOPS",
                      "note": "the same step replayed from a CUDA graph (no host launch cost)"}
         except Exception as ex:
@@ -824,7 +1069,6 @@ def main():
 
     # ---- end to end through the public call, host buffers --------------------------------
     from pretrain_b200.quant.linear import _gemm
-    fmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3", "int8": "int8"}[kind]
     # B is replicated over the ranks: with more than one rank each copies only ITS 1/world of B's rows from its
     # host buffer and the ranks all-gather the rest over NVLink (NCCL), so the host link carries every input
     # byte of the job once per step instead of B once per rank.
@@ -832,13 +1076,13 @@ def main():
     nb = n // world if shard_b else n
     b_lo = rank * nb if shard_b else 0
     ha, hb = a.cpu().pin_memory(), b[b_lo:b_lo + nb].cpu().pin_memory()
-    hout = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+    hout = torch.empty(m_rank, n, dtype=torch.bfloat16).pin_memory()
 
     # Three streams and two sets of device buffers: step i's host->device copy, step i-1's quantize + GEMM and
     # step i-2's device->host copy overlap (PCIe is full duplex and the copy engines run beside the SMs); every
     # step still copies its own inputs in and its own result out inside the timed region.
     s_in, s_in2, s_c, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-    dbuf = [(torch.empty_like(a), torch.empty_like(b), torch.empty(m, n, device="cuda", dtype=torch.bfloat16)) for _ in range(2)]
+    dbuf = [(torch.empty_like(a), torch.empty_like(b), torch.empty(m_rank, n, device="cuda", dtype=torch.bfloat16)) for _ in range(2)]
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_in2 = [torch.cuda.Event() for _ in range(2)]
     ev_c = [torch.cuda.Event() for _ in range(2)]
@@ -879,76 +1123,80 @@ def main():
     e2e_steps = max(4, min(args.steps, 12))
     e2e_run(4)
     barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     e2e_run(e2e_steps)
     t1.record()
     barrier()
-    e2e_ms = t0.elapsed_time(t1) / e2e_steps
-    if dist is not None:
-        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = t.item()
+    e2e_ms = rank_max(t0.elapsed_time(t1) / e2e_steps)
     e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": ha.numel() * 2 + hb.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2}
     if shard_b:
         e2e["replicated_operand"] = "each rank copies 1/%d of B from host; ncclAllGather over NVLink completes it" % world
 
-    # ---- output all-gather of the M-sharded layout (not on the data path; reported beside) --
+    # ---- the gather in its other forms, beside `value` -----------------------------------------
     allgather = None
-    if dist is not None:
-        full = torch.empty(world * m, n, device="cuda", dtype=torch.bfloat16)
-        for _ in range(2):
-            dist.all_gather_into_tensor(full, out)
-        barrier()
-        t0.record()
-        for _ in range(5):
-            step()
-            dist.all_gather_into_tensor(full, out)
-        t1.record()
-        barrier()
-        t = torch.tensor([t0.elapsed_time(t1) / 5], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ag_ms = t.item()
-        allgather = {"ms_per_step_with_allgather": ag_ms, "tflops_with_allgather": world * flops / (ag_ms * 1e-3) / 1e12,
-                     "bytes_received_per_rank": (world - 1) * m * n * 2, "collective": "ncclAllGather (NCCL over NVLink)"}
-        # the same step with the gather fused into the GEMM epilogue (TMA stores into the peers' buffers)
-        try:
-            from pretrain_b200 import dist as D
-            gout = D.GatheredOutput(m, n)
-            ffmt = {"mxfp8": "mxfp8", "nvfp4": "nvfp4", "fp8": "fp8_e4m3", "int8": "int8"}[kind]
+    if gathered is not None:
+        from pretrain_b200 import dist as D
+        link_bytes = (world - 1) * m_rank * n            # elements every rank receives
+        reps = 10
+        allgather = {"in_value": "bf16 payload, fused into the GEMM epilogue (TMA stores into every rank's gathered buffer), rendezvous included",
+                     "ms_per_step": ms_step, "ingress_gbs_per_rank": link_bytes * 2 / (ms_step * 1e-3) / 1e9,
+                     "bytes_received_per_rank": link_bytes * 2,
+                     "link_bound_ms": link_bytes * 2 / 770e9 * 1e3, "link_note": "770 GB/s per direction per GPU (measured peer copy on this pool)"}
+
+        def timed(fn):
             for _ in range(3):
-                D.sharded_gemm_fused(a, b, ffmt, gout)
+                fn()
             barrier()
             t0.record()
-            for _ in range(20):
-                D.sharded_gemm_fused(a, b, ffmt, gout)
+            for _ in range(reps):
+                fn()
             t1.record()
             barrier()
-            t = torch.tensor([t0.elapsed_time(t1) / 20], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            allgather["fused_ms_per_step"] = t.item()
-            allgather["fused_tflops"] = world * flops / (t.item() * 1e-3) / 1e12
-            allgather["fused"] = "GEMM epilogue stores every tile into all ranks' gathered buffers (symmetric memory, NVLink)"
-        except Exception as ex:                       # symmetric memory not available on this system
-            allgather["fused_error"] = str(ex)[:200]
+            return rank_max(t0.elapsed_time(t1) / reps)
 
-    # ---- data-parallel wgrad: dW = sum over ranks of dY_r^T . X_r, reduce-scattered by rows (not on the data path) ----
+        full = torch.empty(world * m_rank, n, device="cuda", dtype=torch.bfloat16)
+
+        def nccl_step():
+            compute_step()
+            dist.all_gather_into_tensor(full, out)
+
+        nccl_ms = timed(nccl_step)
+        allgather["nccl"] = {"ms_per_step": nccl_ms, "tflops": world * flops / (nccl_ms * 1e-3) / 1e12,
+                             "collective": "ncclAllGather of the bf16 shards after the GEMM"}
+        del full
+        if kind == "mxfp8" and m_rank % 128 == 0 and n % 128 == 0:
+            try:
+                gq = D.GatheredOutput(m_rank, n, payload="mxfp8")
+                q_ms = timed(lambda: D.sharded_gemm_fused(a, b, fmt, gq))
+                qb = link_bytes * 1.03125
+                allgather["mxfp8_payload"] = {
+                    "ms_per_step": q_ms, "tflops": world * flops / (q_ms * 1e-3) / 1e12, "bytes_received_per_rank": qb,
+                    "ingress_gbs_per_rank": qb / (q_ms * 1e-3) / 1e9, "link_bound_ms": qb / 770e9 * 1e3,
+                    "what": "the epilogue quantizes each output tile (rounded to bf16 first) to E4M3 codes + E8M0 scale bytes, bit-identical "
+                            "to quantizing the gathered bf16 matrix along its columns: the form the next block-scaled GEMM consumes"}
+            except Exception as ex:
+                allgather["mxfp8_payload"] = {"error": str(ex)[:200]}
+        ops.device_status()
+
+    # ---- data-parallel wgrad: dW = sum over ranks of dY_r^T . X_r, reduce-scattered by rows ----
     reduce_scatter = None
-    if dist is not None and kind == "mxfp8" and n % (32 * world) == 0:
+    if dist is not None and kind == "mxfp8" and not strong and n % (32 * world) == 0:
         try:
             from pretrain_b200 import dist as D
             e5, e4 = torch.float8_e5m2, torch.float8_e4m3fn
-            dy = (1e-2 * torch.randn(m, n, generator=g, device="cuda")).to(torch.bfloat16)
+            dy = (1e-2 * torch.randn(m_rank, n, generator=g, device="cuda")).to(torch.bfloat16)
             shard = torch.empty(n // world, k, device="cuda", dtype=torch.bfloat16)
 
-            def nccl_step():
+            def nccl_rs_step():
                 gt, gtsf = ops.quantize_mxfp8(dy, 0, e5)
                 xt, xtsf = ops.quantize_mxfp8(a, 0, e4)
                 dist.reduce_scatter_tensor(shard, ops.gemm_mxfp8(gt, gtsf, xt, xtsf, e5, e4))
 
             sc = D.ScatteredSum(n, k)
             times = []
-            for fn in (nccl_step, lambda: D.wgrad_reduce_scatter_fused(dy, a, sc)):
+            for fn in (nccl_rs_step, lambda: D.wgrad_reduce_scatter_fused(dy, a, sc)):
                 for _ in range(3):
                     fn()
                 barrier()
@@ -957,9 +1205,7 @@ def main():
                     fn()
                 t1.record()
                 barrier()
-                t = torch.tensor([t0.elapsed_time(t1) / 10], device="cuda", dtype=torch.float64)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                times.append(t.item())
+                times.append(rank_max(t0.elapsed_time(t1) / 10))
             reduce_scatter = {"workload": "wgrad of the same shape per rank (2 transposing quantizations + GEMM), dW summed over ranks",
                               "nccl_ms_per_step": times[0], "nccl_tflops": world * flops / (times[0] * 1e-3) / 1e12,
                               "fused_ms_per_step": times[1], "fused_tflops": world * flops / (times[1] * 1e-3) / 1e12,
@@ -969,44 +1215,154 @@ def main():
         except Exception as ex:
             reduce_scatter = {"error": str(ex)[:200]}
 
+    # ---- expert-parallel MoE (BASELINE config 4: 16384 tokens in all, 64 experts, top-4) beside the GEMM numbers ----
+    expert_parallel = None
+    if dist is not None and not strong and MOE_EXPERTS % world == 0 and args.workload == "mxfp8_square_8192":
+        try:
+            expert_parallel = expert_parallel_record(dist, rank, world, barrier, rank_max)
+        except Exception as ex:
+            expert_parallel = {"error": str(ex)[:300]}
+
+    secondary, incumbent = {}, None
+    if world == 1 and args.workload == "mxfp8_square_8192" and not args.headline_only:
+        secondary = secondary_kernels(ops, peaks, clocks)
+        incumbent = incumbent_scaled_mm(ops, ["mxfp8", "nvfp4", "fp8"], [(8192, 8192, 8192), (8192, 8192, 8192), (16384, 2048, 2048)])
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    peaks = measured_peaks()
-    # fp8 / fp4 tensor peak is not measured directly: the driver's measured bf16 cuBLAS rate,
-    # sustained (this kernel is timed inside a seconds-long loop), times the format's rate ratio
-    ratio = {"mxfp8": 2.0, "fp8": 2.0, "int8": 2.0, "nvfp4": 4.0}[kind]
-    peak = peaks["bf16_tflops_sustained"] * ratio
-    achieved = flops / (gemm_ms * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": f"gemm_pair_kernel<{kind}> / gemm_kernel<{kind}> (chosen by shape)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "peak_source": f"{ratio:g} x bf16_tflops_sustained, {peaks['source']}",
-                "frac_of_nominal": achieved / NOMINAL_TFLOPS[kind], "nominal_peak": NOMINAL_TFLOPS[kind],
-                "traffic": GEMM_DRAM_TRAFFIC.get(args.workload), "kernel_ms": gemm_ms}
+    # fp8 / fp4 tensor peak is not measured directly: the driver's measured bf16 cuBLAS rate times the format's rate
+    # ratio - the burst figure when the timed region is shorter than a second, the sustained one otherwise
+    roofline = roofline_tensor(f"gemm_pair_kernel<{kind}> / gemm_kernel<{kind}> (chosen by shape)", flops, gemm_ms, ratio, NOMINAL_TFLOPS[kind],
+                               co_region_s, clocks, peaks, traffic=GEMM_DRAM_TRAFFIC.get(args.workload))
     # the quantize kernels of the step against the measured HBM copy bandwidth (algorithmic bytes:
     # bf16 in, codes + scale bytes out; NVFP4 also reads each operand once more for its amax)
     bpe = {"mxfp8": 3.03125, "fp8": 3.0, "int8": 3.0, "nvfp4": 2.0 + 2.5625}[kind]
-    q_bytes = (m * k + n * k) * bpe
-    quantize = {"bound": "hbm", "achieved": q_bytes / (quant_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": q_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": f"hbm_gbs, {peaks['source']}",
-                "kernels_ms": quant_ms, "bytes": q_bytes}
-    line = {"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind,
-            "data": "synthetic", "config": config, "clocks": clk.summary(), "e2e": e2e, "gpu_launches": launches * args.steps,
-            "roofline": roofline, "quantize": quantize}
+    quantize = hbm_record((m_rank * k + n * k) * bpe, quant_ms, peaks, note="the step's quantize launches inside the loop")
+    config = dict(config, M_per_gpu=m_rank, scaling=args.scaling if world > 1 else "single GPU",
+                  step=("quantize A, quantize B, GEMM with the bf16 output all-gather in its epilogue, rendezvous" if gathered is not None
+                        else "quantize A, quantize B, GEMM"))
+    line = {"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": warm,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": kind,
+            "data": "synthetic", "config": config, "clocks": clocks, "timed_region_s": timed_region_s, "timed_blocks": len(block_ms),
+            "block_ms": {"median": median(block_ms), "min": min(block_ms), "max": max(block_ms)},
+            "e2e": e2e, "gpu_launches": launches * args.steps * len(block_ms), "roofline": roofline, "quantize": quantize}
+    if gathered is not None:
+        line["compute_only"] = {"ms_per_step": co_ms, "tflops": world * flops / (co_ms * 1e-3) / 1e12,
+                                "note": "the same step without the gather (N independent shards): what `value` was before the gather moved in"}
+    line.update(secondary)
+    if incumbent is not None:
+        line["incumbent"] = incumbent
     if graph is not None:
         line["cuda_graph"] = graph
     if allgather is not None:
         line["allgather"] = allgather
     if reduce_scatter is not None:
         line["reduce_scatter"] = reduce_scatter
+    if expert_parallel is not None:
+        line["expert_parallel"] = expert_parallel
     if world == 1 and not args.no_cpu_baseline:
         cb = run_cpu(kind, m, n, k, 2, 1)
         line["cpu_baseline"] = {k2: cb[k2] for k2 in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def expert_parallel_record(dist, rank, world, barrier, rank_max, total_tokens=16384, d=768, inter=384):
+    """BASELINE config 4 as written: 16384 tokens in total, tokens sharded over the ranks, 64 experts split E / N per GPU,
+    top-4; forward of the expert path.  Two forms: exchange by NCCL all-to-all, and by the kernels themselves over
+    peer-mapped memory.  FLOP = the two grouped GEMMs over all routed rows of the job."""
+    from oracle import restate as R
+    from pretrain_b200 import dist as D
+    e, k = MOE_EXPERTS, MOE_TOPK
+    t = total_tokens // world
+    x, logits, w_gu, w_d = R.inputs_moe(t, d, e, k, inter, seed=rank)
+    top_i, top_w = R.router_topk(logits, k)
+    x, top_i, top_w, w_gu, w_d = (v.cuda() for v in (x, top_i, top_w, w_gu, w_d))
+    el = e // world
+    w1l, w2l = w_gu[rank * el:(rank + 1) * el].contiguous(), w_d[rank * el:(rank + 1) * el].contiguous()
+    flops = 2.0 * total_tokens * k * (2 * inter * d + d * inter)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        barrier()
+        t0.record()
+        for _ in range(reps):
+            fn()
+        t1.record()
+        barrier()
+        return rank_max(t0.elapsed_time(t1) / reps)
+
+    rec = {"workload": f"{total_tokens} tokens in total ({t} per rank), hidden {d}, {e} experts ({el} per GPU), top-{k}, intermediate {inter}; forward"}
+    with torch.no_grad():
+        nccl_ms = timed(lambda: D.expert_parallel_moe(x, top_i, top_w, w1l, w2l, e))
+        rec.update(nccl_all_to_all_ms=nccl_ms, nccl_tflops=flops / (nccl_ms * 1e-3) / 1e12)
+        ep = D.FusedExpertParallel(t, k, d, e)
+        fused_ms = timed(lambda: ep.forward(x, top_i, top_w, w1l, w2l))
+        rec.update(fused_ms=fused_ms, fused_tflops=flops / (fused_ms * 1e-3) / 1e12,
+                   fused="dispatch = gather + MXFP8 kernel storing into the owners' buffers, combine = unpermute kernel loading from "
+                         "them (symmetric memory, NVLink)")
+    return rec
+
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
+    ap.add_argument("--workload", default="mxfp8_square_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N > 1: weak = every rank brings the workload's M rows; strong = the workload's M rows are split over the ranks")
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
+                    help="repeat the --steps-long block until this much device time has been timed; the median block is reported")
+    ap.add_argument("--headline-only", action="store_true", help="skip the secondary kernels and the incumbent timings of the default line")
+    args = ap.parse_args()
+    kind, m, n, k = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": args.workload, "kind": kind, "M_per_gpu": m, "N": n, "K": k,
+              "sharding": "rows of A (M) across ranks, B replicated" if world > 1 else "single GPU",
+              "l2": "operands, codes and output of a step total > 126 MB (larger than L2); no flush needed"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        torch.set_num_threads(len(os.sched_getaffinity(0)))     # torchrun pins OMP_NUM_THREADS=1
+        steps, warm = 1, 0
+        if kind in ("moe", "moe_train"):
+            cb = cpu_moe_sample(m, n, k)
+        elif kind in ("nvfp4_mlp", "fp8_triple", "mxfp8_triple"):
+            cb = cpu_composite_sample(kind, m, n, k)
+        else:
+            cb = run_cpu(kind, m, n, k, args.steps, args.warmup)      # --steps / --warmup honoured (time budget: see run_cpu)
+            steps, warm = cb["steps"], cb["warmup"]
+        print(json.dumps({"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOPS", "n_gpus": args.gpus,
+                          "steps": steps, "warmup": warm, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "bf16 matmul of fake-quantized operands (CPU)",
+                          "data": "synthetic", "config": config,
+                          "cpu_baseline": {k2: cb[k2] for k2 in ("value", "unit", "cores", "kind", "sample")},
+                          "e2e": {"value": cb["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path for the product arm")
+    torch.cuda.set_device(local)
+    if kind == "moe":
+        return run_moe(args, m, n, k, rank, world, local)
+    if kind == "moe_train":
+        return run_moe_training(args, m, n, k, rank, world, local)
+    if kind in ("nvfp4_mlp", "fp8_triple", "mxfp8_triple"):
+        return run_composite(args, kind, m, n, k, rank, world, local)
+    return run_dense(args, kind, m, n, k, rank, world, local, config)
 
 
 if __name__ == "__main__":
