@@ -432,6 +432,11 @@ int b200q_moe_pair_of_row(const int32_t* row_of, int64_t n_pairs, int64_t padded
  *   b200q_debug_set_gemm_pair(mode): 1 = CTA-pair kernel whenever the shape allows, -1 = never, 0 = by shape. */
 int b200q_debug_set_gemm_bn(int bn);
 int b200q_debug_set_gemm_pair(int mode);
+/* Runs a one-thread kernel whose bounded wait cannot succeed (an mbarrier nobody arrives on), with a limit of
+ * `iterations` polls (1 .. 100000, i.e. milliseconds): the kernel gives up, records a non-zero status and returns,
+ * exactly as the GEMM kernels' waits do after their ~1 s limit.  The next b200q_device_status() returns
+ * B200Q_ERR_DEVICE_TIMEOUT (and clears it).  For testing the failure-reporting path without a fault or a hang. */
+int b200q_debug_expire_wait(int iterations, void* stream);
 
 #ifdef __cplusplus
 }

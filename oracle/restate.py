@@ -31,6 +31,7 @@ FP8_MAX = {E4M3: 448.0, E5M2: 57344.0}
 EPS = 1e-12  # src/quant/fp8.py:6
 
 MX_BLOCK = 32
+MX_NAN_EXP = 128  # scale exponent of a block that holds a NaN: byte 0xFF, the E8M0 NaN
 NV_BLOCK = 16
 E2M1_MAX = 6.0
 NV_TENSOR_DIV = 2688.0  # 448 * 6
@@ -133,6 +134,9 @@ def mx_scale_exponent(amax: torch.Tensor, fp8_dtype: torch.dtype = E4M3) -> torc
     and fp8_max = 1.75 * 2**P (P = 8 for E4M3, 15 for E5M2):
     e = E - P + (m > 1.75), floored at -39 (1e-12 rounds up to 2**-39) and
     capped at 127.  Integer-only: no division, no log.
+
+    A NaN maximum (torch's amax propagates NaN, as in src/quant/fp8.py:26-29) gives
+    e = 128: the scale max(NaN / fp8_max, 1e-12) is NaN, which E8M0 stores as 0xFF.
     """
     p = 8 if fp8_dtype == E4M3 else 15
     bits = amax.float().contiguous().view(torch.int32)
@@ -140,7 +144,8 @@ def mx_scale_exponent(amax: torch.Tensor, fp8_dtype: torch.dtype = E4M3) -> torc
     mant = bits & 0x7FFFFF
     e = expf - 127 - p + (mant > 0x600000).to(torch.int32)
     # fp32 subnormals / zero have expf == 0 and land far below the floor anyway
-    return e.clamp(min=-39, max=127)
+    e = e.clamp(min=-39, max=127)
+    return torch.where(amax.float().isnan(), torch.full_like(e, MX_NAN_EXP), e)
 
 
 def mx_scale_exponent_by_division(amax: torch.Tensor, fp8_dtype: torch.dtype = E4M3):
@@ -158,7 +163,9 @@ def quantize_mxfp8(x: torch.Tensor, axis: int = -1, fp8_dtype: torch.dtype = E4M
     (for axis=0 the result is transposed, shape (cols, rows)); ``sf`` is the
     uint8 E8M0 byte e+127 per block, shape (outer, C/32), natural layout.
     codes = e4m3_rne(clamp(x * 2**-e, +-fp8_max)) — an exact scaling followed by
-    the same cast quantize_fp8 uses.
+    the same cast quantize_fp8 uses.  A block that holds a NaN follows quantize_fp8's
+    arithmetic literally: NaN maximum -> NaN scale (byte 0xFF) -> every code of the
+    block is NaN (0x7F).
     """
     assert x.dim() == 2
     xt = x.t() if axis in (0, -2) else x
@@ -169,9 +176,11 @@ def quantize_mxfp8(x: torch.Tensor, axis: int = -1, fp8_dtype: torch.dtype = E4M
     amax = xb.abs().amax(dim=-1)
     e = mx_scale_exponent(amax, fp8_dtype)
     inv = torch.ldexp(torch.ones_like(amax), -e)  # exact 2**-e
+    inv = torch.where(e == MX_NAN_EXP, torch.full_like(inv, float("nan")), inv)
     fp8_max = FP8_MAX[fp8_dtype]
-    codes = (xb * inv.unsqueeze(-1)).clamp(-fp8_max, fp8_max).to(fp8_dtype)
-    return codes.view(torch.uint8).view(outer, c), (e + 127).to(torch.uint8)
+    codes = (xb * inv.unsqueeze(-1)).clamp(-fp8_max, fp8_max).to(fp8_dtype).view(torch.uint8)
+    codes = torch.where((e == MX_NAN_EXP).unsqueeze(-1), torch.full_like(codes, 0x7F), codes)   # +NaN whatever the operands' signs
+    return codes.view(outer, c), (e + 127).to(torch.uint8)
 
 
 def dequantize_mxfp8(codes: torch.Tensor, sf: torch.Tensor, fp8_dtype: torch.dtype = E4M3):
@@ -189,8 +198,11 @@ def dequantize_mxfp8(codes: torch.Tensor, sf: torch.Tensor, fp8_dtype: torch.dty
 def e2m1_rne(v: np.ndarray) -> np.ndarray:
     """Round fp32 values (already clamped to [-6, 6]) to E2M1 codes 0..15:
     magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6}, ties to the even code, sign in bit 3
-    (-0 keeps its sign)."""
+    (-0 keeps its sign).  E2M1 has no NaN: a NaN becomes +6 (code 7), the saturating
+    conversion's answer."""
     v = np.asarray(v, dtype=np.float32)
+    nan = np.isnan(v)
+    v = np.where(nan, np.float32(6.0), v)
     a = np.abs(v)
     hi = np.searchsorted(_E2M1_VALUES, a, side="left").clip(0, 7)
     lo = (hi - 1).clip(0, 7)
@@ -221,6 +233,9 @@ def quantize_nvfp4(x: torch.Tensor, axis: int = -1, tensor_amax: torch.Tensor | 
       d_b  = max(amax_block / 6, 1e-12);  sq_b = e4m3_rne(min(d_b / s_t, 448))
       eff  = float(sq_b) * s_t;  codes = e2m1_rne(clamp(x.float() / eff, +-6)),
       all +0 when sq_b == 0.
+    A NaN anywhere makes the tensor maximum, hence s_t, hence every block scale byte
+    (0x7F, the E4M3 NaN) and every effective scale NaN: the whole tensor dequantizes to
+    NaN, as a per-tensor quantize_fp8 of it would (src/quant/fp8.py:26-31).
     Returns (packed, sf, s_t): ``packed`` uint8 (outer, C/2), element 2i in the low
     nibble; ``sf`` uint8 E4M3 bytes (outer, C/16); ``s_t`` a 0-dim fp32 tensor.
     """
@@ -235,6 +250,7 @@ def quantize_nvfp4(x: torch.Tensor, axis: int = -1, tensor_amax: torch.Tensor | 
     xb = xt.float().view(outer, c // NV_BLOCK, NV_BLOCK)
     d_b = (xb.abs().amax(dim=-1) / E2M1_MAX).clamp_min(EPS)
     sq = (d_b / s_t).clamp(max=448.0).to(E4M3)
+    sq = torch.where(sq.float().isnan(), torch.full_like(sq.view(torch.uint8), 0x7F).view(E4M3), sq)   # +NaN byte
     eff = sq.float() * s_t
     q = (xb / eff.unsqueeze(-1)).clamp(-E2M1_MAX, E2M1_MAX)
     q = torch.where((sq.float() == 0).unsqueeze(-1), torch.zeros_like(q), q)

@@ -104,17 +104,24 @@ __host__ __device__ inline bool aligned32(const void* p) { return (reinterpret_c
 
 // max(|a|, |b|) of two packed bf16 pairs in ONE instruction; the sign bits of the result are
 // unspecified (the xor of the operands' signs): chain freely, then clear them with abs_bf16x2.
-// Exact (comparisons only); a NaN operand loses against a number, as with fmaxf.
+// Exact (comparisons only).  A NaN operand wins (.NaN), as in torch's amax / max, which is what the
+// reference reduces with (src/quant/fp8.py:26-29): a NaN anywhere in a group reaches the group's scale.
 __device__ __forceinline__ uint32_t absmax_raw_bf16x2(uint32_t a, uint32_t b) {
   uint32_t r;
-  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  asm("max.NaN.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// fp32 maximum that returns NaN when either operand is NaN (fmaxf would drop it)
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
   return r;
 }
 __device__ __forceinline__ uint32_t abs_bf16x2(uint32_t m) { return m & 0x7fff7fffu; }
 // |bf16x2| max of two packed words, as packed non-negative bf16x2.
 __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t v) { return abs_bf16x2(absmax_raw_bf16x2(acc, v)); }
 // max magnitude over the two halves of a packed word -> float
-__device__ __forceinline__ float absmax_halves(uint32_t m) { return fmaxf(fabsf(bf16lo(m)), fabsf(bf16hi(m))); }
+__device__ __forceinline__ float absmax_halves(uint32_t m) { return fmax_nan(fabsf(bf16lo(m)), fabsf(bf16hi(m))); }
 // max over the 8 bf16 of a uint4 -> float
 __device__ __forceinline__ float absmax8(uint4 v) {
   return absmax_halves(absmax_raw_bf16x2(absmax_raw_bf16x2(v.x, v.y), absmax_raw_bf16x2(v.z, v.w)));
@@ -129,9 +136,11 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 // Packed bf16 pair (2^-e_lo, 2^-e_hi) for block exponents in [-39, 126], and the packed product.  Scaling a
 // bf16 value by a power of two is exact in bf16 unless the result falls below 2^-126, far under the
 // smallest fp8 subnormal, where it rounds to a (signed) zero code either way - so the packed multiply
-// gives the codes of the fp32 multiply at half the instructions.
+// gives the codes of the fp32 multiply at half the instructions.  kMxNanExp (a block that holds a NaN)
+// gives a NaN multiplier: every code of that block becomes NaN.
+__device__ __forceinline__ uint32_t mx_inv_scale_bf16(int e) { return e == kMxNanExp ? 0x7FC0u : (uint32_t)(127 - e) << 7; }
 __device__ __forceinline__ uint32_t mx_inv_scale_bf16x2(int e_lo, int e_hi) {
-  return ((uint32_t)(127 - e_lo) << 7) | ((uint32_t)(127 - e_hi) << 23);
+  return mx_inv_scale_bf16(e_lo) | (mx_inv_scale_bf16(e_hi) << 16);
 }
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   uint32_t r;

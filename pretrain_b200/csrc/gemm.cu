@@ -677,6 +677,36 @@ using namespace b200q;
 
 extern "C" {
 
+// Test hook: what every bounded wait of the kernels does when it runs out, on a wait that cannot succeed: one thread
+// waits on an mbarrier that nobody ever arrives on, with a limit of `iterations` polls (a few milliseconds at most);
+// when the limit is reached it records status 21 in the device status word and the kernel returns normally.  The host
+// then sees B200Q_ERR_DEVICE_TIMEOUT from b200q_device_status() and the context stays usable.
+}  // extern "C"
+namespace b200q { namespace {
+__global__ void expire_wait_kernel(int iterations) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x != 0) return;
+  const uint32_t b = ptx::smem_u32(&bar);
+  ptx::mbar_init(b, 1);
+  ptx::fence_barrier_init();
+  bool done = false;
+  for (int i = 0; i < iterations && !done; ++i) {
+    done = ptx::mbar_try_wait(b, 0);
+    if (!done) __nanosleep(64);
+  }
+  if (!done) atomicExch(&g_device_status, 21);
+}
+} }  // namespace b200q::{anonymous}
+extern "C" {
+int b200q_debug_expire_wait(int iterations, void* stream) {
+  if (iterations < 1 || iterations > 100000) return B200Q_ERR_INVALID_ARG;
+  int rc = require_sm100();
+  if (rc) return rc;
+  expire_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(iterations);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
 // Test hook: force the N tile width (128, 192 or 256; 0 restores the choice by shape).
 int b200q_debug_set_gemm_bn(int bn) {
   if (bn != 0 && bn != 128 && bn != 192 && bn != 256) return B200Q_ERR_INVALID_ARG;

@@ -279,7 +279,8 @@ __device__ __forceinline__ void epilogue_tile_glu(uint32_t taddr, bool rev, int 
   if (OUT == GLU_BF16) {
     float a = absmax_halves(hmax);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
-    if ((threadIdx.x & 31) == 0 && a > 0.f) atomicMax(reinterpret_cast<unsigned int*>(out.amax), f2u(a));   // a >= 0: uint order == float order
+    for (int o = 16; o > 0; o >>= 1) a = fmax_nan(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+    // a >= 0 or NaN: the unsigned order of the bits is the float order, with NaN above everything
+    if ((threadIdx.x & 31) == 0 && !(a <= 0.f)) atomicMax(reinterpret_cast<unsigned int*>(out.amax), f2u(a));
   }
 }

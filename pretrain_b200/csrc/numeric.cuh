@@ -27,6 +27,7 @@ enum Fp8Fmt : int { FMT_E4M3 = 0, FMT_E5M2 = 1, FMT_I8 = 2 };   // FMT_I8: the i
 
 constexpr float kEps = 1e-12f;            // src/quant/fp8.py:6
 constexpr int kMxFloorExp = -39;          // 2^-39 is the smallest power of two >= 1e-12
+constexpr int kMxNanExp = 128;            // block maximum is NaN: scale byte 128 + 127 = 0xFF, the E8M0 NaN
 constexpr float kE2M1Max = 6.0f;
 constexpr float kNvTensorDiv = 2688.0f;   // 448 * 6
 
@@ -186,14 +187,17 @@ B200Q_HD uint32_t cvt_codes_x4(float a, float b, float c, float d, int fmt, floa
 // ---- MXFP8 block scale -------------------------------------------------------------
 // Unbiased exponent e of the smallest power of two >= max(amax / qmax, 1e-12).
 // amax = m * 2^E, qmax = 1.75 * 2^P  =>  e = E - P + (m > 1.75), floored at -39.
+// A NaN maximum (some element of the block is NaN) gives kMxNanExp: the scale "max(NaN / qmax, 1e-12)" of the
+// reference's formula is NaN, which E8M0 stores as 0xFF, and every code of the block is NaN.
 B200Q_HD int mx_scale_exp(float amax, int fmt) {
   uint32_t u = f2u(amax) & 0x7FFFFFFFu;
+  if (u > 0x7F800000u) return kMxNanExp;
   int e = (int)(u >> 23) - 127 - (fmt == FMT_E4M3 ? 8 : 15) + ((u & 0x7FFFFFu) > 0x600000u ? 1 : 0);
   e = e < kMxFloorExp ? kMxFloorExp : e;
   return e > 127 ? 127 : e;
 }
-// exact 2^-e for e in [-39, 126]
-B200Q_HD float mx_inv_scale(int e) { return u2f((uint32_t)(127 - e) << 23); }
+// exact 2^-e for e in [-39, 126]; NaN for kMxNanExp
+B200Q_HD float mx_inv_scale(int e) { return e == kMxNanExp ? u2f(0x7FC00000u) : u2f((uint32_t)(127 - e) << 23); }
 
 // ---- NVFP4 two-level scale -----------------------------------------------------------
 B200Q_HD float nv_tensor_scale(float amax_tensor) {

@@ -34,7 +34,7 @@ constexpr int kWarps = kThreads / 32;
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  for (int o = 16; o > 0; o >>= 1) v = fmax_nan(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));   // a NaN reaches every lane
   return v;
 }
 
@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const uint16_t* __restri
   __syncthreads();
   if (warp == 0) {
     a = warp_max(lane < kWarps ? s[lane] : 0.f);
-    if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), f2u(a));   // a >= 0: uint order == float order
+    // a >= 0 or NaN: the unsigned order of the bits is the float order, with NaN above everything
+    if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), f2u(a));
   }
 }
 
@@ -115,7 +116,7 @@ rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t
       uint8_t sq2[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const float a = fmaxf(absmax8(v[2 * h]), absmax8(v[2 * h + 1]));
+        const float a = fmax_nan(absmax8(v[2 * h]), absmax8(v[2 * h + 1]));
         const uint8_t sq = nv_block_scale_fast(a, s_t, rcp_st);
         const float eff = mul_rn(e4m3_to_float(sq), s_t);
         const float rcp = rcp_rn(eff);
@@ -195,7 +196,7 @@ rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, i
     if (wpr > 1) {
       if (lane == 0) smax[it & 1][warp] = amax;
       __syncthreads();
-      for (int j = 0; j < wpr; ++j) amax = fmaxf(amax, smax[it & 1][grp * wpr + j]);
+      for (int j = 0; j < wpr; ++j) amax = fmax_nan(amax, smax[it & 1][grp * wpr + j]);
     }
     if (tensor_amax) amax = *tensor_amax;
     const float scale = scale_from_amax(amax, fmt, qmax);
@@ -369,7 +370,7 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
   if (MODE == MODE_MX) {
     float a = 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) a = fmaxf(a, fabsf(f[i]));
+    for (int i = 0; i < 32; ++i) a = fmax_nan(a, fabsf(f[i]));
     const int e = mx_scale_exp(a, fmt);
     const float inv = mx_inv_scale(e);
     uint32_t o[8];
@@ -385,7 +386,7 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
     for (int h = 0; h < 2; ++h) {
       float a = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) a = fmaxf(a, fabsf(f[16 * h + i]));
+      for (int i = 0; i < 16; ++i) a = fmax_nan(a, fabsf(f[16 * h + i]));
       const uint8_t sq = nv_block_scale_fast(a, s_t, rcp_st);
       const float eff = mul_rn(e4m3_to_float(sq), s_t);
       const float rcp = rcp_rn(eff);

@@ -77,6 +77,18 @@ def main(ref_root: str) -> None:
                 out[f"q_{name}_{dname}_{dimname}_scale"] = scale.reshape(-1).numpy()
         out[f"fq_{name}_e4m3_row"] = _bf16_bits(fake_quantize_fp8(t, e4, dim=-1))
 
+    # NaN inputs: the reference's amax propagates a NaN into the scale of its group (row / column / tensor), and with
+    # it into every code of the group (src/quant/fp8.py:26-31).  Two NaNs, in different rows and columns.
+    nan_in = torch.randn(16, 64, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    nan_in[3, 5] = float("nan")
+    nan_in[9, 40] = float("nan")
+    out["in_nan"] = _bf16_bits(nan_in)
+    for dname, dt in (("e4m3", e4), ("e5m2", e5)):
+        for dimname, dim in (("tensor", None), ("row", -1), ("col", 0)):
+            codes, scale = quantize_fp8(nan_in, dt, dim)
+            out[f"q_nan_{dname}_{dimname}_codes"] = _u8(codes)
+            out[f"q_nan_{dname}_{dimname}_scale"] = scale.reshape(-1).numpy()
+
     # The reference's CPU form of its rowwise FP8 GEMM (src/quant/linear.py:52-56).
     out["gemm_rowwise_e4m3"] = _bf16_bits(
         fake_quantize_fp8(a, e4, dim=-1) @ fake_quantize_fp8(b, e4, dim=0)

@@ -27,6 +27,53 @@ def test_quantize_fp8_matches_reference_vectors(golden, name, dname, dt, dimname
                           golden[f"q_{name}_{dname}_{dimname}_scale"].view(np.uint32))
 
 
+def _same_up_to_nan_sign(codes_u8, gold_u8, fp8_dtype):
+    """Equal bytes, except that where the reference's code is a NaN ours must be a NaN too (its sign and payload
+    depend on which torch kernel reduced the maximum: 0x7F from the row reduction, 0xFF from the column one)."""
+    got = torch.from_numpy(np.ascontiguousarray(codes_u8)).view(fp8_dtype).float()
+    ref = torch.from_numpy(np.ascontiguousarray(gold_u8)).view(fp8_dtype).float()
+    nan = ref.isnan()
+    return bool(torch.equal(got.isnan(), nan)) and np.array_equal(codes_u8[~nan.numpy()], gold_u8[~nan.numpy()])
+
+
+@pytest.mark.parametrize("dname,dt", [("e4m3", E4), ("e5m2", E5)])
+@pytest.mark.parametrize("dimname,dim", [("tensor", None), ("row", -1), ("col", 0)])
+def test_quantize_fp8_nan_inputs_match_reference_vectors(golden, dname, dt, dimname, dim):
+    """The reference's amax carries a NaN into the scale of its row / column / tensor and from there into every code of
+    that group (src/quant/fp8.py:26-31); groups without a NaN are untouched."""
+    x = bf16_from_bits(golden["in_nan"])
+    codes, scale = R.quantize_fp8(x, dt, dim)
+    gold_scale = golden[f"q_nan_{dname}_{dimname}_scale"]
+    assert _same_up_to_nan_sign(codes.view(torch.uint8).numpy(), golden[f"q_nan_{dname}_{dimname}_codes"], dt)
+    got = scale.reshape(-1).numpy()
+    assert np.array_equal(np.isnan(got), np.isnan(gold_scale))
+    assert np.array_equal(got[~np.isnan(got)].view(np.uint32), gold_scale[~np.isnan(gold_scale)].view(np.uint32))
+    n_groups = {"tensor": 1, "row": 2, "col": 2}[dimname]
+    assert int(np.isnan(gold_scale).sum()) == n_groups
+
+
+def test_block_scaled_nan_rule():
+    """MXFP8 / NVFP4 follow the same arithmetic at their own granularity: a block with a NaN gets the NaN scale byte
+    (E8M0 0xFF) and NaN codes; an NVFP4 tensor with a NaN gets a NaN tensor scale, so every block scale byte is the
+    E4M3 NaN (0x7F) and the whole tensor dequantizes to NaN."""
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(8, 128, generator=g).bfloat16()
+    clean_codes, clean_sf = R.quantize_mxfp8(x)
+    x[2, 70] = float("nan")
+    for dt in (E4, E5):
+        cc, cs = R.quantize_mxfp8(x.nan_to_num(0.0), -1, dt)
+        codes, sf = R.quantize_mxfp8(x, -1, dt)
+        hit = torch.zeros(8, 4, dtype=torch.bool); hit[2, 2] = True
+        assert torch.equal(sf[hit], torch.tensor([255], dtype=torch.uint8)) and torch.equal(sf[~hit], cs[~hit])
+        assert (codes[2, 64:96] == 0x7F).all()
+        keep = torch.ones(8, 128, dtype=torch.bool); keep[2, 64:96] = False
+        assert torch.equal(codes[keep], cc[keep])
+        assert R.dequantize_mxfp8(codes, sf, dt)[2, 64:96].isnan().all()
+    p, sq, s_t = R.quantize_nvfp4(x)
+    assert s_t.isnan() and (sq == 0x7F).all() and (p == 0x77).all()
+    assert R.dequantize_nvfp4(p, sq, s_t).isnan().all()
+
+
 def test_fake_quant_and_gemm_forms_match_reference_vectors(golden):
     a, b, g = (bf16_from_bits(golden[f"in_{n}"]) for n in ("a", "b", "grad"))
     fq = R.fake_quantize_fp8(a, E4, dim=-1)

@@ -272,6 +272,47 @@ def test_rows_that_are_only_16_byte_aligned(ops):
     assert torch.equal(packed.cpu(), rp) and torch.equal(sf.cpu(), rs.reshape(-1)) and ts.item() == rt.item()
 
 
+def test_baseline_config_1_operands_bit_exact_at_full_size(ops):
+    """MXFP8 linear of the GPT-2 MLP up-projection: X [8192, 768], W [3072, 768], seed 0, both along K - every code and
+    every scale byte against the CPU oracle, row-wise, transposing and both-directions kernels."""
+    x, w = R.inputs_mxfp8_linear()
+    assert x.shape == (8192, 768) and w.shape == (3072, 768)
+    for t in (x, w):
+        tc = t.cuda()
+        rc, rs = R.quantize_mxfp8(t, -1, E4)
+        codes, sf = ops.quantize_mxfp8(tc, 1, E4, 0)
+        assert torch.equal(codes.cpu(), rc) and torch.equal(sf.cpu().view(rs.shape), rs)
+        codes, sf = ops.quantize_mxfp8(tc, 1, E4, 1)
+        assert torch.equal(codes.cpu(), rc) and torch.equal(sf.cpu(), R.swizzle_sf(rs))
+        r0, s0 = R.quantize_mxfp8(t, 0, E4)
+        codes, sf = ops.quantize_mxfp8(tc, 0, E4, 0)
+        assert torch.equal(codes.cpu(), r0) and torch.equal(sf.cpu().view(s0.shape), s0)
+        cr, sr, cc, sc = ops.quantize_mxfp8_dual(tc, E4, 1)
+        assert torch.equal(cr.cpu(), rc) and torch.equal(cc.cpu(), r0)
+        assert torch.equal(sr.cpu(), R.swizzle_sf(rs)) and torch.equal(sc.cpu(), R.swizzle_sf(s0))
+
+
+def test_baseline_config_2_operands_bit_exact_at_full_size(ops):
+    """NVFP4 SwiGLU MLP: X [16384, 1024] with 0.1 % outliers x 50, gate/up W [6144, 1024], down W [1024, 3072] - packed
+    codes, E4M3 block scales and the fp32 tensor scale against the CPU oracle; then an operand of the hidden activation's
+    shape [16384, 3072] with per-row magnitudes, quantized along 3072 as the second GEMM needs it."""
+    x, w_gu, w_d = R.inputs_nvfp4_mlp()
+    assert x.shape == (16384, 1024) and w_gu.shape == (6144, 1024) and w_d.shape == (1024, 3072)
+    for t in (x, w_gu, w_d):
+        rp, rs, rt = R.quantize_nvfp4(t, -1)
+        p, sf, ts = ops.quantize_nvfp4(t.cuda(), 1, None, 0)
+        assert ts.item() == rt.item()
+        assert torch.equal(p.cpu(), rp) and torch.equal(sf.cpu().view(rs.shape), rs)
+        p, sf, ts = ops.quantize_nvfp4(t.cuda(), 1, None, 1)
+        assert torch.equal(p.cpu(), rp) and torch.equal(sf.cpu(), R.swizzle_sf(rs))
+    assert x.abs().max().item() > 100 and (rs.view(E4).float() > 0).all()          # the outliers reach the tensor scale
+    g = torch.Generator().manual_seed(2)
+    h = (torch.randn(16384, 3072, generator=g) * torch.rand(16384, 1, generator=g)).bfloat16()     # an activation-shaped operand
+    rp, rs, rt = R.quantize_nvfp4(h, -1)
+    p, sf, ts = ops.quantize_nvfp4(h.cuda(), 1, None, 0)
+    assert ts.item() == rt.item() and torch.equal(p.cpu(), rp) and torch.equal(sf.cpu().view(rs.shape), rs)
+
+
 def test_full_size_properties(ops):
     """Benchmark-size square operand (8192 x 8192): properties that need no CPU pass over the
     data — never clips, scale is tight, transposing kernel == row-wise kernel on the transpose."""
@@ -294,27 +335,70 @@ def test_full_size_properties(ops):
     assert torch.equal(c1, c2) and torch.equal(sc1, sc2)
 
 
-def test_a_nan_stays_where_it_is(ops):
-    """Non-finite inputs are outside the reference's tests; what the kernels do with them is pinned here: a NaN
-    becomes a NaN code in place and takes part in no maximum, so every other code and every scale are those of the
-    same tensor with the NaN replaced by zero."""
+def _nan_pattern_equal(codes_u8, gold_u8, fp8_dtype):
+    """Equal bytes outside the reference's NaN codes, NaN exactly where it has NaN (the sign / payload of a NaN code
+    depends on which torch reduction produced the scale: 0x7F by rows, 0xFF by columns)."""
+    got, ref = torch.from_numpy(codes_u8).view(fp8_dtype).float(), torch.from_numpy(np.ascontiguousarray(gold_u8)).view(fp8_dtype).float()
+    nan = ref.isnan()
+    return bool(torch.equal(got.isnan(), nan)) and np.array_equal(codes_u8[~nan.numpy()], np.ascontiguousarray(gold_u8)[~nan.numpy()])
+
+
+def _scales_equal_with_nans(got, gold):
+    return np.array_equal(np.isnan(got), np.isnan(gold)) and np.array_equal(got[~np.isnan(got)].view(np.uint32), gold[~np.isnan(gold)].view(np.uint32))
+
+
+@pytest.mark.parametrize("dname,dt", [("e4m3", E4), ("e5m2", E5)])
+def test_nan_inputs_reproduce_the_reference(ops, golden, dname, dt):
+    """src/quant/fp8.py:26-31 on a tensor with two NaNs, run by the reference itself (tests/golden/make_golden.py): the
+    NaN reaches the scale of its row / column / tensor and every code of that group; all other groups are untouched."""
+    x = bf16_from_bits(golden["in_nan"]).cuda()
+    codes, scales = ops.quantize_fp8(x, dt, 1)
+    assert _nan_pattern_equal(codes.cpu().numpy(), golden[f"q_nan_{dname}_row_codes"], dt)
+    assert _scales_equal_with_nans(scales.cpu().numpy(), golden[f"q_nan_{dname}_row_scale"])
+    codes, scales = ops.quantize_fp8(x, dt, 0)
+    assert _nan_pattern_equal(codes.cpu().numpy(), golden[f"q_nan_{dname}_col_codes"].T, dt)
+    assert _scales_equal_with_nans(scales.cpu().numpy(), golden[f"q_nan_{dname}_col_scale"])
+    for transpose in (False, True):
+        codes, scale = ops.quantize_fp8_tensorwise(x, dt, transpose)
+        gold = golden[f"q_nan_{dname}_tensor_codes"]
+        assert _nan_pattern_equal(codes.cpu().numpy(), gold.T if transpose else gold, dt)
+        assert np.isnan(scale.cpu().numpy()).all()
+    cr, sr, cc, sc = ops.quantize_fp8_both(x, dt)
+    assert _nan_pattern_equal(cr.cpu().numpy(), golden[f"q_nan_{dname}_row_codes"], dt)
+    assert _nan_pattern_equal(cc.cpu().numpy(), golden[f"q_nan_{dname}_col_codes"].T, dt)
+    assert _scales_equal_with_nans(sr.cpu().numpy(), golden[f"q_nan_{dname}_row_scale"])
+    assert _scales_equal_with_nans(sc.cpu().numpy(), golden[f"q_nan_{dname}_col_scale"])
+
+
+def test_block_scaled_quantizers_follow_the_same_nan_rule(ops):
+    """MXFP8 / NVFP4 against the oracle on inputs with NaNs, every kernel form: the block (MXFP8) or the tensor
+    (NVFP4) that holds a NaN gets the NaN scale and NaN codes, bit for bit as the oracle states it."""
     g = torch.Generator().manual_seed(17)
-    x = torch.randn(64, 256, generator=g).bfloat16()
-    clean = x.clone()
+    x = torch.randn(128, 256, generator=g).bfloat16()
     x[3, 5] = float("nan")
-    clean[3, 5] = 0.0
-    is_nan = lambda codes, dt: codes.view(dt).float().isnan()
+    x[77, 200] = float("nan")
+    xc = x.cuda()
     for dt in (E4, E5):
-        for fn in (lambda t: ops.quantize_fp8(t, dt, 1), lambda t: ops.quantize_mxfp8(t, 1, dt, 0)):
-            codes, scales = fn(x.cuda())
-            want, want_scales = fn(clean.cuda())
-            assert is_nan(codes[3, 5].cpu(), dt)
-            codes = codes.clone()
-            codes[3, 5] = want[3, 5]
-            assert torch.equal(codes, want) and torch.equal(scales.view(torch.uint8), want_scales.view(torch.uint8))
-        cr, sr, cc, sc = ops.quantize_mxfp8_dual(x.cuda(), dt, 0)
-        wr, wsr, wc, wsc = ops.quantize_mxfp8_dual(clean.cuda(), dt, 0)
-        assert is_nan(cr[3, 5].cpu(), dt) and is_nan(cc[5, 3].cpu(), dt)
-        cr, cc = cr.clone(), cc.clone()
-        cr[3, 5], cc[5, 3] = wr[3, 5], wc[5, 3]
-        assert torch.equal(cr, wr) and torch.equal(cc, wc) and torch.equal(sr, wsr) and torch.equal(sc, wsc)
+        for axis in (1, 0):
+            codes, sf = ops.quantize_mxfp8(xc, axis, dt, 0)
+            rc, rs = R.quantize_mxfp8(x, -1 if axis == 1 else 0, dt)
+            assert torch.equal(codes.cpu(), rc) and torch.equal(sf.cpu().view(rs.shape), rs)
+            assert int((rs == 255).sum()) == 2
+        cr, sr, cc, sc = ops.quantize_mxfp8_dual(xc, dt, 0)
+        r1, s1 = R.quantize_mxfp8(x, -1, dt)
+        r0, s0 = R.quantize_mxfp8(x, 0, dt)
+        assert torch.equal(cr.cpu(), r1) and torch.equal(cc.cpu(), r0)
+        assert torch.equal(sr.cpu().view(s1.shape), s1) and torch.equal(sc.cpu().view(s0.shape), s0)
+    for axis in (1, 0):
+        p, sq, ts = ops.quantize_nvfp4(xc, axis, None, 0)
+        rp, rsq, rt = R.quantize_nvfp4(x, -1 if axis == 1 else 0)
+        assert ts.isnan().all() and rt.isnan()
+        assert torch.equal(p.cpu(), rp) and torch.equal(sq.cpu().view(rsq.shape), rsq)
+    assert ops.amax(xc).isnan().all()
+    # a GEMM over such operands gives NaN exactly in the output rows / columns the NaN blocks feed
+    ca, sfa = ops.quantize_mxfp8(xc, 1)
+    w = torch.randn(128, 256, generator=g).bfloat16().cuda()
+    cb, sfb = ops.quantize_mxfp8(w, 1)
+    out = ops.gemm_mxfp8(ca, sfa, cb, sfb).float().cpu()
+    bad = out.isnan().any(1)
+    assert bad[3] and bad[77] and int(bad.sum()) == 2
