@@ -715,7 +715,7 @@ def run_composite(args, kind, d0, d1, d2, rank, world, local):
             def ref_gemm(a_, b_, adt, bdt):                      # a_ (M, C), b_ (C, N)
                 qa, sa_ = q_ref(a_, adt, -1)
                 qb, sb_ = q_ref(b_, bdt, 0)
-                return torch._scaled_mm(qa, qb.t().contiguous().t(), scale_a=sa_, scale_b=sb_, out_dtype=torch.bfloat16)
+                return torch._scaled_mm(qa.contiguous(), qb.t().contiguous().t(), scale_a=sa_, scale_b=sb_, out_dtype=torch.bfloat16)
 
             def ref_step():
                 ref_gemm(x, w.t(), E4, E4)
@@ -1007,43 +1007,36 @@ def run_dense(args, kind, m, n, k, rank, world, local, config):
     if dist is not None and kind != "int8":
         from pretrain_b200 import dist as D
         gathered = D.GatheredOutput(m_rank, n)
-        step = lambda marks=None: D.sharded_gemm_fused(a, b, fmt, gathered)      # the product call: quantize x 2, GEMM + gather, rendezvous
+        step = lambda: D.sharded_gemm_fused(a, b, fmt, gathered)      # the product call: quantize x 2, GEMM + gather, rendezvous
+    elif kind == "mxfp8":
+        step = lambda: ops.linear_mxfp8(a, 1, b, 1, out=out)          # what `_gemm(a, b, "mxfp8", "mxfp8")` runs: one library call
     else:
         step = compute_step
 
-    # ---- headline: blocks of --steps steps until MIN_TIMED_SECONDS of device time -------------
+    # ---- headline: blocks of --steps steps until --min-seconds of device time -------------------
     for _ in range(warm):
         step()
     barrier()
-    marks = []
     with ClockSampler(local) as clk:
-        block_ms = timed_blocks(lambda: [step(marks) for _ in range(args.steps)], args.min_seconds, barrier, dist)
+        block_ms = timed_blocks(lambda: [step() for _ in range(args.steps)], args.min_seconds, barrier, dist)
     ops.device_status()
     clocks = clk.summary()
     timed_region_s = sum(block_ms) * 1e-3
     ms_step = median(block_ms) / args.steps
     value = world * flops / (ms_step * 1e-3) / 1e12
 
-    # ---- the compute-only step (no gather), with its quantize / GEMM split from events ---------
-    if step is compute_step:
-        trip = [marks[i:i + 3] for i in range(0, len(marks), 3)]
-        co_ms = ms_step
-        co_region_s = timed_region_s
-    else:
-        marks = []
-        for _ in range(3):
-            compute_step()
-        barrier()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n_co = max(args.steps, 20)
-        t0.record()
-        for _ in range(n_co):
-            compute_step(marks)
-        t1.record()
-        barrier()
-        co_ms = rank_max(t0.elapsed_time(t1) / n_co)
-        co_region_s = co_ms * n_co * 1e-3
-        trip = [marks[i:i + 3] for i in range(0, len(marks), 3)]
+    # ---- the same work as separate launches with CUDA events between them: the quantize / GEMM split, and (N > 1) the
+    # step without the gather.  Runs as long as the headline loop, so the GEMM's rate is a sustained one like the headline's. ----
+    marks = []
+    for _ in range(3):
+        compute_step()
+    barrier()
+    with ClockSampler(local) as clk_split:
+        split_ms = timed_blocks(lambda: [compute_step(marks) for _ in range(args.steps)], args.min_seconds, barrier, dist)
+    co_ms = median(split_ms) / args.steps
+    co_region_s = sum(split_ms) * 1e-3
+    split_clocks = clk_split.summary()
+    trip = [marks[i:i + 3] for i in range(0, len(marks), 3)]
     quant_ms = sum(q.elapsed_time(g0) for q, g0, _ in trip) / len(trip)
     gemm_ms = sum(g0.elapsed_time(g1) for _, g0, g1 in trip) / len(trip)
     gemm_ms, quant_ms = rank_max(gemm_ms, quant_ms)
@@ -1236,22 +1229,26 @@ def run_dense(args, kind, m, n, k, rank, world, local, config):
     # fp8 / fp4 tensor peak is not measured directly: the driver's measured bf16 cuBLAS rate times the format's rate
     # ratio - the burst figure when the timed region is shorter than a second, the sustained one otherwise
     roofline = roofline_tensor(f"gemm_pair_kernel<{kind}> / gemm_kernel<{kind}> (chosen by shape)", flops, gemm_ms, ratio, NOMINAL_TFLOPS[kind],
-                               co_region_s, clocks, peaks, traffic=GEMM_DRAM_TRAFFIC.get(args.workload))
+                               co_region_s, split_clocks, peaks, traffic=GEMM_DRAM_TRAFFIC.get(args.workload),
+                               timed="CUDA events around the GEMM launch of every step of the separate-launch loop")
     # the quantize kernels of the step against the measured HBM copy bandwidth (algorithmic bytes:
     # bf16 in, codes + scale bytes out; NVFP4 also reads each operand once more for its amax)
     bpe = {"mxfp8": 3.03125, "fp8": 3.0, "int8": 3.0, "nvfp4": 2.0 + 2.5625}[kind]
-    quantize = hbm_record((m_rank * k + n * k) * bpe, quant_ms, peaks, note="the step's quantize launches inside the loop")
+    quantize = hbm_record((m_rank * k + n * k) * bpe, quant_ms, peaks, note="the quantize launches of every step of the separate-launch loop")
     config = dict(config, M_per_gpu=m_rank, scaling=args.scaling if world > 1 else "single GPU",
                   step=("quantize A, quantize B, GEMM with the bf16 output all-gather in its epilogue, rendezvous" if gathered is not None
-                        else "quantize A, quantize B, GEMM"))
+                        else ("one b200q_linear_mxfp8 call: A and B quantized by one launch, GEMM launched behind it (programmatic dependent launch)"
+                              if kind == "mxfp8" else "quantize A, quantize B, GEMM")))
     line = {"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": kind,
             "data": "synthetic", "config": config, "clocks": clocks, "timed_region_s": timed_region_s, "timed_blocks": len(block_ms),
             "block_ms": {"median": median(block_ms), "min": min(block_ms), "max": max(block_ms)},
-            "e2e": e2e, "gpu_launches": launches * args.steps * len(block_ms), "roofline": roofline, "quantize": quantize}
+            "e2e": e2e, "gpu_launches": (launches - (1 if kind == "mxfp8" and gathered is None else 0)) * args.steps * len(block_ms), "roofline": roofline, "quantize": quantize}
+    line["separate_launches"] = {"ms_per_step": co_ms, "tflops": world * flops / (co_ms * 1e-3) / 1e12, "timed_region_s": co_region_s,
+                                 "note": "quantize A, quantize B, GEMM as three library calls with CUDA events between them" +
+                                         (" and no gather (N independent shards): the compute-only step" if gathered is not None else "")}
     if gathered is not None:
-        line["compute_only"] = {"ms_per_step": co_ms, "tflops": world * flops / (co_ms * 1e-3) / 1e12,
-                                "note": "the same step without the gather (N independent shards): what `value` was before the gather moved in"}
+        line["compute_only"] = line["separate_launches"]
     line.update(secondary)
     if incumbent is not None:
         line["incumbent"] = incumbent

@@ -152,6 +152,19 @@ int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, i
                      const void* sfB, int64_t M, int64_t N, int64_t K, void* D, int64_t ldd,
                      void* stream);
 
+/* `_gemm(a, b, "mxfp8", "mxfp8", ...)` of src/quant/linear.py:27-56 in ONE call: both bf16 operands quantized to MXFP8
+ * along the contraction dimension and multiplied, D (bf16 [M, N], pitch ldd) = A . B^T.  Each operand is given as it
+ * lies in memory with the axis its blocks run along, exactly as for b200q_quantize_mxfp8: axis = 1 - a [M, K] (or
+ * b [N, K]) with K contiguous; axis = 0 - the operand stored [K, M] (or [K, N]), quantized by the transposing
+ * kernel.  When both have K contiguous and the same format, ONE launch quantizes the two; the GEMM is launched
+ * behind it with programmatic stream serialization, so its set-up overlaps the quantizer's tail.  Results are
+ * bit-identical to b200q_quantize_mxfp8 x 2 + b200q_gemm_mxfp8.  `workspace` (256-byte aligned) holds
+ * b200q_linear_mxfp8_workspace_bytes(M, N, K) bytes: the codes and scale factors, which are left there. */
+int64_t b200q_linear_mxfp8_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int b200q_linear_mxfp8(const void* a, int64_t a_rows, int64_t a_cols, int64_t lda, int a_axis, int a_fmt,
+                       const void* b, int64_t b_rows, int64_t b_cols, int64_t ldb, int b_axis, int b_fmt,
+                       void* D, int64_t ldd, void* workspace, void* stream);
+
 /* Block-scaled NVFP4 GEMM; D is multiplied by (*tsA) * (*tsB) (device fp32).  K % 32 == 0;
  * A and B hold K/2 bytes per row. */
 int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* sfB,

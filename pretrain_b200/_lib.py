@@ -31,6 +31,8 @@ SIGNATURES = {
     "b200q_gemm_int8": (_int, [_vp, _vp, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_fp8": (_int, [_vp, _int, _vp, _int, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_mxfp8": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "b200q_linear_mxfp8_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "b200q_linear_mxfp8": (_int, [_vp, _i64, _i64, _i64, _int, _int, _vp, _i64, _i64, _i64, _int, _int, _vp, _i64, _vp, _vp]),
     "b200q_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b200q_gemm_fp8_allgather": (_int, [_vp, _int, _vp, _int, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),
     "b200q_gemm_mxfp8_allgather": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _int, _int, _i64, _vp]),

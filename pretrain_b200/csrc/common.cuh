@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/b200q.h"
 #include "numeric.cuh"
@@ -67,6 +68,38 @@ inline int blocks_per_sm(Kernel kernel, int threads, int fallback) {
     f->value = (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) == cudaSuccess && per_sm >= 1) ? per_sm : fallback;
   }
   return f->value;
+}
+
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while the kernel before it
+// in the stream is still running, once every CTA of that kernel has executed grid_launch_dependents() (or exited);
+// everything the later kernel does before grid_dependency_wait() - CTA set-up, barrier initialisation, tensor-memory
+// allocation, descriptor prefetch - then overlaps the earlier kernel's tail.  grid_dependency_wait() returns once the
+// earlier kernel has completed and its memory operations are visible; without the launch attribute it returns at once.
+// Only kernels whose whole grid is resident at once call grid_launch_dependents() at their start (so that a waiting
+// successor can never hold resources a not-yet-started CTA of theirs needs).
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with (or without) the programmatic-serialization attribute.  B200Q_PDL=0 in the environment turns it off.
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200Q_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {

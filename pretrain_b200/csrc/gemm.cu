@@ -191,6 +191,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Grouped forms read the permute plan's tables right away: wait for the kernels before this one first.  The dense
+  // forms read nothing of theirs until the roles start, so their set-up below overlaps the previous kernel's tail.
+  const bool reads_plan = p.num_tiles != nullptr || p.ragged_offs != nullptr;
+  if (reads_plan) grid_dependency_wait();
   int num_m = p.num_m;
   if (p.num_tiles != nullptr) {
     const int live = __ldg(p.num_tiles);
@@ -224,6 +228,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (!reads_plan) grid_dependency_wait();      // operands, scales and the output buffer belong to earlier kernels until here
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------------------
@@ -496,8 +501,7 @@ int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t 
   B200Q_CUDA(ensure_dynamic_smem(gemm_kernel<KIND, BN, EPI>, C::SMEM_BYTES));
   const int64_t tiles = (int64_t)p.num_m * p.num_n * (p.ragged_offs != nullptr ? p.n_experts : 1);
   const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
-  gemm_kernel<KIND, BN, EPI><<<grid, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, md, p);
-  B200Q_CUDA(cudaGetLastError());
+  B200Q_CUDA(launch_pdl(gemm_kernel<KIND, BN, EPI>, dim3(grid), dim3(gemm_threads(EPI)), C::SMEM_BYTES, st, ma, mb, md, p));
   return B200Q_OK;
 }
 
@@ -747,6 +751,57 @@ int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, i
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   p.M = M; p.N = N; p.K = K;
   return dispatch<KIND_MX>(A, B, one_output(D), ldd, N, p, (cudaStream_t)stream);
+}
+
+// ---- the `_gemm` seam for MXFP8 in one call ---------------------------------------------------------------------
+static inline int64_t align256(int64_t v) { return (v + 255) & ~(int64_t)255; }
+
+int64_t b200q_linear_mxfp8_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return align256(M * K) + align256(b200q_sf_bytes(M, K / 32, B200Q_SF_SWIZZLE_128x4)) + align256(N * K) +
+         align256(b200q_sf_bytes(N, K / 32, B200Q_SF_SWIZZLE_128x4));
+}
+
+int b200q_linear_mxfp8(const void* a, int64_t a_rows, int64_t a_cols, int64_t lda, int a_axis, int a_fmt, const void* b,
+                       int64_t b_rows, int64_t b_cols, int64_t ldb, int b_axis, int b_fmt, void* D, int64_t ldd, void* workspace,
+                       void* stream) {
+  int rc = check_matrix(a, a_rows, a_cols, lda);
+  if (rc) return rc;
+  if ((rc = check_matrix(b, b_rows, b_cols, ldb))) return rc;
+  if (D == nullptr || workspace == nullptr || (a_axis != 0 && a_axis != 1) || (b_axis != 0 && b_axis != 1) || ((a_fmt | b_fmt) & ~1))
+    return B200Q_ERR_INVALID_ARG;
+  const int64_t M = a_axis == 1 ? a_rows : a_cols, K = a_axis == 1 ? a_cols : a_rows;
+  const int64_t N = b_axis == 1 ? b_rows : b_cols, Kb = b_axis == 1 ? b_cols : b_rows;
+  if (K != Kb || ldd < N) return B200Q_ERR_INVALID_ARG;
+  if ((K & 31) || (N & 7) || (ldd & 7)) return B200Q_ERR_SHAPE;
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B200Q_ERR_SHAPE;
+  if (!aligned16(D) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return B200Q_ERR_ALIGNMENT;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int swz = B200Q_SF_SWIZZLE_128x4;
+  uint8_t* ca = static_cast<uint8_t*>(workspace);
+  uint8_t* sfa = ca + align256(M * K);
+  uint8_t* cb = sfa + align256(b200q_sf_bytes(M, K / 32, swz));
+  uint8_t* sfb = cb + align256(N * K);
+  if ((rc = zero_sf_pads(sfa, M, K / 32, swz, st))) return rc;
+  if ((rc = zero_sf_pads(sfb, N, K / 32, swz, st))) return rc;
+  const uint16_t* xa = static_cast<const uint16_t*>(a);
+  const uint16_t* xb = static_cast<const uint16_t*>(b);
+  if (a_axis == 1 && b_axis == 1 && a_fmt == b_fmt) {
+    // both operands have K contiguous (fprop of a linear layer): one launch quantizes the two of them
+    const RowQuantJob ja = {xa, a_rows, a_cols, lda, ca, sfa, nullptr}, jb = {xb, b_rows, b_cols, ldb, cb, sfb, nullptr};
+    launch_rowwise_block<MODE_MX>(ja, jb, a_fmt, swz, nullptr, nullptr, st);
+  } else {
+    if (a_axis == 1) launch_rowwise_block<MODE_MX>(xa, a_rows, a_cols, lda, a_fmt, ca, sfa, swz, nullptr, nullptr, st);
+    else launch_transpose<MODE_MX>(xa, a_rows, a_cols, lda, a_fmt, ca, sfa, swz, nullptr, nullptr, nullptr, st);
+    if (b_axis == 1) launch_rowwise_block<MODE_MX>(xb, b_rows, b_cols, ldb, b_fmt, cb, sfb, swz, nullptr, nullptr, st);
+    else launch_transpose<MODE_MX>(xb, b_rows, b_cols, ldb, b_fmt, cb, sfb, swz, nullptr, nullptr, nullptr, st);
+  }
+  B200Q_CUDA(cudaGetLastError());
+  GemmParams p = {};
+  p.sfa = sfa; p.sfb = sfb; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.M = M; p.N = N; p.K = K;
+  return dispatch<KIND_MX>(ca, cb, one_output(D), ldd, N, p, st);
 }
 
 int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,

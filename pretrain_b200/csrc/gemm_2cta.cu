@@ -182,6 +182,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   int* g_first = reinterpret_cast<int*>(smem_gen + C::GRP_OFF);        // GROUPED: first 128-row tile of every expert (+ end)
   int* g_pairs = g_first + pair::kPairMaxExperts + 1;                   //          pair tiles before every expert (+ total)
   const bool by_expert = GROUPED && p.tile_expert != nullptr;
+  if (GROUPED) grid_dependency_wait();            // the grouped forms read the permute plan's tables right away
   int live_tiles = 0;
   if (by_expert) {
     live_tiles = __ldg(p.num_tiles);
@@ -261,6 +262,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   ptx::cluster_sync();            // both CTAs' barriers exist before anyone signals the peer
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (!GROUPED) grid_dependency_wait();           // operands, scales and the output buffer belong to earlier kernels until here
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) ---------------------------------
@@ -463,8 +465,7 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   p.glu = gp.glu;
   B200Q_CUDA(ensure_dynamic_smem(gemm_pair_kernel<KIND, EPI>, C::SMEM_BYTES));
   const int tiles = p.num_mp * p.num_n, pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
-  gemm_pair_kernel<KIND, EPI><<<2 * pairs, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, msa, msb, md, p);
-  B200Q_CUDA(cudaGetLastError());
+  B200Q_CUDA(launch_pdl(gemm_pair_kernel<KIND, EPI>, dim3(2 * pairs), dim3(gemm_threads(EPI)), C::SMEM_BYTES, st, ma, mb, msa, msb, md, p));
   return B200Q_OK;
 }
 
@@ -518,8 +519,7 @@ int launch_pair_grouped(const void* A, const void* B, const OutSpec& D, int64_t 
   // the pair-tile count of the expert forms is only known on the device: every pair of the GPU starts
   const int64_t tiles = ragged ? (int64_t)p.num_mp * p.num_n * gp.n_experts : (int64_t)(p.num_m128 + 1) / 2 * p.num_n;
   const int pairs = (int)(tiles < kNumSMs / 2 ? tiles : kNumSMs / 2);
-  gemm_pair_kernel<KIND_MX, EPI, true><<<2 * pairs, gemm_threads(EPI), C::SMEM_BYTES, st>>>(ma, mb, msa, msb, md, p);
-  B200Q_CUDA(cudaGetLastError());
+  B200Q_CUDA(launch_pdl(gemm_pair_kernel<KIND_MX, EPI, true>, dim3(2 * pairs), dim3(gemm_threads(EPI)), C::SMEM_BYTES, st, ma, mb, msa, msb, md, p));
   return B200Q_OK;
 }
 

@@ -83,60 +83,81 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const uint16_t* __restri
 // ------------------------------------------------------------------------------------------
 enum { MODE_MX = 0, MODE_NV = 1, MODE_FP8 = 2 };
 
+// One matrix to quantize row-wise: bf16 [rows, cols] pitch ld -> codes [rows, cols] (+ scale factors), input row r
+// written as output row dst_row[r] when a map is given.
+struct RowQuantJob {
+  const uint16_t* x;
+  int64_t rows, cols, ld;
+  uint8_t* codes;
+  uint8_t* sf;
+  const int32_t* dst_row;
+};
+
+// Up to two matrices per launch (MXFP8 only; second.rows == 0: one matrix): both operands of a GEMM quantized by one
+// grid, each thread taking its round-robin share of the first matrix's runs and then of the second's.
 template <int MODE, bool WIDE, int FMT>
 __global__ void __launch_bounds__(kThreads)
-rowwise_block_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
-                           uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, int swz,
-                           const float* __restrict__ tensor_amax, float* __restrict__ tensor_scale_out,
-                           const int32_t* __restrict__ dst_row) {
+rowwise_block_quant_kernel(const RowQuantJob first, const RowQuantJob second, int swz,
+                           const float* __restrict__ tensor_amax, float* __restrict__ tensor_scale_out) {
+  grid_launch_dependents();                    // the whole grid is resident: a GEMM launched behind this kernel may set up now
   constexpr int BS = MODE == MODE_MX ? 32 : 16;
-  const int64_t nblk = cols / BS;
   float s_t = 0.f, rcp_st = 0.f;
   if (MODE == MODE_NV) {
     s_t = nv_tensor_scale(*tensor_amax);
     rcp_st = rcp_rn(s_t);
     if (blockIdx.x == 0 && threadIdx.x == 0) *tensor_scale_out = s_t;
   }
-  const int runs = (int)(cols >> 5);            // 32-element runs per row
-  const int64_t kt = (nblk + 3) >> 2;
-  for (ItemWalker w((int64_t)blockIdx.x * kThreads + threadIdx.x, (int64_t)gridDim.x * kThreads, runs); w.row < rows; w.next()) {
-    const int c = w.chunk << 5;
-    const uint16_t* xp = x + w.row * ld + c;
-    uint4 v[4];
-    ld_nc_32B<WIDE>(xp, v[0], v[1]);
-    ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
-    const int64_t row = dst_row ? (int64_t)__ldg(dst_row + w.row) : w.row;   // output row (codes and scale factors)
-    if (MODE == MODE_MX) {
-      uint32_t o[8];
-      const int e = mx_quant_block32<FMT>(v, o);
-      st_32B<WIDE>(codes + row * cols + c, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
-      sf[swz ? sf_swizzled(row, w.chunk, kt) : row * nblk + w.chunk] = (uint8_t)(e + 127);
-    } else {
-      uint32_t o[4];
-      uint8_t sq2[2];
+#pragma unroll 1
+  for (int t = 0; t < 2; ++t) {
+    const RowQuantJob& job = t == 0 ? first : second;
+    if (job.rows == 0) continue;
+    const uint16_t* __restrict__ x = job.x;
+    uint8_t* __restrict__ codes = job.codes;
+    uint8_t* __restrict__ sf = job.sf;
+    const int32_t* __restrict__ dst_row = job.dst_row;
+    const int64_t rows = job.rows, cols = job.cols, ld = job.ld;
+    const int64_t nblk = cols / BS;
+    const int runs = (int)(cols >> 5);            // 32-element runs per row
+    const int64_t kt = (nblk + 3) >> 2;
+    for (ItemWalker w((int64_t)blockIdx.x * kThreads + threadIdx.x, (int64_t)gridDim.x * kThreads, runs); w.row < rows; w.next()) {
+      const int c = w.chunk << 5;
+      const uint16_t* xp = x + w.row * ld + c;
+      uint4 v[4];
+      ld_nc_32B<WIDE>(xp, v[0], v[1]);
+      ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
+      const int64_t row = dst_row ? (int64_t)__ldg(dst_row + w.row) : w.row;   // output row (codes and scale factors)
+      if (MODE == MODE_MX) {
+        uint32_t o[8];
+        const int e = mx_quant_block32<FMT>(v, o);
+        st_32B<WIDE>(codes + row * cols + c, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+        sf[swz ? sf_swizzled(row, w.chunk, kt) : row * nblk + w.chunk] = (uint8_t)(e + 127);
+      } else {
+        uint32_t o[4];
+        uint8_t sq2[2];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const float a = fmax_nan(absmax8(v[2 * h]), absmax8(v[2 * h + 1]));
-        const uint8_t sq = nv_block_scale_fast(a, s_t, rcp_st);
-        const float eff = mul_rn(e4m3_to_float(sq), s_t);
-        const float rcp = rcp_rn(eff);
-        sq2[h] = sq;
+        for (int h = 0; h < 2; ++h) {
+          const float a = fmax_nan(absmax8(v[2 * h]), absmax8(v[2 * h + 1]));
+          const uint8_t sq = nv_block_scale_fast(a, s_t, rcp_st);
+          const float eff = mul_rn(e4m3_to_float(sq), s_t);
+          const float rcp = rcp_rn(eff);
+          sq2[h] = sq;
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          float f[8];
-          unpack8(v[2 * h + q], f);
-          uint32_t t = 0;
+          for (int q = 0; q < 2; ++q) {
+            float f[8];
+            unpack8(v[2 * h + q], f);
+            uint32_t tt = 0;
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            t |= (uint32_t)cvt_e2m1x2(quot_for_cast(f[2 * i], eff, rcp), quot_for_cast(f[2 * i + 1], eff, rcp)) << (8 * i);
-          o[2 * h + q] = sq != 0 ? t : 0u;
+            for (int i = 0; i < 4; ++i)
+              tt |= (uint32_t)cvt_e2m1x2(quot_for_cast(f[2 * i], eff, rcp), quot_for_cast(f[2 * i + 1], eff, rcp)) << (8 * i);
+            o[2 * h + q] = sq != 0 ? tt : 0u;
+          }
         }
+        *reinterpret_cast<uint4*>(codes + ((row * cols + c) >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
+        const int kb = 2 * w.chunk;   // even: the pair of scale bytes is adjacent in both layouts
+        uint8_t* sp = sf + (swz ? sf_swizzled(row, kb, kt) : row * nblk + kb);
+        sp[0] = sq2[0];
+        sp[1] = sq2[1];
       }
-      *reinterpret_cast<uint4*>(codes + ((row * cols + c) >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
-      const int kb = 2 * w.chunk;   // even: the pair of scale bytes is adjacent in both layouts
-      uint8_t* sp = sf + (swz ? sf_swizzled(row, kb, kt) : row * nblk + kb);
-      sp[0] = sq2[0];
-      sp[1] = sq2[1];
     }
   }
 }
@@ -767,22 +788,29 @@ int zero_sf_pads(void* sf, int64_t outer, int64_t nblk, int layout, cudaStream_t
 
 // Launch helpers: the kernels take the fp8 format and the load width as template arguments.
 template <int MODE, bool WIDE, int FMT>
-void launch_rowwise_block(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, uint8_t* codes, uint8_t* sf, int swz,
-                          const float* tensor_amax, float* tensor_scale_out, const int32_t* dst_row, cudaStream_t st) {
+void launch_rowwise_block(const RowQuantJob& j0, const RowQuantJob& j1, int swz, const float* tensor_amax, float* tensor_scale_out,
+                          cudaStream_t st) {
   auto kernel = rowwise_block_quant_kernel<MODE, WIDE, FMT>;
-  kernel<<<rowwise_grid(kernel, rows * (cols / 32), kThreads), kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, tensor_amax,
-                                                                                 tensor_scale_out, dst_row);
+  const int64_t items = j0.rows * (j0.cols / 32) + j1.rows * (j1.cols / 32);
+  kernel<<<rowwise_grid(kernel, items, kThreads), kThreads, 0, st>>>(j0, j1, swz, tensor_amax, tensor_scale_out);
+}
+// 256-bit loads and stores need 32-byte aligned rows on both sides
+inline bool job_is_wide(const RowQuantJob& j) { return j.rows == 0 || (aligned32(j.x) && aligned32(j.codes) && (j.ld & 15) == 0); }
+template <int MODE>
+void launch_rowwise_block(const RowQuantJob& j0, const RowQuantJob& j1, int fmt, int swz, const float* tensor_amax,
+                          float* tensor_scale_out, cudaStream_t st) {
+  const bool wide = job_is_wide(j0) && job_is_wide(j1);
+#define B200Q_GO(W, F) launch_rowwise_block<MODE, W, F>(j0, j1, swz, tensor_amax, tensor_scale_out, st)
+  if (MODE == MODE_NV || fmt == FMT_E4M3) { if (wide) B200Q_GO(true, FMT_E4M3); else B200Q_GO(false, FMT_E4M3); }
+  else { if (wide) B200Q_GO(true, FMT_E5M2); else B200Q_GO(false, FMT_E5M2); }
+#undef B200Q_GO
 }
 template <int MODE>
 void launch_rowwise_block(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes, uint8_t* sf,
                           int swz, const float* tensor_amax, float* tensor_scale_out, cudaStream_t st,
                           const int32_t* dst_row = nullptr) {
-  // 256-bit loads and stores need 32-byte aligned rows on both sides
-  const bool wide = aligned32(x) && aligned32(codes) && (ld & 15) == 0;
-#define B200Q_GO(W, F) launch_rowwise_block<MODE, W, F>(x, rows, cols, ld, codes, sf, swz, tensor_amax, tensor_scale_out, dst_row, st)
-  if (MODE == MODE_NV || fmt == FMT_E4M3) { if (wide) B200Q_GO(true, FMT_E4M3); else B200Q_GO(false, FMT_E4M3); }
-  else { if (wide) B200Q_GO(true, FMT_E5M2); else B200Q_GO(false, FMT_E5M2); }
-#undef B200Q_GO
+  const RowQuantJob j0 = {x, rows, cols, ld, codes, sf, dst_row}, none = {};
+  launch_rowwise_block<MODE>(j0, none, fmt, swz, tensor_amax, tensor_scale_out, st);
 }
 template <int MODE>
 void launch_transpose(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, int fmt, uint8_t* codes, uint8_t* sf, int swz,

@@ -255,6 +255,21 @@ def gemm_mxfp8(a_codes, a_sf, b_codes, b_sf, a_fmt=E4M3, b_fmt=E4M3, out=None):
     return d
 
 
+def linear_mxfp8(a: torch.Tensor, a_axis: int, b: torch.Tensor, b_axis: int, a_fmt=E4M3, b_fmt=E4M3, out=None):
+    """D = A . B^T with both bf16 operands quantized to MXFP8 along the contraction dimension, in one library call:
+    `a` is the (M, K) operand when a_axis == 1, or its (K, M) storage when a_axis == 0 (likewise `b` with N)."""
+    a, b = _mat(a), _mat(b)
+    m, k = (a.shape if a_axis == 1 else a.shape[::-1])
+    n = b.shape[0] if b_axis == 1 else b.shape[1]
+    d = _out(m, n, a.device, out)
+    lib = _lib.load()
+    ws = torch.empty(lib.b200q_linear_mxfp8_workspace_bytes(m, n, k), dtype=torch.uint8, device=a.device)
+    _lib.check(lib.b200q_linear_mxfp8(a.data_ptr(), a.shape[0], a.shape[1], a.stride(0), a_axis, fmt_of(a_fmt), b.data_ptr(), b.shape[0],
+                                      b.shape[1], b.stride(0), b_axis, fmt_of(b_fmt), d.data_ptr(), d.stride(0), ws.data_ptr(), _stream()),
+               "b200q_linear_mxfp8")
+    return d
+
+
 def gemm_nvfp4(a_packed, a_sf, a_ts, b_packed, b_sf, b_ts, out=None):
     m, k2 = a_packed.shape
     n = b_packed.shape[0]

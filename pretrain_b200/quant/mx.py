@@ -30,10 +30,8 @@ def mxfp8_gemm(a, b, out_dtype, a_dtype=torch.float8_e4m3fn, b_dtype=torch.float
     """`a @ b`, a (M, K), b (K, N), both block-quantized along K."""
     am, a_axis = _k_major(a, 1)
     bm, b_axis = _k_major(b, 0)
-    fa, fb = fmt_of(a_dtype), fmt_of(b_dtype)
-    ca, sfa = T.quantize_mxfp8(am, a_axis, fa, SF_SWIZZLED)
-    cb, sfb = T.quantize_mxfp8(bm, b_axis, fb, SF_SWIZZLED)
-    out = T.gemm_mxfp8(ca, sfa, cb, sfb, fa, fb)
+    # one library call: both quantizations (one launch when both operands have K contiguous) and the GEMM behind them
+    out = T.linear_mxfp8(am, a_axis, bm, b_axis, fmt_of(a_dtype), fmt_of(b_dtype))
     return out if out_dtype == torch.bfloat16 else out.to(out_dtype)
 
 

@@ -175,6 +175,18 @@ def _(a, a_sf, b, b_sf, a_fmt, b_fmt):
     return a.new_empty(a.shape[0], b.shape[0], dtype=torch.bfloat16)
 
 
+@_lib_def("b200q::linear_mxfp8", mutates_args=())
+def linear_mxfp8(a: torch.Tensor, a_axis: int, b: torch.Tensor, b_axis: int, a_fmt: int, b_fmt: int) -> torch.Tensor:
+    return ops.linear_mxfp8(a, a_axis, b, b_axis, a_fmt, b_fmt)
+
+
+@linear_mxfp8.register_fake
+def _(a, a_axis, b, b_axis, a_fmt, b_fmt):
+    m = a.shape[0] if a_axis == 1 else a.shape[1]
+    n = b.shape[0] if b_axis == 1 else b.shape[1]
+    return a.new_empty(m, n, dtype=torch.bfloat16)
+
+
 @_lib_def("b200q::gemm_nvfp4", mutates_args=())
 def gemm_nvfp4(a: torch.Tensor, a_sf: torch.Tensor, a_ts: torch.Tensor, b: torch.Tensor, b_sf: torch.Tensor, b_ts: torch.Tensor) -> torch.Tensor:
     return ops.gemm_nvfp4(a, a_sf, a_ts, b, b_sf, b_ts)

@@ -292,3 +292,29 @@ def test_fake_kernels_of_the_linear_ops_describe_the_real_outputs():
     xn, xns, xnt = T.quantize_nvfp4(x, 1, 1)
     wn, wns, wnt = T.quantize_nvfp4(w, 1, 1)
     check(T.gemm_nvfp4, xn, xns, xnt, wn, wns, wnt)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 384, 128), (8192, 3072, 768), (200, 264, 96), (64, 4096, 2048)])
+def test_one_call_mxfp8_linear_equals_the_three_call_path(m, n, k):
+    """b200q_linear_mxfp8 (one launch quantizes both operands, the GEMM follows by programmatic dependent launch) gives
+    the bits of quantize + quantize + GEMM, for K-contiguous operands and for transposed storage of either one, and
+    repeated back to back (the GEMM's early set-up must never read codes of the call before)."""
+    from pretrain_b200 import build, ops
+    build.build()
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).bfloat16().cuda()
+    b = (0.05 * torch.randn(n, k, generator=g)).bfloat16().cuda()
+    ca, sfa = ops.quantize_mxfp8(a, 1); cb, sfb = ops.quantize_mxfp8(b, 1)
+    want = ops.gemm_mxfp8(ca, sfa, cb, sfb)
+    assert torch.equal(ops.linear_mxfp8(a, 1, b, 1), want)
+    for scale in (1.0, 0.5, 2.0, 0.25):                       # different inputs through the same allocator blocks
+        a2 = (a * scale).bfloat16()
+        c2, s2 = ops.quantize_mxfp8(a2, 1)
+        assert torch.equal(ops.linear_mxfp8(a2, 1, b, 1), ops.gemm_mxfp8(c2, s2, cb, sfb))
+    if m % 32 == 0:
+        at, bt = a.t().contiguous(), b.t().contiguous()       # (K, M) and (K, N) storage: the transposing quantizer
+        assert torch.equal(ops.linear_mxfp8(at, 0, b, 1), want)
+        assert torch.equal(ops.linear_mxfp8(a, 1, bt, 0), want)
+        assert torch.equal(ops.linear_mxfp8(a, 1, b, 1, ops.E5M2, ops.E4M3),
+                           ops.gemm_mxfp8(*ops.quantize_mxfp8(a, 1, ops.E5M2), cb, sfb, ops.E5M2, ops.E4M3))
+    ops.device_status()
