@@ -199,6 +199,44 @@ def wgrad_reduce_scatter_fused(dy_shard: torch.Tensor, x_shard: torch.Tensor, ou
     return ops.sum_slots(out.bufs[turn])
 
 
+class DataParallelGrad:
+    """Sum of a linear layer's weight gradient over the ranks of a data-parallel group (the all-reduce DDP would do for
+    the parameter), with the reduce-scatter half fused into the wgrad GEMM: ``wgrad`` runs the MXFP8 GEMM in scatter mode
+    (every 32-row block of this rank's partial dW goes to this rank's slot in its owner's staging buffer over NVLink),
+    rendezvous, each owner adds its slots in fp32 in rank order and rounds once, and an all-gather of the owners' shards
+    gives every rank the full summed gradient - bit-identical on all ranks, and equal to adding the ranks' bf16 partials
+    in fp32.  The reference is single-GPU: its wgrad is src/quant/linear.py:102-109 and nothing sums it."""
+
+    def __init__(self, out_features: int, in_features: int, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.n, self.k = out_features, in_features
+        self.fused = out_features % (32 * self.world) == 0 and in_features % 8 == 0
+        self.stage = ScatteredSum(out_features, in_features, self.group) if self.fused else None
+
+    def wgrad(self, gc, gsc, xc, xsc, fg, fa) -> torch.Tensor:
+        """dW (n, k) bf16 summed over the ranks from this rank's transposed MXFP8 codes of the output gradient (n, m) and
+        of the layer input (k, m)."""
+        from . import ops
+        if not self.fused:
+            return self.reduce_small(ops.gemm_mxfp8(gc, gsc, xc, xsc, fg, fa))
+        st = self.stage
+        turn = st._turn
+        st._turn ^= 1
+        ops.gemm_mxfp8_scatter(gc, gsc, xc, xsc, st.ptrs[turn], st.rank, self.k, self.k, fg, fa)
+        st.sync()
+        shard = ops.sum_slots(st.bufs[turn])                                # this rank's rows of the sum
+        full = torch.empty(self.n, self.k, dtype=torch.bfloat16, device=shard.device)
+        dist.all_gather_into_tensor(full, shard, group=self.group)
+        return full
+
+    def reduce_small(self, t: torch.Tensor) -> torch.Tensor:
+        """fp32 sum over the ranks of a gradient that has no fused form (a bias, or a weight of another format)."""
+        acc = t.float().contiguous()
+        dist.all_reduce(acc, group=self.group)
+        return acc.to(t.dtype)
+
+
 # ---- expert parallelism ---------------------------------------------------------------------
 
 @dataclass

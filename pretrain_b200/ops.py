@@ -213,6 +213,18 @@ def quantize_nvfp4(x: torch.Tensor, axis: int = 1, tensor_amax: torch.Tensor | N
     return codes, sf, ts
 
 
+def quantize_nvfp4_both(x: torch.Tensor, tensor_amax: torch.Tensor | None = None, layout: int = SF_SWIZZLED):
+    """Both NVFP4 copies of x (rows, cols) under ONE tensor scale: (packed_row (rows, cols/2), sf_row, packed_col
+    (cols, rows/2), sf_col, tensor_scale) - what quantize_nvfp4(x, 1) and quantize_nvfp4(x, 0) give, with the tensor
+    maximum taken once (three passes over x instead of four).  rows % 32 == 0 and cols % 32 == 0."""
+    x = _mat(x)
+    if tensor_amax is None:
+        tensor_amax = amax(x)
+    pr, sr, ts = quantize_nvfp4(x, 1, tensor_amax, layout)
+    pc, sc, _ = quantize_nvfp4(x, 0, tensor_amax, layout)
+    return pr, sr, pc, sc, ts
+
+
 def _out(m: int, n: int, device, out: torch.Tensor | None) -> torch.Tensor:
     if out is None:
         return torch.empty(m, n, dtype=torch.bfloat16, device=device)

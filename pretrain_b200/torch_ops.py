@@ -155,6 +155,19 @@ def _(x, axis, layout):
             x.new_empty(1, dtype=torch.float32))
 
 
+@_lib_def("b200q::quantize_nvfp4_both", mutates_args=())
+def quantize_nvfp4_both(x: torch.Tensor, layout: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    return ops.quantize_nvfp4_both(x, None, layout)
+
+
+@quantize_nvfp4_both.register_fake
+def _(x, layout):
+    rows, cols = x.shape
+    return (x.new_empty(rows, cols // 2, dtype=torch.uint8), x.new_empty(_sf_numel(rows, cols // 16, layout), dtype=torch.uint8),
+            x.new_empty(cols, rows // 2, dtype=torch.uint8), x.new_empty(_sf_numel(cols, rows // 16, layout), dtype=torch.uint8),
+            x.new_empty(1, dtype=torch.float32))
+
+
 @_lib_def("b200q::gemm_fp8", mutates_args=())
 def gemm_fp8(a: torch.Tensor, a_fmt: int, b: torch.Tensor, b_fmt: int, scale_a: torch.Tensor, scale_b: torch.Tensor) -> torch.Tensor:
     return ops.gemm_fp8(a, a_fmt, b, b_fmt, scale_a, scale_b)

@@ -318,3 +318,40 @@ def test_one_call_mxfp8_linear_equals_the_three_call_path(m, n, k):
         assert torch.equal(ops.linear_mxfp8(a, 1, b, 1, ops.E5M2, ops.E4M3),
                            ops.gemm_mxfp8(*ops.quantize_mxfp8(a, 1, ops.E5M2), cb, sfb, ops.E5M2, ops.E4M3))
     ops.device_status()
+
+
+def test_nvfp4_training_path_takes_each_maximum_once_and_equals_the_per_gemm_path():
+    """All-NVFP4 layers quantize x, w and g in both directions under one tensor scale each (the tensor maximum taken
+    once), save the transposed codes for backward and keep the weight's copies on the parameter; y, dx and dw equal what
+    the three separate `_gemm` calls give, bit for bit."""
+    from pretrain_b200.quant.linear import QuantLinear, QuantizedLinearFn, _gemm
+    torch.manual_seed(2)
+    cfg = _cfg("nvfp4")
+    m, k, n = 256, 160, 96
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = nn.Parameter((0.05 * torch.randn(n, k, device="cuda")).bfloat16())
+    g = (1e-2 * torch.randn(m, n, device="cuda")).bfloat16()
+    y = QuantizedLinearFn.apply(x, w, None, cfg)
+    y.backward(g)
+    d = cfg.dtype
+    with torch.no_grad():
+        y_ref = _gemm(x, w.t(), d["act"], d["weight"], torch.bfloat16)
+        dx_ref = _gemm(g, w, d["input_grad"], d["weight"], torch.bfloat16)
+        dw_ref = _gemm(g.t(), x, d["weight_grad"], d["act"], torch.bfloat16)
+    assert torch.equal(y, y_ref) and torch.equal(x.grad, dx_ref) and torch.equal(w.grad, dw_ref)
+    cached = w._b200q_nv
+    QuantizedLinearFn.apply(x, w, None, cfg).sum().backward()
+    assert w._b200q_nv is cached
+    with torch.no_grad():
+        w.mul_(1.5)
+    QuantizedLinearFn.apply(x, w, None, cfg)
+    assert w._b200q_nv is not cached
+    # against the unquantized gradients: NVFP4 noise only
+    xf, wf = x.detach().float(), w.detach().float()
+    q = QuantLinear(k, n, True, cfg).cuda().bfloat16()
+    with torch.no_grad():
+        q.weight.copy_(w); q.bias.zero_()
+    xi = x.detach().clone().requires_grad_(True)
+    q(xi).backward(g)
+    assert _rel(q.weight.grad.float(), g.float().t() @ xf) < 0.2 and _rel(xi.grad.float(), g.float() @ wf) < 0.2
+    assert torch.equal(q.bias.grad, g.sum(0))

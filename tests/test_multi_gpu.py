@@ -153,6 +153,45 @@ def test_fused_wgrad_reduce_scatter_equals_sum_of_partials():
     _run(_wgrad_rs_rank, 2)
 
 
+def _dp_linear_rank(rank, world, recipe):
+    import torch.nn as nn
+    from pretrain_b200.quant.config import TrainingConfig
+    from pretrain_b200.quant.linear import QuantLinear
+    q = {"enabled": True, "dtype_recipe": recipe}
+    if recipe == "fp8":
+        q["scaling"] = {"granularity": "rowwise"}
+    cfg = TrainingConfig(quant=q).quant[0]
+    m, k, n = 512, 256, 384
+    torch.manual_seed(0)                                            # the same weights on every rank
+    lin = nn.Linear(k, n, bias=True)
+    g = torch.Generator().manual_seed(100 + rank)                   # its own shard of the batch
+    x = torch.randn(m, k, generator=g).bfloat16().cuda()
+    dy = (1e-2 * torch.randn(m, n, generator=g)).bfloat16().cuda()
+    plain = QuantLinear.from_linear(lin, cfg).cuda().bfloat16()
+    dp = QuantLinear.from_linear(lin, cfg).cuda().bfloat16().enable_data_parallel()
+    for _ in range(2):                                              # the staging buffers alternate
+        plain.zero_grad(); dp.zero_grad()
+        plain(x).backward(dy)
+        dp(x).backward(dy)
+    # what summing the single-GPU gradients of the ranks gives: bf16 partials added in fp32 in rank order, one rounding
+    parts = [torch.empty_like(plain.weight.grad) for _ in range(world)]
+    dist.all_gather(parts, plain.weight.grad.contiguous())
+    want_w = torch.stack([p.float() for p in parts]).sum(0).bfloat16()
+    bparts = [torch.empty_like(plain.bias.grad) for _ in range(world)]
+    dist.all_gather(bparts, plain.bias.grad.contiguous())
+    want_b = torch.stack([p.float() for p in bparts]).sum(0).bfloat16()
+    torch.cuda.synchronize()
+    assert torch.equal(dp.weight.grad, want_w), (dp.weight.grad.float() - want_w.float()).abs().max()
+    assert torch.equal(dp.bias.grad, want_b)
+
+
+@pytest.mark.parametrize("recipe", ["mxfp8", "fp8"])
+def test_data_parallel_quant_linear_sums_the_weight_gradient_over_the_ranks(recipe):
+    """QuantLinear.enable_data_parallel: w.grad == the sum over the ranks of the single-GPU dW, bit for bit - for MXFP8
+    through the wgrad GEMM whose epilogue scatters into the owners' staging buffers."""
+    _run(_dp_linear_rank, 2, recipe)
+
+
 def _ep_rank(rank, world):
     from pretrain_b200 import dist as D, ops
     from pretrain_b200.layers.mlp import _grouped_ffn_padded, silu_glu
