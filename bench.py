@@ -1299,11 +1299,23 @@ def expert_parallel_record(dist, rank, world, barrier, rank_max, total_tokens=16
     with torch.no_grad():
         nccl_ms = timed(lambda: D.expert_parallel_moe(x, top_i, top_w, w1l, w2l, e))
         rec.update(nccl_all_to_all_ms=nccl_ms, nccl_tflops=flops / (nccl_ms * 1e-3) / 1e12)
-        ep = D.FusedExpertParallel(t, k, d, e)
+        cap = min(world * t * k, 2 * t * k)                  # twice the balanced share per rank (checked every call)
+        ep = D.FusedExpertParallel(t, k, d, e, capacity_rows=cap if world > 2 else None, training=True)
         fused_ms = timed(lambda: ep.forward(x, top_i, top_w, w1l, w2l))
         rec.update(fused_ms=fused_ms, fused_tflops=flops / (fused_ms * 1e-3) / 1e12,
                    fused="dispatch = gather + MXFP8 kernel storing into the owners' buffers, combine = unpermute kernel loading from "
-                         "them (symmetric memory, NVLink)")
+                         "them (symmetric memory, NVLink); phases ordered by flag barriers in peer memory, index tables by one kernel")
+    # forward + backward of the same block (bf16 rows on the wire, the owners' six grouped GEMMs in MXFP8)
+    w1p, w2p = torch.nn.Parameter(w1l), torch.nn.Parameter(w2l)
+    xg, wg = x.clone().requires_grad_(True), top_w.clone().requires_grad_(True)
+    dout = torch.randn(t, d, device="cuda", dtype=torch.bfloat16)
+
+    def train_step():
+        out = ep.train(xg, top_i, wg, w1p, w2p)
+        torch.autograd.grad(out, (xg, wg, w1p, w2p), dout)
+
+    train_ms = timed(train_step, reps=10)
+    rec.update(fused_train_ms=train_ms, fused_train_tflops=3 * flops / (train_ms * 1e-3) / 1e12)
     return rec
 
 

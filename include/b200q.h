@@ -105,10 +105,12 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
  * A linear layer needs both of each tensor: the activation for fprop and wgrad
  * (src/quant/linear.py:74,102), the weight for fprop and dgrad (:74,98), the output gradient for
  * dgrad and wgrad (:98,102); the reference re-reads the bf16 tensor for each.  rows % 32 == 0 and
- * cols % 32 == 0.  4.0625 bytes of traffic per element instead of 2 x 3.03125. */
+ * cols % 32 == 0.  4.0625 bytes of traffic per element instead of 2 x 3.03125.
+ * num_tiles (device int32, may be NULL): only the first *num_tiles 128-row tiles of x are processed - the rows in use of
+ * a padded expert-sorted buffer whose size is an upper bound; outputs belonging to later rows are left untouched. */
 int b200q_quantize_mxfp8_dual(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt,
                               void* codes_row, void* sf_row, void* codes_col, void* sf_col,
-                              int sf_layout, void* stream);
+                              int sf_layout, const int32_t* num_tiles, void* stream);
 
 /* Row-wise b200q_quantize_mxfp8 (axis = 1) that writes input row r as output row dst_row[r]
  * (codes and scale factors alike); dst_row is a permutation of 0 .. rows-1 in device memory.
@@ -353,10 +355,12 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
  *                        tile into dot_workspace ((D / 128) * padded_rows floats) and then per pair.
  *   swiglu:              silu(gate) * up of g = [gate | up]  (b200q_swiglu with quantize = 0)
  *   swiglu backward:     [d_gate | d_up] of b200q_swiglu_backward
- * Row counts are multiples of 128; D % 128 == 0; I % 128 == 0 (swiglu) / I % 64 == 0 (swiglu backward). */
+ * Row counts are multiples of 128; D % 128 == 0; I % 128 == 0 (swiglu) / I % 64 == 0 (swiglu backward).
+ * num_tiles (device int32, may be NULL) limits the work to the first *num_tiles 128-row tiles, as for
+ * b200q_quantize_mxfp8_dual. */
 int b200q_moe_gather_quantize_dual(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row,
                                    int64_t padded_rows, int fmt, void* codes_row, void* sf_row,
-                                   void* codes_col, void* sf_col, void* stream);
+                                   void* codes_col, void* sf_col, const int32_t* num_tiles, void* stream);
 int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, const void* w,
                                                const int32_t* pair_of_row, int k, int64_t padded_rows,
                                                int64_t D, int fmt, void* codes_row, void* sf_row,
@@ -365,10 +369,11 @@ int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, con
                                                float* dot_workspace, float* dw, void* stream);
 int b200q_swiglu_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, int fmt,
                                void* codes_row, void* sf_row, void* codes_col, void* sf_col,
-                               void* stream);
+                               const int32_t* num_tiles, void* stream);
 int b200q_swiglu_backward_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg,
                                         const void* dh, int64_t lddh, int fmt, void* codes_row,
-                                        void* sf_row, void* codes_col, void* sf_col, void* stream);
+                                        void* sf_row, void* codes_col, void* sf_col,
+                                        const int32_t* num_tiles, void* stream);
 
 /* Expert parallelism inside one NVLink domain without a collective on the data path: ranks own
  * contiguous ranges of experts_per_rank experts and expose their buffers to each other (peer-mapped
@@ -395,6 +400,36 @@ int b200q_moe_zero_pad_rows(const int32_t* src_of_row, const int32_t* num_tiles,
 int b200q_moe_combine_peers(void* const* peer_y, int world, int64_t ldy, const void* w,
                             const int32_t* pair_peer, const int32_t* pair_row, int64_t T, int k,
                             int64_t D, void* out, void* stream);
+
+/* Expert parallelism, the pieces around the kernels above (all new functionality; the reference is single-GPU).
+ *
+ * ep_index: from the gathered per-sender cumulative counts all_offs[world][E] (every rank's `offs` of its own permute
+ * plan) - row_base[E]: where THIS rank's rows for every global expert start inside the owner's padded expert-sorted
+ * buffer (segments of the owner's experts in order, each padded to 128 rows, senders in rank order inside a segment);
+ * own_offs[E / world]: cumulative ends of the segments this rank owns (the `offs` input of b200q_moe_pad_plan);
+ * pair_peer / pair_row [T*k]: owner and row there of every routed pair.  One launch replaces a dozen index operations.
+ *
+ * peer_barrier: stream-ordered rendezvous of the ranks through flag words in peer-mapped memory (flag_ptrs[g] = rank g's
+ * int32[world] array, zero before the first use; `epoch` must grow by one per call on every rank): every rank stores
+ * the epoch into its slot of every array and waits until all slots of its own array have reached it.  The wait is
+ * bounded (about a second); a rank that gives up sets the device status word (b200q_device_status) and returns.
+ *
+ * scatter_rows_peers: out_{pair_peer[p]}[pair_row[p]] = (w[p] *) x[p / k] for every routed pair p, bf16 - the training
+ * dispatch (w = NULL) and the backward of the combine (x = dout, w = routing weights).  Stores only.
+ * zero_pad_rows_bf16: the owner clears the rows no sender writes (src_of_row < 0 in its pad plan).
+ * pair_dots_peers: dw[p] = <dout[p / k], y_{pair_peer[p]}[pair_row[p]]> in fp32, the routing weights' gradient. */
+int b200q_moe_ep_index(const int32_t* all_offs, int world, int rank, int E, const int64_t* top_idx,
+                       const int32_t* row_of, const int32_t* padded_offs, int64_t n_pairs, int32_t* row_base,
+                       int32_t* own_offs, int32_t* pair_peer, int32_t* pair_row, void* stream);
+int b200q_peer_barrier(void* const* flag_ptrs, int world, int rank, int epoch, void* stream);
+int b200q_moe_scatter_rows_peers(const void* x, int64_t ld, const void* w, const int32_t* pair_peer,
+                                 const int32_t* pair_row, int64_t T, int k, int64_t D, void* const* peer_y,
+                                 int world, int64_t ldy, void* stream);
+int b200q_moe_zero_pad_rows_bf16(const int32_t* src_of_row, const int32_t* num_tiles, int64_t padded_rows,
+                                 int64_t D, void* buf, int64_t ld, void* stream);
+int b200q_moe_pair_dots_peers(const void* dout, int64_t ld, void* const* peer_y, int world, int64_t ldy,
+                              const int32_t* pair_peer, const int32_t* pair_row, int64_t T, int k, int64_t D,
+                              float* dw, void* stream);
 
 /* Backward of b200q_swiglu(quantize = 0): dg[r] = [dh * up * silu'(gate) | dh * silu(gate)] for
  * g[r] = [gate | up]; bf16 in and out, fp32 arithmetic (the reference gets this from autograd through

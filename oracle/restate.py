@@ -342,6 +342,43 @@ def moe_permute(top_indices: torch.Tensor, n_experts: int):
     return order, token_ids[order], counts, offs
 
 
+def moe_padded_plan(top_indices: torch.Tensor, n_experts: int):
+    """Host restatement of the padded expert-sorted layout the kernels use between permute and unpermute: the reference's
+    stable expert order (src/layers/mlp.py:447-452) with every expert's segment starting on a multiple of 128 rows.
+    Returns (offs (E,) cumulative unpadded ends, padded_offs (E+1,), row_of (T*k,) padded row of every pair)."""
+    flat = top_indices.reshape(-1)
+    order, _, counts, offs = moe_permute(top_indices, n_experts)
+    padded = (counts + 127) // 128 * 128
+    padded_offs = torch.cat([padded.new_zeros(1), padded.cumsum(0)])
+    starts = offs - counts
+    row_of = torch.empty(flat.numel(), dtype=torch.int64)
+    sorted_e = flat[order]
+    row_of[order] = padded_offs[sorted_e] + torch.arange(flat.numel()) - starts[sorted_e]
+    return offs.to(torch.int32), padded_offs.to(torch.int32), row_of.to(torch.int32)
+
+
+def ep_index(all_offs: torch.Tensor, rank: int, top_indices: torch.Tensor, row_of: torch.Tensor, padded_offs: torch.Tensor):
+    """Host restatement of the expert-parallel index tables (no counterpart in the reference, which is single-GPU).
+
+    all_offs (world, E): every sender's cumulative per-expert counts.  An owner's buffer holds the segments of its
+    E / world experts in order, each padded to 128 rows; inside a segment the senders' rows follow in rank order, each
+    sender's in its own stable order.  Returns (row_base (E,): where `rank`'s rows for every expert start at the owner;
+    own_offs (E / world,): cumulative ends of the segments `rank` owns; pair_peer, pair_row (T*k,))."""
+    world, e = all_offs.shape
+    el = e // world
+    counts = torch.diff(all_offs.long(), dim=1, prepend=torch.zeros(world, 1, dtype=torch.long))       # [sender][expert]
+    totals = counts.sum(0)
+    padded = (totals + 127) // 128 * 128
+    seg = padded.view(world, el)
+    seg_start = (seg.cumsum(1) - seg).reshape(-1)
+    row_base = seg_start + counts[:rank].sum(0)
+    own_offs = totals.view(world, el)[rank].cumsum(0)
+    flat = top_indices.reshape(-1).long()
+    pair_peer = flat // el
+    pair_row = row_base[flat] + row_of.long() - padded_offs.long()[flat]
+    return row_base.to(torch.int32), own_offs.to(torch.int32), pair_peer.to(torch.int32), pair_row.to(torch.int32)
+
+
 def silu_glu(gate, up):
     """src/layers/activation.py:80-81."""
     return torch.nn.functional.silu(gate) * up

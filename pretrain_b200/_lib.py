@@ -53,18 +53,23 @@ SIGNATURES = {
     "b200q_gemm_mxfp8_swiglu": (_int, [_vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "b200q_grouped_gemm_mxfp8_swiglu": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _i64, _int, _i64, _i64, _vp, _i64,
                                                _vp, _vp]),
-    "b200q_quantize_mxfp8_dual": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _int, _vp]),
+    "b200q_quantize_mxfp8_dual": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _int, _vp, _vp]),
     "b200q_gemm_nvfp4_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "b200q_quantize_nvfp4_rowmap": (_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp]),
     "b200q_quantize_mxfp8_rowmap": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp]),
-    "b200q_moe_gather_quantize_dual": (_int, [_vp, _i64, _i64, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_moe_gather_quantize_dual": (_int, [_vp, _i64, _i64, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_unpermute_backward_quantize_dual": (_int, [_vp, _i64, _vp, _vp, _int, _i64, _i64, _int, _vp, _vp, _vp, _vp,
                                                          _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
-    "b200q_swiglu_quantize_dual": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
-    "b200q_swiglu_backward_quantize_dual": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_swiglu_quantize_dual": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_swiglu_backward_quantize_dual": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_dispatch_peers": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _int, _int, _vp, _vp, _vp]),
     "b200q_moe_zero_pad_rows": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "b200q_moe_combine_peers": (_int, [_vp, _int, _i64, _vp, _vp, _vp, _i64, _int, _i64, _vp, _vp]),
+    "b200q_moe_ep_index": (_int, [_vp, _int, _int, _int, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_peer_barrier": (_int, [_vp, _int, _int, _int, _vp]),
+    "b200q_moe_scatter_rows_peers": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _int, _i64, _vp, _int, _i64, _vp]),
+    "b200q_moe_zero_pad_rows_bf16": (_int, [_vp, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "b200q_moe_pair_dots_peers": (_int, [_vp, _i64, _vp, _int, _i64, _vp, _vp, _i64, _int, _i64, _vp, _vp]),
     "b200q_swiglu_backward": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
     "b200q_moe_unpermute_backward": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _int, _i64, _i64, _vp, _vp, _vp]),
     "b200q_moe_router_topk": (_int, [_vp, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp]),

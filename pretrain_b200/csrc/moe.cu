@@ -558,6 +558,146 @@ moe_combine_kernel(const PeerRows peers, int64_t ldy, const uint16_t* __restrict
   }
 }
 
+// ---- expert parallelism: index tables, flag barrier, bf16 row scatter, pair dot products ------------------------
+// Index tables of one rank, from the gathered per-sender counts: where this rank's rows for every (global) expert
+// start inside the owner's padded expert-sorted buffer, the segment ends of the experts it owns, and for every routed
+// pair the owner and the row there.  all_offs[r][e] = cumulative count of sender r's pairs up to and including
+// expert e (its permute plan's `offs`).  Layout of an owner's buffer: its experts' segments in order, each padded to
+// 128 rows, senders in rank order inside a segment, a sender's rows in its own stable order.
+// Every CTA rebuilds the small per-expert tables in shared memory (E <= 256, world <= 8); CTA 0 writes them out.
+__global__ void __launch_bounds__(256)
+moe_ep_index_kernel(const int32_t* __restrict__ all_offs, int world, int rank, int E, int e_local,
+                    const int64_t* __restrict__ top_idx, const int32_t* __restrict__ row_of, const int32_t* __restrict__ padded_offs,
+                    int64_t n_pairs, int32_t* __restrict__ row_base, int32_t* __restrict__ own_offs,
+                    int32_t* __restrict__ pair_peer, int32_t* __restrict__ pair_row) {
+  __shared__ int s_total[kMaxExperts], s_before[kMaxExperts], s_base[kMaxExperts];
+  for (int e = threadIdx.x; e < E; e += 256) {
+    int tot = 0, before = 0;
+    for (int r = 0; r < world; ++r) {
+      const int c = all_offs[r * E + e] - (e > 0 ? all_offs[r * E + e - 1] : 0);
+      tot += c;
+      if (r < rank) before += c;
+    }
+    s_total[e] = tot;
+    s_before[e] = before;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += 256) {
+    int start = 0;
+    for (int j = (e / e_local) * e_local; j < e; ++j) start += (s_total[j] + 127) & ~127;
+    s_base[e] = start + s_before[e];
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e < E; e += 256) row_base[e] = s_base[e];
+    for (int j = threadIdx.x; j < e_local; j += 256) {
+      int acc = 0;
+      for (int i = 0; i <= j; ++i) acc += s_total[rank * e_local + i];
+      own_offs[j] = acc;
+    }
+  }
+  for (int64_t p = (int64_t)blockIdx.x * 256 + threadIdx.x; p < n_pairs; p += (int64_t)gridDim.x * 256) {
+    const int e = (int)top_idx[p];
+    pair_peer[p] = e / e_local;
+    pair_row[p] = s_base[e] + row_of[p] - padded_offs[e];
+  }
+}
+
+// Rendezvous of the ranks of one NVLink domain without a collective: every rank writes the epoch into its slot of every
+// rank's flag array (peer-mapped memory, release at system scope) and then waits until every slot of its own array has
+// reached the epoch (acquire at system scope).  Stream-ordered: the stores of the kernels before it have been performed
+// when it starts, the kernels after it start once every rank has arrived.  The wait is bounded (about a second); a rank
+// that gives up records status 31 and returns, it never spins forever.
+struct PeerFlags {
+  int32_t* f[kMaxPeers];
+};
+constexpr uint32_t kBarrierPolls = 4000000u;
+
+__global__ void peer_barrier_kernel(const PeerFlags flags, int world, int rank, int epoch) {
+  const int lane = threadIdx.x;
+  __threadfence_system();
+  if (lane < world) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.f[lane] + rank), "r"(epoch) : "memory");
+    bool ok = false;
+    for (uint32_t i = 0; i < kBarrierPolls && !ok; ++i) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags.f[rank] + lane) : "memory");
+      ok = v - epoch >= 0;
+      if (!ok && i > 2048u) __nanosleep(200);
+    }
+    if (!ok) atomicExch(&g_device_status, 31);
+  }
+  __syncwarp();
+  __threadfence_system();
+}
+
+// Rows of x (optionally scaled by the pair's routing weight, fp32 multiply, one rounding) stored as bf16 into the
+// buffers of the ranks that own the pairs' experts: the transpose of moe_combine_kernel.  Stores only cross NVLink.
+struct PeerRowsW {
+  uint16_t* y[kMaxPeers];
+};
+
+__global__ void __launch_bounds__(256)
+moe_scatter_rows_peers_kernel(const uint16_t* __restrict__ x, int64_t ld, const uint16_t* __restrict__ w,
+                              const int32_t* __restrict__ pair_peer, const int32_t* __restrict__ pair_row, int64_t n_pairs, int k,
+                              int64_t D, const PeerRowsW peers, int64_t ldy) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (ItemWalker it((int64_t)blockIdx.x * 8 + warp, (int64_t)gridDim.x * 8, (int)((D + 255) >> 8)); it.row < n_pairs; it.next()) {
+    const int64_t p = it.row, c = (int64_t)it.chunk * 256 + lane * 8;
+    if (c >= D) continue;
+    uint4 v = ld_nc_v4(x + (p / k) * ld + c);
+    if (w != nullptr) {
+      const float wj = u2f((uint32_t)w[p] << 16);
+      float f[8];
+      unpack8(v, f);
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 pk = __floats2bfloat162_rn(wj * f[2 * i], wj * f[2 * i + 1]);
+        o[i] = *reinterpret_cast<uint32_t*>(&pk);
+      }
+      v = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    *reinterpret_cast<uint4*>(peers.y[pair_peer[p]] + (int64_t)pair_row[p] * ldy + c) = v;
+  }
+}
+
+// The receiver clears the rows of its bf16 buffer that no sender writes (the pad rows of every live segment).
+__global__ void __launch_bounds__(256)
+moe_zero_pad_rows_bf16_kernel(const int32_t* __restrict__ src_of_row, const int32_t* __restrict__ num_tiles, int64_t padded_rows,
+                              int64_t D, uint16_t* __restrict__ buf, int64_t ld) {
+  int64_t live_rows = (int64_t)(*num_tiles) << 7;
+  if (live_rows > padded_rows) live_rows = padded_rows;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t r = (int64_t)blockIdx.x * 8 + warp; r < live_rows; r += (int64_t)gridDim.x * 8) {
+    if (src_of_row[r] >= 0) continue;
+    for (int64_t c = lane * 8; c < D; c += 256) *reinterpret_cast<uint4*>(buf + r * ld + c) = make_uint4(0, 0, 0, 0);
+  }
+}
+
+// dw[p] = <dout[token of p], y_owner[row of p]> in fp32, the expert outputs read in place from their owners.
+__global__ void __launch_bounds__(256)
+moe_pair_dots_peers_kernel(const uint16_t* __restrict__ dout, int64_t ld, const PeerRows peers, int64_t ldy,
+                           const int32_t* __restrict__ pair_peer, const int32_t* __restrict__ pair_row, int64_t n_pairs, int k,
+                           int64_t D, float* __restrict__ dw) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t p = (int64_t)blockIdx.x * 8 + warp; p < n_pairs; p += (int64_t)gridDim.x * 8) {
+    const uint16_t* yr = peers.y[pair_peer[p]] + (int64_t)pair_row[p] * ldy;
+    const uint16_t* dr = dout + (p / k) * ld;
+    float dot = 0.f;
+    for (int64_t c = lane * 8; c < D; c += 256) {
+      float a[8], b[8];
+      unpack8(ld_nc_v4(dr + c), a);
+      unpack8(*reinterpret_cast<const uint4*>(yr + c), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot = fmaf(a[i], b[i], dot);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
+    if (lane == 0) dw[p] = dot;
+  }
+}
+
 // ---- backward of SwiGLU: dg = [dh * up * silu'(gate) | dh * silu(gate)] -------------------------
 // silu'(x) = s (1 + x (1 - s)), s = 1 / (1 + e^-x); fp32 arithmetic on the bf16 inputs, one rounding.
 __global__ void __launch_bounds__(256)
@@ -819,6 +959,93 @@ int b200q_moe_combine_peers(void* const* peer_y, int world, int64_t ldy, const v
   if (rc) return rc;
   moe_combine_kernel<<<row_grid(T * ((D + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(peers, ldy, (const uint16_t*)w, pair_peer,
                                                                                       pair_row, T, k, D, (uint16_t*)out);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_ep_index(const int32_t* all_offs, int world, int rank, int E, const int64_t* top_idx, const int32_t* row_of,
+                       const int32_t* padded_offs, int64_t n_pairs, int32_t* row_base, int32_t* own_offs, int32_t* pair_peer,
+                       int32_t* pair_row, void* stream) {
+  if (all_offs == nullptr || top_idx == nullptr || row_of == nullptr || padded_offs == nullptr || row_base == nullptr ||
+      own_offs == nullptr || pair_peer == nullptr || pair_row == nullptr || n_pairs <= 0 || world < 1 || world > kMaxPeers ||
+      rank < 0 || rank >= world || E <= 0)
+    return B200Q_ERR_INVALID_ARG;
+  if (E > kMaxExperts || E % world) return B200Q_ERR_SHAPE;
+  int rc = require_sm100();
+  if (rc) return rc;
+  const int64_t want = (n_pairs + 255) / 256, cap = (int64_t)kNumSMs * 4;
+  moe_ep_index_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, (cudaStream_t)stream>>>(
+      all_offs, world, rank, E, E / world, top_idx, row_of, padded_offs, n_pairs, row_base, own_offs, pair_peer, pair_row);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_peer_barrier(void* const* flag_ptrs, int world, int rank, int epoch, void* stream) {
+  if (flag_ptrs == nullptr || world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return B200Q_ERR_INVALID_ARG;
+  PeerFlags flags = {};
+  for (int i = 0; i < world; ++i) {
+    if (flag_ptrs[i] == nullptr) return B200Q_ERR_INVALID_ARG;
+    if (reinterpret_cast<uintptr_t>(flag_ptrs[i]) & 3) return B200Q_ERR_ALIGNMENT;
+    flags.f[i] = (int32_t*)flag_ptrs[i];
+  }
+  int rc = require_sm100();
+  if (rc) return rc;
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, world, rank, epoch);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_scatter_rows_peers(const void* x, int64_t ld, const void* w, const int32_t* pair_peer, const int32_t* pair_row, int64_t T,
+                                 int k, int64_t D, void* const* peer_y, int world, int64_t ldy, void* stream) {
+  if (x == nullptr || pair_peer == nullptr || pair_row == nullptr || peer_y == nullptr || T <= 0 || k <= 0 || D <= 0 || ld < D ||
+      ldy < D || world < 1 || world > kMaxPeers)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 7) || (ld & 7) || (ldy & 7)) return B200Q_ERR_SHAPE;
+  if (!aligned16(x)) return B200Q_ERR_ALIGNMENT;
+  PeerRowsW peers = {};
+  for (int i = 0; i < world; ++i) {
+    if (peer_y[i] == nullptr) return B200Q_ERR_INVALID_ARG;
+    if (!aligned16(peer_y[i])) return B200Q_ERR_ALIGNMENT;
+    peers.y[i] = (uint16_t*)peer_y[i];
+  }
+  int rc = require_sm100();
+  if (rc) return rc;
+  moe_scatter_rows_peers_kernel<<<row_grid(T * k * ((D + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(
+      (const uint16_t*)x, ld, (const uint16_t*)w, pair_peer, pair_row, T * k, k, D, peers, ldy);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_zero_pad_rows_bf16(const int32_t* src_of_row, const int32_t* num_tiles, int64_t padded_rows, int64_t D, void* buf,
+                                 int64_t ld, void* stream) {
+  if (src_of_row == nullptr || num_tiles == nullptr || buf == nullptr || padded_rows <= 0 || D <= 0 || ld < D) return B200Q_ERR_INVALID_ARG;
+  if ((D & 7) || (ld & 7) || (padded_rows & 127)) return B200Q_ERR_SHAPE;
+  if (!aligned16(buf)) return B200Q_ERR_ALIGNMENT;
+  int rc = require_sm100();
+  if (rc) return rc;
+  moe_zero_pad_rows_bf16_kernel<<<row_grid(padded_rows), 256, 0, (cudaStream_t)stream>>>(src_of_row, num_tiles, padded_rows, D,
+                                                                                        (uint16_t*)buf, ld);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int b200q_moe_pair_dots_peers(const void* dout, int64_t ld, void* const* peer_y, int world, int64_t ldy, const int32_t* pair_peer,
+                              const int32_t* pair_row, int64_t T, int k, int64_t D, float* dw, void* stream) {
+  if (dout == nullptr || peer_y == nullptr || pair_peer == nullptr || pair_row == nullptr || dw == nullptr || T <= 0 || k <= 0 ||
+      D <= 0 || ld < D || ldy < D || world < 1 || world > kMaxPeers)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 7) || (ld & 7) || (ldy & 7)) return B200Q_ERR_SHAPE;
+  if (!aligned16(dout)) return B200Q_ERR_ALIGNMENT;
+  PeerRows peers = {};
+  for (int i = 0; i < world; ++i) {
+    if (peer_y[i] == nullptr) return B200Q_ERR_INVALID_ARG;
+    if (!aligned16(peer_y[i])) return B200Q_ERR_ALIGNMENT;
+    peers.y[i] = (const uint16_t*)peer_y[i];
+  }
+  int rc = require_sm100();
+  if (rc) return rc;
+  moe_pair_dots_peers_kernel<<<row_grid(T * k), 256, 0, (cudaStream_t)stream>>>((const uint16_t*)dout, ld, peers, ldy, pair_peer, pair_row,
+                                                                               T * k, k, D, dw);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -509,6 +509,8 @@ struct TileSrc {
   const uint16_t* y;       // SCALED_GATHER, optional: expert outputs [rows, cols]; <dout[token], y[row]> per row and
   int64_t ldy;             //                column tile goes to dot_partial[column tile][row] (the routing weights' gradient)
   float* dot_partial;
+  const int32_t* live_tiles;   // optional (device): only the first *live_tiles 128-row tiles are processed (the rows of the
+                               // padded expert-sorted layout that are in use); the outputs past them are left untouched
 };
 
 template <int SRC, bool WIDE>
@@ -596,6 +598,7 @@ mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __r
   const int64_t width = NT == 2 ? src.I : cols;
   const int tid = threadIdx.x;
   const int64_t c0 = (int64_t)blockIdx.x * kDT, r0 = (int64_t)blockIdx.y * kDT;
+  if (src.live_tiles != nullptr && r0 >= ((int64_t)__ldg(src.live_tiles) << 7)) return;      // CTA-uniform: kDT == 128
   const int64_t nblk_r = cols >> 5, kt_r = (nblk_r + 3) >> 2;
 
 #pragma unroll
@@ -1085,7 +1088,7 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
 }
 
 int b200q_quantize_mxfp8_dual(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt, void* codes_row, void* sf_row,
-                              void* codes_col, void* sf_col, int sf_layout, void* stream) {
+                              void* codes_col, void* sf_col, int sf_layout, const int32_t* num_tiles, void* stream) {
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes_row == nullptr || sf_row == nullptr || codes_col == nullptr || sf_col == nullptr ||
@@ -1098,7 +1101,7 @@ int b200q_quantize_mxfp8_dual(const void* x, int64_t rows, int64_t cols, int64_t
   if ((rc = zero_sf_pads(sf_row, rows, cols / 32, sf_layout, st))) return rc;
   if ((rc = zero_sf_pads(sf_col, cols, rows / 32, sf_layout, st))) return rc;
   TileSrc src = {};
-  src.x = (const uint16_t*)x; src.ld = ld;
+  src.x = (const uint16_t*)x; src.ld = ld; src.live_tiles = num_tiles;
   return launch_mx_tile_quant<SRC_PLAIN>(src, rows_32B_aligned(x, ld), rows, cols, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row,
                                          (uint8_t*)codes_col, (uint8_t*)sf_col, sf_layout, st);
 }
@@ -1112,7 +1115,8 @@ static int check_dual_out(void* codes_row, void* sf_row, void* codes_col, void* 
 }
 
 int b200q_moe_gather_quantize_dual(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row, int64_t padded_rows, int fmt,
-                                   void* codes_row, void* sf_row, void* codes_col, void* sf_col, void* stream) {
+                                   void* codes_row, void* sf_row, void* codes_col, void* sf_col, const int32_t* num_tiles,
+                                   void* stream) {
   int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
   if (rc) return rc;
   if (x == nullptr || src_of_row == nullptr || D <= 0 || ld < D || padded_rows <= 0) return B200Q_ERR_INVALID_ARG;
@@ -1120,7 +1124,7 @@ int b200q_moe_gather_quantize_dual(const void* x, int64_t D, int64_t ld, const i
   if (!aligned16(x)) return B200Q_ERR_ALIGNMENT;
   if ((rc = require_sm100())) return rc;
   TileSrc src = {};
-  src.x = (const uint16_t*)x; src.ld = ld; src.index = src_of_row;
+  src.x = (const uint16_t*)x; src.ld = ld; src.index = src_of_row; src.live_tiles = num_tiles;
   return launch_mx_tile_quant<SRC_GATHER>(src, rows_32B_aligned(x, ld), padded_rows, D, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row,
                                           (uint8_t*)codes_col, (uint8_t*)sf_col, B200Q_SF_SWIZZLE_128x4, (cudaStream_t)stream);
 }
@@ -1160,7 +1164,7 @@ int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, con
 }
 
 int b200q_swiglu_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, int fmt, void* codes_row, void* sf_row,
-                               void* codes_col, void* sf_col, void* stream) {
+                               void* codes_col, void* sf_col, const int32_t* num_tiles, void* stream) {
   int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
   if (rc) return rc;
   if (g == nullptr || rows <= 0 || I <= 0 || ldg < 2 * I) return B200Q_ERR_INVALID_ARG;
@@ -1168,14 +1172,15 @@ int b200q_swiglu_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t l
   if (!aligned16(g)) return B200Q_ERR_ALIGNMENT;
   if ((rc = require_sm100())) return rc;
   TileSrc src = {};
-  src.x = (const uint16_t*)g; src.ld = ldg; src.I = I;
+  src.x = (const uint16_t*)g; src.ld = ldg; src.I = I; src.live_tiles = num_tiles;
   return launch_mx_tile_quant<SRC_SWIGLU>(src, rows_32B_aligned(g, ldg) && (I & 15) == 0, rows, I, fmt, (uint8_t*)codes_row,
                                           (uint8_t*)sf_row, (uint8_t*)codes_col, (uint8_t*)sf_col, B200Q_SF_SWIZZLE_128x4,
                                           (cudaStream_t)stream);
 }
 
 int b200q_swiglu_backward_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, const void* dh, int64_t lddh, int fmt,
-                                        void* codes_row, void* sf_row, void* codes_col, void* sf_col, void* stream) {
+                                        void* codes_row, void* sf_row, void* codes_col, void* sf_col, const int32_t* num_tiles,
+                                        void* stream) {
   int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
   if (rc) return rc;
   if (g == nullptr || dh == nullptr || rows <= 0 || I <= 0 || ldg < 2 * I || lddh < I) return B200Q_ERR_INVALID_ARG;
@@ -1183,7 +1188,7 @@ int b200q_swiglu_backward_quantize_dual(const void* g, int64_t rows, int64_t I, 
   if (!aligned16(g) || !aligned16(dh)) return B200Q_ERR_ALIGNMENT;
   if ((rc = require_sm100())) return rc;
   TileSrc src = {};
-  src.x = (const uint16_t*)g; src.ld = ldg; src.I = I; src.dh = (const uint16_t*)dh; src.lddh = lddh;
+  src.x = (const uint16_t*)g; src.ld = ldg; src.I = I; src.dh = (const uint16_t*)dh; src.lddh = lddh; src.live_tiles = num_tiles;
   return launch_mx_tile_quant<SRC_SWIGLU_BWD>(src, rows_32B_aligned(g, ldg) && rows_32B_aligned(dh, lddh) && (I & 15) == 0, rows, 2 * I,
                                               fmt, (uint8_t*)codes_row, (uint8_t*)sf_row, (uint8_t*)codes_col, (uint8_t*)sf_col,
                                               B200Q_SF_SWIZZLE_128x4, (cudaStream_t)stream);

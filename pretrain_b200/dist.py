@@ -290,17 +290,26 @@ def ep_combine(y: torch.Tensor, state: DispatchState, top_weights: torch.Tensor,
 
 
 class FusedExpertParallel:
-    """Expert-parallel MoE forward inside one NVLink domain with the exchange done by the kernels
-    themselves: the dispatch is the permute's gather + MXFP8 kernel storing each routed row straight
-    into the buffer of the rank that owns its expert, the combine is the unpermute kernel loading the
-    expert outputs in place from their owners.  The only collectives left are one all-gather of the
-    per-expert counts (E integers per rank) and two stream-ordered rendezvous.
+    """Expert-parallel MoE inside one NVLink domain with the exchange done by the kernels themselves: the dispatch
+    stores each routed row straight into the buffer of the rank that owns its expert, the combine loads the expert outputs
+    in place from their owners.  Per call there is ONE collective, an all-gather of the per-expert counts (E integers per
+    rank); the phases are ordered by a flag barrier in peer-mapped memory (b200q_peer_barrier: bounded waits, no NCCL),
+    and every index table - where my rows start at each owner, the segment ends of my own experts, owner and row of each
+    routed pair - comes from one kernel (b200q_moe_ep_index).
 
-    Buffers are symmetric memory sized for `capacity_rows` received rows per rank (default: every
-    routed row of every rank).  Results equal the single-GPU block on the concatenated tokens bit
-    for bit when the ranks hold consecutive token ranges."""
+    ``forward`` is the gradient-free path (MXFP8 codes + scale factors on the wire, SwiGLU in the first GEMM's epilogue).
+    ``train`` is differentiable: bf16 rows on the wire (an owner needs both MXFP8 directions of what it receives, and the
+    transposed one cannot be made by the senders), the owner's four backward GEMMs in MXFP8 as on one GPU, the output
+    gradient scattered to the owners and the input gradient combined back the same way.
 
-    def __init__(self, tokens_per_rank: int, top_k: int, d_model: int, n_experts: int, group=None, capacity_rows: int | None = None):
+    Buffers are symmetric memory sized for `capacity_rows` received rows per rank (default: every routed row of every
+    rank, which cannot overflow; a smaller capacity is checked on the host every call).  One instance serves one layer:
+    ``train`` keeps the expert outputs in its buffer until the matching backward has run.  Results equal the single-GPU
+    block on the concatenated tokens bit for bit when the ranks hold consecutive token ranges (the routing weights'
+    gradient, a dot product summed in another order, within fp32 rounding)."""
+
+    def __init__(self, tokens_per_rank: int, top_k: int, d_model: int, n_experts: int, group=None, capacity_rows: int | None = None,
+                 training: bool = False):
         import torch.distributed._symmetric_memory as symm
         from . import ops
         self.group = group if group is not None else dist.group.WORLD
@@ -312,51 +321,137 @@ class FusedExpertParallel:
         self.rows, self.check_capacity = rows, capacity_rows is not None       # the default capacity cannot overflow
         self.cap = ops.moe_padded_rows(rows, self.e_local)
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.codes = symm.empty((self.cap, d_model), dtype=torch.uint8, device=dev)
-        self.sf = symm.empty((ops.sf_bytes(self.cap, d_model // 32),), dtype=torch.uint8, device=dev)
-        self.y = symm.empty((self.cap, d_model), dtype=torch.bfloat16, device=dev)
-        hs = [symm.rendezvous(b, self.group) for b in (self.codes, self.sf, self.y)]
-        self.codes_ptrs, self.sf_ptrs, self.y_ptrs = ([int(p) for p in h.buffer_ptrs] for h in hs)
-        self._handles = hs
-        self._flag = torch.zeros(1, device=dev)
+        self._handles = []
+
+        def shared(shape, dtype):
+            buf = symm.empty(shape, dtype=dtype, device=dev)
+            h = symm.rendezvous(buf, self.group)
+            self._handles.append(h)
+            return buf, [int(p) for p in h.buffer_ptrs]
+
+        self.codes, self.codes_ptrs = shared((self.cap, d_model), torch.uint8)
+        self.sf, self.sf_ptrs = shared((ops.sf_bytes(self.cap, d_model // 32),), torch.uint8)
+        self.y, self.y_ptrs = shared((self.cap, d_model), torch.bfloat16)
+        self.flags, self.flag_ptrs = shared((8,), torch.int32)
+        self.training = training
+        if training:
+            self.xin, self.xin_ptrs = shared((self.cap, d_model), torch.bfloat16)     # received rows
+            self.dy, self.dy_ptrs = shared((self.cap, d_model), torch.bfloat16)       # received output gradients
+            self.da, self.da_ptrs = shared((self.cap, d_model), torch.bfloat16)       # input gradients of my experts' rows
+        self.flags.zero_()
+        self._epoch = 0
+        self._ones = None
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)                       # every rank's flags are zero before anyone signals
 
     def _rendezvous(self):
-        dist.all_reduce(self._flag, group=self.group)      # stream-ordered: every rank's stores before it have landed
+        """Stream-ordered: the kernels before it have stored, the kernels after it start once every rank has arrived."""
+        from . import ops
+        self._epoch += 1
+        ops.peer_barrier(self.flag_ptrs, self.rank, self._epoch)
+
+    def _tables(self, top_indices: torch.Tensor):
+        from . import ops
+        plan = ops.moe_permute_plan(top_indices, self.e)                                       # my rows in my own stable expert order
+        all_offs = torch.empty(self.world, self.e, dtype=torch.int32, device=top_indices.device)
+        dist.all_gather_into_tensor(all_offs, plan.offs, group=self.group)                      # [sender][global expert], cumulative
+        row_base, own_offs, pair_peer, pair_row = ops.moe_ep_index(all_offs, self.rank, top_indices, plan)
+        if self.check_capacity:                                                                 # host sync
+            counts = torch.diff(all_offs, dim=1, prepend=all_offs.new_zeros(self.world, 1)).sum(0)
+            need = ((counts + 127) // 128 * 128).view(self.world, self.e_local).sum(1).max()
+            if int(need) > self.cap or int(own_offs[-1]) > self.rows:
+                raise RuntimeError("received rows exceed the capacity of the expert-parallel buffers")
+        own = ops.moe_pad_plan(own_offs, self.rows)                                             # segment table of the experts I own
+        return plan, own, row_base, pair_peer, pair_row
 
     def forward(self, x: torch.Tensor, top_indices: torch.Tensor, top_weights: torch.Tensor, w_in_local: torch.Tensor,
                 w_down_local: torch.Tensor) -> torch.Tensor:
         from . import ops
         from .layers.mlp import _grouped_ffn_padded, silu_glu
-        t, k = top_indices.shape
-        counts = torch.bincount(top_indices.reshape(-1), minlength=self.e).to(torch.int32)
-        all_counts = torch.empty(self.world, self.e, dtype=torch.int32, device=x.device)
-        dist.all_gather_into_tensor(all_counts, counts, group=self.group)                       # [src rank][global expert]
-        # layout of every owner's buffer: experts' segments padded to 128 rows, senders in rank order inside a segment
-        totals = all_counts.sum(0)
-        padded = (totals + 127) // 128 * 128
-        seg_start = (padded.view(self.world, self.e_local).cumsum(1) - padded.view(self.world, self.e_local)).reshape(-1)
-        before_me = all_counts[: self.rank].sum(0)
-        row_base = (seg_start + before_me).to(torch.int32)
-        if self.check_capacity and int(padded.view(self.world, self.e_local).sum(1).max()) > self.cap:     # host sync
-            raise RuntimeError("received rows exceed the capacity of the expert-parallel buffers")
-        # my rows leave in my own stable expert order
-        plan = ops.moe_permute_plan(top_indices, self.e)
-        # what I own: segment table of my experts
-        my_totals = totals.view(self.world, self.e_local)[self.rank]
-        own = ops.moe_pad_plan(my_totals.cumsum(0).to(torch.int32), self.rows)
+        plan, own, row_base, pair_peer, pair_row = self._tables(top_indices)
         ops.moe_zero_pad_rows(own, self.d, self.codes, self.sf)
         ops.moe_dispatch_peers(x.to(torch.bfloat16), plan, row_base, self.e_local, self.codes_ptrs, self.sf_ptrs)
         self._rendezvous()
         _grouped_ffn_padded(self.codes, self.sf, own, w_in_local.to(torch.bfloat16), w_down_local.to(torch.bfloat16), silu_glu, True,
                             out=self.y)                        # the second GEMM writes where the peers will read
         self._rendezvous()
-        # where every (token, slot) pair's output row lives
-        flat_e = top_indices.reshape(-1)
-        pair_peer = (flat_e // self.e_local).to(torch.int32)
-        pair_row = (row_base.long()[flat_e] + plan.row_of.long() - plan.padded_offs.long()[flat_e]).to(torch.int32)
         out = ops.moe_combine_peers(self.y_ptrs, self.d, top_weights, pair_peer, pair_row, self.d)
         self._rendezvous()                                   # nobody overwrites y or the codes while a peer still reads them
         return out.to(x.dtype)
+
+    def train(self, x: torch.Tensor, top_indices: torch.Tensor, top_weights: torch.Tensor, w_in_local: torch.Tensor,
+              w_down_local: torch.Tensor) -> torch.Tensor:
+        """Differentiable forward: gradients flow to x, top_weights and this rank's expert weights."""
+        if not self.training:
+            raise RuntimeError("construct FusedExpertParallel(..., training=True) for the differentiable path")
+        return _FusedEPTrainFn.apply(x, top_weights, w_in_local, w_down_local, self, top_indices)
+
+
+class _FusedEPTrainFn(torch.autograd.Function):
+    """Forward and backward of the expert-parallel block (SwiGLU experts without biases): the single-GPU expert path
+    (layers/mlp.py::_ExpertFFN) with its gather and unpermute replaced by peer scatters and combines."""
+
+    @staticmethod
+    def forward(ctx, x, top_w, w_in, w_down, ep, top_indices):
+        from . import ops
+        from .layers.mlp import _expert_weight_copies
+        E4, SWZ = ops.E4M3, ops.SF_SWIZZLED
+        d, k = ep.d, ep.k
+        n1 = w_in.shape[1]
+        inter = n1 // 2
+        if d % 128 or n1 % 128 or inter % 32:
+            raise NotImplementedError("d_model and 2 * intermediate_size must be multiples of 128, intermediate_size of 32")
+        plan, own, row_base, pair_peer, pair_row = ep._tables(top_indices)
+        nt = own.num_tiles
+        ops.moe_zero_pad_rows_bf16(own, ep.xin)
+        ops.moe_scatter_rows_peers(x.to(torch.bfloat16), None, pair_peer, pair_row, k, ep.xin_ptrs, d)      # dispatch: bf16 rows
+        ep._rendezvous()
+        ar, asr, ac, asc = ops.quantize_mxfp8_dual(ep.xin, E4, SWZ, num_tiles=nt)
+        w1r, w1sr, w1c, w1sc = _expert_weight_copies(w_in, "dual")
+        w2r, w2sr, w2c, w2sc = _expert_weight_copies(w_down, "dual")
+        g = ops.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, own, n1)                                  # (cap, 2I) bf16, kept for backward
+        if inter % 128 == 0:
+            hr, hsr, hc, hsc = ops.swiglu_quantize_dual(g, E4, num_tiles=nt)
+        else:
+            hr, hsr, hc, hsc = ops.quantize_mxfp8_dual(ops.swiglu(g, False), E4, SWZ, num_tiles=nt)
+        ops.grouped_gemm_mxfp8(hr, hsr, w2r, w2sr, own, d, out=ep.y)                             # where the peers read
+        ep._rendezvous()
+        out = ops.moe_combine_peers(ep.y_ptrs, d, top_w, pair_peer, pair_row, d)
+        ep._rendezvous()
+        ctx.save_for_backward(top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, pair_peer, pair_row, own.offs, own.padded_offs,
+                              own.src_of_row, own.tile_expert, own.num_tiles)
+        ctx.ep, ctx.own_rows, ctx.inter = ep, own.padded_rows, inter
+        ctx.dtypes = (x.dtype, top_w.dtype, w_in.dtype, w_down.dtype)
+        return out.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from . import ops
+        (top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, pair_peer, pair_row, o_offs, o_poffs, o_src, o_tile, o_nt) = ctx.saved_tensors
+        ep, inter = ctx.ep, ctx.inter
+        E4, E5, SWZ = ops.E4M3, ops.E5M2, ops.SF_SWIZZLED
+        d, k = ep.d, ep.k
+        own = ops.MoEPlan()
+        own.offs, own.padded_offs, own.src_of_row, own.tile_expert, own.num_tiles = o_offs, o_poffs, o_src, o_tile, o_nt
+        own.row_of, own.padded_rows, own.n_experts = None, ctx.own_rows, ep.e_local
+        dout = dout.reshape(-1, d).to(torch.bfloat16).contiguous()
+        dw = ops.moe_pair_dots_peers(dout, ep.y_ptrs, d, pair_peer, pair_row, k)                 # <dout, y>: y still in the owners' buffers
+        ops.moe_zero_pad_rows_bf16(own, ep.dy)
+        ops.moe_scatter_rows_peers(dout, top_w, pair_peer, pair_row, k, ep.dy_ptrs, d)           # dy = w * dout, to the owners
+        ep._rendezvous()
+        dyr, dysr, dyc, dysc = ops.quantize_mxfp8_dual(ep.dy, E5, SWZ, num_tiles=o_nt)
+        dh = ops.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, own, inter, E5, E4)              # (cap, I)
+        dw2 = ops.grouped_gemm_mxfp8_wgrad(dyc, dysc, hc, hsc, own, E5, E4)                      # (E_local, D, I)
+        dgr, dgsr, dgc, dgsc = ops.swiglu_backward_quantize_dual(g, dh, E5, num_tiles=o_nt)
+        ops.grouped_gemm_mxfp8_dgrad(dgr, dgsr, w1c, w1sc, own, d, E5, E4, out=ep.da)            # where the peers read
+        dw1 = ops.grouped_gemm_mxfp8_wgrad(dgc, dgsc, ac, asc, own, E5, E4)                      # (E_local, 2I, D)
+        ep._rendezvous()
+        if ep._ones is None or ep._ones.shape != top_w.shape:
+            ep._ones = torch.ones(top_w.shape, dtype=torch.bfloat16, device=dout.device)
+        dx = ops.moe_combine_peers(ep.da_ptrs, d, ep._ones, pair_peer, pair_row, d)              # sum over the k slots
+        ep._rendezvous()
+        xd, twd, w1d, w2d = ctx.dtypes
+        return dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d), None, None
 
 
 def expert_ffn_local(rows: torch.Tensor, expert_ids: torch.Tensor, w_in: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:

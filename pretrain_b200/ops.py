@@ -139,9 +139,14 @@ def quantize_mxfp8(x: torch.Tensor, axis: int = 1, fmt=E4M3, layout: int = SF_SW
     return codes, sf
 
 
-def quantize_mxfp8_dual(x: torch.Tensor, fmt=E4M3, layout: int = SF_SWIZZLED):
+def _nt(num_tiles):
+    return num_tiles.data_ptr() if num_tiles is not None else None
+
+
+def quantize_mxfp8_dual(x: torch.Tensor, fmt=E4M3, layout: int = SF_SWIZZLED, num_tiles: torch.Tensor | None = None):
     """One pass over x (rows, cols): returns (codes_row, sf_row, codes_col, sf_col), equal to
-    quantize_mxfp8(x, 1) + quantize_mxfp8(x, 0).  rows % 32 == 0 and cols % 32 == 0."""
+    quantize_mxfp8(x, 1) + quantize_mxfp8(x, 0).  rows % 32 == 0 and cols % 32 == 0.  `num_tiles` (device int32):
+    only the first num_tiles 128-row tiles are processed, the rest of the outputs is left as allocated."""
     x = _mat(x)
     rows, cols = x.shape
     cr = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
@@ -149,7 +154,7 @@ def quantize_mxfp8_dual(x: torch.Tensor, fmt=E4M3, layout: int = SF_SWIZZLED):
     sr = torch.empty(sf_bytes(rows, cols // 32, layout), dtype=torch.uint8, device=x.device)
     sc = torch.empty(sf_bytes(cols, rows // 32, layout), dtype=torch.uint8, device=x.device)
     _lib.check(_lib.load().b200q_quantize_mxfp8_dual(x.data_ptr(), rows, cols, x.stride(0), fmt_of(fmt), cr.data_ptr(), sr.data_ptr(),
-                                                     cc.data_ptr(), sc.data_ptr(), layout, _stream()), "b200q_quantize_mxfp8_dual")
+                                                     cc.data_ptr(), sc.data_ptr(), layout, _nt(num_tiles), _stream()), "b200q_quantize_mxfp8_dual")
     return cr, sr, cc, sc
 
 
@@ -455,11 +460,11 @@ def gemm_mxfp8_swiglu(a_codes, a_sf, b_codes, b_sf, a_fmt=E4M3, b_fmt=E4M3):
     return h, sf
 
 
-def grouped_gemm_mxfp8_dgrad(a_codes, a_sf, bt_codes, bt_sf, plan: MoEPlan, n: int, a_fmt=E4M3, b_fmt=E4M3):
+def grouped_gemm_mxfp8_dgrad(a_codes, a_sf, bt_codes, bt_sf, plan: MoEPlan, n: int, a_fmt=E4M3, b_fmt=E4M3, out=None):
     """D[r] = A[r] . W_e(r) for the padded layout, where the weight stack (E*K, n) was quantized along
     axis 0 as a whole: bt_codes is (n, E*K).  A is (padded_rows, K)."""
     rows, k = a_codes.shape
-    d = torch.empty(rows, n, dtype=torch.bfloat16, device=a_codes.device)
+    d = _out(rows, n, a_codes.device, out)
     _lib.check(_lib.load().b200q_grouped_gemm_mxfp8_dgrad(a_codes.data_ptr(), fmt_of(a_fmt), a_sf.data_ptr(), bt_codes.data_ptr(),
                                                           fmt_of(b_fmt), bt_sf.data_ptr(), plan.tile_expert.data_ptr(),
                                                           plan.num_tiles.data_ptr(), rows, plan.n_experts, n, k, d.data_ptr(),
@@ -527,7 +532,7 @@ def _dual_outputs(rows: int, cols: int, device):
             torch.empty(cols, rows, dtype=torch.uint8, device=device), torch.empty(sf_bytes(cols, rows // 32), dtype=torch.uint8, device=device))
 
 
-def moe_gather_quantize_dual(x: torch.Tensor, plan: MoEPlan, fmt=E4M3):
+def moe_gather_quantize_dual(x: torch.Tensor, plan: MoEPlan, fmt=E4M3, live_only: bool = False):
     """quantize_mxfp8_dual(moe_gather(x, plan, False)) without the bf16 copy of the gathered rows (all
     padded_rows rows are defined: rows without a source are zero)."""
     x = _mat(x)
@@ -535,7 +540,7 @@ def moe_gather_quantize_dual(x: torch.Tensor, plan: MoEPlan, fmt=E4M3):
     cr, sr, cc, sc = _dual_outputs(plan.padded_rows, d, x.device)
     _lib.check(_lib.load().b200q_moe_gather_quantize_dual(x.data_ptr(), d, x.stride(0), plan.src_of_row.data_ptr(), plan.padded_rows,
                                                           fmt_of(fmt), cr.data_ptr(), sr.data_ptr(), cc.data_ptr(), sc.data_ptr(),
-                                                          _stream()), "b200q_moe_gather_quantize_dual")
+                                                          _nt(plan.num_tiles if live_only else None), _stream()), "b200q_moe_gather_quantize_dual")
     return cr, sr, cc, sc
 
 
@@ -572,24 +577,24 @@ def moe_unpermute_backward_quantize_dual(dout: torch.Tensor, weights: torch.Tens
     return (cr, sr, cc, sc) if dw is None else (cr, sr, cc, sc, dw)
 
 
-def swiglu_quantize_dual(g: torch.Tensor, fmt=E4M3):
+def swiglu_quantize_dual(g: torch.Tensor, fmt=E4M3, num_tiles: torch.Tensor | None = None):
     """quantize_mxfp8_dual(swiglu(g, False)) without the bf16 h."""
     g = _mat(g)
     rows, i2 = g.shape
     cr, sr, cc, sc = _dual_outputs(rows, i2 // 2, g.device)
     _lib.check(_lib.load().b200q_swiglu_quantize_dual(g.data_ptr(), rows, i2 // 2, g.stride(0), fmt_of(fmt), cr.data_ptr(), sr.data_ptr(),
-                                                      cc.data_ptr(), sc.data_ptr(), _stream()), "b200q_swiglu_quantize_dual")
+                                                      cc.data_ptr(), sc.data_ptr(), _nt(num_tiles), _stream()), "b200q_swiglu_quantize_dual")
     return cr, sr, cc, sc
 
 
-def swiglu_backward_quantize_dual(g: torch.Tensor, dh: torch.Tensor, fmt=E5M2):
+def swiglu_backward_quantize_dual(g: torch.Tensor, dh: torch.Tensor, fmt=E5M2, num_tiles: torch.Tensor | None = None):
     """quantize_mxfp8_dual(swiglu_backward(g, dh)) without the bf16 dg."""
     g, dh = _mat(g), _mat(dh)
     rows, i2 = g.shape
     cr, sr, cc, sc = _dual_outputs(rows, i2, g.device)
     _lib.check(_lib.load().b200q_swiglu_backward_quantize_dual(g.data_ptr(), rows, i2 // 2, g.stride(0), dh.data_ptr(), dh.stride(0),
                                                                fmt_of(fmt), cr.data_ptr(), sr.data_ptr(), cc.data_ptr(), sc.data_ptr(),
-                                                               _stream()), "b200q_swiglu_backward_quantize_dual")
+                                                               _nt(num_tiles), _stream()), "b200q_swiglu_backward_quantize_dual")
     return cr, sr, cc, sc
 
 
@@ -616,6 +621,52 @@ def moe_combine_peers(peer_y, ldy: int, weights: torch.Tensor, pair_peer: torch.
     _lib.check(_lib.load().b200q_moe_combine_peers(_ptr_array(peer_y), len(peer_y), ldy, w.data_ptr(), pair_peer.data_ptr(),
                                                    pair_row.data_ptr(), t, k, d, out.data_ptr(), _stream()), "b200q_moe_combine_peers")
     return out
+
+
+def moe_ep_index(all_offs: torch.Tensor, rank: int, top_indices: torch.Tensor, plan: MoEPlan):
+    """(row_base (E,), own_offs (E / world,), pair_peer (T*k,), pair_row (T*k,)), all int32: the expert-parallel index
+    tables of this rank from the gathered cumulative counts all_offs (world, E) and its own permute plan."""
+    world, e = all_offs.shape
+    idx = top_indices.contiguous().view(-1)
+    n = idx.numel()
+    i32 = dict(dtype=torch.int32, device=idx.device)
+    row_base, own_offs = torch.empty(e, **i32), torch.empty(e // world, **i32)
+    pair_peer, pair_row = torch.empty(n, **i32), torch.empty(n, **i32)
+    _lib.check(_lib.load().b200q_moe_ep_index(all_offs.data_ptr(), world, rank, e, idx.data_ptr(), plan.row_of.data_ptr(),
+                                              plan.padded_offs.data_ptr(), n, row_base.data_ptr(), own_offs.data_ptr(), pair_peer.data_ptr(),
+                                              pair_row.data_ptr(), _stream()), "b200q_moe_ep_index")
+    return row_base, own_offs, pair_peer, pair_row
+
+
+def peer_barrier(flag_ptrs, rank: int, epoch: int):
+    """Stream-ordered rendezvous of the ranks through flag words in peer-mapped memory (bounded wait)."""
+    _lib.check(_lib.load().b200q_peer_barrier(_ptr_array(flag_ptrs), len(flag_ptrs), rank, epoch, _stream()), "b200q_peer_barrier")
+
+
+def moe_scatter_rows_peers(x: torch.Tensor, weights: torch.Tensor | None, pair_peer: torch.Tensor, pair_row: torch.Tensor, k: int,
+                           peer_bufs, ldy: int):
+    """bf16 rows of x (T, D), scaled by the pairs' weights when given, stored into row pair_row[p] of rank pair_peer[p]'s buffer."""
+    x = _mat(x)
+    t, d = x.shape
+    w = weights.to(torch.bfloat16).contiguous() if weights is not None else None
+    _lib.check(_lib.load().b200q_moe_scatter_rows_peers(x.data_ptr(), x.stride(0), w.data_ptr() if w is not None else None,
+                                                        pair_peer.data_ptr(), pair_row.data_ptr(), t, k, d, _ptr_array(peer_bufs),
+                                                        len(peer_bufs), ldy, _stream()), "b200q_moe_scatter_rows_peers")
+
+
+def moe_zero_pad_rows_bf16(plan: MoEPlan, buf: torch.Tensor):
+    _lib.check(_lib.load().b200q_moe_zero_pad_rows_bf16(plan.src_of_row.data_ptr(), plan.num_tiles.data_ptr(), plan.padded_rows, buf.shape[1],
+                                                        buf.data_ptr(), buf.stride(0), _stream()), "b200q_moe_zero_pad_rows_bf16")
+
+
+def moe_pair_dots_peers(dout: torch.Tensor, peer_y, ldy: int, pair_peer: torch.Tensor, pair_row: torch.Tensor, k: int) -> torch.Tensor:
+    """dw (T, k) fp32 = <dout[t], y_owner[row of the pair]>, the rows read from their owners' buffers."""
+    dout = _mat(dout)
+    t, d = dout.shape
+    dw = torch.empty(t, k, dtype=torch.float32, device=dout.device)
+    _lib.check(_lib.load().b200q_moe_pair_dots_peers(dout.data_ptr(), dout.stride(0), _ptr_array(peer_y), len(peer_y), ldy, pair_peer.data_ptr(),
+                                                     pair_row.data_ptr(), t, k, d, dw.data_ptr(), _stream()), "b200q_moe_pair_dots_peers")
+    return dw
 
 
 def swiglu_backward(g: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:

@@ -100,3 +100,52 @@ def _ep_rank(rank, world, skew):
 @pytest.mark.parametrize("skew", [False, True])
 def test_expert_parallel_dispatch_combine(skew):
     _run(_ep_rank, 2, skew)
+
+
+def _ep_index_rank(rank, world, skew):
+    """The index tables of the fused expert-parallel path (the host restatement of b200q_moe_ep_index), with the count
+    exchange done over gloo: together the ranks' rows must tile every owner's expert segments exactly - no row claimed
+    twice, none left out, senders in rank order, each sender's rows in its own stable order."""
+    g = torch.Generator().manual_seed(11)
+    t, e, k = 200, 8, 2
+    logits = torch.randn(world * t, e, generator=g)
+    if skew:
+        logits[:, 4:] -= 1e9
+        logits[:, 1] -= 1e9
+    top_i, _ = R.router_topk(logits, k)
+    lo, hi, el = rank * t, (rank + 1) * t, e // world
+    mine = top_i[lo:hi]
+    offs, padded_offs, row_of = R.moe_padded_plan(mine, e)
+    all_offs = [torch.empty_like(offs) for _ in range(world)]
+    dist.all_gather(all_offs, offs)
+    all_offs = torch.stack(all_offs)
+    row_base, own_offs, pair_peer, pair_row = R.ep_index(all_offs, rank, mine, row_of, padded_offs)
+    # gather everyone's claims: (owner, row, global expert, sender, position in the sender's stable order)
+    pos = row_of.long() - padded_offs.long()[mine.reshape(-1)]
+    claim = torch.stack([pair_peer.long(), pair_row.long(), mine.reshape(-1), torch.full_like(pos, rank), pos], 1)
+    claims = [torch.empty_like(claim) for _ in range(world)]
+    dist.all_gather(claims, claim)
+    claims = torch.cat(claims)
+    own_lists = [torch.empty_like(own_offs) for _ in range(world)]
+    dist.all_gather(own_lists, own_offs)
+    for owner in range(world):
+        c = claims[claims[:, 0] == owner]
+        assert (c[:, 2] // el == owner).all()
+        assert c[:, 1].unique().numel() == c.shape[0]                           # no row claimed twice
+        ends = own_lists[owner].long()
+        counts = torch.diff(ends, prepend=ends.new_zeros(1))
+        start = 0
+        for j in range(el):
+            seg = c[c[:, 2] == owner * el + j]
+            assert seg.shape[0] == counts[j]                                       # every pair of the expert has a row
+            if seg.shape[0]:
+                seg = seg[seg[:, 1].argsort()]
+                assert torch.equal(seg[:, 1], start + torch.arange(seg.shape[0]))  # contiguous from the 128-aligned segment start
+                key = seg[:, 3] * (2 * world * t) + seg[:, 4]
+                assert (key[1:] > key[:-1]).all()                                  # rank order, then each sender's stable order
+            start += (int(counts[j]) + 127) // 128 * 128
+
+
+@pytest.mark.parametrize("skew", [False, True])
+def test_expert_parallel_index_tables_tile_the_owners_buffers(skew):
+    _run(_ep_index_rank, 2, skew)

@@ -861,3 +861,54 @@ def test_fake_kernels_of_the_moe_ops_describe_the_real_outputs(ops):
     check(T._grouped_gemm_mxfp8_wgrad, dyc, dysc, hc, hsc, plan.padded_offs, 1, 0)
     dh = T.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, plan, inter, 1, 0)
     check(T.swiglu_backward_quantize_dual, gu, dh, 1)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_expert_parallel_index_kernel_matches_its_restatement(ops, world):
+    """b200q_moe_ep_index against oracle.restate.ep_index, for every rank of a simulated group (the counts of the other
+    ranks are made up on the host; no second GPU is involved)."""
+    t, e, k = 777, 64, 4
+    g = torch.Generator().manual_seed(world)
+    logits = torch.randn(world * t, e, generator=g)
+    logits[:, 5] = -1e9
+    top_all, _ = R.router_topk(logits, k)
+    offs_all = torch.stack([R.moe_padded_plan(top_all[r * t:(r + 1) * t], e)[0] for r in range(world)])
+    for rank in sorted({0, world // 2, world - 1}):
+        mine = top_all[rank * t:(rank + 1) * t]
+        plan = ops.moe_permute_plan(mine.cuda(), e)
+        offs, padded_offs, row_of = R.moe_padded_plan(mine, e)
+        assert torch.equal(plan.offs.cpu(), offs) and torch.equal(plan.padded_offs.cpu(), padded_offs) and torch.equal(plan.row_of.cpu(), row_of)
+        got = ops.moe_ep_index(offs_all.cuda(), rank, mine.cuda(), plan)
+        want = R.ep_index(offs_all, rank, mine, row_of, padded_offs)
+        for a, b in zip(got, want):
+            assert torch.equal(a.cpu(), b)
+
+
+def test_peer_scatter_dots_and_barrier_on_one_rank(ops):
+    """The expert-parallel row movers with a group of one (every "peer" is this GPU): the scatter is the inverse of the
+    combine, the dot products are the routing weights' gradient, the flag barrier returns at once and stays clean."""
+    t, d, e, k = 512, 256, 8, 2
+    x, logits, _, _ = R.inputs_moe(t, d, e, k, 64, seed=4)
+    top_i, top_w = R.router_topk(logits, k)
+    x, top_i, top_w = x.cuda(), top_i.cuda(), top_w.cuda()
+    plan = ops.moe_permute_plan(top_i, e)
+    row_base, own_offs, pair_peer, pair_row = ops.moe_ep_index(plan.offs.view(1, e).contiguous(), 0, top_i, plan)
+    assert torch.equal(pair_row, plan.row_of) and (pair_peer == 0).all() and torch.equal(own_offs, plan.offs)
+    own = ops.moe_pad_plan(own_offs, t * k)
+    buf = torch.full((own.padded_rows, d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.moe_zero_pad_rows_bf16(own, buf)
+    ops.moe_scatter_rows_peers(x, None, pair_peer, pair_row, k, [buf.data_ptr()], d)
+    live = int(own.num_tiles.item()) * 128
+    assert torch.equal(buf[:live], ops.moe_gather(x, plan, False)[:live])                 # the same padded layout, pad rows zero
+    ops.moe_scatter_rows_peers(x, top_w, pair_peer, pair_row, k, [buf.data_ptr()], d)
+    want = (top_w.float().reshape(-1, 1) * x.float().repeat_interleave(k, 0)).bfloat16()
+    assert torch.equal(buf[plan.row_of.long()], want)
+    dots = ops.moe_pair_dots_peers(x, [buf.data_ptr()], d, pair_peer, pair_row, k)
+    ref = (x.float().repeat_interleave(k, 0) * want.float()).sum(1).view(t, k)
+    assert ((dots - ref).abs().max() / ref.abs().max()).item() < 1e-5
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    for epoch in (1, 2, 3):
+        ops.peer_barrier([flags.data_ptr()], 0, epoch)
+    torch.cuda.synchronize()
+    assert flags[0].item() == 3
+    ops.device_status()
