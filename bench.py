@@ -66,7 +66,7 @@ MOE_EXPERTS, MOE_TOPK = 64, 4
 NOMINAL_TFLOPS = {"mxfp8": 4500.0, "fp8": 4500.0, "int8": 4500.0, "nvfp4": 9000.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the ncu captures summarised
 # under profiles/ (null until captured for that workload)
-GEMM_DRAM_TRAFFIC = {"mxfp8_square_8192": 475.8e6, "nvfp4_square_8192": 273.4e6,
+GEMM_DRAM_TRAFFIC = {"mxfp8_square_8192": 386.3e6, "nvfp4_square_8192": 273.4e6,
                      "fp8_rowwise_linear_16384x2048x2048": 55.1e6}   # gemm_pair_kernel captures
 
 
@@ -1017,8 +1017,14 @@ def run_dense(args, kind, m, n, k, rank, world, local, config):
     for _ in range(warm):
         step()
     barrier()
+    if args.profile:
+        torch.cuda.profiler.start()
+        torch.cuda.nvtx.range_push("b200q timed region")
     with ClockSampler(local) as clk:
         block_ms = timed_blocks(lambda: [step() for _ in range(args.steps)], args.min_seconds, barrier, dist)
+    if args.profile:
+        torch.cuda.nvtx.range_pop()
+        torch.cuda.profiler.stop()
     ops.device_status()
     clocks = clk.summary()
     timed_region_s = sum(block_ms) * 1e-3
@@ -1333,6 +1339,9 @@ def main():
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
                     help="repeat the --steps-long block until this much device time has been timed; the median block is reported")
     ap.add_argument("--headline-only", action="store_true", help="skip the secondary kernels and the incumbent timings of the default line")
+    ap.add_argument("--profile", action="store_true",
+                    help="bracket the headline timed region with cudaProfilerStart / cudaProfilerStop and an NVTX range "
+                         "(for `ncu --profile-from-start off` / a timeline); numbers printed under a profiler are not bench values")
     args = ap.parse_args()
     kind, m, n, k = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))

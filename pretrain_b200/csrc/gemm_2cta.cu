@@ -79,6 +79,7 @@ struct PairParams {
   int b_along_k;                 // dgrad: B is [N, E*K]
   int sf_kt_b;                   // scale atoms per row group of B
   int64_t K;                     // contraction length per expert (bytes), dgrad's K offset unit
+  int raster_gm;                 // dense form: pair-tile rows per raster group
 };
 
 // Everything the roles of one CTA need to know about pair tile t.
@@ -95,8 +96,10 @@ struct PTile {
   bool live;           // this CTA owns output rows
 };
 
-__device__ __forceinline__ void pair_tile_coords(int t, int num_mp, int num_n, int& mp, int& n) {
-  constexpr int GM = 8;          // 8 pair tiles = 2048 rows per raster group
+// Raster: groups of GM pair-tile rows, inside a group the row index runs fastest.  The pairs that are resident together
+// then share GM tiles of A and about 74 / GM tiles of B through L2, and over a whole group A is read from DRAM once
+// and B once per group: the larger GM, the fewer re-reads of B, as long as the group's rows of A stay in L2.
+__device__ __forceinline__ void pair_tile_coords(int t, int num_mp, int num_n, int& mp, int& n, int GM = 8) {
   const int per_group = GM * num_n;
   const int g = t / per_group, r = t - g * per_group;
   const int first = g * GM;
@@ -111,7 +114,7 @@ __device__ __forceinline__ PTile get_ptile(const PairParams& p, int t, int total
   ti.k0 = 0; ti.nk = p.num_k; ti.bk0 = 0; ti.sfb_k0 = 0; ti.drow_off = 0; ti.zero = false;
   int mp;
   if (!GROUPED) {
-    pair_tile_coords(t, p.num_mp, p.num_n, mp, ti.n_blk);
+    pair_tile_coords(t, p.num_mp, p.num_n, mp, ti.n_blk, p.raster_gm);
     ti.row0 = mp * 256 + cta * BM;
     ti.live = true;                                   // rows beyond M are clipped by the epilogue
     ti.brow0 = ti.n_blk * PBN + cta * HALF_N;
@@ -427,6 +430,19 @@ bool pair_eligible(int64_t M, int64_t N, int64_t row_bytes, bool grouped) {
   return tiles >= kNumSMs / 2;     // measured faster than the one-CTA kernel from K = 384 up once the pairs are busy
 }
 
+// Pair-tile rows per raster group: as many as keep the group's rows of A (GM x 256 x row_bytes) within 32 MB, a quarter
+// of L2, between 4 and 32.  B200Q_RASTER_GM overrides it (experiments).
+int pair_raster_gm(int64_t row_bytes) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("B200Q_RASTER_GM");
+    forced = e != nullptr ? atoi(e) : 0;
+  }
+  if (forced > 0) return forced;
+  int64_t gm = ((int64_t)32 << 20) / (256 * (row_bytes > 0 ? row_bytes : 1));
+  return (int)(gm < 4 ? 4 : (gm > 32 ? 32 : gm));
+}
+
 template <int KIND, int EPI>
 int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, const GemmParams& gp, cudaStream_t st) {
   using C = pair::PCfg<KIND>;
@@ -463,6 +479,7 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   p.num_k = (int)((row_bytes + BKB - 1) / BKB);
   p.sf_kt = sf_kt;
   p.glu = gp.glu;
+  p.raster_gm = pair_raster_gm(row_bytes);
   B200Q_CUDA(ensure_dynamic_smem(gemm_pair_kernel<KIND, EPI>, C::SMEM_BYTES));
   const int tiles = p.num_mp * p.num_n, pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
   B200Q_CUDA(launch_pdl(gemm_pair_kernel<KIND, EPI>, dim3(2 * pairs), dim3(gemm_threads(EPI)), C::SMEM_BYTES, st, ma, mb, msa, msb, md, p));

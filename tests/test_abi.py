@@ -59,3 +59,20 @@ def test_ops_refuse_cpu_tensors(lib_path):
     from pretrain_b200 import ops
     with pytest.raises(RuntimeError):
         ops.quantize_mxfp8(torch.zeros(4, 32, dtype=torch.bfloat16))
+
+
+def test_nvtx_ranges_around_every_entry_point(lib_path, monkeypatch):
+    """B200Q_NVTX=1: each C-ABI call runs inside an NVTX range named after the entry point."""
+    import torch
+    from pretrain_b200 import _lib
+    seen = []
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: seen.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: seen.append(("pop", None)))
+    monkeypatch.setenv("B200Q_NVTX", "1")
+    monkeypatch.setattr(_lib, "_lib", None)
+    lib = _lib.load()
+    assert lib.b200q_sf_bytes(128, 4, 1) == 512
+    assert lib.b200q_status_string(0) == b"ok"
+    assert seen == [("push", "b200q_sf_bytes"), ("pop", None), ("push", "b200q_status_string"), ("pop", None)]
+    assert all(hasattr(lib, n) for n in _lib.SIGNATURES)
+    monkeypatch.setattr(_lib, "_lib", None)                    # later tests load the plain library again
