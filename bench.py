@@ -1305,8 +1305,7 @@ def expert_parallel_record(dist, rank, world, barrier, rank_max, total_tokens=16
     with torch.no_grad():
         nccl_ms = timed(lambda: D.expert_parallel_moe(x, top_i, top_w, w1l, w2l, e))
         rec.update(nccl_all_to_all_ms=nccl_ms, nccl_tflops=flops / (nccl_ms * 1e-3) / 1e12)
-        cap = min(world * t * k, 2 * t * k)                  # twice the balanced share per rank (checked every call)
-        ep = D.FusedExpertParallel(t, k, d, e, capacity_rows=cap if world > 2 else None, training=True)
+        ep = D.FusedExpertParallel(t, k, d, e, training=True)     # default capacity: cannot overflow, no host check per call
         fused_ms = timed(lambda: ep.forward(x, top_i, top_w, w1l, w2l))
         rec.update(fused_ms=fused_ms, fused_tflops=flops / (fused_ms * 1e-3) / 1e12,
                    fused="dispatch = gather + MXFP8 kernel storing into the owners' buffers, combine = unpermute kernel loading from "

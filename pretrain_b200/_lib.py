@@ -78,6 +78,7 @@ SIGNATURES = {
     # test hooks (process-wide kernel-choice overrides; see the end of include/b200q.h)
     "b200q_debug_set_gemm_bn": (_int, [_int]),
     "b200q_debug_set_gemm_pair": (_int, [_int]),
+    "b200q_debug_set_gemm_bstat": (_int, [_int]),
     "b200q_debug_expire_wait": (_int, [_int, _vp]),
 }
 

@@ -3,4 +3,5 @@
 #include "quantize.cu"
 #include "gemm.cu"
 #include "gemm_2cta.cu"
+#include "gemm_bstat.cu"
 #include "moe.cu"
