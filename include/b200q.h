@@ -479,10 +479,13 @@ int b200q_moe_pair_of_row(const int32_t* row_of, int64_t n_pairs, int64_t padded
  *   b200q_debug_set_gemm_bn(bn):    N tile width of the one-CTA kernel, 128 / 192 / 256; 0 = by shape.
  *   b200q_debug_set_gemm_pair(mode): 1 = CTA-pair kernel whenever the shape allows, -1 = never, 0 = by shape.
  *   b200q_debug_set_gemm_bstat(mode): grouped fprop / dgrad GEMMs with K <= 768 on the kernel that keeps the expert's
- *                                    weight tile in shared memory: 1 = whenever the shape allows, -1 = never, 0 = by shape and size. */
+ *                                    weight tile in shared memory: 1 = whenever the shape allows, -1 = never, 0 = by shape and size.
+ *   b200q_debug_set_gemm_rowstat(mode): the same GEMMs on the CTA-pair kernel that keeps the rows of A in shared memory
+ *                                    (tried before the one above): 1 = whenever the shape allows, -1 = never, 0 = by shape and size. */
 int b200q_debug_set_gemm_bn(int bn);
 int b200q_debug_set_gemm_pair(int mode);
 int b200q_debug_set_gemm_bstat(int mode);
+int b200q_debug_set_gemm_rowstat(int mode);
 /* Runs a one-thread kernel whose bounded wait cannot succeed (an mbarrier nobody arrives on), with a limit of
  * `iterations` polls (1 .. 100000, i.e. milliseconds): the kernel gives up, records a non-zero status and returns,
  * exactly as the GEMM kernels' waits do after their ~1 s limit.  The next b200q_device_status() returns

@@ -79,6 +79,7 @@ SIGNATURES = {
     "b200q_debug_set_gemm_bn": (_int, [_int]),
     "b200q_debug_set_gemm_pair": (_int, [_int]),
     "b200q_debug_set_gemm_bstat": (_int, [_int]),
+    "b200q_debug_set_gemm_rowstat": (_int, [_int]),
     "b200q_debug_expire_wait": (_int, [_int, _vp]),
 }
 

@@ -4,4 +4,5 @@
 #include "gemm.cu"
 #include "gemm_2cta.cu"
 #include "gemm_bstat.cu"
+#include "gemm_rowstat.cu"
 #include "moe.cu"

@@ -180,6 +180,12 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
+// two floats rounded to nearest-even bf16, `lo` in the low half
+__device__ __forceinline__ uint32_t pack_bf16_rn(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 
 // One MXFP8 block held by one thread: 32 bf16 in four 16-byte words -> 32 code bytes in o[0..7];
 // returns the block's unbiased scale exponent.
@@ -203,22 +209,34 @@ __device__ __forceinline__ int mx_quant_block32(const uint4 (&v)[4], uint32_t (&
   return e;
 }
 
-__device__ __forceinline__ float bf16_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
-
 // h = bf16(bf16(silu(gate)) * up) for 8 (gate, up) pairs packed as bf16: the roundings of the
-// reference's bf16 tensor ops.  silu(x) = x / (1 + e^-x) with the hardware exponential and
-// reciprocal: within 2 fp32 ulp, far inside the bf16 rounding that follows.
+// reference's bf16 tensor ops.  silu(x) = x * (1 / (1 + e^-x)) with the hardware exponential and
+// reciprocal: within 2 fp32 ulp, far inside the bf16 rounding that follows.  Both roundings are packed
+// instructions: one conversion rounds two silu values to bf16, and the bf16 x bf16 product (exact in
+// fp32, 16 significant bits) is rounded once by the packed multiply, as the fp32 multiply + conversion
+// would.  That leaves the exponential and the reciprocal as the only work for the special-function
+// unit, which bounds this arithmetic (a scalar float -> bf16 conversion runs there too).
+// 1 / (1 + e^-x) in exactly five instructions' worth of arithmetic with silu below: the flush-to-zero forms of the
+// hardware exponential and reciprocal need none of the range fix-ups that the compiler wraps around __expf / __fdividef
+// (a third of this arithmetic's instructions), and give the same bits wherever those are specified: e^-x below 2^-126
+// vanishes against the 1 either way, and a denominator above 2^126 gives a zero quotient in both.
+__device__ __forceinline__ float sigmoid_fast(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  return r;
+}
+
 __device__ __forceinline__ uint4 swiglu8(const uint4& vg, const uint4& vu) {
-  float a[8], b[8];
+  float a[8];
   unpack8(vg, a);
-  unpack8(vu, b);
+  const uint32_t u[4] = {vu.x, vu.y, vu.z, vu.w};
   uint32_t h[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float s0 = bf16_round(__fdividef(a[2 * i], 1.f + __expf(-a[2 * i])));
-    const float s1 = bf16_round(__fdividef(a[2 * i + 1], 1.f + __expf(-a[2 * i + 1])));
-    __nv_bfloat162 p = __floats2bfloat162_rn(s0 * b[2 * i], s1 * b[2 * i + 1]);
-    h[i] = *reinterpret_cast<uint32_t*>(&p);
+    const float s0 = a[2 * i] * sigmoid_fast(a[2 * i]);
+    const float s1 = a[2 * i + 1] * sigmoid_fast(a[2 * i + 1]);
+    h[i] = mul_bf16x2(pack_bf16_rn(s0, s1), u[i]);
   }
   return make_uint4(h[0], h[1], h[2], h[3]);
 }
@@ -237,7 +255,7 @@ __device__ __forceinline__ void swiglu_bwd8(const uint4& vg, const uint4& vu, co
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const float x = a[2 * i + j];
-      const float sg = __fdividef(1.f, 1.f + __expf(-x));
+      const float sg = sigmoid_fast(x);
       pu[j] = d[2 * i + j] * x * sg;
       pg[j] = d[2 * i + j] * b[2 * i + j] * sg * (1.f + x * (1.f - sg));
     }

@@ -547,6 +547,10 @@ int launch_pair_grouped(const void* A, const void* B, const OutSpec& D, int64_t 
 constexpr int kBstatNotApplicable = -1000;
 template <int EPI>
 int try_bstat(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, const GemmParams& p, cudaStream_t st);
+// Row-stationary pair form of the same GEMMs (gemm_rowstat.cu, same translation unit)
+constexpr int kRowstatNotApplicable = -1001;
+template <int EPI>
+int try_rowstat(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, const GemmParams& p, cudaStream_t st);
 
 template <int KIND>
 int dispatch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t b_rows, const GemmParams& p, cudaStream_t st) {
@@ -834,6 +838,8 @@ int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const vo
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   p.M = padded_rows; p.N = N; p.K = K; p.tile_expert = tile_expert; p.num_tiles = num_tiles; p.n_experts = E;
+  rc = try_rowstat<EPI_BF16>(A, B, one_output(D), ldd, (int64_t)E * N, p, (cudaStream_t)stream);
+  if (rc != kRowstatNotApplicable) return rc;
   rc = try_bstat<EPI_BF16>(A, B, one_output(D), ldd, (int64_t)E * N, p, (cudaStream_t)stream);
   if (rc != kBstatNotApplicable) return rc;
   if (pair_grouped_eligible(p)) return launch_pair_grouped<EPI_BF16>(A, B, one_output(D), ldd, (int64_t)E * N, p, (cudaStream_t)stream);
@@ -857,6 +863,8 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
   int rc = prepare_glu(&p, A, sfA, B, sfB, a_fmt, b_fmt, padded_rows, N, K, H, ldh, sfH, true, (cudaStream_t)stream);
   if (rc) return rc;
   p.tile_expert = tile_expert; p.num_tiles = num_tiles; p.n_experts = E;
+  rc = try_rowstat<EPI_GLU>(A, B, OutSpec{}, 0, (int64_t)E * N, p, (cudaStream_t)stream);
+  if (rc != kRowstatNotApplicable) return rc;
   rc = try_bstat<EPI_GLU>(A, B, OutSpec{}, 0, (int64_t)E * N, p, (cudaStream_t)stream);
   if (rc != kBstatNotApplicable) return rc;
   if (pair_grouped_eligible(p)) return launch_pair_grouped<EPI_GLU>(A, B, OutSpec{}, 0, (int64_t)E * N, p, (cudaStream_t)stream);
@@ -885,7 +893,9 @@ int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const
 // the grouped backward forms: CTA pairs when the shape allows, else the one-CTA kernel with the tile width of the cost model
 static int dispatch_one_cta_mx(const void* A, const void* B, void* D, int64_t ldd, int64_t b_rows, const GemmParams& p,
                                cudaStream_t st) {
-  const int rc = try_bstat<EPI_BF16>(A, B, one_output(D), ldd, b_rows, p, st);      // dgrad with a short K; never the ragged wgrad
+  int rc = try_rowstat<EPI_BF16>(A, B, one_output(D), ldd, b_rows, p, st);          // dgrad with a short K; never the ragged wgrad
+  if (rc != kRowstatNotApplicable) return rc;
+  rc = try_bstat<EPI_BF16>(A, B, one_output(D), ldd, b_rows, p, st);
   if (rc != kBstatNotApplicable) return rc;
   if (pair_grouped_eligible(p)) return launch_pair_grouped<EPI_BF16>(A, B, one_output(D), ldd, b_rows, p, st);
   // ragged form: every expert has its own output tiles and (on average) its share of the K range

@@ -159,6 +159,68 @@ __device__ __forceinline__ PTile get_ptile(const PairParams& p, int t, int total
   return ti;
 }
 
+// The (first tile, pair-tile prefix) table of the experts, built by all THREADS threads of a CTA in shared memory:
+// g_first[e] = first 128-row tile of expert e (an expert without tiles starts where the next one does; entry E = tiles in
+// use), g_pairs[e] = pair tiles of the experts before e (entry E = their total).  Returns the tiles in use.
+template <int THREADS>
+__device__ __forceinline__ int build_expert_pairs(const int32_t* tile_expert, const int32_t* num_tiles, int num_m128, int n_experts,
+                                                  int* g_first, int* g_pairs) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int live_tiles = __ldg(num_tiles);
+  live_tiles = live_tiles < num_m128 ? live_tiles : num_m128;
+  for (int e = threadIdx.x; e <= n_experts; e += THREADS) g_first[e] = e == n_experts ? live_tiles : 0x7fffffff;
+  __syncthreads();
+  for (int t = threadIdx.x; t < live_tiles; t += THREADS) {
+    const int e = __ldg(tile_expert + t), prev = t > 0 ? __ldg(tile_expert + t - 1) : -1;
+    if (e != prev && e >= 0 && e < n_experts) g_first[e] = t;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // suffix minimum (an expert without tiles starts where the next one does), pair-tile counts, their prefix sums
+    constexpr int PER = kPairMaxExperts / 32;
+    const int E = n_experts, base = lane * PER;
+    int v[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) v[i] = base + i < E ? g_first[base + i] : live_tiles;
+#pragma unroll
+    for (int i = PER - 2; i >= 0; --i) v[i] = v[i] < v[i + 1] ? v[i] : v[i + 1];
+    int suf = v[0];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int x = __shfl_down_sync(0xffffffffu, suf, o);
+      if (lane + o < 32 && x < suf) suf = x;
+    }
+    int later = __shfl_down_sync(0xffffffffu, suf, 1);       // minimum over all later lanes
+    if (lane == 31) later = live_tiles;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) v[i] = v[i] < later ? v[i] : later;
+    int next0 = __shfl_down_sync(0xffffffffu, v[0], 1);
+    if (lane == 31) next0 = live_tiles;
+    int cnt[PER], sum = 0;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int end = i + 1 < PER ? v[i + 1] : next0;
+      cnt[i] = base + i < E ? (end - v[i] + 1) >> 1 : 0;
+      sum += cnt[i];
+    }
+    int inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int x = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += x;
+    }
+    int run = inc - sum;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      if (base + i < E) { g_first[base + i] = v[i]; g_pairs[base + i] = run; }
+      run += cnt[i];
+    }
+    if (lane == 31) g_pairs[E] = inc;
+  }
+  __syncthreads();
+  return live_tiles;
+}
+
 }  // namespace pair
 
 template <int KIND, int EPI, bool GROUPED = false>
@@ -186,61 +248,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   int* g_pairs = g_first + pair::kPairMaxExperts + 1;                   //          pair tiles before every expert (+ total)
   const bool by_expert = GROUPED && p.tile_expert != nullptr;
   if (GROUPED) grid_dependency_wait();            // the grouped forms read the permute plan's tables right away
-  int live_tiles = 0;
-  if (by_expert) {
-    live_tiles = __ldg(p.num_tiles);
-    live_tiles = live_tiles < p.num_m128 ? live_tiles : p.num_m128;
-    for (int e = threadIdx.x; e <= p.n_experts; e += gemm_threads(EPI)) g_first[e] = e == p.n_experts ? live_tiles : 0x7fffffff;
-    __syncthreads();
-    for (int t = threadIdx.x; t < live_tiles; t += gemm_threads(EPI)) {
-      const int e = __ldg(p.tile_expert + t), prev = t > 0 ? __ldg(p.tile_expert + t - 1) : -1;
-      if (e != prev && e >= 0 && e < p.n_experts) g_first[e] = t;
-    }
-    __syncthreads();
-    if (warp == 0) {
-      // suffix minimum (an expert without tiles starts where the next one does), pair-tile counts, their prefix sums
-      constexpr int PER = pair::kPairMaxExperts / 32;
-      const int E = p.n_experts, base = lane * PER;
-      int v[PER];
-#pragma unroll
-      for (int i = 0; i < PER; ++i) v[i] = base + i < E ? g_first[base + i] : live_tiles;
-#pragma unroll
-      for (int i = PER - 2; i >= 0; --i) v[i] = v[i] < v[i + 1] ? v[i] : v[i + 1];
-      int suf = v[0];
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int x = __shfl_down_sync(0xffffffffu, suf, o);
-        if (lane + o < 32 && x < suf) suf = x;
-      }
-      int later = __shfl_down_sync(0xffffffffu, suf, 1);       // minimum over all later lanes
-      if (lane == 31) later = live_tiles;
-#pragma unroll
-      for (int i = 0; i < PER; ++i) v[i] = v[i] < later ? v[i] : later;
-      int next0 = __shfl_down_sync(0xffffffffu, v[0], 1);
-      if (lane == 31) next0 = live_tiles;
-      int cnt[PER], sum = 0;
-#pragma unroll
-      for (int i = 0; i < PER; ++i) {
-        const int end = i + 1 < PER ? v[i + 1] : next0;
-        cnt[i] = base + i < E ? (end - v[i] + 1) >> 1 : 0;
-        sum += cnt[i];
-      }
-      int inc = sum;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int x = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += x;
-      }
-      int run = inc - sum;
-#pragma unroll
-      for (int i = 0; i < PER; ++i) {
-        if (base + i < E) { g_first[base + i] = v[i]; g_pairs[base + i] = run; }
-        run += cnt[i];
-      }
-      if (lane == 31) g_pairs[E] = inc;
-    }
-    __syncthreads();
-  }
+  if (by_expert) pair::build_expert_pairs<gemm_threads(EPI)>(p.tile_expert, p.num_tiles, p.num_m128, p.n_experts, g_first, g_pairs);
   const int total_pt = by_expert ? g_pairs[p.n_experts] : 0;
   const int total_tiles = by_expert ? total_pt * p.num_n
                                     : p.num_mp * p.num_n * (GROUPED && p.ragged_offs != nullptr ? p.n_experts : 1);

@@ -96,7 +96,7 @@ _MANY = [int(c) for c in torch.randint(0, 700, (37,), generator=torch.Generator(
 
 @pytest.mark.parametrize("counts", [[5, 0, 7, 4], [200, 0, 0, 131], [128, 256, 1, 0], [0, 0, 300, 0], "many"])
 @pytest.mark.parametrize("k,n", [(256, 384), (768, 384), (384, 768)])
-@pytest.mark.parametrize("bn", [0, 128, 192, 256, "pair", "bstat"])   # tile width of the one-CTA kernel (0 = by shape) / CTA pairs / weight tile kept in shared memory (dgrad)
+@pytest.mark.parametrize("bn", [0, 128, 192, 256, "pair", "bstat", "rowstat"])   # tile width of the one-CTA kernel (0 = by shape) / CTA pairs / weight tile kept in shared memory / rows of A kept in shared memory (dgrad)
 def test_grouped_backward_gemms(ops, counts, k, n, bn):
     """dgrad (operand = transposed weight stack, expert offset along K) and wgrad (ragged K range per
     expert, one output matrix per expert, zeros for experts without rows) against dequantize-then-matmul."""
@@ -120,8 +120,9 @@ def test_grouped_backward_gemms(ops, counts, k, n, bn):
     gt, gtsf = ops.quantize_mxfp8(gy_pad, 0)                             # (k, padded_rows)
     xt, xtsf = ops.quantize_mxfp8(x_pad, 0)                              # (n, padded_rows)
     _lib.load().b200q_debug_set_gemm_pair(1 if bn == "pair" else 0)
-    _lib.load().b200q_debug_set_gemm_bn(0 if bn in ("pair", "bstat") else bn)
+    _lib.load().b200q_debug_set_gemm_bn(0 if bn in ("pair", "bstat", "rowstat") else bn)
     _lib.load().b200q_debug_set_gemm_bstat(1 if bn == "bstat" else -1)
+    _lib.load().b200q_debug_set_gemm_rowstat(1 if bn == "rowstat" else -1)
     try:
         dx = ops.grouped_gemm_mxfp8_dgrad(a, sfa, wt, wtsf, plan, n)     # (padded_rows, n)
         dw = ops.grouped_gemm_mxfp8_wgrad(gt, gtsf, xt, xtsf, plan)      # (E, k, n)
@@ -130,6 +131,7 @@ def test_grouped_backward_gemms(ops, counts, k, n, bn):
         _lib.load().b200q_debug_set_gemm_bn(0)
         _lib.load().b200q_debug_set_gemm_pair(0)
         _lib.load().b200q_debug_set_gemm_bstat(0)
+        _lib.load().b200q_debug_set_gemm_rowstat(0)
     a_deq = G.deq_mxfp8(a, sfa)
     wt_deq = G.deq_mxfp8(wt, wtsf)                                       # (n, E*k)
     gt_deq, xt_deq = G.deq_mxfp8(gt, gtsf), G.deq_mxfp8(xt, xtsf)
@@ -237,7 +239,7 @@ def _grouped_ref(a_deq, w_deq, counts):
     return out
 
 
-@pytest.mark.parametrize("pair", [1, -1, "bstat"])   # CTA pairs formed inside every expert (opt-in) / the one-CTA kernel / the B-stationary kernel
+@pytest.mark.parametrize("pair", [1, -1, "bstat", "rowstat"])   # CTA pairs formed inside every expert (opt-in) / the one-CTA kernel / the B-stationary kernel / the row-stationary pair kernel
 @pytest.mark.parametrize("counts", [[5, 0, 7, 4], [0, 5, 7, 4], [5, 7, 4, 0], [200, 0, 0, 131], [128, 256, 1, 0], [300, 129, 0, 513, 1], _MANY])
 @pytest.mark.parametrize("d,n", [(256, 384), (768, 768)])
 def test_grouped_gemm_with_empty_experts(ops, counts, d, n, pair):
@@ -250,14 +252,16 @@ def test_grouped_gemm_with_empty_experts(ops, counts, d, n, pair):
     plan = ops.moe_pad_plan(offs, r)
     a, sfa = ops.moe_gather(x, plan, True)
     wq, wsf = ops.quantize_mxfp8(w.reshape(e * n, d), 1)
-    _lib.load().b200q_debug_set_gemm_pair(0 if pair == "bstat" else pair)
+    _lib.load().b200q_debug_set_gemm_pair(0 if pair in ("bstat", "rowstat") else pair)
     _lib.load().b200q_debug_set_gemm_bstat(1 if pair == "bstat" else -1)
+    _lib.load().b200q_debug_set_gemm_rowstat(1 if pair == "rowstat" else -1)
     try:
         out = ops.grouped_gemm_mxfp8(a, sfa, wq, wsf, plan, n)
         ops.device_status()
     finally:
         _lib.load().b200q_debug_set_gemm_pair(0)
         _lib.load().b200q_debug_set_gemm_bstat(0)
+        _lib.load().b200q_debug_set_gemm_rowstat(0)
     xq, xsf = ops.quantize_mxfp8(x, 1)
     ref = _grouped_ref(G.deq_mxfp8(xq, xsf), G.deq_mxfp8(wq, wsf).view(e, n, d), counts)
     pstart = plan.padded_offs.cpu().tolist()
@@ -273,7 +277,7 @@ def test_grouped_gemm_with_empty_experts(ops, counts, d, n, pair):
 
 @pytest.mark.parametrize("counts", [[5, 0, 7, 4], [200, 0, 0, 131], [128, 256, 1, 0]])
 @pytest.mark.parametrize("d,inter", [(256, 64), (768, 384), (512, 192)])
-@pytest.mark.parametrize("bn", [0, 128, 192, 256, "pair", "bstat"])
+@pytest.mark.parametrize("bn", [0, 128, 192, 256, "pair", "bstat", "rowstat"])
 def test_swiglu_epilogue_equals_gemm_then_swiglu(ops, counts, d, inter, bn):
     """Grouped GEMM with the SwiGLU + MXFP8 epilogue over interleaved weights == grouped GEMM to
     bf16 followed by the stand-alone SwiGLU + MXFP8 kernel over the plain weights, byte for byte."""
@@ -293,8 +297,9 @@ def test_swiglu_epilogue_equals_gemm_then_swiglu(ops, counts, d, inter, bn):
     hb = ops.grouped_gemm_mxfp8(a, sfa, wq, wsf, plan, n_pad)[:live, : 2 * inter].contiguous()
     want_codes, want_sf = ops.swiglu(hb, True)
     _lib.load().b200q_debug_set_gemm_pair(1 if bn == "pair" else 0)
-    _lib.load().b200q_debug_set_gemm_bn(0 if bn in ("pair", "bstat") else bn)
+    _lib.load().b200q_debug_set_gemm_bn(0 if bn in ("pair", "bstat", "rowstat") else bn)
     _lib.load().b200q_debug_set_gemm_bstat(1 if bn == "bstat" else -1)
+    _lib.load().b200q_debug_set_gemm_rowstat(1 if bn == "rowstat" else -1)
     try:
         wqi, wsfi = ops.quantize_mxfp8_rowmap(w.reshape(e * 2 * inter, d), ops.glu_row_map(e, inter, "cuda"))
         got_codes, got_sf = ops.grouped_gemm_mxfp8_swiglu(a, sfa, wqi, wsfi, plan, 2 * inter)
@@ -303,6 +308,7 @@ def test_swiglu_epilogue_equals_gemm_then_swiglu(ops, counts, d, inter, bn):
         _lib.load().b200q_debug_set_gemm_bn(0)
         _lib.load().b200q_debug_set_gemm_pair(0)
         _lib.load().b200q_debug_set_gemm_bstat(0)
+        _lib.load().b200q_debug_set_gemm_rowstat(0)
     assert torch.equal(got_codes[:live], want_codes)
     n_sf = live // 128 * ((inter // 32 + 3) // 4) * 512
     assert torch.equal(got_sf[:n_sf], want_sf[:n_sf])
@@ -920,9 +926,10 @@ def test_peer_scatter_dots_and_barrier_on_one_rank(ops):
     ops.device_status()
 
 
+@pytest.mark.parametrize("form", ["bstat", "rowstat"])
 @pytest.mark.parametrize("d,inter", [(768, 384), (512, 256), (256, 128)])
-def test_b_stationary_grouped_gemms_equal_the_general_kernel_bit_for_bit(ops, d, inter):
-    """The grouped GEMMs with the expert's weight tile kept in shared memory against the general grouped kernel on a
+def test_stationary_grouped_gemms_equal_the_general_kernel_bit_for_bit(ops, d, inter, form):
+    """The grouped GEMMs with the expert's weight tile, or the pair's rows of A, kept in shared memory against the general grouped kernel on a
     routing of BASELINE config 4's kind (many experts, ragged and empty ones, several thousand rows): same codes and
     scale bytes from the SwiGLU epilogue form, same bf16 outputs from the plain and the dgrad forms."""
     from pretrain_b200 import _lib
@@ -943,7 +950,8 @@ def test_b_stationary_grouped_gemms_equal_the_general_kernel_bit_for_bit(ops, d,
     live = int(plan.num_tiles.item()) * 128
     res = {}
     for mode in (-1, 1):
-        lib.b200q_debug_set_gemm_bstat(mode)
+        lib.b200q_debug_set_gemm_bstat(mode if form == "bstat" else -1)
+        lib.b200q_debug_set_gemm_rowstat(mode if form == "rowstat" else -1)
         try:
             hq, hs = ops.grouped_gemm_mxfp8_swiglu(a, sfa, w1q, w1s, plan, 2 * inter)
             g = ops.grouped_gemm_mxfp8(a, sfa, w1p, w1ps, plan, 2 * inter)
@@ -953,6 +961,7 @@ def test_b_stationary_grouped_gemms_equal_the_general_kernel_bit_for_bit(ops, d,
             ops.device_status()
         finally:
             lib.b200q_debug_set_gemm_bstat(0)
+            lib.b200q_debug_set_gemm_rowstat(0)
         n_sf = live // 128 * ((inter // 32 + 3) // 4) * 512
         res[mode] = (hq[:live].clone(), hs[:n_sf].clone(), g[:live].clone(), y[:live].clone(), dh[:live].clone())
     for got, want in zip(res[1], res[-1]):
