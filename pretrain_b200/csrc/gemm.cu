@@ -188,6 +188,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * C::STAGES + 2 + a); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::BAR_OFF + 8 * (2 * C::STAGES + 4));
+  // set by a role whose bounded wait ran out; the others look at it once per tile (not per K step: a shared-memory
+  // read after every ring wait costs the issuing threads 30 clocks each) and otherwise run into their own limits
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -241,7 +243,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int64_t brow0 = ti.brow0;
         for (int kl = 0; kl < ti.nk; ++kl) {
           const int k = ti.k0 + kl;
-          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1) || *abort_flag) { ok = false; break; }
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1)) { ok = false; break; }
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           const uint32_t fb = full_bar(stage);
           uint32_t tx = C::A_BYTES + C::B_BYTES;
@@ -293,7 +295,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (acc ? C::ACC1_COL0 : 0);
         for (int k = 0; k < ti.nk; ++k) {
-          if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
+          if (!ptx::mbar_wait(full_bar(stage), phase)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           if (!row_scaled(KIND)) {

@@ -286,7 +286,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int brow0 = ti.brow0;                                  // this CTA's rows of B
         for (int kl = 0; kl < ti.nk; ++kl) {
           const int k = ti.k0 + kl;
-          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1) || *abort_flag) { ok = false; break; }
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1)) { ok = false; break; }
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           const uint32_t fb = full_bar(stage) & ptx::kLeaderMask;    // the leader's barrier, from either CTA
           ptx::mbar_expect_tx_cluster(fb, C::TX_BYTES);
@@ -327,7 +327,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // only the ragged form has a K range per tile; the others need no tile lookup here
         const int nk = GROUPED && p.ragged_offs != nullptr ? pair::get_ptile<GROUPED>(p, t, total_pt, 0, g_first, g_pairs).nk : p.num_k;
         for (int k = 0; k < nk; ++k) {
-          if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
+          if (!ptx::mbar_wait(full_bar(stage), phase)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + stage * C::STAGE_BYTES, sb = sa + C::A_BYTES;
           if (!row_scaled(KIND)) {

@@ -202,7 +202,7 @@ gemm_bstat_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         new_run = !w.next_shares_b();
         for (int k = 0; k < L.nk; ++k) {
-          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1) || *abort_flag) { ok = false; break; }
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1)) { ok = false; break; }
           const uint32_t sa = smem_base + L.ring_off + stage * bstat::A_STAGE, fb = full_bar(stage);
           ptx::mbar_expect_tx(fb, BM * BKB + 512);
           ptx::bulk_load(sa + BM * BKB, p.sfa + ((int64_t)m_blk * p.sf_kt + k) * 512, 512, fb);
@@ -240,7 +240,7 @@ gemm_bstat_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (acc ? C::ACC1_COL0 : 0);
         for (int k = 0; k < L.nk; ++k) {
-          if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
+          if (!ptx::mbar_wait(full_bar(stage), phase)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + L.ring_off + stage * bstat::A_STAGE;
           ptx::tmem_cp_32x128b_warpx4(tmem_base + C::SFA_COL0, ptx::smem_desc_sf(sa + BM * BKB));

@@ -10,15 +10,21 @@
 // as soon as the last tile of the old run is done with step k (one "free" / "full" barrier pair per K step), so the
 // reload runs behind the last tile's main loop instead of after it.
 //
-// What it buys, measured at 69632 x 768 x 768 over 64 experts (B200, steady loop): the SwiGLU form 44.6 us against 46.4 us
-// for the general kernel; the bf16 forms tie.  Timelines (clock64 per role and tile) and runs with parts switched off
-// show why the gain is small although a third of the operand bytes remain: with the epilogue arithmetic AND the stores
-// removed the kernel still takes 40 us, as do the general and the B-stationary kernel with two and 1.3 times its bytes.
-// About 13 us of that is the start of the kernel (table of the experts' pair tiles, then every SM filling 200 KB of
-// shared memory from cold DRAM at once: the first tile completes after 22000 clocks, the later ones every 5400), and
-// in the steady state a load takes 2000 - 4500 clocks to arrive whatever the kernel, i.e. the memory system, not the
-// ring depth, sets the pace.  The SwiGLU epilogue's stores (16 bytes per lane to 32 rows per instruction) cost another
-// 7 - 9 us in every kernel.
+// What it buys, measured at 69632 x 768 x 768 over 64 experts (B200): in a steady loop of the one kernel the SwiGLU form
+// takes 44.6 us against 46.4 us for the general kernel and the bf16 forms tie; inside the MoE block (gather + quantize
+// before it) it is 1 us SLOWER (53.4 against 52.4 us), so it is an opt-in, kept for the record and covered by the same
+// tests as the other forms.  Timelines (clock64 per role, tile and K step) and runs with parts switched off show why a
+// kernel that moves a third of the operand bytes gains nothing:
+//   * with the MMAs, the epilogue arithmetic and the stores all removed the kernel still takes 38 us, and just as long
+//     when every load is pointed at one and the same small tile: the floor is not set by the memory system;
+//   * the thread that issues the MMAs needs about 500 clocks per K step for waiting on the "full" barrier (300, on a
+//     barrier that completed long before), three scale-factor copies into tensor memory and the commit (230), before any
+//     MMA - as long as the four MMAs of a 256 x 192 (384 clocks) or 256 x 256 (512 clocks) step run.  The dense kernels
+//     hide the same cost behind 64 K steps per tile; here a tile has six;
+//   * about 13 us are the start of the kernel: 3 us of set-up (table of the experts' pair tiles, barriers, tensor memory),
+//     then every SM fills 200 KB of shared memory at once and the first tile completes after 22000 clocks;
+//   * the SwiGLU epilogue's stores (16 bytes per lane to 32 rows per instruction) add 7 - 9 us in every kernel form.
+// Running the producer and MMA loops with the whole warp (one elected lane issuing) instead of one thread measured slower.
 //
 // Roles, pair protocol (who signals whom) and epilogues are those of gemm_pair_kernel; two epilogue warps share each
 // tensor-memory lane quarter for every output form.  Forms: fprop (B rows e*N + n) and dgrad (B = transposed weight
@@ -216,7 +222,7 @@ gemm_rowstat_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             ptx::tma_load_2d_pair(smem_base + k * A_STEP, &tmap_a, k * BKB, r.row0, ab);
             ptx::tma_load_2d_pair(smem_base + L.sfa_off + k * 512, &tmap_sfa, 0, 2 * ((r.row0 >> 7) * p.sf_kt + k), ab);
           }
-          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1) || *abort_flag) { ok = false; break; }
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1)) { ok = false; break; }
           const uint32_t sb = smem_base + L.ring_off + stage * B_STAGE, ssfb = sb + HALF_N * BKB;
           const uint32_t fb = full_bar(stage) & ptx::kLeaderMask;    // the leader's barrier, from either CTA
           ptx::mbar_expect_tx_cluster(fb, B_TX);
@@ -254,7 +260,7 @@ gemm_rowstat_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t d_tmem = tmem_base + (acc ? C::ACC1_COL0 : 0);
         for (int k = 0; k < L.nk; ++k) {
           if (new_run && (!ptx::mbar_wait(afull_bar(k), runs & 1) || *abort_flag)) { ok = false; break; }
-          if (!ptx::mbar_wait(full_bar(stage), phase) || *abort_flag) { ok = false; break; }
+          if (!ptx::mbar_wait(full_bar(stage), phase)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + k * A_STEP, sb = smem_base + L.ring_off + stage * B_STAGE;
           const uint32_t ssfb = sb + HALF_N * BKB;
@@ -401,11 +407,9 @@ int try_rowstat(const void* A, const void* B, const OutSpec& D, int64_t ldd, int
   if (p.tile_expert == nullptr || p.num_tiles == nullptr || p.ragged_offs != nullptr || (p.K & 127) || p.K > rowstat::kMaxNk * BKB ||
       (p.N & 127) || p.n_experts > pair::kPairMaxExperts)
     return kRowstatNotApplicable;
-  if (g_rowstat_mode == 0 && p.M < 32 * BM) return kRowstatNotApplicable;      // too few pair tiles to occupy the pairs
-  // By default only where it measured faster than the general kernel (65536 x 768 rows, 64 experts): the SwiGLU form
-  // (44.6 us against 46.4 us at K = N = 768).  The bf16 forms tie or lose by a few per cent (their TMA stores compete with
-  // the loads for the same unit).
-  if (g_rowstat_mode == 0 && EPI != EPI_GLU) return kRowstatNotApplicable;
+  // Opt-in only (b200q_debug_set_gemm_rowstat(1) / B200Q_ROWSTAT=1): see the account at the top of this file - a tie with
+  // the general kernel inside the MoE block, where the kernels before it leave other things in L2 than a steady loop does.
+  if (g_rowstat_mode == 0) return kRowstatNotApplicable;
   int rc = kRowstatNotApplicable;
   auto attempt = [&](auto bn_tag) {
     constexpr int BN = decltype(bn_tag)::value;
