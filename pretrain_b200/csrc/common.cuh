@@ -76,12 +76,26 @@ inline int blocks_per_sm(Kernel kernel, int threads, int fallback) {
 // everything the later kernel does before grid_dependency_wait() - CTA set-up, barrier initialisation, tensor-memory
 // allocation, descriptor prefetch - then overlaps the earlier kernel's tail.  grid_dependency_wait() returns once the
 // earlier kernel has completed and its memory operations are visible; without the launch attribute it returns at once.
-// Only kernels whose whole grid is resident at once call grid_launch_dependents() at their start (so that a waiting
-// successor can never hold resources a not-yet-started CTA of theirs needs).
+// The hardware schedules the later kernel only when ALL CTAs of the earlier one have executed the instruction or exited, so a
+// successor waiting in griddepcontrol.wait never holds resources that a not-yet-started CTA of the earlier kernel needs.
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// First statement of every kernel outside the GEMMs: let the next kernel of the stream be scheduled as soon as all CTAs of
+// this one have started, and touch no memory before everything earlier in the stream is complete.  A chain of short kernels
+// (permute plan, gather, quantizers, unpermute) then runs without the launch latency between its links.
+__device__ __forceinline__ void pdl_prologue() {
+  grid_launch_dependents();
+  grid_dependency_wait();
+}
 
 // Launch with (or without) the programmatic-serialization attribute.  B200Q_PDL=0 in the environment turns it off.
+//
+// The attribute is given ONLY to a kernel that directly follows another kernel of the same entry point in the stream.
+// A kernel that carries it is not held back by a copy or memset that precedes it (measured on B200, CUDA 12.9: a
+// quantizer launched with the attribute after cudaMemcpyAsync of its input, or after torch's clone(), read the old
+// contents in 27 - 30 of 30 runs), and griddepcontrol.wait only waits for kernels.  What the caller enqueued before an
+// entry point is unknown, so the first kernel of every entry point is a plain launch; inside an entry point a
+// cudaMemsetAsync restarts the chain (memset_async below).
 inline bool pdl_enabled() {
   static int v = -1;
   if (v < 0) {
@@ -89,6 +103,19 @@ inline bool pdl_enabled() {
     v = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
   return v == 1;
+}
+// kernels launched so far in the entry point's chain; -1 = no chain open (every launch is plain)
+inline thread_local int t_pdl_chain = -1;
+struct PdlChain {                       // opened at the top of an entry point that launches several kernels
+  bool outer;
+  PdlChain() : outer(t_pdl_chain < 0) { if (outer) t_pdl_chain = 0; }
+  ~PdlChain() { if (outer) t_pdl_chain = -1; }
+  PdlChain(const PdlChain&) = delete;
+  PdlChain& operator=(const PdlChain&) = delete;
+};
+inline cudaError_t memset_async(void* p, int value, size_t bytes, cudaStream_t st) {
+  if (t_pdl_chain > 0) t_pdl_chain = 0;         // the next kernel follows a memset, not a kernel
+  return cudaMemsetAsync(p, value, bytes, st);
 }
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
@@ -98,13 +125,14 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = t_pdl_chain > 0 && pdl_enabled() ? 1 : 0;
+  if (t_pdl_chain >= 0) ++t_pdl_chain;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
@@ -114,12 +142,12 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
 template <bool WIDE>
 __device__ __forceinline__ void ld_nc_32B(const void* p, uint4& a, uint4& b) {
   if (WIDE) {
-    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+    asm volatile("ld.global.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p));
   } else {
-    asm volatile("ld.global.nc.L1::evict_first.v4.u32 {%0,%1,%2,%3}, [%4];"
+    asm volatile("ld.global.L1::evict_first.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p));
-    asm volatile("ld.global.nc.L1::evict_first.v4.u32 {%0,%1,%2,%3}, [%4];"
+    asm volatile("ld.global.L1::evict_first.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(static_cast<const char*>(p) + 16));
   }
 }

@@ -151,11 +151,11 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, int t, int num_m) 
     local = t - e * per;
   }
   tile_coords(local, num_m, p.num_n, ti.m_blk, ti.n_blk);
-  if (p.tile_expert != nullptr) e = __ldg(p.tile_expert + ti.m_blk);
+  if (p.tile_expert != nullptr) e = __ldcg(p.tile_expert + ti.m_blk);
   ti.k0 = 0; ti.nk = p.num_k; ti.sfb_k0 = 0; ti.bk0 = 0; ti.drow_off = 0; ti.zero = false;
   ti.brow0 = (int64_t)ti.n_blk * BN;
   if (p.ragged_offs != nullptr) {
-    const int r0 = __ldg(p.ragged_offs + e), r1 = __ldg(p.ragged_offs + e + 1);
+    const int r0 = __ldcg(p.ragged_offs + e), r1 = __ldcg(p.ragged_offs + e + 1);
     ti.k0 = r0 >> 7;
     ti.nk = (r1 - r0) >> 7;
     if (ti.nk <= 0) {                      // no rows: nothing is loaded or multiplied (the operands there may hold
@@ -199,7 +199,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (reads_plan) grid_dependency_wait();
   int num_m = p.num_m;
   if (p.num_tiles != nullptr) {
-    const int live = __ldg(p.num_tiles);
+    const int live = __ldcg(p.num_tiles);
     num_m = live < num_m ? live : num_m;
   }
   const int total_tiles = num_m * p.num_n * (p.ragged_offs != nullptr ? p.n_experts : 1);
@@ -346,7 +346,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int tile_iter = 0;
     bool ok = true;
     float alpha = 1.f;
-    if (KIND == KIND_NV) alpha = __ldg(p.scale_a) * __ldg(p.scale_b);
+    if (KIND == KIND_NV) alpha = __ldcg(p.scale_a) * __ldcg(p.scale_b);
     constexpr int NBLK = BN / EPI_COLS;
     const int64_t m_out = p.ragged_offs != nullptr ? p.M * p.n_experts : p.M;    // rows of the output
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
@@ -357,7 +357,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int64_t row0 = ti.drow_off + (int64_t)m_blk * BM + q * 32, row = row0 + lane;
       const int64_t col0 = (int64_t)n_blk * BN;
       float row_scale = alpha;
-      if (row_scaled(KIND)) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
+      if (row_scaled(KIND)) row_scale = row < p.M ? __ldcg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
       // Block order: natural, except that an overlapped accumulator 0 is read from its last
@@ -618,7 +618,7 @@ int prepare_glu(GemmParams* p, const void* A, const void* sfA, const void* B, co
   if (rc) return rc;
   const int64_t hblk = N / 64;
   if (zero_pads && ((M & 127) || (hblk & 3)))
-    B200Q_CUDA(cudaMemsetAsync(sfH, 0, (size_t)b200q_sf_bytes(M, hblk, B200Q_SF_SWIZZLE_128x4), st));
+    B200Q_CUDA(memset_async(sfH, 0, (size_t)b200q_sf_bytes(M, hblk, B200Q_SF_SWIZZLE_128x4), st));
   *p = GemmParams{};
   p->sfa = (const uint8_t*)sfA; p->sfb = (const uint8_t*)sfB; p->a_fmt = a_fmt; p->b_fmt = b_fmt;
   p->M = M; p->N = N; p->K = K;
@@ -714,6 +714,7 @@ __global__ void expire_wait_kernel(int iterations) {
 } }  // namespace b200q::{anonymous}
 extern "C" {
 int b200q_debug_expire_wait(int iterations, void* stream) {
+  PdlChain pdl_chain;
   if (iterations < 1 || iterations > 100000) return B200Q_ERR_INVALID_ARG;
   int rc = require_sm100();
   if (rc) return rc;
@@ -732,6 +733,7 @@ int b200q_debug_set_gemm_bn(int bn) {
 int b200q_gemm_fp8(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a, int a_scale_is_scalar,
                    const float* scale_b, int b_scale_is_scalar, int64_t M, int64_t N, int64_t K, void* D, int64_t ldd,
                    void* stream) {
+  PdlChain pdl_chain;
   int rc = check_gemm(A, B, D, M, N, K, ldd, 16);
   if (rc) return rc;
   if (scale_a == nullptr || scale_b == nullptr || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
@@ -743,6 +745,7 @@ int b200q_gemm_fp8(const void* A, int a_fmt, const void* B, int b_fmt, const flo
 
 int b200q_gemm_int8(const void* A, const void* B, const float* scale_a, int a_scale_is_scalar, const float* scale_b,
                     int b_scale_is_scalar, int64_t M, int64_t N, int64_t K, void* D, int64_t ldd, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_gemm(A, B, D, M, N, K, ldd, 16);
   if (rc) return rc;
   if (scale_a == nullptr || scale_b == nullptr) return B200Q_ERR_INVALID_ARG;
@@ -754,6 +757,7 @@ int b200q_gemm_int8(const void* A, const void* B, const float* scale_a, int a_sc
 
 int b200q_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
                      int64_t N, int64_t K, void* D, int64_t ldd, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_gemm(A, B, D, M, N, K, ldd, 32);
   if (rc) return rc;
   if (sfA == nullptr || sfB == nullptr || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
@@ -776,6 +780,7 @@ int64_t b200q_linear_mxfp8_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 int b200q_linear_mxfp8(const void* a, int64_t a_rows, int64_t a_cols, int64_t lda, int a_axis, int a_fmt, const void* b,
                        int64_t b_rows, int64_t b_cols, int64_t ldb, int b_axis, int b_fmt, void* D, int64_t ldd, void* workspace,
                        void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(a, a_rows, a_cols, lda);
   if (rc) return rc;
   if ((rc = check_matrix(b, b_rows, b_cols, ldb))) return rc;
@@ -817,6 +822,7 @@ int b200q_linear_mxfp8(const void* a, int64_t a_rows, int64_t a_cols, int64_t ld
 
 int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,
                      int64_t M, int64_t N, int64_t K, void* D, int64_t ldd, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_gemm(A, B, D, M, N, K, ldd, 32);
   if (rc) return rc;
   if (sfA == nullptr || sfB == nullptr || tsA == nullptr || tsB == nullptr) return B200Q_ERR_INVALID_ARG;
@@ -830,6 +836,7 @@ int b200q_gemm_nvfp4(const void* A, const void* sfA, const void* B, const void* 
 int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB,
                              const int32_t* tile_expert, const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
                              int64_t K, void* D, int64_t ldd, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_gemm(A, B, D, padded_rows, N, K, ldd, 32);
   if (rc) return rc;
   if (sfA == nullptr || sfB == nullptr || tile_expert == nullptr || num_tiles == nullptr || E <= 0 || (a_fmt | b_fmt) & ~1)
@@ -850,6 +857,7 @@ int b200q_grouped_gemm_mxfp8(const void* A, int a_fmt, const void* sfA, const vo
 
 int b200q_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
                             int64_t N, int64_t K, void* H, int64_t ldh, void* sfH, void* stream) {
+  PdlChain pdl_chain;
   GemmParams p;
   int rc = prepare_glu(&p, A, sfA, B, sfB, a_fmt, b_fmt, M, N, K, H, ldh, sfH, true, (cudaStream_t)stream);
   if (rc) return rc;
@@ -859,6 +867,7 @@ int b200q_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const voi
 int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB,
                                     const int32_t* tile_expert, const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
                                     int64_t K, void* H, int64_t ldh, void* sfH, void* stream) {
+  PdlChain pdl_chain;
   if (tile_expert == nullptr || num_tiles == nullptr || E <= 0) return B200Q_ERR_INVALID_ARG;
   if ((padded_rows & 127) || (N & 127) || (int64_t)E * N > INT32_MAX) return B200Q_ERR_SHAPE;
   GemmParams p;
@@ -875,6 +884,7 @@ int b200q_grouped_gemm_mxfp8_swiglu(const void* A, int a_fmt, const void* sfA, c
 
 int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,
                             int64_t M, int64_t N, int64_t K, void* H, int64_t ldh, float* amax_out, void* stream) {
+  PdlChain pdl_chain;
   if (A == nullptr || B == nullptr || sfA == nullptr || sfB == nullptr || tsA == nullptr || tsB == nullptr || H == nullptr ||
       amax_out == nullptr || M <= 0 || N <= 0 || K <= 0 || ldh < N / 2)
     return B200Q_ERR_INVALID_ARG;
@@ -884,7 +894,7 @@ int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const
   int rc = require_sm100();
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  B200Q_CUDA(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+  B200Q_CUDA(memset_async(amax_out, 0, sizeof(float), st));
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.scale_a = tsA; p.scale_b = tsB;
   p.M = M; p.N = N; p.K = K;
@@ -914,6 +924,7 @@ static int dispatch_one_cta_mx(const void* A, const void* B, void* D, int64_t ld
 int b200q_grouped_gemm_mxfp8_dgrad(const void* A, int a_fmt, const void* sfA, const void* Bt, int b_fmt, const void* sfBt,
                                    const int32_t* tile_expert, const int32_t* num_tiles, int64_t padded_rows, int E, int64_t N,
                                    int64_t K, void* D, int64_t ldd, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_gemm(A, Bt, D, padded_rows, N, K, ldd, 128);
   if (rc) return rc;
   if (sfA == nullptr || sfBt == nullptr || tile_expert == nullptr || num_tiles == nullptr || E <= 0 || (a_fmt | b_fmt) & ~1)
@@ -930,6 +941,7 @@ int b200q_grouped_gemm_mxfp8_dgrad(const void* A, int a_fmt, const void* sfA, co
 int b200q_grouped_gemm_mxfp8_wgrad(const void* At, int a_fmt, const void* sfAt, const void* Bt, int b_fmt, const void* sfBt,
                                    const int32_t* padded_offs, int E, int64_t M, int64_t N, int64_t padded_rows, void* D,
                                    int64_t ldd, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_gemm(At, Bt, D, M, N, padded_rows, ldd, 128);
   if (rc) return rc;
   if (sfAt == nullptr || sfBt == nullptr || padded_offs == nullptr || E <= 0 || (a_fmt | b_fmt) & ~1) return B200Q_ERR_INVALID_ARG;
@@ -944,6 +956,7 @@ int b200q_grouped_gemm_mxfp8_wgrad(const void* At, int a_fmt, const void* sfAt, 
 int b200q_gemm_fp8_allgather(const void* A, int a_fmt, const void* B, int b_fmt, const float* scale_a, int a_scale_is_scalar,
                              const float* scale_b, int b_scale_is_scalar, int64_t M, int64_t N, int64_t K, void* const* D_all,
                              int world, int rank, int64_t ldd, void* stream) {
+  PdlChain pdl_chain;
   OutSpec outs;
   int rc = gathered_outputs(&outs, D_all, world, rank, M, ldd);
   if (rc) return rc;
@@ -957,6 +970,7 @@ int b200q_gemm_fp8_allgather(const void* A, int a_fmt, const void* B, int b_fmt,
 
 int b200q_gemm_mxfp8_allgather(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
                                int64_t N, int64_t K, void* const* D_all, int world, int rank, int64_t ldd, void* stream) {
+  PdlChain pdl_chain;
   OutSpec outs;
   int rc = gathered_outputs(&outs, D_all, world, rank, M, ldd);
   if (rc) return rc;
@@ -972,6 +986,7 @@ int b200q_gemm_mxfp8_allgather(const void* A, int a_fmt, const void* sfA, const 
 int b200q_gemm_mxfp8_allgather_mxfp8(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
                                      int64_t N, int64_t K, void* const* C_all, void* const* SF_all, int world, int rank,
                                      int64_t ldc, void* stream) {
+  PdlChain pdl_chain;
   if (A == nullptr || B == nullptr || sfA == nullptr || sfB == nullptr || C_all == nullptr || SF_all == nullptr || M <= 0 || N <= 0 ||
       K <= 0 || ldc < N || world < 1 || world > kMaxOutputs || rank < 0 || rank >= world || ((a_fmt | b_fmt) & ~1))
     return B200Q_ERR_INVALID_ARG;
@@ -999,6 +1014,7 @@ int b200q_gemm_mxfp8_allgather_mxfp8(const void* A, int a_fmt, const void* sfA, 
 
 int b200q_gemm_mxfp8_scatter(const void* A, int a_fmt, const void* sfA, const void* B, int b_fmt, const void* sfB, int64_t M,
                              int64_t N, int64_t K, void* const* stage_all, int world, int rank, int64_t ldd, void* stream) {
+  PdlChain pdl_chain;
   OutSpec outs;
   int rc = scattered_outputs(&outs, stage_all, world, rank, M, ldd);
   if (rc) return rc;
@@ -1012,6 +1028,7 @@ int b200q_gemm_mxfp8_scatter(const void* A, int a_fmt, const void* sfA, const vo
 }
 
 int b200q_sum_slots(const void* stage, int slots, int64_t rows, int64_t cols, int64_t ld, void* out, int64_t ldo, void* stream) {
+  PdlChain pdl_chain;
   if (stage == nullptr || out == nullptr || slots < 1 || rows <= 0 || cols <= 0 || ld < cols || ldo < cols) return B200Q_ERR_INVALID_ARG;
   if ((cols & 7) || (ld & 7) || (ldo & 7)) return B200Q_ERR_SHAPE;
   if (!aligned16(stage) || !aligned16(out)) return B200Q_ERR_ALIGNMENT;
@@ -1027,6 +1044,7 @@ int b200q_sum_slots(const void* stage, int slots, int64_t rows, int64_t cols, in
 int b200q_gemm_nvfp4_allgather(const void* A, const void* sfA, const void* B, const void* sfB, const float* tsA, const float* tsB,
                                int64_t M, int64_t N, int64_t K, void* const* D_all, int world, int rank, int64_t ldd,
                                void* stream) {
+  PdlChain pdl_chain;
   OutSpec outs;
   int rc = gathered_outputs(&outs, D_all, world, rank, M, ldd);
   if (rc) return rc;

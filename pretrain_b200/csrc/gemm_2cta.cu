@@ -127,7 +127,7 @@ __device__ __forceinline__ PTile get_ptile(const PairParams& p, int t, int total
     ti.live = ti.row0 < p.M;
     ti.brow0 = ti.n_blk * PBN + cta * HALF_N;
     ti.bgroup = ti.n_blk * 2;
-    const int r0 = __ldg(p.ragged_offs + e), r1 = __ldg(p.ragged_offs + e + 1);
+    const int r0 = __ldcg(p.ragged_offs + e), r1 = __ldcg(p.ragged_offs + e + 1);
     ti.k0 = r0 >> 7;
     ti.nk = (r1 - r0) >> 7;
     if (ti.nk <= 0) {                                 // no rows: nothing is loaded or multiplied, zeros are stored
@@ -166,12 +166,12 @@ template <int THREADS>
 __device__ __forceinline__ int build_expert_pairs(const int32_t* tile_expert, const int32_t* num_tiles, int num_m128, int n_experts,
                                                   int* g_first, int* g_pairs) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int live_tiles = __ldg(num_tiles);
+  int live_tiles = __ldcg(num_tiles);
   live_tiles = live_tiles < num_m128 ? live_tiles : num_m128;
   for (int e = threadIdx.x; e <= n_experts; e += THREADS) g_first[e] = e == n_experts ? live_tiles : 0x7fffffff;
   __syncthreads();
   for (int t = threadIdx.x; t < live_tiles; t += THREADS) {
-    const int e = __ldg(tile_expert + t), prev = t > 0 ? __ldg(tile_expert + t - 1) : -1;
+    const int e = __ldcg(tile_expert + t), prev = t > 0 ? __ldcg(tile_expert + t - 1) : -1;
     if (e != prev && e >= 0 && e < n_experts) g_first[e] = t;
   }
   __syncthreads();
@@ -378,7 +378,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int tile_iter = 0;
     bool ok = true;
     float alpha = 1.f;
-    if (KIND == KIND_NV) alpha = __ldg(p.scale_a) * __ldg(p.scale_b);
+    if (KIND == KIND_NV) alpha = __ldcg(p.scale_a) * __ldcg(p.scale_b);
     constexpr int NBLK = BN / EPI_COLS;
     for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++tile_iter) {
       const pair::PTile ti = pair::get_ptile<GROUPED>(p, t, total_pt, (int)cta, g_first, g_pairs);
@@ -389,7 +389,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // rows this CTA may store: none for the idle half of an expert's odd last pair
       const int64_t m_lim = !ti.live ? 0 : (GROUPED && p.ragged_offs != nullptr ? ti.drow_off + p.M : p.M);
       float row_scale = alpha;
-      if (row_scaled(KIND)) row_scale = row < p.M ? __ldg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
+      if (row_scaled(KIND)) row_scale = row < p.M ? __ldcg(p.scale_a + (p.a_scalar ? 0 : row)) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (acc ? C::ACC1_COL0 : 0);
 
       constexpr int RELEASE_AFTER = C::OVERLAP ? C::OVL / EPI_COLS - 1 : NBLK - 1;

@@ -97,7 +97,7 @@ gemm_bstat_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   grid_dependency_wait();                          // the permute plan's tables are read right away
   int num_m = p.num_m;
   {
-    const int live = __ldg(p.num_tiles);
+    const int live = __ldcg(p.num_tiles);
     num_m = live < num_m ? live : num_m;
   }
   // this CTA's contiguous range of (column block, row tile) pairs, row tile fastest
@@ -148,16 +148,16 @@ gemm_bstat_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       n_blk = (int)(t0 / num_m_); m_blk = (int)(t0 - (int64_t)n_blk * num_m_);
       next_of(n_blk, m_blk, n1, m1);
       next_of(n1, m1, n2, m2);
-      e = left > 0 ? __ldg(te + m_blk) : -1;
-      e1 = left > 1 ? __ldg(te + m1) : -1;
-      e2 = left > 2 ? __ldg(te + m2) : -1;
+      e = left > 0 ? __ldcg(te + m_blk) : -1;
+      e1 = left > 1 ? __ldcg(te + m1) : -1;
+      e2 = left > 2 ? __ldcg(te + m2) : -1;
     }
     __device__ __forceinline__ void step() {
       n_blk = n1; m_blk = m1; e = e1;
       n1 = n2; m1 = m2; e1 = e2;
       --left;
       next_of(n1, m1, n2, m2);
-      e2 = left > 2 ? __ldg(te + m2) : -1;
+      e2 = left > 2 ? __ldcg(te + m2) : -1;
     }
     // the following pair exists and uses the same tile of B
     __device__ __forceinline__ bool next_shares_b() const { return left > 1 && n1 == n_blk && e1 == e; }

@@ -54,10 +54,10 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, bool zer
     float sb0 = 1.f, sb1 = 1.f;
     if (COL_SCALE) {
       if (b_scalar) {
-        sb0 = sb1 = __ldg(scale_b);
+        sb0 = sb1 = __ldcg(scale_b);
       } else {
-        sb0 = colg + lane < N ? __ldg(scale_b + colg + lane) : 0.f;
-        sb1 = colg + 32 + lane < N ? __ldg(scale_b + colg + 32 + lane) : 0.f;
+        sb0 = colg + lane < N ? __ldcg(scale_b + colg + lane) : 0.f;
+        sb1 = colg + 32 + lane < N ? __ldcg(scale_b + colg + 32 + lane) : 0.f;
       }
     }
     uint32_t o[32];

@@ -21,6 +21,7 @@ constexpr int kMaxExperts = 256;
 // ---- plan, step 1: per-CTA histogram of expert ids -------------------------------------------
 __global__ void __launch_bounds__(kPlanThreads)
 moe_hist_kernel(const int64_t* __restrict__ top_idx, int64_t n, int E, int32_t* __restrict__ block_counts) {
+  pdl_prologue();
   __shared__ int hist[kMaxExperts];
   for (int i = threadIdx.x; i < E; i += kPlanThreads) hist[i] = 0;
   __syncthreads();
@@ -40,6 +41,7 @@ __global__ void __launch_bounds__(kMaxExperts)
 moe_scan_kernel(int32_t* __restrict__ block_counts, int nblocks, int E, int32_t* __restrict__ offs,
                 int32_t* __restrict__ padded_offs, int32_t* __restrict__ tile_expert, int32_t* __restrict__ num_tiles,
                 int max_tiles) {
+  pdl_prologue();
   __shared__ int count[kMaxExperts];
   __shared__ int pstart[kMaxExperts + 1];
   const int e = threadIdx.x;
@@ -81,6 +83,7 @@ moe_scan_kernel(int32_t* __restrict__ block_counts, int nblocks, int E, int32_t*
 __global__ void __launch_bounds__(kPlanThreads)
 moe_scatter_kernel(const int64_t* __restrict__ top_idx, int64_t n, int k, int E, const int32_t* __restrict__ block_excl,
                    const int32_t* __restrict__ padded_offs, int32_t* __restrict__ row_of, int32_t* __restrict__ src_of_row) {
+  pdl_prologue();
   extern __shared__ int warp_counts[];      // [32 warps][E]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < 32 * E; i += kPlanThreads) warp_counts[i] = 0;
@@ -124,6 +127,7 @@ moe_scatter_tables_kernel(const int64_t* __restrict__ top_idx, int64_t n, int k,
                           int nblocks, int32_t* __restrict__ offs, int32_t* __restrict__ padded_offs,
                           int32_t* __restrict__ row_of, int32_t* __restrict__ src_of_row, int32_t* __restrict__ tile_expert,
                           int32_t* __restrict__ num_tiles, int max_tiles, int64_t padded_rows) {
+  pdl_prologue();
   extern __shared__ int warp_counts[];      // [32 warps][E]
   __shared__ int total[kMaxExperts], excl[kMaxExperts], pstart[kMaxExperts + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -211,6 +215,7 @@ moe_scatter_tables_kernel(const int64_t* __restrict__ top_idx, int64_t n, int k,
 __global__ void __launch_bounds__(kMaxExperts)
 moe_pad_plan_kernel(const int32_t* __restrict__ offs, int E, int32_t* __restrict__ padded_offs,
                     int32_t* __restrict__ tile_expert, int32_t* __restrict__ num_tiles, int max_tiles) {
+  pdl_prologue();
   __shared__ int pstart[kMaxExperts + 1];
   if (threadIdx.x == 0) {
     int prev = 0, p = 0;
@@ -235,6 +240,7 @@ moe_pad_plan_kernel(const int32_t* __restrict__ offs, int E, int32_t* __restrict
 __global__ void moe_pad_src_kernel(const int32_t* __restrict__ offs, const int32_t* __restrict__ padded_offs,
                                    const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ num_tiles,
                                    int32_t* __restrict__ src_of_row, int64_t padded_rows) {
+  pdl_prologue();
   const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= padded_rows) return;
   int src = -1;
@@ -256,6 +262,7 @@ __global__ void __launch_bounds__(256)
 moe_gather_kernel(const uint16_t* __restrict__ x, int64_t D, int64_t ld, const int32_t* __restrict__ src_of_row,
                   const int32_t* __restrict__ num_tiles, int64_t padded_rows, uint8_t* __restrict__ out,
                   uint8_t* __restrict__ sf) {
+  pdl_prologue();
   int64_t live_rows = (int64_t)(*num_tiles) << 7;
   if (live_rows > padded_rows) live_rows = padded_rows;
   const int runs = (int)(D >> 5);
@@ -289,6 +296,7 @@ template <int QUANT, bool WIDE, int FMT>
 __global__ void __launch_bounds__(256)
 swiglu_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t ld, uint8_t* __restrict__ out,
               uint8_t* __restrict__ sf) {
+  pdl_prologue();
   const int runs = (int)(I >> 5);
   const int64_t kt = ((I >> 5) + 3) >> 2;
   for (ItemWalker w((int64_t)blockIdx.x * 256 + threadIdx.x, (int64_t)gridDim.x * 256, runs); w.row < rows; w.next()) {
@@ -331,6 +339,7 @@ __global__ void __launch_bounds__(256)
 moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k, int sigmoid, int normalize,
                        int64_t* __restrict__ top_idx, void* __restrict__ top_w, void* __restrict__ probs_out,
                        int32_t* __restrict__ counts, const float* __restrict__ select_bias, int out_fp32) {
+  pdl_prologue();
   __shared__ int hist[kMaxExperts];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < E; i += 256) hist[i] = 0;
@@ -436,6 +445,7 @@ moe_router_topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k
 // ---- inverse of row_of: the pair that owns every padded row (the array is preset to -1) -------------
 __global__ void moe_pair_of_row_kernel(const int32_t* __restrict__ row_of, int64_t n_pairs, int64_t padded_rows,
                                        int32_t* __restrict__ pair_of_row) {
+  pdl_prologue();
   const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= n_pairs) return;
   const int r = row_of[p];
@@ -446,6 +456,7 @@ __global__ void moe_pair_of_row_kernel(const int32_t* __restrict__ row_of, int64
 __global__ void __launch_bounds__(256)
 moe_unpermute_kernel(const uint16_t* __restrict__ y, int64_t ldy, const uint16_t* __restrict__ w,
                      const int32_t* __restrict__ row_of, int64_t T, int k, int64_t D, uint16_t* __restrict__ out) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (ItemWalker it((int64_t)blockIdx.x * 8 + warp, (int64_t)gridDim.x * 8, (int)((D + 255) >> 8)); it.row < T; it.next()) {
     const int64_t t = it.row, c = (int64_t)it.chunk * 256 + lane * 8;
@@ -486,6 +497,7 @@ moe_dispatch_kernel(const uint16_t* __restrict__ x, int64_t D, int64_t ld, const
                     const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ padded_offs,
                     const int32_t* __restrict__ num_tiles, int64_t padded_rows, const int32_t* __restrict__ row_base,
                     int experts_per_rank, const PeerBufs peers) {
+  pdl_prologue();
   int64_t live_rows = (int64_t)(*num_tiles) << 7;
   if (live_rows > padded_rows) live_rows = padded_rows;
   const int runs = (int)(D >> 5);
@@ -513,6 +525,7 @@ moe_dispatch_kernel(const uint16_t* __restrict__ x, int64_t D, int64_t ld, const
 __global__ void __launch_bounds__(256)
 moe_zero_pad_rows_kernel(const int32_t* __restrict__ src_of_row, const int32_t* __restrict__ num_tiles, int64_t padded_rows,
                          int64_t D, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf) {
+  pdl_prologue();
   int64_t live_rows = (int64_t)(*num_tiles) << 7;
   if (live_rows > padded_rows) live_rows = padded_rows;
   const int runs = (int)(D >> 5);
@@ -534,6 +547,7 @@ struct PeerRows {
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const PeerRows peers, int64_t ldy, const uint16_t* __restrict__ w, const int32_t* __restrict__ pair_peer,
                    const int32_t* __restrict__ pair_row, int64_t T, int k, int64_t D, uint16_t* __restrict__ out) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (ItemWalker it((int64_t)blockIdx.x * 8 + warp, (int64_t)gridDim.x * 8, (int)((D + 255) >> 8)); it.row < T; it.next()) {
     const int64_t t = it.row, c = (int64_t)it.chunk * 256 + lane * 8;
@@ -570,6 +584,7 @@ moe_ep_index_kernel(const int32_t* __restrict__ all_offs, int world, int rank, i
                     const int64_t* __restrict__ top_idx, const int32_t* __restrict__ row_of, const int32_t* __restrict__ padded_offs,
                     int64_t n_pairs, int32_t* __restrict__ row_base, int32_t* __restrict__ own_offs,
                     int32_t* __restrict__ pair_peer, int32_t* __restrict__ pair_row) {
+  pdl_prologue();
   __shared__ int s_total[kMaxExperts], s_before[kMaxExperts], s_base[kMaxExperts];
   for (int e = threadIdx.x; e < E; e += 256) {
     int tot = 0, before = 0;
@@ -614,6 +629,7 @@ struct PeerFlags {
 constexpr uint32_t kBarrierPolls = 4000000u;
 
 __global__ void peer_barrier_kernel(const PeerFlags flags, int world, int rank, int epoch) {
+  pdl_prologue();
   const int lane = threadIdx.x;
   __threadfence_system();
   if (lane < world) {
@@ -641,6 +657,7 @@ __global__ void __launch_bounds__(256)
 moe_scatter_rows_peers_kernel(const uint16_t* __restrict__ x, int64_t ld, const uint16_t* __restrict__ w,
                               const int32_t* __restrict__ pair_peer, const int32_t* __restrict__ pair_row, int64_t n_pairs, int k,
                               int64_t D, const PeerRowsW peers, int64_t ldy) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (ItemWalker it((int64_t)blockIdx.x * 8 + warp, (int64_t)gridDim.x * 8, (int)((D + 255) >> 8)); it.row < n_pairs; it.next()) {
     const int64_t p = it.row, c = (int64_t)it.chunk * 256 + lane * 8;
@@ -666,6 +683,7 @@ moe_scatter_rows_peers_kernel(const uint16_t* __restrict__ x, int64_t ld, const 
 __global__ void __launch_bounds__(256)
 moe_zero_pad_rows_bf16_kernel(const int32_t* __restrict__ src_of_row, const int32_t* __restrict__ num_tiles, int64_t padded_rows,
                               int64_t D, uint16_t* __restrict__ buf, int64_t ld) {
+  pdl_prologue();
   int64_t live_rows = (int64_t)(*num_tiles) << 7;
   if (live_rows > padded_rows) live_rows = padded_rows;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -680,6 +698,7 @@ __global__ void __launch_bounds__(256)
 moe_pair_dots_peers_kernel(const uint16_t* __restrict__ dout, int64_t ld, const PeerRows peers, int64_t ldy,
                            const int32_t* __restrict__ pair_peer, const int32_t* __restrict__ pair_row, int64_t n_pairs, int k,
                            int64_t D, float* __restrict__ dw) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int64_t p = (int64_t)blockIdx.x * 8 + warp; p < n_pairs; p += (int64_t)gridDim.x * 8) {
     const uint16_t* yr = peers.y[pair_peer[p]] + (int64_t)pair_row[p] * ldy;
@@ -703,6 +722,7 @@ moe_pair_dots_peers_kernel(const uint16_t* __restrict__ dout, int64_t ld, const 
 __global__ void __launch_bounds__(256)
 swiglu_backward_kernel(const uint16_t* __restrict__ g, int64_t rows, int64_t I, int64_t ldg, const uint16_t* __restrict__ dh,
                        int64_t lddh, uint16_t* __restrict__ dg, int64_t lddg) {
+  pdl_prologue();
   const int runs = (int)(I >> 3);
   for (ItemWalker w((int64_t)blockIdx.x * 256 + threadIdx.x, (int64_t)gridDim.x * 256, runs); w.row < rows; w.next()) {
     const int64_t r = w.row;
@@ -723,6 +743,7 @@ moe_unpermute_backward_kernel(const uint16_t* __restrict__ dout, const uint16_t*
                               int64_t ldy, const int32_t* __restrict__ row_of, const int32_t* __restrict__ src_of_row,
                               int64_t n_pairs, int k, int64_t D, int64_t padded_rows, uint16_t* __restrict__ dy,
                               float* __restrict__ dw) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t total = n_pairs + padded_rows;
   for (int64_t it = (int64_t)blockIdx.x * 8 + warp; it < total; it += (int64_t)gridDim.x * 8) {
@@ -776,20 +797,20 @@ int run_permute_plan(const int64_t* top_idx, int64_t n_pairs, int k, int E, int3
                      cudaStream_t st) {
   const int nblocks = (int)((n_pairs + kPlanThreads - 1) / kPlanThreads);
   const int64_t padded_rows = b200q_moe_padded_rows(n_pairs, E);
-  moe_hist_kernel<<<nblocks, kPlanThreads, 0, st>>>(top_idx, n_pairs, E, block_counts);
+  launch_pdl(moe_hist_kernel, dim3(nblocks), dim3(kPlanThreads), (size_t)(0), st, top_idx, n_pairs, E, block_counts);
   B200Q_CUDA(cudaGetLastError());
   if (nblocks <= kFusedPlanBlocks) {
-    moe_scatter_tables_kernel<<<nblocks, kPlanThreads, 32 * E * sizeof(int), st>>>(
+    launch_pdl(moe_scatter_tables_kernel, dim3(nblocks), dim3(kPlanThreads), (size_t)(32 * E * sizeof(int)), st, 
         top_idx, n_pairs, k, E, block_counts, nblocks, offs, padded_offs, row_of, src_of_row, tile_expert, num_tiles,
         (int)(padded_rows / 128), padded_rows);
     B200Q_CUDA(cudaGetLastError());
     return B200Q_OK;
   }
-  B200Q_CUDA(cudaMemsetAsync(src_of_row, 0xFF, (size_t)padded_rows * sizeof(int32_t), st));   // -1 = pad row
-  moe_scan_kernel<<<1, kMaxExperts, 0, st>>>(block_counts, nblocks, E, offs, padded_offs, tile_expert, num_tiles,
+  B200Q_CUDA(memset_async(src_of_row, 0xFF, (size_t)padded_rows * sizeof(int32_t), st));   // -1 = pad row
+  launch_pdl(moe_scan_kernel, dim3(1), dim3(kMaxExperts), (size_t)(0), st, block_counts, nblocks, E, offs, padded_offs, tile_expert, num_tiles,
                                              (int)(padded_rows / 128));
   B200Q_CUDA(cudaGetLastError());
-  moe_scatter_kernel<<<nblocks, kPlanThreads, 32 * E * sizeof(int), st>>>(top_idx, n_pairs, k, E, block_counts, padded_offs,
+  launch_pdl(moe_scatter_kernel, dim3(nblocks), dim3(kPlanThreads), (size_t)(32 * E * sizeof(int)), st, top_idx, n_pairs, k, E, block_counts, padded_offs,
                                                                            row_of, src_of_row);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -828,6 +849,7 @@ int64_t b200q_moe_plan_workspace_bytes(int64_t n_pairs, int E) {
 int b200q_moe_permute_plan(const int64_t* top_idx, int64_t n_pairs, int k, int E, int32_t* offs, int32_t* padded_offs,
                            int32_t* row_of, int32_t* src_of_row, int32_t* tile_expert, int32_t* num_tiles, void* workspace,
                            void* stream) {
+  PdlChain pdl_chain;
   if (top_idx == nullptr || offs == nullptr || padded_offs == nullptr || row_of == nullptr || src_of_row == nullptr ||
       tile_expert == nullptr || num_tiles == nullptr || workspace == nullptr || n_pairs <= 0 || k <= 0 || E <= 0)
     return B200Q_ERR_INVALID_ARG;
@@ -841,6 +863,7 @@ int b200q_moe_permute_plan(const int64_t* top_idx, int64_t n_pairs, int k, int E
 
 int b200q_moe_pad_plan(const int32_t* offs, int E, int64_t n_rows, int32_t* padded_offs, int32_t* src_of_row,
                        int32_t* tile_expert, int32_t* num_tiles, void* stream) {
+  PdlChain pdl_chain;
   if (offs == nullptr || padded_offs == nullptr || src_of_row == nullptr || tile_expert == nullptr || num_tiles == nullptr ||
       E <= 0 || n_rows < 0)
     return B200Q_ERR_INVALID_ARG;
@@ -849,9 +872,9 @@ int b200q_moe_pad_plan(const int32_t* offs, int E, int64_t n_rows, int32_t* padd
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t padded_rows = b200q_moe_padded_rows(n_rows, E);
-  moe_pad_plan_kernel<<<1, kMaxExperts, 0, st>>>(offs, E, padded_offs, tile_expert, num_tiles, (int)(padded_rows / 128));
+  launch_pdl(moe_pad_plan_kernel, dim3(1), dim3(kMaxExperts), (size_t)(0), st, offs, E, padded_offs, tile_expert, num_tiles, (int)(padded_rows / 128));
   B200Q_CUDA(cudaGetLastError());
-  moe_pad_src_kernel<<<(unsigned)((padded_rows + 255) / 256), 256, 0, st>>>(offs, padded_offs, tile_expert, num_tiles, src_of_row,
+  launch_pdl(moe_pad_src_kernel, dim3((unsigned)((padded_rows + 255) / 256)), dim3(256), (size_t)(0), st, offs, padded_offs, tile_expert, num_tiles, src_of_row,
                                                                             padded_rows);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -859,6 +882,7 @@ int b200q_moe_pad_plan(const int32_t* offs, int E, int64_t n_rows, int32_t* padd
 
 int b200q_moe_gather(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row, const int32_t* num_tiles,
                      int64_t padded_rows, int quantize, int fmt, void* out, void* sf, void* stream) {
+  PdlChain pdl_chain;
   if (x == nullptr || src_of_row == nullptr || num_tiles == nullptr || out == nullptr || D <= 0 || ld < D || padded_rows <= 0 ||
       (quantize && sf == nullptr) || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
     return B200Q_ERR_INVALID_ARG;
@@ -868,11 +892,11 @@ int b200q_moe_gather(const void* x, int64_t D, int64_t ld, const int32_t* src_of
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (quantize && ((D >> 5) & 3))
-    B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(padded_rows, D >> 5, B200Q_SF_SWIZZLE_128x4), st));
+    B200Q_CUDA(memset_async(sf, 0, (size_t)b200q_sf_bytes(padded_rows, D >> 5, B200Q_SF_SWIZZLE_128x4), st));
   const bool wide = aligned32(x) && aligned32(out) && (ld & 15) == 0;
   const int grid = thread_item_grid(padded_rows * (D >> 5));
 #define B200Q_GO(Q, W, F)                                                                                              \
-  moe_gather_kernel<Q, W, F><<<grid, 256, 0, st>>>((const uint16_t*)x, D, ld, src_of_row, num_tiles, padded_rows, (uint8_t*)out, \
+  launch_pdl(moe_gather_kernel<Q, W, F>, dim3(grid), dim3(256), (size_t)(0), st, (const uint16_t*)x, D, ld, src_of_row, num_tiles, padded_rows, (uint8_t*)out, \
                                                    (uint8_t*)sf)
   if (!quantize) { if (wide) B200Q_GO(0, true, FMT_E4M3); else B200Q_GO(0, false, FMT_E4M3); }
   else if (fmt == B200Q_E4M3) { if (wide) B200Q_GO(1, true, FMT_E4M3); else B200Q_GO(1, false, FMT_E4M3); }
@@ -883,6 +907,7 @@ int b200q_moe_gather(const void* x, int64_t D, int64_t ld, const int32_t* src_of
 }
 
 int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantize, int fmt, void* out, void* sf, void* stream) {
+  PdlChain pdl_chain;
   if (g == nullptr || out == nullptr || rows <= 0 || I <= 0 || ld < 2 * I || (quantize && sf == nullptr) ||
       (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
     return B200Q_ERR_INVALID_ARG;
@@ -892,10 +917,10 @@ int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantiz
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (quantize && ((rows & 127) || ((I >> 5) & 3)))
-    B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(rows, I >> 5, B200Q_SF_SWIZZLE_128x4), st));
+    B200Q_CUDA(memset_async(sf, 0, (size_t)b200q_sf_bytes(rows, I >> 5, B200Q_SF_SWIZZLE_128x4), st));
   const bool wide = aligned32(g) && aligned32(out) && (ld & 15) == 0;
   const int grid = thread_item_grid(rows * (I >> 5));
-#define B200Q_GO(Q, W, F) swiglu_kernel<Q, W, F><<<grid, 256, 0, st>>>((const uint16_t*)g, rows, I, ld, (uint8_t*)out, (uint8_t*)sf)
+#define B200Q_GO(Q, W, F) launch_pdl(swiglu_kernel<Q, W, F>, dim3(grid), dim3(256), (size_t)(0), st, (const uint16_t*)g, rows, I, ld, (uint8_t*)out, (uint8_t*)sf)
   if (!quantize) { if (wide) B200Q_GO(0, true, FMT_E4M3); else B200Q_GO(0, false, FMT_E4M3); }
   else if (fmt == B200Q_E4M3) { if (wide) B200Q_GO(1, true, FMT_E4M3); else B200Q_GO(1, false, FMT_E4M3); }
   else { if (wide) B200Q_GO(1, true, FMT_E5M2); else B200Q_GO(1, false, FMT_E5M2); }
@@ -907,6 +932,7 @@ int b200q_swiglu(const void* g, int64_t rows, int64_t I, int64_t ld, int quantiz
 int b200q_moe_dispatch_peers(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row, const int32_t* tile_expert,
                              const int32_t* padded_offs, const int32_t* num_tiles, int64_t padded_rows, const int32_t* row_base,
                              int experts_per_rank, int world, void* const* peer_codes, void* const* peer_sf, void* stream) {
+  PdlChain pdl_chain;
   if (x == nullptr || src_of_row == nullptr || tile_expert == nullptr || padded_offs == nullptr || num_tiles == nullptr ||
       row_base == nullptr || peer_codes == nullptr || peer_sf == nullptr || D <= 0 || ld < D || padded_rows <= 0 ||
       experts_per_rank <= 0 || world < 1 || world > kMaxPeers)
@@ -922,7 +948,7 @@ int b200q_moe_dispatch_peers(const void* x, int64_t D, int64_t ld, const int32_t
   }
   int rc = require_sm100();
   if (rc) return rc;
-  moe_dispatch_kernel<<<thread_item_grid(padded_rows * (D >> 5)), 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(moe_dispatch_kernel, dim3(thread_item_grid(padded_rows * (D >> 5))), dim3(256), (size_t)(0), (cudaStream_t)stream, 
       (const uint16_t*)x, D, ld, src_of_row, tile_expert, padded_offs, num_tiles, padded_rows, row_base, experts_per_rank, peers);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -930,13 +956,14 @@ int b200q_moe_dispatch_peers(const void* x, int64_t D, int64_t ld, const int32_t
 
 int b200q_moe_zero_pad_rows(const int32_t* src_of_row, const int32_t* num_tiles, int64_t padded_rows, int64_t D, void* codes,
                             void* sf, void* stream) {
+  PdlChain pdl_chain;
   if (src_of_row == nullptr || num_tiles == nullptr || codes == nullptr || sf == nullptr || padded_rows <= 0 || D <= 0)
     return B200Q_ERR_INVALID_ARG;
   if ((D & 127) || (padded_rows & 127)) return B200Q_ERR_SHAPE;
   if (!aligned16(codes)) return B200Q_ERR_ALIGNMENT;
   int rc = require_sm100();
   if (rc) return rc;
-  moe_zero_pad_rows_kernel<<<thread_item_grid(padded_rows * (D >> 5)), 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(moe_zero_pad_rows_kernel, dim3(thread_item_grid(padded_rows * (D >> 5))), dim3(256), (size_t)(0), (cudaStream_t)stream, 
       src_of_row, num_tiles, padded_rows, D, (uint8_t*)codes, (uint8_t*)sf);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -944,6 +971,7 @@ int b200q_moe_zero_pad_rows(const int32_t* src_of_row, const int32_t* num_tiles,
 
 int b200q_moe_combine_peers(void* const* peer_y, int world, int64_t ldy, const void* w, const int32_t* pair_peer,
                             const int32_t* pair_row, int64_t T, int k, int64_t D, void* out, void* stream) {
+  PdlChain pdl_chain;
   if (peer_y == nullptr || w == nullptr || pair_peer == nullptr || pair_row == nullptr || out == nullptr || T <= 0 || k <= 0 ||
       D <= 0 || ldy < D || world < 1 || world > kMaxPeers)
     return B200Q_ERR_INVALID_ARG;
@@ -957,7 +985,7 @@ int b200q_moe_combine_peers(void* const* peer_y, int world, int64_t ldy, const v
   }
   int rc = require_sm100();
   if (rc) return rc;
-  moe_combine_kernel<<<row_grid(T * ((D + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(peers, ldy, (const uint16_t*)w, pair_peer,
+  launch_pdl(moe_combine_kernel, dim3(row_grid(T * ((D + 255) / 256))), dim3(256), (size_t)(0), (cudaStream_t)stream, peers, ldy, (const uint16_t*)w, pair_peer,
                                                                                       pair_row, T, k, D, (uint16_t*)out);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -966,6 +994,7 @@ int b200q_moe_combine_peers(void* const* peer_y, int world, int64_t ldy, const v
 int b200q_moe_ep_index(const int32_t* all_offs, int world, int rank, int E, const int64_t* top_idx, const int32_t* row_of,
                        const int32_t* padded_offs, int64_t n_pairs, int32_t* row_base, int32_t* own_offs, int32_t* pair_peer,
                        int32_t* pair_row, void* stream) {
+  PdlChain pdl_chain;
   if (all_offs == nullptr || top_idx == nullptr || row_of == nullptr || padded_offs == nullptr || row_base == nullptr ||
       own_offs == nullptr || pair_peer == nullptr || pair_row == nullptr || n_pairs <= 0 || world < 1 || world > kMaxPeers ||
       rank < 0 || rank >= world || E <= 0)
@@ -974,13 +1003,14 @@ int b200q_moe_ep_index(const int32_t* all_offs, int world, int rank, int E, cons
   int rc = require_sm100();
   if (rc) return rc;
   const int64_t want = (n_pairs + 255) / 256, cap = (int64_t)kNumSMs * 4;
-  moe_ep_index_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(moe_ep_index_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), (size_t)(0), (cudaStream_t)stream, 
       all_offs, world, rank, E, E / world, top_idx, row_of, padded_offs, n_pairs, row_base, own_offs, pair_peer, pair_row);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
 
 int b200q_peer_barrier(void* const* flag_ptrs, int world, int rank, int epoch, void* stream) {
+  PdlChain pdl_chain;
   if (flag_ptrs == nullptr || world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return B200Q_ERR_INVALID_ARG;
   PeerFlags flags = {};
   for (int i = 0; i < world; ++i) {
@@ -990,13 +1020,14 @@ int b200q_peer_barrier(void* const* flag_ptrs, int world, int rank, int epoch, v
   }
   int rc = require_sm100();
   if (rc) return rc;
-  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, world, rank, epoch);
+  launch_pdl(peer_barrier_kernel, dim3(1), dim3(32), (size_t)(0), (cudaStream_t)stream, flags, world, rank, epoch);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
 
 int b200q_moe_scatter_rows_peers(const void* x, int64_t ld, const void* w, const int32_t* pair_peer, const int32_t* pair_row, int64_t T,
                                  int k, int64_t D, void* const* peer_y, int world, int64_t ldy, void* stream) {
+  PdlChain pdl_chain;
   if (x == nullptr || pair_peer == nullptr || pair_row == nullptr || peer_y == nullptr || T <= 0 || k <= 0 || D <= 0 || ld < D ||
       ldy < D || world < 1 || world > kMaxPeers)
     return B200Q_ERR_INVALID_ARG;
@@ -1010,7 +1041,7 @@ int b200q_moe_scatter_rows_peers(const void* x, int64_t ld, const void* w, const
   }
   int rc = require_sm100();
   if (rc) return rc;
-  moe_scatter_rows_peers_kernel<<<row_grid(T * k * ((D + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(moe_scatter_rows_peers_kernel, dim3(row_grid(T * k * ((D + 255) / 256))), dim3(256), (size_t)(0), (cudaStream_t)stream, 
       (const uint16_t*)x, ld, (const uint16_t*)w, pair_peer, pair_row, T * k, k, D, peers, ldy);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -1018,12 +1049,13 @@ int b200q_moe_scatter_rows_peers(const void* x, int64_t ld, const void* w, const
 
 int b200q_moe_zero_pad_rows_bf16(const int32_t* src_of_row, const int32_t* num_tiles, int64_t padded_rows, int64_t D, void* buf,
                                  int64_t ld, void* stream) {
+  PdlChain pdl_chain;
   if (src_of_row == nullptr || num_tiles == nullptr || buf == nullptr || padded_rows <= 0 || D <= 0 || ld < D) return B200Q_ERR_INVALID_ARG;
   if ((D & 7) || (ld & 7) || (padded_rows & 127)) return B200Q_ERR_SHAPE;
   if (!aligned16(buf)) return B200Q_ERR_ALIGNMENT;
   int rc = require_sm100();
   if (rc) return rc;
-  moe_zero_pad_rows_bf16_kernel<<<row_grid(padded_rows), 256, 0, (cudaStream_t)stream>>>(src_of_row, num_tiles, padded_rows, D,
+  launch_pdl(moe_zero_pad_rows_bf16_kernel, dim3(row_grid(padded_rows)), dim3(256), (size_t)(0), (cudaStream_t)stream, src_of_row, num_tiles, padded_rows, D,
                                                                                         (uint16_t*)buf, ld);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -1031,6 +1063,7 @@ int b200q_moe_zero_pad_rows_bf16(const int32_t* src_of_row, const int32_t* num_t
 
 int b200q_moe_pair_dots_peers(const void* dout, int64_t ld, void* const* peer_y, int world, int64_t ldy, const int32_t* pair_peer,
                               const int32_t* pair_row, int64_t T, int k, int64_t D, float* dw, void* stream) {
+  PdlChain pdl_chain;
   if (dout == nullptr || peer_y == nullptr || pair_peer == nullptr || pair_row == nullptr || dw == nullptr || T <= 0 || k <= 0 ||
       D <= 0 || ld < D || ldy < D || world < 1 || world > kMaxPeers)
     return B200Q_ERR_INVALID_ARG;
@@ -1044,7 +1077,7 @@ int b200q_moe_pair_dots_peers(const void* dout, int64_t ld, void* const* peer_y,
   }
   int rc = require_sm100();
   if (rc) return rc;
-  moe_pair_dots_peers_kernel<<<row_grid(T * k), 256, 0, (cudaStream_t)stream>>>((const uint16_t*)dout, ld, peers, ldy, pair_peer, pair_row,
+  launch_pdl(moe_pair_dots_peers_kernel, dim3(row_grid(T * k)), dim3(256), (size_t)(0), (cudaStream_t)stream, (const uint16_t*)dout, ld, peers, ldy, pair_peer, pair_row,
                                                                                T * k, k, D, dw);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -1052,13 +1085,14 @@ int b200q_moe_pair_dots_peers(const void* dout, int64_t ld, void* const* peer_y,
 
 int b200q_swiglu_backward(const void* g, int64_t rows, int64_t I, int64_t ldg, const void* dh, int64_t lddh, void* dg, int64_t lddg,
                           void* stream) {
+  PdlChain pdl_chain;
   if (g == nullptr || dh == nullptr || dg == nullptr || rows <= 0 || I <= 0 || ldg < 2 * I || lddh < I || lddg < 2 * I)
     return B200Q_ERR_INVALID_ARG;
   if ((I & 7) || (ldg & 7) || (lddh & 7) || (lddg & 7)) return B200Q_ERR_SHAPE;
   if (!aligned16(g) || !aligned16(dh) || !aligned16(dg)) return B200Q_ERR_ALIGNMENT;
   int rc = require_sm100();
   if (rc) return rc;
-  swiglu_backward_kernel<<<thread_item_grid(rows * (I >> 3)), 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(swiglu_backward_kernel, dim3(thread_item_grid(rows * (I >> 3))), dim3(256), (size_t)(0), (cudaStream_t)stream, 
       (const uint16_t*)g, rows, I, ldg, (const uint16_t*)dh, lddh, (uint16_t*)dg, lddg);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -1067,6 +1101,7 @@ int b200q_swiglu_backward(const void* g, int64_t rows, int64_t I, int64_t ldg, c
 int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y, int64_t ldy, const int32_t* row_of,
                                  const int32_t* src_of_row, int64_t T, int k, int64_t D, int64_t padded_rows, void* dy, float* dw,
                                  void* stream) {
+  PdlChain pdl_chain;
   if (dout == nullptr || w == nullptr || row_of == nullptr || src_of_row == nullptr || (dy == nullptr && dw == nullptr) || T <= 0 ||
       k <= 0 || D <= 0 || padded_rows <= 0 || (y != nullptr && ldy < D) || (dw != nullptr && y == nullptr))
     return B200Q_ERR_INVALID_ARG;
@@ -1074,7 +1109,7 @@ int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y,
   if (!aligned16(dout) || (dy != nullptr && !aligned16(dy)) || (y != nullptr && !aligned16(y))) return B200Q_ERR_ALIGNMENT;
   int rc = require_sm100();
   if (rc) return rc;
-  moe_unpermute_backward_kernel<<<row_grid(T * k + (dy != nullptr ? padded_rows : 0)), 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(moe_unpermute_backward_kernel, dim3(row_grid(T * k + (dy != nullptr ? padded_rows : 0))), dim3(256), (size_t)(0), (cudaStream_t)stream, 
       (const uint16_t*)dout, (const uint16_t*)w, (const uint16_t*)y, ldy, row_of, src_of_row, T * k, k, D,
       dy != nullptr ? padded_rows : 0, (uint16_t*)dy, dw);
   B200Q_CUDA(cudaGetLastError());
@@ -1084,20 +1119,21 @@ int b200q_moe_unpermute_backward(const void* dout, const void* w, const void* y,
 int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int score_fn, int normalize, int64_t* top_idx,
                           void* top_w, void* probs, int32_t* expert_counts, const float* select_bias, int out_fp32,
                           void* stream) {
+  PdlChain pdl_chain;
   if (logits == nullptr || top_idx == nullptr || top_w == nullptr || T <= 0 || E <= 0 || k <= 0 || (score_fn != 0 && score_fn != 1))
     return B200Q_ERR_INVALID_ARG;
   if (E > kMaxExperts || k > 32 || k > E) return B200Q_ERR_SHAPE;
   int rc = require_sm100();
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  if (expert_counts != nullptr) B200Q_CUDA(cudaMemsetAsync(expert_counts, 0, (size_t)E * sizeof(int32_t), st));
+  if (expert_counts != nullptr) B200Q_CUDA(memset_async(expert_counts, 0, (size_t)E * sizeof(int32_t), st));
 #define B200Q_GO(P)                                                                                                          \
   do {                                                                                                                       \
     if (select_bias != nullptr)                                                                                              \
-      moe_router_topk_kernel<P, true><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, top_w, probs,       \
+      launch_pdl(moe_router_topk_kernel<P, true>, dim3(row_grid(T)), dim3(256), (size_t)(0), st, logits, T, E, k, score_fn, normalize, top_idx, top_w, probs,       \
                                                                    expert_counts, select_bias, out_fp32);                    \
     else                                                                                                                     \
-      moe_router_topk_kernel<P, false><<<row_grid(T), 256, 0, st>>>(logits, T, E, k, score_fn, normalize, top_idx, top_w, probs,      \
+      launch_pdl(moe_router_topk_kernel<P, false>, dim3(row_grid(T)), dim3(256), (size_t)(0), st, logits, T, E, k, score_fn, normalize, top_idx, top_w, probs,      \
                                                                     expert_counts, nullptr, out_fp32);                       \
   } while (0)
   if (E <= 32) B200Q_GO(1);
@@ -1110,25 +1146,27 @@ int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int scor
 }
 
 int b200q_moe_pair_of_row(const int32_t* row_of, int64_t n_pairs, int64_t padded_rows, int32_t* pair_of_row, void* stream) {
+  PdlChain pdl_chain;
   if (row_of == nullptr || pair_of_row == nullptr || n_pairs <= 0 || padded_rows <= 0 || n_pairs > INT32_MAX) return B200Q_ERR_INVALID_ARG;
   int rc = require_sm100();
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  B200Q_CUDA(cudaMemsetAsync(pair_of_row, 0xff, (size_t)padded_rows * sizeof(int32_t), st));      // -1 everywhere
-  moe_pair_of_row_kernel<<<(unsigned)((n_pairs + 255) / 256), 256, 0, st>>>(row_of, n_pairs, padded_rows, pair_of_row);
+  B200Q_CUDA(memset_async(pair_of_row, 0xff, (size_t)padded_rows * sizeof(int32_t), st));      // -1 everywhere
+  launch_pdl(moe_pair_of_row_kernel, dim3((unsigned)((n_pairs + 255) / 256)), dim3(256), (size_t)(0), st, row_of, n_pairs, padded_rows, pair_of_row);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
 
 int b200q_moe_unpermute(const void* y, int64_t ldy, const void* w, const int32_t* row_of, int64_t T, int k, int64_t D, void* out,
                         void* stream) {
+  PdlChain pdl_chain;
   if (y == nullptr || row_of == nullptr || out == nullptr || T <= 0 || k <= 0 || D <= 0 || ldy < D)
     return B200Q_ERR_INVALID_ARG;
   if ((D & 7) || (ldy & 7)) return B200Q_ERR_SHAPE;
   if (!aligned16(y) || !aligned16(out)) return B200Q_ERR_ALIGNMENT;
   int rc = require_sm100();
   if (rc) return rc;
-  moe_unpermute_kernel<<<row_grid(T * ((D + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(moe_unpermute_kernel, dim3(row_grid(T * ((D + 255) / 256))), dim3(256), (size_t)(0), (cudaStream_t)stream, 
       (const uint16_t*)y, ldy, (const uint16_t*)w, row_of, T, k, D, (uint16_t*)out);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -1148,6 +1186,7 @@ int b200q_moe_unpermute(const void* y, int64_t ldy, const void* w, const int32_t
 int b200q_moe_permute_plan_static(const int64_t* top_idx, int64_t n_pairs, int k, int E, int32_t* offs,
                                   int32_t* padded_offs, int32_t* row_of, int32_t* src_of_row, int32_t* tile_expert,
                                   int32_t* num_tiles, void* stream) {
+  PdlChain pdl_chain;
   if (top_idx == nullptr || offs == nullptr || padded_offs == nullptr || row_of == nullptr || src_of_row == nullptr ||
       tile_expert == nullptr || num_tiles == nullptr || n_pairs <= 0 || k <= 0 || E <= 0)
     return B200Q_ERR_INVALID_ARG;

@@ -43,6 +43,7 @@ __device__ __forceinline__ float warp_max(float v) {
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads) amax_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
                                                         int64_t ld, float* __restrict__ amax) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t m = 0;
   // work item = (row, 1024-column chunk); items are dealt round-robin to all warps of the grid
@@ -99,7 +100,7 @@ template <int MODE, bool WIDE, int FMT>
 __global__ void __launch_bounds__(kThreads)
 rowwise_block_quant_kernel(const RowQuantJob first, const RowQuantJob second, int swz,
                            const float* __restrict__ tensor_amax, float* __restrict__ tensor_scale_out) {
-  grid_launch_dependents();                    // the whole grid is resident: a GEMM launched behind this kernel may set up now
+  pdl_prologue();
   constexpr int BS = MODE == MODE_MX ? 32 : 16;
   float s_t = 0.f, rcp_st = 0.f;
   if (MODE == MODE_NV) {
@@ -125,7 +126,7 @@ rowwise_block_quant_kernel(const RowQuantJob first, const RowQuantJob second, in
       uint4 v[4];
       ld_nc_32B<WIDE>(xp, v[0], v[1]);
       ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
-      const int64_t row = dst_row ? (int64_t)__ldg(dst_row + w.row) : w.row;   // output row (codes and scale factors)
+      const int64_t row = dst_row ? (int64_t)__ldcg(dst_row + w.row) : w.row;   // output row (codes and scale factors)
       if (MODE == MODE_MX) {
         uint32_t o[8];
         const int e = mx_quant_block32<FMT>(v, o);
@@ -176,6 +177,7 @@ __global__ void __launch_bounds__(kThreads)
 rowwise_fp8_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                    uint8_t* __restrict__ codes, float* __restrict__ scales, const float* __restrict__ tensor_amax,
                    float* __restrict__ tensor_scale_out, int wpr, float qmax, unsigned int* __restrict__ col_partials = nullptr) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int fmt = FMT;
   const int grp = warp / wpr, wig = warp - grp * wpr, rpc = kWarps / wpr;
@@ -276,6 +278,7 @@ constexpr int kRedWords = 8, kRedSlices = 128;        // a CTA: 8 packed column 
 __global__ void __launch_bounds__(kRedWords * kRedSlices)
 col_partials_to_scale_kernel(const unsigned int* __restrict__ partials, int nparts, int64_t cols, int fmt, float qmax,
                              float* __restrict__ scales) {
+  pdl_prologue();
   // few loads per thread (nparts / 128), many CTAs: the reduction is a chain of load latencies, not of bytes
   __shared__ uint32_t red[kRedSlices][kRedWords + 1];
   const int tx = threadIdx.x & (kRedWords - 1), ty = threadIdx.x / kRedWords;
@@ -303,6 +306,7 @@ col_partials_to_scale_kernel(const unsigned int* __restrict__ partials, int npar
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 col_amax_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, unsigned int* __restrict__ amax_bits) {
+  pdl_prologue();
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int64_t c = ((int64_t)blockIdx.x * 32 + tx) * 8;
   uint32_t m[4] = {0, 0, 0, 0};
@@ -338,6 +342,7 @@ col_amax_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int6
 }
 
 __global__ void amax_to_scale_kernel(float* __restrict__ scales, int64_t n, int fmt, float qmax) {
+  pdl_prologue();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) scales[i] = scale_from_amax(scales[i], fmt, qmax);
 }
@@ -356,6 +361,7 @@ transpose_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t col
                        uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, int swz,
                        const float* __restrict__ col_scales, const float* __restrict__ tensor_amax,
                        float* __restrict__ tensor_scale_out, float qmax) {
+  pdl_prologue();
   __shared__ __align__(16) uint16_t tin[kTR * kTC];
   constexpr int OUT_PITCH = (MODE == MODE_NV ? kTR / 2 : kTR) + 16;
   __shared__ __align__(16) uint8_t tout[kTC * OUT_PITCH];
@@ -592,13 +598,14 @@ template <int FMT, bool WIDE, int SRC = SRC_PLAIN>
 __global__ void __launch_bounds__(kThreads)
 mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __restrict__ codes_r,
                      uint8_t* __restrict__ sf_r, uint8_t* __restrict__ codes_c, uint8_t* __restrict__ sf_c, int swz) {
+  pdl_prologue();
   extern __shared__ __align__(16) uint8_t dual_smem[];
   constexpr int NT = tile_parts<SRC>();
   // part t covers columns [t * width + c0, ...) below (t + 1) * width of the output matrix
   const int64_t width = NT == 2 ? src.I : cols;
   const int tid = threadIdx.x;
   const int64_t c0 = (int64_t)blockIdx.x * kDT, r0 = (int64_t)blockIdx.y * kDT;
-  if (src.live_tiles != nullptr && r0 >= ((int64_t)__ldg(src.live_tiles) << 7)) return;      // CTA-uniform: kDT == 128
+  if (src.live_tiles != nullptr && r0 >= ((int64_t)__ldcg(src.live_tiles) << 7)) return;      // CTA-uniform: kDT == 128
   const int64_t nblk_r = cols >> 5, kt_r = (nblk_r + 3) >> 2;
 
 #pragma unroll
@@ -678,6 +685,7 @@ mx_tile_quant_kernel(const TileSrc src, int64_t rows, int64_t cols, uint8_t* __r
 // dw[pair] = sum over the column tiles of the partial dot products of the pair's row (0 for a dropped pair).
 __global__ void dot_partials_to_pairs_kernel(const float* __restrict__ partial, int parts, int64_t rows,
                                              const int32_t* __restrict__ row_of, int64_t n_pairs, float* __restrict__ dw) {
+  pdl_prologue();
   const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= n_pairs) return;
   const int r = row_of[p];
@@ -697,7 +705,7 @@ int launch_mx_tile_quant(const TileSrc& src, bool aligned_src, int64_t rows, int
   do {                                                                                                                  \
     auto kernel = mx_tile_quant_kernel<F, W, SRC>;                                                                      \
     B200Q_CUDA(ensure_dynamic_smem(kernel, NT * kDualSmem));                                                           \
-    kernel<<<grid, kThreads, NT * kDualSmem, st>>>(src, rows, cols, codes_r, sf_r, codes_c, sf_c, swz);                 \
+    launch_pdl(kernel, dim3(grid), dim3(kThreads), (size_t)(NT * kDualSmem), st, src, rows, cols, codes_r, sf_r, codes_c, sf_c, swz);                 \
   } while (0)
   if (fmt == FMT_E4M3) { if (wide) B200Q_GO(FMT_E4M3, true); else B200Q_GO(FMT_E4M3, false); }
   else { if (wide) B200Q_GO(FMT_E5M2, true); else B200Q_GO(FMT_E5M2, false); }
@@ -718,6 +726,7 @@ template <int FMT, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
 fp8_col_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                           const float* __restrict__ col_scales, uint8_t* __restrict__ codes_c, float qmax) {
+  pdl_prologue();
   extern __shared__ __align__(16) uint8_t dual_smem[];
   uint8_t* tin = dual_smem;
   uint8_t* tout = dual_smem;                  // written only after every thread has read its columns (barrier below)
@@ -747,7 +756,7 @@ fp8_col_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t 
     for (int i = 0; i < 32; ++i) w[i] = col[i * (kDPitch / 4)];
     __syncthreads();                            // all column reads done: the tile may be overwritten
     const int64_t gc = c0 + 2 * cp;
-    const float s0 = gc < cols ? __ldg(col_scales + gc) : 1.f, s1 = gc + 1 < cols ? __ldg(col_scales + gc + 1) : 1.f;
+    const float s0 = gc < cols ? __ldcg(col_scales + gc) : 1.f, s1 = gc + 1 < cols ? __ldcg(col_scales + gc + 1) : 1.f;
     const float rc0 = rcp_rn(s0), rc1 = rcp_rn(s1);
     uint32_t o0[8], o1[8];
 #pragma unroll
@@ -785,7 +794,7 @@ int rowwise_grid(Kernel kernel, int64_t items, int per_cta) {
 
 int zero_sf_pads(void* sf, int64_t outer, int64_t nblk, int layout, cudaStream_t st) {
   if (layout == B200Q_SF_SWIZZLE_128x4 && ((outer & 127) || (nblk & 3)))
-    B200Q_CUDA(cudaMemsetAsync(sf, 0, (size_t)b200q_sf_bytes(outer, nblk, layout), st));
+    B200Q_CUDA(memset_async(sf, 0, (size_t)b200q_sf_bytes(outer, nblk, layout), st));
   return B200Q_OK;
 }
 
@@ -795,7 +804,7 @@ void launch_rowwise_block(const RowQuantJob& j0, const RowQuantJob& j1, int swz,
                           cudaStream_t st) {
   auto kernel = rowwise_block_quant_kernel<MODE, WIDE, FMT>;
   const int64_t items = j0.rows * (j0.cols / 32) + j1.rows * (j1.cols / 32);
-  kernel<<<rowwise_grid(kernel, items, kThreads), kThreads, 0, st>>>(j0, j1, swz, tensor_amax, tensor_scale_out);
+  launch_pdl(kernel, dim3(rowwise_grid(kernel, items, kThreads)), dim3(kThreads), (size_t)(0), st, j0, j1, swz, tensor_amax, tensor_scale_out);
 }
 // 256-bit loads and stores need 32-byte aligned rows on both sides
 inline bool job_is_wide(const RowQuantJob& j) { return j.rows == 0 || (aligned32(j.x) && aligned32(j.codes) && (j.ld & 15) == 0); }
@@ -821,11 +830,11 @@ void launch_transpose(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld,
                       float qmax = 0.f) {
   dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
   if (MODE == MODE_FP8 && fmt == FMT_I8)
-    transpose_quant_kernel<MODE_FP8, FMT_I8><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
+    launch_pdl(transpose_quant_kernel<MODE_FP8, FMT_I8>, dim3(grid), dim3(kThreads), (size_t)(0), st, x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
   else if (MODE == MODE_NV || fmt == FMT_E4M3)
-    transpose_quant_kernel<MODE, FMT_E4M3><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
+    launch_pdl(transpose_quant_kernel<MODE, FMT_E4M3>, dim3(grid), dim3(kThreads), (size_t)(0), st, x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
   else
-    transpose_quant_kernel<MODE, FMT_E5M2><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
+    launch_pdl(transpose_quant_kernel<MODE, FMT_E5M2>, dim3(grid), dim3(kThreads), (size_t)(0), st, x, rows, cols, ld, codes, sf, swz, col_scales, tensor_amax, tensor_scale_out, qmax);
 }
 
 // Per-column codes from given column scales: the tile kernel on whole 32 x 32 blocks, else the general transposing kernel.
@@ -839,8 +848,8 @@ void launch_fp8_cols(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, 
   const bool wide = rows_32B_aligned(x, ld);
 #define B200Q_TILE(F)                                                                                                        \
   do {                                                                                                                       \
-    if (wide) fp8_col_tile_quant_kernel<F, true><<<grid, kThreads, kDualSmem, st>>>(x, rows, cols, ld, col_scales, codes, qmax);      \
-    else fp8_col_tile_quant_kernel<F, false><<<grid, kThreads, kDualSmem, st>>>(x, rows, cols, ld, col_scales, codes, qmax);          \
+    if (wide) launch_pdl(fp8_col_tile_quant_kernel<F, true>, dim3(grid), dim3(kThreads), (size_t)(kDualSmem), st, x, rows, cols, ld, col_scales, codes, qmax);      \
+    else launch_pdl(fp8_col_tile_quant_kernel<F, false>, dim3(grid), dim3(kThreads), (size_t)(kDualSmem), st, x, rows, cols, ld, col_scales, codes, qmax);          \
   } while (0)
   if (fmt == FMT_I8) B200Q_TILE(FMT_I8);
   else if (fmt == FMT_E4M3) B200Q_TILE(FMT_E4M3);
@@ -887,13 +896,14 @@ int64_t b200q_sf_bytes(int64_t outer, int64_t nblk, int sf_layout) {
 }
 
 int b200q_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, float* amax, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (amax == nullptr) return B200Q_ERR_INVALID_ARG;
   if ((rc = require_sm100())) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  B200Q_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), st));
-  amax_kernel<<<rowwise_grid(amax_kernel, rows * ((cols + 1023) / 1024), kWarps), kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, amax);
+  B200Q_CUDA(memset_async(amax, 0, sizeof(float), st));
+  launch_pdl(amax_kernel, dim3(rowwise_grid(amax_kernel, rows * ((cols + 1023) / 1024), kWarps)), dim3(kThreads), (size_t)(0), st, (const uint16_t*)x, rows, cols, ld, amax);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -911,11 +921,11 @@ static int launch_rowwise_fp8(const uint16_t* x, int64_t rows, int64_t cols, int
 #define B200Q_LAUNCH(NV)                                                                                                   \
   do {                                                                                                                     \
     if (fmt == FMT_E4M3)                                                                                                   \
-      rowwise_fp8_kernel<NV, FMT_E4M3><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr, qmax); \
+      launch_pdl(rowwise_fp8_kernel<NV, FMT_E4M3>, dim3(grid), dim3(kThreads), (size_t)(0), st, x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr, qmax, nullptr); \
     else if (fmt == FMT_E5M2)                                                                                              \
-      rowwise_fp8_kernel<NV, FMT_E5M2><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr, qmax); \
+      launch_pdl(rowwise_fp8_kernel<NV, FMT_E5M2>, dim3(grid), dim3(kThreads), (size_t)(0), st, x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr, qmax, nullptr); \
     else                                                                                                                   \
-      rowwise_fp8_kernel<NV, FMT_I8><<<grid, kThreads, 0, st>>>(x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr, qmax); \
+      launch_pdl(rowwise_fp8_kernel<NV, FMT_I8>, dim3(grid), dim3(kThreads), (size_t)(0), st, x, rows, cols, ld, codes, scales, tensor_amax, tensor_scale_out, wpr, qmax, nullptr); \
   } while (0)
   if (nvec <= 1) B200Q_LAUNCH(1);
   else if (nvec <= 2) B200Q_LAUNCH(2);
@@ -930,6 +940,7 @@ static int launch_rowwise_fp8(const uint16_t* x, int64_t rows, int64_t cols, int
 
 int b200q_quantize_fp8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int fmt, void* codes,
                        float* scales, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes == nullptr || scales == nullptr || (axis != 0 && axis != 1) || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
@@ -939,16 +950,16 @@ int b200q_quantize_fp8(const void* x, int64_t rows, int64_t cols, int64_t ld, in
   cudaStream_t st = (cudaStream_t)stream;
   if (axis == 1) return launch_rowwise_fp8((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, scales, nullptr, nullptr, st);
   if (rows & 15) return B200Q_ERR_SHAPE;
-  B200Q_CUDA(cudaMemsetAsync(scales, 0, (size_t)cols * sizeof(float), st));
+  B200Q_CUDA(memset_async(scales, 0, (size_t)cols * sizeof(float), st));
   {
     dim3 grid((unsigned)((cols / 8 + 31) / 32), 1);
     int64_t ymax = (rows + kWarps * 4 - 1) / (kWarps * 4);
     int64_t want = (int64_t)kNumSMs * 4 / grid.x + 1;
     grid.y = (unsigned)(want < ymax ? want : ymax);
-    col_amax_kernel<<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, (unsigned int*)scales);
+    launch_pdl(col_amax_kernel, dim3(grid), dim3(kThreads), (size_t)(0), st, (const uint16_t*)x, rows, cols, ld, (unsigned int*)scales);
     B200Q_CUDA(cudaGetLastError());
   }
-  amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, fmt, 0.f);
+  launch_pdl(amax_to_scale_kernel, dim3((unsigned)((cols + 255) / 256)), dim3(256), (size_t)(0), st, scales, cols, fmt, 0.f);
   B200Q_CUDA(cudaGetLastError());
   launch_fp8_cols((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, scales, st);
   B200Q_CUDA(cudaGetLastError());
@@ -962,6 +973,7 @@ int64_t b200q_quantize_fp8_both_workspace_bytes(int64_t cols) { return cols > 0 
 
 int b200q_quantize_fp8_both(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt, void* codes_row, float* scales_row,
                             void* codes_col, float* scales_col, void* workspace, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes_row == nullptr || scales_row == nullptr || codes_col == nullptr || scales_col == nullptr || workspace == nullptr ||
@@ -984,7 +996,7 @@ int b200q_quantize_fp8_both(const void* x, int64_t rows, int64_t cols, int64_t l
   const int grid = (int)(want < wave ? want : wave);
   const size_t smem = (size_t)rpc * cols * 2;          // packed bf16 column maxima of every row group
 #define B200Q_GO(NV, F)                                                                                                      \
-  rowwise_fp8_kernel<NV, F, true><<<grid, kThreads, smem, st>>>(xp, rows, cols, ld, (uint8_t*)codes_row, scales_row, nullptr, nullptr, \
+  launch_pdl(rowwise_fp8_kernel<NV, F, true>, dim3(grid), dim3(kThreads), (size_t)(smem), st, xp, rows, cols, ld, (uint8_t*)codes_row, scales_row, nullptr, nullptr, \
                                                                 wpr, 0.f, parts)
 #define B200Q_PICK(NV) do { if (fmt == FMT_E4M3) B200Q_GO(NV, FMT_E4M3); else B200Q_GO(NV, FMT_E5M2); } while (0)
   if (nvec <= 1) B200Q_PICK(1);
@@ -995,7 +1007,7 @@ int b200q_quantize_fp8_both(const void* x, int64_t rows, int64_t cols, int64_t l
 #undef B200Q_GO
   B200Q_CUDA(cudaGetLastError());
   // pass 2: column scales, then the transposed codes
-  col_partials_to_scale_kernel<<<(unsigned)((cols / 2 + kRedWords - 1) / kRedWords), kRedWords * kRedSlices, 0, st>>>(parts, grid, cols, fmt,
+  launch_pdl(col_partials_to_scale_kernel, dim3((unsigned)((cols / 2 + kRedWords - 1) / kRedWords)), dim3(kRedWords * kRedSlices), (size_t)(0), st, parts, grid, cols, fmt,
                                                                                                                 0.f, scales_col);
   B200Q_CUDA(cudaGetLastError());
   launch_fp8_cols(xp, rows, cols, ld, fmt, (uint8_t*)codes_col, scales_col, st);     // the second read comes mostly from L2
@@ -1006,6 +1018,7 @@ int b200q_quantize_fp8_both(const void* x, int64_t rows, int64_t cols, int64_t l
 // int8 series: the FP8 kernels with integer rounding and qmax = 2^(bits-1) - 1 (src/quant/int8.py:9-19)
 int b200q_quantize_int8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int qmax, void* codes, float* scales,
                         void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes == nullptr || scales == nullptr || (axis != 0 && axis != 1) || qmax < 1 || qmax > 127) return B200Q_ERR_INVALID_ARG;
@@ -1015,16 +1028,16 @@ int b200q_quantize_int8(const void* x, int64_t rows, int64_t cols, int64_t ld, i
   if (axis == 1)
     return launch_rowwise_fp8((const uint16_t*)x, rows, cols, ld, FMT_I8, (uint8_t*)codes, scales, nullptr, nullptr, st, (float)qmax);
   if (rows & 15) return B200Q_ERR_SHAPE;
-  B200Q_CUDA(cudaMemsetAsync(scales, 0, (size_t)cols * sizeof(float), st));
+  B200Q_CUDA(memset_async(scales, 0, (size_t)cols * sizeof(float), st));
   {
     dim3 grid((unsigned)((cols / 8 + 31) / 32), 1);
     int64_t ymax = (rows + kWarps * 4 - 1) / (kWarps * 4);
     int64_t want = (int64_t)kNumSMs * 4 / grid.x + 1;
     grid.y = (unsigned)(want < ymax ? want : ymax);
-    col_amax_kernel<<<grid, kThreads, 0, st>>>((const uint16_t*)x, rows, cols, ld, (unsigned int*)scales);
+    launch_pdl(col_amax_kernel, dim3(grid), dim3(kThreads), (size_t)(0), st, (const uint16_t*)x, rows, cols, ld, (unsigned int*)scales);
     B200Q_CUDA(cudaGetLastError());
   }
-  amax_to_scale_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scales, cols, FMT_I8, (float)qmax);
+  launch_pdl(amax_to_scale_kernel, dim3((unsigned)((cols + 255) / 256)), dim3(256), (size_t)(0), st, scales, cols, FMT_I8, (float)qmax);
   B200Q_CUDA(cudaGetLastError());
   launch_fp8_cols((const uint16_t*)x, rows, cols, ld, FMT_I8, (uint8_t*)codes, scales, st, (float)qmax);
   B200Q_CUDA(cudaGetLastError());
@@ -1033,6 +1046,7 @@ int b200q_quantize_int8(const void* x, int64_t rows, int64_t cols, int64_t ld, i
 
 int b200q_quantize_int8_tensorwise(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose, int qmax,
                                    const float* tensor_amax, void* codes, float* scale_out, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes == nullptr || tensor_amax == nullptr || scale_out == nullptr || qmax < 1 || qmax > 127) return B200Q_ERR_INVALID_ARG;
@@ -1051,6 +1065,7 @@ int b200q_quantize_int8_tensorwise(const void* x, int64_t rows, int64_t cols, in
 
 int b200q_quantize_fp8_tensorwise(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose, int fmt,
                                   const float* tensor_amax, void* codes, float* scale_out, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes == nullptr || tensor_amax == nullptr || scale_out == nullptr || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2))
@@ -1068,6 +1083,7 @@ int b200q_quantize_fp8_tensorwise(const void* x, int64_t rows, int64_t cols, int
 
 int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, int fmt, void* codes,
                          void* sf, int sf_layout, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes == nullptr || sf == nullptr || (axis != 0 && axis != 1) || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2) ||
@@ -1089,6 +1105,7 @@ int b200q_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld, 
 
 int b200q_quantize_mxfp8_dual(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt, void* codes_row, void* sf_row,
                               void* codes_col, void* sf_col, int sf_layout, const int32_t* num_tiles, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes_row == nullptr || sf_row == nullptr || codes_col == nullptr || sf_col == nullptr ||
@@ -1117,6 +1134,7 @@ static int check_dual_out(void* codes_row, void* sf_row, void* codes_col, void* 
 int b200q_moe_gather_quantize_dual(const void* x, int64_t D, int64_t ld, const int32_t* src_of_row, int64_t padded_rows, int fmt,
                                    void* codes_row, void* sf_row, void* codes_col, void* sf_col, const int32_t* num_tiles,
                                    void* stream) {
+  PdlChain pdl_chain;
   int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
   if (rc) return rc;
   if (x == nullptr || src_of_row == nullptr || D <= 0 || ld < D || padded_rows <= 0) return B200Q_ERR_INVALID_ARG;
@@ -1134,6 +1152,7 @@ int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, con
                                                void* codes_col, void* sf_col, const void* y, int64_t ldy,
                                                const int32_t* row_of, int64_t n_pairs, float* dot_workspace, float* dw,
                                                void* stream) {
+  PdlChain pdl_chain;
   int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
   if (rc) return rc;
   if (dout == nullptr || w == nullptr || pair_of_row == nullptr || k <= 0 || D <= 0 || ld < D || padded_rows <= 0)
@@ -1157,7 +1176,7 @@ int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, con
   rc = launch_mx_tile_quant<SRC_SCALED_GATHER>(src, wide, padded_rows, D, fmt, (uint8_t*)codes_row, (uint8_t*)sf_row,
                                                (uint8_t*)codes_col, (uint8_t*)sf_col, B200Q_SF_SWIZZLE_128x4, st);
   if (rc || dw == nullptr) return rc;
-  dot_partials_to_pairs_kernel<<<(unsigned)((n_pairs + kThreads - 1) / kThreads), kThreads, 0, st>>>(
+  launch_pdl(dot_partials_to_pairs_kernel, dim3((unsigned)((n_pairs + kThreads - 1) / kThreads)), dim3(kThreads), (size_t)(0), st, 
       dot_workspace, (int)(D / kDT), padded_rows, row_of, n_pairs, dw);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -1165,6 +1184,7 @@ int b200q_moe_unpermute_backward_quantize_dual(const void* dout, int64_t ld, con
 
 int b200q_swiglu_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, int fmt, void* codes_row, void* sf_row,
                                void* codes_col, void* sf_col, const int32_t* num_tiles, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
   if (rc) return rc;
   if (g == nullptr || rows <= 0 || I <= 0 || ldg < 2 * I) return B200Q_ERR_INVALID_ARG;
@@ -1181,6 +1201,7 @@ int b200q_swiglu_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t l
 int b200q_swiglu_backward_quantize_dual(const void* g, int64_t rows, int64_t I, int64_t ldg, const void* dh, int64_t lddh, int fmt,
                                         void* codes_row, void* sf_row, void* codes_col, void* sf_col, const int32_t* num_tiles,
                                         void* stream) {
+  PdlChain pdl_chain;
   int rc = check_dual_out(codes_row, sf_row, codes_col, sf_col, fmt);
   if (rc) return rc;
   if (g == nullptr || dh == nullptr || rows <= 0 || I <= 0 || ldg < 2 * I || lddh < I) return B200Q_ERR_INVALID_ARG;
@@ -1196,6 +1217,7 @@ int b200q_swiglu_backward_quantize_dual(const void* g, int64_t rows, int64_t I, 
 
 int b200q_quantize_mxfp8_rowmap(const void* x, int64_t rows, int64_t cols, int64_t ld, int fmt, const int32_t* dst_row,
                                 void* codes, void* sf, int sf_layout, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes == nullptr || sf == nullptr || dst_row == nullptr || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2) ||
@@ -1215,6 +1237,7 @@ int b200q_quantize_mxfp8_rowmap(const void* x, int64_t rows, int64_t cols, int64
 int b200q_quantize_nvfp4_rowmap(const void* x, int64_t rows, int64_t cols, int64_t ld, const float* tensor_amax,
                                 const int32_t* dst_row, void* codes, void* sf, int sf_layout, float* tensor_scale_out,
                                 void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes == nullptr || sf == nullptr || tensor_amax == nullptr || tensor_scale_out == nullptr || dst_row == nullptr ||
@@ -1233,6 +1256,7 @@ int b200q_quantize_nvfp4_rowmap(const void* x, int64_t rows, int64_t cols, int64
 
 int b200q_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t ld, int axis, const float* tensor_amax,
                          void* codes, void* sf, int sf_layout, float* tensor_scale_out, void* stream) {
+  PdlChain pdl_chain;
   int rc = check_matrix(x, rows, cols, ld);
   if (rc) return rc;
   if (codes == nullptr || sf == nullptr || tensor_amax == nullptr || tensor_scale_out == nullptr ||
