@@ -1346,6 +1346,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        # NCCL only carries the comparators and the plumbing here; without NVLink multicast objects a rank that dies cannot
+        # leave its peers with memory bound to one
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     config = {"workload": args.workload, "kind": kind, "M_per_gpu": m, "N": n, "K": k,
               "sharding": "rows of A (M) across ranks, B replicated" if world > 1 else "single GPU",
               "l2": "operands, codes and output of a step total > 126 MB (larger than L2); no flush needed"}

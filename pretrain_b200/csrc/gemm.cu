@@ -41,6 +41,7 @@ constexpr int BM = 128;
 constexpr int BKB = 128;                 // bytes of K per stage (= one 128-byte swizzle row)
 constexpr int kGemmThreads = 192;
 constexpr int kSmemBudget = 227 * 1024;
+constexpr int kSfStageBytes = 2048;             // EPI_MXQ: scale-factor staging, two sets of up to two 512-byte atoms
 
 #include "gemm_epilogue.cuh"
 
@@ -373,7 +374,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       };
       if constexpr (EPI == EPI_MXQ)
         epilogue_tile_mxq<NBLK, C::EPI_BUFS, RELEASE_AFTER>(taddr, C::OVERLAP && acc == 0, row0, col0, m_out, p.N, alpha, &outs, epi_s,
-                                                            epi_g, buf, lane, release);
+                                                            epi_g, buf, lane, smem_gen + C::BAR_OFF + 256 + acc * (NBLK / 2) * 512,
+                                                            smem_base + C::BAR_OFF + 256 + acc * (NBLK / 2) * 512, q, 1, release);
       else if constexpr (EPI != EPI_BF16)
         // the two warp groups swap block sets from tile to tile, so an odd block count evens out
         epilogue_tile_glu<EPI == EPI_GLU ? GLU_MX : GLU_BF16, NBLK, RELEASE_AFTER, 2>(
@@ -500,10 +502,13 @@ int launch(const void* A, const void* B, const OutSpec& D, int64_t ldd, int64_t 
   p.sf_kt = (int)((nblk + 3) / 4);
   p.sf_kt_b = p.b_along_k ? p.sf_kt * p.n_experts : p.sf_kt;
   p.sfb_groups = (b_rows + 127) / 128;
-  B200Q_CUDA(ensure_dynamic_smem(gemm_kernel<KIND, BN, EPI>, C::SMEM_BYTES));
+  // the quantized-output epilogue stages its scale-factor atoms behind the barriers (two sets of BN / 128 atoms)
+  constexpr int SMEM = C::SMEM_BYTES + (EPI == EPI_MXQ ? kSfStageBytes : 0);
+  static_assert(SMEM <= kSmemBudget, "shared memory overflow");
+  B200Q_CUDA(ensure_dynamic_smem(gemm_kernel<KIND, BN, EPI>, SMEM));
   const int64_t tiles = (int64_t)p.num_m * p.num_n * (p.ragged_offs != nullptr ? p.n_experts : 1);
   const int grid = (int)(tiles < kNumSMs ? tiles : kNumSMs);
-  B200Q_CUDA(launch_pdl(gemm_kernel<KIND, BN, EPI>, dim3(grid), dim3(gemm_threads(EPI)), C::SMEM_BYTES, st, ma, mb, md, p));
+  B200Q_CUDA(launch_pdl(gemm_kernel<KIND, BN, EPI>, dim3(grid), dim3(gemm_threads(EPI)), SMEM, st, ma, mb, md, p));
   return B200Q_OK;
 }
 

@@ -401,7 +401,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       };
       if constexpr (EPI == EPI_MXQ)
         epilogue_tile_mxq<NBLK, 2, RELEASE_AFTER>(taddr, C::OVERLAP && acc == 0, row0, col0, m_lim, p.N, alpha, &outs, epi_s, epi_g, buf,
-                                                  lane, release);
+                                                  lane, smem_gen + C::BAR_OFF + 256 + acc * (NBLK / 2) * 512,
+                                                  smem_base + C::BAR_OFF + 256 + acc * (NBLK / 2) * 512, q, 1, release);
       else if constexpr (EPI != EPI_BF16)
         epilogue_tile_glu<EPI == EPI_GLU ? GLU_MX : GLU_BF16, NBLK, RELEASE_AFTER, 2>(
             taddr, C::OVERLAP && acc == 0, (((warp - 2) >> 2) + tile_iter) & 1, row, col0, m_lim, p.N, alpha, p.glu, release);
@@ -488,9 +489,12 @@ int launch_pair(const void* A, const void* B, const OutSpec& D, int64_t ldd, con
   p.sf_kt = sf_kt;
   p.glu = gp.glu;
   p.raster_gm = pair_raster_gm(row_bytes);
-  B200Q_CUDA(ensure_dynamic_smem(gemm_pair_kernel<KIND, EPI>, C::SMEM_BYTES));
+  // the quantized-output epilogue stages its scale-factor atoms behind the barriers
+  constexpr int SMEM = C::SMEM_BYTES + (EPI == EPI_MXQ ? kSfStageBytes : 0);
+  static_assert(SMEM <= kSmemBudget, "shared memory overflow");
+  B200Q_CUDA(ensure_dynamic_smem(gemm_pair_kernel<KIND, EPI>, SMEM));
   const int tiles = p.num_mp * p.num_n, pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
-  B200Q_CUDA(launch_pdl(gemm_pair_kernel<KIND, EPI>, dim3(2 * pairs), dim3(gemm_threads(EPI)), C::SMEM_BYTES, st, ma, mb, msa, msb, md, p));
+  B200Q_CUDA(launch_pdl(gemm_pair_kernel<KIND, EPI>, dim3(2 * pairs), dim3(gemm_threads(EPI)), SMEM, st, ma, mb, msa, msb, md, p));
   return B200Q_OK;
 }
 

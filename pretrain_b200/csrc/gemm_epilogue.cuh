@@ -126,13 +126,19 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, bool rev, bool zer
 // b200q_quantize_mxfp8(axis = 1) would quantize that bf16 matrix - E4M3 codes, one E8M0 scale per 32
 // columns - so 1.03 bytes per element leave the SM instead of 2.  A thread owns a row, so it owns whole
 // 32-column blocks.  Two 64-column blocks make one 128-byte row of codes in the (128-byte-swizzled)
-// staging block, stored by TMA to every output; the four scale bytes of those 128 columns are one
-// aligned 32-bit word of the 128x4-tiled layout, stored by the lane itself to every output.
-// NBLK must be even; rows [row0, row0 + 32) and columns [col0, col0 + 64 * NBLK).
+// staging block, stored by TMA to every output.  The four scale bytes of a row and a 128-column chunk are
+// one aligned 32-bit word of the 128x4-tiled layout, and the 128 rows of the tile times one chunk are exactly
+// one 512-byte atom of it: the four epilogue warps (one lane quarter each) put their words into a staging
+// atom in shared memory, meet at a named barrier once per tile, and one lane sends every atom to every
+// output with ONE bulk store - 512 bytes per store instead of 128 four-byte stores, which matters when the
+// outputs are peers' buffers across NVLink (a four-byte remote store costs a whole packet).
+// NBLK must be even; rows [row0, row0 + 32) and columns [col0, col0 + 64 * NBLK); row0 - 32 * q is a multiple of 128.
+// sfst_g / sfst_s: this tile's staging atoms (NBLK / 2 x 512 bytes; the caller alternates two sets by
+// accumulator); q: the warp's lane quarter; bar_id: a named barrier of the four epilogue warps.
 template <int NBLK, int EPI_BUFS, int RELEASE_AFTER, class Release>
 __device__ __forceinline__ void epilogue_tile_mxq(uint32_t taddr, bool rev, int64_t row0, int64_t col0, int64_t M, int64_t N,
                                                   float alpha, const OutMaps* outs, uint32_t epi_s, uint8_t* epi_g, int& buf,
-                                                  int lane, Release release) {
+                                                  int lane, uint8_t* sfst_g, uint32_t sfst_s, int q, int bar_id, Release release) {
   static_assert(NBLK % 2 == 0, "the quantized-output epilogue stores 128-column chunks");
   uint32_t sfw = 0;                                        // the chunk's four scale bytes, lowest block first
   auto emit = [&](int c, const uint32_t (&r)[64]) {
@@ -162,17 +168,14 @@ __device__ __forceinline__ void epilogue_tile_mxq(uint32_t taddr, bool rev, int6
     }
     if (half == (rev ? 0 : 1)) {                           // chunk complete
       const int64_t colg = col0 + (int64_t)(c >> 1) * 128;
+      // this row's word of the chunk's atom: (row % 32) * 16 + (row / 32 % 4) * 4
+      *reinterpret_cast<uint32_t*>(sfst_g + (c >> 1) * 512 + lane * 16 + q * 4) = sfw;
       ptx::fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
         for (int g = 0; g < outs->count; ++g)
           ptx::tma_store_2d(&outs->m[g], (int32_t)colg, (int32_t)row0, epi_s + buf * EPI_BLOCK_BYTES);
         ptx::bulk_commit();
-      }
-      const int64_t row = row0 + lane;
-      if (row < M) {
-        const int64_t off = sf_swizzled(row, (int)(colg >> 5), outs->sf_kt);      // a multiple of 4: colg % 128 == 0
-        for (int g = 0; g < outs->count; ++g) *reinterpret_cast<uint32_t*>(outs->sf[g] + off) = sfw;
       }
       buf = (buf + 1) % EPI_BUFS;
     }
@@ -194,6 +197,23 @@ __device__ __forceinline__ void epilogue_tile_mxq(uint32_t taddr, bool rev, int6
       if (i & 1) emit(c, rb);
       else emit(c, ra);
     }
+  }
+  // The staging atoms of the tile before the previous one are about to be rewritten by the other warps: the bulk store that
+  // read them must be done (at most the newest group - this tile's last codes - may still be reading).  Then all four
+  // lane quarters meet: every word of this tile's atoms is in place (every warp executes this, in range or not).
+  if (q == 0 && lane == 0) ptx::bulk_wait_read<1>();
+  ptx::named_bar_sync(bar_id, 128);
+  if (q == 0 && lane == 0 && row0 < M) {
+    const int64_t tile_row = row0;                          // q == 0: the tile's first row, a multiple of 128
+#pragma unroll
+    for (int j = 0; j < NBLK / 2; ++j) {
+      const int64_t colg = col0 + (int64_t)j * 128;
+      if (colg < N) {
+        const int64_t off = sf_swizzled(tile_row, (int)(colg >> 5), outs->sf_kt);     // the atom's first byte
+        for (int g = 0; g < outs->count; ++g) ptx::bulk_store(outs->sf[g] + off, sfst_s + j * 512, 512);
+      }
+    }
+    ptx::bulk_commit();
   }
 }
 

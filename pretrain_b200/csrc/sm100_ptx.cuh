@@ -85,6 +85,16 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, int32_t x, int32_
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(src)
                : "memory");
 }
+// Untiled bulk store shared -> global (16-byte aligned addresses, size % 16 == 0), bulk async-group completion.
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes)
+               : "memory");
+}
+// Barrier number `id` (1 .. 15; 0 is __syncthreads) among `nthreads` threads (whole warps) of the CTA.
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until at most N of this thread's bulk groups still READ their shared-memory source.
 template <int N>
