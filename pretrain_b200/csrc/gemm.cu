@@ -628,6 +628,7 @@ int prepare_glu(GemmParams* p, const void* A, const void* sfA, const void* B, co
   p->sfa = (const uint8_t*)sfA; p->sfb = (const uint8_t*)sfB; p->a_fmt = a_fmt; p->b_fmt = b_fmt;
   p->M = M; p->N = N; p->K = K;
   p->glu.codes = (uint8_t*)H; p->glu.ldh = ldh; p->glu.sf = (uint8_t*)sfH; p->glu.kt = (hblk + 3) / 4;
+  p->glu.wide = aligned32(H) && (ldh & 31) == 0;
   return B200Q_OK;
 }
 
@@ -904,6 +905,7 @@ int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.scale_a = tsA; p.scale_b = tsB;
   p.M = M; p.N = N; p.K = K;
   p.glu.codes = (uint8_t*)H; p.glu.ldh = ldh * 2; p.glu.amax = amax_out;
+  p.glu.wide = aligned32(H) && ((ldh * 2) & 31) == 0;
   return dispatch_glu_nv(A, B, N, p, st);
 }
 

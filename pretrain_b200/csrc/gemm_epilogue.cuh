@@ -235,6 +235,7 @@ struct GluOut {
   uint8_t* sf;      // GLU_MX: 128x4-tiled E8M0 scale factors over (M, N/64)
   int64_t kt;       // K-tiles per row tile of that layout
   float* amax;      // GLU_BF16: max |h| over the tensor (zeroed before the launch)
+  int wide;         // codes and ldh are 32-byte aligned: a lane's 32 bytes go out as one 256-bit store (a whole sector)
 };
 
 // Two warps share each tensor-memory lane quarter here (the arithmetic per block is long):
@@ -263,16 +264,17 @@ __device__ __forceinline__ void epilogue_tile_glu(uint32_t taddr, bool rev, int 
       uint32_t o[8];
       const int e = mx_quant_block32<FMT_E4M3>(h, o);
       if (row < M) {
-        uint4* dst = reinterpret_cast<uint4*>(out.codes + row * out.ldh + hb * 32);
-        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        uint8_t* dst = out.codes + row * out.ldh + hb * 32;
+        if (out.wide) st_32B<true>(dst, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+        else st_32B<false>(dst, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
         out.sf[sf_swizzled(row, (int)hb, out.kt)] = (uint8_t)(e + 127);
       }
     } else if (row < M) {
-      uint4* dst = reinterpret_cast<uint4*>(out.codes + row * out.ldh + hb * 64);
+      uint8_t* dst = out.codes + row * out.ldh + hb * 64;
+      if (out.wide) { st_32B<true>(dst, h[0], h[1]); st_32B<true>(dst + 32, h[2], h[3]); }
+      else { st_32B<false>(dst, h[0], h[1]); st_32B<false>(dst + 32, h[2], h[3]); }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        dst[u] = h[u];
         hmax = absmax_raw_bf16x2(hmax, absmax_raw_bf16x2(h[u].x, h[u].y));
         hmax = absmax_raw_bf16x2(hmax, absmax_raw_bf16x2(h[u].z, h[u].w));
       }
