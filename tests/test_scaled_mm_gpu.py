@@ -4,8 +4,8 @@ codes and the (swizzled) scale factors the quantizers here produce and must agre
 the north star's 1e-2 (max relative and Frobenius, bf16 output).  That pins, against code this repository did not
 write, (a) the E8M0 / E4M3 scale bytes and their 128x4 tiling, (b) the packing of E2M1 pairs, (c) which operand
 each scale belongs to.  Where torch refuses a mode on this build the test is skipped with torch's message, which is
-also appended to gpurun_out/scaled_mm_refusals.txt.  Test infrastructure only: nothing in the package calls torch's
-scaled matmul."""
+also appended to scaled_mm_refusals.txt in the directory B200Q_TEST_ARTIFACTS names (when it is set).  Test
+infrastructure only: nothing in the package calls torch's scaled matmul."""
 
 import os
 
@@ -14,7 +14,6 @@ import torch
 
 from oracle import restate as R
 import gpu_ref as G
-from conftest import ROOT
 
 pytestmark = pytest.mark.gpu
 E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
@@ -30,9 +29,11 @@ def ops():
 
 def _refused(what, exc):
     msg = f"{what}: {type(exc).__name__}: {str(exc).splitlines()[0][:300]}"
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    with open(os.path.join(ROOT, "gpurun_out", "scaled_mm_refusals.txt"), "a") as f:
-        f.write(msg + "\n")
+    out_dir = os.environ.get("B200Q_TEST_ARTIFACTS")
+    if out_dir:
+        os.makedirs(out_dir, exist_ok=True)
+        with open(os.path.join(out_dir, "scaled_mm_refusals.txt"), "a") as f:
+            f.write(msg + "\n")
     pytest.skip(msg)
 
 
