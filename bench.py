@@ -282,9 +282,20 @@ def run_moe(args, t, d, inter, rank, world, local):
         ev(marks)
         return out
 
+    ffn_ws = torch.empty(ops.moe_ffn_workspace_bytes(t, k, d, e, inter), dtype=torch.uint8, device=x.device)
+
+    def product_step():
+        # the product call: the two weight quantizations (every step, as the reference re-reads its weights every forward),
+        # then plan, gather + MXFP8, both grouped GEMMs and the unpermute as ONE library call on a standing workspace
+        wq1, wsf1 = ops.quantize_mxfp8_rowmap(w_gu.view(e * 2 * inter, d), row_map)
+        wq2, wsf2 = ops.quantize_mxfp8(w_d.view(e * d, inter), 1)
+        return ops.moe_ffn_forward(x, top_i, top_w, wq1, wsf1, wq2, wsf2, e, inter, workspace=ffn_ws)[0]
+
     for _ in range(max(args.warmup, 3)):
         step()
+        product_step()
     torch.cuda.synchronize()
+    assert torch.equal(step(), product_step())
     marks = []
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     def barrier():
@@ -296,7 +307,7 @@ def run_moe(args, t, d, inter, rank, world, local):
         barrier()
         t0.record()
         for _ in range(args.steps):
-            step(marks)
+            product_step()
         t1.record()
         barrier()
     ops.device_status()
@@ -305,9 +316,42 @@ def run_moe(args, t, d, inter, rank, world, local):
         tt = torch.tensor([ms_step], device="cuda", dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms_step = tt.item()
+    # the same step as seven library calls with events between them: the split into its parts
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step(marks)
+    t1.record()
+    barrier()
+    separate_ms = t0.elapsed_time(t1) / args.steps
     seg = [marks[i:i + 6] for i in range(0, len(marks), 6)]
     avg = lambda i: sum(sg[i].elapsed_time(sg[i + 1]) for sg in seg) / len(seg)
     permute_ms, wquant_ms, gemm1_ms, gemm2_ms, unperm_ms = (avg(i) for i in range(5))
+
+    # eight launches of 10-50 us each: also replay the step from a CUDA graph (no host launch cost between them)
+    graph = None
+    try:
+        cg = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            product_step()
+            with torch.cuda.graph(cg, stream=side):
+                product_step()
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            cg.replay()
+        torch.cuda.synchronize()
+        t0.record()
+        for _ in range(args.steps):
+            cg.replay()
+        t1.record()
+        torch.cuda.synchronize()
+        g_ms = t0.elapsed_time(t1) / args.steps
+        graph = {"ms_per_step": g_ms, "value": world * flops / (g_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+                 "note": "the same step replayed from a CUDA graph (no host launch cost)"}
+    except Exception as ex:
+        graph = {"error": str(ex)[:200]}
 
     blk = SparseMoEBlock(d, intermediate_size=inter, n_routed_experts=e, n_routed_experts_per_token=k, router_score_fn="softmax").cuda()
     with torch.no_grad():
@@ -427,12 +471,16 @@ def run_moe(args, t, d, inter, rank, world, local):
             "clocks": clocks,
             "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2},
-            "gpu_launches": 9 * args.steps,
+            "gpu_launches": 8 * args.steps,
             "roofline": roofline_tensor("grouped MXFP8 GEMMs (2 launches; the first one's epilogue does SwiGLU + MXFP8)", flops, gemm_ms, 2.0,
                                         4500.0, gemm_ms * args.steps * 1e-3, clocks, peaks, gemm1_swiglu_ms=gemm1_ms, gemm2_ms=gemm2_ms),
             "permute": dict(bound="hbm", **hbm(n_pairs * d * 3.03125, permute_ms), note="plan kernels + gather fused with MXFP8"),
             "weight_quantize": dict(bound="hbm", **hbm((w_gu.numel() + w_d.numel()) * 3.03125, wquant_ms)),
             "unpermute": dict(bound="hbm", **hbm(n_pairs * d * 2 + t * d * 2, unperm_ms))}
+    line["separate_launches"] = {"ms_per_step": separate_ms, "note": "the same step as seven library calls (plan, gather, two weight quantizations, "
+                                 "two grouped GEMMs, unpermute) with CUDA events between them: where the per-part times come from"}
+    if graph is not None:
+        line["cuda_graph"] = graph
     if expert_parallel is not None:
         line["expert_parallel"] = expert_parallel
     if incumbent is not None:

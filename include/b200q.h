@@ -459,6 +459,23 @@ int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int scor
                           int64_t* top_idx, void* top_w, void* probs, int32_t* expert_counts,
                           const float* select_bias, int out_fp32, void* stream);
 
+/* The expert path of the MoE block in one call (src/layers/mlp.py:446-477 with grouped_mlp, :55-100, between
+ * permute and unpermute), for bias-free SwiGLU experts, forward only: b200q_moe_permute_plan, b200q_moe_gather with
+ * MXFP8 quantization, b200q_grouped_gemm_mxfp8_swiglu, b200q_grouped_gemm_mxfp8 and b200q_moe_unpermute, issued
+ * back to back by one host call, every launch after the first allowed to start while its predecessor drains; the
+ * result equals the five calls bit for bit.  x bf16 [T, D] (pitch ldx elements); top_idx int64 [T, k]; top_w
+ * bf16 [T, k]; w1: the gate/up weight stack [E * 2I, D], rows interleaved gate / up in blocks of 32 per expert as
+ * b200q_grouped_gemm_mxfp8_swiglu wants them, MXFP8 along D (E4M3 codes, swizzled scale factors); w2: the down
+ * weight stack [E * D, I], MXFP8 along I; out bf16 [T, D] contiguous; offs (optional): int32 [E], the cumulative
+ * number of routed pairs per expert as b200q_moe_permute_plan returns it.  workspace: 256-byte aligned,
+ * b200q_moe_ffn_workspace_bytes(T, k, D, E, I) bytes, holds the plan's tables and the intermediates (a, h as
+ * MXFP8, y as bf16); needs no initialisation and may be reused by the next call on the same stream.
+ * D % 128 == 0, I % 64 == 0, E <= 256. */
+int64_t b200q_moe_ffn_workspace_bytes(int64_t T, int k, int64_t D, int E, int64_t I);
+int b200q_moe_ffn_forward(const void* x, int64_t ldx, const int64_t* top_idx, const void* top_w, int64_t T, int k,
+                          int64_t D, int E, int64_t I, const void* w1_codes, const void* w1_sf, const void* w2_codes,
+                          const void* w2_sf, void* out, int32_t* offs, void* workspace, void* stream);
+
 /* Weighted unpermute (src/layers/mlp.py:472-477): out[t, :] = sum_j w[t, j] * y[row_of[t*k+j], :],
  * accumulated in fp32 and rounded once to bf16.  y bf16 [padded_rows, D] pitch ldy; w bf16 [T, k], or
  * NULL for unit weights (the sum over the k slots: the backward of the gather). */

@@ -71,31 +71,29 @@ inline int blocks_per_sm(Kernel kernel, int threads, int fallback) {
 }
 
 // ---- programmatic dependent launch ---------------------------------------------------------------
-// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while the kernel before it
-// in the stream is still running, once every CTA of that kernel has executed grid_launch_dependents() (or exited);
-// everything the later kernel does before grid_dependency_wait() - CTA set-up, barrier initialisation, tensor-memory
-// allocation, descriptor prefetch - then overlaps the earlier kernel's tail.  grid_dependency_wait() returns once the
-// earlier kernel has completed and its memory operations are visible; without the launch attribute it returns at once.
-// The hardware schedules the later kernel only when ALL CTAs of the earlier one have executed the instruction or exited, so a
-// successor waiting in griddepcontrol.wait never holds resources that a not-yet-started CTA of the earlier kernel needs.
+// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization is scheduled as soon as the kernel before it
+// in the stream has "triggered": explicitly, once every CTA has executed grid_launch_dependents() or exited, or implicitly
+// when it completes.  What the later kernel does before grid_dependency_wait() - CTA set-up, barrier initialisation,
+// tensor-memory allocation, descriptor prefetch - overlaps the earlier kernel's tail; grid_dependency_wait() returns once
+// the earlier kernel has completed and its memory operations are visible (without the attribute it returns at once).
+//
+// Two rules, both learnt from wrong results on B200 / CUDA 12.9:
+//  * After a kernel has triggered EXPLICITLY, not only an attributed kernel but also a copy or memset enqueued behind it
+//    starts before it is complete, and so does whatever follows that copy (a gather kernel that triggered at its start,
+//    then the next entry point's cudaMemsetAsync and GEMM: the GEMM read half-written rows; a quantizer behind torch's
+//    clone() read the old contents in 27 - 30 of 30 runs).  So a kernel triggers early only where the entry point that
+//    launches it puts an attributed kernel, which waits, directly behind it; everywhere else the trigger is the implicit
+//    one at completion, which is safe with anything behind it.
+//  * The attribute is given only to a kernel that directly follows another kernel of the same entry point: what the
+//    caller enqueued before an entry point is unknown, and a memset inside one restarts the chain (memset_async).
+// Every kernel of the library executes grid_dependency_wait() before it touches memory (pdl_prologue(); the GEMMs after
+// their set-up), so a follower gains the launch latency and its set-up time, never correctness risk; and because a
+// follower may run while its predecessor still writes, no load of possibly-produced data is non-coherent (.nc / __ldg).
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// First statement of every kernel outside the GEMMs: let the next kernel of the stream be scheduled as soon as all CTAs of
-// this one have started, and touch no memory before everything earlier in the stream is complete.  A chain of short kernels
-// (permute plan, gather, quantizers, unpermute) then runs without the launch latency between its links.
-__device__ __forceinline__ void pdl_prologue() {
-  grid_launch_dependents();
-  grid_dependency_wait();
-}
+__device__ __forceinline__ void pdl_prologue() { grid_dependency_wait(); }
 
-// Launch with (or without) the programmatic-serialization attribute.  B200Q_PDL=0 in the environment turns it off.
-//
-// The attribute is given ONLY to a kernel that directly follows another kernel of the same entry point in the stream.
-// A kernel that carries it is not held back by a copy or memset that precedes it (measured on B200, CUDA 12.9: a
-// quantizer launched with the attribute after cudaMemcpyAsync of its input, or after torch's clone(), read the old
-// contents in 27 - 30 of 30 runs), and griddepcontrol.wait only waits for kernels.  What the caller enqueued before an
-// entry point is unknown, so the first kernel of every entry point is a plain launch; inside an entry point a
-// cudaMemsetAsync restarts the chain (memset_async below).
+// B200Q_PDL=0 in the environment turns the attribute off.
 inline bool pdl_enabled() {
   static int v = -1;
   if (v < 0) {
@@ -106,7 +104,7 @@ inline bool pdl_enabled() {
 }
 // kernels launched so far in the entry point's chain; -1 = no chain open (every launch is plain)
 inline thread_local int t_pdl_chain = -1;
-struct PdlChain {                       // opened at the top of an entry point that launches several kernels
+struct PdlChain {                       // opened at the top of every entry point
   bool outer;
   PdlChain() : outer(t_pdl_chain < 0) { if (outer) t_pdl_chain = 0; }
   ~PdlChain() { if (outer) t_pdl_chain = -1; }

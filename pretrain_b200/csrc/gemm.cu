@@ -811,7 +811,8 @@ int b200q_linear_mxfp8(const void* a, int64_t a_rows, int64_t a_cols, int64_t ld
   const uint16_t* xb = static_cast<const uint16_t*>(b);
   if (a_axis == 1 && b_axis == 1 && a_fmt == b_fmt) {
     // both operands have K contiguous (fprop of a linear layer): one launch quantizes the two of them
-    const RowQuantJob ja = {xa, a_rows, a_cols, lda, ca, sfa, nullptr}, jb = {xb, b_rows, b_cols, ldb, cb, sfb, nullptr};
+    // the GEMM is launched directly behind this kernel, with the attribute: the quantizer may let it set up early
+    const RowQuantJob ja = {xa, a_rows, a_cols, lda, ca, sfa, nullptr, pdl_enabled() ? 1 : 0}, jb = {xb, b_rows, b_cols, ldb, cb, sfb, nullptr, 0};
     launch_rowwise_block<MODE_MX>(ja, jb, a_fmt, swz, nullptr, nullptr, st);
   } else {
     if (a_axis == 1) launch_rowwise_block<MODE_MX>(xa, a_rows, a_cols, lda, a_fmt, ca, sfa, swz, nullptr, nullptr, st);

@@ -1208,4 +1208,74 @@ int b200q_moe_permute_plan_static(const int64_t* top_idx, int64_t n_pairs, int k
                           num_tiles, (cudaStream_t)stream);
 }
 
+// ---- the expert path of the MoE block in one call ----------------------------------------------------
+// permute plan -> gather + MXFP8 -> grouped GEMM 1 with SwiGLU + MXFP8 epilogue -> grouped GEMM 2 -> weighted
+// unpermute (src/layers/mlp.py:446-477 with grouped_mlp, :55-100, between permute and unpermute), for bias-free
+// SwiGLU experts without gradients.  Each step is the entry point of that name; what this call adds is that the
+// eight launches are issued back to back by one host call (the Python layer spends more time between two of its
+// calls than most of these kernels run) and that every launch after the first may start while its predecessor
+// drains.  The workspace holds the plan's tables and the intermediates; nothing in it needs to be initialised.
+static inline int64_t ws_align(int64_t v) { return (v + 255) & ~(int64_t)255; }
+
+struct FfnWorkspace {
+  int64_t padded_rows, plan, offs, padded_offs, row_of, src_of_row, tile_expert, num_tiles, a, a_sf, h, h_sf, y, total;
+};
+static FfnWorkspace ffn_workspace(int64_t T, int k, int64_t D, int E, int64_t I) {
+  FfnWorkspace w = {};
+  const int64_t n_pairs = T * k;
+  w.padded_rows = b200q_moe_padded_rows(n_pairs, E);
+  int64_t o = 0;
+  auto take = [&](int64_t bytes) { const int64_t at = o; o += ws_align(bytes); return at; };
+  w.plan = take(b200q_moe_plan_workspace_bytes(n_pairs, E));
+  w.offs = take((int64_t)E * 4);
+  w.padded_offs = take((int64_t)(E + 1) * 4);
+  w.row_of = take(n_pairs * 4);
+  w.src_of_row = take(w.padded_rows * 4);
+  w.tile_expert = take(w.padded_rows / 128 * 4);
+  w.num_tiles = take(4);
+  w.a = take(w.padded_rows * D);
+  w.a_sf = take(b200q_sf_bytes(w.padded_rows, D / 32, B200Q_SF_SWIZZLE_128x4));
+  w.h = take(w.padded_rows * I);
+  w.h_sf = take(b200q_sf_bytes(w.padded_rows, I / 32, B200Q_SF_SWIZZLE_128x4));
+  w.y = take(w.padded_rows * D * 2);
+  w.total = o;
+  return w;
+}
+
+int64_t b200q_moe_ffn_workspace_bytes(int64_t T, int k, int64_t D, int E, int64_t I) {
+  if (T <= 0 || k <= 0 || D <= 0 || E <= 0 || I <= 0) return 0;
+  return ffn_workspace(T, k, D, E, I).total;
+}
+
+int b200q_moe_ffn_forward(const void* x, int64_t ldx, const int64_t* top_idx, const void* top_w, int64_t T, int k, int64_t D, int E,
+                          int64_t I, const void* w1_codes, const void* w1_sf, const void* w2_codes, const void* w2_sf, void* out,
+                          int32_t* offs, void* workspace, void* stream) {
+  PdlChain pdl_chain;
+  if (x == nullptr || top_idx == nullptr || top_w == nullptr || w1_codes == nullptr || w1_sf == nullptr || w2_codes == nullptr ||
+      w2_sf == nullptr || out == nullptr || workspace == nullptr || T <= 0 || k <= 0 || D <= 0 || E <= 0 || I <= 0)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 127) || (I & 63) || ((2 * I) & 127)) return B200Q_ERR_SHAPE;      // both GEMMs' N % 128, h blocks of 32 per 64 gate/up columns
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return B200Q_ERR_ALIGNMENT;
+  const FfnWorkspace w = ffn_workspace(T, k, D, E, I);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int32_t* padded_offs = reinterpret_cast<int32_t*>(ws + w.padded_offs);
+  int32_t* row_of = reinterpret_cast<int32_t*>(ws + w.row_of);
+  int32_t* src_of_row = reinterpret_cast<int32_t*>(ws + w.src_of_row);
+  int32_t* tile_expert = reinterpret_cast<int32_t*>(ws + w.tile_expert);
+  int32_t* num_tiles = reinterpret_cast<int32_t*>(ws + w.num_tiles);
+  int rc = b200q_moe_permute_plan(top_idx, T * k, k, E, offs != nullptr ? offs : reinterpret_cast<int32_t*>(ws + w.offs), padded_offs, row_of,
+                                  src_of_row,
+                                  tile_expert, num_tiles, ws + w.plan, stream);
+  if (rc) return rc;
+  if ((rc = b200q_moe_gather(x, D, ldx, src_of_row, num_tiles, w.padded_rows, 1, B200Q_E4M3, ws + w.a, ws + w.a_sf, stream))) return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8_swiglu(ws + w.a, B200Q_E4M3, ws + w.a_sf, w1_codes, B200Q_E4M3, w1_sf, tile_expert, num_tiles,
+                                            w.padded_rows, E, 2 * I, D, ws + w.h, I, ws + w.h_sf, stream)))
+    return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8(ws + w.h, B200Q_E4M3, ws + w.h_sf, w2_codes, B200Q_E4M3, w2_sf, tile_expert, num_tiles,
+                                     w.padded_rows, E, D, I, ws + w.y, D, stream)))
+    return rc;
+  return b200q_moe_unpermute(ws + w.y, D, top_w, row_of, T, k, D, out, stream);
+}
+
+
 }  // extern "C"

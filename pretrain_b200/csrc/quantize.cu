@@ -92,6 +92,7 @@ struct RowQuantJob {
   uint8_t* codes;
   uint8_t* sf;
   const int32_t* dst_row;
+  int trigger_early;     // (first job only) an attributed kernel that waits is launched directly behind this one
 };
 
 // Up to two matrices per launch (MXFP8 only; second.rows == 0: one matrix): both operands of a GEMM quantized by one
@@ -100,6 +101,7 @@ template <int MODE, bool WIDE, int FMT>
 __global__ void __launch_bounds__(kThreads)
 rowwise_block_quant_kernel(const RowQuantJob first, const RowQuantJob second, int swz,
                            const float* __restrict__ tensor_amax, float* __restrict__ tensor_scale_out) {
+  if (first.trigger_early) grid_launch_dependents();   // the whole grid is resident: the GEMM behind this kernel may set up now
   pdl_prologue();
   constexpr int BS = MODE == MODE_MX ? 32 : 16;
   float s_t = 0.f, rcp_st = 0.f;

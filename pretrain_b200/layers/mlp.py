@@ -611,8 +611,18 @@ class SparseMoEBlock(nn.Module):
         top_indices, top_weights, router_probs = self.router(x_flat)
         w_in = self.expert_gate_up if self.gated else self.expert_up
         b_in = self.expert_gate_up_bias if self.gated else self.expert_up_bias
+        wants_grad = _wants_grad(x, top_weights, w_in, self.expert_down, b_in, self.expert_down_bias)
+        if (not wants_grad and self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None
+                and not (self.training and self.expert_dropout.p > 0) and d % 128 == 0 and w_in.shape[1] % 128 == 0
+                and self.expert_down.shape[2] % 64 == 0 and x_flat.is_cuda):
+            # bias-free SwiGLU experts without gradients: plan, gather + MXFP8, both grouped GEMMs (SwiGLU in the first one's
+            # epilogue) and the weighted unpermute as one library call
+            out, offs = T.moe_ffn_forward(x_flat.to(torch.bfloat16), top_indices, top_weights.to(torch.bfloat16),
+                                          *_expert_weight_copies(w_in, "glu"), *_expert_weight_copies(self.expert_down, "rows"),
+                                          e, self.expert_down.shape[2])
+            return self._finish(x, out.to(x.dtype), offs, router_probs)
         plan = T.moe_permute_plan(top_indices, e)                          # stable sort by expert
-        if _wants_grad(x, top_weights, w_in, self.expert_down, b_in, self.expert_down_bias):
+        if wants_grad:
             _trainable_widths(d, w_in.shape[1], self.expert_down.shape[2])
             dropping = self.training and self.expert_dropout.p > 0
             if self.gated and self.act_fn is silu_glu and b_in is None and self.expert_down_bias is None and not dropping:
@@ -629,7 +639,13 @@ class SparseMoEBlock(nn.Module):
             y = _grouped_ffn_padded(a, sfa, plan, w_in, self.expert_down, self.act_fn, self.gated, b_in, self.expert_down_bias)
             out = T.moe_unpermute(self.expert_dropout(y), top_weights.to(torch.bfloat16), plan.row_of, b * s).to(x.dtype)
 
-        counts = torch.diff(plan.offs, prepend=plan.offs.new_zeros(1))
+        return self._finish(x, out, plan.offs, router_probs)
+
+    def _finish(self, x, out, offs, router_probs):
+        """Load bookkeeping, auxiliary loss and shared experts (src/layers/mlp.py:479-494)."""
+        b, s, d = x.shape
+        e = self.n_routed_experts
+        counts = torch.diff(offs, prepend=offs.new_zeros(1))
         self.expert_load.record_load(counts.detach(), self.training)
         aux = None
         if self.aux_loss:

@@ -679,6 +679,37 @@ def swiglu_backward(g: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
     return dg
 
 
+def moe_ffn_forward(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, w1_codes: torch.Tensor, w1_sf: torch.Tensor,
+                    w2_codes: torch.Tensor, w2_sf: torch.Tensor, n_experts: int, inter: int, workspace: torch.Tensor | None = None):
+    """The expert path of the MoE block in one library call (src/layers/mlp.py:446-477 around grouped_mlp): permute plan,
+    gather + MXFP8, grouped GEMM with SwiGLU + MXFP8 epilogue, grouped GEMM, weighted unpermute.  x (T, D) bf16;
+    top_idx (T, k) int64; top_w (T, k); w1: the gate / up stack quantized through glu_row_map (E * 2I, D); w2: the down
+    stack (E * D, I), both MXFP8 along their last axis.  Returns (out (T, D) bf16, offs (E,) int32: cumulative pairs per
+    expert).  `workspace` (uint8, 256-byte aligned, moe_ffn_workspace_bytes long) may be passed to keep the call free of
+    allocations besides the results."""
+    x = _mat(x)
+    t, d = x.shape
+    k = top_idx.shape[1]
+    w = top_w.to(torch.bfloat16).contiguous()
+    idx = top_idx.contiguous()
+    lib = _lib.load()
+    need = lib.b200q_moe_ffn_workspace_bytes(t, k, d, n_experts, inter)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    elif workspace.numel() < need or workspace.dtype != torch.uint8:
+        raise ValueError(f"workspace: {need} bytes of uint8 wanted")
+    out = torch.empty(t, d, dtype=torch.bfloat16, device=x.device)
+    offs = torch.empty(n_experts, dtype=torch.int32, device=x.device)
+    _lib.check(lib.b200q_moe_ffn_forward(x.data_ptr(), x.stride(0), idx.data_ptr(), w.data_ptr(), t, k, d, n_experts, inter,
+                                         w1_codes.data_ptr(), w1_sf.data_ptr(), w2_codes.data_ptr(), w2_sf.data_ptr(), out.data_ptr(),
+                                         offs.data_ptr(), workspace.data_ptr(), _stream()), "b200q_moe_ffn_forward")
+    return out, offs
+
+
+def moe_ffn_workspace_bytes(tokens: int, top_k: int, d_model: int, n_experts: int, inter: int) -> int:
+    return _lib.load().b200q_moe_ffn_workspace_bytes(tokens, top_k, d_model, n_experts, inter)
+
+
 def moe_unpermute_backward(dout: torch.Tensor, weights: torch.Tensor, y: torch.Tensor | None, plan: MoEPlan, want_dy: bool = True):
     """(dy bf16 (padded_rows, D), dw fp32 (T, k) | None): gradients of moe_unpermute w.r.t. the expert
     outputs and, when y is given, the routing weights.  want_dy=False returns dw alone."""

@@ -430,6 +430,18 @@ def _(y, weights, row_of, n_tokens):
     return y.new_empty(n_tokens, y.shape[1], dtype=torch.bfloat16)
 
 
+@_lib_def("b200q::moe_ffn_forward", mutates_args=())
+def moe_ffn_forward(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, w1_codes: torch.Tensor, w1_sf: torch.Tensor,
+                    w2_codes: torch.Tensor, w2_sf: torch.Tensor, n_experts: int, inter: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The expert path in one library call: (out (T, D) bf16, offs (E,) int32)."""
+    return ops.moe_ffn_forward(x, top_idx, top_w, w1_codes, w1_sf, w2_codes, w2_sf, n_experts, inter)
+
+
+@moe_ffn_forward.register_fake
+def _(x, top_idx, top_w, w1_codes, w1_sf, w2_codes, w2_sf, n_experts, inter):
+    return x.new_empty(x.shape[0], x.shape[1], dtype=torch.bfloat16), x.new_empty(n_experts, dtype=torch.int32)
+
+
 @_lib_def("b200q::moe_unpermute_backward_quantize_dual", mutates_args=())
 def moe_unpermute_backward_quantize_dual(dout: torch.Tensor, weights: torch.Tensor, row_of: torch.Tensor, padded_rows: int, fmt: int,
                                          y: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:

@@ -966,3 +966,31 @@ def test_stationary_grouped_gemms_equal_the_general_kernel_bit_for_bit(ops, d, i
         res[mode] = (hq[:live].clone(), hs[:n_sf].clone(), g[:live].clone(), y[:live].clone(), dh[:live].clone())
     for got, want in zip(res[1], res[-1]):
         assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("t,d,inter,e,k", [(4096, 768, 384, 64, 4), (1000, 256, 128, 8, 2), (512, 128, 64, 16, 1)])
+def test_expert_path_in_one_call_equals_the_five_calls(ops, t, d, inter, e, k):
+    """b200q_moe_ffn_forward against permute plan, gather + MXFP8, grouped GEMM with the SwiGLU epilogue, grouped GEMM and
+    unpermute called one by one: the same output bits and the same per-expert offsets, with experts that get no token, twice
+    in a row on one workspace (nothing in it needs to be cleared)."""
+    x, logits, w_gu, w_d = R.inputs_moe(t, d, e, k, inter, seed=21)
+    logits[:, 1] = -1e9                                               # an expert without tokens
+    logits[:, e - 1] = -1e9
+    top_i, top_w = R.router_topk(logits, k)
+    x, top_i, top_w, w_gu, w_d = x.cuda(), top_i.cuda(), top_w.cuda(), w_gu.cuda(), w_d.cuda()
+    w1q, w1s = ops.quantize_mxfp8_rowmap(w_gu.view(e * 2 * inter, d), ops.glu_row_map(e, inter, "cuda"))
+    w2q, w2s = ops.quantize_mxfp8(w_d.view(e * d, inter), 1)
+    plan = ops.moe_permute_plan(top_i, e)
+    a, sfa = ops.moe_gather(x, plan, True)
+    hq, hs = ops.grouped_gemm_mxfp8_swiglu(a, sfa, w1q, w1s, plan, 2 * inter)
+    y = ops.grouped_gemm_mxfp8(hq, hs, w2q, w2s, plan, d)
+    want = ops.moe_unpermute(y, top_w, plan.row_of, t)
+    ws = torch.empty(ops.moe_ffn_workspace_bytes(t, k, d, e, inter), dtype=torch.uint8, device="cuda")
+    ws.fill_(0xA5)
+    for rep in range(2):
+        got, offs = ops.moe_ffn_forward(x, top_i, top_w, w1q, w1s, w2q, w2s, e, inter, workspace=ws)
+        ops.device_status()
+        assert torch.equal(offs, plan.offs), rep
+        assert torch.equal(got, want), (rep, int((got != want).sum()), int((got != want).any(1).sum()))
+    got, offs = ops.moe_ffn_forward(x, top_i, top_w, w1q, w1s, w2q, w2s, e, inter)
+    assert torch.equal(got, want)
