@@ -94,14 +94,15 @@ __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepco
 __device__ __forceinline__ void pdl_prologue() { grid_dependency_wait(); }
 
 // B200Q_PDL=0 in the environment turns the attribute off.
-inline bool pdl_enabled() {
+inline int pdl_mode() {                 // 0: never, 1: followers inside an entry point, 2: every launch (experiments only)
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("B200Q_PDL");
-    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    v = e == nullptr ? 1 : (e[0] == '0' ? 0 : (e[0] == '2' ? 2 : 1));
   }
-  return v == 1;
+  return v;
 }
+inline bool pdl_enabled() { return pdl_mode() != 0; }
 // kernels launched so far in the entry point's chain; -1 = no chain open (every launch is plain)
 inline thread_local int t_pdl_chain = -1;
 struct PdlChain {                       // opened at the top of every entry point
@@ -123,7 +124,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = t_pdl_chain > 0 && pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = (pdl_mode() == 2 || (t_pdl_chain > 0 && pdl_mode() == 1)) ? 1 : 0;
   if (t_pdl_chain >= 0) ++t_pdl_chain;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
