@@ -285,10 +285,9 @@ def run_moe(args, t, d, inter, rank, world, local):
     ffn_ws = torch.empty(ops.moe_ffn_workspace_bytes(t, k, d, e, inter), dtype=torch.uint8, device=x.device)
 
     def product_step():
-        # the product call: the two weight quantizations (every step, as the reference re-reads its weights every forward),
+        # the product call: both weight stacks quantized by one launch (every step, as the reference re-reads its weights every forward),
         # then plan, gather + MXFP8, both grouped GEMMs and the unpermute as ONE library call on a standing workspace
-        wq1, wsf1 = ops.quantize_mxfp8_rowmap(w_gu.view(e * 2 * inter, d), row_map)
-        wq2, wsf2 = ops.quantize_mxfp8(w_d.view(e * d, inter), 1)
+        wq1, wsf1, wq2, wsf2 = ops.quantize_mxfp8_pair(w_gu.view(e * 2 * inter, d), w_d.view(e * d, inter), row_map, None)
         return ops.moe_ffn_forward(x, top_i, top_w, wq1, wsf1, wq2, wsf2, e, inter, workspace=ffn_ws)[0]
 
     for _ in range(max(args.warmup, 3)):
@@ -471,7 +470,7 @@ def run_moe(args, t, d, inter, rank, world, local):
             "clocks": clocks,
             "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2},
-            "gpu_launches": 8 * args.steps,
+            "gpu_launches": 7 * args.steps,
             "roofline": roofline_tensor("grouped MXFP8 GEMMs (2 launches; the first one's epilogue does SwiGLU + MXFP8)", flops, gemm_ms, 2.0,
                                         4500.0, gemm_ms * args.steps * 1e-3, clocks, peaks, gemm1_swiglu_ms=gemm1_ms, gemm2_ms=gemm2_ms),
             "permute": dict(bound="hbm", **hbm(n_pairs * d * 3.03125, permute_ms), note="plan kernels + gather fused with MXFP8"),

@@ -120,6 +120,14 @@ int b200q_quantize_mxfp8_rowmap(const void* x, int64_t rows, int64_t cols, int64
                                 const int32_t* dst_row, void* codes, void* sf, int sf_layout,
                                 void* stream);
 
+/* Two matrices quantized along their rows by ONE launch (same element format and scale-factor layout): the two weight
+ * stacks of an expert FFN, or any two operands of one step; dst_row0 / dst_row1 as in b200q_quantize_mxfp8_rowmap, or
+ * NULL for the identity.  Equal to two b200q_quantize_mxfp8(axis = 1) / _rowmap calls bit for bit.  The reference
+ * quantizes one tensor per call (src/quant/linear.py:73-80); no counterpart. */
+int b200q_quantize_mxfp8_pair(const void* x0, int64_t rows0, int64_t cols0, int64_t ld0, const int32_t* dst_row0,
+                              void* codes0, void* sf0, const void* x1, int64_t rows1, int64_t cols1, int64_t ld1,
+                              const int32_t* dst_row1, void* codes1, void* sf1, int fmt, int sf_layout, void* stream);
+
 /* NVFP4: 16-element blocks, packed E2M1 codes (element 2i in the low nibble), one E4M3 scale
  * byte per block and one fp32 scale per tensor derived from *tensor_amax (device):
  * s_t = max(amax/2688, 1e-12), written to *tensor_scale_out.  No counterpart in the reference

@@ -57,6 +57,7 @@ SIGNATURES = {
     "b200q_gemm_nvfp4_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "b200q_quantize_nvfp4_rowmap": (_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp]),
     "b200q_quantize_mxfp8_rowmap": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp]),
+    "b200q_quantize_mxfp8_pair": (_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _int, _int, _vp]),
     "b200q_moe_gather_quantize_dual": (_int, [_vp, _i64, _i64, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_unpermute_backward_quantize_dual": (_int, [_vp, _i64, _vp, _vp, _int, _i64, _i64, _int, _vp, _vp, _vp, _vp,
                                                          _vp, _i64, _vp, _i64, _vp, _vp, _vp]),

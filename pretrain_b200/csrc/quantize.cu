@@ -1236,6 +1236,31 @@ int b200q_quantize_mxfp8_rowmap(const void* x, int64_t rows, int64_t cols, int64
   return B200Q_OK;
 }
 
+// Two matrices along their rows in ONE launch (same format and layout; each with an optional output-row map): the two
+// weight stacks of an expert FFN, or any two operands of one step.  Equal to two b200q_quantize_mxfp8(_rowmap) calls.
+int b200q_quantize_mxfp8_pair(const void* x0, int64_t rows0, int64_t cols0, int64_t ld0, const int32_t* dst_row0, void* codes0,
+                              void* sf0, const void* x1, int64_t rows1, int64_t cols1, int64_t ld1, const int32_t* dst_row1,
+                              void* codes1, void* sf1, int fmt, int sf_layout, void* stream) {
+  PdlChain pdl_chain;
+  int rc = check_matrix(x0, rows0, cols0, ld0);
+  if (rc) return rc;
+  if ((rc = check_matrix(x1, rows1, cols1, ld1))) return rc;
+  if (codes0 == nullptr || sf0 == nullptr || codes1 == nullptr || sf1 == nullptr || (fmt != B200Q_E4M3 && fmt != B200Q_E5M2) ||
+      (sf_layout != B200Q_SF_NATURAL && sf_layout != B200Q_SF_SWIZZLE_128x4))
+    return B200Q_ERR_INVALID_ARG;
+  if (!aligned16(codes0) || !aligned16(codes1)) return B200Q_ERR_ALIGNMENT;
+  if ((cols0 & 31) || (cols1 & 31) || rows0 > INT32_MAX || rows1 > INT32_MAX) return B200Q_ERR_SHAPE;
+  if ((rc = require_sm100())) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((rc = zero_sf_pads(sf0, rows0, cols0 / 32, sf_layout, st))) return rc;
+  if ((rc = zero_sf_pads(sf1, rows1, cols1 / 32, sf_layout, st))) return rc;
+  const RowQuantJob j0 = {(const uint16_t*)x0, rows0, cols0, ld0, (uint8_t*)codes0, (uint8_t*)sf0, dst_row0, 0};
+  const RowQuantJob j1 = {(const uint16_t*)x1, rows1, cols1, ld1, (uint8_t*)codes1, (uint8_t*)sf1, dst_row1, 0};
+  launch_rowwise_block<MODE_MX>(j0, j1, fmt, sf_layout, nullptr, nullptr, st);
+  B200Q_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
 int b200q_quantize_nvfp4_rowmap(const void* x, int64_t rows, int64_t cols, int64_t ld, const float* tensor_amax,
                                 const int32_t* dst_row, void* codes, void* sf, int sf_layout, float* tensor_scale_out,
                                 void* stream) {

@@ -185,6 +185,24 @@ def quantize_mxfp8_rowmap(x: torch.Tensor, dst_row: torch.Tensor, fmt=E4M3, layo
     return codes, sf
 
 
+def quantize_mxfp8_pair(x0: torch.Tensor, x1: torch.Tensor, dst_row0: torch.Tensor | None = None, dst_row1: torch.Tensor | None = None,
+                        fmt=E4M3, layout: int = SF_SWIZZLED):
+    """Row-wise MXFP8 of two matrices in one launch (each optionally through an output-row map): (codes0, sf0, codes1, sf1),
+    equal to two quantize_mxfp8 / quantize_mxfp8_rowmap calls."""
+    x0, x1 = _mat(x0), _mat(x1)
+    outs = []
+    for x, m in ((x0, dst_row0), (x1, dst_row1)):
+        if m is not None and (m.numel() != x.shape[0] or m.dtype != torch.int32 or not m.is_cuda):
+            raise ValueError("dst_row: one int32 per row, on the GPU")
+        outs.append(torch.empty(x.shape[0], x.shape[1], dtype=torch.uint8, device=x.device))
+        outs.append(torch.empty(sf_bytes(x.shape[0], x.shape[1] // 32, layout), dtype=torch.uint8, device=x.device))
+    _lib.check(_lib.load().b200q_quantize_mxfp8_pair(
+        x0.data_ptr(), x0.shape[0], x0.shape[1], x0.stride(0), dst_row0.data_ptr() if dst_row0 is not None else None, outs[0].data_ptr(),
+        outs[1].data_ptr(), x1.data_ptr(), x1.shape[0], x1.shape[1], x1.stride(0), dst_row1.data_ptr() if dst_row1 is not None else None,
+        outs[2].data_ptr(), outs[3].data_ptr(), fmt_of(fmt), layout, _stream()), "b200q_quantize_mxfp8_pair")
+    return tuple(outs)
+
+
 def quantize_nvfp4_rowmap(x: torch.Tensor, dst_row: torch.Tensor, tensor_amax: torch.Tensor | None = None, layout: int = SF_SWIZZLED):
     """Row-wise NVFP4 of x with input row r written as output row dst_row[r] (a permutation)."""
     x = _mat(x)

@@ -402,3 +402,21 @@ def test_block_scaled_quantizers_follow_the_same_nan_rule(ops):
     out = ops.gemm_mxfp8(ca, sfa, cb, sfb).float().cpu()
     bad = out.isnan().any(1)
     assert bad[3] and bad[77] and int(bad.sum()) == 2
+
+
+def test_two_matrices_in_one_launch_equal_two_calls(ops):
+    """b200q_quantize_mxfp8_pair against quantize_mxfp8 / quantize_mxfp8_rowmap on each matrix: different shapes, one of them
+    through a row map, a ragged scale-factor tile, both formats."""
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(1000, 768, generator=g).bfloat16().cuda()
+    b = (0.02 * torch.randn(384, 96, generator=g)).bfloat16().cuda()
+    perm = torch.randperm(1000, generator=g).int().cuda()
+    for fmt in (ops.E4M3, ops.E5M2):
+        c0, s0, c1, s1 = ops.quantize_mxfp8_pair(a, b, perm, None, fmt)
+        w0, t0 = ops.quantize_mxfp8_rowmap(a, perm, fmt)
+        w1, t1 = ops.quantize_mxfp8(b, 1, fmt)
+        assert torch.equal(c0, w0) and torch.equal(s0, t0) and torch.equal(c1, w1) and torch.equal(s1, t1)
+        c0, s0, c1, s1 = ops.quantize_mxfp8_pair(b, a, None, None, fmt)
+        w0, t0 = ops.quantize_mxfp8(b, 1, fmt)
+        w1, t1 = ops.quantize_mxfp8(a, 1, fmt)
+        assert torch.equal(c0, w0) and torch.equal(s0, t0) and torch.equal(c1, w1) and torch.equal(s1, t1)
