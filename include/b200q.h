@@ -484,6 +484,33 @@ int b200q_moe_ffn_forward(const void* x, int64_t ldx, const int64_t* top_idx, co
                           int64_t D, int E, int64_t I, const void* w1_codes, const void* w1_sf, const void* w2_codes,
                           const void* w2_sf, void* out, int32_t* offs, void* workspace, void* stream);
 
+/* The TRAINABLE expert path, forward and backward as one call each (bias-free SwiGLU experts; the reference differentiates
+ * src/layers/mlp.py:446-477 through torch._grouped_mm with autograd, here the backward is explicit).  Forward =
+ * b200q_moe_gather_quantize_dual, b200q_grouped_gemm_mxfp8 (g, kept), b200q_swiglu_quantize_dual, b200q_grouped_gemm_mxfp8
+ * (y, kept), b200q_moe_unpermute; backward = b200q_moe_pair_of_row, b200q_moe_unpermute_backward_quantize_dual (with dw),
+ * dgrad / wgrad of the second GEMM, b200q_swiglu_backward_quantize_dual, dgrad / wgrad of the first GEMM, unpermute with
+ * unit weights.  Results equal the separate calls bit for bit; what the one call adds is that its kernels are issued back to
+ * back and may be scheduled while their predecessors drain.  The plan's tables come from b200q_moe_permute_plan.
+ * Shapes (R = padded_rows): x bf16 [T, D]; top_w bf16 [T, k]; w1r / w1sr: gate | up stack [E * 2I, D] MXFP8 along D (rows NOT
+ * interleaved), w2r / w2sr: down stack [E * D, I] along I; w1c / w1sc and w2c / w2sc: the same stacks quantized along axis 0
+ * ([D, E * 2I], [I, E * D]).  Saved by the forward for the backward: ac / asc ([D, R] codes of the gathered rows along R),
+ * g bf16 [R, 2I], hc / hsc ([I, R]), y bf16 [R, D].  Gradients: dx bf16 [T, D], dw fp32 [T, k], dw1 bf16 [E, 2I, D],
+ * dw2 bf16 [E, D, I].  Activations and weights E4M3, gradients E5M2.  D % 128 == 0, I % 128 == 0; workspaces 256-byte
+ * aligned, sized by the *_workspace_bytes functions, no initialisation needed. */
+int64_t b200q_moe_ffn_train_forward_workspace_bytes(int64_t padded_rows, int64_t D, int64_t I);
+int b200q_moe_ffn_train_forward(const void* x, int64_t ldx, const void* top_w, int64_t T, int k, int64_t D, int E, int64_t I,
+                                int64_t padded_rows, const int32_t* row_of, const int32_t* src_of_row,
+                                const int32_t* tile_expert, const int32_t* num_tiles, const void* w1r, const void* w1sr,
+                                const void* w2r, const void* w2sr, void* ac, void* asc, void* g, void* hc, void* hsc, void* y,
+                                void* out, void* workspace, void* stream);
+int64_t b200q_moe_ffn_train_backward_workspace_bytes(int64_t padded_rows, int64_t D, int64_t I);
+int b200q_moe_ffn_train_backward(const void* dout, int64_t lddout, const void* top_w, int64_t T, int k, int64_t D, int E,
+                                 int64_t I, int64_t padded_rows, const int32_t* row_of, const int32_t* padded_offs,
+                                 const int32_t* tile_expert, const int32_t* num_tiles, const void* y, const void* g,
+                                 const void* ac, const void* asc, const void* hc, const void* hsc, const void* w1c,
+                                 const void* w1sc, const void* w2c, const void* w2sc, void* dx, float* dw, void* dw1, void* dw2,
+                                 void* workspace, void* stream);
+
 /* Weighted unpermute (src/layers/mlp.py:472-477): out[t, :] = sum_j w[t, j] * y[row_of[t*k+j], :],
  * accumulated in fp32 and rounded once to bf16.  y bf16 [padded_rows, D] pitch ldy; w bf16 [T, k], or
  * NULL for unit weights (the sum over the k slots: the backward of the gather). */

@@ -76,6 +76,10 @@ SIGNATURES = {
     "b200q_moe_router_topk": (_int, [_vp, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "b200q_moe_unpermute": (_int, [_vp, _i64, _vp, _vp, _i64, _int, _i64, _vp, _vp]),
     "b200q_moe_ffn_workspace_bytes": (_i64, [_i64, _int, _i64, _int, _i64]),
+    "b200q_moe_ffn_train_forward_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "b200q_moe_ffn_train_forward": (_int, [_vp, _i64, _vp, _i64, _int, _i64, _int, _i64, _i64] + [_vp] * 17),
+    "b200q_moe_ffn_train_backward_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "b200q_moe_ffn_train_backward": (_int, [_vp, _i64, _vp, _i64, _int, _i64, _int, _i64, _i64] + [_vp] * 20),
     "b200q_moe_ffn_forward": (_int, [_vp, _i64, _vp, _vp, _i64, _int, _i64, _int, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_pair_of_row": (_int, [_vp, _i64, _i64, _vp, _vp]),
     # test hooks (process-wide kernel-choice overrides; see the end of include/b200q.h)

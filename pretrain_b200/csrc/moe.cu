@@ -1278,4 +1278,111 @@ int b200q_moe_ffn_forward(const void* x, int64_t ldx, const int64_t* top_idx, co
 }
 
 
+// ---- the trainable expert path: forward and backward as one call each ---------------------------------
+// The sequences of the autograd function of SparseMoEBlock for bias-free SwiGLU experts (the explicit backward of
+// src/layers/mlp.py:446-477, which the reference leaves to autograd through torch._grouped_mm), each issued by one host
+// call: every kernel after the first of a call may be scheduled while its predecessor drains.  Each step is the entry
+// point of that name; results equal the separate calls bit for bit.  The plan comes from b200q_moe_permute_plan.
+static int64_t sfb(int64_t rows, int64_t cols) { return ws_align(b200q_sf_bytes(rows, cols / 32, B200Q_SF_SWIZZLE_128x4)); }
+
+int64_t b200q_moe_ffn_train_forward_workspace_bytes(int64_t padded_rows, int64_t D, int64_t I) {
+  if (padded_rows <= 0 || D <= 0 || I <= 0) return 0;
+  return ws_align(padded_rows * D) + sfb(padded_rows, D) + ws_align(padded_rows * I) + sfb(padded_rows, I);
+}
+
+int b200q_moe_ffn_train_forward(const void* x, int64_t ldx, const void* top_w, int64_t T, int k, int64_t D, int E, int64_t I,
+                                int64_t padded_rows, const int32_t* row_of, const int32_t* src_of_row, const int32_t* tile_expert,
+                                const int32_t* num_tiles, const void* w1r, const void* w1sr, const void* w2r, const void* w2sr,
+                                void* ac, void* asc, void* g, void* hc, void* hsc, void* y, void* out, void* workspace, void* stream) {
+  PdlChain pdl_chain;
+  if (x == nullptr || top_w == nullptr || row_of == nullptr || src_of_row == nullptr || tile_expert == nullptr || num_tiles == nullptr ||
+      w1r == nullptr || w1sr == nullptr || w2r == nullptr || w2sr == nullptr || ac == nullptr || asc == nullptr || g == nullptr ||
+      hc == nullptr || hsc == nullptr || y == nullptr || out == nullptr || workspace == nullptr || T <= 0 || k <= 0 || E <= 0)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 127) || (I & 127) || (padded_rows & 127) || padded_rows <= 0) return B200Q_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return B200Q_ERR_ALIGNMENT;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* ar = ws;
+  uint8_t* asr = ar + ws_align(padded_rows * D);
+  uint8_t* hr = asr + sfb(padded_rows, D);
+  uint8_t* hsr = hr + ws_align(padded_rows * I);
+  int rc = b200q_moe_gather_quantize_dual(x, D, ldx, src_of_row, padded_rows, B200Q_E4M3, ar, asr, ac, asc, nullptr, stream);
+  if (rc) return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8(ar, B200Q_E4M3, asr, w1r, B200Q_E4M3, w1sr, tile_expert, num_tiles, padded_rows, E, 2 * I, D, g, 2 * I,
+                                     stream)))
+    return rc;
+  if ((rc = b200q_swiglu_quantize_dual(g, padded_rows, I, 2 * I, B200Q_E4M3, hr, hsr, hc, hsc, nullptr, stream))) return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8(hr, B200Q_E4M3, hsr, w2r, B200Q_E4M3, w2sr, tile_expert, num_tiles, padded_rows, E, D, I, y, D, stream)))
+    return rc;
+  return b200q_moe_unpermute(y, D, top_w, row_of, T, k, D, out, stream);
+}
+
+struct FfnBwdWorkspace { int64_t pair_of_row, dyr, dysr, dyc, dysc, dots, dh, dgr, dgsr, dgc, dgsc, da, total; };
+static FfnBwdWorkspace ffn_bwd_workspace(int64_t R, int64_t D, int64_t I) {
+  FfnBwdWorkspace w = {};
+  int64_t o = 0;
+  auto take = [&](int64_t bytes) { const int64_t at = o; o += ws_align(bytes); return at; };
+  w.pair_of_row = take(R * 4);
+  w.dyr = take(R * D);
+  w.dysr = take(sfb(R, D));
+  w.dyc = take(D * R);
+  w.dysc = take(sfb(D, R));
+  w.dots = take(D / 128 * R * 4);
+  w.dh = take(R * I * 2);
+  w.dgr = take(R * 2 * I);
+  w.dgsr = take(sfb(R, 2 * I));
+  w.dgc = take(2 * I * R);
+  w.dgsc = take(sfb(2 * I, R));
+  w.da = take(R * D * 2);
+  w.total = o;
+  return w;
+}
+
+int64_t b200q_moe_ffn_train_backward_workspace_bytes(int64_t padded_rows, int64_t D, int64_t I) {
+  if (padded_rows <= 0 || D <= 0 || I <= 0) return 0;
+  return ffn_bwd_workspace(padded_rows, D, I).total;
+}
+
+int b200q_moe_ffn_train_backward(const void* dout, int64_t lddout, const void* top_w, int64_t T, int k, int64_t D, int E, int64_t I,
+                                 int64_t padded_rows, const int32_t* row_of, const int32_t* padded_offs, const int32_t* tile_expert,
+                                 const int32_t* num_tiles, const void* y, const void* g, const void* ac, const void* asc, const void* hc,
+                                 const void* hsc, const void* w1c, const void* w1sc, const void* w2c, const void* w2sc, void* dx, float* dw,
+                                 void* dw1, void* dw2, void* workspace, void* stream) {
+  PdlChain pdl_chain;
+  if (dout == nullptr || top_w == nullptr || row_of == nullptr || padded_offs == nullptr || tile_expert == nullptr ||
+      num_tiles == nullptr || y == nullptr || g == nullptr || ac == nullptr || asc == nullptr || hc == nullptr || hsc == nullptr ||
+      w1c == nullptr || w1sc == nullptr || w2c == nullptr || w2sc == nullptr || dx == nullptr || dw == nullptr || dw1 == nullptr ||
+      dw2 == nullptr || workspace == nullptr || T <= 0 || k <= 0 || E <= 0)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 127) || (I & 127) || (padded_rows & 127) || padded_rows <= 0) return B200Q_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return B200Q_ERR_ALIGNMENT;
+  const FfnBwdWorkspace w = ffn_bwd_workspace(padded_rows, D, I);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int32_t* pair_of_row = reinterpret_cast<int32_t*>(ws + w.pair_of_row);
+  const int64_t n_pairs = T * k;
+  int rc = b200q_moe_pair_of_row(row_of, n_pairs, padded_rows, pair_of_row, stream);
+  if (rc) return rc;
+  // dy = w * dout scattered into the padded layout, both ways in E5M2, and dw = <dout, y>
+  if ((rc = b200q_moe_unpermute_backward_quantize_dual(dout, lddout, top_w, pair_of_row, k, padded_rows, D, B200Q_E5M2, ws + w.dyr,
+                                                       ws + w.dysr, ws + w.dyc, ws + w.dysc, y, D, row_of, n_pairs,
+                                                       reinterpret_cast<float*>(ws + w.dots), dw, stream)))
+    return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8_dgrad(ws + w.dyr, B200Q_E5M2, ws + w.dysr, w2c, B200Q_E4M3, w2sc, tile_expert, num_tiles, padded_rows, E,
+                                           I, D, ws + w.dh, I, stream)))
+    return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8_wgrad(ws + w.dyc, B200Q_E5M2, ws + w.dysc, hc, B200Q_E4M3, hsc, padded_offs, E, D, I, padded_rows, dw2, I,
+                                           stream)))
+    return rc;
+  if ((rc = b200q_swiglu_backward_quantize_dual(g, padded_rows, I, 2 * I, ws + w.dh, I, B200Q_E5M2, ws + w.dgr, ws + w.dgsr, ws + w.dgc,
+                                                ws + w.dgsc, nullptr, stream)))
+    return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8_dgrad(ws + w.dgr, B200Q_E5M2, ws + w.dgsr, w1c, B200Q_E4M3, w1sc, tile_expert, num_tiles, padded_rows, E,
+                                           D, 2 * I, ws + w.da, D, stream)))
+    return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8_wgrad(ws + w.dgc, B200Q_E5M2, ws + w.dgsc, ac, B200Q_E4M3, asc, padded_offs, E, 2 * I, D, padded_rows, dw1,
+                                           D, stream)))
+    return rc;
+  return b200q_moe_unpermute(ws + w.da, D, nullptr, row_of, T, k, D, dx, stream);
+}
+
 }  // extern "C"

@@ -94,14 +94,16 @@ class _ExpertFFN(torch.autograd.Function):
         e, n1, _ = w_in.shape
         inter = n1 // 2
         # every element-wise step hands its result to the both-directions quantizer inside one kernel
-        ar, asr, ac, asc = T.moe_gather_quantize_dual(x, plan, E4M3)                          # (R, D) | (D, R), pad rows zero
-        g = T.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, n1)                        # (R, 2I) bf16, kept for backward
         if inter % 128 == 0:
-            hr, hsr, hc, hsc = T.swiglu_quantize_dual(g, E4M3)
+            # the five launches below as one library call (issued back to back, each may be scheduled while its predecessor drains)
+            out, ac, asc, g, hc, hsc, y = T.moe_ffn_train_forward(x, top_w.to(torch.bfloat16), w1r, w1sr, w2r, w2sr, e, inter, plan.row_of,
+                                                                  plan.src_of_row, plan.tile_expert, plan.num_tiles)
         else:
+            ar, asr, ac, asc = T.moe_gather_quantize_dual(x, plan, E4M3)                      # (R, D) | (D, R), pad rows zero
+            g = T.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, n1)                    # (R, 2I) bf16, kept for backward
             hr, hsr, hc, hsc = T.quantize_mxfp8_dual(T.swiglu(g), E4M3, SWZ)
-        y = T.grouped_gemm_mxfp8(hr, hsr, w2r, w2sr, plan, d)                         # (R, D) bf16
-        out = T.moe_unpermute(y, top_w, plan.row_of, t)
+            y = T.grouped_gemm_mxfp8(hr, hsr, w2r, w2sr, plan, d)                     # (R, D) bf16
+            out = T.moe_unpermute(y, top_w, plan.row_of, t)
         ctx.save_for_backward(top_w, ac, asc, g, hc, hsc, w1c, w1sc, w2c, w2sc, y, *plan_tensors)
         ctx.shapes = (t, d, e, inter, top_w.shape[1])
         ctx.dtypes = (x.dtype, top_w.dtype, w_in.dtype, w_down.dtype)
@@ -113,6 +115,11 @@ class _ExpertFFN(torch.autograd.Function):
         plan = T.MoEPlan(*plan_tensors)
         t, d, e, inter, k = ctx.shapes
         dout = dout.reshape(t, d).to(torch.bfloat16)
+        xd, twd, w1d, w2d = ctx.dtypes
+        if inter % 128 == 0:
+            dx, dw, dw1, dw2 = T.moe_ffn_train_backward(dout.contiguous(), top_w.to(torch.bfloat16), y, g, ac, asc, hc, hsc, w1c, w1sc, w2c,
+                                                        w2sc, e, plan.padded_offs, plan.row_of, plan.tile_expert, plan.num_tiles)
+            return (dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d)) + (None,) * (8 + len(plan_tensors))
         dyr, dysr, dyc, dysc, dw = T.moe_unpermute_backward_quantize_dual(                      # dw (T, k) fp32
             dout, top_w.to(torch.bfloat16), plan.row_of, plan.padded_rows, E5M2, y)
         dh = T.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, plan, inter, E5M2, E4M3)         # (R, I)
@@ -121,7 +128,6 @@ class _ExpertFFN(torch.autograd.Function):
         da = T.grouped_gemm_mxfp8_dgrad(dgr, dgsr, w1c, w1sc, plan, d, E5M2, E4M3)             # (R, D)
         dw1 = T.grouped_gemm_mxfp8_wgrad(dgc, dgsc, ac, asc, plan, E5M2, E4M3)                 # (E, 2I, D)
         dx = T.moe_unpermute(da, None, plan.row_of, t)                                           # sum over the k slots
-        xd, twd, w1d, w2d = ctx.dtypes
         return (dx.to(xd), dw.to(twd), dw1.to(w1d), dw2.to(w2d)) + (None,) * (8 + len(plan_tensors))
 
 

@@ -724,6 +724,53 @@ def moe_ffn_forward(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor,
     return out, offs
 
 
+def moe_ffn_train_forward(x: torch.Tensor, top_w: torch.Tensor, plan: MoEPlan, w1r, w1sr, w2r, w2sr, inter: int):
+    """Forward of the trainable expert path in one library call: (out (T, D) bf16, ac, asc, g, hc, hsc, y), the last six
+    being what the backward needs (transposed MXFP8 copies of the gathered rows and of h, bf16 g and y)."""
+    x = _mat(x)
+    t, d = x.shape
+    r, e = plan.padded_rows, plan.n_experts
+    w = top_w.to(torch.bfloat16).contiguous()
+    dev = x.device
+    u8 = dict(dtype=torch.uint8, device=dev)
+    ac, asc = torch.empty(d, r, **u8), torch.empty(sf_bytes(d, r // 32), **u8)
+    hc, hsc = torch.empty(inter, r, **u8), torch.empty(sf_bytes(inter, r // 32), **u8)
+    g = torch.empty(r, 2 * inter, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(r, d, dtype=torch.bfloat16, device=dev)
+    out = torch.empty(t, d, dtype=torch.bfloat16, device=dev)
+    lib = _lib.load()
+    ws = torch.empty(lib.b200q_moe_ffn_train_forward_workspace_bytes(r, d, inter), **u8)
+    _lib.check(lib.b200q_moe_ffn_train_forward(
+        x.data_ptr(), x.stride(0), w.data_ptr(), t, w.shape[1], d, e, inter, r, plan.row_of.data_ptr(), plan.src_of_row.data_ptr(),
+        plan.tile_expert.data_ptr(), plan.num_tiles.data_ptr(), w1r.data_ptr(), w1sr.data_ptr(), w2r.data_ptr(), w2sr.data_ptr(),
+        ac.data_ptr(), asc.data_ptr(), g.data_ptr(), hc.data_ptr(), hsc.data_ptr(), y.data_ptr(), out.data_ptr(), ws.data_ptr(), _stream()),
+        "b200q_moe_ffn_train_forward")
+    return out, ac, asc, g, hc, hsc, y
+
+
+def moe_ffn_train_backward(dout: torch.Tensor, top_w: torch.Tensor, plan: MoEPlan, y, g, ac, asc, hc, hsc, w1c, w1sc, w2c, w2sc):
+    """Backward of the trainable expert path in one library call: (dx (T, D) bf16, dw (T, k) fp32, dw1 (E, 2I, D) bf16,
+    dw2 (E, D, I) bf16)."""
+    dout = _mat(dout)
+    t, d = dout.shape
+    r, e = plan.padded_rows, plan.n_experts
+    inter = g.shape[1] // 2
+    w = top_w.to(torch.bfloat16).contiguous()
+    dev = dout.device
+    dx = torch.empty(t, d, dtype=torch.bfloat16, device=dev)
+    dw = torch.empty(w.shape, dtype=torch.float32, device=dev)
+    dw1 = torch.empty(e, 2 * inter, d, dtype=torch.bfloat16, device=dev)
+    dw2 = torch.empty(e, d, inter, dtype=torch.bfloat16, device=dev)
+    lib = _lib.load()
+    ws = torch.empty(lib.b200q_moe_ffn_train_backward_workspace_bytes(r, d, inter), dtype=torch.uint8, device=dev)
+    _lib.check(lib.b200q_moe_ffn_train_backward(
+        dout.data_ptr(), dout.stride(0), w.data_ptr(), t, w.shape[1], d, e, inter, r, plan.row_of.data_ptr(), plan.padded_offs.data_ptr(),
+        plan.tile_expert.data_ptr(), plan.num_tiles.data_ptr(), y.data_ptr(), g.data_ptr(), ac.data_ptr(), asc.data_ptr(), hc.data_ptr(),
+        hsc.data_ptr(), w1c.data_ptr(), w1sc.data_ptr(), w2c.data_ptr(), w2sc.data_ptr(), dx.data_ptr(), dw.data_ptr(), dw1.data_ptr(),
+        dw2.data_ptr(), ws.data_ptr(), _stream()), "b200q_moe_ffn_train_backward")
+    return dx, dw, dw1, dw2
+
+
 def moe_ffn_workspace_bytes(tokens: int, top_k: int, d_model: int, n_experts: int, inter: int) -> int:
     return _lib.load().b200q_moe_ffn_workspace_bytes(tokens, top_k, d_model, n_experts, inter)
 

@@ -442,6 +442,45 @@ def _(x, top_idx, top_w, w1_codes, w1_sf, w2_codes, w2_sf, n_experts, inter):
     return x.new_empty(x.shape[0], x.shape[1], dtype=torch.bfloat16), x.new_empty(n_experts, dtype=torch.int32)
 
 
+_T7 = Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]
+
+
+@_lib_def("b200q::moe_ffn_train_forward", mutates_args=())
+def moe_ffn_train_forward(x: torch.Tensor, top_w: torch.Tensor, w1r: torch.Tensor, w1sr: torch.Tensor, w2r: torch.Tensor, w2sr: torch.Tensor,
+                          n_experts: int, inter: int, row_of: torch.Tensor, src_of_row: torch.Tensor, tile_expert: torch.Tensor,
+                          num_tiles: torch.Tensor) -> _T7:
+    """Forward of the trainable expert path in one library call: (out, ac, asc, g, hc, hsc, y)."""
+    plan = _plan(n_experts, row_of=row_of, src_of_row=src_of_row, tile_expert=tile_expert, num_tiles=num_tiles)
+    return ops.moe_ffn_train_forward(x, top_w, plan, w1r, w1sr, w2r, w2sr, inter)
+
+
+@moe_ffn_train_forward.register_fake
+def _(x, top_w, w1r, w1sr, w2r, w2sr, n_experts, inter, row_of, src_of_row, tile_expert, num_tiles):
+    r, d = src_of_row.shape[0], x.shape[1]
+    u8, bf = dict(dtype=torch.uint8), dict(dtype=torch.bfloat16)
+    return (x.new_empty(x.shape[0], d, **bf), x.new_empty(d, r, **u8), x.new_empty(ops.sf_bytes(d, r // 32), **u8),
+            x.new_empty(r, 2 * inter, **bf), x.new_empty(inter, r, **u8), x.new_empty(ops.sf_bytes(inter, r // 32), **u8),
+            x.new_empty(r, d, **bf))
+
+
+@_lib_def("b200q::moe_ffn_train_backward", mutates_args=())
+def moe_ffn_train_backward(dout: torch.Tensor, top_w: torch.Tensor, y: torch.Tensor, g: torch.Tensor, ac: torch.Tensor, asc: torch.Tensor,
+                           hc: torch.Tensor, hsc: torch.Tensor, w1c: torch.Tensor, w1sc: torch.Tensor, w2c: torch.Tensor, w2sc: torch.Tensor,
+                           n_experts: int, padded_offs: torch.Tensor, row_of: torch.Tensor, tile_expert: torch.Tensor,
+                           num_tiles: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Backward of the trainable expert path in one library call: (dx, dw fp32, dw1, dw2)."""
+    plan = _plan(n_experts, padded_offs=padded_offs, row_of=row_of, tile_expert=tile_expert, num_tiles=num_tiles, padded_rows=y.shape[0])
+    return ops.moe_ffn_train_backward(dout, top_w, plan, y, g, ac, asc, hc, hsc, w1c, w1sc, w2c, w2sc)
+
+
+@moe_ffn_train_backward.register_fake
+def _(dout, top_w, y, g, ac, asc, hc, hsc, w1c, w1sc, w2c, w2sc, n_experts, padded_offs, row_of, tile_expert, num_tiles):
+    d, inter = dout.shape[1], g.shape[1] // 2
+    bf = dict(dtype=torch.bfloat16)
+    return (dout.new_empty(dout.shape[0], d, **bf), dout.new_empty(top_w.shape, dtype=torch.float32),
+            dout.new_empty(n_experts, 2 * inter, d, **bf), dout.new_empty(n_experts, d, inter, **bf))
+
+
 @_lib_def("b200q::moe_unpermute_backward_quantize_dual", mutates_args=())
 def moe_unpermute_backward_quantize_dual(dout: torch.Tensor, weights: torch.Tensor, row_of: torch.Tensor, padded_rows: int, fmt: int,
                                          y: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:

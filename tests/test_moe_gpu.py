@@ -994,3 +994,43 @@ def test_expert_path_in_one_call_equals_the_five_calls(ops, t, d, inter, e, k):
         assert torch.equal(got, want), (rep, int((got != want).sum()), int((got != want).any(1).sum()))
     got, offs = ops.moe_ffn_forward(x, top_i, top_w, w1q, w1s, w2q, w2s, e, inter)
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("t,d,inter,e,k", [(4096, 768, 384, 64, 4), (1000, 256, 128, 8, 2)])
+def test_trainable_expert_path_in_one_call_equals_the_separate_calls(ops, t, d, inter, e, k):
+    """b200q_moe_ffn_train_forward / _backward against the same steps called one by one: every saved tensor, the output and
+    all four gradients bit for bit (live rows; experts without tokens included)."""
+    x, logits, w_gu, w_d = R.inputs_moe(t, d, e, k, inter, seed=31)
+    logits[:, 2] = -1e9
+    top_i, top_w = R.router_topk(logits, k)
+    g0 = torch.Generator().manual_seed(7)
+    dout = (0.01 * torch.randn(t, d, generator=g0)).bfloat16().cuda()
+    x, top_i, top_w, w_gu, w_d = x.cuda(), top_i.cuda(), top_w.cuda(), w_gu.cuda(), w_d.cuda()
+    w1r, w1sr, w1c, w1sc = ops.quantize_mxfp8_dual(w_gu.view(e * 2 * inter, d))
+    w2r, w2sr, w2c, w2sc = ops.quantize_mxfp8_dual(w_d.view(e * d, inter))
+    plan = ops.moe_permute_plan(top_i, e)
+    live = int(plan.num_tiles.item()) * 128
+    # one by one
+    ar, asr, ac, asc = ops.moe_gather_quantize_dual(x, plan)
+    g = ops.grouped_gemm_mxfp8(ar, asr, w1r, w1sr, plan, 2 * inter)
+    hr, hsr, hc, hsc = ops.swiglu_quantize_dual(g)
+    y = ops.grouped_gemm_mxfp8(hr, hsr, w2r, w2sr, plan, d)
+    out = ops.moe_unpermute(y, top_w, plan.row_of, t)
+    got = ops.moe_ffn_train_forward(x, top_w, plan, w1r, w1sr, w2r, w2sr, inter)
+    ops.device_status()
+    assert torch.equal(got[0], out) and torch.equal(got[1], ac) and torch.equal(got[2], asc)
+    assert torch.equal(got[3][:live], g[:live]) and torch.equal(got[6][:live], y[:live])
+    # the transposed copies of h cover every padded row, the dead ones included, whose gate / up rows no GEMM wrote: compare
+    # the columns of the live rows
+    assert torch.equal(got[4][:, :live], hc[:, :live])
+    # backward, fed with the one-by-one forward's tensors on both sides
+    dyr, dysr, dyc, dysc, dw = ops.moe_unpermute_backward_quantize_dual(dout, top_w, ops.moe_pair_of_row(plan), ops.E5M2, y=y, row_of=plan.row_of)
+    dh = ops.grouped_gemm_mxfp8_dgrad(dyr, dysr, w2c, w2sc, plan, inter, ops.E5M2, ops.E4M3)
+    dw2 = ops.grouped_gemm_mxfp8_wgrad(dyc, dysc, hc, hsc, plan, ops.E5M2, ops.E4M3)
+    dgr, dgsr, dgc, dgsc = ops.swiglu_backward_quantize_dual(g, dh, ops.E5M2)
+    da = ops.grouped_gemm_mxfp8_dgrad(dgr, dgsr, w1c, w1sc, plan, d, ops.E5M2, ops.E4M3)
+    dw1 = ops.grouped_gemm_mxfp8_wgrad(dgc, dgsc, ac, asc, plan, ops.E5M2, ops.E4M3)
+    dx = ops.moe_unpermute(da, None, plan.row_of, t)
+    gdx, gdw, gdw1, gdw2 = ops.moe_ffn_train_backward(dout, top_w, plan, y, g, ac, asc, hc, hsc, w1c, w1sc, w2c, w2sc)
+    ops.device_status()
+    assert torch.equal(gdx, dx) and torch.equal(gdw, dw) and torch.equal(gdw1, dw1) and torch.equal(gdw2, dw2)
