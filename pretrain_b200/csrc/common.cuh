@@ -193,6 +193,43 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
 }
 
+// quot_for_cast() for the two bf16 of a word at once on the packed fp32 pair instructions (sm_100): the same three
+// IEEE operations per lane - q = x r, e = b q - x, q' = q - e r - at half the issue slots.  The pair is unpacked
+// NEGATED (one shift-add and one logic operation, like the plain unpack), and the reciprocal is passed negated, so that
+// q = (-x)(-r), e = b q + (-x) and q' = e (-r) + q need no sign change of their own.  Pays only in a kernel that is
+// bound by instruction issue (the NVFP4 row quantizer once its loads run ahead); the FP8 kernels did not change.
+struct QuotScale {
+  uint64_t b2, nr2;      // (b, b) and (-r, -r)
+};
+__device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ QuotScale quot_scale(float b, float r) {
+  QuotScale s;
+  s.b2 = pack_f32x2(__float_as_uint(b), __float_as_uint(b));
+  s.nr2 = pack_f32x2(__float_as_uint(-r), __float_as_uint(-r));
+  return s;
+}
+__device__ __forceinline__ void quot2_for_cast(uint32_t w, const QuotScale& s, float& q_lo, float& q_hi) {
+  const uint64_t na = pack_f32x2((w << 16) + 0x80000000u, (w & 0xFFFF0000u) ^ 0x80000000u);
+  uint64_t q, e;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q) : "l"(na), "l"(s.nr2));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(e) : "l"(s.b2), "l"(q), "l"(na));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q) : "l"(e), "l"(s.nr2), "l"(q));
+  uint32_t lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(q));
+  q_lo = __uint_as_float(lo);
+  q_hi = __uint_as_float(hi);
+}
+__device__ __forceinline__ void quot8_for_cast(const uint4& v, const QuotScale& s, float (&q)[8]) {
+  quot2_for_cast(v.x, s, q[0], q[1]);
+  quot2_for_cast(v.y, s, q[2], q[3]);
+  quot2_for_cast(v.z, s, q[4], q[5]);
+  quot2_for_cast(v.w, s, q[6], q[7]);
+}
+
 // Packed bf16 pair (2^-e_lo, 2^-e_hi) for block exponents in [-39, 126], and the packed product.  Scaling a
 // bf16 value by a power of two is exact in bf16 unless the result falls below 2^-126, far under the
 // smallest fp8 subnormal, where it rounds to a (signed) zero code either way - so the packed multiply
