@@ -1208,6 +1208,57 @@ def run_dense(args, kind, m, n, k, rank, world, local, config):
            "h2d_bytes_per_step": ha.numel() * 2 + hb.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2}
     if shard_b:
         e2e["replicated_operand"] = "each rank copies 1/%d of B from host; ncclAllGather over NVLink completes it" % world
+    if kind == "mxfp8":
+        # The same product with B as a layer's weight: QuantLinear keeps the weight (and its codes, made once) on the
+        # device, so a step copies only the activation in and the result out - what src/quant/linear.py:73-76 would
+        # re-quantize every call.  Reported beside the main figure, which copies and quantizes both operands every step.
+        from pretrain_b200.quant.config import QuantConfig, normalize_quant_rules
+        from pretrain_b200.quant.linear import QuantLinear
+        rule = normalize_quant_rules(QuantConfig(enabled=True, dtype_recipe="mxfp8"))[0]
+        layer = QuantLinear(k, n, False, rule).to("cuda", torch.bfloat16)
+        with torch.no_grad():
+            layer.weight.copy_(b)
+        ev_r = [torch.cuda.Event() for _ in range(2)]
+
+        def resident_step(i):
+            j = i & 1
+            da, _, dd = dbuf[j]
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_c[j])
+                da.copy_(ha, non_blocking=True)
+                ev_in[j].record()
+            with torch.cuda.stream(s_c):
+                s_c.wait_event(ev_in[j])
+                s_c.wait_event(ev_out[j])
+                with torch.no_grad():
+                    dd.copy_(layer(da))
+                ev_c[j].record()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_c[j])
+                hout.copy_(dd, non_blocking=True)
+                ev_out[j].record()
+
+        def resident_run(count):
+            for st in (s_in, s_c, s_out):
+                st.wait_stream(torch.cuda.current_stream())
+            for i in range(count):
+                resident_step(i)
+            for st in (s_in, s_c, s_out):
+                torch.cuda.current_stream().wait_stream(st)
+
+        try:
+            resident_run(4)
+            barrier()
+            t0.record()
+            resident_run(e2e_steps)
+            t1.record()
+            barrier()
+            r_ms = rank_max(t0.elapsed_time(t1) / e2e_steps)
+            e2e["weight_resident"] = {"value": world * flops / (r_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": r_ms,
+                                      "h2d_bytes_per_step": ha.numel() * 2, "d2h_bytes_per_step": hout.numel() * 2,
+                                      "note": "B held by a QuantLinear as its weight (codes cached on the parameter); only A travels in"}
+        except Exception as ex:
+            e2e["weight_resident"] = {"error": str(ex)[:200]}
 
     # ---- the gather in its other forms, beside `value` -----------------------------------------
     allgather = None
