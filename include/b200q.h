@@ -439,6 +439,27 @@ int b200q_moe_pair_dots_peers(const void* dout, int64_t ld, void* const* peer_y,
                               const int32_t* pair_peer, const int32_t* pair_row, int64_t T, int k, int64_t D,
                               float* dw, void* stream);
 
+/* Expert-parallel MoE forward after the index tables (b200q_moe_permute_plan, the all-gather of the counts,
+ * b200q_moe_ep_index, b200q_moe_pad_plan) as ONE call: b200q_moe_zero_pad_rows on this rank's receive buffers,
+ * b200q_moe_dispatch_peers, rendezvous, b200q_grouped_gemm_mxfp8_swiglu and b200q_grouped_gemm_mxfp8 over the experts
+ * this rank owns (the second one writes peer_y[rank]), rendezvous, b200q_moe_combine_peers into out[T, D] bf16,
+ * rendezvous.  The rendezvous are b200q_peer_barrier with epochs epoch + 1, epoch + 2, epoch + 3 (the caller advances
+ * its epoch by 3).  src_of_row .. padded_rows: this rank's plan over ALL experts; own_*: the plan of the experts it owns
+ * (own_padded_rows rows in every receive buffer); w1: (experts_per_rank * 2I, D) gate / up rows interleaved in blocks of
+ * 32, w2: (experts_per_rank * D, I), both MXFP8 E4M3 with swizzled scale factors.  D % 128 == 0, I % 64 == 0.
+ * workspace: b200q_moe_ep_forward_workspace_bytes(own_padded_rows, I) bytes, 256-byte aligned.  Equal to the separate
+ * calls bit for bit. */
+int64_t b200q_moe_ep_forward_workspace_bytes(int64_t own_padded_rows, int64_t I);
+int b200q_moe_ep_forward(const void* x, int64_t ldx, const void* top_w, int64_t T, int k, int64_t D, int64_t I,
+                         int experts_per_rank, int world, int rank, int epoch, const int32_t* src_of_row,
+                         const int32_t* tile_expert, const int32_t* padded_offs, const int32_t* num_tiles,
+                         int64_t padded_rows, const int32_t* row_base, const int32_t* pair_peer,
+                         const int32_t* pair_row, const int32_t* own_src_of_row, const int32_t* own_tile_expert,
+                         const int32_t* own_num_tiles, int64_t own_padded_rows, void* const* peer_codes,
+                         void* const* peer_sf, void* const* peer_y, void* const* flag_ptrs, const void* w1_codes,
+                         const void* w1_sf, const void* w2_codes, const void* w2_sf, void* out, void* workspace,
+                         void* stream);
+
 /* Backward of b200q_swiglu(quantize = 0): dg[r] = [dh * up * silu'(gate) | dh * silu(gate)] for
  * g[r] = [gate | up]; bf16 in and out, fp32 arithmetic (the reference gets this from autograd through
  * src/layers/activation.py:80-81).  I % 8 == 0. */

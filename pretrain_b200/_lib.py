@@ -82,6 +82,9 @@ SIGNATURES = {
     "b200q_moe_ffn_train_backward": (_int, [_vp, _i64, _vp, _i64, _int, _i64, _int, _i64, _i64] + [_vp] * 20),
     "b200q_moe_ffn_forward": (_int, [_vp, _i64, _vp, _vp, _i64, _int, _i64, _int, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_moe_pair_of_row": (_int, [_vp, _i64, _i64, _vp, _vp]),
+    "b200q_moe_ep_forward_workspace_bytes": (_i64, [_i64, _i64]),
+    "b200q_moe_ep_forward": (_int, [_vp, _i64, _vp, _i64, _int, _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp,
+                                    _vp, _vp, _vp, _i64] + [_vp] * 11),
     # test hooks (process-wide kernel-choice overrides; see the end of include/b200q.h)
     "b200q_debug_set_gemm_bn": (_int, [_int]),
     "b200q_debug_set_gemm_pair": (_int, [_int]),

@@ -1385,4 +1385,54 @@ int b200q_moe_ffn_train_backward(const void* dout, int64_t lddout, const void* t
   return b200q_moe_unpermute(ws + w.da, D, nullptr, row_of, T, k, D, dx, stream);
 }
 
+// ---- expert-parallel forward after the index tables: one call ------------------------------------------
+// zero the pad rows of my receive buffers, dispatch (gather + MXFP8, stored into the owners' buffers), rendezvous, both
+// grouped GEMMs over the experts I own (SwiGLU in the first one's epilogue, the second one writing where the peers will
+// read), rendezvous, combine (weighted rows loaded from their owners), rendezvous - the steps of
+// b200q_moe_zero_pad_rows, b200q_moe_dispatch_peers, b200q_peer_barrier, b200q_grouped_gemm_mxfp8_swiglu,
+// b200q_grouped_gemm_mxfp8 and b200q_moe_combine_peers, issued by one host call: per step the host spends more time
+// between two calls than most of these kernels run.  The three rendezvous use epochs epoch + 1 .. epoch + 3.
+int64_t b200q_moe_ep_forward_workspace_bytes(int64_t own_padded_rows, int64_t I) {
+  if (own_padded_rows <= 0 || I <= 0) return 0;
+  return ws_align(own_padded_rows * I) + sfb(own_padded_rows, I);
+}
+
+int b200q_moe_ep_forward(const void* x, int64_t ldx, const void* top_w, int64_t T, int k, int64_t D, int64_t I, int experts_per_rank,
+                         int world, int rank, int epoch, const int32_t* src_of_row, const int32_t* tile_expert,
+                         const int32_t* padded_offs, const int32_t* num_tiles, int64_t padded_rows, const int32_t* row_base,
+                         const int32_t* pair_peer, const int32_t* pair_row, const int32_t* own_src_of_row,
+                         const int32_t* own_tile_expert, const int32_t* own_num_tiles, int64_t own_padded_rows,
+                         void* const* peer_codes, void* const* peer_sf, void* const* peer_y, void* const* flag_ptrs,
+                         const void* w1_codes, const void* w1_sf, const void* w2_codes, const void* w2_sf, void* out, void* workspace,
+                         void* stream) {
+  PdlChain pdl_chain;
+  if (x == nullptr || top_w == nullptr || src_of_row == nullptr || tile_expert == nullptr || padded_offs == nullptr || num_tiles == nullptr ||
+      row_base == nullptr || pair_peer == nullptr || pair_row == nullptr || own_src_of_row == nullptr || own_tile_expert == nullptr ||
+      own_num_tiles == nullptr || peer_codes == nullptr || peer_sf == nullptr || peer_y == nullptr || flag_ptrs == nullptr ||
+      w1_codes == nullptr || w1_sf == nullptr || w2_codes == nullptr || w2_sf == nullptr || out == nullptr || workspace == nullptr ||
+      T <= 0 || k <= 0 || experts_per_rank <= 0 || world <= 0 || rank < 0 || rank >= world)
+    return B200Q_ERR_INVALID_ARG;
+  if ((D & 127) || (I & 63) || ((2 * I) & 127)) return B200Q_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return B200Q_ERR_ALIGNMENT;
+  uint8_t* h = static_cast<uint8_t*>(workspace);
+  uint8_t* h_sf = h + ws_align(own_padded_rows * I);
+  void* my_codes = peer_codes[rank];
+  void* my_sf = peer_sf[rank];
+  int rc = b200q_moe_zero_pad_rows(own_src_of_row, own_num_tiles, own_padded_rows, D, my_codes, my_sf, stream);
+  if (rc) return rc;
+  if ((rc = b200q_moe_dispatch_peers(x, D, ldx, src_of_row, tile_expert, padded_offs, num_tiles, padded_rows, row_base, experts_per_rank,
+                                     world, peer_codes, peer_sf, stream)))
+    return rc;
+  if ((rc = b200q_peer_barrier(flag_ptrs, world, rank, epoch + 1, stream))) return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8_swiglu(my_codes, B200Q_E4M3, my_sf, w1_codes, B200Q_E4M3, w1_sf, own_tile_expert, own_num_tiles,
+                                            own_padded_rows, experts_per_rank, 2 * I, D, h, I, h_sf, stream)))
+    return rc;
+  if ((rc = b200q_grouped_gemm_mxfp8(h, B200Q_E4M3, h_sf, w2_codes, B200Q_E4M3, w2_sf, own_tile_expert, own_num_tiles, own_padded_rows,
+                                     experts_per_rank, D, I, peer_y[rank], D, stream)))
+    return rc;
+  if ((rc = b200q_peer_barrier(flag_ptrs, world, rank, epoch + 2, stream))) return rc;
+  if ((rc = b200q_moe_combine_peers(peer_y, world, D, top_w, pair_peer, pair_row, T, k, D, out, stream))) return rc;
+  return b200q_peer_barrier(flag_ptrs, world, rank, epoch + 3, stream);     // nobody overwrites y or the codes while a peer still reads them
+}
+
 }  // extern "C"

@@ -341,6 +341,7 @@ class FusedExpertParallel:
         self.flags.zero_()
         self._epoch = 0
         self._ones = None
+        self._ws = None
         torch.cuda.synchronize()
         dist.barrier(group=self.group)                       # every rank's flags are zero before anyone signals
 
@@ -369,6 +370,20 @@ class FusedExpertParallel:
         from . import ops
         from .layers.mlp import _grouped_ffn_padded, silu_glu
         plan, own, row_base, pair_peer, pair_row = self._tables(top_indices)
+        inter = w_down_local.shape[2]
+        if w_in_local.shape[1] == 2 * inter and inter % 64 == 0 and own.padded_rows == self.cap:
+            # everything after the tables as one library call on a standing workspace
+            from .layers.mlp import _expert_weight_copies
+            w1c, w1s = _expert_weight_copies(w_in_local if w_in_local.dtype == torch.bfloat16 else w_in_local.to(torch.bfloat16), "glu")
+            w2c, w2s = _expert_weight_copies(w_down_local if w_down_local.dtype == torch.bfloat16 else w_down_local.to(torch.bfloat16), "rows")
+            need = ops.moe_ep_forward_workspace_bytes(self.cap, inter)
+            if self._ws is None or self._ws.numel() < need:
+                self._ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+            out = ops.moe_ep_forward(x.to(torch.bfloat16), top_weights, plan, own, row_base, pair_peer, pair_row, self.e_local, self.rank,
+                                     self._epoch, self.codes_ptrs, self.sf_ptrs, self.y_ptrs, self.flag_ptrs, w1c, w1s, w2c, w2s, inter,
+                                     self._ws)
+            self._epoch += 3
+            return out.to(x.dtype)
         ops.moe_zero_pad_rows(own, self.d, self.codes, self.sf)
         ops.moe_dispatch_peers(x.to(torch.bfloat16), plan, row_base, self.e_local, self.codes_ptrs, self.sf_ptrs)
         self._rendezvous()

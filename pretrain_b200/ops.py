@@ -656,6 +656,36 @@ def moe_ep_index(all_offs: torch.Tensor, rank: int, top_indices: torch.Tensor, p
     return row_base, own_offs, pair_peer, pair_row
 
 
+def moe_ep_forward_workspace_bytes(own_padded_rows: int, inter: int) -> int:
+    return int(_lib.load().b200q_moe_ep_forward_workspace_bytes(own_padded_rows, inter))
+
+
+def moe_ep_forward(x: torch.Tensor, top_weights: torch.Tensor, plan: MoEPlan, own: MoEPlan, row_base: torch.Tensor, pair_peer: torch.Tensor,
+                   pair_row: torch.Tensor, experts_per_rank: int, rank: int, epoch: int, codes_ptrs, sf_ptrs, y_ptrs, flag_ptrs,
+                   w1_codes: torch.Tensor, w1_sf: torch.Tensor, w2_codes: torch.Tensor, w2_sf: torch.Tensor, inter: int,
+                   workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """The expert-parallel forward after the index tables as one library call (b200q_moe_ep_forward): pad rows zeroed,
+    dispatch into the owners' buffers, rendezvous, both grouped GEMMs over the experts this rank owns, rendezvous, combine,
+    rendezvous (epochs epoch + 1 .. epoch + 3).  Returns out (T, D) bf16."""
+    lib = _lib.load()
+    x = _mat(x)
+    t, d = x.shape
+    k = top_weights.shape[1]
+    w = top_weights.to(torch.bfloat16).contiguous()
+    need = lib.b200q_moe_ep_forward_workspace_bytes(own.padded_rows, inter)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    out = torch.empty(t, d, dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.b200q_moe_ep_forward(x.data_ptr(), x.stride(0), w.data_ptr(), t, k, d, inter, experts_per_rank, len(codes_ptrs), rank, epoch,
+                                        plan.src_of_row.data_ptr(), plan.tile_expert.data_ptr(), plan.padded_offs.data_ptr(),
+                                        plan.num_tiles.data_ptr(), plan.padded_rows, row_base.data_ptr(), pair_peer.data_ptr(),
+                                        pair_row.data_ptr(), own.src_of_row.data_ptr(), own.tile_expert.data_ptr(), own.num_tiles.data_ptr(),
+                                        own.padded_rows, _ptr_array(codes_ptrs), _ptr_array(sf_ptrs), _ptr_array(y_ptrs), _ptr_array(flag_ptrs),
+                                        w1_codes.data_ptr(), w1_sf.data_ptr(), w2_codes.data_ptr(), w2_sf.data_ptr(), out.data_ptr(),
+                                        workspace.data_ptr(), _stream()), "b200q_moe_ep_forward")
+    return out
+
+
 def peer_barrier(flag_ptrs, rank: int, epoch: int):
     """Stream-ordered rendezvous of the ranks through flag words in peer-mapped memory (bounded wait)."""
     _lib.check(_lib.load().b200q_peer_barrier(_ptr_array(flag_ptrs), len(flag_ptrs), rank, epoch, _stream()), "b200q_peer_barrier")
