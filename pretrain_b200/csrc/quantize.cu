@@ -739,58 +739,50 @@ int launch_mx_tile_quant(const TileSrc& src, bool aligned_src, int64_t rows, int
 }
 
 // ------------------------------------------------------------------------------------------
-// Per-column FP8 codes (transposed output) given the column scales, on the tile structure of
-// mx_tile_quant_kernel: 128 x 128 tile staged with 32-byte loads, a thread takes two adjacent
-// columns x 32 rows as packed bf16 pairs (32 four-byte shared-memory loads), the codes go back
-// through the same memory as 128-byte rows of the transposed matrix.  The arithmetic is the
-// scaled-FP8 one (a division by the fp32 scale: hoisted reciprocal + one correction).
+// Per-column FP8 / int8 codes (transposed output) given the column scales.  The scales are known, so no thread needs to
+// own a column: a 128 x 128 tile per CTA, warp w takes the tile's columns [16 w, 16 w + 16) (32 bytes of every row),
+// lane l its rows 4 l .. 4 l + 3 straight from global memory (four 32-byte loads in flight per thread; the eight warps
+// together read whole 256-byte row segments).  The four codes a thread makes for one column are one 32-bit word of that
+// column's row in the staging tile (lanes = consecutive words: no bank conflicts), and the tile leaves as 128-byte rows
+// of the transposed matrix.  One pass through shared memory and one barrier, where staging the input as well took
+// three passes and three barriers.  The arithmetic is the scaled-FP8 one (division by the fp32 scale: hoisted reciprocal
+// + one correction); a column's scale and reciprocal are made by one lane and handed round by shuffles.
 // rows % 32 == 0, cols % 32 == 0; other shapes use transpose_quant_kernel.
 // ------------------------------------------------------------------------------------------
+constexpr int kColTileSmem = kDT * kDOutPitch;
 template <int FMT, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
 fp8_col_tile_quant_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                           const float* __restrict__ col_scales, uint8_t* __restrict__ codes_c, float qmax) {
   pdl_prologue();
   extern __shared__ __align__(16) uint8_t dual_smem[];
-  uint8_t* tin = dual_smem;
-  uint8_t* tout = dual_smem;                  // written only after every thread has read its columns (barrier below)
-  const int tid = threadIdx.x;
+  uint8_t* tout = dual_smem;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t c0 = (int64_t)blockIdx.x * kDT, r0 = (int64_t)blockIdx.y * kDT;
+  const int64_t gc = c0 + 16 * warp, gr = r0 + 4 * lane;
+  const bool live = gc < cols && gr < rows;          // whole groups of 16 columns and of 4 rows are in or out
 
+  uint4 v[4][2];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int item = i * kThreads + tid, r = item >> 2, q = item & 3;     // 4 runs of 32 per tile row
-    const int64_t gr = r0 + r, gc = c0 + q * 32;
-    uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-    if (gr < rows && gc < cols) {
-      const uint16_t* xp = x + gr * ld + gc;
-      ld_nc_32B<WIDE>(xp, v[0], v[1]);
-      ld_nc_32B<WIDE>(xp + 16, v[2], v[3]);
-    }
-    uint4* dst = reinterpret_cast<uint4*>(tin + r * kDPitch + q * 64);
-    dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; dst[3] = v[3];
+  for (int i = 0; i < 4; ++i) {
+    v[i][0] = v[i][1] = make_uint4(0, 0, 0, 0);
+    if (live) ld_nc_32B<WIDE>(x + (gr + i) * ld + gc, v[i][0], v[i][1]);
   }
-  __syncthreads();
-
-  {
-    const int cp = tid & 63, j = tid >> 6;            // column pair, block of 32 rows
-    const uint32_t* col = reinterpret_cast<const uint32_t*>(tin + (32 * j) * kDPitch) + cp;
-    uint32_t w[32];
+  const int64_t my_col = gc + (lane & 15);
+  const float my_scale = my_col < cols ? __ldcg(col_scales + my_col) : 1.f;
+  const float my_rcp = rcp_rn(my_scale);
+  uint32_t* dst = reinterpret_cast<uint32_t*>(tout + (16 * warp) * kDOutPitch) + lane;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) w[i] = col[i * (kDPitch / 4)];
-    __syncthreads();                            // all column reads done: the tile may be overwritten
-    const int64_t gc = c0 + 2 * cp;
-    const float s0 = gc < cols ? __ldcg(col_scales + gc) : 1.f, s1 = gc + 1 < cols ? __ldcg(col_scales + gc + 1) : 1.f;
-    const float rc0 = rcp_rn(s0), rc1 = rcp_rn(s1);
-    uint32_t o0[8], o1[8];
+  for (int j = 0; j < 16; ++j) {
+    const float sc = __shfl_sync(0xffffffffu, my_scale, j), rc = __shfl_sync(0xffffffffu, my_rcp, j);
+    float q[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      o0[i] = cvt_codes_x4(quot_for_cast(bf16lo(w[4 * i]), s0, rc0), quot_for_cast(bf16lo(w[4 * i + 1]), s0, rc0),
-                           quot_for_cast(bf16lo(w[4 * i + 2]), s0, rc0), quot_for_cast(bf16lo(w[4 * i + 3]), s0, rc0), FMT, qmax);
-      o1[i] = cvt_codes_x4(quot_for_cast(bf16hi(w[4 * i]), s1, rc1), quot_for_cast(bf16hi(w[4 * i + 1]), s1, rc1),
-                           quot_for_cast(bf16hi(w[4 * i + 2]), s1, rc1), quot_for_cast(bf16hi(w[4 * i + 3]), s1, rc1), FMT, qmax);
+    for (int i = 0; i < 4; ++i) {
+      const uint4& h = v[i][j >> 3];
+      const uint32_t word = ((j >> 1) & 3) == 0 ? h.x : ((j >> 1) & 3) == 1 ? h.y : ((j >> 1) & 3) == 2 ? h.z : h.w;
+      q[i] = quot_for_cast((j & 1) ? bf16hi(word) : bf16lo(word), sc, rc);
     }
-    tile_park_columns(tout, cp, j, o0, o1);
+    dst[j * (kDOutPitch / 4)] = cvt_codes_x4(q[0], q[1], q[2], q[3], FMT, qmax);
   }
   __syncthreads();
 
@@ -872,8 +864,8 @@ void launch_fp8_cols(const uint16_t* x, int64_t rows, int64_t cols, int64_t ld, 
   const bool wide = rows_32B_aligned(x, ld);
 #define B200Q_TILE(F)                                                                                                        \
   do {                                                                                                                       \
-    if (wide) launch_pdl(fp8_col_tile_quant_kernel<F, true>, dim3(grid), dim3(kThreads), (size_t)(kDualSmem), st, x, rows, cols, ld, col_scales, codes, qmax);      \
-    else launch_pdl(fp8_col_tile_quant_kernel<F, false>, dim3(grid), dim3(kThreads), (size_t)(kDualSmem), st, x, rows, cols, ld, col_scales, codes, qmax);          \
+    if (wide) launch_pdl(fp8_col_tile_quant_kernel<F, true>, dim3(grid), dim3(kThreads), (size_t)(kColTileSmem), st, x, rows, cols, ld, col_scales, codes, qmax);      \
+    else launch_pdl(fp8_col_tile_quant_kernel<F, false>, dim3(grid), dim3(kThreads), (size_t)(kColTileSmem), st, x, rows, cols, ld, col_scales, codes, qmax);          \
   } while (0)
   if (fmt == FMT_I8) B200Q_TILE(FMT_I8);
   else if (fmt == FMT_E4M3) B200Q_TILE(FMT_E4M3);
