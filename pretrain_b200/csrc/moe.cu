@@ -1410,9 +1410,10 @@ int b200q_moe_ep_forward(const void* x, int64_t ldx, const void* top_w, int64_t 
       row_base == nullptr || pair_peer == nullptr || pair_row == nullptr || own_src_of_row == nullptr || own_tile_expert == nullptr ||
       own_num_tiles == nullptr || peer_codes == nullptr || peer_sf == nullptr || peer_y == nullptr || flag_ptrs == nullptr ||
       w1_codes == nullptr || w1_sf == nullptr || w2_codes == nullptr || w2_sf == nullptr || out == nullptr || workspace == nullptr ||
-      T <= 0 || k <= 0 || experts_per_rank <= 0 || world <= 0 || rank < 0 || rank >= world)
+      T <= 0 || k <= 0 || D <= 0 || I <= 0 || padded_rows <= 0 || own_padded_rows <= 0 || experts_per_rank <= 0 || world <= 0 ||
+      rank < 0 || rank >= world)
     return B200Q_ERR_INVALID_ARG;
-  if ((D & 127) || (I & 63) || ((2 * I) & 127)) return B200Q_ERR_SHAPE;
+  if ((D & 127) || (I & 63) || ((2 * I) & 127) || (own_padded_rows & 127)) return B200Q_ERR_SHAPE;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return B200Q_ERR_ALIGNMENT;
   uint8_t* h = static_cast<uint8_t*>(workspace);
   uint8_t* h_sf = h + ws_align(own_padded_rows * I);

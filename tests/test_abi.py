@@ -52,6 +52,24 @@ def test_host_only_entry_points(lib_path):
     assert lib.b200q_amax(None, 4, 8, 8, None, None) == -1
     assert lib.b200q_quantize_mxfp8(ctypes.c_void_p(16), 4, 12, 16, 1, 0, ctypes.c_void_p(16), ctypes.c_void_p(16), 1, None) == -2
     assert lib.b200q_quantize_mxfp8(ctypes.c_void_p(8), 4, 32, 32, 1, 0, ctypes.c_void_p(16), ctypes.c_void_p(16), 1, None) == -3
+    # the composed entry points: workspace sizes are pure functions, and bad shapes / null pointers are refused up front
+    p = ctypes.c_void_p(256)
+    assert lib.b200q_moe_ffn_workspace_bytes(0, 4, 768, 64, 384) == 0
+    assert lib.b200q_moe_ffn_workspace_bytes(16384, 4, 768, 64, 384) % 256 == 0 and lib.b200q_moe_ffn_workspace_bytes(16384, 4, 768, 64, 384) > 0
+    assert lib.b200q_moe_ffn_forward(None, 768, p, p, 128, 4, 768, 8, 384, p, p, p, p, p, None, p, None) == -1
+    assert lib.b200q_moe_ffn_forward(p, 768, p, p, 128, 4, 760, 8, 384, p, p, p, p, p, None, p, None) == -2       # D % 128
+    assert lib.b200q_moe_ffn_forward(p, 768, p, p, 128, 4, 768, 8, 384, p, p, p, p, p, None, ctypes.c_void_p(128), None) == -3
+    assert lib.b200q_moe_ep_forward_workspace_bytes(0, 384) == 0
+    need = lib.b200q_moe_ep_forward_workspace_bytes(1024, 384)
+    assert need >= 1024 * 384 + lib.b200q_sf_bytes(1024, 12, 1) and need % 256 == 0
+    ptrs = (ctypes.c_void_p * 2)(256, 512)
+    ep_args = [p, 768, p, 128, 4, 768, 384, 4, 2, 0, 0, p, p, p, p, 1024, p, p, p, p, p, p, 1024, ptrs, ptrs, ptrs, ptrs, p, p, p, p, p, p, None]
+    bad_rank = list(ep_args); bad_rank[9] = 2
+    assert lib.b200q_moe_ep_forward(*bad_rank) == -1
+    bad_rows = list(ep_args); bad_rows[22] = 1000                     # rows of the receive buffers: whole 128-row tiles
+    assert lib.b200q_moe_ep_forward(*bad_rows) == -2
+    bad_inter = list(ep_args); bad_inter[6] = 96
+    assert lib.b200q_moe_ep_forward(*bad_inter) == -2
 
 
 def test_ops_refuse_cpu_tensors(lib_path):
