@@ -901,7 +901,7 @@ int b200q_gemm_nvfp4_swiglu(const void* A, const void* sfA, const void* B, const
   int rc = require_sm100();
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  B200Q_CUDA(memset_async(amax_out, 0, sizeof(float), st));
+  B200Q_CUDA(zero_before_kernel(amax_out, sizeof(float), st));
   GemmParams p = {};
   p.sfa = (const uint8_t*)sfA; p.sfb = (const uint8_t*)sfB; p.scale_a = tsA; p.scale_b = tsB;
   p.M = M; p.N = N; p.K = K;

@@ -1126,7 +1126,7 @@ int b200q_moe_router_topk(const float* logits, int64_t T, int E, int k, int scor
   int rc = require_sm100();
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  if (expert_counts != nullptr) B200Q_CUDA(memset_async(expert_counts, 0, (size_t)E * sizeof(int32_t), st));
+  if (expert_counts != nullptr) B200Q_CUDA(zero_before_kernel(expert_counts, (size_t)E * sizeof(int32_t), st));
 #define B200Q_GO(P)                                                                                                          \
   do {                                                                                                                       \
     if (select_bias != nullptr)                                                                                              \

@@ -918,7 +918,7 @@ int b200q_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, float* ama
   if (amax == nullptr) return B200Q_ERR_INVALID_ARG;
   if ((rc = require_sm100())) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  B200Q_CUDA(memset_async(amax, 0, sizeof(float), st));
+  B200Q_CUDA(zero_before_kernel(amax, sizeof(float), st));
   launch_pdl(amax_kernel, dim3(rowwise_grid(amax_kernel, rows * ((cols + 1023) / 1024), kWarps)), dim3(kThreads), (size_t)(0), st, (const uint16_t*)x, rows, cols, ld, amax);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
@@ -966,7 +966,7 @@ int b200q_quantize_fp8(const void* x, int64_t rows, int64_t cols, int64_t ld, in
   cudaStream_t st = (cudaStream_t)stream;
   if (axis == 1) return launch_rowwise_fp8((const uint16_t*)x, rows, cols, ld, fmt, (uint8_t*)codes, scales, nullptr, nullptr, st);
   if (rows & 15) return B200Q_ERR_SHAPE;
-  B200Q_CUDA(memset_async(scales, 0, (size_t)cols * sizeof(float), st));
+  B200Q_CUDA(zero_before_kernel(scales, (size_t)cols * sizeof(float), st));
   {
     dim3 grid((unsigned)((cols / 8 + 31) / 32), 1);
     int64_t ymax = (rows + kWarps * 4 - 1) / (kWarps * 4);
@@ -1044,7 +1044,7 @@ int b200q_quantize_int8(const void* x, int64_t rows, int64_t cols, int64_t ld, i
   if (axis == 1)
     return launch_rowwise_fp8((const uint16_t*)x, rows, cols, ld, FMT_I8, (uint8_t*)codes, scales, nullptr, nullptr, st, (float)qmax);
   if (rows & 15) return B200Q_ERR_SHAPE;
-  B200Q_CUDA(memset_async(scales, 0, (size_t)cols * sizeof(float), st));
+  B200Q_CUDA(zero_before_kernel(scales, (size_t)cols * sizeof(float), st));
   {
     dim3 grid((unsigned)((cols / 8 + 31) / 32), 1);
     int64_t ymax = (rows + kWarps * 4 - 1) / (kWarps * 4);
