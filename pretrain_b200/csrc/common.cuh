@@ -135,18 +135,21 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 // point's launch chain instead, and triggers its dependents at once - allowed by the first rule above, because every
 // caller launches an attributed kernel, which waits, directly behind it - so that kernel's CTAs are resident and
 // waiting by the time the words are zero.
-static __global__ void zero_words_kernel(uint32_t* __restrict__ p, int64_t n, int trigger_early) {
+static __global__ void fill_words_kernel(uint32_t* __restrict__ p, int64_t n, uint32_t word, int trigger_early) {
   if (trigger_early) grid_launch_dependents();
   grid_dependency_wait();
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = 0u;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = word;
 }
-// `bytes` zeroed ahead of a kernel launch of the same entry point (the caller MUST launch a kernel next).
-inline cudaError_t zero_before_kernel(void* p, size_t bytes, cudaStream_t st) {
-  if ((bytes & 3) || (reinterpret_cast<uintptr_t>(p) & 3) || bytes > (1u << 20)) return memset_async(p, 0, bytes, st);
+// `bytes` set to `value` (a byte, as for memset) ahead of a kernel launch of the same entry point: the caller MUST launch a
+// kernel next.  Up to 1 MiB; larger or unaligned ranges go to cudaMemsetAsync.
+inline cudaError_t fill_before_kernel(void* p, int value, size_t bytes, cudaStream_t st) {
+  if ((bytes & 3) || (reinterpret_cast<uintptr_t>(p) & 3) || bytes > (1u << 20)) return memset_async(p, value, bytes, st);
   const int64_t n = (int64_t)(bytes >> 2);
   const int grid = (int)((n + 255) / 256 < 64 ? (n + 255) / 256 : 64);
-  return launch_pdl(zero_words_kernel, dim3(grid), dim3(256), (size_t)0, st, reinterpret_cast<uint32_t*>(p), n, pdl_mode() == 1 ? 1 : 0);
+  const uint32_t word = 0x01010101u * (uint32_t)(value & 0xFF);
+  return launch_pdl(fill_words_kernel, dim3(grid), dim3(256), (size_t)0, st, reinterpret_cast<uint32_t*>(p), n, word, pdl_mode() == 1 ? 1 : 0);
 }
+inline cudaError_t zero_before_kernel(void* p, size_t bytes, cudaStream_t st) { return fill_before_kernel(p, 0, bytes, st); }
 
 __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
   uint4 v;

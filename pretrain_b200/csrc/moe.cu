@@ -1151,7 +1151,7 @@ int b200q_moe_pair_of_row(const int32_t* row_of, int64_t n_pairs, int64_t padded
   int rc = require_sm100();
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  B200Q_CUDA(memset_async(pair_of_row, 0xff, (size_t)padded_rows * sizeof(int32_t), st));      // -1 everywhere
+  B200Q_CUDA(fill_before_kernel(pair_of_row, 0xff, (size_t)padded_rows * sizeof(int32_t), st));      // -1 everywhere
   launch_pdl(moe_pair_of_row_kernel, dim3((unsigned)((n_pairs + 255) / 256)), dim3(256), (size_t)(0), st, row_of, n_pairs, padded_rows, pair_of_row);
   B200Q_CUDA(cudaGetLastError());
   return B200Q_OK;
