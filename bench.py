@@ -219,7 +219,8 @@ def make_step(kind, a, b, out):
         ev()                                        # end of the GEMM
         return out
 
-    launches = {"mxfp8": 3, "nvfp4": 5, "fp8": 3, "int8": 3}[kind]
+    # nvfp4: each tensor maximum is two kernels (the kernel that zeroes its word, then the reduction)
+    launches = {"mxfp8": 3, "nvfp4": 7, "fp8": 3, "int8": 3}[kind]
     return step, launches
 
 
@@ -584,7 +585,9 @@ def run_moe_training(args, t, d, inter, rank, world, local):
             "clocks": clocks,
             "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": (hx.numel() + hd.numel()) * 2, "d2h_bytes_per_step": hgx.numel() * 2},
-            "gpu_launches": 24 * args.steps,
+            # plan 2, forward 5, backward 10 (fill + pair table 2, dy both ways + its dot partials 2, two dgrads, two wgrads,
+            # SwiGLU backward, scatter to tokens), the two weight stacks 2: counted in an ncu launch list of this workload
+            "gpu_launches": 19 * args.steps,
             "roofline": roofline_tensor("whole step (6 grouped GEMMs and the HBM-bound kernels between them)", flops, ms_step, 2.0, 4500.0,
                                         ms_step * args.steps * 1e-3, clocks, peaks)}
     if graph is not None:
