@@ -632,7 +632,8 @@ def run_composite(args, kind, d0, d1, d2, rank, world, local):
             out = ops.gemm_nvfp4(ph, sh, th, pd, sd, td)
             ev(None, 0)
             return out
-        launches, dtype, peak_ratio, nominal = 11, "nvfp4", 4.0, 9000.0
+        # x, w_gu and w_d: zero + tensor maximum + quantize each (9); GEMM 1: zero of its maximum + GEMM (2); h: quantize (1); GEMM 2 (1)
+        launches, dtype, peak_ratio, nominal = 13, "nvfp4", 4.0, 9000.0
         desc = {"tokens_per_gpu": t, "hidden": h, "intermediate": inter}
     else:
         m, n, k = d0, d1, d2
