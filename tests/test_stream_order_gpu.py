@@ -65,3 +65,23 @@ def test_a_memset_inside_an_entry_point_is_ordered(ops):
         assert amax.item() == h.float().abs().max().item(), rep
         want_codes, want_scales = R.quantize_fp8(h, e4, dim=0)
         assert torch.equal(scales.cpu(), want_scales.reshape(-1)), rep
+
+
+def test_a_copy_right_behind_an_entry_point_that_zeroes_by_kernel(ops):
+    """The tensor maximum and the per-column scales are accumulated with atomics into words that a one-CTA kernel zeroes
+    first; that kernel lets its successor be scheduled at once.  A device copy (or a read-back) enqueued directly behind
+    the entry point must still see the finished result."""
+    e4 = torch.float8_e4m3fn
+    keep = []
+    for rep in range(REPS):
+        h = _inputs(rep, 4096, 1024)
+        x = h.cuda()
+        got = ops.amax(x).clone()                                        # device copy right behind the reduction
+        back = ops.amax(x).cpu()                                         # and a read-back right behind another
+        scales = ops.quantize_fp8(x, e4, 0)[1].clone()
+        keep.append((h, got, back, scales))
+    torch.cuda.synchronize()
+    for rep, (h, got, back, scales) in enumerate(keep):
+        want = h.float().abs().max().item()
+        assert got.item() == want and back.item() == want, rep
+        assert torch.equal(scales.cpu(), R.quantize_fp8(h, e4, dim=0)[1].reshape(-1)), rep
