@@ -235,7 +235,7 @@ __device__ __forceinline__ QuotScale quot_scale(float b, float r) {
   return s;
 }
 __device__ __forceinline__ void quot2_for_cast(uint32_t w, const QuotScale& s, float& q_lo, float& q_hi) {
-  const uint64_t na = pack_f32x2((w << 16) + 0x80000000u, (w & 0xFFFF0000u) ^ 0x80000000u);
+  const uint64_t na = pack_f32x2(neg_bf16lo_bits(w), neg_bf16hi_bits(w));     // per lane: quot_for_cast_negated()
   uint64_t q, e;
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q) : "l"(na), "l"(s.nr2));
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(e) : "l"(s.b2), "l"(q), "l"(na));

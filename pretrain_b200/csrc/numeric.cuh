@@ -112,6 +112,19 @@ B200Q_HD float quot_for_cast(float a, float b, float r) {
   return fma_rn(e, -r, q);   // negate the reciprocal, not e: no compiler may fold that into e's fma
 }
 
+// The same quotient from the NEGATED operand and the negated reciprocal, which is how the packed fp32 pair form in
+// common.cuh computes it: q = (-a)(-r), e = b q + (-a), q' = e (-r) + q are the three operations above with the
+// signs moved into the operands, so the bits are the same (the host check walks every bf16 a, unpacked negated from
+// either half of a word as the kernel does, against quot_for_cast).
+B200Q_HD float quot_for_cast_negated(float na, float b, float nr) {
+  float q = mul_rn(na, nr);
+  float e = fma_rn(b, q, na);
+  return fma_rn(e, nr, q);
+}
+// bits of -x for the bf16 x in the low / high half of a word
+B200Q_HD uint32_t neg_bf16lo_bits(uint32_t w) { return (w << 16) + 0x80000000u; }
+B200Q_HD uint32_t neg_bf16hi_bits(uint32_t w) { return (w & 0xFFFF0000u) ^ 0x80000000u; }
+
 // scale = max(amax / qmax, 1e-12)   (src/quant/fp8.py:30)
 B200Q_HD float fp8_scale_from_amax(float amax, int fmt) {
   float s = div_rn(amax, fp8_max(fmt));

@@ -60,6 +60,37 @@ void hc_div_random_fp4(int64_t count, uint64_t seed, int64_t* out) {
   out[0] = bad_code; out[1] = bad_f32;
 }
 
+// The packed-pair form of the quotient (common.cuh: quot2_for_cast) works on operands unpacked NEGATED from the two
+// halves of a word.  Every bf16 bit pattern in either half, `n_scales` scales (bf16-derived FP8 scales and random
+// fp32 ones): same bits as quot_for_cast on the plainly unpacked value (NaN for NaN).  out[0] = mismatches, out[1] = cases
+void hc_negated_quotient(int n_scales, uint64_t seed, int64_t* out) {
+  int64_t bad = 0, n = 0;
+  uint64_t s = seed * 6364136223846793005ull + 1442695040888963407ull;
+  for (int i = 0; i < n_scales; ++i) {
+    s = s * 6364136223846793005ull + 1442695040888963407ull;
+    float b;
+    if (i & 1) {
+      const int ee = (int)((s >> 40) % 86) - 45;
+      b = u2f(((uint32_t)(ee + 127) << 23) | (uint32_t)((s >> 8) & 0x7FFFFFu));
+    } else {
+      b = fp8_scale_from_amax(bf((uint16_t)(1 + (s >> 33) % 0x7F7Fu)), i & 2 ? FMT_E5M2 : FMT_E4M3);
+    }
+    const float r = rcp_rn(b);
+    for (uint32_t xb = 0; xb < 0x10000u; ++xb) {
+      const uint32_t other = (uint32_t)(s >> 13) & 0xFFFFu;
+      const uint32_t w_lo = xb | (other << 16), w_hi = (xb << 16) | other;
+      const float x = u2f(xb << 16);
+      const float want = quot_for_cast(x, b, r);
+      const float got_lo = quot_for_cast_negated(u2f(neg_bf16lo_bits(w_lo)), b, -r);
+      const float got_hi = quot_for_cast_negated(u2f(neg_bf16hi_bits(w_hi)), b, -r);
+      ++n;
+      if (want != want) { if (got_lo == got_lo || got_hi == got_hi) ++bad; continue; }
+      if (f2u(want) != f2u(got_lo) || f2u(want) != f2u(got_hi)) ++bad;
+    }
+  }
+  out[0] = bad; out[1] = n;
+}
+
 // The fp4 cast can only differ where the quotient is within an fp32 ulp of a rounding
 // boundary of E2M1, so walk exactly those: for every block scale byte and every `stride`-th
 // tensor scale derived from a bf16 maximum (plus `extra` random fp32 tensor scales), the

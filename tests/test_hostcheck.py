@@ -53,6 +53,12 @@ def test_division_by_hoisted_reciprocal_is_exact(hc, fmt, dt):
     assert out[2] > 4e7 and out[0] == 0 and out[1] == 0
 
 
+def test_packed_pair_quotient_on_negated_operands_gives_the_same_bits(hc):
+    out = (ctypes.c_int64 * 2)()
+    hc.hc_negated_quotient(400, ctypes.c_uint64(11), out)
+    assert out[1] == 400 * 65536 and out[0] == 0
+
+
 def test_division_random_fp4(hc):
     out = (ctypes.c_int64 * 3)()
     hc.hc_div_random_fp4(ctypes.c_int64(20_000_000), ctypes.c_uint64(7), out)
